@@ -1,0 +1,133 @@
+/*
+ * b200_ttperf.h — C ABI of the B200 (sm_100a) implementation of tt-perf's dense-matmul hot path.
+ *
+ * tt-perf's C++ executors (autograd/dynamic, autograd/static, autograd/traced) do all their
+ * arithmetic through the TTNN op library: `ttnn::matmul`, `ttnn::linear`, element-wise ops,
+ * row reductions, `ttnn::softmax`, `ttnn::embedding`, plus `ttnn::all_gather` for the sharded
+ * matmul. This header declares the plain-C entry points those ops forward to; the C++ header
+ * shim under include/ttnn/ and the ctypes binding in the Python package are both written on
+ * top of exactly these functions. Each declaration cites the reference interface it stands
+ * in for (paths are relative to the tt-perf tree).
+ *
+ * Conventions
+ *  - every function returns a b200_status code (0 = success); b200_last_error() gives the text
+ *    of the calling thread's last failure. No function throws, aborts or prints.
+ *  - pointers named `d_*`, A, B, C, x, y ... are DEVICE pointers unless the comment says host.
+ *  - `stream` is a cudaStream_t passed as void* (NULL = the context's own stream). Calls are
+ *    asynchronous and in order on that stream, like ops on a TTNN command queue.
+ *  - matrices are row-major with an explicit leading dimension in ELEMENTS; bf16 is the
+ *    16-bit brain float stored as uint16_t bit patterns.
+ *  - there is no CPU fallback: with no usable sm_100 device every compute call fails with
+ *    B200_ERR_CUDA.
+ */
+#ifndef B200_TTPERF_H
+#define B200_TTPERF_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define B200_TTPERF_ABI_VERSION 1
+
+typedef enum b200_status {
+    B200_OK = 0,
+    B200_ERR_INVALID_ARG = 1,    /* null pointer, negative size, bad enum, misaligned operand */
+    B200_ERR_CUDA = 2,           /* a CUDA runtime/driver call failed (text in b200_last_error) */
+    B200_ERR_UNSUPPORTED = 3,    /* valid request this build cannot serve */
+    B200_ERR_DEVICE_TIMEOUT = 4, /* a kernel's bounded wait ran out; results of that launch are invalid */
+    B200_ERR_NOMEM = 5,          /* device arena / workspace exhausted */
+    B200_ERR_COMM = 6            /* collective layer (NCCL) failure */
+} b200_status;
+
+typedef enum b200_dtype { B200_BF16 = 0, B200_F32 = 1, B200_U32 = 2 } b200_dtype;
+
+/* Fused activations of ttnn::linear / ttnn::matmul (static/nn.hpp:145-146, bench/metal/bench_fusion.cpp:119). */
+typedef enum b200_activation { B200_ACT_NONE = 0, B200_ACT_RELU = 1, B200_ACT_GELU = 2 } b200_activation;
+
+/* MathFidelity of WormholeComputeKernelConfig (verify/verify_fidelity.cpp:50-55). On tcgen05 the
+ * accumulator is always fp32; the knob selects the precision of split-K partial sums and of the
+ * epilogue math: HIFI4/HIFI3 fp32 partials + exact erf GELU; HIFI2 bf16-rounded partials; LOFI
+ * bf16-rounded partials + tanh-approximated GELU. */
+typedef enum b200_fidelity { B200_LOFI = 0, B200_HIFI2 = 1, B200_HIFI3 = 2, B200_HIFI4 = 3 } b200_fidelity;
+
+typedef enum b200_gemm_algo {
+    B200_GEMM_AUTO = 0,    /* tcgen05 when operands meet the TMA alignment rules, else SIMT */
+    B200_GEMM_TCGEN05 = 1, /* TMA + tcgen05.mma + TMEM; fails with INVALID_ARG on misaligned operands */
+    B200_GEMM_SIMT = 2     /* CUDA-core tiled kernel: any alignment, any leading dimension */
+} b200_gemm_algo;
+
+typedef struct b200_ctx b200_ctx; /* one per (process, GPU): device ordinal, stream, scratch, status word */
+
+/* ---- context / device (MeshDevice::create_unit_mesh, autograd/common.hpp:31-37; Finish / Synchronize,
+ *      examples/train_mlp.cpp:129, bench/autograd/bench_mlp.cpp:119) ---------------------------------- */
+int b200_ctx_create(int device_ordinal, b200_ctx** out_ctx);
+int b200_ctx_destroy(b200_ctx* ctx);
+int b200_ctx_device(const b200_ctx* ctx, int* out_device_ordinal);
+int b200_ctx_sm_count(const b200_ctx* ctx, int* out_sm_count);
+/* Blocks until all work queued on `stream` has finished, then reports a kernel wait that timed out
+ * since the last call as B200_ERR_DEVICE_TIMEOUT (and clears it). */
+int b200_synchronize(b200_ctx* ctx, void* stream);
+const char* b200_last_error(void);
+int b200_abi_version(void);
+
+/* ---- device memory (Tensor::to_device / .cpu() / .deallocate(), traced/nn.hpp:46-47, common.hpp:53) - */
+int b200_malloc(b200_ctx* ctx, size_t bytes, void** out_dptr);
+int b200_free(b200_ctx* ctx, void* dptr);
+int b200_memcpy_h2d(b200_ctx* ctx, void* d_dst, const void* h_src, size_t bytes, void* stream);
+int b200_memcpy_d2h(b200_ctx* ctx, void* h_dst, const void* d_src, size_t bytes, void* stream);
+int b200_memset(b200_ctx* ctx, void* d_dst, int byte_value, size_t bytes, void* stream);
+
+/* ---- dense matmul: ttnn::matmul(a, b, transpose_a, transpose_b, ..., activation, compute_kernel_config)
+ *      (dynamic/ops.hpp:21-46, static/ops.hpp:21-45, traced/ops.hpp:26-36) and
+ *      ttnn::linear(x, w, bias, ta, tb, ..., "relu") (static/nn.hpp:145-146) --------------------------
+ *
+ *   C[b] = act( mask( alpha * op(A[b]) . op(B[b]) + bias ) )          b = 0 .. batch-1
+ *
+ *   op(A) is M x K: A is stored [M, K] (transpose_a = 0) or [K, M] (transpose_a = 1), leading dim lda.
+ *   op(B) is K x N: B is stored [K, N] (transpose_b = 0) or [N, K] (transpose_b = 1), leading dim ldb.
+ *   stride_a / stride_b / stride_c: elements between consecutive batch entries; 0 broadcasts an
+ *   operand over the batch (rank-2 weight against [B,S,D] activations, traced/transformer.hpp:198).
+ *   bias: optional [N] row vector broadcast over rows ([1,N] bias add, traced/nn.hpp:73).
+ *   causal_mask: entries with column > row are replaced by mask_value before the activation
+ *   (the -1e9 upper-triangular mask of traced/nn.hpp:158-168, fused with the 1/sqrt(dh) scale = alpha).
+ *   Inputs bf16, accumulation fp32, output bf16 or fp32 (fp32_dest_acc_en / K-split partial sums).
+ */
+typedef struct b200_gemm_desc {
+    int32_t transpose_a;
+    int32_t transpose_b;
+    int64_t M, N, K;
+    int64_t batch; /* >= 1 */
+    const void* A;
+    int64_t lda;
+    int64_t stride_a;
+    const void* B;
+    int64_t ldb;
+    int64_t stride_b;
+    void* C;
+    int64_t ldc;
+    int64_t stride_c;
+    int32_t c_dtype;    /* B200_BF16 or B200_F32 */
+    const void* bias;   /* NULL or [N] */
+    int32_t bias_dtype; /* B200_BF16 or B200_F32 */
+    int32_t activation; /* b200_activation */
+    float alpha;
+    int32_t causal_mask;
+    float mask_value;
+    int32_t fidelity; /* b200_fidelity */
+    int32_t algo;     /* b200_gemm_algo */
+    int32_t split_k;  /* 0 = choose; 1 = never split; n > 1 = split K into n slices (fp32 scratch + reduce) */
+} b200_gemm_desc;
+
+/* Fills a descriptor with defaults: no transposes, batch 1, alpha 1, bf16 output, HIFI4, AUTO. */
+void b200_gemm_desc_init(b200_gemm_desc* desc);
+int b200_gemm(b200_ctx* ctx, const b200_gemm_desc* desc, void* stream);
+/* Bytes of context scratch the split-K path of this descriptor will use (0 when it does not split). */
+int b200_gemm_scratch_bytes(b200_ctx* ctx, const b200_gemm_desc* desc, size_t* out_bytes);
+
+#ifdef __cplusplus
+} /* extern "C" */
+#endif
+#endif /* B200_TTPERF_H */

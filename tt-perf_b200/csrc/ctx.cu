@@ -1,0 +1,196 @@
+// Context, error text and raw device-memory entry points of the C ABI.
+#include <stdarg.h>
+
+#include "common.cuh"
+
+namespace b200 {
+
+static thread_local std::string g_last_error;
+
+void set_error(const char* fmt, ...) {
+    char buf[1024];
+    va_list ap;
+    va_start(ap, fmt);
+    vsnprintf(buf, sizeof(buf), fmt, ap);
+    va_end(ap);
+    g_last_error = buf;
+}
+
+int fail(int code, const char* fmt, ...) {
+    char buf[1024];
+    va_list ap;
+    va_start(ap, fmt);
+    vsnprintf(buf, sizeof(buf), fmt, ap);
+    va_end(ap);
+    g_last_error = buf;
+    return code;
+}
+
+int ensure_scratch(b200_ctx* ctx, size_t bytes) {
+    if (bytes <= ctx->scratch_bytes) return B200_OK;
+    DeviceScope scope(ctx->device);
+    // Round up so that a sweep over growing shapes reallocates rarely.
+    size_t want = (bytes + (size_t(64) << 20) - 1) & ~((size_t(64) << 20) - 1);
+    if (ctx->d_scratch) {
+        B200_CUDA_TRY(cudaDeviceSynchronize());
+        B200_CUDA_TRY(cudaFree(ctx->d_scratch));
+        ctx->d_scratch = nullptr;
+        ctx->scratch_bytes = 0;
+    }
+    cudaError_t e = cudaMalloc(&ctx->d_scratch, want);
+    if (e != cudaSuccess) {
+        cudaGetLastError();
+        return fail(B200_ERR_NOMEM, "scratch allocation of %zu bytes failed: %s", want, cudaGetErrorString(e));
+    }
+    ctx->scratch_bytes = want;
+    return B200_OK;
+}
+
+}  // namespace b200
+
+using namespace b200;
+
+extern "C" {
+
+const char* b200_last_error(void) { return g_last_error.c_str(); }
+
+int b200_abi_version(void) { return B200_TTPERF_ABI_VERSION; }
+
+int b200_ctx_create(int device_ordinal, b200_ctx** out_ctx) {
+    B200_REQUIRE(out_ctx != nullptr, "b200_ctx_create: out_ctx is NULL");
+    *out_ctx = nullptr;
+    int count = 0;
+    cudaError_t e = cudaGetDeviceCount(&count);
+    if (e != cudaSuccess || count == 0) {
+        cudaGetLastError();
+        return fail(B200_ERR_CUDA, "b200_ctx_create: no CUDA device (%s); this library has no CPU path",
+                    e == cudaSuccess ? "device count is 0" : cudaGetErrorString(e));
+    }
+    B200_REQUIRE(device_ordinal >= 0 && device_ordinal < count, "b200_ctx_create: device %d out of range [0,%d)",
+                 device_ordinal, count);
+    cudaDeviceProp prop;
+    B200_CUDA_TRY(cudaGetDeviceProperties(&prop, device_ordinal));
+    if (prop.major != 10) {
+        return fail(B200_ERR_UNSUPPORTED, "b200_ctx_create: device %d is sm_%d%d; the kernels are built for sm_100a only",
+                    device_ordinal, prop.major, prop.minor);
+    }
+    DeviceScope scope(device_ordinal);
+    b200_ctx* ctx = new b200_ctx();
+    ctx->device = device_ordinal;
+    ctx->sm_count = prop.multiProcessorCount;
+    ctx->cc_major = prop.major;
+    ctx->cc_minor = prop.minor;
+    e = cudaStreamCreateWithFlags(&ctx->stream, cudaStreamNonBlocking);
+    if (e != cudaSuccess) {
+        delete ctx;
+        return fail(B200_ERR_CUDA, "cudaStreamCreate failed: %s", cudaGetErrorString(e));
+    }
+    e = cudaMalloc(&ctx->d_status, 256);
+    if (e == cudaSuccess) e = cudaMemset(ctx->d_status, 0, 256);
+    if (e != cudaSuccess) {
+        cudaStreamDestroy(ctx->stream);
+        delete ctx;
+        return fail(B200_ERR_CUDA, "status word allocation failed: %s", cudaGetErrorString(e));
+    }
+    void* fn = nullptr;
+    cudaDriverEntryPointQueryResult qres;
+    e = cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &qres);
+    if (e != cudaSuccess || qres != cudaDriverEntryPointSuccess || fn == nullptr) {
+        cudaGetLastError();
+        cudaFree(ctx->d_status);
+        cudaStreamDestroy(ctx->stream);
+        delete ctx;
+        return fail(B200_ERR_CUDA, "cuTensorMapEncodeTiled is not available from this driver");
+    }
+    ctx->encode_tiled = reinterpret_cast<EncodeTiledFn>(fn);
+    *out_ctx = ctx;
+    return B200_OK;
+}
+
+int b200_ctx_destroy(b200_ctx* ctx) {
+    if (!ctx) return B200_OK;
+    DeviceScope scope(ctx->device);
+    cudaDeviceSynchronize();
+    if (ctx->d_scratch) cudaFree(ctx->d_scratch);
+    if (ctx->d_status) cudaFree(ctx->d_status);
+    if (ctx->stream) cudaStreamDestroy(ctx->stream);
+    delete ctx;
+    return B200_OK;
+}
+
+int b200_ctx_device(const b200_ctx* ctx, int* out) {
+    B200_REQUIRE(ctx && out, "b200_ctx_device: NULL argument");
+    *out = ctx->device;
+    return B200_OK;
+}
+
+int b200_ctx_sm_count(const b200_ctx* ctx, int* out) {
+    B200_REQUIRE(ctx && out, "b200_ctx_sm_count: NULL argument");
+    *out = ctx->sm_count;
+    return B200_OK;
+}
+
+int b200_synchronize(b200_ctx* ctx, void* stream) {
+    B200_REQUIRE(ctx != nullptr, "b200_synchronize: ctx is NULL");
+    DeviceScope scope(ctx->device);
+    B200_CUDA_TRY(cudaStreamSynchronize(ctx->pick(stream)));
+    int status = 0;
+    B200_CUDA_TRY(cudaMemcpy(&status, ctx->d_status, sizeof(int), cudaMemcpyDeviceToHost));
+    if (status != 0) {
+        cudaMemset(ctx->d_status, 0, sizeof(int));
+        return fail(B200_ERR_DEVICE_TIMEOUT, "a kernel gave up a bounded wait (status word %d); its output is invalid",
+                    status);
+    }
+    return B200_OK;
+}
+
+int b200_malloc(b200_ctx* ctx, size_t bytes, void** out_dptr) {
+    B200_REQUIRE(ctx && out_dptr, "b200_malloc: NULL argument");
+    *out_dptr = nullptr;
+    if (bytes == 0) return B200_OK;
+    DeviceScope scope(ctx->device);
+    cudaError_t e = cudaMalloc(out_dptr, bytes);
+    if (e != cudaSuccess) {
+        cudaGetLastError();
+        return fail(B200_ERR_NOMEM, "b200_malloc(%zu) failed: %s", bytes, cudaGetErrorString(e));
+    }
+    return B200_OK;
+}
+
+int b200_free(b200_ctx* ctx, void* dptr) {
+    B200_REQUIRE(ctx != nullptr, "b200_free: ctx is NULL");
+    if (!dptr) return B200_OK;
+    DeviceScope scope(ctx->device);
+    B200_CUDA_TRY(cudaFree(dptr));
+    return B200_OK;
+}
+
+int b200_memcpy_h2d(b200_ctx* ctx, void* d_dst, const void* h_src, size_t bytes, void* stream) {
+    B200_REQUIRE(ctx != nullptr, "b200_memcpy_h2d: ctx is NULL");
+    if (bytes == 0) return B200_OK;
+    B200_REQUIRE(d_dst && h_src, "b200_memcpy_h2d: NULL buffer");
+    DeviceScope scope(ctx->device);
+    B200_CUDA_TRY(cudaMemcpyAsync(d_dst, h_src, bytes, cudaMemcpyHostToDevice, ctx->pick(stream)));
+    return B200_OK;
+}
+
+int b200_memcpy_d2h(b200_ctx* ctx, void* h_dst, const void* d_src, size_t bytes, void* stream) {
+    B200_REQUIRE(ctx != nullptr, "b200_memcpy_d2h: ctx is NULL");
+    if (bytes == 0) return B200_OK;
+    B200_REQUIRE(h_dst && d_src, "b200_memcpy_d2h: NULL buffer");
+    DeviceScope scope(ctx->device);
+    B200_CUDA_TRY(cudaMemcpyAsync(h_dst, d_src, bytes, cudaMemcpyDeviceToHost, ctx->pick(stream)));
+    B200_CUDA_TRY(cudaStreamSynchronize(ctx->pick(stream)));
+    return B200_OK;
+}
+
+int b200_memset(b200_ctx* ctx, void* d_dst, int byte_value, size_t bytes, void* stream) {
+    B200_REQUIRE(ctx != nullptr, "b200_memset: ctx is NULL");
+    if (bytes == 0) return B200_OK;
+    B200_REQUIRE(d_dst != nullptr, "b200_memset: NULL buffer");
+    DeviceScope scope(ctx->device);
+    B200_CUDA_TRY(cudaMemsetAsync(d_dst, byte_value, bytes, ctx->pick(stream)));
+    return B200_OK;
+}
+
+}  // extern "C"

@@ -1,0 +1,539 @@
+// bf16 x bf16 -> fp32-accumulate GEMM for sm_100a: TMA-fed shared-memory ring, tcgen05.mma with the
+// accumulator in TMEM, warp-specialised persistent CTAs.
+//
+//   warp 0      : TMA producer (one elected lane) — fills a STAGES-deep ring of {A tile, B tile}
+//   warp 1      : allocates TMEM; one elected lane issues tcgen05.mma for every 64-deep K block
+//   warps 2..5  : epilogue — read the finished accumulator out of TMEM (tcgen05.ld), apply
+//                 alpha / bias / causal mask / activation, convert and store to global memory
+//
+// The accumulator is double buffered in TMEM (2 x BLOCK_N fp32 columns) so the epilogue of tile i
+// overlaps the main loop of tile i+1. One CTA per SM; CTA `x` handles work items x, x+grid, ...
+//
+// Operand layouts. op(A) is M x K and op(B) is K x N. An operand whose K index is contiguous in
+// memory ("K-major": A stored [M,K], B stored [N,K]) is loaded as one box of 64 k x ROWS with the
+// 128-byte swizzle. An operand whose M/N index is contiguous ("MN-major": A stored [K,M], B stored
+// [K,N]) is loaded as ROWS/64 boxes of 64 mn x 64 k. tcgen05 reads both forms directly through the
+// shared-memory descriptor, so NN, NT and TN products need no transposed copy.
+//
+// Ragged sizes: TMA zero-fills out-of-range box elements, so any M, N, K work; the epilogue
+// predicates its stores. The leading dimensions and base addresses must be multiples of 16 bytes.
+#include "gemm_common.cuh"
+#include "ptx.cuh"
+
+#include <algorithm>
+
+namespace b200 {
+
+using namespace ptx;
+
+namespace {
+
+constexpr int BM = 128;
+constexpr int BK = 64;
+constexpr int UMMA_K = 16;
+constexpr int NUM_THREADS = 192;
+constexpr int GROUP_M = 8;  // tile rasterisation: GROUP_M row-tiles share each B tile while it is hot in L2
+
+template <int BN>
+struct TileCfg {
+    static constexpr int A_BYTES = BM * BK * 2;
+    static constexpr int B_BYTES = BN * BK * 2;
+    static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
+    static constexpr int STAGES = (BN == 256) ? 4 : (BN == 128 ? 6 : 8);
+    static constexpr int TMEM_COLS = 2 * BN;
+    static constexpr int BARRIER_BYTES = 256;
+    static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + BARRIER_BYTES + 1024;
+};
+
+struct WorkItem {
+    int b, m0, n0, kb_begin, kb_end, split;
+};
+
+__device__ __forceinline__ WorkItem decode_work(const GemmParams& p, int w, int BN) {
+    WorkItem it;
+    const int tiles_mn = p.num_m_tiles * p.num_n_tiles;
+    const int per_split = p.batch * tiles_mn;
+    it.split = w / per_split;
+    int r = w - it.split * per_split;
+    it.b = r / tiles_mn;
+    int t = r - it.b * tiles_mn;
+    const int tiles_per_group = GROUP_M * p.num_n_tiles;
+    const int g = t / tiles_per_group;
+    const int first_m = g * GROUP_M;
+    const int gsz = min(p.num_m_tiles - first_m, GROUP_M);
+    const int rr = t - g * tiles_per_group;
+    const int mi = first_m + rr % gsz;
+    const int ni = rr / gsz;
+    it.m0 = mi * BM;
+    it.n0 = ni * BN;
+    it.kb_begin = it.split * p.kb_per_split;
+    it.kb_end = min(p.num_kb, it.kb_begin + p.kb_per_split);
+    return it;
+}
+
+template <int BN, bool A_KMAJOR, bool B_KMAJOR>
+__global__ void __launch_bounds__(NUM_THREADS, 1)
+gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
+                    const GemmParams p) {
+    using Cfg = TileCfg<BN>;
+    constexpr int STAGES = Cfg::STAGES;
+
+    extern __shared__ uint8_t smem_raw[];
+    // 128-byte-swizzled tiles must start on a 1024-byte boundary.
+    uint8_t* smem = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
+    uint8_t* bar_base = smem + STAGES * Cfg::STAGE_BYTES;
+    uint64_t* full_bar = reinterpret_cast<uint64_t*>(bar_base);
+    uint64_t* empty_bar = full_bar + STAGES;
+    uint64_t* tmem_full_bar = empty_bar + STAGES;
+    uint64_t* tmem_empty_bar = tmem_full_bar + 2;
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(tmem_empty_bar + 2);
+    volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+    const int warp = threadIdx.x >> 5;
+    const int lane = threadIdx.x & 31;
+
+    if (threadIdx.x == 0) {
+        prefetch_tensormap(&tmA);
+        prefetch_tensormap(&tmB);
+        for (int s = 0; s < STAGES; ++s) {
+            mbar_init(&full_bar[s], 1);
+            mbar_init(&empty_bar[s], 1);
+        }
+        for (int a = 0; a < 2; ++a) {
+            mbar_init(&tmem_full_bar[a], 1);
+            mbar_init(&tmem_empty_bar[a], 4);  // one arrival per epilogue warp
+        }
+        *abort_flag = 0;
+        mbar_fence_init();
+    }
+    if (warp == 1) {
+        tmem_alloc(tmem_slot, Cfg::TMEM_COLS);
+        tmem_relinquish_alloc_permit();
+    }
+    tcgen05_fence_before_sync();
+    __syncthreads();
+    tcgen05_fence_after_sync();
+    const uint32_t tmem_base = *tmem_slot;
+
+    if (warp == 0) {
+        // ------------------------------------------------------------------ TMA producer
+        if (lane == 0) {
+            int stage = 0;
+            uint32_t phase = 0;
+            bool ok = true;
+            for (int w = blockIdx.x; ok && w < p.total_work; w += gridDim.x) {
+                const WorkItem it = decode_work(p, w, BN);
+                const int ab = p.a_batched ? it.b : 0;
+                const int bb = p.b_batched ? it.b : 0;
+                for (int kb = it.kb_begin; kb < it.kb_end; ++kb) {
+                    if (!mbar_wait(&empty_bar[stage], phase ^ 1u, abort_flag)) {
+                        ok = false;
+                        break;
+                    }
+                    uint8_t* sA = smem + stage * Cfg::STAGE_BYTES;
+                    uint8_t* sB = sA + Cfg::A_BYTES;
+                    mbar_arrive_expect_tx(&full_bar[stage], Cfg::STAGE_BYTES);
+                    if (A_KMAJOR) {
+                        tma_load_3d(sA, &tmA, &full_bar[stage], kb * BK, it.m0, ab);
+                    } else {
+#pragma unroll
+                        for (int j = 0; j < BM / 64; ++j)
+                            tma_load_3d(sA + j * (64 * BK * 2), &tmA, &full_bar[stage], it.m0 + 64 * j, kb * BK, ab);
+                    }
+                    if (B_KMAJOR) {
+                        tma_load_3d(sB, &tmB, &full_bar[stage], kb * BK, it.n0, bb);
+                    } else {
+#pragma unroll
+                        for (int j = 0; j < BN / 64; ++j)
+                            tma_load_3d(sB + j * (64 * BK * 2), &tmB, &full_bar[stage], it.n0 + 64 * j, kb * BK, bb);
+                    }
+                    if (++stage == STAGES) {
+                        stage = 0;
+                        phase ^= 1u;
+                    }
+                }
+            }
+            if (!ok) {
+                // Gave up: let every copy already issued land before the CTA's shared memory goes away.
+                // A stage armed in the current pass completes phase `phase`, one from the pass before `phase ^ 1`.
+                for (int s = 0; s < STAGES; ++s) {
+                    const uint32_t par = (s < stage) ? phase : (phase ^ 1u);
+                    const uint64_t t0 = globaltimer_ns();
+                    while (!mbar_try_wait(&full_bar[s], par)) {
+                        if (globaltimer_ns() - t0 > 100000000ull) break;
+                    }
+                }
+            }
+        }
+    } else if (warp == 1) {
+        // ------------------------------------------------------------------ MMA issuer
+        if (lane == 0) {
+            constexpr uint32_t idesc = make_idesc_bf16_f32(BM, BN, A_KMAJOR ? 0u : 1u, B_KMAJOR ? 0u : 1u);
+            // Byte step between consecutive 16-deep K slices inside a stage, and the descriptor strides.
+            constexpr uint32_t A_KSTEP = A_KMAJOR ? (UMMA_K * 2) : (UMMA_K * 128);
+            constexpr uint32_t B_KSTEP = B_KMAJOR ? (UMMA_K * 2) : (UMMA_K * 128);
+            constexpr uint32_t A_LBO = A_KMAJOR ? 0u : (BK * 128);
+            constexpr uint32_t B_LBO = B_KMAJOR ? 0u : (BK * 128);
+            int stage = 0;
+            uint32_t phase = 0;
+            int acc = 0;
+            uint32_t acc_phase = 0;
+            bool ok = true;
+            for (int w = blockIdx.x; ok && w < p.total_work; w += gridDim.x) {
+                const WorkItem it = decode_work(p, w, BN);
+                if (!mbar_wait(&tmem_empty_bar[acc], acc_phase ^ 1u, abort_flag)) break;
+                tcgen05_fence_after_sync();
+                const uint32_t d_tmem = tmem_base + static_cast<uint32_t>(acc * BN);
+                for (int kb = it.kb_begin; kb < it.kb_end; ++kb) {
+                    if (!mbar_wait(&full_bar[stage], phase, abort_flag)) {
+                        ok = false;
+                        break;
+                    }
+                    tcgen05_fence_after_sync();
+                    const uint32_t a_addr = smem_u32(smem + stage * Cfg::STAGE_BYTES);
+                    const uint32_t b_addr = a_addr + Cfg::A_BYTES;
+#pragma unroll
+                    for (int k = 0; k < BK / UMMA_K; ++k) {
+                        const uint64_t da = make_smem_desc_sw128(a_addr + k * A_KSTEP, A_LBO, 1024);
+                        const uint64_t db = make_smem_desc_sw128(b_addr + k * B_KSTEP, B_LBO, 1024);
+                        umma_f16_ss(d_tmem, da, db, idesc, (kb > it.kb_begin || k > 0) ? 1u : 0u);
+                    }
+                    umma_commit(&empty_bar[stage]);  // frees the stage once these MMAs have read it
+                    if (++stage == STAGES) {
+                        stage = 0;
+                        phase ^= 1u;
+                    }
+                }
+                if (!ok) break;
+                umma_commit(&tmem_full_bar[acc]);  // accumulator complete
+                acc ^= 1;
+                if (acc == 0) acc_phase ^= 1u;
+            }
+        }
+    } else {
+        // ------------------------------------------------------------------ epilogue (warps 2..5)
+        const int q = warp & 3;  // TMEM lane quarter this warp may read
+        int acc = 0;
+        uint32_t acc_phase = 0;
+        for (int w = blockIdx.x; w < p.total_work; w += gridDim.x) {
+            const WorkItem it = decode_work(p, w, BN);
+            const bool got = mbar_wait(&tmem_full_bar[acc], acc_phase, abort_flag);
+            if (!__all_sync(0xffffffffu, got)) break;
+            tcgen05_fence_after_sync();
+            const int row = it.m0 + q * 32 + lane;
+            const bool row_ok = row < p.M;
+            const uint32_t taddr = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + static_cast<uint32_t>(acc * BN);
+
+            if (p.k_splits > 1) {
+                // fp32 partial sums, no epilogue math: [split][batch][M][N]
+                float* prow = p.partial +
+                              ((static_cast<size_t>(it.split) * p.batch + it.b) * p.M + (row_ok ? row : 0)) * p.N;
+                const bool vec = (p.N & 3) == 0;
+#pragma unroll 1
+                for (int c = 0; c < BN; c += 32) {
+                    const int n = it.n0 + c;
+                    if (n >= p.N) break;
+                    uint32_t v[32];
+                    tmem_ld_32x32b_x32(taddr + c, v);
+                    tmem_ld_wait();
+                    if (p.partial_round_bf16) {
+#pragma unroll
+                        for (int i = 0; i < 32; ++i)
+                            v[i] = __float_as_uint(__bfloat162float(__float2bfloat16_rn(__uint_as_float(v[i]))));
+                    }
+                    if (row_ok) {
+                        if (vec && n + 32 <= p.N) {
+                            float4* dst = reinterpret_cast<float4*>(prow + n);
+#pragma unroll
+                            for (int i = 0; i < 8; ++i)
+                                dst[i] = make_float4(__uint_as_float(v[4 * i]), __uint_as_float(v[4 * i + 1]),
+                                                     __uint_as_float(v[4 * i + 2]), __uint_as_float(v[4 * i + 3]));
+                        } else {
+#pragma unroll
+                            for (int i = 0; i < 32; ++i)
+                                if (n + i < p.N) prow[n + i] = __uint_as_float(v[i]);
+                        }
+                    }
+                }
+            } else {
+                const size_t crow = static_cast<size_t>(it.b) * p.stride_c + static_cast<size_t>(row_ok ? row : 0) * p.ldc;
+#pragma unroll 1
+                for (int c = 0; c < BN; c += 32) {
+                    const int n = it.n0 + c;
+                    if (n >= p.N) break;
+                    uint32_t v[32];
+                    tmem_ld_32x32b_x32(taddr + c, v);
+                    tmem_ld_wait();
+                    const bool full = (n + 32 <= p.N);
+                    float f[32];
+#pragma unroll
+                    for (int i = 0; i < 32; ++i) {
+                        const int nn = full ? (n + i) : min(n + i, p.N - 1);
+                        f[i] = epi_apply(p.epi, __uint_as_float(v[i]), row, nn);
+                    }
+                    if (row_ok) {
+                        if (p.c_f32) {
+                            float* dst = static_cast<float*>(p.C) + crow + n;
+                            if (full && p.c_vec_ok) {
+                                float4* d4 = reinterpret_cast<float4*>(dst);
+#pragma unroll
+                                for (int i = 0; i < 8; ++i)
+                                    d4[i] = make_float4(f[4 * i], f[4 * i + 1], f[4 * i + 2], f[4 * i + 3]);
+                            } else {
+#pragma unroll
+                                for (int i = 0; i < 32; ++i)
+                                    if (n + i < p.N) dst[i] = f[i];
+                            }
+                        } else {
+                            __nv_bfloat16* dst = static_cast<__nv_bfloat16*>(p.C) + crow + n;
+                            if (full && p.c_vec_ok) {
+                                uint4* d4 = reinterpret_cast<uint4*>(dst);
+#pragma unroll
+                                for (int i = 0; i < 4; ++i)
+                                    d4[i] = make_uint4(pack_bf16x2(f[8 * i], f[8 * i + 1]), pack_bf16x2(f[8 * i + 2], f[8 * i + 3]),
+                                                       pack_bf16x2(f[8 * i + 4], f[8 * i + 5]),
+                                                       pack_bf16x2(f[8 * i + 6], f[8 * i + 7]));
+                            } else {
+#pragma unroll
+                                for (int i = 0; i < 32; ++i)
+                                    if (n + i < p.N) dst[i] = __float2bfloat16_rn(f[i]);
+                            }
+                        }
+                    }
+                }
+            }
+            // Hand the accumulator buffer back to the MMA warp.
+            tcgen05_fence_before_sync();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&tmem_empty_bar[acc]);
+            acc ^= 1;
+            if (acc == 0) acc_phase ^= 1u;
+        }
+    }
+
+    // ---------------------------------------------------------------------- teardown
+    tcgen05_fence_before_sync();
+    __syncthreads();
+    if (threadIdx.x == 0 && *abort_flag != 0) atomicExch(p.status, 1);
+    if (warp == 1) {
+        tcgen05_fence_after_sync();
+        tmem_dealloc(tmem_base, Cfg::TMEM_COLS);
+    }
+}
+
+// Sums the K slices, applies the epilogue and writes C. One thread per 4 consecutive columns.
+__global__ void splitk_reduce_kernel(const GemmParams p) {
+    const long long cols4 = (p.N + 3) / 4;
+    const long long total = static_cast<long long>(p.batch) * p.M * cols4;
+    const size_t slice = static_cast<size_t>(p.batch) * p.M * p.N;
+    for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < total;
+         i += static_cast<long long>(gridDim.x) * blockDim.x) {
+        const int c4 = static_cast<int>(i % cols4);
+        const long long rm = i / cols4;
+        const int m = static_cast<int>(rm % p.M);
+        const int b = static_cast<int>(rm / p.M);
+        const int n = c4 * 4;
+        const size_t off = (static_cast<size_t>(b) * p.M + m) * p.N + n;
+        float acc[4] = {0.f, 0.f, 0.f, 0.f};
+        if ((p.N & 3) == 0) {
+            for (int s = 0; s < p.k_splits; ++s) {
+                const float4 v = *reinterpret_cast<const float4*>(p.partial + s * slice + off);
+                acc[0] += v.x;
+                acc[1] += v.y;
+                acc[2] += v.z;
+                acc[3] += v.w;
+            }
+        } else {
+            for (int s = 0; s < p.k_splits; ++s)
+                for (int j = 0; j < 4; ++j)
+                    if (n + j < p.N) acc[j] += p.partial[s * slice + off + j];
+        }
+        const size_t coff = static_cast<size_t>(b) * p.stride_c + static_cast<size_t>(m) * p.ldc + n;
+        for (int j = 0; j < 4; ++j) {
+            if (n + j < p.N) {
+                const float v = epi_apply(p.epi, acc[j], m, n + j);
+                if (p.c_f32)
+                    static_cast<float*>(p.C)[coff + j] = v;
+                else
+                    static_cast<__nv_bfloat16*>(p.C)[coff + j] = __float2bfloat16_rn(v);
+            }
+        }
+    }
+}
+
+// 3-D tensor map {inner, rows, batch} over a bf16 matrix with a 128-byte-swizzled box.
+int make_tensor_map(b200_ctx* ctx, CUtensorMap* out, const void* base, uint64_t inner, uint64_t rows, uint64_t batch,
+                    uint64_t ld_elems, uint64_t batch_stride_elems, uint32_t box_inner, uint32_t box_rows) {
+    cuuint64_t dims[3] = {inner, rows, batch};
+    if (batch <= 1 || batch_stride_elems == 0) {
+        dims[2] = 1;
+        batch_stride_elems = rows * ld_elems;
+    }
+    cuuint64_t strides[2] = {ld_elems * 2, batch_stride_elems * 2};
+    cuuint32_t box[3] = {box_inner, box_rows, 1};
+    cuuint32_t estr[3] = {1, 1, 1};
+    CUresult r = ctx->encode_tiled(out, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, const_cast<void*>(base), dims, strides, box,
+                                   estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                                   CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) {
+        return fail(B200_ERR_CUDA,
+                    "cuTensorMapEncodeTiled failed (%d): base %p dims {%llu,%llu,%llu} strides {%llu,%llu} box {%u,%u}",
+                    static_cast<int>(r), base, (unsigned long long)dims[0], (unsigned long long)dims[1],
+                    (unsigned long long)dims[2], (unsigned long long)strides[0], (unsigned long long)strides[1], box_inner,
+                    box_rows);
+    }
+    return B200_OK;
+}
+
+template <int BN, bool A_KMAJOR, bool B_KMAJOR>
+int launch_variant(const CUtensorMap& tmA, const CUtensorMap& tmB, const GemmParams& p, int grid, cudaStream_t stream) {
+    using Cfg = TileCfg<BN>;
+    auto kernel = gemm_tcgen05_kernel<BN, A_KMAJOR, B_KMAJOR>;
+    static bool configured[64] = {};  // per template instance and device: the attribute is per device function
+    int dev = 0;
+    B200_CUDA_TRY(cudaGetDevice(&dev));
+    if (dev < 0 || dev >= 64 || !configured[dev]) {
+        B200_CUDA_TRY(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::SMEM_BYTES));
+        if (dev >= 0 && dev < 64) configured[dev] = true;
+    }
+    kernel<<<grid, NUM_THREADS, Cfg::SMEM_BYTES, stream>>>(tmA, tmB, p);
+    B200_CUDA_TRY(cudaGetLastError());
+    return B200_OK;
+}
+
+template <int BN>
+int launch_bn(bool a_kmajor, bool b_kmajor, const CUtensorMap& tmA, const CUtensorMap& tmB, const GemmParams& p, int grid,
+              cudaStream_t stream) {
+    if (a_kmajor && b_kmajor) return launch_variant<BN, true, true>(tmA, tmB, p, grid, stream);
+    if (a_kmajor && !b_kmajor) return launch_variant<BN, true, false>(tmA, tmB, p, grid, stream);
+    if (!a_kmajor && b_kmajor) return launch_variant<BN, false, true>(tmA, tmB, p, grid, stream);
+    return launch_variant<BN, false, false>(tmA, tmB, p, grid, stream);
+}
+
+inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
+
+}  // namespace
+
+bool gemm_tcgen05_eligible(const b200_gemm_desc& d, const char** why) {
+    const char* w = nullptr;
+    if (!aligned16(d.A) || !aligned16(d.B))
+        w = "A and B must be 16-byte aligned";
+    else if ((d.lda & 7) || (d.ldb & 7))
+        w = "lda and ldb must be multiples of 8 elements";
+    else if (d.batch > 1 && ((d.stride_a & 7) || (d.stride_b & 7)))
+        w = "batch strides of A and B must be multiples of 8 elements";
+    else if (d.M >= (1ll << 31) || d.N >= (1ll << 31) || d.K >= (1ll << 31) || d.batch >= (1ll << 31))
+        w = "dimension too large";
+    if (why) *why = w;
+    return w == nullptr;
+}
+
+int gemm_choose_block_n(const b200_ctx* ctx, const b200_gemm_desc& d) {
+    if (d.N <= 64) return 64;
+    if (d.N <= 128) return 128;
+    // Prefer the 256-wide tile (best operand reuse) unless it leaves most SMs idle and a
+    // narrower tile fills more of them.
+    const long long m_tiles = (d.M + BM - 1) / BM;
+    const long long t256 = d.batch * m_tiles * ((d.N + 255) / 256);
+    if (t256 >= ctx->sm_count) return 256;
+    const long long t128 = d.batch * m_tiles * ((d.N + 127) / 128);
+    if (t128 > t256 && (d.N % 256) != 0 && (d.N % 256) <= 128) return 128;
+    return (t256 * 2 <= ctx->sm_count && t128 > t256) ? 128 : 256;
+}
+
+int gemm_choose_split_k(const b200_ctx* ctx, const b200_gemm_desc& d) {
+    if (d.split_k == 1) return 1;
+    const int num_kb = static_cast<int>((d.K + BK - 1) / BK);
+    if (num_kb <= 1) return 1;
+    int want;
+    if (d.split_k > 1) {
+        want = d.split_k;
+    } else {
+        const int bn = gemm_choose_block_n(ctx, d);
+        const long long tiles = d.batch * ((d.M + BM - 1) / BM) * ((d.N + bn - 1) / bn);
+        if (tiles * 2 > ctx->sm_count || num_kb < 8) return 1;
+        want = static_cast<int>(ctx->sm_count / tiles);
+        want = min(want, num_kb / 4);  // keep at least 4 K blocks per slice
+        want = min(want, 32);
+    }
+    want = max(1, min(want, num_kb));
+    const int per = (num_kb + want - 1) / want;
+    return (num_kb + per - 1) / per;  // every slice gets at least one K block
+}
+
+int launch_gemm_tcgen05(b200_ctx* ctx, const b200_gemm_desc& d, int k_splits, cudaStream_t stream) {
+    const bool a_kmajor = d.transpose_a == 0;  // A stored [M,K]
+    const bool b_kmajor = d.transpose_b != 0;  // B stored [N,K]
+    const int bn = gemm_choose_block_n(ctx, d);
+
+    GemmParams p{};
+    p.M = static_cast<int>(d.M);
+    p.N = static_cast<int>(d.N);
+    p.K = static_cast<int>(d.K);
+    p.batch = static_cast<int>(d.batch);
+    p.num_m_tiles = (p.M + BM - 1) / BM;
+    p.num_n_tiles = (p.N + bn - 1) / bn;
+    p.num_kb = (p.K + BK - 1) / BK;
+    p.k_splits = k_splits;
+    p.kb_per_split = (p.num_kb + k_splits - 1) / k_splits;
+    const long long total = static_cast<long long>(k_splits) * p.batch * p.num_m_tiles * p.num_n_tiles;
+    B200_REQUIRE(total < (1ll << 31), "b200_gemm: too many tiles (%lld)", total);
+    p.total_work = static_cast<int>(total);
+    p.a_batched = (d.batch > 1 && d.stride_a != 0) ? 1 : 0;
+    p.b_batched = (d.batch > 1 && d.stride_b != 0) ? 1 : 0;
+    p.C = d.C;
+    p.ldc = d.ldc;
+    p.stride_c = d.stride_c;
+    p.c_f32 = d.c_dtype == B200_F32;
+    const int cvec = p.c_f32 ? 4 : 8;
+    p.c_vec_ok = aligned16(d.C) && (d.ldc % cvec) == 0 && (d.batch <= 1 || (d.stride_c % cvec) == 0);
+    p.epi.alpha = d.alpha;
+    p.epi.bias = d.bias;
+    p.epi.bias_f32 = d.bias_dtype == B200_F32;
+    p.epi.act = d.activation;
+    p.epi.gelu_tanh = d.fidelity == B200_LOFI;
+    p.epi.causal = d.causal_mask;
+    p.epi.mask_value = d.mask_value;
+    p.status = ctx->d_status;
+    p.partial = nullptr;
+    p.partial_round_bf16 = (d.fidelity == B200_LOFI || d.fidelity == B200_HIFI2) ? 1 : 0;
+    if (k_splits > 1) {
+        const size_t bytes = static_cast<size_t>(k_splits) * p.batch * p.M * p.N * sizeof(float);
+        int rc = ensure_scratch(ctx, bytes);
+        if (rc != B200_OK) return rc;
+        p.partial = static_cast<float*>(ctx->d_scratch);
+    }
+
+    CUtensorMap tmA, tmB;
+    int rc;
+    if (a_kmajor)
+        rc = make_tensor_map(ctx, &tmA, d.A, d.K, d.M, d.batch, d.lda, d.stride_a, BK, BM);
+    else
+        rc = make_tensor_map(ctx, &tmA, d.A, d.M, d.K, d.batch, d.lda, d.stride_a, 64, BK);
+    if (rc != B200_OK) return rc;
+    if (b_kmajor)
+        rc = make_tensor_map(ctx, &tmB, d.B, d.K, d.N, d.batch, d.ldb, d.stride_b, BK, bn);
+    else
+        rc = make_tensor_map(ctx, &tmB, d.B, d.N, d.K, d.batch, d.ldb, d.stride_b, 64, BK);
+    if (rc != B200_OK) return rc;
+
+    const int grid = min(p.total_work, ctx->sm_count);
+    if (bn == 256)
+        rc = launch_bn<256>(a_kmajor, b_kmajor, tmA, tmB, p, grid, stream);
+    else if (bn == 128)
+        rc = launch_bn<128>(a_kmajor, b_kmajor, tmA, tmB, p, grid, stream);
+    else
+        rc = launch_bn<64>(a_kmajor, b_kmajor, tmA, tmB, p, grid, stream);
+    if (rc != B200_OK) return rc;
+
+    if (k_splits > 1) {
+        const long long work = static_cast<long long>(p.batch) * p.M * ((p.N + 3) / 4);
+        const int threads = 256;
+        const int blocks = static_cast<int>(std::min<long long>((work + threads - 1) / threads, ctx->sm_count * 8ll));
+        splitk_reduce_kernel<<<blocks, threads, 0, stream>>>(p);
+        B200_CUDA_TRY(cudaGetLastError());
+    }
+    return B200_OK;
+}
+
+}  // namespace b200
