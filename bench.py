@@ -1,0 +1,294 @@
+#!/usr/bin/env python3
+"""Benchmark of the dense-matmul hot path on B200.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl b200|reference]
+
+N = 1   one bf16 GEMM C = A.B with M = N = K = 8192 per step (the shape the headline metric is quoted on),
+        inputs resident in HBM, through the C ABI (b200_gemm).
+N > 1   launched by torchrun, one rank per GPU: the distributed matmul M = N = K = 16384 with B split on N
+        across the ranks and C all-gathered (scripts/matmul_2dev_distributed.py generalised), strong scaling.
+
+Prints ONE JSON line on rank 0. `value` is whole-job TFLOP/s (2.M.N.K per product, counted once for the
+sharded product). `e2e` repeats the measurement with host buffers: pinned host A/B -> device, GEMM, C -> host.
+`--impl reference` times the reference's CPU path for the same workload (torch CPU fp32 matmul, the baseline
+scripts/matmul_sweep.py:84-108 uses) on a bounded slab of rows.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import threading
+import time
+from pathlib import Path
+
+REPO = Path(__file__).resolve().parent
+sys.path.insert(0, str(REPO))
+
+L2_BYTES = 126 * 1024 * 1024
+
+# dram__bytes_read.sum + dram__bytes_write.sum of one 8192^3 launch, from the ncu capture summarised in
+# profiles/ (null until a capture of the current kernel exists).
+GEMM_8192_DRAM_TRAFFIC_BYTES = None
+
+
+def load_peaks() -> dict:
+    p = REPO / "MEASURED_PEAKS.json"
+    if p.exists():
+        d = json.loads(p.read_text())
+        return {"hbm_gbs": d["hbm_gbs"], "bf16_tflops": d["bf16_tflops"],
+                "bf16_tflops_sustained": d.get("bf16_tflops_sustained", d["bf16_tflops"]), "source": "measured"}
+    return {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0, "source": "fallback"}
+
+
+class ClockSampler:
+    """Samples nvidia-smi clocks and throttle reasons while the timed region runs."""
+    FIELDS = ("clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,"
+              "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+              "clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, gpu_index: int):
+        self.gpu_index = gpu_index
+        self.samples: list[list[str]] = []
+        self._stop = threading.Event()
+        self._thread = None
+
+    def _run(self):
+        # one streaming nvidia-smi process: a sample every 100 ms until stop()
+        try:
+            self._proc = subprocess.Popen(["nvidia-smi", f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits",
+                                           "-lms", "100", "-i", str(self.gpu_index)], stdout=subprocess.PIPE,
+                                          stderr=subprocess.DEVNULL, text=True)
+        except OSError:
+            return
+        for line in self._proc.stdout:
+            if self._stop.is_set():
+                break
+            if line.strip():
+                self.samples.append([c.strip() for c in line.strip().split(",")])
+
+    def start(self):
+        self._proc = None
+        self._thread = threading.Thread(target=self._run, daemon=True)
+        self._thread.start()
+
+    def stop(self) -> dict:
+        self._stop.set()
+        if self._proc is not None:
+            self._proc.terminate()
+        if self._thread:
+            self._thread.join(timeout=6)
+        sm, mx, reasons = [], [], set()
+        names = ("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap")
+        for s in self.samples:
+            try:
+                sm.append(float(s[0]))
+                mx.append(float(s[1]))
+            except (ValueError, IndexError):
+                continue
+            for name, val in zip(names, s[3:7]):
+                if val.lower().startswith("active"):
+                    reasons.add(name)
+        return {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": max(mx) if mx else None,
+                "reasons": sorted(reasons), "samples": len(sm)}
+
+
+def cpu_matmul_baseline(M: int, N: int, K: int, target_s: float = 12.0) -> dict:
+    """The reference's CPU path for this workload — torch CPU fp32 matmul on bf16-rounded inputs, as
+    scripts/matmul_sweep.py:84-108 times it — on a slab of rows of A sized for about `target_s` seconds."""
+    import torch
+    threads = torch.get_num_threads()
+    g = torch.Generator().manual_seed(42)
+    rows = min(M, 256)
+    b = torch.randn(K, N, generator=g).bfloat16().float()
+    a = torch.randn(rows, K, generator=g).bfloat16().float()
+    torch.matmul(a, b)  # warm-up
+    t0 = time.perf_counter()
+    torch.matmul(a, b)
+    dt = time.perf_counter() - t0
+    rate = 2.0 * rows * N * K / dt
+    rows_big = int(min(M, max(rows, (target_s * rate) / (2.0 * N * K))))
+    rows_big = max(64, rows_big // 64 * 64)
+    a = torch.randn(rows_big, K, generator=g).bfloat16().float()
+    reps = max(1, int(round(target_s * rate / (2.0 * rows_big * N * K))))
+    t0 = time.perf_counter()
+    for _ in range(reps):
+        torch.matmul(a, b)
+    dt = time.perf_counter() - t0
+    tflops = 2.0 * rows_big * N * K * reps / dt / 1e12
+    return {"value": tflops, "unit": "TFLOP/s", "cores": threads, "kind": "port",
+            "sample": f"torch CPU fp32 matmul of a {rows_big}-row slab of A[{M},{K}] against the full B[{K},{N}], "
+                      f"{reps} repetitions ({dt:.2f} s, {threads} threads of {os.cpu_count()} cpus)",
+            "seconds": dt}
+
+
+def run_reference_arm(args) -> None:
+    """`--impl reference`: the reference's own CPU implementation of the path (torch CPU fp32 matmul) with all
+    host threads, each step a bounded slab of the workload. Rank 0 only."""
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    import torch
+    n = args.gpus
+    size = 8192 if n == 1 else 16384
+    M = N = K = size
+    threads = torch.get_num_threads()
+    g = torch.Generator().manual_seed(42)
+    b = torch.randn(K, N, generator=g).bfloat16().float()
+    probe = torch.randn(128, K, generator=g).bfloat16().float()
+    torch.matmul(probe, b)
+    t0 = time.perf_counter()
+    torch.matmul(probe, b)
+    rate = 2.0 * 128 * N * K / (time.perf_counter() - t0)
+    total_steps = max(1, args.steps + args.warmup)
+    per_step_s = min(10.0, 120.0 / total_steps)
+    rows = int(min(M, max(64, per_step_s * rate / (2.0 * N * K))) // 64 * 64) or 64
+    a = torch.randn(rows, K, generator=g).bfloat16().float()
+    for _ in range(args.warmup):
+        torch.matmul(a, b)
+    t0 = time.perf_counter()
+    for _ in range(args.steps):
+        torch.matmul(a, b)
+    dt = time.perf_counter() - t0
+    tflops = 2.0 * rows * N * K * args.steps / dt / 1e12
+    sample = (f"torch CPU fp32 matmul, {rows}-row slab of A[{M},{K}] x B[{K},{N}] per step, {threads} threads of "
+              f"{os.cpu_count()} cpus")
+    line = {
+        "impl": "reference", "metric": "bf16 GEMM TFLOP/s", "value": tflops, "unit": "TFLOP/s", "n_gpus": n,
+        "steps": args.steps, "warmup": args.warmup, "ms_per_step": dt / args.steps * 1e3,
+        "higher_is_better": True, "scaling": "strong" if n > 1 else "weak", "vs_baseline": None, "dtype": "f32",
+        "data": "synthetic", "config": workload_config(n),
+        "cpu_baseline": {"value": tflops, "unit": "TFLOP/s", "cores": threads, "kind": "port", "sample": sample},
+        "e2e": {"value": tflops, "unit": "TFLOP/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "gpu_launches": 0,
+    }
+    print(json.dumps(line), flush=True)
+
+
+def workload_config(n: int) -> dict:
+    if n == 1:
+        return {"workload": "matmul_sweep M=N=K=8192: C[M,N] = A[M,K] . B[K,N], bf16 in, fp32 accumulate, bf16 out",
+                "M": 8192, "N": 8192, "K": 8192, "seed": 42,
+                "l2_policy": "inputs (A+B = 256 MiB) larger than the 126 MiB L2; no flush between steps"}
+    return {"workload": f"distributed matmul M=N=K=16384, B column-sharded on N across {n} GPUs, all-gather of C",
+            "M": 16384, "N": 16384, "K": 16384, "seed": 42, "shards": n,
+            "l2_policy": "inputs larger than the 126 MiB L2; no flush between steps"}
+
+
+def run_b200_single(args) -> None:
+    import torch
+    from __graft_entry__ import load_package
+    pkg = load_package()
+    torch.cuda.set_device(0)
+    ctx = pkg.Context(0)
+    st = torch.cuda.Stream()
+    torch.cuda.set_stream(st)
+    s = st.cuda_stream
+    M = N = K = 8192
+    g = torch.Generator().manual_seed(42)
+    a_h = torch.randn(M, K, generator=g).bfloat16().pin_memory()
+    b_h = torch.randn(K, N, generator=g).bfloat16().pin_memory()
+    c_h = torch.empty(M, N, dtype=torch.bfloat16).pin_memory()
+    a = a_h.cuda(non_blocking=True)
+    b = b_h.cuda(non_blocking=True)
+    c = torch.empty(M, N, dtype=torch.bfloat16, device="cuda")
+    desc = ctx.gemm_desc(a, b, c, M, N, K)
+    flops = 2.0 * M * N * K
+
+    for _ in range(max(args.warmup, 3)):
+        ctx.gemm(desc, s)
+    ctx.synchronize(s)
+
+    sampler = ClockSampler(0)
+    sampler.start()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    torch.cuda.synchronize()
+    e0.record(st)
+    for _ in range(args.steps):
+        ctx.gemm(desc, s)
+    e1.record(st)
+    torch.cuda.synchronize()
+    ms = e0.elapsed_time(e1)
+    # keep the sampler over a region long enough to see clocks under load
+    t_end = time.perf_counter() + 1.5
+    while time.perf_counter() < t_end:
+        for _ in range(20):
+            ctx.gemm(desc, s)
+        torch.cuda.synchronize()
+    clocks = sampler.stop()
+    ctx.synchronize(s)
+    ms_per_step = ms / args.steps
+    tflops = flops / (ms_per_step * 1e-3) / 1e12
+
+    # sanity: the timed kernel really computed the product (a sample of rows against fp32 torch on the device)
+    rows = torch.arange(0, M, 257, device="cuda")
+    ref = a[rows].float() @ b.float()
+    err = ((c[rows].float() - ref).norm() / ref.norm()).item()
+    if not err < 1e-2:
+        raise RuntimeError(f"bench: GEMM output fails parity (relative Frobenius error {err:.3e})")
+
+    # end to end through the C ABI with host buffers
+    e2e_steps = max(1, min(args.steps, 5))
+    nbytes = M * K * 2
+    for _ in range(2):
+        ctx.h2d(a, a_h, nbytes, s)
+        ctx.h2d(b, b_h, nbytes, s)
+        ctx.gemm(desc, s)
+        ctx.d2h(c_h, c, nbytes, s)
+    torch.cuda.synchronize()
+    t0 = time.perf_counter()
+    for _ in range(e2e_steps):
+        ctx.h2d(a, a_h, nbytes, s)
+        ctx.h2d(b, b_h, nbytes, s)
+        ctx.gemm(desc, s)
+        ctx.d2h(c_h, c, nbytes, s)   # synchronises the stream
+    torch.cuda.synchronize()
+    e2e_s = (time.perf_counter() - t0) / e2e_steps
+    e2e_tflops = flops / e2e_s / 1e12
+
+    peaks = load_peaks()
+    peak = peaks["bf16_tflops"]
+    cpu = cpu_matmul_baseline(M, N, K)
+    cpu.pop("seconds", None)
+    line = {
+        "metric": "bf16 GEMM TFLOP/s", "value": tflops, "unit": "TFLOP/s", "n_gpus": 1, "steps": args.steps,
+        "warmup": max(args.warmup, 3), "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "weak",
+        "vs_baseline": None, "dtype": "bf16", "data": "synthetic", "config": workload_config(1),
+        "pct_of_peak": tflops / peak,
+        "roofline": {"bound": "tensor", "achieved": tflops, "peak": peak, "unit": "TFLOP/s", "frac": tflops / peak,
+                     "traffic": GEMM_8192_DRAM_TRAFFIC_BYTES,
+                     "peak_source": f"{peaks['source']} (MEASURED_PEAKS.json bf16_tflops, burst: kernel timed alone)",
+                     "kernel": "gemm_tcgen05_kernel<256,K-major A,MN-major B>", "flops_per_launch": flops},
+        "cpu_baseline": cpu,
+        "e2e": {"value": e2e_tflops, "unit": "TFLOP/s", "h2d_bytes_per_step": 2 * nbytes, "d2h_bytes_per_step": nbytes,
+                "ms_per_step": e2e_s * 1e3, "steps": e2e_steps},
+        "gpu_launches": args.steps,
+        "clocks": clocks,
+        "parity_sample_rel_frobenius": err,
+    }
+    print(json.dumps(line), flush=True)
+    ctx.close()
+
+
+def main() -> None:
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
+    args = ap.parse_args()
+    if args.impl == "reference":
+        run_reference_arm(args)
+        return
+    if args.gpus == 1 and int(os.environ.get("WORLD_SIZE", "1")) == 1:
+        run_b200_single(args)
+    else:
+        from bench_dist import run_b200_distributed  # noqa: WPS433 (kept separate: needs torch.distributed)
+        run_b200_distributed(args, load_peaks, workload_config, ClockSampler)
+
+
+if __name__ == "__main__":
+    main()

@@ -1,0 +1,83 @@
+"""CPU-side checks of the C ABI: the library loads, exports every symbol the header declares, the ctypes
+table matches the header, and argument validation rejects bad calls without touching a GPU."""
+import ctypes as C
+import re
+import subprocess
+
+import pytest
+
+from conftest import REPO
+
+HEADER = REPO / "include" / "b200_ttperf.h"
+
+
+def header_functions():
+    text = re.sub(r"/\*.*?\*/", "", HEADER.read_text(), flags=re.S)
+    return sorted(set(re.findall(r"\b(b200_[a-z0-9_]+)\s*\(", text)))
+
+
+def test_library_exports_every_declared_symbol(pkg):
+    lib = pkg.lib()
+    names = header_functions()
+    assert "b200_gemm" in names and "b200_ctx_create" in names
+    for n in names:
+        assert hasattr(lib, n), f"{n} is declared in the header but not exported"
+
+
+def test_ctypes_table_covers_the_header(pkg):
+    assert sorted(pkg.capi.SIGNATURES) == header_functions()
+
+
+def test_only_c_abi_symbols_are_exported(pkg):
+    out = subprocess.run(["nm", "-D", "--defined-only", str(pkg.lib_path())], capture_output=True, text=True,
+                         check=True).stdout
+    syms = [line.split()[-1] for line in out.splitlines() if line.strip()]
+    assert syms and all(s.startswith("b200_") for s in syms), [s for s in syms if not s.startswith("b200_")][:5]
+
+
+def test_header_compiles_as_plain_c(tmp_path):
+    src = tmp_path / "t.c"
+    src.write_text('#include "b200_ttperf.h"\nint main(void){ b200_gemm_desc d; (void)d; return B200_OK; }\n')
+    subprocess.run(["gcc", "-std=c99", "-Wall", "-Werror", "-I", str(REPO / "include"), "-c", str(src), "-o",
+                    str(tmp_path / "t.o")], check=True)
+
+
+def test_struct_layout_matches_the_header(pkg, tmp_path):
+    src = tmp_path / "sz.c"
+    src.write_text('#include <stdio.h>\n#include <stddef.h>\n#include "b200_ttperf.h"\n'
+                   'int main(void){ printf("%zu %zu %zu %zu", sizeof(b200_gemm_desc), offsetof(b200_gemm_desc, C),'
+                   ' offsetof(b200_gemm_desc, alpha), offsetof(b200_gemm_desc, split_k)); return 0; }\n')
+    exe = tmp_path / "sz"
+    subprocess.run(["gcc", "-I", str(REPO / "include"), str(src), "-o", str(exe)], check=True)
+    size, off_c, off_alpha, off_split = map(int, subprocess.run([str(exe)], capture_output=True, text=True,
+                                                                check=True).stdout.split())
+    G = pkg.GemmDesc
+    assert (C.sizeof(G), G.C.offset, G.alpha.offset, G.split_k.offset) == (size, off_c, off_alpha, off_split)
+
+
+def test_abi_version_and_desc_defaults(pkg):
+    lib = pkg.lib()
+    assert lib.b200_abi_version() == 1
+    d = pkg.GemmDesc()
+    lib.b200_gemm_desc_init(C.byref(d))
+    assert (d.batch, d.alpha, d.c_dtype, d.fidelity, d.algo, d.split_k) == (1, 1.0, pkg.BF16, pkg.HIFI4, 0, 0)
+    assert d.transpose_a == 0 and d.transpose_b == 0 and d.activation == pkg.ACT_NONE
+
+
+def test_no_cpu_fallback_context_creation_fails_without_a_gpu(pkg):
+    torch = pytest.importorskip("torch")
+    if torch.cuda.is_available():
+        pytest.skip("a GPU is present; this test pins the behaviour on a GPU-less host")
+    with pytest.raises(pkg.B200Error) as e:
+        pkg.Context(0)
+    assert e.value.code == pkg.capi.ERR_CUDA and "no CPU path" in str(e.value)
+
+
+def test_null_arguments_are_rejected(pkg):
+    lib = pkg.lib()
+    assert lib.b200_gemm(None, None, None) == pkg.capi.ERR_INVALID_ARG
+    assert b"ctx is NULL" in lib.b200_last_error()
+    assert lib.b200_ctx_create(0, None) == pkg.capi.ERR_INVALID_ARG
+    assert lib.b200_synchronize(None, None) == pkg.capi.ERR_INVALID_ARG
+    assert lib.b200_malloc(None, 16, None) == pkg.capi.ERR_INVALID_ARG
+    assert lib.b200_ctx_destroy(None) == pkg.capi.OK  # destroying nothing is not an error
