@@ -127,6 +127,26 @@ int b200_gemm(b200_ctx* ctx, const b200_gemm_desc* desc, void* stream);
 /* Bytes of context scratch the split-K path of this descriptor will use (0 when it does not split). */
 int b200_gemm_scratch_bytes(b200_ctx* ctx, const b200_gemm_desc* desc, size_t* out_bytes);
 
+/* ---- split-K matmul without device allocation (no counterpart in the reference: TTNN owns its device
+ *      memory, so the question never arises there) ----------------------------------------------------
+ * Same arguments and result as b200_gemm on the tcgen05 path, for hosts that must not allocate device
+ * memory at call time: executors that gave all of HBM to their own arena, loops with a latency bound
+ * (cudaMalloc / cudaFree synchronise the device), code running under stream capture. The fp32 partial
+ * sums of the K slices live in a fixed 32 MiB array inside the library image (held by every GPU that
+ * loads the library until the process exits) instead of context scratch; the call performs no
+ * cudaMalloc, cudaFree or other allocating routine and needs no b200_ctx.
+ *   device    ordinal of the GPU that owns A, B, C and `stream`
+ *   stream    required (non-NULL) cudaStream_t
+ *   split_k   0 = same choice as b200_gemm, lowered until the partial sums fit; n > 1 = exactly n slices
+ * Fails with B200_ERR_INVALID_ARG when k_slices * batch * M * N * 4 bytes exceed 32 MiB, or when the
+ * operands do not meet the TMA alignment rules (there is no SIMT path here).
+ * All calls on a device share the array: calls whose kernels may overlap on the GPU (different streams
+ * or threads) race on it — keep them on one stream. The first call on each device looks up the array's
+ * device address and configures the kernels; make it before any stream capture starts. A bounded wait
+ * that runs out inside these kernels is recorded in a status word inside the library image, which
+ * b200_synchronize does not report. */
+int b200_gemm_static_scratch(int device, const b200_gemm_desc* desc, void* stream);
+
 #ifdef __cplusplus
 } /* extern "C" */
 #endif

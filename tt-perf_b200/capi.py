@@ -66,6 +66,7 @@ SIGNATURES = {
     "b200_gemm_desc_init": (None, [C.POINTER(GemmDesc)]),
     "b200_gemm": (C.c_int, [C.c_void_p, C.POINTER(GemmDesc), C.c_void_p]),
     "b200_gemm_scratch_bytes": (C.c_int, [C.c_void_p, C.POINTER(GemmDesc), C.POINTER(C.c_size_t)]),
+    "b200_gemm_static_scratch": (C.c_int, [C.c_int, C.POINTER(GemmDesc), C.c_void_p]),
 }
 
 _lib = None
@@ -184,6 +185,11 @@ class Context:
 
     def gemm(self, desc: GemmDesc, stream=None) -> None:
         check(lib().b200_gemm(self._h, C.byref(desc), C.c_void_p(ptr(stream))))
+
+    def gemm_static_scratch(self, desc: GemmDesc, stream) -> None:
+        """Split-K matmul whose partial sums use the library's fixed 32 MiB array: no device allocation at
+        call time (see b200_gemm_static_scratch in the header). `stream` is required."""
+        check(lib().b200_gemm_static_scratch(self.device, C.byref(desc), C.c_void_p(ptr(stream))))
 
     def gemm_scratch_bytes(self, desc: GemmDesc) -> int:
         n = C.c_size_t()
