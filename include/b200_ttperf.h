@@ -127,6 +127,96 @@ int b200_gemm(b200_ctx* ctx, const b200_gemm_desc* desc, void* stream);
 /* Bytes of context scratch the split-K path of this descriptor will use (0 when it does not split). */
 int b200_gemm_scratch_bytes(b200_ctx* ctx, const b200_gemm_desc* desc, size_t* out_bytes);
 
+/* ---- row softmax family (traced/ops.hpp:77-81 softmax, :102-106 softmax_backward; py/engine.py:352-384) ----
+ * [rows, cols] bf16 matrices, leading dimensions in elements.
+ * b200_softmax: y = softmax(alpha * x) along each row. causal_period P > 0 additionally hides, in row r, the
+ *   columns > r % P — the [B,H,S,S] score tensor flattened to [B*H*S, S] with P = S gets the upper-triangular
+ *   -1e9 mask of traced/nn.hpp:158-168 and the 1/sqrt(dh) scale (alpha) in the same pass.
+ * b200_softmax_backward: dx = alpha * y * (dy - sum_row(dy * y)).
+ * b200_log_softmax / _backward: y = log softmax(x); dx = dy - exp(y) * sum_row(dy) (py/engine.py:368-381). */
+int b200_softmax(b200_ctx* ctx, const void* x, int64_t ldx, void* y, int64_t ldy, int64_t rows, int64_t cols, float alpha,
+                 int64_t causal_period, void* stream);
+int b200_softmax_backward(b200_ctx* ctx, const void* dy, int64_t lddy, const void* y, int64_t ldy, void* dx, int64_t lddx,
+                          int64_t rows, int64_t cols, float alpha, void* stream);
+int b200_log_softmax(b200_ctx* ctx, const void* x, int64_t ldx, void* y, int64_t ldy, int64_t rows, int64_t cols,
+                     void* stream);
+int b200_log_softmax_backward(b200_ctx* ctx, const void* dy, int64_t lddy, const void* log_y, int64_t ldy, void* dx,
+                              int64_t lddx, int64_t rows, int64_t cols, void* stream);
+
+/* ---- fused cross-entropy (CrossEntropyLoss, py/nn.py:149-222; last_token_cross_entropy, py/experiment.py:50-118) -
+ * One pass over bf16 logits [rows, classes]: per-row loss -log softmax(x)[label] and, when d_logits is not NULL,
+ * d_logits = (softmax(x) - onehot(label)) * grad_scale (grad_scale = 1/rows for the mean reduction). Labels are
+ * uint32 class ids on the device (no one-hot tensor is built). loss_sum (device fp32 scalar, optional) receives
+ * grad_scale * sum of row losses, i.e. the mean loss for grad_scale = 1/rows; row_loss (device fp32 [rows], optional)
+ * receives the unscaled per-row losses. */
+int b200_cross_entropy(b200_ctx* ctx, const void* logits, int64_t ld, const uint32_t* labels, int64_t rows, int64_t classes,
+                       float grad_scale, float* loss_sum, float* row_loss, void* d_logits, int64_t ldd, void* stream);
+
+/* ---- LayerNorm (TracedLayerNorm forward ~10 TTNN ops / backward ~14, traced/nn.hpp:226-269) ----------------
+ * Forward: y = (x - mean) * rstd * gamma + beta over the last dim (biased variance, eps inside the sqrt); mean and
+ * rstd (device fp32 [rows], optional) are saved for the backward pass.
+ * Backward: dx (bf16, optional) and fp32 dgamma / dbeta [cols] (optional; overwritten, not accumulated). */
+int b200_layernorm_forward(b200_ctx* ctx, const void* x, int64_t ldx, const void* gamma, const void* beta, void* y,
+                           int64_t ldy, float* mean, float* rstd, int64_t rows, int64_t cols, float eps, void* stream);
+int b200_layernorm_backward(b200_ctx* ctx, const void* dy, int64_t lddy, const void* x, int64_t ldx, const void* gamma,
+                            const float* mean, const float* rstd, void* dx, int64_t lddx, float* dgamma_f32,
+                            float* dbeta_f32, int64_t rows, int64_t cols, void* stream);
+
+/* ---- element-wise ops on bf16 buffers ------------------------------------------------------------------------
+ * Unary (ttnn::neg / relu / gtz / gelu / rsqrt ..., traced/ops.hpp:54-61; tensor (+,*) float forms, traced/ops.hpp:38-52). */
+typedef enum b200_unary_op {
+    B200_U_NEG = 0, B200_U_RELU = 1, B200_U_GTZ = 2, B200_U_GELU = 3, B200_U_RSQRT = 4, B200_U_EXP = 5, B200_U_LOG = 6,
+    B200_U_TANH = 7, B200_U_SQRT = 8, B200_U_ADD_SCALAR = 9, B200_U_MUL_SCALAR = 10, B200_U_RSUB_SCALAR = 11,
+    B200_U_COPY = 12, B200_U_RECIP = 13, B200_U_SQUARE = 14
+} b200_unary_op;
+int b200_unary(b200_ctx* ctx, int op, const void* x, void* y, int64_t n, float scalar, void* stream);
+
+/* Binary with numpy-style broadcasting (ttnn::add / subtract / multiply with [1,N], [1,1,S,S], [B,S,1] operands,
+ * dynamic/ops.hpp:50-134). Shapes are rank 4 (pad with leading 1s); each dim must match or be 1. RELU_BW and GELU_BW
+ * take (dy, x): dy * (x > 0) (the gtz mask multiply, traced/ops.hpp:55-57) and ttnn::gelu_bw(dy, x, "none")
+ * (traced/ops.hpp:96-99). */
+typedef enum b200_binary_op {
+    B200_B_ADD = 0, B200_B_SUB = 1, B200_B_MUL = 2, B200_B_DIV = 3, B200_B_RELU_BW = 4, B200_B_GELU_BW = 5, B200_B_MAX = 6
+} b200_binary_op;
+int b200_binary(b200_ctx* ctx, int op, const void* a, const int64_t a_shape[4], const void* b, const int64_t b_shape[4],
+                void* out, void* stream);
+
+/* Reduction of the middle dim of a contiguous bf16 [outer, R, inner] view (ttnn::sum / mean / max(t, dim, keepdim),
+ * traced/ops.hpp:63-73; bias gradient = column sum over the batch, traced/nn.hpp:81). Output [outer, inner] bf16.
+ * inner > 1 uses outer*inner fp32 words of context scratch. */
+typedef enum b200_reduce_op { B200_R_SUM = 0, B200_R_MEAN = 1, B200_R_MAX = 2 } b200_reduce_op;
+int b200_reduce(b200_ctx* ctx, int op, const void* x, int64_t outer, int64_t R, int64_t inner, void* y, void* stream);
+
+/* Creation and conversion (ttnn::zeros / ones / full / full_like, traced/nn.hpp:30-52). `value` is converted to dtype. */
+int b200_fill(b200_ctx* ctx, void* dst, int64_t n, int dtype, float value, void* stream);
+int b200_cast(b200_ctx* ctx, const void* src, int src_dtype, void* dst, int dst_dtype, int64_t n, void* stream);
+
+/* Layout: out = permute(x, perm) for a contiguous rank-4 16-bit tensor (ttnn::transpose(t, 1, 2) for the head
+ * split/merge, transformer_train.hpp:167-177; ttnn::transpose(weight), dynamic/nn.hpp:25). */
+int b200_permute(b200_ctx* ctx, const void* x, const int64_t in_shape[4], const int32_t perm[4], void* y, void* stream);
+/* ttnn::triu(t, diagonal) on the last two dims of [batch, rows, cols] (traced/nn.hpp:160). */
+int b200_triu(b200_ctx* ctx, const void* x, void* y, int64_t batch, int64_t rows, int64_t cols, int diagonal, void* stream);
+
+/* ---- embedding (TracedEmbedding, traced/nn.hpp:303-321: ttnn::embedding / ttnn::embedding_bw) ----------------
+ * forward: out[i, :] = table[ids[i], :]; backward: d_table (fp32 [vocab, dim], overwritten) += dy rows by id. */
+int b200_embedding_forward(b200_ctx* ctx, const uint32_t* ids, int64_t n_ids, const void* table, int64_t vocab, int64_t dim,
+                           void* out, void* stream);
+int b200_embedding_backward(b200_ctx* ctx, const uint32_t* ids, int64_t n_ids, const void* dy, int64_t vocab, int64_t dim,
+                            float* d_table_f32, void* stream);
+
+/* ---- optimisers ------------------------------------------------------------------------------------------------
+ * Multi-tensor updates: `count` tensors given as HOST arrays of device pointers and element counts.
+ * SGD  p <- p - lr * g (traced/ops.hpp:132-134, dynamic/optim.hpp:21-27, py/optim.py:13-22).
+ * Adam with bias correction and eps added after the square root (py/optim.py:49-87); m and v are fp32 (the
+ * reference keeps them in bf16 tensors, which loses precision); `step` counts from 1. Parameters and gradients are
+ * bf16 or fp32 (one dtype for all tensors of a call). shadow_bf16 (optional table, entries may be NULL): bf16 copies of
+ * fp32 master parameters, rewritten in the same pass so the next matmul reads up-to-date bf16 weights. */
+int b200_sgd_step(b200_ctx* ctx, int64_t count, void* const* params, const void* const* grads, void* const* shadow_bf16,
+                  const int64_t* sizes, int p_dtype, int g_dtype, float lr, void* stream);
+int b200_adam_step(b200_ctx* ctx, int64_t count, void* const* params, const void* const* grads, float* const* m,
+                   float* const* v, void* const* shadow_bf16, const int64_t* sizes, int p_dtype, int g_dtype, float lr,
+                   float beta1, float beta2, float eps, int64_t step, void* stream);
+
 /* ---- split-K matmul without device allocation (no counterpart in the reference: TTNN owns its device
  *      memory, so the question never arises there) ----------------------------------------------------
  * Same arguments and result as b200_gemm on the tcgen05 path, for hosts that must not allocate device

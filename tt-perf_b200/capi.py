@@ -67,7 +67,44 @@ SIGNATURES = {
     "b200_gemm": (C.c_int, [C.c_void_p, C.POINTER(GemmDesc), C.c_void_p]),
     "b200_gemm_scratch_bytes": (C.c_int, [C.c_void_p, C.POINTER(GemmDesc), C.POINTER(C.c_size_t)]),
     "b200_gemm_static_scratch": (C.c_int, [C.c_int, C.POINTER(GemmDesc), C.c_void_p]),
+    "b200_softmax": (C.c_int, [C.c_void_p, C.c_void_p, C.c_int64, C.c_void_p, C.c_int64, C.c_int64, C.c_int64, C.c_float,
+                               C.c_int64, C.c_void_p]),
+    "b200_softmax_backward": (C.c_int, [C.c_void_p, C.c_void_p, C.c_int64, C.c_void_p, C.c_int64, C.c_void_p, C.c_int64,
+                                        C.c_int64, C.c_int64, C.c_float, C.c_void_p]),
+    "b200_log_softmax": (C.c_int, [C.c_void_p, C.c_void_p, C.c_int64, C.c_void_p, C.c_int64, C.c_int64, C.c_int64,
+                                   C.c_void_p]),
+    "b200_log_softmax_backward": (C.c_int, [C.c_void_p, C.c_void_p, C.c_int64, C.c_void_p, C.c_int64, C.c_void_p,
+                                            C.c_int64, C.c_int64, C.c_int64, C.c_void_p]),
+    "b200_cross_entropy": (C.c_int, [C.c_void_p, C.c_void_p, C.c_int64, C.c_void_p, C.c_int64, C.c_int64, C.c_float,
+                                     C.c_void_p, C.c_void_p, C.c_void_p, C.c_int64, C.c_void_p]),
+    "b200_layernorm_forward": (C.c_int, [C.c_void_p, C.c_void_p, C.c_int64, C.c_void_p, C.c_void_p, C.c_void_p, C.c_int64,
+                                         C.c_void_p, C.c_void_p, C.c_int64, C.c_int64, C.c_float, C.c_void_p]),
+    "b200_layernorm_backward": (C.c_int, [C.c_void_p, C.c_void_p, C.c_int64, C.c_void_p, C.c_int64, C.c_void_p, C.c_void_p,
+                                          C.c_void_p, C.c_void_p, C.c_int64, C.c_void_p, C.c_void_p, C.c_int64, C.c_int64,
+                                          C.c_void_p]),
+    "b200_unary": (C.c_int, [C.c_void_p, C.c_int, C.c_void_p, C.c_void_p, C.c_int64, C.c_float, C.c_void_p]),
+    "b200_binary": (C.c_int, [C.c_void_p, C.c_int, C.c_void_p, C.POINTER(C.c_int64), C.c_void_p, C.POINTER(C.c_int64),
+                              C.c_void_p, C.c_void_p]),
+    "b200_reduce": (C.c_int, [C.c_void_p, C.c_int, C.c_void_p, C.c_int64, C.c_int64, C.c_int64, C.c_void_p, C.c_void_p]),
+    "b200_fill": (C.c_int, [C.c_void_p, C.c_void_p, C.c_int64, C.c_int, C.c_float, C.c_void_p]),
+    "b200_cast": (C.c_int, [C.c_void_p, C.c_void_p, C.c_int, C.c_void_p, C.c_int, C.c_int64, C.c_void_p]),
+    "b200_permute": (C.c_int, [C.c_void_p, C.c_void_p, C.POINTER(C.c_int64), C.POINTER(C.c_int32), C.c_void_p, C.c_void_p]),
+    "b200_triu": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_int64, C.c_int64, C.c_int64, C.c_int, C.c_void_p]),
+    "b200_embedding_forward": (C.c_int, [C.c_void_p, C.c_void_p, C.c_int64, C.c_void_p, C.c_int64, C.c_int64, C.c_void_p,
+                                         C.c_void_p]),
+    "b200_embedding_backward": (C.c_int, [C.c_void_p, C.c_void_p, C.c_int64, C.c_void_p, C.c_int64, C.c_int64, C.c_void_p,
+                                          C.c_void_p]),
+    "b200_sgd_step": (C.c_int, [C.c_void_p, C.c_int64, C.POINTER(C.c_void_p), C.POINTER(C.c_void_p), C.POINTER(C.c_void_p),
+                                C.POINTER(C.c_int64), C.c_int, C.c_int, C.c_float, C.c_void_p]),
+    "b200_adam_step": (C.c_int, [C.c_void_p, C.c_int64, C.POINTER(C.c_void_p), C.POINTER(C.c_void_p), C.POINTER(C.c_void_p),
+                                 C.POINTER(C.c_void_p), C.POINTER(C.c_void_p), C.POINTER(C.c_int64), C.c_int, C.c_int, C.c_float, C.c_float,
+                                 C.c_float, C.c_float, C.c_int64, C.c_void_p]),
 }
+
+U_NEG, U_RELU, U_GTZ, U_GELU, U_RSQRT, U_EXP, U_LOG, U_TANH, U_SQRT, U_ADD_SCALAR, U_MUL_SCALAR, U_RSUB_SCALAR, U_COPY, \
+    U_RECIP, U_SQUARE = range(15)
+B_ADD, B_SUB, B_MUL, B_DIV, B_RELU_BW, B_GELU_BW, B_MAX = range(7)
+R_SUM, R_MEAN, R_MAX = range(3)
 
 _lib = None
 
@@ -195,3 +232,90 @@ class Context:
         n = C.c_size_t()
         check(lib().b200_gemm_scratch_bytes(self._h, C.byref(desc), C.byref(n)))
         return n.value
+
+    # ---- row ops, element-wise ops, optimisers: thin pass-throughs (see the header for semantics) ---------------
+    def _s(self, stream):
+        return C.c_void_p(ptr(stream))
+
+    def softmax(self, x, y, rows, cols, *, ldx=None, ldy=None, alpha=1.0, causal_period=0, stream=None):
+        check(lib().b200_softmax(self._h, ptr(x), ldx or cols, ptr(y), ldy or cols, rows, cols, alpha, causal_period,
+                                 self._s(stream)))
+
+    def softmax_backward(self, dy, y, dx, rows, cols, *, alpha=1.0, stream=None):
+        check(lib().b200_softmax_backward(self._h, ptr(dy), cols, ptr(y), cols, ptr(dx), cols, rows, cols, alpha,
+                                          self._s(stream)))
+
+    def log_softmax(self, x, y, rows, cols, *, stream=None):
+        check(lib().b200_log_softmax(self._h, ptr(x), cols, ptr(y), cols, rows, cols, self._s(stream)))
+
+    def log_softmax_backward(self, dy, log_y, dx, rows, cols, *, stream=None):
+        check(lib().b200_log_softmax_backward(self._h, ptr(dy), cols, ptr(log_y), cols, ptr(dx), cols, rows, cols,
+                                              self._s(stream)))
+
+    def cross_entropy(self, logits, labels, rows, classes, *, ld=None, grad_scale=None, loss_sum=None, row_loss=None,
+                      d_logits=None, ldd=None, stream=None):
+        gs = (1.0 / rows if rows else 1.0) if grad_scale is None else grad_scale
+        check(lib().b200_cross_entropy(self._h, ptr(logits), ld or classes, ptr(labels), rows, classes, gs, ptr(loss_sum),
+                                       ptr(row_loss), ptr(d_logits), ldd or classes, self._s(stream)))
+
+    def layernorm_forward(self, x, gamma, beta, y, mean, rstd, rows, cols, *, eps=1e-5, stream=None):
+        check(lib().b200_layernorm_forward(self._h, ptr(x), cols, ptr(gamma), ptr(beta), ptr(y), cols, ptr(mean), ptr(rstd),
+                                           rows, cols, eps, self._s(stream)))
+
+    def layernorm_backward(self, dy, x, gamma, mean, rstd, dx, dgamma, dbeta, rows, cols, *, stream=None):
+        check(lib().b200_layernorm_backward(self._h, ptr(dy), cols, ptr(x), cols, ptr(gamma), ptr(mean), ptr(rstd), ptr(dx),
+                                            cols, ptr(dgamma), ptr(dbeta), rows, cols, self._s(stream)))
+
+    def unary(self, op, x, y, n, *, scalar=0.0, stream=None):
+        check(lib().b200_unary(self._h, op, ptr(x), ptr(y), n, scalar, self._s(stream)))
+
+    @staticmethod
+    def _shape4(shape):
+        shape = tuple(int(d) for d in shape)
+        if len(shape) > 4:
+            raise ValueError("rank > 4 is not supported")
+        return (C.c_int64 * 4)(*((1,) * (4 - len(shape)) + shape))
+
+    def binary(self, op, a, a_shape, b, b_shape, out, *, stream=None):
+        check(lib().b200_binary(self._h, op, ptr(a), self._shape4(a_shape), ptr(b), self._shape4(b_shape), ptr(out),
+                                self._s(stream)))
+
+    def reduce(self, op, x, outer, R, inner, y, *, stream=None):
+        check(lib().b200_reduce(self._h, op, ptr(x), outer, R, inner, ptr(y), self._s(stream)))
+
+    def fill(self, dst, n, dtype, value, *, stream=None):
+        check(lib().b200_fill(self._h, ptr(dst), n, dtype, value, self._s(stream)))
+
+    def cast(self, src, src_dtype, dst, dst_dtype, n, *, stream=None):
+        check(lib().b200_cast(self._h, ptr(src), src_dtype, ptr(dst), dst_dtype, n, self._s(stream)))
+
+    def permute(self, x, in_shape, perm, y, *, stream=None):
+        check(lib().b200_permute(self._h, ptr(x), self._shape4(in_shape), (C.c_int32 * 4)(*perm), ptr(y), self._s(stream)))
+
+    def triu(self, x, y, batch, rows, cols, diagonal, *, stream=None):
+        check(lib().b200_triu(self._h, ptr(x), ptr(y), batch, rows, cols, diagonal, self._s(stream)))
+
+    def embedding_forward(self, ids, n_ids, table, vocab, dim, out, *, stream=None):
+        check(lib().b200_embedding_forward(self._h, ptr(ids), n_ids, ptr(table), vocab, dim, ptr(out), self._s(stream)))
+
+    def embedding_backward(self, ids, n_ids, dy, vocab, dim, d_table_f32, *, stream=None):
+        check(lib().b200_embedding_backward(self._h, ptr(ids), n_ids, ptr(dy), vocab, dim, ptr(d_table_f32),
+                                            self._s(stream)))
+
+    @staticmethod
+    def _ptr_array(items):
+        return (C.c_void_p * len(items))(*[ptr(i) or None for i in items])
+
+    def sgd_step(self, params, grads, sizes, lr, *, p_dtype=BF16, g_dtype=BF16, shadows=None, stream=None):
+        n = len(params)
+        check(lib().b200_sgd_step(self._h, n, self._ptr_array(params), self._ptr_array(grads),
+                                  self._ptr_array(shadows) if shadows else None, (C.c_int64 * n)(*sizes),
+                                  p_dtype, g_dtype, lr, self._s(stream)))
+
+    def adam_step(self, params, grads, m, v, sizes, step, *, lr=1e-3, beta1=0.9, beta2=0.999, eps=1e-8, p_dtype=BF16,
+                  g_dtype=BF16, shadows=None, stream=None):
+        n = len(params)
+        check(lib().b200_adam_step(self._h, n, self._ptr_array(params), self._ptr_array(grads), self._ptr_array(m),
+                                   self._ptr_array(v), self._ptr_array(shadows) if shadows else None,
+                                   (C.c_int64 * n)(*sizes), p_dtype, g_dtype, lr, beta1, beta2, eps, step,
+                                   self._s(stream)))

@@ -1,0 +1,560 @@
+// Element-wise, broadcast, reduction, layout and gather/scatter kernels around the matmuls.
+// All are HBM-bandwidth bound: 16-byte vector accesses on the contiguous dimension, grid-stride loops
+// sized to a multiple of the SM count, fp32 arithmetic on bf16 storage.
+#include "common.cuh"
+#include "gemm_common.cuh"
+
+#include <algorithm>
+#include <cfloat>
+
+namespace b200 {
+namespace {
+
+constexpr int kThreads = 256;
+
+inline int grid_for(const b200_ctx* ctx, long long work_items) {
+    const long long blocks = (work_items + kThreads - 1) / kThreads;
+    return static_cast<int>(std::max<long long>(1, std::min<long long>(blocks, ctx->sm_count * 16ll)));
+}
+
+__device__ __forceinline__ void unpack8(const uint4& u, float (&f)[8]) {
+    const uint32_t w[4] = {u.x, u.y, u.z, u.w};
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        f[2 * i] = __uint_as_float(w[i] << 16);
+        f[2 * i + 1] = __uint_as_float(w[i] & 0xffff0000u);
+    }
+}
+__device__ __forceinline__ uint4 pack8(const float (&f)[8]) {
+    return make_uint4(pack_bf16x2(f[0], f[1]), pack_bf16x2(f[2], f[3]), pack_bf16x2(f[4], f[5]), pack_bf16x2(f[6], f[7]));
+}
+
+// ---- unary / scalar ops ------------------------------------------------------------------------------
+enum UnaryOp : int {
+    U_NEG = 0, U_RELU = 1, U_GTZ = 2, U_GELU = 3, U_RSQRT = 4, U_EXP = 5, U_LOG = 6, U_TANH = 7, U_SQRT = 8,
+    U_ADD_SCALAR = 9, U_MUL_SCALAR = 10, U_RSUB_SCALAR = 11, U_COPY = 12, U_RECIP = 13, U_SQUARE = 14, U_COUNT = 15
+};
+
+__device__ __forceinline__ float unary_apply(int op, float x, float s) {
+    switch (op) {
+        case U_NEG: return -x;
+        case U_RELU: return fmaxf(x, 0.0f);
+        case U_GTZ: return x > 0.0f ? 1.0f : 0.0f;
+        case U_GELU: return gelu_exact(x);
+        case U_RSQRT: return rsqrtf(x);
+        case U_EXP: return __expf(x);
+        case U_LOG: return __logf(x);
+        case U_TANH: return tanhf(x);
+        case U_SQRT: return sqrtf(x);
+        case U_ADD_SCALAR: return x + s;
+        case U_MUL_SCALAR: return x * s;
+        case U_RSUB_SCALAR: return s - x;
+        case U_RECIP: return 1.0f / x;
+        case U_SQUARE: return x * x;
+        default: return x;
+    }
+}
+
+__global__ void __launch_bounds__(kThreads) unary_kernel(const __nv_bfloat16* x, __nv_bfloat16* y, long long n, int op,
+                                                          float s, int vec) {
+    const long long nvec = vec ? n / 8 : 0;
+    const long long stride = static_cast<long long>(gridDim.x) * blockDim.x;
+    for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < nvec; i += stride) {
+        float f[8];
+        unpack8(reinterpret_cast<const uint4*>(x)[i], f);
+#pragma unroll
+        for (int k = 0; k < 8; ++k) f[k] = unary_apply(op, f[k], s);
+        reinterpret_cast<uint4*>(y)[i] = pack8(f);
+    }
+    for (long long i = nvec * 8 + blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < n; i += stride)
+        y[i] = __float2bfloat16_rn(unary_apply(op, __bfloat162float(x[i]), s));
+}
+
+// ---- binary ops with numpy-style broadcasting over up to 4 dims --------------------------------------
+enum BinaryOp : int { B_ADD = 0, B_SUB = 1, B_MUL = 2, B_DIV = 3, B_RELU_BW = 4, B_GELU_BW = 5, B_MAX = 6, B_COUNT = 7 };
+
+__device__ __forceinline__ float binary_apply(int op, float a, float b) {
+    switch (op) {
+        case B_ADD: return a + b;
+        case B_SUB: return a - b;
+        case B_MUL: return a * b;
+        case B_DIV: return a / b;
+        case B_RELU_BW: return b > 0.0f ? a : 0.0f;  // a = dy, b = x
+        case B_GELU_BW: {                             // a = dy, b = x; derivative of the exact (erf) GELU
+            const float cdf = 0.5f * (1.0f + erff(b * 0.70710678118654752f));
+            const float pdf = 0.3989422804014327f * __expf(-0.5f * b * b);
+            return a * (cdf + b * pdf);
+        }
+        case B_MAX: return fmaxf(a, b);
+        default: return a;
+    }
+}
+
+struct BinaryParams {
+    const __nv_bfloat16* a;
+    const __nv_bfloat16* b;
+    __nv_bfloat16* out;
+    long long od[4];      // output dims
+    long long as[4];      // element strides of a per output dim (0 = broadcast)
+    long long bs[4];
+    long long n;          // total output elements
+    int op;
+    int vec;              // last output dim % 8 == 0, all pointers 16-byte aligned, last strides in {0,1}
+};
+
+__global__ void __launch_bounds__(kThreads) binary_kernel(const BinaryParams p) {
+    const long long stride = static_cast<long long>(gridDim.x) * blockDim.x;
+    if (p.vec) {
+        const long long nvec = p.n / 8;
+        const long long d3v = p.od[3] / 8;
+        for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < nvec; i += stride) {
+            const long long c = (i % d3v) * 8;
+            long long r = i / d3v;
+            const long long i2 = r % p.od[2];
+            r /= p.od[2];
+            const long long i1 = r % p.od[1];
+            const long long i0 = r / p.od[1];
+            const long long ao = i0 * p.as[0] + i1 * p.as[1] + i2 * p.as[2] + c * p.as[3];
+            const long long bo = i0 * p.bs[0] + i1 * p.bs[1] + i2 * p.bs[2] + c * p.bs[3];
+            float fa[8], fb[8];
+            if (p.as[3] == 1) {
+                unpack8(*reinterpret_cast<const uint4*>(p.a + ao), fa);
+            } else {
+                const float v = __bfloat162float(p.a[ao]);
+#pragma unroll
+                for (int k = 0; k < 8; ++k) fa[k] = v;
+            }
+            if (p.bs[3] == 1) {
+                unpack8(*reinterpret_cast<const uint4*>(p.b + bo), fb);
+            } else {
+                const float v = __bfloat162float(p.b[bo]);
+#pragma unroll
+                for (int k = 0; k < 8; ++k) fb[k] = v;
+            }
+#pragma unroll
+            for (int k = 0; k < 8; ++k) fa[k] = binary_apply(p.op, fa[k], fb[k]);
+            reinterpret_cast<uint4*>(p.out)[i] = pack8(fa);
+        }
+    } else {
+        for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < p.n; i += stride) {
+            const long long i3 = i % p.od[3];
+            long long r = i / p.od[3];
+            const long long i2 = r % p.od[2];
+            r /= p.od[2];
+            const long long i1 = r % p.od[1];
+            const long long i0 = r / p.od[1];
+            const float a = __bfloat162float(p.a[i0 * p.as[0] + i1 * p.as[1] + i2 * p.as[2] + i3 * p.as[3]]);
+            const float b = __bfloat162float(p.b[i0 * p.bs[0] + i1 * p.bs[1] + i2 * p.bs[2] + i3 * p.bs[3]]);
+            p.out[i] = __float2bfloat16_rn(binary_apply(p.op, a, b));
+        }
+    }
+}
+
+// ---- reductions over one dim of [outer, R, inner] ----------------------------------------------------
+enum ReduceOp : int { R_SUM = 0, R_MEAN = 1, R_MAX = 2, R_COUNT = 3 };
+
+// inner == 1: one warp per output (row reduction).
+__global__ void __launch_bounds__(kThreads) reduce_rows_kernel(const __nv_bfloat16* x, __nv_bfloat16* y, long long outer,
+                                                                long long R, int op, int vec) {
+    const int lane = threadIdx.x & 31;
+    const long long o = blockIdx.x * static_cast<long long>(kThreads / 32) + (threadIdx.x >> 5);
+    if (o >= outer) return;
+    const __nv_bfloat16* row = x + o * R;
+    float acc = (op == R_MAX) ? -FLT_MAX : 0.0f;
+    const long long nvec = vec ? R / 8 : 0;
+    for (long long v = lane; v < nvec; v += 32) {
+        float f[8];
+        unpack8(reinterpret_cast<const uint4*>(row)[v], f);
+#pragma unroll
+        for (int k = 0; k < 8; ++k) acc = (op == R_MAX) ? fmaxf(acc, f[k]) : acc + f[k];
+    }
+    for (long long i = nvec * 8 + lane; i < R; i += 32) {
+        const float f = __bfloat162float(row[i]);
+        acc = (op == R_MAX) ? fmaxf(acc, f) : acc + f;
+    }
+#pragma unroll
+    for (int s = 16; s > 0; s >>= 1) {
+        const float other = __shfl_xor_sync(0xffffffffu, acc, s);
+        acc = (op == R_MAX) ? fmaxf(acc, other) : acc + other;
+    }
+    if (lane == 0) y[o] = __float2bfloat16_rn(op == R_MEAN ? acc / static_cast<float>(R) : acc);
+}
+
+// inner > 1: CTA = 32 columns x 8 row lanes; partial results of the row slabs combined in fp32.
+__global__ void __launch_bounds__(kThreads) reduce_cols_kernel(const __nv_bfloat16* x, float* acc_out, long long R,
+                                                                long long inner, int op, long long rows_per_cta) {
+    __shared__ float sh[8][33];
+    const long long o = blockIdx.z;
+    const long long c = blockIdx.x * 32ll + (threadIdx.x & 31);
+    const int sub = threadIdx.x >> 5;
+    const long long r0 = blockIdx.y * rows_per_cta, r1 = min(R, r0 + rows_per_cta);
+    float acc = (op == R_MAX) ? -FLT_MAX : 0.0f;
+    if (c < inner) {
+        const __nv_bfloat16* base = x + o * R * inner + c;
+        for (long long r = r0 + sub; r < r1; r += 8) {
+            const float f = __bfloat162float(base[r * inner]);
+            acc = (op == R_MAX) ? fmaxf(acc, f) : acc + f;
+        }
+    }
+    sh[sub][threadIdx.x & 31] = acc;
+    __syncthreads();
+    if (sub == 0 && c < inner) {
+        for (int k = 1; k < 8; ++k) {
+            const float other = sh[k][threadIdx.x];
+            acc = (op == R_MAX) ? fmaxf(acc, other) : acc + other;
+        }
+        float* dst = acc_out + o * inner + c;
+        if (op == R_MAX) {
+            // float max through integer atomics (valid for any mix of signs)
+            if (acc >= 0.0f)
+                atomicMax(reinterpret_cast<int*>(dst), __float_as_int(acc));
+            else
+                atomicMin(reinterpret_cast<unsigned int*>(dst), __float_as_uint(acc));
+        } else {
+            atomicAdd(dst, acc);
+        }
+    }
+}
+
+__global__ void fill_f32_kernel(float* p, long long n, float v) {
+    const long long stride = static_cast<long long>(gridDim.x) * blockDim.x;
+    for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < n; i += stride) p[i] = v;
+}
+__global__ void fill_bf16_kernel(__nv_bfloat16* p, long long n, float v) {
+    const __nv_bfloat16 b = __float2bfloat16_rn(v);
+    const long long stride = static_cast<long long>(gridDim.x) * blockDim.x;
+    for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < n; i += stride) p[i] = b;
+}
+__global__ void fill_u32_kernel(uint32_t* p, long long n, uint32_t v) {
+    const long long stride = static_cast<long long>(gridDim.x) * blockDim.x;
+    for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < n; i += stride) p[i] = v;
+}
+__global__ void cast_f32_to_bf16_kernel(const float* x, __nv_bfloat16* y, long long n, float scale) {
+    const long long stride = static_cast<long long>(gridDim.x) * blockDim.x;
+    for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < n; i += stride)
+        y[i] = __float2bfloat16_rn(x[i] * scale);
+}
+__global__ void cast_bf16_to_f32_kernel(const __nv_bfloat16* x, float* y, long long n) {
+    const long long stride = static_cast<long long>(gridDim.x) * blockDim.x;
+    for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < n; i += stride)
+        y[i] = __bfloat162float(x[i]);
+}
+
+// ---- layout: permutation of a rank-4 tensor ----------------------------------------------------------
+struct PermuteParams {
+    const uint16_t* x;
+    uint16_t* y;
+    long long od[4];   // output dims
+    long long is[4];   // input element stride for each OUTPUT dim
+    long long n;
+    int vec;           // innermost output dim is also the input's innermost (stride 1), % 8 == 0, aligned
+};
+
+__global__ void __launch_bounds__(kThreads) permute_kernel(const PermuteParams p) {
+    const long long stride = static_cast<long long>(gridDim.x) * blockDim.x;
+    if (p.vec) {
+        const long long d3v = p.od[3] / 8, nvec = p.n / 8;
+        for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < nvec; i += stride) {
+            const long long c = (i % d3v) * 8;
+            long long r = i / d3v;
+            const long long i2 = r % p.od[2];
+            r /= p.od[2];
+            const long long i1 = r % p.od[1];
+            const long long i0 = r / p.od[1];
+            reinterpret_cast<uint4*>(p.y)[i] =
+                *reinterpret_cast<const uint4*>(p.x + i0 * p.is[0] + i1 * p.is[1] + i2 * p.is[2] + c);
+        }
+    } else {
+        for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < p.n; i += stride) {
+            const long long i3 = i % p.od[3];
+            long long r = i / p.od[3];
+            const long long i2 = r % p.od[2];
+            r /= p.od[2];
+            const long long i1 = r % p.od[1];
+            const long long i0 = r / p.od[1];
+            p.y[i] = p.x[i0 * p.is[0] + i1 * p.is[1] + i2 * p.is[2] + i3 * p.is[3]];
+        }
+    }
+}
+
+// Batched matrix transpose [batch, R, C] -> [batch, C, R] through a padded shared-memory tile.
+__global__ void __launch_bounds__(256) transpose_tile_kernel(const uint16_t* x, uint16_t* y, long long R, long long C) {
+    __shared__ uint16_t tile[32][33];
+    const long long b = blockIdx.z;
+    const long long c0 = blockIdx.x * 32ll, r0 = blockIdx.y * 32ll;
+    const int tx = threadIdx.x & 31, ty = threadIdx.x >> 5;  // 32 x 8
+    const uint16_t* xb = x + b * R * C;
+    uint16_t* yb = y + b * R * C;
+    for (int k = ty; k < 32; k += 8)
+        if (r0 + k < R && c0 + tx < C) tile[k][tx] = xb[(r0 + k) * C + c0 + tx];
+    __syncthreads();
+    for (int k = ty; k < 32; k += 8)
+        if (c0 + k < C && r0 + tx < R) yb[(c0 + k) * R + r0 + tx] = tile[tx][k];
+}
+
+// Upper-triangular part of the last two dims: y = x where col - row >= diagonal, else 0.
+__global__ void triu_kernel(const __nv_bfloat16* x, __nv_bfloat16* y, long long n, long long R, long long C, int diagonal) {
+    const long long stride = static_cast<long long>(gridDim.x) * blockDim.x;
+    for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < n; i += stride) {
+        const long long c = i % C, r = (i / C) % R;
+        y[i] = (c - r >= diagonal) ? x[i] : __float2bfloat16_rn(0.0f);
+    }
+}
+
+// ---- embedding ---------------------------------------------------------------------------------------
+__global__ void __launch_bounds__(kThreads) embedding_fw_kernel(const uint32_t* ids, const uint16_t* table, uint16_t* out,
+                                                                 long long n_ids, long long dim, long long vocab, int vec) {
+    const long long per_row = vec ? dim / 8 : dim;
+    const long long total = n_ids * per_row;
+    const long long stride = static_cast<long long>(gridDim.x) * blockDim.x;
+    for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < total; i += stride) {
+        const long long r = i / per_row, c = i % per_row;
+        long long id = ids[r];
+        if (id >= vocab) id = vocab - 1;  // clamp instead of reading out of bounds
+        if (vec)
+            reinterpret_cast<uint4*>(out + r * dim)[c] = reinterpret_cast<const uint4*>(table + id * dim)[c];
+        else
+            out[r * dim + c] = table[id * dim + c];
+    }
+}
+__global__ void __launch_bounds__(kThreads) embedding_bw_kernel(const uint32_t* ids, const __nv_bfloat16* dy, float* dtable,
+                                                                 long long n_ids, long long dim, long long vocab) {
+    const long long total = n_ids * dim;
+    const long long stride = static_cast<long long>(gridDim.x) * blockDim.x;
+    for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < total; i += stride) {
+        const long long r = i / dim, c = i % dim;
+        const long long id = ids[r];
+        if (id < vocab) atomicAdd(&dtable[id * dim + c], __bfloat162float(dy[i]));
+    }
+}
+
+inline bool al16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
+
+}  // namespace
+}  // namespace b200
+
+using namespace b200;
+
+extern "C" {
+
+int b200_unary(b200_ctx* ctx, int op, const void* x, void* y, int64_t n, float scalar, void* stream) {
+    B200_REQUIRE(ctx != nullptr, "b200_unary: ctx is NULL");
+    B200_REQUIRE(op >= 0 && op < U_COUNT, "b200_unary: unknown op %d", op);
+    B200_REQUIRE(n >= 0, "b200_unary: negative size");
+    if (n == 0) return B200_OK;
+    B200_REQUIRE(x && y, "b200_unary: NULL buffer");
+    DeviceScope scope(ctx->device);
+    const int vec = al16(x) && al16(y);
+    unary_kernel<<<grid_for(ctx, (n + 7) / 8), kThreads, 0, ctx->pick(stream)>>>(
+        static_cast<const __nv_bfloat16*>(x), static_cast<__nv_bfloat16*>(y), n, op, scalar, vec);
+    B200_CUDA_TRY(cudaGetLastError());
+    return B200_OK;
+}
+
+int b200_binary(b200_ctx* ctx, int op, const void* a, const int64_t* a_shape, const void* b, const int64_t* b_shape, void* out,
+                void* stream) {
+    B200_REQUIRE(ctx != nullptr, "b200_binary: ctx is NULL");
+    B200_REQUIRE(op >= 0 && op < B_COUNT, "b200_binary: unknown op %d", op);
+    B200_REQUIRE(a_shape && b_shape, "b200_binary: NULL shape");
+    BinaryParams p{};
+    long long ad[4], bd[4];
+    p.n = 1;
+    for (int i = 0; i < 4; ++i) {
+        ad[i] = a_shape[i];
+        bd[i] = b_shape[i];
+        B200_REQUIRE(ad[i] >= 0 && bd[i] >= 0, "b200_binary: negative dimension");
+        B200_REQUIRE(ad[i] == bd[i] || ad[i] == 1 || bd[i] == 1, "b200_binary: shapes [%lld,%lld,%lld,%lld] and "
+                     "[%lld,%lld,%lld,%lld] do not broadcast", (long long)a_shape[0], (long long)a_shape[1],
+                     (long long)a_shape[2], (long long)a_shape[3], (long long)b_shape[0], (long long)b_shape[1],
+                     (long long)b_shape[2], (long long)b_shape[3]);
+        p.od[i] = (ad[i] == 1) ? bd[i] : ad[i];
+        p.n *= p.od[i];
+    }
+    if (p.n == 0) return B200_OK;
+    B200_REQUIRE(a && b && out, "b200_binary: NULL buffer");
+    long long sa = 1, sb = 1;
+    for (int i = 3; i >= 0; --i) {
+        p.as[i] = (ad[i] == 1 && p.od[i] != 1) ? 0 : sa;
+        p.bs[i] = (bd[i] == 1 && p.od[i] != 1) ? 0 : sb;
+        sa *= ad[i];
+        sb *= bd[i];
+    }
+    p.a = static_cast<const __nv_bfloat16*>(a);
+    p.b = static_cast<const __nv_bfloat16*>(b);
+    p.out = static_cast<__nv_bfloat16*>(out);
+    p.op = op;
+    auto rows_aligned = [&](const long long* s, const long long* d) {
+        // every row start of the operand must stay 16-byte aligned when its last dim is walked in vectors
+        if (s[3] == 0) return true;
+        return (d[3] % 8) == 0;
+    };
+    p.vec = (p.od[3] % 8 == 0) && al16(a) && al16(b) && al16(out) && rows_aligned(p.as, ad) && rows_aligned(p.bs, bd);
+    DeviceScope scope(ctx->device);
+    binary_kernel<<<grid_for(ctx, p.vec ? p.n / 8 : p.n), kThreads, 0, ctx->pick(stream)>>>(p);
+    B200_CUDA_TRY(cudaGetLastError());
+    return B200_OK;
+}
+
+int b200_reduce(b200_ctx* ctx, int op, const void* x, int64_t outer, int64_t R, int64_t inner, void* y, void* stream) {
+    B200_REQUIRE(ctx != nullptr, "b200_reduce: ctx is NULL");
+    B200_REQUIRE(op >= 0 && op < R_COUNT, "b200_reduce: unknown op %d", op);
+    B200_REQUIRE(outer >= 0 && R >= 1 && inner >= 0, "b200_reduce: bad sizes (outer %lld, R %lld, inner %lld)",
+                 (long long)outer, (long long)R, (long long)inner);
+    if (outer == 0 || inner == 0) return B200_OK;
+    B200_REQUIRE(x && y, "b200_reduce: NULL buffer");
+    DeviceScope scope(ctx->device);
+    cudaStream_t s = ctx->pick(stream);
+    if (inner == 1) {
+        const int vec = al16(x) && (R % 8 == 0);
+        const long long blocks = (outer + 7) / 8;
+        B200_REQUIRE(blocks < (1ll << 31), "b200_reduce: too many rows");
+        reduce_rows_kernel<<<static_cast<unsigned>(blocks), kThreads, 0, s>>>(
+            static_cast<const __nv_bfloat16*>(x), static_cast<__nv_bfloat16*>(y), outer, R, op, vec);
+        B200_CUDA_TRY(cudaGetLastError());
+        return B200_OK;
+    }
+    // column reduction: fp32 accumulators in context scratch, then a cast
+    const long long outs = outer * inner;
+    int rc = ensure_scratch(ctx, static_cast<size_t>(outs) * sizeof(float));
+    if (rc != B200_OK) return rc;
+    float* acc = static_cast<float*>(ctx->d_scratch);
+    fill_f32_kernel<<<grid_for(ctx, outs), kThreads, 0, s>>>(acc, outs, op == R_MAX ? -FLT_MAX : 0.0f);
+    const long long col_blocks = (inner + 31) / 32;
+    long long row_blocks = std::max<long long>(1, std::min<long long>((R + 63) / 64, (ctx->sm_count * 4ll) / std::max<long long>(1, col_blocks * outer)));
+    const long long rows_per = (R + row_blocks - 1) / row_blocks;
+    row_blocks = (R + rows_per - 1) / rows_per;
+    B200_REQUIRE(outer <= 65535 && row_blocks <= 65535, "b200_reduce: outer dimension too large for a column reduction");
+    dim3 grid(static_cast<unsigned>(col_blocks), static_cast<unsigned>(row_blocks), static_cast<unsigned>(outer));
+    reduce_cols_kernel<<<grid, kThreads, 0, s>>>(static_cast<const __nv_bfloat16*>(x), acc, R, inner, op, rows_per);
+    cast_f32_to_bf16_kernel<<<grid_for(ctx, outs), kThreads, 0, s>>>(acc, static_cast<__nv_bfloat16*>(y), outs,
+                                                                     op == R_MEAN ? 1.0f / static_cast<float>(R) : 1.0f);
+    B200_CUDA_TRY(cudaGetLastError());
+    return B200_OK;
+}
+
+int b200_fill(b200_ctx* ctx, void* dst, int64_t n, int dtype, float value, void* stream) {
+    B200_REQUIRE(ctx != nullptr, "b200_fill: ctx is NULL");
+    B200_REQUIRE(n >= 0, "b200_fill: negative size");
+    if (n == 0) return B200_OK;
+    B200_REQUIRE(dst != nullptr, "b200_fill: NULL buffer");
+    DeviceScope scope(ctx->device);
+    cudaStream_t s = ctx->pick(stream);
+    if (dtype == B200_BF16)
+        fill_bf16_kernel<<<grid_for(ctx, n), kThreads, 0, s>>>(static_cast<__nv_bfloat16*>(dst), n, value);
+    else if (dtype == B200_F32)
+        fill_f32_kernel<<<grid_for(ctx, n), kThreads, 0, s>>>(static_cast<float*>(dst), n, value);
+    else if (dtype == B200_U32)
+        fill_u32_kernel<<<grid_for(ctx, n), kThreads, 0, s>>>(static_cast<uint32_t*>(dst), n, static_cast<uint32_t>(value));
+    else
+        return fail(B200_ERR_INVALID_ARG, "b200_fill: unknown dtype %d", dtype);
+    B200_CUDA_TRY(cudaGetLastError());
+    return B200_OK;
+}
+
+int b200_cast(b200_ctx* ctx, const void* src, int src_dtype, void* dst, int dst_dtype, int64_t n, void* stream) {
+    B200_REQUIRE(ctx != nullptr, "b200_cast: ctx is NULL");
+    B200_REQUIRE(n >= 0, "b200_cast: negative size");
+    if (n == 0) return B200_OK;
+    B200_REQUIRE(src && dst, "b200_cast: NULL buffer");
+    DeviceScope scope(ctx->device);
+    cudaStream_t s = ctx->pick(stream);
+    if (src_dtype == B200_F32 && dst_dtype == B200_BF16)
+        cast_f32_to_bf16_kernel<<<grid_for(ctx, n), kThreads, 0, s>>>(static_cast<const float*>(src),
+                                                                      static_cast<__nv_bfloat16*>(dst), n, 1.0f);
+    else if (src_dtype == B200_BF16 && dst_dtype == B200_F32)
+        cast_bf16_to_f32_kernel<<<grid_for(ctx, n), kThreads, 0, s>>>(static_cast<const __nv_bfloat16*>(src),
+                                                                      static_cast<float*>(dst), n);
+    else
+        return fail(B200_ERR_INVALID_ARG, "b200_cast: only f32<->bf16 is supported (got %d -> %d)", src_dtype, dst_dtype);
+    B200_CUDA_TRY(cudaGetLastError());
+    return B200_OK;
+}
+
+int b200_permute(b200_ctx* ctx, const void* x, const int64_t* in_shape, const int32_t* perm, void* y, void* stream) {
+    B200_REQUIRE(ctx != nullptr, "b200_permute: ctx is NULL");
+    B200_REQUIRE(in_shape && perm, "b200_permute: NULL shape or permutation");
+    bool seen[4] = {false, false, false, false};
+    for (int i = 0; i < 4; ++i) {
+        B200_REQUIRE(perm[i] >= 0 && perm[i] < 4 && !seen[perm[i]], "b200_permute: not a permutation of 0..3");
+        seen[perm[i]] = true;
+        B200_REQUIRE(in_shape[i] >= 0, "b200_permute: negative dimension");
+    }
+    long long istr[4];
+    long long s = 1;
+    for (int i = 3; i >= 0; --i) {
+        istr[i] = s;
+        s *= in_shape[i];
+    }
+    PermuteParams p{};
+    p.n = s;
+    if (p.n == 0) return B200_OK;
+    B200_REQUIRE(x && y, "b200_permute: NULL buffer");
+    for (int i = 0; i < 4; ++i) {
+        p.od[i] = in_shape[perm[i]];
+        p.is[i] = istr[perm[i]];
+    }
+    p.x = static_cast<const uint16_t*>(x);
+    p.y = static_cast<uint16_t*>(y);
+    DeviceScope scope(ctx->device);
+    cudaStream_t st = ctx->pick(stream);
+    if (perm[0] == 0 && perm[1] == 1 && perm[2] == 3 && perm[3] == 2 && in_shape[0] * in_shape[1] <= 65535) {
+        const long long R = in_shape[2], Cc = in_shape[3];
+        dim3 grid(static_cast<unsigned>((Cc + 31) / 32), static_cast<unsigned>((R + 31) / 32),
+                  static_cast<unsigned>(in_shape[0] * in_shape[1]));
+        if (grid.y <= 65535) {
+            transpose_tile_kernel<<<grid, 256, 0, st>>>(p.x, p.y, R, Cc);
+            B200_CUDA_TRY(cudaGetLastError());
+            return B200_OK;
+        }
+    }
+    p.vec = (perm[3] == 3) && (p.od[3] % 8 == 0) && al16(x) && al16(y);
+    permute_kernel<<<grid_for(ctx, p.vec ? p.n / 8 : p.n), kThreads, 0, st>>>(p);
+    B200_CUDA_TRY(cudaGetLastError());
+    return B200_OK;
+}
+
+int b200_triu(b200_ctx* ctx, const void* x, void* y, int64_t batch, int64_t rows, int64_t cols, int diagonal, void* stream) {
+    B200_REQUIRE(ctx != nullptr, "b200_triu: ctx is NULL");
+    B200_REQUIRE(batch >= 0 && rows >= 0 && cols >= 0, "b200_triu: negative size");
+    const long long n = batch * rows * cols;
+    if (n == 0) return B200_OK;
+    B200_REQUIRE(x && y, "b200_triu: NULL buffer");
+    DeviceScope scope(ctx->device);
+    triu_kernel<<<grid_for(ctx, n), kThreads, 0, ctx->pick(stream)>>>(static_cast<const __nv_bfloat16*>(x),
+                                                                     static_cast<__nv_bfloat16*>(y), n, rows, cols, diagonal);
+    B200_CUDA_TRY(cudaGetLastError());
+    return B200_OK;
+}
+
+int b200_embedding_forward(b200_ctx* ctx, const uint32_t* ids, int64_t n_ids, const void* table, int64_t vocab, int64_t dim,
+                           void* out, void* stream) {
+    B200_REQUIRE(ctx != nullptr, "b200_embedding_forward: ctx is NULL");
+    B200_REQUIRE(n_ids >= 0 && vocab >= 1 && dim >= 0, "b200_embedding_forward: bad sizes");
+    if (n_ids == 0 || dim == 0) return B200_OK;
+    B200_REQUIRE(ids && table && out, "b200_embedding_forward: NULL buffer");
+    DeviceScope scope(ctx->device);
+    const int vec = (dim % 8 == 0) && al16(table) && al16(out);
+    embedding_fw_kernel<<<grid_for(ctx, n_ids * (vec ? dim / 8 : dim)), kThreads, 0, ctx->pick(stream)>>>(
+        ids, static_cast<const uint16_t*>(table), static_cast<uint16_t*>(out), n_ids, dim, vocab, vec);
+    B200_CUDA_TRY(cudaGetLastError());
+    return B200_OK;
+}
+
+int b200_embedding_backward(b200_ctx* ctx, const uint32_t* ids, int64_t n_ids, const void* dy, int64_t vocab, int64_t dim,
+                            float* d_table_f32, void* stream) {
+    B200_REQUIRE(ctx != nullptr, "b200_embedding_backward: ctx is NULL");
+    B200_REQUIRE(n_ids >= 0 && vocab >= 1 && dim >= 0, "b200_embedding_backward: bad sizes");
+    if (dim == 0) return B200_OK;
+    B200_REQUIRE(d_table_f32 != nullptr, "b200_embedding_backward: NULL output");
+    DeviceScope scope(ctx->device);
+    cudaStream_t s = ctx->pick(stream);
+    B200_CUDA_TRY(cudaMemsetAsync(d_table_f32, 0, sizeof(float) * vocab * dim, s));
+    if (n_ids == 0) return B200_OK;
+    B200_REQUIRE(ids && dy, "b200_embedding_backward: NULL buffer");
+    embedding_bw_kernel<<<grid_for(ctx, n_ids * dim), kThreads, 0, s>>>(ids, static_cast<const __nv_bfloat16*>(dy),
+                                                                        d_table_f32, n_ids, dim, vocab);
+    B200_CUDA_TRY(cudaGetLastError());
+    return B200_OK;
+}
+
+}  // extern "C"

@@ -1,0 +1,725 @@
+// Row-wise, HBM-bandwidth-bound kernels: softmax / log-softmax (forward and backward), fused
+// cross-entropy (loss + d_logits in one pass over the logits) and LayerNorm (forward and backward).
+//
+// Layout: [rows, cols] bf16, row-major with a leading dimension. Rows of up to 1024 columns are
+// handled by one warp each, the whole row held in registers between the reduction and the write
+// (one read + one write of HBM per element); longer rows (vocabulary-sized) by one 256-thread CTA
+// each, with an online max/sum pass followed by a write pass whose re-read is served by L2.
+// All global accesses are 16-byte vectors when the row starts are 16-byte aligned, reductions are
+// warp shuffles, arithmetic is fp32.
+#include "common.cuh"
+#include "gemm_common.cuh"
+
+#include <algorithm>
+#include <cfloat>
+
+namespace b200 {
+namespace {
+
+constexpr int kWarp = 32;
+constexpr int kBlock = 256;
+
+__device__ __forceinline__ float warp_sum(float v) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+    return v;
+}
+__device__ __forceinline__ float warp_max(float v) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
+    return v;
+}
+__device__ __forceinline__ float block_sum(float v, float* sh) {
+    v = warp_sum(v);
+    const int w = threadIdx.x >> 5, l = threadIdx.x & 31;
+    __syncthreads();
+    if (l == 0) sh[w] = v;
+    __syncthreads();
+    float t = (threadIdx.x < (blockDim.x >> 5)) ? sh[threadIdx.x] : 0.0f;
+    if (w == 0) t = warp_sum(t);
+    if (threadIdx.x == 0) sh[0] = t;
+    __syncthreads();
+    return sh[0];
+}
+__device__ __forceinline__ float block_max(float v, float* sh) {
+    v = warp_max(v);
+    const int w = threadIdx.x >> 5, l = threadIdx.x & 31;
+    __syncthreads();
+    if (l == 0) sh[w] = v;
+    __syncthreads();
+    float t = (threadIdx.x < (blockDim.x >> 5)) ? sh[threadIdx.x] : -FLT_MAX;
+    if (w == 0) t = warp_max(t);
+    if (threadIdx.x == 0) sh[0] = t;
+    __syncthreads();
+    return sh[0];
+}
+
+// 8 consecutive bf16 of a row starting at column c (c % 8 == 0) -> fp32; columns >= cols read as `fill`.
+__device__ __forceinline__ void load8(const __nv_bfloat16* row, int c, int cols, bool vec_ok, float fill, float (&f)[8]) {
+    if (vec_ok && c + 8 <= cols) {
+        const uint4 u = *reinterpret_cast<const uint4*>(row + c);
+        const uint32_t w[4] = {u.x, u.y, u.z, u.w};
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            f[2 * i] = __uint_as_float(w[i] << 16);
+            f[2 * i + 1] = __uint_as_float(w[i] & 0xffff0000u);
+        }
+    } else {
+#pragma unroll
+        for (int i = 0; i < 8; ++i) f[i] = (c + i < cols) ? __bfloat162float(row[c + i]) : fill;
+    }
+}
+__device__ __forceinline__ void store8(__nv_bfloat16* row, int c, int cols, bool vec_ok, const float (&f)[8]) {
+    if (vec_ok && c + 8 <= cols) {
+        *reinterpret_cast<uint4*>(row + c) = make_uint4(pack_bf16x2(f[0], f[1]), pack_bf16x2(f[2], f[3]),
+                                                        pack_bf16x2(f[4], f[5]), pack_bf16x2(f[6], f[7]));
+    } else {
+#pragma unroll
+        for (int i = 0; i < 8; ++i)
+            if (c + i < cols) row[c + i] = __float2bfloat16_rn(f[i]);
+    }
+}
+__device__ __forceinline__ void load8f(const float* row, int c, int cols, bool vec_ok, float fill, float (&f)[8]) {
+    if (vec_ok && c + 8 <= cols) {
+        const float4 a = *reinterpret_cast<const float4*>(row + c);
+        const float4 b = *reinterpret_cast<const float4*>(row + c + 4);
+        f[0] = a.x; f[1] = a.y; f[2] = a.z; f[3] = a.w; f[4] = b.x; f[5] = b.y; f[6] = b.z; f[7] = b.w;
+    } else {
+#pragma unroll
+        for (int i = 0; i < 8; ++i) f[i] = (c + i < cols) ? row[c + i] : fill;
+    }
+}
+
+enum RowOp : int {
+    OP_SOFTMAX = 0,         // y = softmax(alpha * x [causal])
+    OP_LOG_SOFTMAX = 1,     // y = log softmax(x)
+    OP_SOFTMAX_BW = 2,      // dx = alpha * y * (dy - sum(dy * y))          in0 = dy, in1 = y
+    OP_LOG_SOFTMAX_BW = 3,  // dx = dy - exp(logy) * sum(dy)                in0 = dy, in1 = logy
+    OP_CROSS_ENTROPY = 4    // loss_row = -log softmax(x)[label]; dx = (softmax(x) - onehot) * alpha
+};
+
+struct RowParams {
+    const __nv_bfloat16* in0;
+    const __nv_bfloat16* in1;
+    __nv_bfloat16* out;       // may be nullptr for OP_CROSS_ENTROPY (loss only)
+    long long ld0, ld1, ldo;
+    int rows, cols;
+    float alpha;
+    int causal_period;        // > 0: row r may only see columns <= r % causal_period
+    const uint32_t* labels;   // OP_CROSS_ENTROPY
+    float* row_loss;          // OP_CROSS_ENTROPY: per-row loss (fp32) or nullptr
+    float* loss_sum;          // OP_CROSS_ENTROPY: atomically accumulated alpha-scaled loss, or nullptr
+    int vec0, vec1, veco;     // 16-byte access legal for in0 / in1 / out
+};
+
+__device__ __forceinline__ int visible_cols(const RowParams& p, int r) {
+    return p.causal_period > 0 ? min(p.cols, (r % p.causal_period) + 1) : p.cols;
+}
+
+// ---- one warp per row, row held in registers: cols <= 256 * VPL --------------------------------------
+template <int VPL, int OP>
+__global__ void __launch_bounds__(kBlock) row_warp_kernel(const RowParams p) {
+    const int lane = threadIdx.x & 31;
+    const int r = blockIdx.x * (kBlock / kWarp) + (threadIdx.x >> 5);
+    if (r >= p.rows) return;
+    const __nv_bfloat16* x0 = p.in0 + static_cast<size_t>(r) * p.ld0;
+    float a[VPL][8];
+    if (OP == OP_SOFTMAX || OP == OP_LOG_SOFTMAX || OP == OP_CROSS_ENTROPY) {
+        const int vis = visible_cols(p, r);
+        const float scale = (OP == OP_SOFTMAX) ? p.alpha : 1.0f;
+        float m = -FLT_MAX;
+#pragma unroll
+        for (int j = 0; j < VPL; ++j) {
+            const int c = (j * kWarp + lane) * 8;
+            load8(x0, c, vis, p.vec0 != 0, -FLT_MAX, a[j]);
+#pragma unroll
+            for (int i = 0; i < 8; ++i) {
+                a[j][i] = (c + i < vis) ? a[j][i] * scale : -FLT_MAX;
+                m = fmaxf(m, a[j][i]);
+            }
+        }
+        m = warp_max(m);
+        float s = 0.0f;
+#pragma unroll
+        for (int j = 0; j < VPL; ++j)
+#pragma unroll
+            for (int i = 0; i < 8; ++i) {
+                const float e = (a[j][i] == -FLT_MAX) ? 0.0f : __expf(a[j][i] - m);
+                if (OP == OP_LOG_SOFTMAX) a[j][i] -= m; else a[j][i] = e;
+                s += e;
+            }
+        s = warp_sum(s);
+        if (OP == OP_SOFTMAX) {
+            const float inv = 1.0f / s;
+            __nv_bfloat16* y = p.out + static_cast<size_t>(r) * p.ldo;
+#pragma unroll
+            for (int j = 0; j < VPL; ++j) {
+                const int c = (j * kWarp + lane) * 8;
+#pragma unroll
+                for (int i = 0; i < 8; ++i) a[j][i] *= inv;
+                if (c < p.cols) store8(y, c, p.cols, p.veco != 0, a[j]);
+            }
+        } else if (OP == OP_LOG_SOFTMAX) {
+            const float ls = __logf(s);
+            __nv_bfloat16* y = p.out + static_cast<size_t>(r) * p.ldo;
+#pragma unroll
+            for (int j = 0; j < VPL; ++j) {
+                const int c = (j * kWarp + lane) * 8;
+#pragma unroll
+                for (int i = 0; i < 8; ++i) a[j][i] -= ls;
+                if (c < p.cols) store8(y, c, p.cols, p.veco != 0, a[j]);
+            }
+        } else {  // cross-entropy
+            const int label = static_cast<int>(p.labels[r]);
+            const float inv = 1.0f / s;
+            float picked = 0.0f;
+#pragma unroll
+            for (int j = 0; j < VPL; ++j) {
+                const int c = (j * kWarp + lane) * 8;
+#pragma unroll
+                for (int i = 0; i < 8; ++i) {
+                    const float prob = a[j][i] * inv;
+                    if (c + i == label) picked = prob;
+                    a[j][i] = (prob - ((c + i == label) ? 1.0f : 0.0f)) * p.alpha;
+                }
+                if (p.out != nullptr && c < p.cols)
+                    store8(p.out + static_cast<size_t>(r) * p.ldo, c, p.cols, p.veco != 0, a[j]);
+            }
+            picked = warp_sum(picked);  // exactly one lane holds the label column
+            if (lane == 0) {
+                const float loss = -__logf(fmaxf(picked, 1e-38f));
+                if (p.row_loss) p.row_loss[r] = loss;
+                if (p.loss_sum) atomicAdd(p.loss_sum, loss * p.alpha);
+            }
+        }
+    } else {
+        const __nv_bfloat16* x1 = p.in1 + static_cast<size_t>(r) * p.ld1;
+        float b[VPL][8];
+        float dot = 0.0f;
+#pragma unroll
+        for (int j = 0; j < VPL; ++j) {
+            const int c = (j * kWarp + lane) * 8;
+            load8(x0, c, p.cols, p.vec0 != 0, 0.0f, a[j]);
+            load8(x1, c, p.cols, p.vec1 != 0, 0.0f, b[j]);
+#pragma unroll
+            for (int i = 0; i < 8; ++i) dot += (OP == OP_SOFTMAX_BW) ? a[j][i] * b[j][i] : a[j][i];
+        }
+        dot = warp_sum(dot);
+        __nv_bfloat16* y = p.out + static_cast<size_t>(r) * p.ldo;
+#pragma unroll
+        for (int j = 0; j < VPL; ++j) {
+            const int c = (j * kWarp + lane) * 8;
+#pragma unroll
+            for (int i = 0; i < 8; ++i)
+                a[j][i] = (OP == OP_SOFTMAX_BW) ? p.alpha * b[j][i] * (a[j][i] - dot)
+                                                : a[j][i] - ((c + i < p.cols) ? __expf(b[j][i]) : 0.0f) * dot;
+            if (c < p.cols) store8(y, c, p.cols, p.veco != 0, a[j]);
+        }
+    }
+}
+
+// ---- one CTA per row, any length: online max/sum pass, then a write pass (re-read hits L2) -----------
+template <int OP>
+__global__ void __launch_bounds__(kBlock) row_block_kernel(const RowParams p) {
+    __shared__ float sh[kBlock / kWarp];
+    const int r = blockIdx.x;
+    const __nv_bfloat16* x0 = p.in0 + static_cast<size_t>(r) * p.ld0;
+    const int nvec = (p.cols + 7) / 8;
+    if (OP == OP_SOFTMAX || OP == OP_LOG_SOFTMAX || OP == OP_CROSS_ENTROPY) {
+        const int vis = visible_cols(p, r);
+        const float scale = (OP == OP_SOFTMAX) ? p.alpha : 1.0f;
+        float m = -FLT_MAX, s = 0.0f;  // running max and sum of exp(x - m)
+        for (int v = threadIdx.x; v < nvec; v += kBlock) {
+            float f[8];
+            load8(x0, v * 8, vis, p.vec0 != 0, -FLT_MAX, f);
+            float lm = m;
+#pragma unroll
+            for (int i = 0; i < 8; ++i) {
+                f[i] = (v * 8 + i < vis) ? f[i] * scale : -FLT_MAX;
+                lm = fmaxf(lm, f[i]);
+            }
+            if (lm > m) {
+                s *= __expf(m - lm);
+                m = lm;
+            }
+#pragma unroll
+            for (int i = 0; i < 8; ++i) s += (f[i] == -FLT_MAX) ? 0.0f : __expf(f[i] - m);
+        }
+        const float gm = block_max(m, sh);
+        s = (m == -FLT_MAX) ? 0.0f : s * __expf(m - gm);
+        const float gs = block_sum(s, sh);
+        const float inv = 1.0f / gs, ls = __logf(gs);
+        const int label = (OP == OP_CROSS_ENTROPY) ? static_cast<int>(p.labels[r]) : -1;
+        float picked = 0.0f;
+        __nv_bfloat16* y = p.out ? p.out + static_cast<size_t>(r) * p.ldo : nullptr;
+        for (int v = threadIdx.x; v < nvec; v += kBlock) {
+            float f[8];
+            load8(x0, v * 8, vis, p.vec0 != 0, -FLT_MAX, f);
+#pragma unroll
+            for (int i = 0; i < 8; ++i) {
+                const int c = v * 8 + i;
+                const float xs = (c < vis) ? f[i] * scale : -FLT_MAX;
+                const float e = (xs == -FLT_MAX) ? 0.0f : __expf(xs - gm);
+                if (OP == OP_SOFTMAX) {
+                    f[i] = e * inv;
+                } else if (OP == OP_LOG_SOFTMAX) {
+                    f[i] = xs - gm - ls;
+                } else {
+                    const float prob = e * inv;
+                    if (c == label) picked = prob;
+                    f[i] = (prob - ((c == label) ? 1.0f : 0.0f)) * p.alpha;
+                }
+            }
+            if (y) store8(y, v * 8, p.cols, p.veco != 0, f);
+        }
+        if (OP == OP_CROSS_ENTROPY) {
+            picked = block_sum(picked, sh);
+            if (threadIdx.x == 0) {
+                const float loss = -__logf(fmaxf(picked, 1e-38f));
+                if (p.row_loss) p.row_loss[r] = loss;
+                if (p.loss_sum) atomicAdd(p.loss_sum, loss * p.alpha);
+            }
+        }
+    } else {
+        const __nv_bfloat16* x1 = p.in1 + static_cast<size_t>(r) * p.ld1;
+        float dot = 0.0f;
+        for (int v = threadIdx.x; v < nvec; v += kBlock) {
+            float a[8], b[8];
+            load8(x0, v * 8, p.cols, p.vec0 != 0, 0.0f, a);
+            if (OP == OP_SOFTMAX_BW) load8(x1, v * 8, p.cols, p.vec1 != 0, 0.0f, b);
+#pragma unroll
+            for (int i = 0; i < 8; ++i) dot += (OP == OP_SOFTMAX_BW) ? a[i] * b[i] : a[i];
+        }
+        dot = block_sum(dot, sh);
+        __nv_bfloat16* y = p.out + static_cast<size_t>(r) * p.ldo;
+        for (int v = threadIdx.x; v < nvec; v += kBlock) {
+            float a[8], b[8];
+            load8(x0, v * 8, p.cols, p.vec0 != 0, 0.0f, a);
+            load8(x1, v * 8, p.cols, p.vec1 != 0, 0.0f, b);
+#pragma unroll
+            for (int i = 0; i < 8; ++i)
+                a[i] = (OP == OP_SOFTMAX_BW) ? p.alpha * b[i] * (a[i] - dot) : a[i] - __expf(b[i]) * dot;
+            store8(y, v * 8, p.cols, p.veco != 0, a);
+        }
+    }
+}
+
+template <int OP>
+int launch_row_op(const RowParams& p, cudaStream_t stream) {
+    if (p.rows == 0 || p.cols == 0) return B200_OK;
+    if (p.cols <= 1024) {
+        const int blocks = (p.rows + (kBlock / kWarp) - 1) / (kBlock / kWarp);
+        if (p.cols <= 256)
+            row_warp_kernel<1, OP><<<blocks, kBlock, 0, stream>>>(p);
+        else if (p.cols <= 512)
+            row_warp_kernel<2, OP><<<blocks, kBlock, 0, stream>>>(p);
+        else
+            row_warp_kernel<4, OP><<<blocks, kBlock, 0, stream>>>(p);
+    } else {
+        row_block_kernel<OP><<<p.rows, kBlock, 0, stream>>>(p);
+    }
+    B200_CUDA_TRY(cudaGetLastError());
+    return B200_OK;
+}
+
+inline int vec_ok(const void* p, long long ld) { return ((reinterpret_cast<uintptr_t>(p) & 15u) == 0 && (ld & 7) == 0) ? 1 : 0; }
+
+int check_rows(const char* who, const void* a, long long lda, long long rows, long long cols) {
+    B200_REQUIRE(rows >= 0 && cols >= 0, "%s: negative size", who);
+    B200_REQUIRE(rows < (1ll << 31) && cols < (1ll << 31), "%s: size too large", who);
+    if (rows == 0 || cols == 0) return B200_OK;
+    B200_REQUIRE(a != nullptr, "%s: NULL buffer", who);
+    B200_REQUIRE(lda >= cols, "%s: leading dimension %lld < cols %lld", who, lda, cols);
+    return B200_OK;
+}
+
+// ---- LayerNorm -------------------------------------------------------------------------------------
+// Forward: one warp per row for cols <= 2048 (row in registers), else one CTA per row.
+template <int VPL>
+__global__ void __launch_bounds__(kBlock) layernorm_fw_warp_kernel(const __nv_bfloat16* x, long long ldx,
+                                                                    const __nv_bfloat16* gamma, const __nv_bfloat16* beta,
+                                                                    __nv_bfloat16* y, long long ldy, float* mean_out,
+                                                                    float* rstd_out, int rows, int cols, float eps, int vx,
+                                                                    int vy, int vg) {
+    const int lane = threadIdx.x & 31;
+    const int r = blockIdx.x * (kBlock / kWarp) + (threadIdx.x >> 5);
+    if (r >= rows) return;
+    const __nv_bfloat16* xr = x + static_cast<size_t>(r) * ldx;
+    float a[VPL][8];
+    float s = 0.0f;
+#pragma unroll
+    for (int j = 0; j < VPL; ++j) {
+        load8(xr, (j * kWarp + lane) * 8, cols, vx != 0, 0.0f, a[j]);
+#pragma unroll
+        for (int i = 0; i < 8; ++i) s += a[j][i];
+    }
+    const float mean = warp_sum(s) / cols;
+    float q = 0.0f;
+#pragma unroll
+    for (int j = 0; j < VPL; ++j)
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+            const float d = ((j * kWarp + lane) * 8 + i < cols) ? a[j][i] - mean : 0.0f;
+            q += d * d;
+        }
+    const float rstd = rsqrtf(warp_sum(q) / cols + eps);
+    if (lane == 0) {
+        if (mean_out) mean_out[r] = mean;
+        if (rstd_out) rstd_out[r] = rstd;
+    }
+    __nv_bfloat16* yr = y + static_cast<size_t>(r) * ldy;
+#pragma unroll
+    for (int j = 0; j < VPL; ++j) {
+        const int c = (j * kWarp + lane) * 8;
+        if (c >= cols) continue;
+        float g[8], b[8];
+        load8(gamma, c, cols, vg != 0, 1.0f, g);
+        load8(beta, c, cols, vg != 0, 0.0f, b);
+#pragma unroll
+        for (int i = 0; i < 8; ++i) a[j][i] = (a[j][i] - mean) * rstd * g[i] + b[i];
+        store8(yr, c, cols, vy != 0, a[j]);
+    }
+}
+
+__global__ void __launch_bounds__(kBlock) layernorm_fw_block_kernel(const __nv_bfloat16* x, long long ldx,
+                                                                     const __nv_bfloat16* gamma, const __nv_bfloat16* beta,
+                                                                     __nv_bfloat16* y, long long ldy, float* mean_out,
+                                                                     float* rstd_out, int rows, int cols, float eps, int vx,
+                                                                     int vy, int vg) {
+    __shared__ float sh[kBlock / kWarp];
+    const int r = blockIdx.x;
+    const __nv_bfloat16* xr = x + static_cast<size_t>(r) * ldx;
+    const int nvec = (cols + 7) / 8;
+    float s = 0.0f;
+    for (int v = threadIdx.x; v < nvec; v += kBlock) {
+        float f[8];
+        load8(xr, v * 8, cols, vx != 0, 0.0f, f);
+#pragma unroll
+        for (int i = 0; i < 8; ++i) s += f[i];
+    }
+    const float mean = block_sum(s, sh) / cols;
+    float q = 0.0f;
+    for (int v = threadIdx.x; v < nvec; v += kBlock) {
+        float f[8];
+        load8(xr, v * 8, cols, vx != 0, 0.0f, f);
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+            const float d = (v * 8 + i < cols) ? f[i] - mean : 0.0f;
+            q += d * d;
+        }
+    }
+    const float rstd = rsqrtf(block_sum(q, sh) / cols + eps);
+    if (threadIdx.x == 0) {
+        if (mean_out) mean_out[r] = mean;
+        if (rstd_out) rstd_out[r] = rstd;
+    }
+    __nv_bfloat16* yr = y + static_cast<size_t>(r) * ldy;
+    for (int v = threadIdx.x; v < nvec; v += kBlock) {
+        float f[8], g[8], b[8];
+        load8(xr, v * 8, cols, vx != 0, 0.0f, f);
+        load8(gamma, v * 8, cols, vg != 0, 1.0f, g);
+        load8(beta, v * 8, cols, vg != 0, 0.0f, b);
+#pragma unroll
+        for (int i = 0; i < 8; ++i) f[i] = (f[i] - mean) * rstd * g[i] + b[i];
+        store8(yr, v * 8, cols, vy != 0, f);
+    }
+}
+
+// Backward, input gradient: dx = rstd * (g - mean(g) - xhat * mean(g * xhat)), g = dy * gamma. One warp per row
+// (cols <= 2048) or one CTA per row.
+template <int VPL>
+__global__ void __launch_bounds__(kBlock) layernorm_bw_dx_warp_kernel(const __nv_bfloat16* dy, long long lddy,
+                                                                       const __nv_bfloat16* x, long long ldx,
+                                                                       const __nv_bfloat16* gamma, const float* mean,
+                                                                       const float* rstd, __nv_bfloat16* dx, long long lddx,
+                                                                       int rows, int cols, int vdy, int vx, int vdx, int vg) {
+    const int lane = threadIdx.x & 31;
+    const int r = blockIdx.x * (kBlock / kWarp) + (threadIdx.x >> 5);
+    if (r >= rows) return;
+    const float mu = mean[r], rs = rstd[r];
+    float g[VPL][8], xh[VPL][8];
+    float s1 = 0.0f, s2 = 0.0f;
+#pragma unroll
+    for (int j = 0; j < VPL; ++j) {
+        const int c = (j * kWarp + lane) * 8;
+        float gm[8];
+        load8(dy + static_cast<size_t>(r) * lddy, c, cols, vdy != 0, 0.0f, g[j]);
+        load8(x + static_cast<size_t>(r) * ldx, c, cols, vx != 0, 0.0f, xh[j]);
+        load8(gamma, c, cols, vg != 0, 0.0f, gm);
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+            const bool in = c + i < cols;
+            xh[j][i] = in ? (xh[j][i] - mu) * rs : 0.0f;
+            g[j][i] = in ? g[j][i] * gm[i] : 0.0f;
+            s1 += g[j][i];
+            s2 += g[j][i] * xh[j][i];
+        }
+    }
+    s1 = warp_sum(s1) / cols;
+    s2 = warp_sum(s2) / cols;
+#pragma unroll
+    for (int j = 0; j < VPL; ++j) {
+        const int c = (j * kWarp + lane) * 8;
+        if (c >= cols) continue;
+#pragma unroll
+        for (int i = 0; i < 8; ++i) g[j][i] = rs * (g[j][i] - s1 - xh[j][i] * s2);
+        store8(dx + static_cast<size_t>(r) * lddx, c, cols, vdx != 0, g[j]);
+    }
+}
+
+__global__ void __launch_bounds__(kBlock) layernorm_bw_dx_block_kernel(const __nv_bfloat16* dy, long long lddy,
+                                                                        const __nv_bfloat16* x, long long ldx,
+                                                                        const __nv_bfloat16* gamma, const float* mean,
+                                                                        const float* rstd, __nv_bfloat16* dx, long long lddx,
+                                                                        int rows, int cols, int vdy, int vx, int vdx, int vg) {
+    __shared__ float sh[kBlock / kWarp];
+    const int r = blockIdx.x;
+    const float mu = mean[r], rs = rstd[r];
+    const int nvec = (cols + 7) / 8;
+    float s1 = 0.0f, s2 = 0.0f;
+    for (int v = threadIdx.x; v < nvec; v += kBlock) {
+        float g[8], xv[8], gm[8];
+        load8(dy + static_cast<size_t>(r) * lddy, v * 8, cols, vdy != 0, 0.0f, g);
+        load8(x + static_cast<size_t>(r) * ldx, v * 8, cols, vx != 0, 0.0f, xv);
+        load8(gamma, v * 8, cols, vg != 0, 0.0f, gm);
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+            if (v * 8 + i < cols) {
+                const float gg = g[i] * gm[i];
+                s1 += gg;
+                s2 += gg * (xv[i] - mu) * rs;
+            }
+        }
+    }
+    s1 = block_sum(s1, sh) / cols;
+    s2 = block_sum(s2, sh) / cols;
+    for (int v = threadIdx.x; v < nvec; v += kBlock) {
+        float g[8], xv[8], gm[8];
+        load8(dy + static_cast<size_t>(r) * lddy, v * 8, cols, vdy != 0, 0.0f, g);
+        load8(x + static_cast<size_t>(r) * ldx, v * 8, cols, vx != 0, 0.0f, xv);
+        load8(gamma, v * 8, cols, vg != 0, 0.0f, gm);
+#pragma unroll
+        for (int i = 0; i < 8; ++i) g[i] = rs * (g[i] * gm[i] - s1 - (xv[i] - mu) * rs * s2);
+        store8(dx + static_cast<size_t>(r) * lddx, v * 8, cols, vdx != 0, g);
+    }
+}
+
+// Backward, parameter gradients: dgamma[c] = sum_r dy[r,c] * xhat[r,c], dbeta[c] = sum_r dy[r,c].
+// Each CTA owns 64 columns and a slab of rows; partial sums are combined with fp32 atomics into
+// zero-initialised fp32 accumulators, which a second tiny kernel converts to bf16.
+__global__ void __launch_bounds__(256) layernorm_bw_param_kernel(const __nv_bfloat16* dy, long long lddy,
+                                                                  const __nv_bfloat16* x, long long ldx, const float* mean,
+                                                                  const float* rstd, float* dgamma_acc, float* dbeta_acc,
+                                                                  int rows, int cols, int rows_per_cta) {
+    __shared__ float sg[4][64], sb[4][64];
+    const int c = blockIdx.x * 64 + (threadIdx.x & 63);
+    const int sub = threadIdx.x >> 6;  // 4 row lanes
+    const int r0 = blockIdx.y * rows_per_cta;
+    const int r1 = min(rows, r0 + rows_per_cta);
+    float ag = 0.0f, ab = 0.0f;
+    if (c < cols) {
+        for (int r = r0 + sub; r < r1; r += 4) {
+            const float d = __bfloat162float(dy[static_cast<size_t>(r) * lddy + c]);
+            const float xv = __bfloat162float(x[static_cast<size_t>(r) * ldx + c]);
+            ab += d;
+            if (dgamma_acc) ag += d * (xv - mean[r]) * rstd[r];
+        }
+    }
+    sg[sub][threadIdx.x & 63] = ag;
+    sb[sub][threadIdx.x & 63] = ab;
+    __syncthreads();
+    if (sub == 0 && c < cols) {
+        const int t = threadIdx.x;
+        if (dgamma_acc) atomicAdd(&dgamma_acc[c], sg[0][t] + sg[1][t] + sg[2][t] + sg[3][t]);
+        if (dbeta_acc) atomicAdd(&dbeta_acc[c], sb[0][t] + sb[1][t] + sb[2][t] + sb[3][t]);
+    }
+}
+
+}  // namespace
+}  // namespace b200
+
+using namespace b200;
+
+extern "C" {
+
+int b200_softmax(b200_ctx* ctx, const void* x, int64_t ldx, void* y, int64_t ldy, int64_t rows, int64_t cols, float alpha,
+                 int64_t causal_period, void* stream) {
+    B200_REQUIRE(ctx != nullptr, "b200_softmax: ctx is NULL");
+    int rc = check_rows("b200_softmax", x, ldx, rows, cols);
+    if (rc == B200_OK) rc = check_rows("b200_softmax", y, ldy, rows, cols);
+    if (rc != B200_OK) return rc;
+    B200_REQUIRE(causal_period >= 0, "b200_softmax: causal_period must be >= 0");
+    RowParams p{};
+    p.in0 = static_cast<const __nv_bfloat16*>(x);
+    p.out = static_cast<__nv_bfloat16*>(y);
+    p.ld0 = ldx;
+    p.ldo = ldy;
+    p.rows = static_cast<int>(rows);
+    p.cols = static_cast<int>(cols);
+    p.alpha = alpha;
+    p.causal_period = static_cast<int>(causal_period);
+    p.vec0 = vec_ok(x, ldx);
+    p.veco = vec_ok(y, ldy);
+    DeviceScope scope(ctx->device);
+    return launch_row_op<OP_SOFTMAX>(p, ctx->pick(stream));
+}
+
+int b200_log_softmax(b200_ctx* ctx, const void* x, int64_t ldx, void* y, int64_t ldy, int64_t rows, int64_t cols,
+                     void* stream) {
+    B200_REQUIRE(ctx != nullptr, "b200_log_softmax: ctx is NULL");
+    int rc = check_rows("b200_log_softmax", x, ldx, rows, cols);
+    if (rc == B200_OK) rc = check_rows("b200_log_softmax", y, ldy, rows, cols);
+    if (rc != B200_OK) return rc;
+    RowParams p{};
+    p.in0 = static_cast<const __nv_bfloat16*>(x);
+    p.out = static_cast<__nv_bfloat16*>(y);
+    p.ld0 = ldx;
+    p.ldo = ldy;
+    p.rows = static_cast<int>(rows);
+    p.cols = static_cast<int>(cols);
+    p.alpha = 1.0f;
+    p.vec0 = vec_ok(x, ldx);
+    p.veco = vec_ok(y, ldy);
+    DeviceScope scope(ctx->device);
+    return launch_row_op<OP_LOG_SOFTMAX>(p, ctx->pick(stream));
+}
+
+static int row_backward(b200_ctx* ctx, const char* who, bool log_form, const void* dy, int64_t lddy, const void* y,
+                        int64_t ldy, void* dx, int64_t lddx, int64_t rows, int64_t cols, float alpha, void* stream) {
+    B200_REQUIRE(ctx != nullptr, "%s: ctx is NULL", who);
+    int rc = check_rows(who, dy, lddy, rows, cols);
+    if (rc == B200_OK) rc = check_rows(who, y, ldy, rows, cols);
+    if (rc == B200_OK) rc = check_rows(who, dx, lddx, rows, cols);
+    if (rc != B200_OK) return rc;
+    RowParams p{};
+    p.in0 = static_cast<const __nv_bfloat16*>(dy);
+    p.in1 = static_cast<const __nv_bfloat16*>(y);
+    p.out = static_cast<__nv_bfloat16*>(dx);
+    p.ld0 = lddy;
+    p.ld1 = ldy;
+    p.ldo = lddx;
+    p.rows = static_cast<int>(rows);
+    p.cols = static_cast<int>(cols);
+    p.alpha = alpha;
+    p.vec0 = vec_ok(dy, lddy);
+    p.vec1 = vec_ok(y, ldy);
+    p.veco = vec_ok(dx, lddx);
+    DeviceScope scope(ctx->device);
+    return log_form ? launch_row_op<OP_LOG_SOFTMAX_BW>(p, ctx->pick(stream))
+                    : launch_row_op<OP_SOFTMAX_BW>(p, ctx->pick(stream));
+}
+
+int b200_softmax_backward(b200_ctx* ctx, const void* dy, int64_t lddy, const void* y, int64_t ldy, void* dx, int64_t lddx,
+                          int64_t rows, int64_t cols, float alpha, void* stream) {
+    return row_backward(ctx, "b200_softmax_backward", false, dy, lddy, y, ldy, dx, lddx, rows, cols, alpha, stream);
+}
+
+int b200_log_softmax_backward(b200_ctx* ctx, const void* dy, int64_t lddy, const void* log_y, int64_t ldy, void* dx,
+                              int64_t lddx, int64_t rows, int64_t cols, void* stream) {
+    return row_backward(ctx, "b200_log_softmax_backward", true, dy, lddy, log_y, ldy, dx, lddx, rows, cols, 1.0f, stream);
+}
+
+int b200_cross_entropy(b200_ctx* ctx, const void* logits, int64_t ld, const uint32_t* labels, int64_t rows, int64_t classes,
+                       float grad_scale, float* loss_sum, float* row_loss, void* d_logits, int64_t ldd, void* stream) {
+    B200_REQUIRE(ctx != nullptr, "b200_cross_entropy: ctx is NULL");
+    int rc = check_rows("b200_cross_entropy", logits, ld, rows, classes);
+    if (rc != B200_OK) return rc;
+    if (d_logits) {
+        rc = check_rows("b200_cross_entropy", d_logits, ldd, rows, classes);
+        if (rc != B200_OK) return rc;
+    }
+    if (rows == 0 || classes == 0) return B200_OK;
+    B200_REQUIRE(labels != nullptr, "b200_cross_entropy: labels is NULL");
+    RowParams p{};
+    p.in0 = static_cast<const __nv_bfloat16*>(logits);
+    p.out = static_cast<__nv_bfloat16*>(d_logits);
+    p.ld0 = ld;
+    p.ldo = ldd;
+    p.rows = static_cast<int>(rows);
+    p.cols = static_cast<int>(classes);
+    p.alpha = grad_scale;
+    p.labels = labels;
+    p.row_loss = row_loss;
+    p.loss_sum = loss_sum;
+    p.vec0 = vec_ok(logits, ld);
+    p.veco = d_logits ? vec_ok(d_logits, ldd) : 0;
+    DeviceScope scope(ctx->device);
+    if (loss_sum) B200_CUDA_TRY(cudaMemsetAsync(loss_sum, 0, sizeof(float), ctx->pick(stream)));
+    return launch_row_op<OP_CROSS_ENTROPY>(p, ctx->pick(stream));
+}
+
+int b200_layernorm_forward(b200_ctx* ctx, const void* x, int64_t ldx, const void* gamma, const void* beta, void* y,
+                           int64_t ldy, float* mean, float* rstd, int64_t rows, int64_t cols, float eps, void* stream) {
+    B200_REQUIRE(ctx != nullptr, "b200_layernorm_forward: ctx is NULL");
+    int rc = check_rows("b200_layernorm_forward", x, ldx, rows, cols);
+    if (rc == B200_OK) rc = check_rows("b200_layernorm_forward", y, ldy, rows, cols);
+    if (rc != B200_OK) return rc;
+    if (rows == 0 || cols == 0) return B200_OK;
+    B200_REQUIRE(gamma && beta, "b200_layernorm_forward: gamma or beta is NULL");
+    DeviceScope scope(ctx->device);
+    cudaStream_t s = ctx->pick(stream);
+    const auto* xp = static_cast<const __nv_bfloat16*>(x);
+    const auto* gp = static_cast<const __nv_bfloat16*>(gamma);
+    const auto* bp = static_cast<const __nv_bfloat16*>(beta);
+    auto* yp = static_cast<__nv_bfloat16*>(y);
+    const int vx = vec_ok(x, ldx), vy = vec_ok(y, ldy), vg = vec_ok(gamma, 8) & vec_ok(beta, 8);
+    const int r = static_cast<int>(rows), c = static_cast<int>(cols);
+    const int blocks = (r + 7) / 8;
+    if (c <= 512)
+        layernorm_fw_warp_kernel<2><<<blocks, kBlock, 0, s>>>(xp, ldx, gp, bp, yp, ldy, mean, rstd, r, c, eps, vx, vy, vg);
+    else if (c <= 1024)
+        layernorm_fw_warp_kernel<4><<<blocks, kBlock, 0, s>>>(xp, ldx, gp, bp, yp, ldy, mean, rstd, r, c, eps, vx, vy, vg);
+    else if (c <= 2048)
+        layernorm_fw_warp_kernel<8><<<blocks, kBlock, 0, s>>>(xp, ldx, gp, bp, yp, ldy, mean, rstd, r, c, eps, vx, vy, vg);
+    else
+        layernorm_fw_block_kernel<<<r, kBlock, 0, s>>>(xp, ldx, gp, bp, yp, ldy, mean, rstd, r, c, eps, vx, vy, vg);
+    B200_CUDA_TRY(cudaGetLastError());
+    return B200_OK;
+}
+
+int b200_layernorm_backward(b200_ctx* ctx, const void* dy, int64_t lddy, const void* x, int64_t ldx, const void* gamma,
+                            const float* mean, const float* rstd, void* dx, int64_t lddx, float* dgamma_f32,
+                            float* dbeta_f32, int64_t rows, int64_t cols, void* stream) {
+    B200_REQUIRE(ctx != nullptr, "b200_layernorm_backward: ctx is NULL");
+    int rc = check_rows("b200_layernorm_backward", dy, lddy, rows, cols);
+    if (rc == B200_OK) rc = check_rows("b200_layernorm_backward", x, ldx, rows, cols);
+    if (rc == B200_OK && dx) rc = check_rows("b200_layernorm_backward", dx, lddx, rows, cols);
+    if (rc != B200_OK) return rc;
+    DeviceScope scope(ctx->device);
+    cudaStream_t s = ctx->pick(stream);
+    const int r = static_cast<int>(rows), c = static_cast<int>(cols);
+    if (dgamma_f32 && c > 0) B200_CUDA_TRY(cudaMemsetAsync(dgamma_f32, 0, sizeof(float) * c, s));
+    if (dbeta_f32 && c > 0) B200_CUDA_TRY(cudaMemsetAsync(dbeta_f32, 0, sizeof(float) * c, s));
+    if (rows == 0 || cols == 0) return B200_OK;
+    B200_REQUIRE(mean && rstd, "b200_layernorm_backward: mean or rstd is NULL");
+    const auto* dyp = static_cast<const __nv_bfloat16*>(dy);
+    const auto* xp = static_cast<const __nv_bfloat16*>(x);
+    if (dx) {
+        B200_REQUIRE(gamma != nullptr, "b200_layernorm_backward: gamma is NULL");
+        const auto* gp = static_cast<const __nv_bfloat16*>(gamma);
+        auto* dxp = static_cast<__nv_bfloat16*>(dx);
+        const int vdy = vec_ok(dy, lddy), vx = vec_ok(x, ldx), vdx = vec_ok(dx, lddx), vg = vec_ok(gamma, 8);
+        const int blocks = (r + 7) / 8;
+        if (c <= 512)
+            layernorm_bw_dx_warp_kernel<2><<<blocks, kBlock, 0, s>>>(dyp, lddy, xp, ldx, gp, mean, rstd, dxp, lddx, r, c, vdy, vx, vdx, vg);
+        else if (c <= 1024)
+            layernorm_bw_dx_warp_kernel<4><<<blocks, kBlock, 0, s>>>(dyp, lddy, xp, ldx, gp, mean, rstd, dxp, lddx, r, c, vdy, vx, vdx, vg);
+        else if (c <= 2048)
+            layernorm_bw_dx_warp_kernel<8><<<blocks, kBlock, 0, s>>>(dyp, lddy, xp, ldx, gp, mean, rstd, dxp, lddx, r, c, vdy, vx, vdx, vg);
+        else
+            layernorm_bw_dx_block_kernel<<<r, kBlock, 0, s>>>(dyp, lddy, xp, ldx, gp, mean, rstd, dxp, lddx, r, c, vdy, vx, vdx, vg);
+        B200_CUDA_TRY(cudaGetLastError());
+    }
+    if (dgamma_f32 || dbeta_f32) {
+        const int col_blocks = (c + 63) / 64;
+        int row_blocks = std::max(1, std::min((r + 63) / 64, (ctx->sm_count * 4 + col_blocks - 1) / col_blocks));
+        const int rows_per = (r + row_blocks - 1) / row_blocks;
+        row_blocks = (r + rows_per - 1) / rows_per;
+        dim3 grid(col_blocks, row_blocks);
+        layernorm_bw_param_kernel<<<grid, 256, 0, s>>>(dyp, lddy, xp, ldx, mean, rstd, dgamma_f32, dbeta_f32, r, c, rows_per);
+        B200_CUDA_TRY(cudaGetLastError());
+    }
+    return B200_OK;
+}
+
+}  // extern "C"

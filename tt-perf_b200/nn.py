@@ -1,0 +1,262 @@
+"""Host-side mirror of the reference's layer vocabulary over the C ABI: Linear, ReLU/GELU, causal attention,
+LayerNorm, cross-entropy, SGD/Adam, the 2-layer MLP train step and the pre-LN GPT-2 block forward/backward.
+
+Every function only sequences C-ABI calls on device tensors (tt-perf_b200/tensor.py); no arithmetic happens on
+the host. Names and argument meaning follow the reference's traced executor: `linear_forward/backward`
+(autograd/traced/ops.hpp:113-119, traced/nn.hpp:72-90), `TracedCausalAttention` (traced/nn.hpp:164-192),
+`TracedLayerNorm` (traced/nn.hpp:226-269), `TracedMLP::train_step` (traced/mlp.hpp:72-117), the trainable
+transformer layer (traced/transformer_train.hpp:179-257) with the gradient forms corrected as in
+verify/compare_grads.py:234-249 (weights' gradients reduce over batch AND sequence)."""
+from __future__ import annotations
+
+import math
+
+from . import capi
+from .capi import ACT_GELU, ACT_NONE, ACT_RELU, BF16, F32
+from .tensor import DeviceTensor
+
+_ACT = {None: ACT_NONE, "relu": ACT_RELU, "gelu": ACT_GELU}
+
+
+def _rows(t: DeviceTensor) -> int:
+    return t.numel // t.shape[-1]
+
+
+def matmul(ctx, a: DeviceTensor, b: DeviceTensor, transpose_a=False, transpose_b=False, *, stream=None, alpha=1.0,
+           causal_mask=False, bias=None, activation=None, out_dtype=BF16, **kw) -> DeviceTensor:
+    """ttnn::matmul(a, b, transpose_a, transpose_b) with leading dims batched; a rank-2 `b` broadcasts."""
+    am, ak = (a.shape[-1], a.shape[-2]) if transpose_a else (a.shape[-2], a.shape[-1])
+    bk, bn = (b.shape[-1], b.shape[-2]) if transpose_b else (b.shape[-2], b.shape[-1])
+    if ak != bk:
+        raise ValueError(f"matmul: inner dimensions differ ({a.shape} x {b.shape}, ta={transpose_a}, tb={transpose_b})")
+    lead_a, lead_b = a.shape[:-2], b.shape[:-2]
+    batch = int(math.prod(lead_a)) if lead_a else 1
+    if len(b.shape) == 2:
+        if transpose_a and batch > 1:
+            raise ValueError("matmul: a transposed batched lhs needs a batched rhs")
+        # [B.., M, K] x [K, N]: fold the batch into M (one big GEMM)
+        m_total = batch * am if not transpose_a else am
+        out = DeviceTensor(ctx, lead_a + (am, bn), out_dtype)
+        d = ctx.gemm_desc(a, b, out, m_total, bn, ak, transpose_a=transpose_a, transpose_b=transpose_b, alpha=alpha,
+                          causal_mask=causal_mask, bias=bias, activation=_ACT[activation], c_dtype=out_dtype, **kw)
+    else:
+        if lead_a != lead_b:
+            raise ValueError(f"matmul: batch dims differ ({a.shape} x {b.shape})")
+        out = DeviceTensor(ctx, lead_a + (am, bn), out_dtype)
+        d = ctx.gemm_desc(a, b, out, am, bn, ak, transpose_a=transpose_a, transpose_b=transpose_b, batch=batch, alpha=alpha,
+                          causal_mask=causal_mask, bias=bias, activation=_ACT[activation], c_dtype=out_dtype, **kw)
+    ctx.gemm(d, stream)
+    return out
+
+
+def linear_forward(ctx, x, w, bias=None, activation=None, *, stream=None) -> DeviceTensor:
+    """y = act(x . w^T + b); w is [out, in] (ttnn::linear(x, w, bias, false, true, ..., "relu"))."""
+    return matmul(ctx, x, w, False, True, bias=bias, activation=activation, stream=stream)
+
+
+def linear_backward(ctx, x, w, d_y, *, need_dx=True, stream=None):
+    """Returns (dx, dW, db): dx = dy . w, dW = dy^T . x and db = column sums of dy over all leading positions."""
+    rows, n_out, n_in = _rows(x), w.shape[0], w.shape[1]
+    x2, dy2 = x.reshape(rows, n_in), d_y.reshape(rows, n_out)
+    d_x = matmul(ctx, d_y, w, False, False, stream=stream) if need_dx else None
+    d_w = matmul(ctx, dy2, x2, True, False, stream=stream)
+    d_b = DeviceTensor(ctx, (n_out,), BF16)
+    ctx.reduce(capi.R_SUM, dy2, 1, rows, n_out, d_b, stream=stream)
+    return d_x, d_w, d_b
+
+
+def relu_backward(ctx, d_y, x_pre, *, stream=None) -> DeviceTensor:
+    out = DeviceTensor(ctx, d_y.shape, BF16)
+    ctx.binary(capi.B_RELU_BW, d_y, (d_y.numel,), x_pre, (x_pre.numel,), out, stream=stream)
+    return out
+
+
+def gelu_backward(ctx, d_y, x_pre, *, stream=None) -> DeviceTensor:
+    out = DeviceTensor(ctx, d_y.shape, BF16)
+    ctx.binary(capi.B_GELU_BW, d_y, (d_y.numel,), x_pre, (x_pre.numel,), out, stream=stream)
+    return out
+
+
+def add(ctx, a, b, *, stream=None) -> DeviceTensor:
+    out = DeviceTensor(ctx, a.shape, BF16)
+    ctx.binary(capi.B_ADD, a, a.shape, b, b.shape, out, stream=stream)
+    return out
+
+
+def layernorm_forward(ctx, x, gamma, beta, *, eps=1e-5, stream=None):
+    rows, cols = _rows(x), x.shape[-1]
+    y = DeviceTensor(ctx, x.shape, BF16)
+    mean, rstd = DeviceTensor(ctx, (rows,), F32), DeviceTensor(ctx, (rows,), F32)
+    ctx.layernorm_forward(x, gamma, beta, y, mean, rstd, rows, cols, eps=eps, stream=stream)
+    return y, mean, rstd
+
+
+def layernorm_backward(ctx, d_y, x, gamma, mean, rstd, *, stream=None):
+    rows, cols = _rows(x), x.shape[-1]
+    d_x = DeviceTensor(ctx, x.shape, BF16)
+    dg, db = DeviceTensor(ctx, (cols,), F32), DeviceTensor(ctx, (cols,), F32)
+    ctx.layernorm_backward(d_y, x, gamma, mean, rstd, d_x, dg, db, rows, cols, stream=stream)
+    return d_x, dg, db
+
+
+def causal_attention_forward(ctx, q, k, v, *, scale=None, stream=None):
+    """q, k, v: [..., S, dh]. scores = q k^T with the 1/sqrt(dh) scale and the causal mask fused into one softmax
+    pass; returns (O, P) with P kept for the backward pass."""
+    s_len, dh = q.shape[-2], q.shape[-1]
+    scale = 1.0 / math.sqrt(dh) if scale is None else scale
+    scores = matmul(ctx, q, k, False, True, stream=stream)
+    p = DeviceTensor(ctx, scores.shape, BF16)
+    ctx.softmax(scores, p, _rows(scores), s_len, alpha=scale, causal_period=s_len, stream=stream)
+    return matmul(ctx, p, v, stream=stream), p
+
+
+def causal_attention_backward(ctx, q, k, v, p, d_o, *, scale=None, stream=None):
+    dh = q.shape[-1]
+    scale = 1.0 / math.sqrt(dh) if scale is None else scale
+    d_v = matmul(ctx, p, d_o, True, False, stream=stream)
+    d_p = matmul(ctx, d_o, v, False, True, stream=stream)
+    d_s = DeviceTensor(ctx, p.shape, BF16)
+    ctx.softmax_backward(d_p, p, d_s, _rows(p), p.shape[-1], alpha=scale, stream=stream)
+    d_q = matmul(ctx, d_s, k, stream=stream)
+    d_k = matmul(ctx, d_s, q, True, False, stream=stream)
+    return d_q, d_k, d_v
+
+
+def split_heads(ctx, x, heads, *, stream=None) -> DeviceTensor:
+    """[B, S, D] -> [B, H, S, dh] (reshape + transpose(1, 2), transformer_train.hpp:167-172)."""
+    b, s, d = x.shape
+    out = DeviceTensor(ctx, (b, heads, s, d // heads), BF16)
+    ctx.permute(x, (b, s, heads, d // heads), (0, 2, 1, 3), out, stream=stream)
+    return out
+
+
+def merge_heads(ctx, x, *, stream=None) -> DeviceTensor:
+    b, h, s, dh = x.shape
+    out = DeviceTensor(ctx, (b, s, h * dh), BF16)
+    ctx.permute(x, (b, h, s, dh), (0, 2, 1, 3), out, stream=stream)
+    return out
+
+
+def cross_entropy(ctx, logits, labels, *, need_grad=True, stream=None):
+    """Mean cross-entropy over all rows; returns (loss scalar tensor fp32, d_logits or None)."""
+    rows, classes = _rows(logits), logits.shape[-1]
+    loss = DeviceTensor(ctx, (1,), F32)
+    d_logits = DeviceTensor(ctx, logits.shape, BF16) if need_grad else None
+    ctx.cross_entropy(logits, labels, rows, classes, loss_sum=loss, d_logits=d_logits, stream=stream)
+    return loss, d_logits
+
+
+def sgd_step(ctx, params, grads, lr, *, shadows=None, stream=None) -> None:
+    """p <- p - lr * g. With fp32 master `params`, `shadows` are the bf16 copies the matmuls read."""
+    ctx.sgd_step(params, grads, [p.numel for p in params], lr, p_dtype=params[0].dtype, g_dtype=grads[0].dtype,
+                 shadows=shadows, stream=stream)
+
+
+class Adam:
+    """Adam with fp32 moments (py/optim.py:30-92 argument checks included)."""
+
+    def __init__(self, ctx, params, *, lr=1e-3, betas=(0.9, 0.999), eps=1e-8, shadows=None):
+        if lr <= 0:
+            raise ValueError("lr must be > 0")
+        if eps <= 0:
+            raise ValueError("eps must be > 0")
+        if not isinstance(betas, (tuple, list)) or len(betas) != 2:
+            raise ValueError("betas must be a tuple of (beta1, beta2)")
+        if not (0.0 < betas[0] < 1.0 and 0.0 < betas[1] < 1.0):
+            raise ValueError("betas must be in (0, 1)")
+        self.ctx, self.params = ctx, list(params)
+        self.shadows = list(shadows) if shadows else None
+        self.lr, self.beta1, self.beta2, self.eps = float(lr), float(betas[0]), float(betas[1]), float(eps)
+        self.m = [DeviceTensor.zeros(ctx, p.shape, F32) for p in self.params]
+        self.v = [DeviceTensor.zeros(ctx, p.shape, F32) for p in self.params]
+        self.t = 0
+
+    def step(self, grads, *, stream=None) -> None:
+        self.t += 1
+        self.ctx.adam_step(self.params, grads, self.m, self.v, [p.numel for p in self.params], self.t, lr=self.lr,
+                           beta1=self.beta1, beta2=self.beta2, eps=self.eps, p_dtype=self.params[0].dtype,
+                           g_dtype=grads[0].dtype, shadows=self.shadows, stream=stream)
+
+
+# ---------------------------------------------------------------------------------------------------------------
+# 2-layer MLP (TracedMLP<2>::train_step) with either MSE (the reference's loss) or cross-entropy
+# ---------------------------------------------------------------------------------------------------------------
+def mlp_train_step(ctx, x, target, params, lr, *, loss="ce", masters=None, stream=None):
+    """Forward, loss, backward and SGD update of Linear -> ReLU -> Linear. `params` = [w1, b1, w2, b2] in bf16
+    (what the matmuls read, updated in place); `masters`, when given, are their fp32 master copies: the update is
+    applied to the masters and the bf16 tensors are refreshed from them in the same pass.
+    Returns (loss before the update as an fp32 device scalar, gradients)."""
+    w1, b1, w2, b2 = params
+    h_pre = linear_forward(ctx, x, w1, b1, stream=stream)
+    h = DeviceTensor(ctx, h_pre.shape, BF16)
+    ctx.unary(capi.U_RELU, h_pre, h, h.numel, stream=stream)
+    out = linear_forward(ctx, h, w2, b2, stream=stream)
+    if loss == "ce":
+        loss_t, d_out = cross_entropy(ctx, out, target, stream=stream)
+    elif loss == "mse":
+        # loss = mean((out - target)^2); d_out = 2 (out - target) / n
+        diff = DeviceTensor(ctx, out.shape, BF16)
+        ctx.binary(capi.B_SUB, out, out.shape, target, target.shape, diff, stream=stream)
+        sq = DeviceTensor(ctx, out.shape, BF16)
+        ctx.unary(capi.U_SQUARE, diff, sq, sq.numel, stream=stream)
+        loss_bf = DeviceTensor(ctx, (1,), BF16)
+        ctx.reduce(capi.R_MEAN, sq, 1, sq.numel, 1, loss_bf, stream=stream)
+        loss_t = DeviceTensor(ctx, (1,), F32)
+        ctx.cast(loss_bf, BF16, loss_t, F32, 1, stream=stream)
+        d_out = DeviceTensor(ctx, out.shape, BF16)
+        ctx.unary(capi.U_MUL_SCALAR, diff, d_out, d_out.numel, scalar=2.0 / out.numel, stream=stream)
+    else:
+        raise ValueError(loss)
+    d_h, d_w2, d_b2 = linear_backward(ctx, h, w2, d_out, stream=stream)
+    d_hpre = relu_backward(ctx, d_h, h_pre, stream=stream)
+    _, d_w1, d_b1 = linear_backward(ctx, x, w1, d_hpre, need_dx=False, stream=stream)
+    grads = [d_w1, d_b1, d_w2, d_b2]
+    if masters is not None:
+        sgd_step(ctx, masters, grads, lr, shadows=params, stream=stream)
+    else:
+        sgd_step(ctx, params, grads, lr, stream=stream)
+    return loss_t, grads
+
+
+# ---------------------------------------------------------------------------------------------------------------
+# Pre-LN GPT-2 block (verify/compare_grads.py:37-97)
+# ---------------------------------------------------------------------------------------------------------------
+def transformer_block_forward(ctx, x, w, heads, *, stream=None):
+    """x [B, S, D]; w: dict with ln1_g, ln1_b, wq, bq, wk, bk, wv, bv, wo, bo, ln2_g, ln2_b, w1, b1, w2, b2.
+    Returns (out, cache)."""
+    ln1, mean1, rstd1 = layernorm_forward(ctx, x, w["ln1_g"], w["ln1_b"], stream=stream)
+    q = split_heads(ctx, linear_forward(ctx, ln1, w["wq"], w["bq"], stream=stream), heads, stream=stream)
+    k = split_heads(ctx, linear_forward(ctx, ln1, w["wk"], w["bk"], stream=stream), heads, stream=stream)
+    v = split_heads(ctx, linear_forward(ctx, ln1, w["wv"], w["bv"], stream=stream), heads, stream=stream)
+    attn, p = causal_attention_forward(ctx, q, k, v, stream=stream)
+    merged = merge_heads(ctx, attn, stream=stream)
+    res1 = add(ctx, x, linear_forward(ctx, merged, w["wo"], w["bo"], stream=stream), stream=stream)
+    ln2, mean2, rstd2 = layernorm_forward(ctx, res1, w["ln2_g"], w["ln2_b"], stream=stream)
+    h1 = linear_forward(ctx, ln2, w["w1"], w["b1"], stream=stream)
+    h1g = DeviceTensor(ctx, h1.shape, BF16)
+    ctx.unary(capi.U_GELU, h1, h1g, h1g.numel, stream=stream)
+    out = add(ctx, res1, linear_forward(ctx, h1g, w["w2"], w["b2"], stream=stream), stream=stream)
+    cache = dict(x=x, ln1=ln1, mean1=mean1, rstd1=rstd1, q=q, k=k, v=v, p=p, merged=merged, res1=res1, ln2=ln2,
+                 mean2=mean2, rstd2=rstd2, h1=h1, h1g=h1g)
+    return out, cache
+
+
+def transformer_block_backward(ctx, d_out, w, cache, heads, *, stream=None):
+    """Returns (dx, grads) with grads keyed like `w` (LayerNorm gradients are fp32, the rest bf16)."""
+    c, g = cache, {}
+    d_h1g, g["w2"], g["b2"] = linear_backward(ctx, c["h1g"], w["w2"], d_out, stream=stream)
+    d_h1 = gelu_backward(ctx, d_h1g, c["h1"], stream=stream)
+    d_ln2, g["w1"], g["b1"] = linear_backward(ctx, c["ln2"], w["w1"], d_h1, stream=stream)
+    d_res1_ln, g["ln2_g"], g["ln2_b"] = layernorm_backward(ctx, d_ln2, c["res1"], w["ln2_g"], c["mean2"], c["rstd2"],
+                                                            stream=stream)
+    d_res1 = add(ctx, d_out, d_res1_ln, stream=stream)
+    d_merged, g["wo"], g["bo"] = linear_backward(ctx, c["merged"], w["wo"], d_res1, stream=stream)
+    d_attn = split_heads(ctx, d_merged, heads, stream=stream)
+    d_q, d_k, d_v = causal_attention_backward(ctx, c["q"], c["k"], c["v"], c["p"], d_attn, stream=stream)
+    d_ln1_q, g["wq"], g["bq"] = linear_backward(ctx, c["ln1"], w["wq"], merge_heads(ctx, d_q, stream=stream), stream=stream)
+    d_ln1_k, g["wk"], g["bk"] = linear_backward(ctx, c["ln1"], w["wk"], merge_heads(ctx, d_k, stream=stream), stream=stream)
+    d_ln1_v, g["wv"], g["bv"] = linear_backward(ctx, c["ln1"], w["wv"], merge_heads(ctx, d_v, stream=stream), stream=stream)
+    d_ln1 = add(ctx, add(ctx, d_ln1_q, d_ln1_k, stream=stream), d_ln1_v, stream=stream)
+    d_x_ln, g["ln1_g"], g["ln1_b"] = layernorm_backward(ctx, d_ln1, c["x"], w["ln1_g"], c["mean1"], c["rstd1"],
+                                                         stream=stream)
+    return add(ctx, d_res1, d_x_ln, stream=stream), g
