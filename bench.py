@@ -276,6 +276,130 @@ def run_b200_single(args) -> None:
     ctx.close()
 
 
+def run_b200_distributed(args) -> None:
+    """N > 1 (torchrun, one rank per GPU): C = A . B at 16384^3 with B split on N; the all-gather of C is fused into
+    the GEMM epilogue (TMA stores into every peer's C over NVLink). Per step: one fused launch per rank, then a
+    rank barrier (tiny NCCL all-reduce) so that every rank holds the complete C before the next step starts."""
+    import torch
+    import torch.distributed as dist
+    from __graft_entry__ import load_package
+    pkg = load_package()
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local_rank = int(os.environ.get("LOCAL_RANK", str(rank)))
+    torch.cuda.set_device(local_rank)
+    dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
+    ctx = pkg.Context(local_rank)
+    st = torch.cuda.Stream()
+    torch.cuda.set_stream(st)
+    s = st.cuda_stream
+    M = N = K = 16384
+    off, width = pkg.dist.column_shard(N, world, rank)
+    g = torch.Generator(device="cuda").manual_seed(42)           # same seed on every rank: A and B are replicated inputs
+    a = torch.randn(M, K, generator=g, device="cuda", dtype=torch.float32).bfloat16()
+    b_full = torch.randn(K, N, generator=g, device="cuda", dtype=torch.float32).bfloat16()
+    b = b_full[:, off:off + width].contiguous()
+    mm = pkg.dist.ColumnParallelMatmul(ctx, M, N, K, rank, world)
+    flag = torch.zeros(1, device="cuda")
+    flops = 2.0 * M * N * K
+
+    def step():
+        mm.launch(a, b, s)
+        dist.all_reduce(flag)      # rank barrier on the stream: all peers' stores have landed after it
+
+    for _ in range(max(args.warmup, 3)):
+        step()
+    torch.cuda.synchronize()
+    dist.barrier()
+    sampler = ClockSampler(local_rank)
+    if rank == 0:
+        sampler.start()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    torch.cuda.synchronize()
+    e0.record(st)
+    for _ in range(args.steps):
+        step()
+    e1.record(st)
+    torch.cuda.synchronize()
+    t = torch.tensor([e0.elapsed_time(e1)], device="cuda")
+    dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    ms_per_step = t.item() / args.steps
+    clocks = None
+    # keep all ranks busy together while rank 0 samples clocks
+    for _ in range(0 if args.quick else 30):
+        step()
+    torch.cuda.synchronize()
+    if rank == 0:
+        clocks = sampler.stop()
+    tflops = flops / (ms_per_step * 1e-3) / 1e12
+
+    # parity: rows of the gathered C (every rank's copy) against fp32 torch on this GPU
+    c_host = torch.empty(M, N, dtype=torch.bfloat16).pin_memory()
+    ctx.d2h(c_host, mm.c_ptr, M * N * 2, s)
+    rows = torch.arange(rank, M, 1013)
+    ref = (a[rows.cuda()].float() @ b_full.float()).cpu()
+    err = ((c_host[rows].float() - ref).norm() / ref.norm()).item()
+    errs = torch.tensor([err], device="cuda")
+    dist.all_reduce(errs, op=dist.ReduceOp.MAX)
+    if not errs.item() < 1e-2:
+        raise RuntimeError(f"bench: gathered C fails parity on some rank (relative Frobenius error {errs.item():.3e})")
+
+    # end to end with host buffers: A and the B shard from pinned host memory, fused GEMM + gather, full C to the host
+    e2e = None
+    if not args.quick:
+        a_h = a.cpu().pin_memory()
+        b_h = b.cpu().pin_memory()
+        e2e_steps = 2
+        torch.cuda.synchronize()
+        dist.barrier()
+        t0 = time.perf_counter()
+        for _ in range(e2e_steps):
+            ctx.h2d(a, a_h, M * K * 2, s)
+            ctx.h2d(b, b_h, K * width * 2, s)
+            step()
+            ctx.d2h(c_host, mm.c_ptr, M * N * 2, s)
+        torch.cuda.synchronize()
+        t = torch.tensor([(time.perf_counter() - t0) / e2e_steps], device="cuda")
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        e2e = {"value": flops / t.item() / 1e12, "unit": "TFLOP/s", "h2d_bytes_per_step": (M * K + K * width) * 2,
+               "d2h_bytes_per_step": M * N * 2, "ms_per_step": t.item() * 1e3, "steps": e2e_steps,
+               "note": "per rank: A and the B shard host->device, fused GEMM + all-gather, the full C device->host"}
+
+    if rank == 0:
+        peaks = load_peaks()
+        peak = peaks["bf16_tflops"] * world
+        nvlink_bytes = (world - 1) / world * M * N * 2          # bytes each rank sends to its peers
+        t_compute = flops / world / (peaks["bf16_tflops"] * 1e12)
+        t_link = nvlink_bytes / 770e9
+        line = {
+            "metric": "bf16 GEMM TFLOP/s", "value": tflops, "unit": "TFLOP/s", "n_gpus": world, "steps": args.steps,
+            "warmup": max(args.warmup, 3), "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "strong",
+            "vs_baseline": None, "dtype": "bf16", "data": "synthetic", "config": workload_config(world),
+            "pct_of_peak": tflops / peak,
+            "roofline": {"bound": "tensor", "achieved": tflops, "peak": peak, "unit": "TFLOP/s", "frac": tflops / peak,
+                         "traffic": None,
+                         "peak_source": f"{peaks['source']} (MEASURED_PEAKS.json bf16_tflops x {world} GPUs)",
+                         "kernel": "gemm_tcgen05_kernel<256> with the all-gather fused into its TMA-store epilogue",
+                         "flops_per_launch": flops / world, "nvlink_bytes_sent_per_rank": nvlink_bytes,
+                         "target_ms": max(t_compute, t_link) * 1e3, "target_bound": "tensor" if t_compute >= t_link else "nvlink",
+                         "frac_of_target": max(t_compute, t_link) * 1e3 / ms_per_step},
+            "cpu_baseline": None,
+            "e2e": e2e,
+            "gpu_launches": args.steps * world,
+            "clocks": clocks,
+            "parity_sample_rel_frobenius": errs.item(),
+        }
+        if not args.quick:
+            cpu = cpu_matmul_baseline(M, N, K)
+            cpu.pop("seconds", None)
+            line["cpu_baseline"] = cpu
+        print(json.dumps(line), flush=True)
+    dist.barrier()
+    mm.close()
+    ctx.close()
+    dist.destroy_process_group()
+
+
 def main() -> None:
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -292,8 +416,7 @@ def main() -> None:
     if args.gpus == 1 and int(os.environ.get("WORLD_SIZE", "1")) == 1:
         run_b200_single(args)
     else:
-        from bench_dist import run_b200_distributed  # noqa: WPS433 (kept separate: needs torch.distributed)
-        run_b200_distributed(args, load_peaks, workload_config, ClockSampler)
+        run_b200_distributed(args)
 
 
 if __name__ == "__main__":

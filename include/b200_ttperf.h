@@ -80,6 +80,25 @@ int b200_memcpy_h2d(b200_ctx* ctx, void* d_dst, const void* h_src, size_t bytes,
 int b200_memcpy_d2h(b200_ctx* ctx, void* h_dst, const void* d_src, size_t bytes, void* stream);
 int b200_memset(b200_ctx* ctx, void* d_dst, int byte_value, size_t bytes, void* stream);
 
+/* ---- pooled tensor memory and trace record / replay (TraceContext, autograd/traced/trace.hpp:21-88:
+ *      begin_trace_capture / end_trace_capture / execute_trace / release_trace; raw use in
+ *      bench/autograd/bench_transformer_train.cpp:91-110) -------------------------------------------------
+ * b200_pool_alloc / b200_pool_free: cached device blocks for op results (`out = ttnn::add(a, b)` allocates on every
+ * call); blocks go back to the driver only when the context is destroyed.
+ * b200_trace_begin starts recording the work queued on the CONTEXT stream (pass stream = NULL to the ops) into a
+ * CUDA graph; b200_trace_end instantiates it; b200_trace_execute replays it (blocking != 0 waits for completion);
+ * b200_trace_release destroys it. Blocks allocated while recording belong to the trace until it is released, so a
+ * replay never writes into memory handed to someone else. Ops that would synchronise (b200_synchronize,
+ * b200_memcpy_d2h on the context stream) or grow the context scratch fail with B200_ERR_UNSUPPORTED while
+ * recording: run the step once untraced first, as the reference's benchmarks do (bench_mlp.cpp:99-102). */
+int b200_pool_alloc(b200_ctx* ctx, size_t bytes, void** out_dptr);
+int b200_pool_free(b200_ctx* ctx, void* dptr);
+int b200_pool_stats(b200_ctx* ctx, size_t* reserved_bytes, size_t* in_use_bytes);
+int b200_trace_begin(b200_ctx* ctx, uint32_t* out_trace_id);
+int b200_trace_end(b200_ctx* ctx, uint32_t trace_id);
+int b200_trace_execute(b200_ctx* ctx, uint32_t trace_id, int blocking);
+int b200_trace_release(b200_ctx* ctx, uint32_t trace_id);
+
 /* ---- dense matmul: ttnn::matmul(a, b, transpose_a, transpose_b, ..., activation, compute_kernel_config)
  *      (dynamic/ops.hpp:21-46, static/ops.hpp:21-45, traced/ops.hpp:26-36) and
  *      ttnn::linear(x, w, bias, ta, tb, ..., "relu") (static/nn.hpp:145-146) --------------------------
@@ -216,6 +235,31 @@ int b200_sgd_step(b200_ctx* ctx, int64_t count, void* const* params, const void*
 int b200_adam_step(b200_ctx* ctx, int64_t count, void* const* params, const void* const* grads, float* const* m,
                    float* const* v, void* const* shadow_bf16, const int64_t* sizes, int p_dtype, int g_dtype, float lr,
                    float beta1, float beta2, float eps, int64_t step, void* stream);
+
+/* ---- sharded matmul over the GPUs of one node, one process per GPU ---------------------------------------------
+ * (benchmark_tensor_parallel_matmul, bench/metal/matmul_tensor_parallel.cpp:54-123: replicate A, shard B on dim 1,
+ *  ttnn::matmul then ttnn::all_gather(c, 1); scripts/matmul_2dev_distributed.py:33-109.)
+ * The collective is fused into the GEMM epilogue: finished tiles are stored by TMA directly into peer GPUs' memory.
+ * Peer buffers are exchanged as CUDA IPC handles (64 opaque bytes) by the host program.
+ * Stores to a peer are complete for that peer only after this rank's stream has finished AND the ranks have
+ * synchronised (barrier or any collective issued by the host program). */
+int b200_ipc_get_handle(b200_ctx* ctx, void* dptr, void* out_handle64);
+int b200_ipc_open_handle(b200_ctx* ctx, const void* handle64, void** out_dptr);
+int b200_ipc_close_handle(b200_ctx* ctx, void* dptr);
+/* N-split (column parallel) + all-gather. desc describes the LOCAL product C[:, my_rank*N : (my_rank+1)*N] =
+ * op(A) . op(B_shard) with N = shard width; desc->C is ignored; desc->ldc = leading dimension of the full gathered C
+ * (>= N * n_ranks). peer_c[p] = base of the full C on rank p (peer_c[my_rank] = the local one). Every rank ends up
+ * with the whole C, like ttnn::all_gather(c_sharded, 1). Needs the tcgen05 alignment rules, batch 1, split_k off. */
+int b200_gemm_allgather(b200_ctx* ctx, const b200_gemm_desc* desc, void* const* peer_c, int n_ranks, int my_rank,
+                        void* stream);
+/* K-split (row parallel) + reduce-scatter, step 1: desc describes the LOCAL partial product over this rank's K range
+ * (full M x N). The fp32 partial tiles of row block j (M / n_ranks rows) are stored into slot `my_rank` of rank j's
+ * staging buffer peer_slots[j], laid out [n_ranks][M / n_ranks][N] fp32. M / n_ranks must be a multiple of 128.
+ * Step 2, after the ranks have synchronised: b200_reduce_slices sums a rank's n_slices slices ([n_slices][batch][M][N]
+ * fp32, M = rows of the block), applies desc's alpha / bias / activation and writes desc->C (bf16 or fp32). */
+int b200_gemm_reduce_scatter_partials(b200_ctx* ctx, const b200_gemm_desc* desc, void* const* peer_slots, int n_ranks,
+                                      int my_rank, void* stream);
+int b200_reduce_slices(b200_ctx* ctx, const float* slices, int n_slices, const b200_gemm_desc* desc, void* stream);
 
 /* ---- split-K matmul without device allocation (no counterpart in the reference: TTNN owns its device
  *      memory, so the question never arises there) ----------------------------------------------------

@@ -63,10 +63,24 @@ SIGNATURES = {
     "b200_memcpy_h2d": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_size_t, C.c_void_p]),
     "b200_memcpy_d2h": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_size_t, C.c_void_p]),
     "b200_memset": (C.c_int, [C.c_void_p, C.c_void_p, C.c_int, C.c_size_t, C.c_void_p]),
+    "b200_pool_alloc": (C.c_int, [C.c_void_p, C.c_size_t, C.POINTER(C.c_void_p)]),
+    "b200_pool_free": (C.c_int, [C.c_void_p, C.c_void_p]),
+    "b200_pool_stats": (C.c_int, [C.c_void_p, C.POINTER(C.c_size_t), C.POINTER(C.c_size_t)]),
+    "b200_trace_begin": (C.c_int, [C.c_void_p, C.POINTER(C.c_uint32)]),
+    "b200_trace_end": (C.c_int, [C.c_void_p, C.c_uint32]),
+    "b200_trace_execute": (C.c_int, [C.c_void_p, C.c_uint32, C.c_int]),
+    "b200_trace_release": (C.c_int, [C.c_void_p, C.c_uint32]),
     "b200_gemm_desc_init": (None, [C.POINTER(GemmDesc)]),
     "b200_gemm": (C.c_int, [C.c_void_p, C.POINTER(GemmDesc), C.c_void_p]),
     "b200_gemm_scratch_bytes": (C.c_int, [C.c_void_p, C.POINTER(GemmDesc), C.POINTER(C.c_size_t)]),
     "b200_gemm_static_scratch": (C.c_int, [C.c_int, C.POINTER(GemmDesc), C.c_void_p]),
+    "b200_ipc_get_handle": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p]),
+    "b200_ipc_open_handle": (C.c_int, [C.c_void_p, C.c_void_p, C.POINTER(C.c_void_p)]),
+    "b200_ipc_close_handle": (C.c_int, [C.c_void_p, C.c_void_p]),
+    "b200_gemm_allgather": (C.c_int, [C.c_void_p, C.POINTER(GemmDesc), C.POINTER(C.c_void_p), C.c_int, C.c_int, C.c_void_p]),
+    "b200_gemm_reduce_scatter_partials": (C.c_int, [C.c_void_p, C.POINTER(GemmDesc), C.POINTER(C.c_void_p), C.c_int, C.c_int,
+                                                    C.c_void_p]),
+    "b200_reduce_slices": (C.c_int, [C.c_void_p, C.c_void_p, C.c_int, C.POINTER(GemmDesc), C.c_void_p]),
     "b200_softmax": (C.c_int, [C.c_void_p, C.c_void_p, C.c_int64, C.c_void_p, C.c_int64, C.c_int64, C.c_int64, C.c_float,
                                C.c_int64, C.c_void_p]),
     "b200_softmax_backward": (C.c_int, [C.c_void_p, C.c_void_p, C.c_int64, C.c_void_p, C.c_int64, C.c_void_p, C.c_int64,
@@ -319,3 +333,56 @@ class Context:
                                    self._ptr_array(v), self._ptr_array(shadows) if shadows else None,
                                    (C.c_int64 * n)(*sizes), p_dtype, g_dtype, lr, beta1, beta2, eps, step,
                                    self._s(stream)))
+
+    # ---- sharded matmul --------------------------------------------------------------------------------------------
+    def ipc_get_handle(self, dptr) -> bytes:
+        buf = C.create_string_buffer(64)
+        check(lib().b200_ipc_get_handle(self._h, ptr(dptr), buf))
+        return buf.raw
+
+    def ipc_open_handle(self, handle: bytes) -> int:
+        out = C.c_void_p()
+        check(lib().b200_ipc_open_handle(self._h, C.create_string_buffer(handle, 64), C.byref(out)))
+        return out.value or 0
+
+    def ipc_close_handle(self, dptr) -> None:
+        check(lib().b200_ipc_close_handle(self._h, ptr(dptr)))
+
+    def gemm_allgather(self, desc: GemmDesc, peer_c, my_rank: int, stream=None) -> None:
+        check(lib().b200_gemm_allgather(self._h, C.byref(desc), self._ptr_array(peer_c), len(peer_c), my_rank,
+                                        self._s(stream)))
+
+    def gemm_reduce_scatter_partials(self, desc: GemmDesc, peer_slots, my_rank: int, stream=None) -> None:
+        check(lib().b200_gemm_reduce_scatter_partials(self._h, C.byref(desc), self._ptr_array(peer_slots), len(peer_slots),
+                                                      my_rank, self._s(stream)))
+
+    def reduce_slices(self, slices, n_slices: int, desc: GemmDesc, stream=None) -> None:
+        check(lib().b200_reduce_slices(self._h, ptr(slices), n_slices, C.byref(desc), self._s(stream)))
+
+    # ---- pool and traces ---------------------------------------------------------------------------------------------
+    def pool_alloc(self, nbytes: int) -> int:
+        out = C.c_void_p()
+        check(lib().b200_pool_alloc(self._h, nbytes, C.byref(out)))
+        return out.value or 0
+
+    def pool_free(self, dptr) -> None:
+        check(lib().b200_pool_free(self._h, ptr(dptr)))
+
+    def pool_stats(self) -> tuple[int, int]:
+        r, u = C.c_size_t(), C.c_size_t()
+        check(lib().b200_pool_stats(self._h, C.byref(r), C.byref(u)))
+        return r.value, u.value
+
+    def trace_begin(self) -> int:
+        tid = C.c_uint32()
+        check(lib().b200_trace_begin(self._h, C.byref(tid)))
+        return tid.value
+
+    def trace_end(self, tid: int) -> None:
+        check(lib().b200_trace_end(self._h, tid))
+
+    def trace_execute(self, tid: int, blocking: bool = False) -> None:
+        check(lib().b200_trace_execute(self._h, tid, int(blocking)))
+
+    def trace_release(self, tid: int) -> None:
+        check(lib().b200_trace_release(self._h, tid))

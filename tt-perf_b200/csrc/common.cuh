@@ -71,4 +71,7 @@ struct b200_ctx {
 namespace b200 {
 // Grows the context scratch to at least `bytes` (never shrinks). Not allowed during stream capture.
 int ensure_scratch(b200_ctx* ctx, size_t bytes);
+// Pool / trace state attached to a context (pool.cu).
+void pool_destroy(b200_ctx* ctx);
+bool pool_is_recording(b200_ctx* ctx);
 }  // namespace b200

@@ -28,6 +28,9 @@ int fail(int code, const char* fmt, ...) {
 
 int ensure_scratch(b200_ctx* ctx, size_t bytes) {
     if (bytes <= ctx->scratch_bytes) return B200_OK;
+    if (pool_is_recording(ctx))
+        return fail(B200_ERR_UNSUPPORTED, "an op needs %zu bytes of scratch while a trace is being recorded; run the step "
+                    "once untraced first so the scratch exists", bytes);
     DeviceScope scope(ctx->device);
     // Round up so that a sweep over growing shapes reallocates rarely.
     size_t want = (bytes + (size_t(64) << 20) - 1) & ~((size_t(64) << 20) - 1);
@@ -111,6 +114,7 @@ int b200_ctx_destroy(b200_ctx* ctx) {
     if (!ctx) return B200_OK;
     DeviceScope scope(ctx->device);
     cudaDeviceSynchronize();
+    pool_destroy(ctx);
     if (ctx->d_scratch) cudaFree(ctx->d_scratch);
     if (ctx->d_status) cudaFree(ctx->d_status);
     if (ctx->stream) cudaStreamDestroy(ctx->stream);
@@ -132,6 +136,8 @@ int b200_ctx_sm_count(const b200_ctx* ctx, int* out) {
 
 int b200_synchronize(b200_ctx* ctx, void* stream) {
     B200_REQUIRE(ctx != nullptr, "b200_synchronize: ctx is NULL");
+    if (pool_is_recording(ctx) && ctx->pick(stream) == ctx->stream)
+        return fail(B200_ERR_UNSUPPORTED, "b200_synchronize: the context stream is recording a trace");
     DeviceScope scope(ctx->device);
     B200_CUDA_TRY(cudaStreamSynchronize(ctx->pick(stream)));
     int status = 0;
@@ -178,6 +184,9 @@ int b200_memcpy_d2h(b200_ctx* ctx, void* h_dst, const void* d_src, size_t bytes,
     B200_REQUIRE(ctx != nullptr, "b200_memcpy_d2h: ctx is NULL");
     if (bytes == 0) return B200_OK;
     B200_REQUIRE(h_dst && d_src, "b200_memcpy_d2h: NULL buffer");
+    if (pool_is_recording(ctx) && ctx->pick(stream) == ctx->stream)
+        return fail(B200_ERR_UNSUPPORTED, "b200_memcpy_d2h: the context stream is recording a trace (reading a tensor back "
+                    "synchronises)");
     DeviceScope scope(ctx->device);
     B200_CUDA_TRY(cudaMemcpyAsync(h_dst, d_src, bytes, cudaMemcpyDeviceToHost, ctx->pick(stream)));
     B200_CUDA_TRY(cudaStreamSynchronize(ctx->pick(stream)));

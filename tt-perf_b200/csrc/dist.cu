@@ -1,0 +1,130 @@
+// Sharded matmul across the GPUs of one NVSwitch node, one process per GPU.
+//
+// The collective is fused into the GEMM: the epilogue's TMA stores write each finished output tile straight into
+// its final position in peer GPUs' memory over NVLink (plain peer stores; no TMA multicast, no loads from peers),
+// so the transfer overlaps the tensor-core work tile by tile and no separate gather / scatter pass exists.
+//
+//   N-split + all-gather (bench/metal/matmul_tensor_parallel.cpp:70-92; scripts/matmul_2dev_distributed.py:49-76):
+//     rank r holds B[:, r*N/g:(r+1)*N/g]; its tiles of C[:, slice r] are stored into the full C of every rank.
+//   K-split + reduce-scatter (not in the reference; defined by the distributed-matmul configuration):
+//     rank r holds A[:, K_r], B[K_r, :]; its fp32 partial tiles of row block j are stored into slot r of rank j's
+//     staging buffer; after a barrier every rank sums its g slots and rounds to bf16 once.
+//
+// Peer buffers are shared between the processes with CUDA IPC handles (exchanged by the host program, for example
+// through torch.distributed). Completion: the kernel's stores are visible to a peer only after this rank's stream
+// work has finished AND the ranks have synchronised (a barrier / tiny all-reduce issued by the host program).
+#include <cstring>
+
+#include "gemm_common.cuh"
+
+using namespace b200;
+
+extern "C" {
+
+int b200_ipc_get_handle(b200_ctx* ctx, void* dptr, void* out_handle64) {
+    B200_REQUIRE(ctx && dptr && out_handle64, "b200_ipc_get_handle: NULL argument");
+    static_assert(sizeof(cudaIpcMemHandle_t) == 64, "IPC handle size");
+    DeviceScope scope(ctx->device);
+    cudaIpcMemHandle_t h;
+    B200_CUDA_TRY(cudaIpcGetMemHandle(&h, dptr));
+    memcpy(out_handle64, &h, sizeof(h));
+    return B200_OK;
+}
+
+int b200_ipc_open_handle(b200_ctx* ctx, const void* handle64, void** out_dptr) {
+    B200_REQUIRE(ctx && handle64 && out_dptr, "b200_ipc_open_handle: NULL argument");
+    DeviceScope scope(ctx->device);
+    cudaIpcMemHandle_t h;
+    memcpy(&h, handle64, sizeof(h));
+    B200_CUDA_TRY(cudaIpcOpenMemHandle(out_dptr, h, cudaIpcMemLazyEnablePeerAccess));
+    return B200_OK;
+}
+
+int b200_ipc_close_handle(b200_ctx* ctx, void* dptr) {
+    B200_REQUIRE(ctx != nullptr, "b200_ipc_close_handle: ctx is NULL");
+    if (!dptr) return B200_OK;
+    DeviceScope scope(ctx->device);
+    B200_CUDA_TRY(cudaIpcCloseMemHandle(dptr));
+    return B200_OK;
+}
+
+static int check_dist_desc(const char* who, const b200_gemm_desc* d, int n_ranks, int my_rank) {
+    B200_REQUIRE(d != nullptr, "%s: desc is NULL", who);
+    B200_REQUIRE(n_ranks >= 1 && n_ranks <= 8, "%s: n_ranks must be in [1, 8] (got %d)", who, n_ranks);
+    B200_REQUIRE(my_rank >= 0 && my_rank < n_ranks, "%s: my_rank %d out of range", who, my_rank);
+    B200_REQUIRE(d->M > 0 && d->N > 0 && d->K > 0 && d->batch == 1, "%s: needs M, N, K > 0 and batch 1", who);
+    B200_REQUIRE(d->A && d->B, "%s: A or B is NULL", who);
+    B200_REQUIRE(d->lda >= (d->transpose_a ? d->M : d->K) && d->ldb >= (d->transpose_b ? d->K : d->N),
+                 "%s: lda or ldb shorter than a row", who);
+    const char* why = nullptr;
+    if (!gemm_tcgen05_eligible(*d, &why)) return fail(B200_ERR_INVALID_ARG, "%s: %s", who, why);
+    return B200_OK;
+}
+
+int b200_gemm_allgather(b200_ctx* ctx, const b200_gemm_desc* d, void* const* peer_c, int n_ranks, int my_rank, void* stream) {
+    B200_REQUIRE(ctx != nullptr, "b200_gemm_allgather: ctx is NULL");
+    int rc = check_dist_desc("b200_gemm_allgather", d, n_ranks, my_rank);
+    if (rc != B200_OK) return rc;
+    B200_REQUIRE(peer_c != nullptr, "b200_gemm_allgather: peer_c is NULL");
+    B200_REQUIRE(d->ldc >= d->N * n_ranks, "b200_gemm_allgather: ldc (%lld) must cover the gathered width %lld",
+                 (long long)d->ldc, (long long)(d->N * n_ranks));
+    const size_t es = d->c_dtype == B200_F32 ? 4 : 2;
+    B200_REQUIRE((d->N * es) % 16 == 0, "b200_gemm_allgather: the shard width must be a multiple of 16 bytes");
+    GemmRoute route;
+    route.n_dst = n_ranks;
+    for (int p = 0; p < n_ranks; ++p) {
+        B200_REQUIRE(peer_c[p] != nullptr, "b200_gemm_allgather: peer_c[%d] is NULL", p);
+        route.dst[p] = static_cast<char*>(peer_c[p]) + static_cast<size_t>(my_rank) * d->N * es;
+        route.rows[p] = d->M;
+    }
+    b200_gemm_desc local = *d;
+    local.C = route.dst[my_rank];
+    local.split_k = 1;
+    DeviceScope scope(ctx->device);
+    return launch_gemm_tcgen05(ctx, local, 1, ctx->pick(stream), &route);
+}
+
+int b200_gemm_reduce_scatter_partials(b200_ctx* ctx, const b200_gemm_desc* d, void* const* peer_slots, int n_ranks,
+                                      int my_rank, void* stream) {
+    B200_REQUIRE(ctx != nullptr, "b200_gemm_reduce_scatter_partials: ctx is NULL");
+    int rc = check_dist_desc("b200_gemm_reduce_scatter_partials", d, n_ranks, my_rank);
+    if (rc != B200_OK) return rc;
+    B200_REQUIRE(peer_slots != nullptr, "b200_gemm_reduce_scatter_partials: peer_slots is NULL");
+    B200_REQUIRE(d->M % n_ranks == 0 && (d->M / n_ranks) % 128 == 0,
+                 "b200_gemm_reduce_scatter_partials: M / n_ranks must be a multiple of the 128-row tile (M = %lld)",
+                 (long long)d->M);
+    B200_REQUIRE(d->N % 4 == 0, "b200_gemm_reduce_scatter_partials: N must be a multiple of 4");
+    const long long rows = d->M / n_ranks;
+    GemmRoute route;
+    route.n_dst = n_ranks;
+    route.scatter_rows = static_cast<int>(rows);
+    for (int p = 0; p < n_ranks; ++p) {
+        B200_REQUIRE(peer_slots[p] != nullptr, "b200_gemm_reduce_scatter_partials: peer_slots[%d] is NULL", p);
+        // rank p's staging buffer is [n_ranks][rows][N] fp32; this rank writes slot `my_rank`
+        route.dst[p] = static_cast<float*>(peer_slots[p]) + static_cast<size_t>(my_rank) * rows * d->N;
+        route.rows[p] = rows;
+    }
+    b200_gemm_desc local = *d;
+    local.C = route.dst[my_rank];
+    local.ldc = d->N;
+    local.c_dtype = B200_F32;
+    local.bias = nullptr;
+    local.activation = B200_ACT_NONE;
+    local.alpha = 1.0f;
+    local.causal_mask = 0;
+    local.split_k = 1;
+    DeviceScope scope(ctx->device);
+    return launch_gemm_tcgen05(ctx, local, 1, ctx->pick(stream), &route);
+}
+
+int b200_reduce_slices(b200_ctx* ctx, const float* slices, int n_slices, const b200_gemm_desc* d, void* stream) {
+    B200_REQUIRE(ctx && d, "b200_reduce_slices: NULL argument");
+    B200_REQUIRE(n_slices >= 1 && d->M >= 0 && d->N >= 0 && d->batch >= 1, "b200_reduce_slices: bad sizes");
+    if (d->M == 0 || d->N == 0) return B200_OK;
+    B200_REQUIRE(slices && d->C, "b200_reduce_slices: NULL buffer");
+    B200_REQUIRE(d->ldc >= d->N, "b200_reduce_slices: ldc < N");
+    DeviceScope scope(ctx->device);
+    return launch_splitk_reduce(ctx, *d, slices, n_slices, ctx->pick(stream));
+}
+
+}  // extern "C"

@@ -29,15 +29,57 @@ __device__ __forceinline__ float epi_bias(const EpiParams& e, int n) {
                       : bf16_bits_to_float(static_cast<const uint16_t*>(e.bias)[n]);
 }
 
+// Out of line on purpose: inlined, the compiler evaluates both GELU forms for every element and selects, which
+// costs ~100 instructions per output even when no activation is requested.
+static __device__ __noinline__ float epi_gelu_call(float v, int tanh_form) {
+    return tanh_form ? gelu_tanh_approx(v) : gelu_exact(v);
+}
+
 __device__ __forceinline__ float epi_apply(const EpiParams& e, float acc, int m, int n) {
     float v = acc * e.alpha + epi_bias(e, n);
     if (e.causal && n > m) v = e.mask_value;
     if (e.act == B200_ACT_RELU) {
         v = fmaxf(v, 0.0f);
     } else if (e.act == B200_ACT_GELU) {
-        v = e.gelu_tanh ? gelu_tanh_approx(v) : gelu_exact(v);
+        v = epi_gelu_call(v, e.gelu_tanh);
     }
     return v;
+}
+
+// The same epilogue for 32 consecutive columns n .. n+31 of one row, with every decision hoisted out of the
+// element loops (uniform branches). Columns >= N are computed on clamped bias indices and discarded by the caller.
+__device__ __forceinline__ void epi_apply32(const EpiParams& e, const uint32_t (&v)[32], float (&f)[32], int row, int n,
+                                            int N) {
+#pragma unroll
+    for (int i = 0; i < 32; ++i) f[i] = __uint_as_float(v[i]) * e.alpha;
+    if (e.bias != nullptr) {
+        if (e.bias_f32) {
+            const float* b = static_cast<const float*>(e.bias);
+#pragma unroll
+            for (int i = 0; i < 32; ++i) f[i] += b[min(n + i, N - 1)];
+        } else {
+            const uint16_t* b = static_cast<const uint16_t*>(e.bias);
+#pragma unroll
+            for (int i = 0; i < 32; ++i) f[i] += bf16_bits_to_float(b[min(n + i, N - 1)]);
+        }
+    }
+    if (e.causal) {
+#pragma unroll
+        for (int i = 0; i < 32; ++i)
+            if (n + i > row) f[i] = e.mask_value;
+    }
+    if (e.act == B200_ACT_RELU) {
+#pragma unroll
+        for (int i = 0; i < 32; ++i) f[i] = fmaxf(f[i], 0.0f);
+    } else if (e.act == B200_ACT_GELU) {
+        if (e.gelu_tanh) {
+#pragma unroll
+            for (int i = 0; i < 32; ++i) f[i] = gelu_tanh_approx(f[i]);
+        } else {
+#pragma unroll
+            for (int i = 0; i < 32; ++i) f[i] = gelu_exact(f[i]);
+        }
+    }
 }
 
 __device__ __forceinline__ uint32_t pack_bf16x2(float lo, float hi) {
@@ -62,10 +104,37 @@ struct GemmParams {
     int partial_round_bf16;  // HiFi2 / LoFi: round partial sums to bf16 precision
     EpiParams epi;
     int* status;
+    int group_m;       // tile rasterisation: row-tiles per column sweep
+    // Output routing of the TMA-store epilogue (epi_mode 1). n_dst destination tensor maps receive every tile
+    // (1 = the local C; g = the same column slice of C on every GPU of an all-gather). scatter_rows > 0 selects a
+    // single destination per tile instead: map index m0 / scatter_rows, row coordinate relative to that block
+    // (row-block owner of a reduce-scatter).
+    int epi_mode;      // 0 = direct predicated stores (any alignment), 1 = shared-memory staging + TMA store
+    int n_dst;
+    int scatter_rows;
+#ifdef B200_GEMM_PROFILE
+    long long* prof;   // development builds only: per-CTA clock stamps
+#endif
+};
+
+// Destination tensor maps of the TMA-store epilogue.
+struct CMaps {
+    CUtensorMap m[8];
+};
+
+// Where the output tiles of one launch go when they are not the descriptor's own C.
+struct GemmRoute {
+    int n_dst = 0;                 // 0 = descriptor's C only
+    void* dst[8] = {};             // base address of each destination matrix (already offset to this rank's slice)
+    long long rows[8] = {};        // rows of each destination matrix
+    int scatter_rows = 0;
 };
 
 // Host-side launchers implemented in the kernel translation units.
-int launch_gemm_tcgen05(b200_ctx* ctx, const b200_gemm_desc& d, int k_splits, cudaStream_t stream);
+int launch_gemm_tcgen05(b200_ctx* ctx, const b200_gemm_desc& d, int k_splits, cudaStream_t stream,
+                        const GemmRoute* route = nullptr);
+// Sums `splits` fp32 slices [splits][batch][M][N], applies the descriptor's epilogue and writes C.
+int launch_splitk_reduce(b200_ctx* ctx, const b200_gemm_desc& d, const float* partial, int splits, cudaStream_t stream);
 int launch_gemm_simt(b200_ctx* ctx, const b200_gemm_desc& d, cudaStream_t stream);
 bool gemm_tcgen05_eligible(const b200_gemm_desc& d, const char** why);
 // Chooses the K-slice count for the tcgen05 path (1 = no split).

@@ -21,6 +21,8 @@
 #include "ptx.cuh"
 
 #include <algorithm>
+#include <cstdlib>
+#include <cstring>
 
 namespace b200 {
 
@@ -32,7 +34,7 @@ constexpr int BM = 128;
 constexpr int BK = 64;
 constexpr int UMMA_K = 16;
 constexpr int NUM_THREADS = 192;
-constexpr int GROUP_M = 8;  // tile rasterisation: GROUP_M row-tiles share each B tile while it is hot in L2
+constexpr int EPI_STAGE_BYTES = 4096;  // one 32-row x 128-byte staging box per epilogue warp and buffer
 
 template <int BN>
 struct TileCfg {
@@ -41,8 +43,9 @@ struct TileCfg {
     static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
     static constexpr int STAGES = (BN == 256) ? 4 : (BN == 128 ? 6 : 8);
     static constexpr int TMEM_COLS = 2 * BN;
+    static constexpr int EPI_BYTES = 4 * 2 * EPI_STAGE_BYTES;  // 4 epilogue warps, double buffered
     static constexpr int BARRIER_BYTES = 256;
-    static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + BARRIER_BYTES + 1024;
+    static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + EPI_BYTES + BARRIER_BYTES + 1024;
 };
 
 struct WorkItem {
@@ -57,10 +60,10 @@ __device__ __forceinline__ WorkItem decode_work(const GemmParams& p, int w, int 
     int r = w - it.split * per_split;
     it.b = r / tiles_mn;
     int t = r - it.b * tiles_mn;
-    const int tiles_per_group = GROUP_M * p.num_n_tiles;
+    const int tiles_per_group = p.group_m * p.num_n_tiles;
     const int g = t / tiles_per_group;
-    const int first_m = g * GROUP_M;
-    const int gsz = min(p.num_m_tiles - first_m, GROUP_M);
+    const int first_m = g * p.group_m;
+    const int gsz = min(p.num_m_tiles - first_m, p.group_m);
     const int rr = t - g * tiles_per_group;
     const int mi = first_m + rr % gsz;
     const int ni = rr / gsz;
@@ -74,14 +77,15 @@ __device__ __forceinline__ WorkItem decode_work(const GemmParams& p, int w, int 
 template <int BN, bool A_KMAJOR, bool B_KMAJOR>
 __global__ void __launch_bounds__(NUM_THREADS, 1)
 gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
-                    const GemmParams p) {
+                    const __grid_constant__ CMaps tmC, const GemmParams p) {
     using Cfg = TileCfg<BN>;
     constexpr int STAGES = Cfg::STAGES;
 
     extern __shared__ uint8_t smem_raw[];
     // 128-byte-swizzled tiles must start on a 1024-byte boundary.
     uint8_t* smem = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
-    uint8_t* bar_base = smem + STAGES * Cfg::STAGE_BYTES;
+    uint8_t* epi_smem = smem + STAGES * Cfg::STAGE_BYTES;  // 1024-byte aligned: stage sizes are multiples of 1024
+    uint8_t* bar_base = epi_smem + Cfg::EPI_BYTES;
     uint64_t* full_bar = reinterpret_cast<uint64_t*>(bar_base);
     uint64_t* empty_bar = full_bar + STAGES;
     uint64_t* tmem_full_bar = empty_bar + STAGES;
@@ -184,6 +188,10 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
                 if (!mbar_wait(&tmem_empty_bar[acc], acc_phase ^ 1u, abort_flag)) break;
                 tcgen05_fence_after_sync();
                 const uint32_t d_tmem = tmem_base + static_cast<uint32_t>(acc * BN);
+#ifdef B200_GEMM_PROFILE
+                const int prof_slot = (w - blockIdx.x) / gridDim.x;
+                if (p.prof && prof_slot < 8) p.prof[(blockIdx.x * 8 + prof_slot) * 8 + 0] = clock64();
+#endif
                 for (int kb = it.kb_begin; kb < it.kb_end; ++kb) {
                     if (!mbar_wait(&full_bar[stage], phase, abort_flag)) {
                         ok = false;
@@ -206,6 +214,9 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
                 }
                 if (!ok) break;
                 umma_commit(&tmem_full_bar[acc]);  // accumulator complete
+#ifdef B200_GEMM_PROFILE
+                if (p.prof && prof_slot < 8) p.prof[(blockIdx.x * 8 + prof_slot) * 8 + 1] = clock64();
+#endif
                 acc ^= 1;
                 if (acc == 0) acc_phase ^= 1u;
             }
@@ -215,11 +226,17 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
         const int q = warp & 3;  // TMEM lane quarter this warp may read
         int acc = 0;
         uint32_t acc_phase = 0;
+        int ebuf = 0;  // staging buffer the next TMA-store box uses
+        uint8_t* stage_base = epi_smem + (warp - 2) * 2 * EPI_STAGE_BYTES;
         for (int w = blockIdx.x; w < p.total_work; w += gridDim.x) {
             const WorkItem it = decode_work(p, w, BN);
             const bool got = mbar_wait(&tmem_full_bar[acc], acc_phase, abort_flag);
             if (!__all_sync(0xffffffffu, got)) break;
             tcgen05_fence_after_sync();
+#ifdef B200_GEMM_PROFILE
+            const int eprof_slot = (w - blockIdx.x) / gridDim.x;
+            if (p.prof && eprof_slot < 8 && threadIdx.x == 64) p.prof[(blockIdx.x * 8 + eprof_slot) * 8 + 2] = clock64();
+#endif
             const int row = it.m0 + q * 32 + lane;
             const bool row_ok = row < p.M;
             const uint32_t taddr = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + static_cast<uint32_t>(acc * BN);
@@ -255,6 +272,55 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
                         }
                     }
                 }
+            } else if (p.epi_mode == 1) {
+                // Staged epilogue: each warp converts a 32-row x 128-byte box (64 bf16 or 32 fp32 columns) into
+                // shared memory in the 128-byte-swizzled layout and one lane hands it to TMA, which writes full
+                // lines, clips the ragged edges and can target several destination matrices (peer GPUs).
+                const int box_cols = p.c_f32 ? 32 : 64;
+                int dst_first = 0, dst_count = p.n_dst, row_coord = it.m0 + q * 32;
+                if (p.scatter_rows > 0) {
+                    dst_first = it.m0 / p.scatter_rows;
+                    dst_count = 1;
+                    row_coord -= dst_first * p.scatter_rows;
+                }
+#pragma unroll 1
+                for (int c = 0; c < BN; c += box_cols) {
+                    const int n = it.n0 + c;
+                    if (n >= p.N) break;
+                    uint8_t* sbuf = stage_base + ebuf * EPI_STAGE_BYTES;
+                    if (lane == 0) tma_store_wait_read<1>();  // the box stored two iterations ago has left this buffer
+                    __syncwarp();
+                    uint8_t* srow = sbuf + lane * 128;
+#pragma unroll 1
+                    for (int h = 0; h * 32 < box_cols; ++h) {
+                        const int nh = n + h * 32;
+                        if (nh >= p.N) break;
+                        uint32_t v[32];
+                        tmem_ld_32x32b_x32(taddr + c + h * 32, v);
+                        tmem_ld_wait();
+                        float f[32];
+                        epi_apply32(p.epi, v, f, row, nh, p.N);
+                        if (p.c_f32) {
+#pragma unroll
+                            for (int j = 0; j < 8; ++j)
+                                *reinterpret_cast<float4*>(srow + ((j ^ (lane & 7)) << 4)) =
+                                    make_float4(f[4 * j], f[4 * j + 1], f[4 * j + 2], f[4 * j + 3]);
+                        } else {
+#pragma unroll
+                            for (int j = 0; j < 4; ++j)
+                                *reinterpret_cast<uint4*>(srow + (((h * 4 + j) ^ (lane & 7)) << 4)) =
+                                    make_uint4(pack_bf16x2(f[8 * j], f[8 * j + 1]), pack_bf16x2(f[8 * j + 2], f[8 * j + 3]),
+                                               pack_bf16x2(f[8 * j + 4], f[8 * j + 5]), pack_bf16x2(f[8 * j + 6], f[8 * j + 7]));
+                        }
+                    }
+                    fence_proxy_async_smem();
+                    __syncwarp();
+                    if (lane == 0) {
+                        for (int d = 0; d < dst_count; ++d) tma_store_3d(&tmC.m[dst_first + d], sbuf, n, row_coord, it.b);
+                        tma_store_commit();
+                    }
+                    ebuf ^= 1;
+                }
             } else {
                 const size_t crow = static_cast<size_t>(it.b) * p.stride_c + static_cast<size_t>(row_ok ? row : 0) * p.ldc;
 #pragma unroll 1
@@ -266,11 +332,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
                     tmem_ld_wait();
                     const bool full = (n + 32 <= p.N);
                     float f[32];
-#pragma unroll
-                    for (int i = 0; i < 32; ++i) {
-                        const int nn = full ? (n + i) : min(n + i, p.N - 1);
-                        f[i] = epi_apply(p.epi, __uint_as_float(v[i]), row, nn);
-                    }
+                    epi_apply32(p.epi, v, f, row, n, p.N);
                     if (row_ok) {
                         if (p.c_f32) {
                             float* dst = static_cast<float*>(p.C) + crow + n;
@@ -302,6 +364,9 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
                     }
                 }
             }
+#ifdef B200_GEMM_PROFILE
+            if (p.prof && eprof_slot < 8 && threadIdx.x == 64) p.prof[(blockIdx.x * 8 + eprof_slot) * 8 + 3] = clock64();
+#endif
             // Hand the accumulator buffer back to the MMA warp.
             tcgen05_fence_before_sync();
             __syncwarp();
@@ -309,6 +374,8 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
             acc ^= 1;
             if (acc == 0) acc_phase ^= 1u;
         }
+        // Every TMA store of this warp must have completed before the CTA (and its shared memory) goes away.
+        if (lane == 0) tma_store_wait_all<0>();
     }
 
     // ---------------------------------------------------------------------- teardown
@@ -363,16 +430,18 @@ __global__ void splitk_reduce_kernel(const GemmParams p) {
 
 // 3-D tensor map {inner, rows, batch} over a bf16 matrix with a 128-byte-swizzled box.
 int make_tensor_map(b200_ctx* ctx, CUtensorMap* out, const void* base, uint64_t inner, uint64_t rows, uint64_t batch,
-                    uint64_t ld_elems, uint64_t batch_stride_elems, uint32_t box_inner, uint32_t box_rows) {
+                    uint64_t ld_elems, uint64_t batch_stride_elems, uint32_t box_inner, uint32_t box_rows,
+                    bool f32 = false) {
+    const uint64_t es = f32 ? 4 : 2;
     cuuint64_t dims[3] = {inner, rows, batch};
     if (batch <= 1 || batch_stride_elems == 0) {
         dims[2] = 1;
         batch_stride_elems = rows * ld_elems;
     }
-    cuuint64_t strides[2] = {ld_elems * 2, batch_stride_elems * 2};
+    cuuint64_t strides[2] = {ld_elems * es, batch_stride_elems * es};
     cuuint32_t box[3] = {box_inner, box_rows, 1};
     cuuint32_t estr[3] = {1, 1, 1};
-    CUresult r = ctx->encode_tiled(out, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, const_cast<void*>(base), dims, strides, box,
+    CUresult r = ctx->encode_tiled(out, f32 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT32 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, const_cast<void*>(base), dims, strides, box,
                                    estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
                                    CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
     if (r != CUDA_SUCCESS) {
@@ -386,7 +455,8 @@ int make_tensor_map(b200_ctx* ctx, CUtensorMap* out, const void* base, uint64_t 
 }
 
 template <int BN, bool A_KMAJOR, bool B_KMAJOR>
-int launch_variant(const CUtensorMap& tmA, const CUtensorMap& tmB, const GemmParams& p, int grid, cudaStream_t stream) {
+int launch_variant(const CUtensorMap& tmA, const CUtensorMap& tmB, const CMaps& tmC, const GemmParams& p, int grid,
+                   cudaStream_t stream) {
     using Cfg = TileCfg<BN>;
     auto kernel = gemm_tcgen05_kernel<BN, A_KMAJOR, B_KMAJOR>;
     static bool configured[64] = {};  // per template instance and device: the attribute is per device function
@@ -396,18 +466,18 @@ int launch_variant(const CUtensorMap& tmA, const CUtensorMap& tmB, const GemmPar
         B200_CUDA_TRY(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::SMEM_BYTES));
         if (dev >= 0 && dev < 64) configured[dev] = true;
     }
-    kernel<<<grid, NUM_THREADS, Cfg::SMEM_BYTES, stream>>>(tmA, tmB, p);
+    kernel<<<grid, NUM_THREADS, Cfg::SMEM_BYTES, stream>>>(tmA, tmB, tmC, p);
     B200_CUDA_TRY(cudaGetLastError());
     return B200_OK;
 }
 
 template <int BN>
-int launch_bn(bool a_kmajor, bool b_kmajor, const CUtensorMap& tmA, const CUtensorMap& tmB, const GemmParams& p, int grid,
-              cudaStream_t stream) {
-    if (a_kmajor && b_kmajor) return launch_variant<BN, true, true>(tmA, tmB, p, grid, stream);
-    if (a_kmajor && !b_kmajor) return launch_variant<BN, true, false>(tmA, tmB, p, grid, stream);
-    if (!a_kmajor && b_kmajor) return launch_variant<BN, false, true>(tmA, tmB, p, grid, stream);
-    return launch_variant<BN, false, false>(tmA, tmB, p, grid, stream);
+int launch_bn(bool a_kmajor, bool b_kmajor, const CUtensorMap& tmA, const CUtensorMap& tmB, const CMaps& tmC,
+              const GemmParams& p, int grid, cudaStream_t stream) {
+    if (a_kmajor && b_kmajor) return launch_variant<BN, true, true>(tmA, tmB, tmC, p, grid, stream);
+    if (a_kmajor && !b_kmajor) return launch_variant<BN, true, false>(tmA, tmB, tmC, p, grid, stream);
+    if (!a_kmajor && b_kmajor) return launch_variant<BN, false, true>(tmA, tmB, tmC, p, grid, stream);
+    return launch_variant<BN, false, false>(tmA, tmB, tmC, p, grid, stream);
 }
 
 inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
@@ -461,7 +531,16 @@ int gemm_choose_split_k(const b200_ctx* ctx, const b200_gemm_desc& d) {
     return (num_kb + per - 1) / per;  // every slice gets at least one K block
 }
 
-int launch_gemm_tcgen05(b200_ctx* ctx, const b200_gemm_desc& d, int k_splits, cudaStream_t stream) {
+int group_m_setting() {
+    static const int value = [] {
+        const char* e = getenv("B200_GEMM_GROUP_M");
+        const int v = e ? atoi(e) : 0;
+        return (v >= 1 && v <= 64) ? v : 16;
+    }();
+    return value;
+}
+
+int launch_gemm_tcgen05(b200_ctx* ctx, const b200_gemm_desc& d, int k_splits, cudaStream_t stream, const GemmRoute* route) {
     const bool a_kmajor = d.transpose_a == 0;  // A stored [M,K]
     const bool b_kmajor = d.transpose_b != 0;  // B stored [N,K]
     const int bn = gemm_choose_block_n(ctx, d);
@@ -495,6 +574,10 @@ int launch_gemm_tcgen05(b200_ctx* ctx, const b200_gemm_desc& d, int k_splits, cu
     p.epi.causal = d.causal_mask;
     p.epi.mask_value = d.mask_value;
     p.status = ctx->d_status;
+    p.group_m = group_m_setting();
+#ifdef B200_GEMM_PROFILE
+    p.prof = static_cast<long long*>(ctx->d_scratch);  // the probe sizes the scratch beforehand
+#endif
     p.partial = nullptr;
     p.partial_round_bf16 = (d.fidelity == B200_LOFI || d.fidelity == B200_HIFI2) ? 1 : 0;
     if (k_splits > 1) {
@@ -517,13 +600,41 @@ int launch_gemm_tcgen05(b200_ctx* ctx, const b200_gemm_desc& d, int k_splits, cu
         rc = make_tensor_map(ctx, &tmB, d.B, d.N, d.K, d.batch, d.ldb, d.stride_b, 64, BK);
     if (rc != B200_OK) return rc;
 
+    // Output routing. The staged TMA-store epilogue needs 16-byte aligned rows of C; routed launches require it.
+    CMaps tmC;
+    memset(&tmC, 0, sizeof(tmC));
+    p.epi_mode = 0;
+    p.n_dst = 1;
+    p.scatter_rows = 0;
+    const uint32_t box_cols = p.c_f32 ? 32 : 64;
+    if (k_splits == 1) {
+        if (route != nullptr && route->n_dst > 0) {
+            B200_REQUIRE(route->n_dst <= 8, "b200_gemm: at most 8 destinations");
+            B200_REQUIRE((d.ldc % cvec) == 0, "b200_gemm: routed output needs ldc to be a multiple of %d elements", cvec);
+            for (int i = 0; i < route->n_dst; ++i) {
+                B200_REQUIRE(aligned16(route->dst[i]), "b200_gemm: destination %d is not 16-byte aligned", i);
+                rc = make_tensor_map(ctx, &tmC.m[i], route->dst[i], d.N, route->rows[i], 1, d.ldc, 0, box_cols, 32, p.c_f32);
+                if (rc != B200_OK) return rc;
+            }
+            p.epi_mode = 1;
+            p.n_dst = route->scatter_rows > 0 ? 1 : route->n_dst;
+            p.scatter_rows = route->scatter_rows;
+        } else if (p.c_vec_ok) {
+            rc = make_tensor_map(ctx, &tmC.m[0], d.C, d.N, d.M, d.batch, d.ldc, d.stride_c, box_cols, 32, p.c_f32);
+            if (rc != B200_OK) return rc;
+            p.epi_mode = 1;
+        }
+    } else {
+        B200_REQUIRE(route == nullptr || route->n_dst == 0, "b200_gemm: a routed product cannot be split along K");
+    }
+
     const int grid = min(p.total_work, ctx->sm_count);
     if (bn == 256)
-        rc = launch_bn<256>(a_kmajor, b_kmajor, tmA, tmB, p, grid, stream);
+        rc = launch_bn<256>(a_kmajor, b_kmajor, tmA, tmB, tmC, p, grid, stream);
     else if (bn == 128)
-        rc = launch_bn<128>(a_kmajor, b_kmajor, tmA, tmB, p, grid, stream);
+        rc = launch_bn<128>(a_kmajor, b_kmajor, tmA, tmB, tmC, p, grid, stream);
     else
-        rc = launch_bn<64>(a_kmajor, b_kmajor, tmA, tmB, p, grid, stream);
+        rc = launch_bn<64>(a_kmajor, b_kmajor, tmA, tmB, tmC, p, grid, stream);
     if (rc != B200_OK) return rc;
 
     if (k_splits > 1) {
@@ -533,6 +644,33 @@ int launch_gemm_tcgen05(b200_ctx* ctx, const b200_gemm_desc& d, int k_splits, cu
         splitk_reduce_kernel<<<blocks, threads, 0, stream>>>(p);
         B200_CUDA_TRY(cudaGetLastError());
     }
+    return B200_OK;
+}
+
+int launch_splitk_reduce(b200_ctx* ctx, const b200_gemm_desc& d, const float* partial, int splits, cudaStream_t stream) {
+    GemmParams p{};
+    p.M = static_cast<int>(d.M);
+    p.N = static_cast<int>(d.N);
+    p.batch = static_cast<int>(d.batch);
+    p.k_splits = splits;
+    p.partial = const_cast<float*>(partial);
+    p.C = d.C;
+    p.ldc = d.ldc;
+    p.stride_c = d.stride_c;
+    p.c_f32 = d.c_dtype == B200_F32;
+    p.epi.alpha = d.alpha;
+    p.epi.bias = d.bias;
+    p.epi.bias_f32 = d.bias_dtype == B200_F32;
+    p.epi.act = d.activation;
+    p.epi.gelu_tanh = d.fidelity == B200_LOFI;
+    p.epi.causal = d.causal_mask;
+    p.epi.mask_value = d.mask_value;
+    const long long work = static_cast<long long>(p.batch) * p.M * ((p.N + 3) / 4);
+    if (work == 0) return B200_OK;
+    const int threads = 256;
+    const int blocks = static_cast<int>(std::min<long long>((work + threads - 1) / threads, ctx->sm_count * 8ll));
+    splitk_reduce_kernel<<<blocks, threads, 0, stream>>>(p);
+    B200_CUDA_TRY(cudaGetLastError());
     return B200_OK;
 }
 
