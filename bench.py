@@ -100,6 +100,8 @@ def cpu_matmul_baseline(M: int, N: int, K: int, target_s: float = 12.0) -> dict:
     """The reference's CPU path for this workload — torch CPU fp32 matmul on bf16-rounded inputs, as
     scripts/matmul_sweep.py:84-108 times it — on a slab of rows of A sized for about `target_s` seconds."""
     import torch
+    if torch.get_num_threads() < (os.cpu_count() or 1):
+        torch.set_num_threads(os.cpu_count() or 1)   # torchrun pins OMP_NUM_THREADS=1; the baseline uses every core
     threads = torch.get_num_threads()
     g = torch.Generator().manual_seed(42)
     rows = min(M, 256)
@@ -132,6 +134,8 @@ def run_reference_arm(args) -> None:
     if rank != 0:
         return
     import torch
+    if torch.get_num_threads() < (os.cpu_count() or 1):
+        torch.set_num_threads(os.cpu_count() or 1)
     n = args.gpus
     size = 8192 if n == 1 else 16384
     M = N = K = size
@@ -288,6 +292,9 @@ def run_b200_distributed(args) -> None:
     world = int(os.environ.get("WORLD_SIZE", "1"))
     local_rank = int(os.environ.get("LOCAL_RANK", str(rank)))
     torch.cuda.set_device(local_rank)
+    # NCCL prints its version banner on stdout; keep stdout for the one JSON line
+    real_stdout = os.dup(1)
+    os.dup2(2, 1)
     dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
     ctx = pkg.Context(local_rank)
     st = torch.cuda.Stream()
@@ -326,7 +333,7 @@ def run_b200_distributed(args) -> None:
     ms_per_step = t.item() / args.steps
     clocks = None
     # keep all ranks busy together while rank 0 samples clocks
-    for _ in range(0 if args.quick else 30):
+    for _ in range(0 if args.quick else max(30, int(1500.0 / ms_per_step))):
         step()
     torch.cuda.synchronize()
     if rank == 0:
@@ -393,7 +400,10 @@ def run_b200_distributed(args) -> None:
             cpu = cpu_matmul_baseline(M, N, K)
             cpu.pop("seconds", None)
             line["cpu_baseline"] = cpu
+        sys.stdout.flush()
+        os.dup2(real_stdout, 1)
         print(json.dumps(line), flush=True)
+        os.dup2(2, 1)
     dist.barrier()
     mm.close()
     ctx.close()

@@ -145,7 +145,8 @@ def test_relu_and_gelu_backward(pkg, ctx, DT):
     assert mo.rel_frobenius(got, mo.gelu_backward(dy, x)) <= TOL
 
 
-@pytest.mark.parametrize("outer,R,inner", [(1, 1024, 128), (1, 64, 10), (16, 768, 1), (3, 50, 7), (1, 8192, 768), (4, 9, 1)])
+@pytest.mark.parametrize("outer,R,inner", [(1, 1024, 128), (1, 64, 10), (16, 768, 1), (3, 50, 7), (1, 8192, 768), (4, 9, 1), (1, 524288, 1),
+                                            (5, 100003, 1)])
 def test_reductions(pkg, ctx, DT, outer, R, inner):
     c = pkg.capi
     x = rnd((outer, R, inner), 61)

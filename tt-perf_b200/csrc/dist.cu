@@ -72,6 +72,7 @@ int b200_gemm_allgather(b200_ctx* ctx, const b200_gemm_desc* d, void* const* pee
     B200_REQUIRE((d->N * es) % 16 == 0, "b200_gemm_allgather: the shard width must be a multiple of 16 bytes");
     GemmRoute route;
     route.n_dst = n_ranks;
+    route.rotate = my_rank;  // own copy first, then rank+1, rank+2, ...: at any moment the ranks write to different peers
     for (int p = 0; p < n_ranks; ++p) {
         B200_REQUIRE(peer_c[p] != nullptr, "b200_gemm_allgather: peer_c[%d] is NULL", p);
         route.dst[p] = static_cast<char*>(peer_c[p]) + static_cast<size_t>(my_rank) * d->N * es;

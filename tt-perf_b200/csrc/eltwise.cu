@@ -180,6 +180,53 @@ __global__ void __launch_bounds__(kThreads) reduce_rows_kernel(const __nv_bfloat
     if (lane == 0) y[o] = __float2bfloat16_rn(op == R_MEAN ? acc / static_cast<float>(R) : acc);
 }
 
+// inner == 1 with few, long rows (a loss mean over a whole activation): each CTA reduces one chunk of one row and
+// combines through an fp32 accumulator, so the whole GPU works on the row instead of one warp.
+__global__ void __launch_bounds__(kThreads) reduce_rows_split_kernel(const __nv_bfloat16* x, float* acc_out, long long R, int op,
+                                                                      long long chunk, int vec) {
+    __shared__ float sh[kThreads / 32];
+    const long long o = blockIdx.y;
+    const long long c0 = blockIdx.x * chunk, c1 = min(R, c0 + chunk);
+    const __nv_bfloat16* row = x + o * R;
+    float acc = (op == R_MAX) ? -FLT_MAX : 0.0f;
+    if (vec) {  // chunk and row starts are multiples of 8 elements
+        for (long long v = c0 / 8 + threadIdx.x; v < c1 / 8; v += kThreads) {
+            float f[8];
+            unpack8(reinterpret_cast<const uint4*>(row)[v], f);
+#pragma unroll
+            for (int k = 0; k < 8; ++k) acc = (op == R_MAX) ? fmaxf(acc, f[k]) : acc + f[k];
+        }
+        for (long long i = (c1 / 8) * 8 + threadIdx.x; i < c1; i += kThreads) {
+            const float f = __bfloat162float(row[i]);
+            acc = (op == R_MAX) ? fmaxf(acc, f) : acc + f;
+        }
+    } else {
+        for (long long i = c0 + threadIdx.x; i < c1; i += kThreads) {
+            const float f = __bfloat162float(row[i]);
+            acc = (op == R_MAX) ? fmaxf(acc, f) : acc + f;
+        }
+    }
+#pragma unroll
+    for (int s = 16; s > 0; s >>= 1) {
+        const float other = __shfl_xor_sync(0xffffffffu, acc, s);
+        acc = (op == R_MAX) ? fmaxf(acc, other) : acc + other;
+    }
+    if ((threadIdx.x & 31) == 0) sh[threadIdx.x >> 5] = acc;
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        for (int k = 1; k < kThreads / 32; ++k) acc = (op == R_MAX) ? fmaxf(acc, sh[k]) : acc + sh[k];
+        float* dst = acc_out + o;
+        if (op == R_MAX) {
+            if (acc >= 0.0f)
+                atomicMax(reinterpret_cast<int*>(dst), __float_as_int(acc));
+            else
+                atomicMin(reinterpret_cast<unsigned int*>(dst), __float_as_uint(acc));
+        } else {
+            atomicAdd(dst, acc);
+        }
+    }
+}
+
 // inner > 1: CTA = 32 columns x 8 row lanes; partial results of the row slabs combined in fp32.
 __global__ void __launch_bounds__(kThreads) reduce_cols_kernel(const __nv_bfloat16* x, float* acc_out, long long R,
                                                                 long long inner, int op, long long rows_per_cta) {
@@ -404,6 +451,22 @@ int b200_reduce(b200_ctx* ctx, int op, const void* x, int64_t outer, int64_t R, 
     B200_REQUIRE(x && y, "b200_reduce: NULL buffer");
     DeviceScope scope(ctx->device);
     cudaStream_t s = ctx->pick(stream);
+    if (inner == 1 && R >= 16384 && outer <= ctx->sm_count && outer <= 65535) {
+        int rc = ensure_scratch(ctx, static_cast<size_t>(outer) * sizeof(float));
+        if (rc != B200_OK) return rc;
+        float* acc = static_cast<float*>(ctx->d_scratch);
+        fill_f32_kernel<<<grid_for(ctx, outer), kThreads, 0, s>>>(acc, outer, op == R_MAX ? -FLT_MAX : 0.0f);
+        long long chunks = std::max<long long>(1, std::min<long long>((ctx->sm_count * 4ll) / outer, R / 4096));
+        long long chunk = ((R + chunks - 1) / chunks + 7) / 8 * 8;
+        chunks = (R + chunk - 1) / chunk;
+        const int vec = al16(x) && (R % 8 == 0);
+        dim3 grid(static_cast<unsigned>(chunks), static_cast<unsigned>(outer));
+        reduce_rows_split_kernel<<<grid, kThreads, 0, s>>>(static_cast<const __nv_bfloat16*>(x), acc, R, op, chunk, vec);
+        cast_f32_to_bf16_kernel<<<grid_for(ctx, outer), kThreads, 0, s>>>(acc, static_cast<__nv_bfloat16*>(y), outer,
+                                                                       op == R_MEAN ? 1.0f / static_cast<float>(R) : 1.0f);
+        B200_CUDA_TRY(cudaGetLastError());
+        return B200_OK;
+    }
     if (inner == 1) {
         const int vec = al16(x) && (R % 8 == 0);
         const long long blocks = (outer + 7) / 8;

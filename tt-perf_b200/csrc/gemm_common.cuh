@@ -112,6 +112,7 @@ struct GemmParams {
     int epi_mode;      // 0 = direct predicated stores (any alignment), 1 = shared-memory staging + TMA store
     int n_dst;
     int scatter_rows;
+    int dst_rotate;    // first destination each box is sent to (ranks start at different peers, so no peer is hit by all at once)
 #ifdef B200_GEMM_PROFILE
     long long* prof;   // development builds only: per-CTA clock stamps
 #endif
@@ -128,6 +129,7 @@ struct GemmRoute {
     void* dst[8] = {};             // base address of each destination matrix (already offset to this rank's slice)
     long long rows[8] = {};        // rows of each destination matrix
     int scatter_rows = 0;
+    int rotate = 0;                // index of the destination to store to first
 };
 
 // Host-side launchers implemented in the kernel translation units.

@@ -316,7 +316,11 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
                     fence_proxy_async_smem();
                     __syncwarp();
                     if (lane == 0) {
-                        for (int d = 0; d < dst_count; ++d) tma_store_3d(&tmC.m[dst_first + d], sbuf, n, row_coord, it.b);
+                        for (int d = 0; d < dst_count; ++d) {
+                            int di = d + p.dst_rotate;
+                            if (di >= dst_count) di -= dst_count;
+                            tma_store_3d(&tmC.m[dst_first + di], sbuf, n, row_coord, it.b);
+                        }
                         tma_store_commit();
                     }
                     ebuf ^= 1;
@@ -606,6 +610,7 @@ int launch_gemm_tcgen05(b200_ctx* ctx, const b200_gemm_desc& d, int k_splits, cu
     p.epi_mode = 0;
     p.n_dst = 1;
     p.scatter_rows = 0;
+    p.dst_rotate = 0;
     const uint32_t box_cols = p.c_f32 ? 32 : 64;
     if (k_splits == 1) {
         if (route != nullptr && route->n_dst > 0) {
@@ -619,6 +624,7 @@ int launch_gemm_tcgen05(b200_ctx* ctx, const b200_gemm_desc& d, int k_splits, cu
             p.epi_mode = 1;
             p.n_dst = route->scatter_rows > 0 ? 1 : route->n_dst;
             p.scatter_rows = route->scatter_rows;
+            p.dst_rotate = (route->scatter_rows > 0 || route->rotate < 0 || route->rotate >= route->n_dst) ? 0 : route->rotate;
         } else if (p.c_vec_ok) {
             rc = make_tensor_map(ctx, &tmC.m[0], d.C, d.N, d.M, d.batch, d.ldc, d.stride_c, box_cols, 32, p.c_f32);
             if (rc != B200_OK) return rc;
