@@ -246,6 +246,13 @@ int b200_adam_step(b200_ctx* ctx, int64_t count, void* const* params, const void
 int b200_ipc_get_handle(b200_ctx* ctx, void* dptr, void* out_handle64);
 int b200_ipc_open_handle(b200_ctx* ctx, const void* handle64, void** out_dptr);
 int b200_ipc_close_handle(b200_ctx* ctx, void* dptr);
+/* Several GPUs driven by one process (MeshDevice with MeshShape(1, g), bench/metal/matmul_tensor_parallel.cpp:158-164):
+ * b200_enable_peer_access lets two contexts' GPUs address each other's memory; b200_peer_copy_2d copies a
+ * [rows x width_bytes] block between them on dst_ctx's stream after the work already queued on src_ctx's stream —
+ * the unfused form of ttnn::all_gather(t, dim) when the caller issues matmul and gather as two separate ops. */
+int b200_enable_peer_access(b200_ctx* a, b200_ctx* b);
+int b200_peer_copy_2d(b200_ctx* dst_ctx, void* dst, size_t dst_pitch_bytes, b200_ctx* src_ctx, const void* src,
+                      size_t src_pitch_bytes, size_t width_bytes, size_t rows);
 /* N-split (column parallel) + all-gather. desc describes the LOCAL product C[:, my_rank*N : (my_rank+1)*N] =
  * op(A) . op(B_shard) with N = shard width; desc->C is ignored; desc->ldc = leading dimension of the full gathered C
  * (>= N * n_ranks). peer_c[p] = base of the full C on rank p (peer_c[my_rank] = the local one). Every rank ends up

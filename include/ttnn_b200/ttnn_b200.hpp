@@ -243,6 +243,9 @@ public:
             b200_detail::check(b200_ctx_create(ord, &c), "MeshDevice: b200_ctx_create");
             ctx_.push_back(c);
         }
+        for (size_t i = 0; i < ctx_.size(); ++i)
+            for (size_t j = i + 1; j < ctx_.size(); ++j)
+                b200_detail::check(b200_enable_peer_access(ctx_[i], ctx_[j]), "MeshDevice: peer access");
         cqs_.resize(static_cast<size_t>(std::max(1, num_cqs)));
         for (auto& q : cqs_) q.device = this;
         open_ = true;
@@ -362,8 +365,21 @@ public:
     size_t device_index() const { return st_ ? st_->device_index : 0; }
     void* device_ptr() const { return st_ ? st_->dptr : nullptr; }
     const std::shared_ptr<b200_detail::Storage>& storage() const { return st_; }
+    // Mesh tensors: one storage per device of the mesh, all with this tensor's (per-device) shape.
     const std::vector<std::shared_ptr<b200_detail::Storage>>& shards() const { return shards_; }
-    void set_shards(std::vector<std::shared_ptr<b200_detail::Storage>> s) { shards_ = std::move(s); }
+    size_t num_shards() const { return shards_.empty() ? 1 : shards_.size(); }
+    Tensor shard(size_t i) const {
+        if (shards_.empty()) return *this;
+        return Tensor(shards_.at(i), shape_, dtype_, layout_);
+    }
+    static Tensor from_shards(const std::vector<Tensor>& parts) {
+        Tensor t = parts.at(0);
+        if (parts.size() > 1) {
+            t.shards_.clear();
+            for (const Tensor& p : parts) t.shards_.push_back(p.st_);
+        }
+        return t;
+    }
     MemoryConfig memory_config() const { return MemoryConfig{}; }
 
     // Same storage, different shape (ttnn::reshape is a view here: storage is always contiguous row-major).
@@ -559,7 +575,20 @@ inline Shape broadcast_shape(const Shape& a, const Shape& b, const char* op) {
     return Shape(out);
 }
 
+// Runs a single-device op on every device of a mesh tensor and reassembles the results.
+template <typename Fn>
+inline Tensor per_shard(const Tensor& a, Fn&& fn) {
+    if (a.num_shards() == 1) return fn(a, 0);
+    std::vector<Tensor> parts;
+    for (size_t i = 0; i < a.num_shards(); ++i) parts.push_back(fn(a.shard(i), i));
+    return Tensor::from_shards(parts);
+}
+
+inline Tensor binary1(int op, const Tensor& a, const Tensor& b, const char* name);
 inline Tensor binary(int op, const Tensor& a, const Tensor& b, const char* name) {
+    return per_shard(a, [&](const Tensor& as, size_t i) { return binary1(op, as, b.shard(i), name); });
+}
+inline Tensor binary1(int op, const Tensor& a, const Tensor& b, const char* name) {
     const Shape os = broadcast_shape(a.logical_shape(), b.logical_shape(), name);
     Tensor out = alloc_like(a, os, DataType::BFLOAT16, a.layout(), name);
     int64_t sa[4], sb[4];
@@ -568,7 +597,11 @@ inline Tensor binary(int op, const Tensor& a, const Tensor& b, const char* name)
     check(b200_binary(ctx_of(a, name), op, a.device_ptr(), sa, b.device_ptr(), sb, out.device_ptr(), nullptr), name);
     return out;
 }
+inline Tensor unary1(int op, const Tensor& x, float scalar, const char* name);
 inline Tensor unary(int op, const Tensor& x, float scalar, const char* name) {
+    return per_shard(x, [&](const Tensor& xs, size_t) { return unary1(op, xs, scalar, name); });
+}
+inline Tensor unary1(int op, const Tensor& x, float scalar, const char* name) {
     Tensor out = alloc_like(x, x.logical_shape(), DataType::BFLOAT16, x.layout(), name);
     check(b200_unary(ctx_of(x, name), op, x.device_ptr(), out.device_ptr(), static_cast<int64_t>(x.volume()), scalar, nullptr),
           name);
@@ -680,9 +713,15 @@ inline Tensor reduce(int op, const Tensor& x, std::optional<int> dim, bool keepd
 }
 
 inline Tensor filled(const Shape& shape, float value, DataType dt, Layout layout, MeshDevice& dev) {
-    Tensor out = alloc_on(dev, shape, dt, layout);
-    check(b200_fill(dev.ctx(0), out.device_ptr(), static_cast<int64_t>(shape.volume()), abi_dtype(dt), value, nullptr), "fill");
-    return out;
+    std::vector<Tensor> parts;  // on a multi-device mesh the tensor is replicated on every device
+    for (size_t i = 0; i < dev.num_devices(); ++i) {
+        auto st = device_storage(&dev, shape.volume() * dtype_size(dt), i);
+        Tensor out(st, shape, dt, layout);
+        check(b200_fill(dev.ctx(i), out.device_ptr(), static_cast<int64_t>(shape.volume()), abi_dtype(dt), value, nullptr),
+              "fill");
+        parts.push_back(out);
+    }
+    return Tensor::from_shards(parts);
 }
 
 }  // namespace detail
@@ -695,7 +734,10 @@ inline Tensor matmul(const Tensor& a, const Tensor& b, bool transpose_a = false,
                      const std::optional<std::string>& activation = std::nullopt,
                      const std::optional<DeviceComputeKernelConfig>& compute_kernel_config = std::nullopt,
                      const std::optional<CoreGrid>& = std::nullopt) {
-    return detail::matmul_impl(a, b, transpose_a, transpose_b, nullptr, activation, compute_kernel_config, "ttnn::matmul");
+    return detail::per_shard(a, [&](const Tensor& as, size_t i) {
+        return detail::matmul_impl(as, b.shard(i), transpose_a, transpose_b, nullptr, activation, compute_kernel_config,
+                                   "ttnn::matmul");
+    });
 }
 
 inline Tensor linear(const Tensor& a, const Tensor& w, const std::optional<Tensor>& bias = std::nullopt,
@@ -882,6 +924,95 @@ inline std::shared_ptr<MeshDevice> open_mesh_device(int device_id, size_t l1_sma
 inline void close_device(MeshDevice& dev) { dev.close(); }
 inline void close_mesh_device(const std::shared_ptr<MeshDevice>& dev) {
     if (dev) dev->close();
+}
+
+// ---- mesh tensors: mappers, distribute_tensor, all_gather (bench/metal/matmul_tensor_parallel.cpp:70-92, :153-186) ---
+namespace distributed {
+using tt::tt_metal::distributed::MeshShape;
+
+struct TensorToMesh {
+    MeshDevice* mesh = nullptr;
+    int shard_dim = -1;  // -1: replicate
+};
+
+inline std::unique_ptr<TensorToMesh> replicate_tensor_to_mesh_mapper(MeshDevice& mesh) {
+    return std::make_unique<TensorToMesh>(TensorToMesh{&mesh, -1});
+}
+inline std::unique_ptr<TensorToMesh> shard_tensor_to_mesh_mapper(MeshDevice& mesh, int dim) {
+    return std::make_unique<TensorToMesh>(TensorToMesh{&mesh, dim});
+}
+
+// Host tensor -> one shard (or replica) per device of the mesh. Slicing happens on the host, as in the reference.
+inline Tensor distribute_tensor(const Tensor& host, const TensorToMesh& mapper,
+                                std::optional<std::reference_wrapper<MeshDevice>> mesh = std::nullopt) {
+    MeshDevice& dev = mesh ? mesh->get() : *mapper.mesh;
+    const size_t n = dev.num_devices();
+    const Tensor h = host.on_device() ? host.cpu() : host;
+    const Shape& s = h.logical_shape();
+    const size_t es = detail::dtype_size(h.dtype());
+    std::vector<Tensor> parts;
+    if (mapper.shard_dim < 0) {
+        for (size_t i = 0; i < n; ++i) parts.push_back(h.to_device(&dev, MemoryConfig{}, i));
+        return Tensor::from_shards(parts);
+    }
+    int dim = mapper.shard_dim < 0 ? mapper.shard_dim + static_cast<int>(s.rank()) : mapper.shard_dim;
+    if (dim >= static_cast<int>(s.rank()) || s[dim] % n != 0)
+        throw std::invalid_argument("shard_tensor_to_mesh_mapper: dimension is not divisible by the mesh size");
+    uint64_t outer = 1, inner = 1;
+    for (int i = 0; i < dim; ++i) outer *= s[i];
+    for (int i = dim + 1; i < static_cast<int>(s.rank()); ++i) inner *= s[i];
+    const uint64_t piece = s[dim] / n;
+    std::vector<uint32_t> sd(s.view());
+    sd[static_cast<size_t>(dim)] = static_cast<uint32_t>(piece);
+    const uint8_t* src = h.storage()->host.data();
+    for (size_t i = 0; i < n; ++i) {
+        auto st = std::make_shared<tt::tt_metal::b200_detail::Storage>();
+        st->bytes = outer * piece * inner * es;
+        st->host.resize(st->bytes);
+        for (uint64_t o = 0; o < outer; ++o)
+            std::memcpy(st->host.data() + o * piece * inner * es, src + (o * s[dim] + i * piece) * inner * es, piece * inner * es);
+        parts.push_back(Tensor(st, Shape(sd), h.dtype(), h.layout()).to_device(&dev, MemoryConfig{}, i));
+    }
+    return Tensor::from_shards(parts);
+}
+
+inline std::shared_ptr<MeshDevice> open_mesh_device(const MeshShape& shape, size_t l1_small = DEFAULT_L1_SMALL_SIZE,
+                                                    size_t trace_region = DEFAULT_TRACE_REGION_SIZE, int num_cqs = 1,
+                                                    const tt::tt_metal::DispatchCoreConfig& cfg = {}) {
+    return MeshDevice::create(tt::tt_metal::distributed::MeshDeviceConfig(shape), l1_small, trace_region, num_cqs, cfg);
+}
+inline void close_mesh_device(const std::shared_ptr<MeshDevice>& dev) {
+    if (dev) dev->close();
+}
+}  // namespace distributed
+
+// Every device ends with the concatenation of all devices' shards along `dim` (copy engines over NVLink, ordered after
+// the producing ops). The fused form — matmul whose epilogue stores into every peer — is b200_gemm_allgather.
+inline Tensor all_gather(const Tensor& t, int dim, int /*num_links*/ = 1) {
+    const size_t n = t.num_shards();
+    if (n == 1) return t;
+    const Shape& s = t.logical_shape();
+    if (dim < 0) dim += static_cast<int>(s.rank());
+    uint64_t outer = 1, inner = 1;
+    for (int i = 0; i < dim; ++i) outer *= s[i];
+    for (int i = dim; i < static_cast<int>(s.rank()); ++i) inner *= s[i];  // contiguous run of one shard per outer index
+    const size_t es = detail::dtype_size(t.dtype());
+    std::vector<uint32_t> od(s.view());
+    od[static_cast<size_t>(dim)] *= static_cast<uint32_t>(n);
+    MeshDevice* dev = t.device();
+    std::vector<Tensor> parts;
+    for (size_t d = 0; d < n; ++d) {
+        auto st = detail::device_storage(dev, Shape(od).volume() * es, d);
+        Tensor out(st, Shape(od), t.dtype(), t.layout());
+        for (size_t src = 0; src < n; ++src) {
+            const Tensor sh = t.shard(src);
+            detail::check(b200_peer_copy_2d(dev->ctx(d), static_cast<uint8_t*>(out.device_ptr()) + src * inner * es,
+                                            n * inner * es, dev->ctx(src), sh.device_ptr(), inner * es, inner * es, outer),
+                          "ttnn::all_gather");
+        }
+        parts.push_back(out);
+    }
+    return Tensor::from_shards(parts);
 }
 
 // ---- traces (traced/trace.hpp:57-78) ----------------------------------------------------------------------------------

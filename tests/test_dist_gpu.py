@@ -86,3 +86,28 @@ def test_two_gpu_torchrun_bench_line():
                         "--steps", "3", "--warmup", "3", "--quick"], capture_output=True, text=True, timeout=600, env=env)
     assert r.returncode == 0, r.stderr[-2000:]
     assert '"n_gpus": 2' in r.stdout
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs two GPUs")
+def test_multi_gpu_parity_all_gather_and_reduce_scatter():
+    """torchrun over all visible GPUs (2, 4 or 8): fused all-gather and fused reduce-scatter against the oracle."""
+    n = min(8, torch.cuda.device_count())
+    n = 8 if n >= 8 else 4 if n >= 4 else 2
+    env = dict(os.environ, NCCL_NVLS_ENABLE="0")
+    r = subprocess.run([sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node", str(n),
+                        "--master-addr", "127.0.0.1", "--master-port", "29544", str(REPO / "tests" / "dist_rank_worker.py")],
+                       capture_output=True, text=True, timeout=600, env=env)
+    assert r.returncode == 0 and f"DIST_PARITY_OK {n}" in r.stdout, (r.stdout[-1500:], r.stderr[-3000:])
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs two GPUs")
+def test_reference_tensor_parallel_program_on_a_two_gpu_mesh():
+    """bench/metal/matmul_tensor_parallel.cpp, compiled unchanged: 1x2 mesh in one process, A replicated, B sharded
+    on dim 1, ttnn::matmul then ttnn::all_gather(c, 1)."""
+    exe = REPO / "build" / "ref_mains" / "matmul_tensor_parallel"
+    if not exe.exists():
+        pytest.skip("reference mains not built")
+    r = subprocess.run([str(exe)], capture_output=True, text=True, timeout=600)
+    assert r.returncode == 0, r.stderr[-2000:]
+    rows = [l for l in r.stdout.splitlines() if l and l[0].isdigit()]
+    assert len(rows) >= 5 and "Error" not in r.stderr

@@ -77,6 +77,9 @@ SIGNATURES = {
     "b200_ipc_get_handle": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p]),
     "b200_ipc_open_handle": (C.c_int, [C.c_void_p, C.c_void_p, C.POINTER(C.c_void_p)]),
     "b200_ipc_close_handle": (C.c_int, [C.c_void_p, C.c_void_p]),
+    "b200_enable_peer_access": (C.c_int, [C.c_void_p, C.c_void_p]),
+    "b200_peer_copy_2d": (C.c_int, [C.c_void_p, C.c_void_p, C.c_size_t, C.c_void_p, C.c_void_p, C.c_size_t, C.c_size_t,
+                                    C.c_size_t]),
     "b200_gemm_allgather": (C.c_int, [C.c_void_p, C.POINTER(GemmDesc), C.POINTER(C.c_void_p), C.c_int, C.c_int, C.c_void_p]),
     "b200_gemm_reduce_scatter_partials": (C.c_int, [C.c_void_p, C.POINTER(GemmDesc), C.POINTER(C.c_void_p), C.c_int, C.c_int,
                                                     C.c_void_p]),

@@ -48,6 +48,48 @@ int b200_ipc_close_handle(b200_ctx* ctx, void* dptr) {
     return B200_OK;
 }
 
+// ---- several GPUs driven by ONE process (the reference's MeshDevice model) ------------------------------------------
+int b200_enable_peer_access(b200_ctx* a, b200_ctx* b) {
+    B200_REQUIRE(a && b, "b200_enable_peer_access: NULL context");
+    if (a->device == b->device) return B200_OK;
+    for (int dir = 0; dir < 2; ++dir) {
+        b200_ctx* from = dir ? b : a;
+        b200_ctx* to = dir ? a : b;
+        int can = 0;
+        B200_CUDA_TRY(cudaDeviceCanAccessPeer(&can, from->device, to->device));
+        if (!can) return fail(B200_ERR_UNSUPPORTED, "GPU %d cannot access GPU %d directly", from->device, to->device);
+        DeviceScope scope(from->device);
+        cudaError_t e = cudaDeviceEnablePeerAccess(to->device, 0);
+        if (e == cudaErrorPeerAccessAlreadyEnabled) {
+            cudaGetLastError();
+        } else if (e != cudaSuccess) {
+            return fail(B200_ERR_CUDA, "cudaDeviceEnablePeerAccess(%d -> %d) failed: %s", from->device, to->device,
+                        cudaGetErrorString(e));
+        }
+    }
+    return B200_OK;
+}
+
+int b200_peer_copy_2d(b200_ctx* dst_ctx, void* dst, size_t dst_pitch, b200_ctx* src_ctx, const void* src, size_t src_pitch,
+                      size_t width_bytes, size_t rows) {
+    B200_REQUIRE(dst_ctx && src_ctx, "b200_peer_copy_2d: NULL context");
+    if (width_bytes == 0 || rows == 0) return B200_OK;
+    B200_REQUIRE(dst && src, "b200_peer_copy_2d: NULL buffer");
+    B200_REQUIRE(dst_pitch >= width_bytes && src_pitch >= width_bytes, "b200_peer_copy_2d: pitch smaller than the row width");
+    // order after the producer's queued work, then copy on the consumer's stream (copy engine over NVLink)
+    cudaEvent_t ev;
+    {
+        DeviceScope scope(src_ctx->device);
+        B200_CUDA_TRY(cudaEventCreateWithFlags(&ev, cudaEventDisableTiming));
+        B200_CUDA_TRY(cudaEventRecord(ev, src_ctx->stream));
+    }
+    DeviceScope scope(dst_ctx->device);
+    B200_CUDA_TRY(cudaStreamWaitEvent(dst_ctx->stream, ev, 0));
+    B200_CUDA_TRY(cudaMemcpy2DAsync(dst, dst_pitch, src, src_pitch, width_bytes, rows, cudaMemcpyDefault, dst_ctx->stream));
+    B200_CUDA_TRY(cudaEventDestroy(ev));
+    return B200_OK;
+}
+
 static int check_dist_desc(const char* who, const b200_gemm_desc* d, int n_ranks, int my_rank) {
     B200_REQUIRE(d != nullptr, "%s: desc is NULL", who);
     B200_REQUIRE(n_ranks >= 1 && n_ranks <= 8, "%s: n_ranks must be in [1, 8] (got %d)", who, n_ranks);
