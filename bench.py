@@ -182,6 +182,56 @@ def workload_config(n: int) -> dict:
             "l2_policy": "inputs larger than the 126 MiB L2; no flush between steps"}
 
 
+def gpt2_train_bench(steps: int = 10, warmup: int = 3) -> dict:
+    """GPT-2-small-shaped training step (12 layers, d_model 768, 12 heads, d_ff 3072, seq 1024, batch 8, vocab 50257,
+    random N(0, 0.02) weights, uniform random token ids, Adam lr 3e-4 betas (0.9, 0.95)): forward, cross-entropy,
+    backward and the Adam update, recorded once as a trace (CUDA graph) and replayed, as the reference's traced
+    executor does (bench/autograd/bench_gpt2_full.cpp). Every kernel comes from the C ABI; the host side is
+    tt-perf_b200/nn.py. Returns tokens/s and ms/step."""
+    import numpy as np
+    from __graft_entry__ import load_package
+    pkg = load_package()
+    ctx = pkg.Context(0)
+    DT = pkg.DeviceTensor
+    L, D, H, S, V, B = 12, 768, 12, 1024, 50257, 8
+    model = pkg.nn.GPT2(ctx, layers=L, d_model=D, heads=H, seq=S, vocab=V)
+    model.init_random(42)
+    rng = np.random.default_rng(42)
+    ids = rng.integers(0, V, (B, S)).astype(np.uint32)
+    targets = np.roll(ids, -1, axis=1)
+    idd = DT.from_numpy(ctx, ids, pkg.U32)
+    tgd = DT.from_numpy(ctx, targets.ravel(), pkg.U32)
+    pos = DT.from_numpy(ctx, np.arange(S, dtype=np.uint32), pkg.U32)
+
+    def step():
+        loss, grads = model.forward_backward(idd, tgd, pos)
+        model.adam_step(grads)
+        return loss
+
+    losses = []
+    for _ in range(max(2, warmup)):          # eager steps: allocate the pool and scratch, check the loss moves
+        losses.append(float(step().numpy()[0]))
+    tid = ctx.trace_begin()
+    loss = step()
+    ctx.trace_end(tid)
+    ctx.trace_execute(tid)
+    ctx.synchronize()
+    t0 = time.perf_counter()
+    for _ in range(steps):
+        ctx.trace_execute(tid)
+    ctx.synchronize()
+    dt = (time.perf_counter() - t0) / steps
+    final = float(loss.numpy()[0])
+    ctx.trace_release(tid)
+    flops = 3 * (12 * 24 * B * S * D * D + 2 * B * S * D * V) + 12 * 12 * B * H * 64 * (S * (S + 1) // 2)
+    out = {"metric": "GPT-2-small train tokens/s", "tokens_per_s": B * S / dt, "ms_per_step": dt * 1e3,
+           "model_tflops_per_s": flops / dt / 1e12, "params": model.num_params(), "batch": B, "seq": S,
+           "first_losses": losses, "loss_after_replays": final, "executor": "trace replay (CUDA graph)",
+           "data": "synthetic: uniform token ids, targets = ids shifted by one"}
+    ctx.close()
+    return out
+
+
 def run_b200_single(args) -> None:
     import torch
     from __graft_entry__ import load_package
@@ -276,6 +326,8 @@ def run_b200_single(args) -> None:
     if args.quick:
         line["quick"] = True
         line["e2e"] = None
+    else:
+        line["gpt2_small_train"] = gpt2_train_bench()
     print(json.dumps(line), flush=True)
     ctx.close()
 
@@ -416,12 +468,18 @@ def main() -> None:
     ap.add_argument("--steps", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
+    ap.add_argument("--workload", default="gemm", choices=["gemm", "gpt2"],
+                    help="gemm: the headline matmul line (default). gpt2: only the GPT-2-small training step "
+                         "(its own JSON object; used for profiling that workload)")
     ap.add_argument("--quick", action="store_true",
                     help="timed region only: skip the CPU baseline, the host-buffer leg and the clock soak "
                          "(for runs under a profiler; its line is not a bench result)")
     args = ap.parse_args()
     if args.impl == "reference":
         run_reference_arm(args)
+        return
+    if args.workload == "gpt2":
+        print(json.dumps(gpt2_train_bench(steps=args.steps, warmup=args.warmup)), flush=True)
         return
     if args.gpus == 1 and int(os.environ.get("WORLD_SIZE", "1")) == 1:
         run_b200_single(args)

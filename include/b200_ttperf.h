@@ -70,6 +70,11 @@ int b200_ctx_sm_count(const b200_ctx* ctx, int* out_sm_count);
 /* Blocks until all work queued on `stream` has finished, then reports a kernel wait that timed out
  * since the last call as B200_ERR_DEVICE_TIMEOUT (and clears it). */
 int b200_synchronize(b200_ctx* ctx, void* stream);
+/* Device-side timing as the reference's benchmarks do around Finish() (bench/metal/matmul_sweep.cpp:44-79), but with
+ * CUDA events on the stream: start records an event, stop records a second one, waits for it and returns the elapsed
+ * milliseconds between the two (and releases the timer). */
+int b200_timer_start(b200_ctx* ctx, void* stream, void** out_timer);
+int b200_timer_stop(b200_ctx* ctx, void* stream, void* timer, float* out_ms);
 const char* b200_last_error(void);
 int b200_abi_version(void);
 

@@ -134,3 +134,50 @@ def test_gpt2_block_larger_against_oracle(pkg, ctx):
     assert mo.rel_frobenius(d_x.numpy(), ref_dx) <= 1e-2
     for k in ("wq", "wk", "wv", "wo", "w1", "w2", "b1", "b2", "bo", "bv", "bq", "ln1_g", "ln2_g", "ln1_b", "ln2_b"):
         assert mo.rel_frobenius(grads[k].numpy(), ref_g[k]) <= 2e-2, (k, mo.rel_frobenius(grads[k].numpy(), ref_g[k]))
+
+
+def test_gpt2_model_loss_and_gradients_small_config(pkg, ctx):
+    """Embeddings + 2 blocks + final LayerNorm + untied head + cross-entropy with an unaligned vocabulary (257 -> padded
+    to 264 rows) against the oracle; then one Adam step (lr 3e-4, betas 0.9 / 0.95) on every parameter."""
+    DT = pkg.DeviceTensor
+    rng = np.random.default_rng(5)
+    L, D, H, S, V, B = 2, 128, 2, 64, 257, 2
+    model = pkg.nn.GPT2(ctx, layers=L, d_model=D, heads=H, seq=S, vocab=V)
+
+    def w(*shape, std=0.05):
+        return mo.bf16_round(rng.standard_normal(shape).astype(np.float32) * std)
+
+    blocks = []
+    for _ in range(L):
+        blk = {}
+        for k, shape in model.block_shapes().items():
+            blk[k] = (mo.bf16_round(1 + 0.1 * rng.standard_normal(shape).astype(np.float32)) if k.endswith("_g")
+                      else w(*shape, std=0.02) if len(shape) == 1 else w(*shape))
+        blocks.append(blk)
+    host = {"tok_emb": w(V, D, std=0.3), "pos_emb": w(S, D, std=0.3), "lnf_g": np.ones(D, np.float32),
+            "lnf_b": np.zeros(D, np.float32), "head": w(V, D), "blocks": blocks}
+    model.load(host)
+    ids = rng.integers(0, V, (B, S)).astype(np.uint32)
+    targets = rng.integers(0, V, (B, S)).astype(np.uint32)
+    loss_t, grads = model.forward_backward(DT.from_numpy(ctx, ids, pkg.U32), DT.from_numpy(ctx, targets.ravel(), pkg.U32),
+                                           DT.from_numpy(ctx, np.arange(S, dtype=np.uint32), pkg.U32))
+    ref_loss, ref = mo.gpt2_forward_backward(ids, targets, host, H)
+    loss = float(loss_t.numpy()[0])
+    assert abs(loss - ref_loss) <= 1e-3 * abs(ref_loss), (loss, ref_loss)
+    assert mo.rel_frobenius(grads["head"].numpy()[:V], ref["head"]) <= 2e-2
+    assert np.all(grads["head"].numpy()[V:] == 0)
+    assert mo.rel_frobenius(grads["tok_emb"].numpy(), ref["tok_emb"]) <= 3e-2
+    assert mo.rel_frobenius(grads["pos_emb"].numpy(), ref["pos_emb"]) <= 3e-2
+    for i in range(L):
+        for k in ("wq", "wv", "wo", "w1", "w2", "ln1_g", "ln2_g", "b1"):
+            err = mo.rel_frobenius(grads["blocks"][i][k].numpy(), ref["blocks"][i][k])
+            assert err <= 4e-2, (i, k, err)
+    before = model.params["blocks"][0]["w1"].numpy().copy()
+    model.adam_step(grads)
+    after = model.params["blocks"][0]["w1"].numpy()
+    g = mo.bf16_round(grads["blocks"][0]["w1"].numpy())
+    expect, _, _ = mo.adam_update(before, g, 0, 0, 1, lr=3e-4, beta1=0.9, beta2=0.95)
+    assert mo.rel_frobenius(after, expect) <= 1e-2
+    assert model.num_params() == sum(int(np.prod(v.shape)) for v in (host["tok_emb"], host["pos_emb"], host["lnf_g"],
+                                                                     host["lnf_b"], host["head"])) + sum(
+        int(np.prod(v.shape)) for blk in blocks for v in blk.values())

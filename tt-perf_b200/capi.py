@@ -56,6 +56,8 @@ SIGNATURES = {
     "b200_ctx_device": (C.c_int, [C.c_void_p, C.POINTER(C.c_int)]),
     "b200_ctx_sm_count": (C.c_int, [C.c_void_p, C.POINTER(C.c_int)]),
     "b200_synchronize": (C.c_int, [C.c_void_p, C.c_void_p]),
+    "b200_timer_start": (C.c_int, [C.c_void_p, C.c_void_p, C.POINTER(C.c_void_p)]),
+    "b200_timer_stop": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.POINTER(C.c_float)]),
     "b200_last_error": (C.c_char_p, []),
     "b200_abi_version": (C.c_int, []),
     "b200_malloc": (C.c_int, [C.c_void_p, C.c_size_t, C.POINTER(C.c_void_p)]),
@@ -190,6 +192,16 @@ class Context:
 
     def synchronize(self, stream=None) -> None:
         check(lib().b200_synchronize(self._h, C.c_void_p(ptr(stream))))
+
+    def timer_start(self, stream=None):
+        t = C.c_void_p()
+        check(lib().b200_timer_start(self._h, C.c_void_p(ptr(stream)), C.byref(t)))
+        return t
+
+    def timer_stop(self, timer, stream=None) -> float:
+        ms = C.c_float()
+        check(lib().b200_timer_stop(self._h, C.c_void_p(ptr(stream)), timer, C.byref(ms)))
+        return ms.value
 
     # ---- memory -------------------------------------------------------------------------------------
     def malloc(self, nbytes: int) -> int:

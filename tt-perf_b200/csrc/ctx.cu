@@ -150,6 +150,36 @@ int b200_synchronize(b200_ctx* ctx, void* stream) {
     return B200_OK;
 }
 
+// Device-side stopwatch: two events on the stream, elapsed time read after the second has completed.
+int b200_timer_start(b200_ctx* ctx, void* stream, void** out_timer) {
+    B200_REQUIRE(ctx && out_timer, "b200_timer_start: NULL argument");
+    DeviceScope scope(ctx->device);
+    cudaEvent_t* ev = new cudaEvent_t[2];
+    cudaError_t e = cudaEventCreate(&ev[0]);
+    if (e == cudaSuccess) e = cudaEventCreate(&ev[1]);
+    if (e == cudaSuccess) e = cudaEventRecord(ev[0], ctx->pick(stream));
+    if (e != cudaSuccess) {
+        delete[] ev;
+        return fail(B200_ERR_CUDA, "b200_timer_start: %s", cudaGetErrorString(e));
+    }
+    *out_timer = ev;
+    return B200_OK;
+}
+
+int b200_timer_stop(b200_ctx* ctx, void* stream, void* timer, float* out_ms) {
+    B200_REQUIRE(ctx && timer && out_ms, "b200_timer_stop: NULL argument");
+    DeviceScope scope(ctx->device);
+    cudaEvent_t* ev = static_cast<cudaEvent_t*>(timer);
+    cudaError_t e = cudaEventRecord(ev[1], ctx->pick(stream));
+    if (e == cudaSuccess) e = cudaEventSynchronize(ev[1]);
+    if (e == cudaSuccess) e = cudaEventElapsedTime(out_ms, ev[0], ev[1]);
+    cudaEventDestroy(ev[0]);
+    cudaEventDestroy(ev[1]);
+    delete[] ev;
+    if (e != cudaSuccess) return fail(B200_ERR_CUDA, "b200_timer_stop: %s", cudaGetErrorString(e));
+    return B200_OK;
+}
+
 int b200_malloc(b200_ctx* ctx, size_t bytes, void** out_dptr) {
     B200_REQUIRE(ctx && out_dptr, "b200_malloc: NULL argument");
     *out_dptr = nullptr;

@@ -102,6 +102,20 @@ struct BinaryParams {
     int vec;              // last output dim % 8 == 0, all pointers 16-byte aligned, last strides in {0,1}
 };
 
+// Same-shape operands, 16-byte aligned, n % 8 == 0: flat vector loop without index arithmetic.
+__global__ void __launch_bounds__(kThreads) binary_flat_kernel(const __nv_bfloat16* a, const __nv_bfloat16* b,
+                                                                __nv_bfloat16* out, long long nvec, int op) {
+    const long long stride = static_cast<long long>(gridDim.x) * blockDim.x;
+    for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < nvec; i += stride) {
+        float fa[8], fb[8];
+        unpack8(reinterpret_cast<const uint4*>(a)[i], fa);
+        unpack8(reinterpret_cast<const uint4*>(b)[i], fb);
+#pragma unroll
+        for (int k = 0; k < 8; ++k) fa[k] = binary_apply(op, fa[k], fb[k]);
+        reinterpret_cast<uint4*>(out)[i] = pack8(fa);
+    }
+}
+
 __global__ void __launch_bounds__(kThreads) binary_kernel(const BinaryParams p) {
     const long long stride = static_cast<long long>(gridDim.x) * blockDim.x;
     if (p.vec) {
@@ -227,38 +241,54 @@ __global__ void __launch_bounds__(kThreads) reduce_rows_split_kernel(const __nv_
     }
 }
 
-// inner > 1: CTA = 32 columns x 8 row lanes; partial results of the row slabs combined in fp32.
+// inner > 1: CTA = 32 column groups x 8 row lanes; a column group is 8 adjacent columns read as one 16-byte vector
+// (one column when rows are not 16-byte aligned). Partial results of the row slabs are combined in fp32.
+template <int VEC>
 __global__ void __launch_bounds__(kThreads) reduce_cols_kernel(const __nv_bfloat16* x, float* acc_out, long long R,
                                                                 long long inner, int op, long long rows_per_cta) {
-    __shared__ float sh[8][33];
+    __shared__ float sh[8][32][VEC + 1];
     const long long o = blockIdx.z;
-    const long long c = blockIdx.x * 32ll + (threadIdx.x & 31);
+    const long long c = (blockIdx.x * 32ll + (threadIdx.x & 31)) * VEC;
     const int sub = threadIdx.x >> 5;
     const long long r0 = blockIdx.y * rows_per_cta, r1 = min(R, r0 + rows_per_cta);
-    float acc = (op == R_MAX) ? -FLT_MAX : 0.0f;
+    float acc[VEC];
+#pragma unroll
+    for (int k = 0; k < VEC; ++k) acc[k] = (op == R_MAX) ? -FLT_MAX : 0.0f;
     if (c < inner) {
         const __nv_bfloat16* base = x + o * R * inner + c;
         for (long long r = r0 + sub; r < r1; r += 8) {
-            const float f = __bfloat162float(base[r * inner]);
-            acc = (op == R_MAX) ? fmaxf(acc, f) : acc + f;
+            if (VEC == 8) {
+                float f[8];
+                unpack8(*reinterpret_cast<const uint4*>(base + r * inner), f);
+#pragma unroll
+                for (int k = 0; k < 8; ++k) acc[k] = (op == R_MAX) ? fmaxf(acc[k], f[k]) : acc[k] + f[k];
+            } else {
+                const float f = __bfloat162float(base[r * inner]);
+                acc[0] = (op == R_MAX) ? fmaxf(acc[0], f) : acc[0] + f;
+            }
         }
     }
-    sh[sub][threadIdx.x & 31] = acc;
+#pragma unroll
+    for (int k = 0; k < VEC; ++k) sh[sub][threadIdx.x & 31][k] = acc[k];
     __syncthreads();
     if (sub == 0 && c < inner) {
-        for (int k = 1; k < 8; ++k) {
-            const float other = sh[k][threadIdx.x];
-            acc = (op == R_MAX) ? fmaxf(acc, other) : acc + other;
-        }
-        float* dst = acc_out + o * inner + c;
-        if (op == R_MAX) {
-            // float max through integer atomics (valid for any mix of signs)
-            if (acc >= 0.0f)
-                atomicMax(reinterpret_cast<int*>(dst), __float_as_int(acc));
-            else
-                atomicMin(reinterpret_cast<unsigned int*>(dst), __float_as_uint(acc));
-        } else {
-            atomicAdd(dst, acc);
+#pragma unroll
+        for (int k = 0; k < VEC; ++k) {
+            float a = acc[k];
+            for (int j = 1; j < 8; ++j) {
+                const float other = sh[j][threadIdx.x][k];
+                a = (op == R_MAX) ? fmaxf(a, other) : a + other;
+            }
+            float* dst = acc_out + o * inner + c + k;
+            if (op == R_MAX) {
+                // float max through integer atomics (valid for any mix of signs)
+                if (a >= 0.0f)
+                    atomicMax(reinterpret_cast<int*>(dst), __float_as_int(a));
+                else
+                    atomicMin(reinterpret_cast<unsigned int*>(dst), __float_as_uint(a));
+            } else {
+                atomicAdd(dst, a);
+            }
         }
     }
 }
@@ -437,6 +467,13 @@ int b200_binary(b200_ctx* ctx, int op, const void* a, const int64_t* a_shape, co
     };
     p.vec = (p.od[3] % 8 == 0) && al16(a) && al16(b) && al16(out) && rows_aligned(p.as, ad) && rows_aligned(p.bs, bd);
     DeviceScope scope(ctx->device);
+    bool same = true;
+    for (int i = 0; i < 4; ++i) same = same && ad[i] == bd[i];
+    if (same && (p.n % 8 == 0) && al16(a) && al16(b) && al16(out)) {
+        binary_flat_kernel<<<grid_for(ctx, p.n / 8), kThreads, 0, ctx->pick(stream)>>>(p.a, p.b, p.out, p.n / 8, op);
+        B200_CUDA_TRY(cudaGetLastError());
+        return B200_OK;
+    }
     binary_kernel<<<grid_for(ctx, p.vec ? p.n / 8 : p.n), kThreads, 0, ctx->pick(stream)>>>(p);
     B200_CUDA_TRY(cudaGetLastError());
     return B200_OK;
@@ -482,13 +519,17 @@ int b200_reduce(b200_ctx* ctx, int op, const void* x, int64_t outer, int64_t R, 
     if (rc != B200_OK) return rc;
     float* acc = static_cast<float*>(ctx->d_scratch);
     fill_f32_kernel<<<grid_for(ctx, outs), kThreads, 0, s>>>(acc, outs, op == R_MAX ? -FLT_MAX : 0.0f);
-    const long long col_blocks = (inner + 31) / 32;
+    const bool vec8 = al16(x) && (inner % 8 == 0);
+    const long long col_blocks = vec8 ? (inner / 8 + 31) / 32 : (inner + 31) / 32;
     long long row_blocks = std::max<long long>(1, std::min<long long>((R + 63) / 64, (ctx->sm_count * 4ll) / std::max<long long>(1, col_blocks * outer)));
     const long long rows_per = (R + row_blocks - 1) / row_blocks;
     row_blocks = (R + rows_per - 1) / rows_per;
     B200_REQUIRE(outer <= 65535 && row_blocks <= 65535, "b200_reduce: outer dimension too large for a column reduction");
     dim3 grid(static_cast<unsigned>(col_blocks), static_cast<unsigned>(row_blocks), static_cast<unsigned>(outer));
-    reduce_cols_kernel<<<grid, kThreads, 0, s>>>(static_cast<const __nv_bfloat16*>(x), acc, R, inner, op, rows_per);
+    if (vec8)
+        reduce_cols_kernel<8><<<grid, kThreads, 0, s>>>(static_cast<const __nv_bfloat16*>(x), acc, R, inner, op, rows_per);
+    else
+        reduce_cols_kernel<1><<<grid, kThreads, 0, s>>>(static_cast<const __nv_bfloat16*>(x), acc, R, inner, op, rows_per);
     cast_f32_to_bf16_kernel<<<grid_for(ctx, outs), kThreads, 0, s>>>(acc, static_cast<__nv_bfloat16*>(y), outs,
                                                                      op == R_MEAN ? 1.0f / static_cast<float>(R) : 1.0f);
     B200_CUDA_TRY(cudaGetLastError());

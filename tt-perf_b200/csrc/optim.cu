@@ -38,110 +38,93 @@ __device__ __forceinline__ void unpack8(const uint4& u, float (&f)[8]) {
     }
 }
 
-__device__ __forceinline__ int find_tensor(const TensorTable& t, long long chunk) {
-    int lo = 0, hi = t.count - 1;
-    while (lo < hi) {
-        const int mid = (lo + hi + 1) >> 1;
-        if (t.start[mid] <= chunk) lo = mid; else hi = mid - 1;
-    }
-    return lo;
+__device__ __forceinline__ float adam_update(float p, float g, float& m, float& v, const AdamScalars& s) {
+    m = s.beta1 * m + (1.0f - s.beta1) * g;
+    v = s.beta2 * v + (1.0f - s.beta2) * g * g;
+    return p - __fdividef(s.lr * (m * s.inv_bias1), sqrtf(v * s.inv_bias2) + s.eps);
 }
 
-// p_f32 / g_f32: storage type of parameters and gradients (0 = bf16, 1 = fp32).
-template <bool ADAM>
-__global__ void __launch_bounds__(kThreads) optim_kernel(const TensorTable t, const AdamScalars s, int p_f32, int g_f32) {
-    const long long total = t.start[t.count];
+template <bool F32>
+__device__ __forceinline__ float load_elem(const void* base, long long i) {
+    return F32 ? static_cast<const float*>(base)[i] : __bfloat162float(static_cast<const __nv_bfloat16*>(base)[i]);
+}
+template <bool F32>
+__device__ __forceinline__ void load8(const void* base, long long i, float (&f)[8]) {
+    if (F32) {
+        const float4 a = *reinterpret_cast<const float4*>(static_cast<const float*>(base) + i);
+        const float4 b = *reinterpret_cast<const float4*>(static_cast<const float*>(base) + i + 4);
+        f[0] = a.x; f[1] = a.y; f[2] = a.z; f[3] = a.w; f[4] = b.x; f[5] = b.y; f[6] = b.z; f[7] = b.w;
+    } else {
+        unpack8(*reinterpret_cast<const uint4*>(static_cast<const __nv_bfloat16*>(base) + i), f);
+    }
+}
+template <bool F32>
+__device__ __forceinline__ void store8(void* base, long long i, const float (&f)[8]) {
+    if (F32) {
+        float* p = static_cast<float*>(base) + i;
+        *reinterpret_cast<float4*>(p) = make_float4(f[0], f[1], f[2], f[3]);
+        *reinterpret_cast<float4*>(p + 4) = make_float4(f[4], f[5], f[6], f[7]);
+    } else {
+        *reinterpret_cast<uint4*>(static_cast<__nv_bfloat16*>(base) + i) =
+            make_uint4(pack_bf16x2(f[0], f[1]), pack_bf16x2(f[2], f[3]), pack_bf16x2(f[4], f[5]), pack_bf16x2(f[6], f[7]));
+    }
+}
+
+// blockIdx.y selects the tensor (uniform per CTA); blockIdx.x strides over its 8-element chunks. CTAs beyond a small
+// tensor's last chunk fall straight through. Full, 16-byte aligned chunks use vector accesses with everything in
+// registers; the ragged tail (and unaligned tensors) go element by element.
+template <bool ADAM, bool P_F32, bool G_F32>
+__global__ void __launch_bounds__(kThreads) optim_kernel(const TensorTable t, const AdamScalars s) {
+    const int ti = blockIdx.y;
+    const long long n = t.n[ti];
+    void* const pp = t.p[ti];
+    const void* const gp = t.g[ti];
+    float* const mp = t.m[ti];
+    float* const vp = t.v[ti];
+    void* const sp = t.shadow[ti];
+    const uintptr_t bits = reinterpret_cast<uintptr_t>(pp) | reinterpret_cast<uintptr_t>(gp) |
+                           reinterpret_cast<uintptr_t>(mp) | reinterpret_cast<uintptr_t>(vp) |
+                           reinterpret_cast<uintptr_t>(sp);
+    const bool aligned = (bits & 15u) == 0;
+    const long long nvec = aligned ? n / 8 : 0;
     const long long stride = static_cast<long long>(gridDim.x) * blockDim.x;
-    for (long long chunk = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; chunk < total; chunk += stride) {
-        const int ti = find_tensor(t, chunk);
-        const long long base = (chunk - t.start[ti]) * 8;
-        const long long n = t.n[ti];
-        const int cnt = static_cast<int>(min(8ll, n - base));
+    const long long tid = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x;
+    for (long long chunk = tid; chunk < nvec; chunk += stride) {
+        const long long base = chunk * 8;
         float pv[8], gv[8];
-        const bool full = cnt == 8;
-        // parameters and gradients
-        if (p_f32) {
-            const float* pp = static_cast<const float*>(t.p[ti]) + base;
-            for (int i = 0; i < cnt; ++i) pv[i] = pp[i];
-        } else {
-            const __nv_bfloat16* pp = static_cast<const __nv_bfloat16*>(t.p[ti]) + base;
-            if (full && ((reinterpret_cast<uintptr_t>(pp) & 15u) == 0)) {
-                unpack8(*reinterpret_cast<const uint4*>(pp), pv);
-            } else {
-                for (int i = 0; i < cnt; ++i) pv[i] = __bfloat162float(pp[i]);
-            }
-        }
-        if (g_f32) {
-            const float* gp = static_cast<const float*>(t.g[ti]) + base;
-            for (int i = 0; i < cnt; ++i) gv[i] = gp[i];
-        } else {
-            const __nv_bfloat16* gp = static_cast<const __nv_bfloat16*>(t.g[ti]) + base;
-            if (full && ((reinterpret_cast<uintptr_t>(gp) & 15u) == 0)) {
-                unpack8(*reinterpret_cast<const uint4*>(gp), gv);
-            } else {
-                for (int i = 0; i < cnt; ++i) gv[i] = __bfloat162float(gp[i]);
-            }
-        }
+        load8<P_F32>(pp, base, pv);
+        load8<G_F32>(gp, base, gv);
         if (ADAM) {
-            float* mp = t.m[ti] + base;
-            float* vp = t.v[ti] + base;
             float mv[8], vv[8];
-            const bool mvec = full && ((reinterpret_cast<uintptr_t>(mp) & 15u) == 0) &&
-                              ((reinterpret_cast<uintptr_t>(vp) & 15u) == 0);
-            if (mvec) {
-                const float4 m0 = reinterpret_cast<const float4*>(mp)[0], m1 = reinterpret_cast<const float4*>(mp)[1];
-                const float4 v0 = reinterpret_cast<const float4*>(vp)[0], v1 = reinterpret_cast<const float4*>(vp)[1];
-                mv[0] = m0.x; mv[1] = m0.y; mv[2] = m0.z; mv[3] = m0.w; mv[4] = m1.x; mv[5] = m1.y; mv[6] = m1.z; mv[7] = m1.w;
-                vv[0] = v0.x; vv[1] = v0.y; vv[2] = v0.z; vv[3] = v0.w; vv[4] = v1.x; vv[5] = v1.y; vv[6] = v1.z; vv[7] = v1.w;
-            } else {
-                for (int i = 0; i < cnt; ++i) {
-                    mv[i] = mp[i];
-                    vv[i] = vp[i];
-                }
-            }
+            load8<true>(mp, base, mv);
+            load8<true>(vp, base, vv);
 #pragma unroll
-            for (int i = 0; i < 8; ++i) {
-                if (i < cnt) {
-                    mv[i] = s.beta1 * mv[i] + (1.0f - s.beta1) * gv[i];
-                    vv[i] = s.beta2 * vv[i] + (1.0f - s.beta2) * gv[i] * gv[i];
-                    pv[i] -= s.lr * (mv[i] * s.inv_bias1) / (sqrtf(vv[i] * s.inv_bias2) + s.eps);
-                }
-            }
-            if (mvec) {
-                reinterpret_cast<float4*>(mp)[0] = make_float4(mv[0], mv[1], mv[2], mv[3]);
-                reinterpret_cast<float4*>(mp)[1] = make_float4(mv[4], mv[5], mv[6], mv[7]);
-                reinterpret_cast<float4*>(vp)[0] = make_float4(vv[0], vv[1], vv[2], vv[3]);
-                reinterpret_cast<float4*>(vp)[1] = make_float4(vv[4], vv[5], vv[6], vv[7]);
-            } else {
-                for (int i = 0; i < cnt; ++i) {
-                    mp[i] = mv[i];
-                    vp[i] = vv[i];
-                }
-            }
+            for (int i = 0; i < 8; ++i) pv[i] = adam_update(pv[i], gv[i], mv[i], vv[i], s);
+            store8<true>(mp, base, mv);
+            store8<true>(vp, base, vv);
         } else {
-            for (int i = 0; i < cnt; ++i) pv[i] -= s.lr * gv[i];
+#pragma unroll
+            for (int i = 0; i < 8; ++i) pv[i] -= s.lr * gv[i];
         }
-        if (t.shadow[ti] != nullptr) {
-            __nv_bfloat16* sp = static_cast<__nv_bfloat16*>(t.shadow[ti]) + base;
-            if (full && ((reinterpret_cast<uintptr_t>(sp) & 15u) == 0)) {
-                *reinterpret_cast<uint4*>(sp) = make_uint4(pack_bf16x2(pv[0], pv[1]), pack_bf16x2(pv[2], pv[3]),
-                                                           pack_bf16x2(pv[4], pv[5]), pack_bf16x2(pv[6], pv[7]));
-            } else {
-                for (int i = 0; i < cnt; ++i) sp[i] = __float2bfloat16_rn(pv[i]);
-            }
-        }
-        if (p_f32) {
-            float* pp = static_cast<float*>(t.p[ti]) + base;
-            for (int i = 0; i < cnt; ++i) pp[i] = pv[i];
+        store8<P_F32>(pp, base, pv);
+        if (sp != nullptr) store8<false>(sp, base, pv);
+    }
+    for (long long i = nvec * 8 + tid; i < n; i += stride) {
+        float p = load_elem<P_F32>(pp, i);
+        const float g = load_elem<G_F32>(gp, i);
+        if (ADAM) {
+            float m = mp[i], v = vp[i];
+            p = adam_update(p, g, m, v, s);
+            mp[i] = m;
+            vp[i] = v;
         } else {
-            __nv_bfloat16* pp = static_cast<__nv_bfloat16*>(t.p[ti]) + base;
-            if (full && ((reinterpret_cast<uintptr_t>(pp) & 15u) == 0)) {
-                *reinterpret_cast<uint4*>(pp) = make_uint4(pack_bf16x2(pv[0], pv[1]), pack_bf16x2(pv[2], pv[3]),
-                                                           pack_bf16x2(pv[4], pv[5]), pack_bf16x2(pv[6], pv[7]));
-            } else {
-                for (int i = 0; i < cnt; ++i) pp[i] = __float2bfloat16_rn(pv[i]);
-            }
+            p -= s.lr * g;
         }
+        if (P_F32)
+            static_cast<float*>(pp)[i] = p;
+        else
+            static_cast<__nv_bfloat16*>(pp)[i] = __float2bfloat16_rn(p);
+        if (sp != nullptr) static_cast<__nv_bfloat16*>(sp)[i] = __float2bfloat16_rn(p);
     }
 }
 
@@ -176,10 +159,20 @@ int run_optim(b200_ctx* ctx, const char* who, int64_t count, void* const* params
             t.start[k + 1] = t.start[k] + (sizes[i] + 7) / 8;
         }
         if (t.count == 0) continue;
-        const long long chunks = t.start[t.count];
-        const int blocks = static_cast<int>(std::max<long long>(1, std::min<long long>((chunks + kThreads - 1) / kThreads,
-                                                                                       ctx->sm_count * 16ll)));
-        optim_kernel<ADAM><<<blocks, kThreads, 0, st>>>(t, s, p_dtype == B200_F32, g_dtype == B200_F32);
+        long long largest = 0;
+        for (int k = 0; k < t.count; ++k) largest = std::max(largest, (t.n[k] + 7) / 8);
+        const int blocks = static_cast<int>(std::max<long long>(1, std::min<long long>((largest + kThreads - 1) / kThreads,
+                                                                                       ctx->sm_count * 8ll)));
+        dim3 grid(static_cast<unsigned>(blocks), static_cast<unsigned>(t.count));
+        const bool pf = p_dtype == B200_F32, gf = g_dtype == B200_F32;
+        if (pf && gf)
+            optim_kernel<ADAM, true, true><<<grid, kThreads, 0, st>>>(t, s);
+        else if (pf)
+            optim_kernel<ADAM, true, false><<<grid, kThreads, 0, st>>>(t, s);
+        else if (gf)
+            optim_kernel<ADAM, false, true><<<grid, kThreads, 0, st>>>(t, s);
+        else
+            optim_kernel<ADAM, false, false><<<grid, kThreads, 0, st>>>(t, s);
         B200_CUDA_TRY(cudaGetLastError());
     }
     return B200_OK;

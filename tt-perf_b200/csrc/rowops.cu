@@ -507,31 +507,57 @@ __global__ void __launch_bounds__(kBlock) layernorm_bw_dx_block_kernel(const __n
 // Backward, parameter gradients: dgamma[c] = sum_r dy[r,c] * xhat[r,c], dbeta[c] = sum_r dy[r,c].
 // Each CTA owns 64 columns and a slab of rows; partial sums are combined with fp32 atomics into
 // zero-initialised fp32 accumulators, which a second tiny kernel converts to bf16.
+// VEC = 8: a thread owns 8 adjacent columns (16-byte loads); VEC = 1 for rows that are not 16-byte aligned.
+template <int VEC>
 __global__ void __launch_bounds__(256) layernorm_bw_param_kernel(const __nv_bfloat16* dy, long long lddy,
                                                                   const __nv_bfloat16* x, long long ldx, const float* mean,
                                                                   const float* rstd, float* dgamma_acc, float* dbeta_acc,
                                                                   int rows, int cols, int rows_per_cta) {
-    __shared__ float sg[4][64], sb[4][64];
-    const int c = blockIdx.x * 64 + (threadIdx.x & 63);
-    const int sub = threadIdx.x >> 6;  // 4 row lanes
+    __shared__ float sg[8][32][VEC + 1], sb[8][32][VEC + 1];
+    const int lane_c = threadIdx.x & 31;
+    const int c = (blockIdx.x * 32 + lane_c) * VEC;
+    const int sub = threadIdx.x >> 5;  // 8 row lanes
     const int r0 = blockIdx.y * rows_per_cta;
     const int r1 = min(rows, r0 + rows_per_cta);
-    float ag = 0.0f, ab = 0.0f;
+    float ag[VEC], ab[VEC];
+#pragma unroll
+    for (int k = 0; k < VEC; ++k) ag[k] = ab[k] = 0.0f;
     if (c < cols) {
-        for (int r = r0 + sub; r < r1; r += 4) {
-            const float d = __bfloat162float(dy[static_cast<size_t>(r) * lddy + c]);
-            const float xv = __bfloat162float(x[static_cast<size_t>(r) * ldx + c]);
-            ab += d;
-            if (dgamma_acc) ag += d * (xv - mean[r]) * rstd[r];
+        for (int r = r0 + sub; r < r1; r += 8) {
+            float d[8], xv[8];
+            if (VEC == 8) {
+                load8(dy + static_cast<size_t>(r) * lddy, c, cols, true, 0.0f, d);
+                load8(x + static_cast<size_t>(r) * ldx, c, cols, true, 0.0f, xv);
+            } else {
+                d[0] = __bfloat162float(dy[static_cast<size_t>(r) * lddy + c]);
+                xv[0] = __bfloat162float(x[static_cast<size_t>(r) * ldx + c]);
+            }
+            const float mu = mean[r], rs = rstd[r];
+#pragma unroll
+            for (int k = 0; k < VEC; ++k) {
+                ab[k] += d[k];
+                ag[k] += d[k] * (xv[k] - mu) * rs;
+            }
         }
     }
-    sg[sub][threadIdx.x & 63] = ag;
-    sb[sub][threadIdx.x & 63] = ab;
+#pragma unroll
+    for (int k = 0; k < VEC; ++k) {
+        sg[sub][lane_c][k] = ag[k];
+        sb[sub][lane_c][k] = ab[k];
+    }
     __syncthreads();
     if (sub == 0 && c < cols) {
-        const int t = threadIdx.x;
-        if (dgamma_acc) atomicAdd(&dgamma_acc[c], sg[0][t] + sg[1][t] + sg[2][t] + sg[3][t]);
-        if (dbeta_acc) atomicAdd(&dbeta_acc[c], sb[0][t] + sb[1][t] + sb[2][t] + sb[3][t]);
+#pragma unroll
+        for (int k = 0; k < VEC; ++k) {
+            if (c + k >= cols) break;
+            float g = 0.0f, b = 0.0f;
+            for (int j = 0; j < 8; ++j) {
+                g += sg[j][lane_c][k];
+                b += sb[j][lane_c][k];
+            }
+            if (dgamma_acc) atomicAdd(&dgamma_acc[c + k], g);
+            if (dbeta_acc) atomicAdd(&dbeta_acc[c + k], b);
+        }
     }
 }
 
@@ -711,12 +737,16 @@ int b200_layernorm_backward(b200_ctx* ctx, const void* dy, int64_t lddy, const v
         B200_CUDA_TRY(cudaGetLastError());
     }
     if (dgamma_f32 || dbeta_f32) {
-        const int col_blocks = (c + 63) / 64;
+        const bool vec8 = vec_ok(dy, lddy) && vec_ok(x, ldx) && (c % 8 == 0);
+        const int col_blocks = vec8 ? (c / 8 + 31) / 32 : (c + 31) / 32;
         int row_blocks = std::max(1, std::min((r + 63) / 64, (ctx->sm_count * 4 + col_blocks - 1) / col_blocks));
         const int rows_per = (r + row_blocks - 1) / row_blocks;
         row_blocks = (r + rows_per - 1) / rows_per;
         dim3 grid(col_blocks, row_blocks);
-        layernorm_bw_param_kernel<<<grid, 256, 0, s>>>(dyp, lddy, xp, ldx, mean, rstd, dgamma_f32, dbeta_f32, r, c, rows_per);
+        if (vec8)
+            layernorm_bw_param_kernel<8><<<grid, 256, 0, s>>>(dyp, lddy, xp, ldx, mean, rstd, dgamma_f32, dbeta_f32, r, c, rows_per);
+        else
+            layernorm_bw_param_kernel<1><<<grid, 256, 0, s>>>(dyp, lddy, xp, ldx, mean, rstd, dgamma_f32, dbeta_f32, r, c, rows_per);
         B200_CUDA_TRY(cudaGetLastError());
     }
     return B200_OK;

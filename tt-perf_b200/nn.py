@@ -54,14 +54,16 @@ def linear_forward(ctx, x, w, bias=None, activation=None, *, stream=None) -> Dev
     return matmul(ctx, x, w, False, True, bias=bias, activation=activation, stream=stream)
 
 
-def linear_backward(ctx, x, w, d_y, *, need_dx=True, stream=None):
+def linear_backward(ctx, x, w, d_y, *, need_dx=True, need_db=True, stream=None):
     """Returns (dx, dW, db): dx = dy . w, dW = dy^T . x and db = column sums of dy over all leading positions."""
     rows, n_out, n_in = _rows(x), w.shape[0], w.shape[1]
     x2, dy2 = x.reshape(rows, n_in), d_y.reshape(rows, n_out)
     d_x = matmul(ctx, d_y, w, False, False, stream=stream) if need_dx else None
     d_w = matmul(ctx, dy2, x2, True, False, stream=stream)
-    d_b = DeviceTensor(ctx, (n_out,), BF16)
-    ctx.reduce(capi.R_SUM, dy2, 1, rows, n_out, d_b, stream=stream)
+    d_b = None
+    if need_db:
+        d_b = DeviceTensor(ctx, (n_out,), BF16)
+        ctx.reduce(capi.R_SUM, dy2, 1, rows, n_out, d_b, stream=stream)
     return d_x, d_w, d_b
 
 
@@ -260,3 +262,125 @@ def transformer_block_backward(ctx, d_out, w, cache, heads, *, stream=None):
     d_x_ln, g["ln1_g"], g["ln1_b"] = layernorm_backward(ctx, d_ln1, c["x"], w["ln1_g"], c["mean1"], c["rstd1"],
                                                          stream=stream)
     return add(ctx, d_res1, d_x_ln, stream=stream), g
+
+
+# ---------------------------------------------------------------------------------------------------------------
+# GPT-2-shaped model: embeddings + L blocks + final LayerNorm + untied LM head + cross-entropy, Adam
+# (TracedTransformerWithEmbedding, autograd/traced/transformer_train.hpp:363-507; bench/autograd/bench_gpt2_full.cpp)
+# ---------------------------------------------------------------------------------------------------------------
+BLOCK_KEYS = ("ln1_g", "ln1_b", "wq", "bq", "wk", "bk", "wv", "bv", "wo", "bo", "ln2_g", "ln2_b", "w1", "b1", "w2", "b2")
+_F32_GRADS = ("ln1_g", "ln1_b", "ln2_g", "ln2_b")   # LayerNorm gradients come out of their kernel in fp32
+
+
+class GPT2:
+    """Parameters live on the device in bf16; the vocabulary dimension is padded to a multiple of 8 rows so that
+    logits rows start 16-byte aligned (50257 -> 50264); the cross-entropy kernel ignores the pad columns."""
+
+    def __init__(self, ctx, *, layers, d_model, heads, seq, vocab, d_ff=None):
+        self.ctx, self.L, self.D, self.H, self.S, self.V = ctx, layers, d_model, heads, seq, vocab
+        self.F = d_ff or 4 * d_model
+        self.Vp = (vocab + 7) // 8 * 8
+        self.params = None
+        self.opt = None
+
+    def block_shapes(self):
+        d, f = self.D, self.F
+        return dict(ln1_g=(d,), ln1_b=(d,), wq=(d, d), bq=(d,), wk=(d, d), bk=(d,), wv=(d, d), bv=(d,), wo=(d, d), bo=(d,),
+                    ln2_g=(d,), ln2_b=(d,), w1=(f, d), b1=(f,), w2=(d, f), b2=(d,))
+
+    def load(self, host_params) -> None:
+        """host_params: numpy arrays structured like the oracle's `gpt2_forward_backward` parameters."""
+        import numpy as np
+        ctx = self.ctx
+        head = np.zeros((self.Vp, self.D), np.float32)
+        head[: self.V] = host_params["head"]
+        self.params = {
+            "tok_emb": DeviceTensor.from_numpy(ctx, host_params["tok_emb"]),
+            "pos_emb": DeviceTensor.from_numpy(ctx, host_params["pos_emb"]),
+            "lnf_g": DeviceTensor.from_numpy(ctx, host_params["lnf_g"]),
+            "lnf_b": DeviceTensor.from_numpy(ctx, host_params["lnf_b"]),
+            "head": DeviceTensor.from_numpy(ctx, head),
+            "blocks": [{k: DeviceTensor.from_numpy(ctx, w[k]) for k in BLOCK_KEYS} for w in host_params["blocks"]],
+        }
+
+    def init_random(self, seed=42, std=0.02) -> None:
+        """N(0, std) weights, zero biases, LayerNorm gain 1 (random-init stand-in for a checkpoint)."""
+        import numpy as np
+        rng = np.random.default_rng(seed)
+
+        def w(*shape):
+            return (rng.standard_normal(shape, dtype=np.float32) * std)
+
+        blocks = []
+        for _ in range(self.L):
+            blk = {}
+            for k, shape in self.block_shapes().items():
+                if k.endswith("_g"):
+                    blk[k] = np.ones(shape, np.float32)
+                elif len(shape) == 1:
+                    blk[k] = np.zeros(shape, np.float32)
+                else:
+                    blk[k] = w(*shape)
+            blocks.append(blk)
+        self.load({"tok_emb": w(self.V, self.D), "pos_emb": w(self.S, self.D), "lnf_g": np.ones(self.D, np.float32),
+                   "lnf_b": np.zeros(self.D, np.float32), "head": w(self.V, self.D), "blocks": blocks})
+
+    def forward_backward(self, ids, targets, pos_ids, *, stream=None):
+        """ids, targets: uint32 device tensors [B, S] / [B*S]; pos_ids: uint32 [S] = 0..S-1.
+        Returns (loss fp32 scalar tensor, grads structured like params)."""
+        ctx, p = self.ctx, self.params
+        b = ids.numel // self.S
+        t = b * self.S
+        tok = DeviceTensor(ctx, (b, self.S, self.D), BF16)
+        ctx.embedding_forward(ids, t, p["tok_emb"], self.V, self.D, tok, stream=stream)
+        pos = DeviceTensor(ctx, (1, self.S, self.D), BF16)
+        ctx.embedding_forward(pos_ids, self.S, p["pos_emb"], self.S, self.D, pos, stream=stream)
+        x = add(ctx, tok, pos, stream=stream)
+        caches = []
+        for w in p["blocks"]:
+            x, cache = transformer_block_forward(ctx, x, w, self.H, stream=stream)
+            caches.append(cache)
+        xf, mean_f, rstd_f = layernorm_forward(ctx, x, p["lnf_g"], p["lnf_b"], stream=stream)
+        logits = matmul(ctx, xf, p["head"], False, True, stream=stream)            # [B, S, Vp]
+        loss = DeviceTensor(ctx, (1,), F32)
+        d_logits = DeviceTensor.zeros(ctx, logits.shape, BF16, stream=stream)        # pad columns stay zero
+        ctx.cross_entropy(logits, targets, t, self.V, ld=self.Vp, loss_sum=loss, d_logits=d_logits, ldd=self.Vp,
+                          stream=stream)
+        grads = {"blocks": [None] * self.L}
+        d_xf, grads["head"], _ = linear_backward(ctx, xf, p["head"], d_logits, need_db=False, stream=stream)
+        d_x, grads["lnf_g"], grads["lnf_b"] = layernorm_backward(ctx, d_xf, x, p["lnf_g"], mean_f, rstd_f, stream=stream)
+        for i in reversed(range(self.L)):
+            d_x, grads["blocks"][i] = transformer_block_backward(ctx, d_x, p["blocks"][i], caches[i], self.H, stream=stream)
+        grads["tok_emb"] = DeviceTensor(ctx, (self.V, self.D), F32)
+        ctx.embedding_backward(ids, t, d_x, self.V, self.D, grads["tok_emb"], stream=stream)
+        pos_g = DeviceTensor(ctx, (self.S, self.D), BF16)
+        ctx.reduce(capi.R_SUM, d_x, 1, b, self.S * self.D, pos_g, stream=stream)
+        grads["pos_emb"] = pos_g
+        return loss, grads
+
+    def _flat(self, tree):
+        """(bf16-gradient tensors, fp32-gradient tensors) in a fixed order, as (param, grad) pairs."""
+        p = self.params
+        bf, f32 = [], []
+        f32.append((p["tok_emb"], tree["tok_emb"]))
+        bf.append((p["pos_emb"], tree["pos_emb"]))
+        f32.append((p["lnf_g"], tree["lnf_g"]))
+        f32.append((p["lnf_b"], tree["lnf_b"]))
+        bf.append((p["head"], tree["head"]))
+        for w, g in zip(p["blocks"], tree["blocks"]):
+            for k in BLOCK_KEYS:
+                (f32 if k in _F32_GRADS else bf).append((w[k], g[k]))
+        return bf, f32
+
+    def adam_step(self, grads, *, lr=3e-4, betas=(0.9, 0.95), eps=1e-8, stream=None) -> None:
+        bf, f32 = self._flat(grads)
+        if self.opt is None:
+            self.opt = (Adam(self.ctx, [p for p, _ in bf], lr=lr, betas=betas, eps=eps),
+                        Adam(self.ctx, [p for p, _ in f32], lr=lr, betas=betas, eps=eps))
+        self.opt[0].step([g for _, g in bf], stream=stream)
+        self.opt[1].step([g for _, g in f32], stream=stream)
+
+    def num_params(self) -> int:
+        bf, f32 = self._flat({"tok_emb": None, "pos_emb": None, "lnf_g": None, "lnf_b": None, "head": None,
+                              "blocks": [dict.fromkeys(BLOCK_KEYS)] * self.L})
+        return sum(p.numel for p, _ in bf + f32) - (self.Vp - self.V) * self.D

@@ -1,5 +1,6 @@
 """Device tensors for the Python host side: a shape + dtype + device pointer owned through the C ABI
-(b200_malloc / b200_free), with host <-> device copies through b200_memcpy_*. No torch, no CPU math:
+(the pooled allocator b200_pool_alloc / b200_pool_free, so that allocation is cheap and legal while a trace is
+being recorded), with host <-> device copies through b200_memcpy_*. No torch, no CPU math:
 numpy is used only to hold host bytes and to convert fp32 <-> bf16 bit patterns at the boundary, the way
 `Tensor::from_vector` / `.cpu().to_vector<bfloat16>()` do in the reference (autograd/common.hpp:53,
 traced/nn.hpp:40-52)."""
@@ -37,7 +38,7 @@ class DeviceTensor:
         self.nbytes = self.numel * _ITEMSIZE[dtype]
         self._owner = owner          # keeps the storage of a view alive
         self._owns = ptr is None
-        self.ptr = ctx.malloc(max(self.nbytes, 16)) if ptr is None else ptr
+        self.ptr = ctx.pool_alloc(max(self.nbytes, 16)) if ptr is None else ptr
 
     # -- construction -------------------------------------------------------------------------------------------
     @classmethod
@@ -95,8 +96,8 @@ class DeviceTensor:
         return self.ptr
 
     def free(self) -> None:
-        if self._owns and self.ptr:
-            self.ctx.free(self.ptr)
+        if self._owns and self.ptr and getattr(self.ctx, "_h", None):
+            self.ctx.pool_free(self.ptr)
         self.ptr = 0
         self._owns = False
 
