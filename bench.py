@@ -315,7 +315,7 @@ def run_b200_single(args) -> None:
         "roofline": {"bound": "tensor", "achieved": tflops, "peak": peak, "unit": "TFLOP/s", "frac": tflops / peak,
                      "traffic": GEMM_8192_DRAM_TRAFFIC_BYTES,
                      "peak_source": f"{peaks['source']} (MEASURED_PEAKS.json bf16_tflops, burst: kernel timed alone)",
-                     "kernel": "gemm_tcgen05_kernel<256,K-major A,MN-major B>", "flops_per_launch": flops},
+                     "kernel": "gemm_tcgen05_2cta_kernel<K-major A,MN-major B> (cta_group::2, 256x256x64 tiles)", "flops_per_launch": flops},
         "cpu_baseline": cpu,
         "e2e": {"value": e2e_tflops, "unit": "TFLOP/s", "h2d_bytes_per_step": 2 * nbytes, "d2h_bytes_per_step": nbytes,
                 "ms_per_step": e2e_s * 1e3, "steps": e2e_steps},

@@ -54,6 +54,8 @@ SHAPES = [
     (8, 8, 8),
     (1, 8, 8),
     (513, 72, 1032),
+    (2600, 2824, 776),  # enough 256 x 256 tiles for the CTA-pair kernel, ragged on every side
+    (4096, 2560, 320),
 ]
 
 

@@ -124,6 +124,7 @@ int b200_gemm_allgather(b200_ctx* ctx, const b200_gemm_desc* d, void* const* pee
     local.C = route.dst[my_rank];
     local.split_k = 1;
     DeviceScope scope(ctx->device);
+    if (gemm_pair_eligible(ctx, local, &route)) return launch_gemm_tcgen05_pair(ctx, local, ctx->pick(stream), &route);
     return launch_gemm_tcgen05(ctx, local, 1, ctx->pick(stream), &route);
 }
 
@@ -157,6 +158,7 @@ int b200_gemm_reduce_scatter_partials(b200_ctx* ctx, const b200_gemm_desc* d, vo
     local.causal_mask = 0;
     local.split_k = 1;
     DeviceScope scope(ctx->device);
+    if (gemm_pair_eligible(ctx, local, &route)) return launch_gemm_tcgen05_pair(ctx, local, ctx->pick(stream), &route);
     return launch_gemm_tcgen05(ctx, local, 1, ctx->pick(stream), &route);
 }
 

@@ -2,6 +2,7 @@
 #include "gemm_common.cuh"
 
 #include <algorithm>
+#include <cstdlib>
 
 namespace b200 {
 namespace {
@@ -52,6 +53,15 @@ int validate(const b200_gemm_desc* d) {
         B200_REQUIRE(d->ldb >= b_cols, "b200_gemm: ldb (%lld) < row length of B (%lld)", (long long)d->ldb, b_cols);
     }
     return B200_OK;
+}
+
+// The CTA-pair kernel serves large products; B200_GEMM_2CTA=0 keeps everything on the single-CTA kernel.
+bool pair_kernel_enabled() {
+    static const bool value = [] {
+        const char* e = getenv("B200_GEMM_2CTA");
+        return e == nullptr || atoi(e) != 0;
+    }();
+    return value;
 }
 
 }  // namespace
@@ -117,6 +127,8 @@ int b200_gemm(b200_ctx* ctx, const b200_gemm_desc* d, void* stream_v) {
         return fail(B200_ERR_INVALID_ARG, "b200_gemm: tcgen05 path requested but %s", why);
     if (d->algo == B200_GEMM_SIMT || !eligible) return launch_gemm_simt(ctx, *d, stream);
     const int splits = gemm_choose_split_k(ctx, *d);
+    if (splits == 1 && pair_kernel_enabled() && gemm_pair_eligible(ctx, *d, nullptr))
+        return launch_gemm_tcgen05_pair(ctx, *d, stream);
     return launch_gemm_tcgen05(ctx, *d, splits, stream);
 }
 

@@ -137,6 +137,9 @@ int launch_gemm_tcgen05(b200_ctx* ctx, const b200_gemm_desc& d, int k_splits, cu
                         const GemmRoute* route = nullptr);
 // Sums `splits` fp32 slices [splits][batch][M][N], applies the descriptor's epilogue and writes C.
 int launch_splitk_reduce(b200_ctx* ctx, const b200_gemm_desc& d, const float* partial, int splits, cudaStream_t stream);
+// CTA-pair (cta_group::2) kernel for large products; `gemm_pair_eligible` says whether it applies.
+bool gemm_pair_eligible(const b200_ctx* ctx, const b200_gemm_desc& d, const GemmRoute* route);
+int launch_gemm_tcgen05_pair(b200_ctx* ctx, const b200_gemm_desc& d, cudaStream_t stream, const GemmRoute* route = nullptr);
 int launch_gemm_simt(b200_ctx* ctx, const b200_gemm_desc& d, cudaStream_t stream);
 bool gemm_tcgen05_eligible(const b200_gemm_desc& d, const char** why);
 // Chooses the K-slice count for the tcgen05 path (1 = no split).

@@ -1,0 +1,463 @@
+// CTA-pair variant of the tcgen05 GEMM for large products: two CTAs of a cluster (one SM each) share a 256 x 256
+// output tile and one `tcgen05.mma.cta_group::2` instruction stream.
+//
+//   * each CTA loads its own 128 rows of A and 128 of the tile's 256 B columns per 64-deep K block (32 KiB per stage,
+//     6 stages) — half the shared-memory fill and half the B reads per SM of the single-CTA kernel;
+//   * the leader CTA (cluster rank 0) issues the MMAs (M = 256, N = 256, K = 16); the hardware reads A and B from both
+//     CTAs' shared memory and writes rows 0-127 of the accumulator to the leader's TMEM, rows 128-255 to the peer's;
+//   * TMA completions of both CTAs are counted on the leader's "full" barrier (cta_group::2 loads, no multicast);
+//     `tcgen05.commit` with a 2-CTA multicast mask releases ring stages and publishes accumulators in both CTAs;
+//   * each CTA's four epilogue warps drain their own 128 accumulator rows through the staged TMA-store epilogue.
+//
+// Same roles, ring protocol, bounded waits and output routing as gemm_tcgen05.cu; requires 16-byte aligned C rows.
+#include <algorithm>
+#include <cstring>
+
+#include "gemm_common.cuh"
+#include "ptx.cuh"
+
+namespace b200 {
+
+using namespace ptx;
+
+namespace {
+
+constexpr int BM_CTA = 128;   // accumulator rows per CTA
+constexpr int BM_PAIR = 256;  // tile rows per CTA pair
+constexpr int BN = 256;
+constexpr int BN_CTA = 128;   // B columns loaded by each CTA
+constexpr int BK = 64;
+constexpr int UMMA_K = 16;
+constexpr int NUM_THREADS = 192;
+constexpr int STAGES = 6;
+constexpr int A_BYTES = BM_CTA * BK * 2;
+constexpr int B_BYTES = BN_CTA * BK * 2;
+constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
+constexpr int EPI_STAGE_BYTES = 4096;
+constexpr int EPI_BYTES = 4 * 2 * EPI_STAGE_BYTES;
+constexpr int BARRIER_BYTES = 256;
+constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + EPI_BYTES + BARRIER_BYTES + 1024;
+
+struct PairWork {
+    int b, m0, n0;
+};
+
+__device__ __forceinline__ PairWork decode_pair(const GemmParams& p, int w) {
+    PairWork it;
+    const int tiles_mn = p.num_m_tiles * p.num_n_tiles;
+    it.b = w / tiles_mn;
+    const int t = w - it.b * tiles_mn;
+    const int tiles_per_group = p.group_m * p.num_n_tiles;
+    const int g = t / tiles_per_group;
+    const int first_m = g * p.group_m;
+    const int gsz = min(p.num_m_tiles - first_m, p.group_m);
+    const int rr = t - g * tiles_per_group;
+    it.m0 = (first_m + rr % gsz) * BM_PAIR;
+    it.n0 = (rr / gsz) * BN;
+    return it;
+}
+
+template <bool A_KMAJOR, bool B_KMAJOR>
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(NUM_THREADS, 1)
+gemm_tcgen05_2cta_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
+                         const __grid_constant__ CMaps tmC, const GemmParams p, const int tmem_cols) {
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t* smem = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
+    uint8_t* epi_smem = smem + STAGES * STAGE_BYTES;
+    uint8_t* bar_base = epi_smem + EPI_BYTES;
+    uint64_t* full_bar = reinterpret_cast<uint64_t*>(bar_base);   // used in the leader only
+    uint64_t* empty_bar = full_bar + STAGES;                       // one per CTA (multicast commit)
+    uint64_t* tmem_full_bar = empty_bar + STAGES;                  // one per CTA (multicast commit)
+    uint64_t* tmem_empty_bar = tmem_full_bar + 2;                  // used in the leader only: 8 arrivals (4 warps x 2 CTAs)
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(tmem_empty_bar + 2);
+    volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+    const int warp = threadIdx.x >> 5;
+    const int lane = threadIdx.x & 31;
+    const uint32_t rank = cluster_ctarank();       // 0 = leader
+    const int cluster_id = blockIdx.x >> 1;
+    const int num_clusters = gridDim.x >> 1;
+    const bool two_bufs = tmem_cols >= 2 * BN;     // accumulator double buffering needs 512 TMEM columns
+
+    if (threadIdx.x == 0) {
+        prefetch_tensormap(&tmA);
+        prefetch_tensormap(&tmB);
+        for (int s = 0; s < STAGES; ++s) {
+            mbar_init(&full_bar[s], 1);
+            mbar_init(&empty_bar[s], 1);
+        }
+        for (int a = 0; a < 2; ++a) {
+            mbar_init(&tmem_full_bar[a], 1);
+            mbar_init(&tmem_empty_bar[a], 8);
+        }
+        *abort_flag = 0;
+        mbar_fence_init();
+    }
+    if (warp == 1) {
+        tmem_alloc_pair(tmem_slot, static_cast<uint32_t>(tmem_cols));
+        tmem_relinquish_alloc_permit_pair();
+    }
+    tcgen05_fence_before_sync();
+    __syncthreads();
+    cluster_sync_all();  // both CTAs' barriers are initialised before anyone signals across the pair
+    tcgen05_fence_after_sync();
+    const uint32_t tmem_base = *tmem_slot;
+
+    if (warp == 0) {
+        // ------------------------------------------------------------------ TMA producer (both CTAs)
+        if (lane == 0) {
+            int stage = 0;
+            uint32_t phase = 0;
+            bool ok = true;
+            for (int w = cluster_id; ok && w < p.total_work; w += num_clusters) {
+                const PairWork it = decode_pair(p, w);
+                const int ab = p.a_batched ? it.b : 0;
+                const int bb = p.b_batched ? it.b : 0;
+                const int m_cta = it.m0 + static_cast<int>(rank) * BM_CTA;
+                const int n_cta = it.n0 + static_cast<int>(rank) * BN_CTA;
+                for (int kb = 0; kb < p.num_kb; ++kb) {
+                    if (!mbar_wait(&empty_bar[stage], phase ^ 1u, abort_flag)) {
+                        ok = false;
+                        break;
+                    }
+                    uint8_t* sA = smem + stage * STAGE_BYTES;
+                    uint8_t* sB = sA + A_BYTES;
+                    // completions of both CTAs are counted on the leader's barrier
+                    const uint32_t full_leader = mapa_shared(smem_u32(&full_bar[stage]), 0);
+                    if (rank == 0) mbar_arrive_expect_tx(&full_bar[stage], 2 * STAGE_BYTES);
+                    if (A_KMAJOR) {
+                        tma_load_3d_pair(sA, &tmA, full_leader, kb * BK, m_cta, ab);
+                    } else {
+#pragma unroll
+                        for (int j = 0; j < BM_CTA / 64; ++j)
+                            tma_load_3d_pair(sA + j * (64 * BK * 2), &tmA, full_leader, m_cta + 64 * j, kb * BK, ab);
+                    }
+                    if (B_KMAJOR) {
+                        tma_load_3d_pair(sB, &tmB, full_leader, kb * BK, n_cta, bb);
+                    } else {
+#pragma unroll
+                        for (int j = 0; j < BN_CTA / 64; ++j)
+                            tma_load_3d_pair(sB + j * (64 * BK * 2), &tmB, full_leader, n_cta + 64 * j, kb * BK, bb);
+                    }
+                    if (++stage == STAGES) {
+                        stage = 0;
+                        phase ^= 1u;
+                    }
+                }
+            }
+            if (!ok && rank == 0) {
+                // Gave up: the leader's barriers count both CTAs' copies; let those already issued land before the
+                // pair's shared memory goes away (the peer leaves only after the cluster barrier below).
+                for (int s = 0; s < STAGES; ++s) {
+                    const uint32_t par = (s < stage) ? phase : (phase ^ 1u);
+                    const uint64_t t0 = globaltimer_ns();
+                    while (!mbar_try_wait(&full_bar[s], par)) {
+                        if (globaltimer_ns() - t0 > 100000000ull) break;
+                    }
+                }
+            }
+        }
+    } else if (warp == 1) {
+        // ------------------------------------------------------------------ MMA issuer (leader CTA only)
+        if (lane == 0 && rank == 0) {
+            constexpr uint32_t idesc = make_idesc_bf16_f32(BM_PAIR, BN, A_KMAJOR ? 0u : 1u, B_KMAJOR ? 0u : 1u);
+            constexpr uint32_t A_KSTEP = A_KMAJOR ? (UMMA_K * 2) : (UMMA_K * 128);
+            constexpr uint32_t B_KSTEP = B_KMAJOR ? (UMMA_K * 2) : (UMMA_K * 128);
+            constexpr uint32_t A_LBO = A_KMAJOR ? 0u : (BK * 128);
+            constexpr uint32_t B_LBO = B_KMAJOR ? 0u : (BK * 128);
+            int stage = 0;
+            uint32_t phase = 0;
+            int acc = 0;
+            uint32_t acc_phase = 0;
+            bool ok = true;
+            for (int w = cluster_id; ok && w < p.total_work; w += num_clusters) {
+                if (!mbar_wait(&tmem_empty_bar[acc], acc_phase ^ 1u, abort_flag)) break;
+                tcgen05_fence_after_sync();
+                const uint32_t d_tmem = tmem_base + static_cast<uint32_t>(acc * BN);
+#ifdef B200_GEMM_PROFILE
+                const int prof_slot = (w - cluster_id) / num_clusters;
+                if (p.prof && prof_slot < 8) p.prof[(blockIdx.x * 8 + prof_slot) * 8 + 0] = clock64();
+#endif
+                for (int kb = 0; kb < p.num_kb; ++kb) {
+                    if (!mbar_wait(&full_bar[stage], phase, abort_flag)) {
+                        ok = false;
+                        break;
+                    }
+                    tcgen05_fence_after_sync();
+                    const uint32_t a_addr = smem_u32(smem + stage * STAGE_BYTES);
+                    const uint32_t b_addr = a_addr + A_BYTES;
+#pragma unroll
+                    for (int k = 0; k < BK / UMMA_K; ++k) {
+                        const uint64_t da = make_smem_desc_sw128(a_addr + k * A_KSTEP, A_LBO, 1024);
+                        const uint64_t db = make_smem_desc_sw128(b_addr + k * B_KSTEP, B_LBO, 1024);
+                        umma_f16_ss_pair(d_tmem, da, db, idesc, (kb > 0 || k > 0) ? 1u : 0u);
+                    }
+                    umma_commit_pair(&empty_bar[stage], 3);  // frees the stage in both CTAs
+                    if (++stage == STAGES) {
+                        stage = 0;
+                        phase ^= 1u;
+                    }
+                }
+                if (!ok) break;
+                umma_commit_pair(&tmem_full_bar[acc], 3);  // accumulator complete, both CTAs' epilogues may read
+#ifdef B200_GEMM_PROFILE
+                if (p.prof && prof_slot < 8) p.prof[(blockIdx.x * 8 + prof_slot) * 8 + 1] = clock64();
+#endif
+                if (two_bufs) {
+                    acc ^= 1;
+                    if (acc == 0) acc_phase ^= 1u;
+                } else {
+                    acc_phase ^= 1u;
+                }
+            }
+        }
+    } else {
+        // ------------------------------------------------------------------ epilogue (warps 2..5, both CTAs)
+        const int q = warp & 3;
+        int acc = 0;
+        uint32_t acc_phase = 0;
+        int ebuf = 0;
+        uint8_t* stage_base = epi_smem + (warp - 2) * 2 * EPI_STAGE_BYTES;
+        const int box_cols = p.c_f32 ? 32 : 64;
+        for (int w = cluster_id; w < p.total_work; w += num_clusters) {
+            const PairWork it = decode_pair(p, w);
+            const bool got = mbar_wait(&tmem_full_bar[acc], acc_phase, abort_flag);
+            if (!__all_sync(0xffffffffu, got)) break;
+            tcgen05_fence_after_sync();
+#ifdef B200_GEMM_PROFILE
+            const int eprof_slot = (w - cluster_id) / num_clusters;
+            if (p.prof && eprof_slot < 8 && threadIdx.x == 64) p.prof[(blockIdx.x * 8 + eprof_slot) * 8 + 2] = clock64();
+#endif
+            const int m_cta = it.m0 + static_cast<int>(rank) * BM_CTA;
+            const int row = m_cta + q * 32 + lane;
+            const uint32_t taddr = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + static_cast<uint32_t>(acc * BN);
+            int dst_first = 0, dst_count = p.n_dst, row_coord = m_cta + q * 32;
+            if (p.scatter_rows > 0) {
+                dst_first = m_cta / p.scatter_rows;
+                dst_count = 1;
+                row_coord -= dst_first * p.scatter_rows;
+            }
+            if (m_cta < p.M) {  // a CTA whose 128 rows lie entirely below the matrix has nothing to store
+#pragma unroll 1
+                for (int c = 0; c < BN; c += box_cols) {
+                    const int n = it.n0 + c;
+                    if (n >= p.N) break;
+                    uint8_t* sbuf = stage_base + ebuf * EPI_STAGE_BYTES;
+                    if (lane == 0) tma_store_wait_read<1>();
+                    __syncwarp();
+                    uint8_t* srow = sbuf + lane * 128;
+#pragma unroll 1
+                    for (int h = 0; h * 32 < box_cols; ++h) {
+                        const int nh = n + h * 32;
+                        if (nh >= p.N) break;
+                        uint32_t v[32];
+                        tmem_ld_32x32b_x32(taddr + c + h * 32, v);
+                        tmem_ld_wait();
+                        float f[32];
+                        epi_apply32(p.epi, v, f, row, nh, p.N);
+                        if (p.c_f32) {
+#pragma unroll
+                            for (int j = 0; j < 8; ++j)
+                                *reinterpret_cast<float4*>(srow + ((j ^ (lane & 7)) << 4)) =
+                                    make_float4(f[4 * j], f[4 * j + 1], f[4 * j + 2], f[4 * j + 3]);
+                        } else {
+#pragma unroll
+                            for (int j = 0; j < 4; ++j)
+                                *reinterpret_cast<uint4*>(srow + (((h * 4 + j) ^ (lane & 7)) << 4)) =
+                                    make_uint4(pack_bf16x2(f[8 * j], f[8 * j + 1]), pack_bf16x2(f[8 * j + 2], f[8 * j + 3]),
+                                               pack_bf16x2(f[8 * j + 4], f[8 * j + 5]), pack_bf16x2(f[8 * j + 6], f[8 * j + 7]));
+                        }
+                    }
+                    fence_proxy_async_smem();
+                    __syncwarp();
+                    if (lane == 0) {
+                        for (int d = 0; d < dst_count; ++d) {
+                            int di = d + p.dst_rotate;
+                            if (di >= dst_count) di -= dst_count;
+                            tma_store_3d(&tmC.m[dst_first + di], sbuf, n, row_coord, it.b);
+                        }
+                        tma_store_commit();
+                    }
+                    ebuf ^= 1;
+                }
+            }
+#ifdef B200_GEMM_PROFILE
+            if (p.prof && eprof_slot < 8 && threadIdx.x == 64) p.prof[(blockIdx.x * 8 + eprof_slot) * 8 + 3] = clock64();
+#endif
+            // Hand the accumulator buffer back to the leader's MMA warp (remote arrive from the peer CTA).
+            tcgen05_fence_before_sync();
+            __syncwarp();
+            if (lane == 0) mbar_arrive_cluster(mapa_shared(smem_u32(&tmem_empty_bar[acc]), 0));
+            if (two_bufs) {
+                acc ^= 1;
+                if (acc == 0) acc_phase ^= 1u;
+            } else {
+                acc_phase ^= 1u;
+            }
+        }
+        if (lane == 0) tma_store_wait_all<0>();
+    }
+
+    // ---------------------------------------------------------------------- teardown
+    tcgen05_fence_before_sync();
+    __syncthreads();
+    cluster_sync_all();  // the peer may still be signalling this CTA's barriers or reading its shared memory
+    if (threadIdx.x == 0 && *abort_flag != 0) atomicExch(p.status, 1);
+    if (warp == 1) {
+        tcgen05_fence_after_sync();
+        tmem_dealloc_pair(tmem_base, static_cast<uint32_t>(tmem_cols));
+    }
+}
+
+template <bool A_KMAJOR, bool B_KMAJOR>
+int launch_pair_variant(const CUtensorMap& tmA, const CUtensorMap& tmB, const CMaps& tmC, const GemmParams& p, int grid,
+                        int tmem_cols, cudaStream_t stream) {
+    auto kernel = gemm_tcgen05_2cta_kernel<A_KMAJOR, B_KMAJOR>;
+    static bool configured[64] = {};
+    int dev = 0;
+    B200_CUDA_TRY(cudaGetDevice(&dev));
+    if (dev < 0 || dev >= 64 || !configured[dev]) {
+        B200_CUDA_TRY(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES));
+        if (dev >= 0 && dev < 64) configured[dev] = true;
+    }
+    kernel<<<grid, NUM_THREADS, SMEM_BYTES, stream>>>(tmA, tmB, tmC, p, tmem_cols);
+    B200_CUDA_TRY(cudaGetLastError());
+    return B200_OK;
+}
+
+int encode_map(b200_ctx* ctx, CUtensorMap* out, const void* base, uint64_t inner, uint64_t rows, uint64_t batch,
+               uint64_t ld_elems, uint64_t batch_stride_elems, uint32_t box_inner, uint32_t box_rows, bool f32) {
+    const uint64_t es = f32 ? 4 : 2;
+    cuuint64_t dims[3] = {inner, rows, batch};
+    if (batch <= 1 || batch_stride_elems == 0) {
+        dims[2] = 1;
+        batch_stride_elems = rows * ld_elems;
+    }
+    cuuint64_t strides[2] = {ld_elems * es, batch_stride_elems * es};
+    cuuint32_t box[3] = {box_inner, box_rows, 1};
+    cuuint32_t estr[3] = {1, 1, 1};
+    CUresult r = ctx->encode_tiled(out, f32 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT32 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3,
+                                   const_cast<void*>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                                   CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                                   CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) return fail(B200_ERR_CUDA, "cuTensorMapEncodeTiled failed (%d)", static_cast<int>(r));
+    return B200_OK;
+}
+
+inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
+
+}  // namespace
+
+// Accumulator columns the pair kernel allocates in each CTA's TMEM: 512 = double buffered (default),
+// 256 = single buffer. B200_GEMM_2CTA_TMEM_COLS overrides (development knob).
+static int pair_tmem_cols() {
+    static const int value = [] {
+        const char* e = getenv("B200_GEMM_2CTA_TMEM_COLS");
+        const int v = e ? atoi(e) : 0;
+        return (v == 256 || v == 512) ? v : 512;
+    }();
+    return value;
+}
+
+// Row-tiles (of 256 rows) per column sweep of the tile order; B200_GEMM_2CTA_GROUP_M overrides (development knob).
+static int pair_group_m(int num_m_tiles) {
+    static const int forced = [] {
+        const char* e = getenv("B200_GEMM_2CTA_GROUP_M");
+        const int v = e ? atoi(e) : 0;
+        return (v >= 1 && v <= 64) ? v : 0;
+    }();
+    if (forced) return forced;
+    return num_m_tiles >= 64 ? 16 : 8;  // measured: 8 is best up to 8192 rows, 16 at 16384
+}
+
+bool gemm_pair_eligible(const b200_ctx* ctx, const b200_gemm_desc& d, const GemmRoute* route) {
+    if (!gemm_tcgen05_eligible(d, nullptr)) return false;
+    const int cvec = d.c_dtype == B200_F32 ? 4 : 8;
+    if ((d.ldc % cvec) != 0 || (d.batch > 1 && (d.stride_c % cvec) != 0)) return false;
+    if (route == nullptr || route->n_dst == 0) {
+        if (!aligned16(d.C)) return false;
+    } else if (route->scatter_rows > 0 && (route->scatter_rows % BM_CTA) != 0) {
+        return false;
+    }
+    // worth it only when the 256 x 256 tiles keep all CTA pairs busy
+    const long long tiles = d.batch * ((d.M + BM_PAIR - 1) / BM_PAIR) * ((d.N + BN - 1) / BN);
+    return d.N >= 256 && d.M >= 256 && tiles >= (ctx->sm_count / 2);
+}
+
+int launch_gemm_tcgen05_pair(b200_ctx* ctx, const b200_gemm_desc& d, cudaStream_t stream, const GemmRoute* route) {
+    const bool a_kmajor = d.transpose_a == 0;
+    const bool b_kmajor = d.transpose_b != 0;
+    GemmParams p{};
+    p.M = static_cast<int>(d.M);
+    p.N = static_cast<int>(d.N);
+    p.K = static_cast<int>(d.K);
+    p.batch = static_cast<int>(d.batch);
+    p.num_m_tiles = (p.M + BM_PAIR - 1) / BM_PAIR;
+    p.num_n_tiles = (p.N + BN - 1) / BN;
+    p.num_kb = (p.K + BK - 1) / BK;
+    p.k_splits = 1;
+    p.kb_per_split = p.num_kb;
+    const long long total = static_cast<long long>(p.batch) * p.num_m_tiles * p.num_n_tiles;
+    B200_REQUIRE(total < (1ll << 31), "b200_gemm: too many tiles (%lld)", total);
+    p.total_work = static_cast<int>(total);
+    p.a_batched = (d.batch > 1 && d.stride_a != 0) ? 1 : 0;
+    p.b_batched = (d.batch > 1 && d.stride_b != 0) ? 1 : 0;
+    p.C = d.C;
+    p.ldc = d.ldc;
+    p.stride_c = d.stride_c;
+    p.c_f32 = d.c_dtype == B200_F32;
+    p.c_vec_ok = 1;
+    p.epi.alpha = d.alpha;
+    p.epi.bias = d.bias;
+    p.epi.bias_f32 = d.bias_dtype == B200_F32;
+    p.epi.act = d.activation;
+    p.epi.gelu_tanh = d.fidelity == B200_LOFI;
+    p.epi.causal = d.causal_mask;
+    p.epi.mask_value = d.mask_value;
+    p.status = ctx->d_status;
+    p.group_m = pair_group_m(p.num_m_tiles);
+    p.epi_mode = 1;
+    p.n_dst = 1;
+#ifdef B200_GEMM_PROFILE
+    p.prof = static_cast<long long*>(ctx->d_scratch);
+#endif
+
+    CUtensorMap tmA, tmB;
+    CMaps tmC;
+    memset(&tmC, 0, sizeof(tmC));
+    int rc;
+    if (a_kmajor)
+        rc = encode_map(ctx, &tmA, d.A, d.K, d.M, d.batch, d.lda, d.stride_a, BK, BM_CTA, false);
+    else
+        rc = encode_map(ctx, &tmA, d.A, d.M, d.K, d.batch, d.lda, d.stride_a, 64, BK, false);
+    if (rc != B200_OK) return rc;
+    if (b_kmajor)
+        rc = encode_map(ctx, &tmB, d.B, d.K, d.N, d.batch, d.ldb, d.stride_b, BK, BN_CTA, false);
+    else
+        rc = encode_map(ctx, &tmB, d.B, d.N, d.K, d.batch, d.ldb, d.stride_b, 64, BK, false);
+    if (rc != B200_OK) return rc;
+    const uint32_t box_cols = p.c_f32 ? 32 : 64;
+    if (route != nullptr && route->n_dst > 0) {
+        B200_REQUIRE(route->n_dst <= 8, "b200_gemm: at most 8 destinations");
+        for (int i = 0; i < route->n_dst; ++i) {
+            B200_REQUIRE(aligned16(route->dst[i]), "b200_gemm: destination %d is not 16-byte aligned", i);
+            rc = encode_map(ctx, &tmC.m[i], route->dst[i], d.N, route->rows[i], 1, d.ldc, 0, box_cols, 32, p.c_f32);
+            if (rc != B200_OK) return rc;
+        }
+        p.n_dst = route->scatter_rows > 0 ? 1 : route->n_dst;
+        p.scatter_rows = route->scatter_rows;
+        p.dst_rotate = (route->scatter_rows > 0 || route->rotate < 0 || route->rotate >= route->n_dst) ? 0 : route->rotate;
+    } else {
+        rc = encode_map(ctx, &tmC.m[0], d.C, d.N, d.M, d.batch, d.ldc, d.stride_c, box_cols, 32, p.c_f32);
+        if (rc != B200_OK) return rc;
+    }
+    const int clusters = std::min(p.total_work, ctx->sm_count / 2);
+    const int grid = 2 * clusters;
+    const int cols = pair_tmem_cols();
+    if (a_kmajor && b_kmajor) return launch_pair_variant<true, true>(tmA, tmB, tmC, p, grid, cols, stream);
+    if (a_kmajor && !b_kmajor) return launch_pair_variant<true, false>(tmA, tmB, tmC, p, grid, cols, stream);
+    if (!a_kmajor && b_kmajor) return launch_pair_variant<false, true>(tmA, tmB, tmC, p, grid, cols, stream);
+    return launch_pair_variant<false, false>(tmA, tmB, tmC, p, grid, cols, stream);
+}
+
+}  // namespace b200
