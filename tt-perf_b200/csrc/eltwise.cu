@@ -116,6 +116,20 @@ __global__ void __launch_bounds__(kThreads) binary_flat_kernel(const __nv_bfloat
     }
 }
 
+// a has the output's shape, b is one row [.., 1, N] broadcast over all rows (bias add): b's vector index is i mod N/8.
+__global__ void __launch_bounds__(kThreads) binary_rowbcast_kernel(const __nv_bfloat16* a, const __nv_bfloat16* b,
+                                                                    __nv_bfloat16* out, long long nvec, int row_vecs, int op) {
+    const long long stride = static_cast<long long>(gridDim.x) * blockDim.x;
+    for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < nvec; i += stride) {
+        float fa[8], fb[8];
+        unpack8(reinterpret_cast<const uint4*>(a)[i], fa);
+        unpack8(reinterpret_cast<const uint4*>(b)[static_cast<int>(i % row_vecs)], fb);
+#pragma unroll
+        for (int k = 0; k < 8; ++k) fa[k] = binary_apply(op, fa[k], fb[k]);
+        reinterpret_cast<uint4*>(out)[i] = pack8(fa);
+    }
+}
+
 __global__ void __launch_bounds__(kThreads) binary_kernel(const BinaryParams p) {
     const long long stride = static_cast<long long>(gridDim.x) * blockDim.x;
     if (p.vec) {
@@ -471,6 +485,14 @@ int b200_binary(b200_ctx* ctx, int op, const void* a, const int64_t* a_shape, co
     for (int i = 0; i < 4; ++i) same = same && ad[i] == bd[i];
     if (same && (p.n % 8 == 0) && al16(a) && al16(b) && al16(out)) {
         binary_flat_kernel<<<grid_for(ctx, p.n / 8), kThreads, 0, ctx->pick(stream)>>>(p.a, p.b, p.out, p.n / 8, op);
+        B200_CUDA_TRY(cudaGetLastError());
+        return B200_OK;
+    }
+    const bool b_is_row = bd[0] == 1 && bd[1] == 1 && bd[2] == 1 && bd[3] == p.od[3] && ad[0] == p.od[0] &&
+                          ad[1] == p.od[1] && ad[2] == p.od[2] && ad[3] == p.od[3];
+    if (b_is_row && (p.od[3] % 8 == 0) && al16(a) && al16(b) && al16(out) && p.od[3] / 8 < (1ll << 31)) {
+        binary_rowbcast_kernel<<<grid_for(ctx, p.n / 8), kThreads, 0, ctx->pick(stream)>>>(p.a, p.b, p.out, p.n / 8,
+                                                                                          static_cast<int>(p.od[3] / 8), op);
         B200_CUDA_TRY(cudaGetLastError());
         return B200_OK;
     }

@@ -110,6 +110,7 @@ struct RowParams {
     float* row_loss;          // OP_CROSS_ENTROPY: per-row loss (fp32) or nullptr
     float* loss_sum;          // OP_CROSS_ENTROPY: atomically accumulated alpha-scaled loss, or nullptr
     int vec0, vec1, veco;     // 16-byte access legal for in0 / in1 / out
+    int stage_row;            // block kernel: keep the row in shared memory between the two passes
 };
 
 __device__ __forceinline__ int visible_cols(const RowParams& p, int r) {
@@ -218,20 +219,165 @@ __global__ void __launch_bounds__(kBlock) row_warp_kernel(const RowParams p) {
     }
 }
 
+// ---- persistent, software-pipelined form of the warp-per-row kernel ------------------------------------
+// Each warp walks rows r, r + W, r + 2W, ...; the raw 16-byte vectors of the NEXT row are requested before the current
+// row is reduced, so every warp always has a row in flight (the plain kernel has nothing in flight while it reduces).
+// Needs 16-byte aligned rows and cols % 8 == 0. A causal row only loads the vectors that contain visible columns.
+__device__ __forceinline__ void unpack_raw(const uint4& u, float (&f)[8]) {
+    const uint32_t w[4] = {u.x, u.y, u.z, u.w};
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        f[2 * i] = __uint_as_float(w[i] << 16);
+        f[2 * i + 1] = __uint_as_float(w[i] & 0xffff0000u);
+    }
+}
+
+template <int VPL, int OP>
+__global__ void __launch_bounds__(kBlock) row_warp_pipe_kernel(const RowParams p) {
+    constexpr bool kTwoInputs = (OP == OP_SOFTMAX_BW || OP == OP_LOG_SOFTMAX_BW);
+    const int lane = threadIdx.x & 31;
+    const int total_warps = gridDim.x * (kBlock / kWarp);
+    int r = blockIdx.x * (kBlock / kWarp) + (threadIdx.x >> 5);
+    uint4 raw0[VPL], raw1[VPL];
+    auto fetch = [&](int row, uint4 (&d0)[VPL], uint4 (&d1)[VPL]) {
+        const int lim = kTwoInputs ? p.cols : visible_cols(p, row);
+        const uint4* s0 = reinterpret_cast<const uint4*>(p.in0 + static_cast<size_t>(row) * p.ld0);
+        const uint4* s1 = kTwoInputs ? reinterpret_cast<const uint4*>(p.in1 + static_cast<size_t>(row) * p.ld1) : nullptr;
+#pragma unroll
+        for (int j = 0; j < VPL; ++j) {
+            const int v = j * kWarp + lane;
+            if (v * 8 < lim) {
+                d0[j] = s0[v];
+                if (kTwoInputs) d1[j] = s1[v];
+            } else {
+                d0[j] = make_uint4(0, 0, 0, 0);
+                if (kTwoInputs) d1[j] = make_uint4(0, 0, 0, 0);
+            }
+        }
+    };
+    if (r < p.rows) fetch(r, raw0, raw1);
+    while (r < p.rows) {
+        const int r_next = r + total_warps;
+        uint4 nxt0[VPL], nxt1[VPL];
+        if (r_next < p.rows) fetch(r_next, nxt0, nxt1);
+        float a[VPL][8];
+        if (OP == OP_SOFTMAX || OP == OP_LOG_SOFTMAX || OP == OP_CROSS_ENTROPY) {
+            const int vis = visible_cols(p, r);
+            const float scale = (OP == OP_SOFTMAX) ? p.alpha : 1.0f;
+            float m = -FLT_MAX;
+#pragma unroll
+            for (int j = 0; j < VPL; ++j) {
+                const int c = (j * kWarp + lane) * 8;
+                unpack_raw(raw0[j], a[j]);
+#pragma unroll
+                for (int i = 0; i < 8; ++i) {
+                    a[j][i] = (c + i < vis) ? a[j][i] * scale : -FLT_MAX;
+                    m = fmaxf(m, a[j][i]);
+                }
+            }
+            m = warp_max(m);
+            float s = 0.0f;
+#pragma unroll
+            for (int j = 0; j < VPL; ++j)
+#pragma unroll
+                for (int i = 0; i < 8; ++i) {
+                    const float e = (a[j][i] == -FLT_MAX) ? 0.0f : __expf(a[j][i] - m);
+                    if (OP == OP_LOG_SOFTMAX) a[j][i] -= m; else a[j][i] = e;
+                    s += e;
+                }
+            s = warp_sum(s);
+            if (OP == OP_SOFTMAX || OP == OP_LOG_SOFTMAX) {
+                const float inv = 1.0f / s, ls = __logf(s);
+                uint4* y = reinterpret_cast<uint4*>(p.out + static_cast<size_t>(r) * p.ldo);
+#pragma unroll
+                for (int j = 0; j < VPL; ++j) {
+                    const int v = j * kWarp + lane;
+                    if (v * 8 >= p.cols) continue;
+#pragma unroll
+                    for (int i = 0; i < 8; ++i) a[j][i] = (OP == OP_SOFTMAX) ? a[j][i] * inv : a[j][i] - ls;
+                    y[v] = make_uint4(pack_bf16x2(a[j][0], a[j][1]), pack_bf16x2(a[j][2], a[j][3]),
+                                      pack_bf16x2(a[j][4], a[j][5]), pack_bf16x2(a[j][6], a[j][7]));
+                }
+            } else {  // cross-entropy
+                const int label = static_cast<int>(p.labels[r]);
+                const float inv = 1.0f / s;
+                float picked = 0.0f;
+                uint4* y = p.out ? reinterpret_cast<uint4*>(p.out + static_cast<size_t>(r) * p.ldo) : nullptr;
+#pragma unroll
+                for (int j = 0; j < VPL; ++j) {
+                    const int v = j * kWarp + lane;
+                    const int c = v * 8;
+#pragma unroll
+                    for (int i = 0; i < 8; ++i) {
+                        const float prob = a[j][i] * inv;
+                        if (c + i == label) picked = prob;
+                        a[j][i] = (prob - ((c + i == label) ? 1.0f : 0.0f)) * p.alpha;
+                    }
+                    if (y != nullptr && c < p.cols)
+                        y[v] = make_uint4(pack_bf16x2(a[j][0], a[j][1]), pack_bf16x2(a[j][2], a[j][3]),
+                                          pack_bf16x2(a[j][4], a[j][5]), pack_bf16x2(a[j][6], a[j][7]));
+                }
+                picked = warp_sum(picked);
+                if (lane == 0) {
+                    const float loss = -__logf(fmaxf(picked, 1e-38f));
+                    if (p.row_loss) p.row_loss[r] = loss;
+                    if (p.loss_sum) atomicAdd(p.loss_sum, loss * p.alpha);
+                }
+            }
+        } else {
+            float b[VPL][8];
+            float dot = 0.0f;
+#pragma unroll
+            for (int j = 0; j < VPL; ++j) {
+                unpack_raw(raw0[j], a[j]);
+                unpack_raw(raw1[j], b[j]);
+#pragma unroll
+                for (int i = 0; i < 8; ++i) dot += (OP == OP_SOFTMAX_BW) ? a[j][i] * b[j][i] : a[j][i];
+            }
+            dot = warp_sum(dot);
+            uint4* y = reinterpret_cast<uint4*>(p.out + static_cast<size_t>(r) * p.ldo);
+#pragma unroll
+            for (int j = 0; j < VPL; ++j) {
+                const int v = j * kWarp + lane;
+                if (v * 8 >= p.cols) continue;
+#pragma unroll
+                for (int i = 0; i < 8; ++i)
+                    a[j][i] = (OP == OP_SOFTMAX_BW) ? p.alpha * b[j][i] * (a[j][i] - dot) : a[j][i] - __expf(b[j][i]) * dot;
+                y[v] = make_uint4(pack_bf16x2(a[j][0], a[j][1]), pack_bf16x2(a[j][2], a[j][3]),
+                                  pack_bf16x2(a[j][4], a[j][5]), pack_bf16x2(a[j][6], a[j][7]));
+            }
+        }
+#pragma unroll
+        for (int j = 0; j < VPL; ++j) {
+            raw0[j] = nxt0[j];
+            if (kTwoInputs) raw1[j] = nxt1[j];
+        }
+        r = r_next;
+    }
+}
+
 // ---- one CTA per row, any length: online max/sum pass, then a write pass (re-read hits L2) -----------
 template <int OP>
-__global__ void __launch_bounds__(kBlock) row_block_kernel(const RowParams p) {
-    __shared__ float sh[kBlock / kWarp];
+__global__ void __launch_bounds__(1024) row_block_kernel(const RowParams p) {
+    __shared__ float sh[32];
+    extern __shared__ uint4 srow[];  // p.stage_row: the row's full 16-byte vectors, so that HBM is read once
     const int r = blockIdx.x;
     const __nv_bfloat16* x0 = p.in0 + static_cast<size_t>(r) * p.ld0;
     const int nvec = (p.cols + 7) / 8;
     if (OP == OP_SOFTMAX || OP == OP_LOG_SOFTMAX || OP == OP_CROSS_ENTROPY) {
         const int vis = visible_cols(p, r);
         const float scale = (OP == OP_SOFTMAX) ? p.alpha : 1.0f;
+        const bool stage = p.stage_row != 0;
         float m = -FLT_MAX, s = 0.0f;  // running max and sum of exp(x - m)
-        for (int v = threadIdx.x; v < nvec; v += kBlock) {
+        for (int v = threadIdx.x; v < nvec; v += blockDim.x) {
             float f[8];
-            load8(x0, v * 8, vis, p.vec0 != 0, -FLT_MAX, f);
+            if (stage && v * 8 + 8 <= vis) {
+                const uint4 u = reinterpret_cast<const uint4*>(x0)[v];
+                srow[v] = u;
+                unpack_raw(u, f);
+            } else {
+                load8(x0, v * 8, vis, p.vec0 != 0, -FLT_MAX, f);
+            }
             float lm = m;
 #pragma unroll
             for (int i = 0; i < 8; ++i) {
@@ -252,9 +398,13 @@ __global__ void __launch_bounds__(kBlock) row_block_kernel(const RowParams p) {
         const int label = (OP == OP_CROSS_ENTROPY) ? static_cast<int>(p.labels[r]) : -1;
         float picked = 0.0f;
         __nv_bfloat16* y = p.out ? p.out + static_cast<size_t>(r) * p.ldo : nullptr;
-        for (int v = threadIdx.x; v < nvec; v += kBlock) {
+        for (int v = threadIdx.x; v < nvec; v += blockDim.x) {
             float f[8];
-            load8(x0, v * 8, vis, p.vec0 != 0, -FLT_MAX, f);
+            if (stage && v * 8 + 8 <= vis) {
+                unpack_raw(srow[v], f);  // written by this same thread in the first pass
+            } else {
+                load8(x0, v * 8, vis, p.vec0 != 0, -FLT_MAX, f);
+            }
 #pragma unroll
             for (int i = 0; i < 8; ++i) {
                 const int c = v * 8 + i;
@@ -283,7 +433,7 @@ __global__ void __launch_bounds__(kBlock) row_block_kernel(const RowParams p) {
     } else {
         const __nv_bfloat16* x1 = p.in1 + static_cast<size_t>(r) * p.ld1;
         float dot = 0.0f;
-        for (int v = threadIdx.x; v < nvec; v += kBlock) {
+        for (int v = threadIdx.x; v < nvec; v += blockDim.x) {
             float a[8], b[8];
             load8(x0, v * 8, p.cols, p.vec0 != 0, 0.0f, a);
             if (OP == OP_SOFTMAX_BW) load8(x1, v * 8, p.cols, p.vec1 != 0, 0.0f, b);
@@ -292,7 +442,7 @@ __global__ void __launch_bounds__(kBlock) row_block_kernel(const RowParams p) {
         }
         dot = block_sum(dot, sh);
         __nv_bfloat16* y = p.out + static_cast<size_t>(r) * p.ldo;
-        for (int v = threadIdx.x; v < nvec; v += kBlock) {
+        for (int v = threadIdx.x; v < nvec; v += blockDim.x) {
             float a[8], b[8];
             load8(x0, v * 8, p.cols, p.vec0 != 0, 0.0f, a);
             load8(x1, v * 8, p.cols, p.vec1 != 0, 0.0f, b);
@@ -307,7 +457,22 @@ __global__ void __launch_bounds__(kBlock) row_block_kernel(const RowParams p) {
 template <int OP>
 int launch_row_op(const RowParams& p, cudaStream_t stream) {
     if (p.rows == 0 || p.cols == 0) return B200_OK;
-    if (p.cols <= 1024) {
+    constexpr bool kTwoInputs = (OP == OP_SOFTMAX_BW || OP == OP_LOG_SOFTMAX_BW);
+    const bool pipe_ok = p.vec0 && (p.out == nullptr || p.veco) && (!kTwoInputs || p.vec1) && (p.cols % 8) == 0 &&
+                         p.rows >= 4096;
+    if (p.cols <= 1024 && pipe_ok) {
+        // persistent warps: enough CTAs to fill every SM several times over, each warp streaming many rows
+        int dev = 0, sms = 148;
+        cudaGetDevice(&dev);
+        cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+        const int blocks = std::min((p.rows + (kBlock / kWarp) - 1) / (kBlock / kWarp), sms * 6);
+        if (p.cols <= 256)
+            row_warp_pipe_kernel<1, OP><<<blocks, kBlock, 0, stream>>>(p);
+        else if (p.cols <= 512)
+            row_warp_pipe_kernel<2, OP><<<blocks, kBlock, 0, stream>>>(p);
+        else
+            row_warp_pipe_kernel<4, OP><<<blocks, kBlock, 0, stream>>>(p);
+    } else if (p.cols <= 1024) {
         const int blocks = (p.rows + (kBlock / kWarp) - 1) / (kBlock / kWarp);
         if (p.cols <= 256)
             row_warp_kernel<1, OP><<<blocks, kBlock, 0, stream>>>(p);
@@ -316,7 +481,15 @@ int launch_row_op(const RowParams& p, cudaStream_t stream) {
         else
             row_warp_kernel<4, OP><<<blocks, kBlock, 0, stream>>>(p);
     } else {
-        row_block_kernel<OP><<<p.rows, kBlock, 0, stream>>>(p);
+        RowParams q = p;
+        const size_t row_bytes = static_cast<size_t>((p.cols + 7) / 8) * 16;
+        constexpr bool kForward = (OP == OP_SOFTMAX || OP == OP_LOG_SOFTMAX || OP == OP_CROSS_ENTROPY);
+        q.stage_row = (kForward && p.vec0 && row_bytes <= 110 * 1024) ? 1 : 0;  // two CTAs per SM still fit
+        const size_t smem = q.stage_row ? row_bytes : 0;
+        if (smem > 48 * 1024)  // per device function and device; cheap enough to repeat
+            B200_CUDA_TRY(cudaFuncSetAttribute(row_block_kernel<OP>, cudaFuncAttributeMaxDynamicSharedMemorySize, 112 * 1024));
+        // a staged row allows two CTAs per SM: give each 1024 threads so the SM still has 64 warps in flight
+        row_block_kernel<OP><<<p.rows, q.stage_row ? 1024 : kBlock, smem, stream>>>(q);
     }
     B200_CUDA_TRY(cudaGetLastError());
     return B200_OK;
@@ -336,7 +509,7 @@ int check_rows(const char* who, const void* a, long long lda, long long rows, lo
 // ---- LayerNorm -------------------------------------------------------------------------------------
 // Forward: one warp per row for cols <= 2048 (row in registers), else one CTA per row.
 template <int VPL>
-__global__ void __launch_bounds__(kBlock) layernorm_fw_warp_kernel(const __nv_bfloat16* x, long long ldx,
+__global__ void __launch_bounds__(kBlock, VPL <= 4 ? 4 : 2) layernorm_fw_warp_kernel(const __nv_bfloat16* x, long long ldx,
                                                                     const __nv_bfloat16* gamma, const __nv_bfloat16* beta,
                                                                     __nv_bfloat16* y, long long ldy, float* mean_out,
                                                                     float* rstd_out, int rows, int cols, float eps, int vx,
@@ -428,7 +601,7 @@ __global__ void __launch_bounds__(kBlock) layernorm_fw_block_kernel(const __nv_b
 // Backward, input gradient: dx = rstd * (g - mean(g) - xhat * mean(g * xhat)), g = dy * gamma. One warp per row
 // (cols <= 2048) or one CTA per row.
 template <int VPL>
-__global__ void __launch_bounds__(kBlock) layernorm_bw_dx_warp_kernel(const __nv_bfloat16* dy, long long lddy,
+__global__ void __launch_bounds__(kBlock, VPL <= 4 ? 3 : 2) layernorm_bw_dx_warp_kernel(const __nv_bfloat16* dy, long long lddy,
                                                                        const __nv_bfloat16* x, long long ldx,
                                                                        const __nv_bfloat16* gamma, const float* mean,
                                                                        const float* rstd, __nv_bfloat16* dx, long long lddx,
