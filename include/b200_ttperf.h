@@ -148,6 +148,12 @@ typedef struct b200_gemm_desc {
 /* Fills a descriptor with defaults: no transposes, batch 1, alpha 1, bf16 output, HIFI4, AUTO. */
 void b200_gemm_desc_init(b200_gemm_desc* desc);
 int b200_gemm(b200_ctx* ctx, const b200_gemm_desc* desc, void* stream);
+/* The same product with A, B and C in HOST memory (pinned memory gives full PCIe speed) — the path a reference program
+ * takes from Tensor::from_vector / to_device through ttnn::matmul to .cpu() (bench/metal/matmul_tensor_parallel.cpp:
+ * 56-93), as one pipelined call: B is uploaded once, A in `panels` row panels (0 = default 8), each panel's GEMM starts
+ * when its rows have landed and its rows of C are downloaded while the next panel computes. Batch 1. Blocks until C is
+ * complete in host memory. Device staging buffers are kept in the context and grown on demand. */
+int b200_matmul_host(b200_ctx* ctx, const b200_gemm_desc* desc_with_host_pointers, int panels);
 /* Bytes of context scratch the split-K path of this descriptor will use (0 when it does not split). */
 int b200_gemm_scratch_bytes(b200_ctx* ctx, const b200_gemm_desc* desc, size_t* out_bytes);
 

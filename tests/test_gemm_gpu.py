@@ -236,3 +236,21 @@ def test_full_size_8192_linearity_and_row_sample(pkg, ctx, stream, ta, tb):
     # scaling A by 2 is exact in bf16, so the product must be exactly doubled
     assert torch.equal(c2.float(), c1.float() * 2)
     del a2
+
+
+@pytest.mark.parametrize("M,N,K,ta,tb", [(1024, 512, 384, False, False), (1000, 520, 776, False, True),
+                                          (2048, 264, 512, True, False), (300, 72, 40, False, False)])
+def test_matmul_host_buffers_pipelined(pkg, ctx, M, N, K, ta, tb):
+    """b200_matmul_host: operands and result in host memory (pinned or pageable), upload / compute / download
+    pipelined over row panels — the from_vector -> to_device -> matmul -> cpu() path of a reference program."""
+    a, b = operands(M, N, K, ta, tb, seed=31)
+    a_h = torch.from_numpy(a).bfloat16().pin_memory()
+    b_h = torch.from_numpy(b).bfloat16()                     # pageable on purpose
+    c_h = torch.full((M, N), float("nan"), dtype=torch.bfloat16).pin_memory()
+    d = ctx.gemm_desc(a_h, b_h, c_h, M, N, K, transpose_a=ta, transpose_b=tb)
+    for panels in (0, 3):
+        c_h.fill_(float("nan"))
+        ctx.matmul_host(d, panels)
+        got = c_h.float().numpy()
+        assert not np.isnan(got).any()
+        assert mo.rel_frobenius(got, mo.matmul(a, b, ta, tb)) <= TOL

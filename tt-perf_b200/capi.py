@@ -74,6 +74,7 @@ SIGNATURES = {
     "b200_trace_release": (C.c_int, [C.c_void_p, C.c_uint32]),
     "b200_gemm_desc_init": (None, [C.POINTER(GemmDesc)]),
     "b200_gemm": (C.c_int, [C.c_void_p, C.POINTER(GemmDesc), C.c_void_p]),
+    "b200_matmul_host": (C.c_int, [C.c_void_p, C.POINTER(GemmDesc), C.c_int]),
     "b200_gemm_scratch_bytes": (C.c_int, [C.c_void_p, C.POINTER(GemmDesc), C.POINTER(C.c_size_t)]),
     "b200_gemm_static_scratch": (C.c_int, [C.c_int, C.POINTER(GemmDesc), C.c_void_p]),
     "b200_ipc_get_handle": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p]),
@@ -256,6 +257,10 @@ class Context:
         """Split-K matmul whose partial sums use the library's fixed 32 MiB array: no device allocation at
         call time (see b200_gemm_static_scratch in the header). `stream` is required."""
         check(lib().b200_gemm_static_scratch(self.device, C.byref(desc), C.c_void_p(ptr(stream))))
+
+    def matmul_host(self, desc: GemmDesc, panels: int = 0) -> None:
+        """The product with HOST operand / result pointers in `desc`: pipelined upload, compute and download."""
+        check(lib().b200_matmul_host(self._h, C.byref(desc), panels))
 
     def gemm_scratch_bytes(self, desc: GemmDesc) -> int:
         n = C.c_size_t()

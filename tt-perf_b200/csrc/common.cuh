@@ -63,6 +63,10 @@ struct b200_ctx {
     void* d_scratch = nullptr;         // split-K partial sums and other per-call scratch
     size_t scratch_bytes = 0;
     b200::EncodeTiledFn encode_tiled = nullptr;
+    // b200_matmul_host: device staging for host operands and the two copy streams of its pipeline
+    void* d_stage[3] = {nullptr, nullptr, nullptr};
+    size_t stage_bytes[3] = {0, 0, 0};
+    cudaStream_t copy_in = nullptr, copy_out = nullptr;
     std::mutex mu;
 
     cudaStream_t pick(void* s) const { return s ? static_cast<cudaStream_t>(s) : stream; }

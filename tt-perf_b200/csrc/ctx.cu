@@ -115,6 +115,10 @@ int b200_ctx_destroy(b200_ctx* ctx) {
     DeviceScope scope(ctx->device);
     cudaDeviceSynchronize();
     pool_destroy(ctx);
+    for (int i = 0; i < 3; ++i)
+        if (ctx->d_stage[i]) cudaFree(ctx->d_stage[i]);
+    if (ctx->copy_in) cudaStreamDestroy(ctx->copy_in);
+    if (ctx->copy_out) cudaStreamDestroy(ctx->copy_out);
     if (ctx->d_scratch) cudaFree(ctx->d_scratch);
     if (ctx->d_status) cudaFree(ctx->d_status);
     if (ctx->stream) cudaStreamDestroy(ctx->stream);
