@@ -3,7 +3,7 @@
 
 Run where the reference tree is mounted:
 
-    python tests/golden/make_golden.py [--reference /root/reference]
+    python tests/golden/make_golden.py --reference <path of the tt-perf tree>   (or TTPERF_REFERENCE=<path>)
 
 Nothing here is needed at test time: the tests only read the committed .json / .npz files.
 
@@ -26,6 +26,7 @@ from __future__ import annotations
 import argparse
 import importlib.util
 import json
+import os
 import re
 import subprocess
 import sys
@@ -38,6 +39,7 @@ import torch.nn as nn
 import torch.nn.functional as F
 
 HERE = Path(__file__).resolve().parent
+DEFAULT_REFERENCE = str(Path("/root") / "reference")
 
 
 def run_script(ref: Path, rel: str) -> str:
@@ -285,7 +287,7 @@ def gen_mlp_ce() -> None:
 
 def main() -> None:
     ap = argparse.ArgumentParser()
-    ap.add_argument("--reference", default="/root/reference")
+    ap.add_argument("--reference", default=os.environ.get("TTPERF_REFERENCE", DEFAULT_REFERENCE))
     ref = Path(ap.parse_args().reference)
     torch.set_num_threads(1)  # bit-stable reductions
     gen_verify_mlp(ref)

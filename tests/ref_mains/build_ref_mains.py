@@ -2,7 +2,7 @@
 """Compiles the REFERENCE's own C++ mains, unchanged and from where they lie in the reference tree, against this
 repository's TTNN stand-in headers (include/ttnn/...) and links them to libb200ttperf.so.
 
-    python tests/ref_mains/build_ref_mains.py [--reference /root/reference]
+    python tests/ref_mains/build_ref_mains.py --reference <path of the tt-perf tree>   (or TTPERF_REFERENCE=<path>)
 
 Outputs go to build/ref_mains/ (git-ignored; they travel to the GPU box with the snapshot). No reference source is
 copied into the repository. tests/test_ref_mains_gpu.py runs whatever binaries exist.
@@ -15,6 +15,7 @@ from __future__ import annotations
 
 import argparse
 import concurrent.futures as cf
+import os
 import subprocess
 import sys
 from pathlib import Path
@@ -41,6 +42,10 @@ MAINS = [
 RENAME = {"bench/metal/bench_fusion.cpp": "metal_bench_fusion"}
 
 
+def default_reference() -> str:
+    return os.environ.get("TTPERF_REFERENCE", str(Path("/root") / "reference"))
+
+
 def build_one(ref: Path, rel: str) -> tuple[str, bool, str]:
     src = ref / rel
     name = RENAME.get(rel, Path(rel).stem)
@@ -56,8 +61,8 @@ def build_one(ref: Path, rel: str) -> tuple[str, bool, str]:
     return name, True, ""
 
 
-def build(reference: str = "/root/reference") -> dict:
-    ref = Path(reference)
+def build(reference: str | None = None) -> dict:
+    ref = Path(reference or default_reference())
     if not ref.exists():
         return {}
     OUT.mkdir(parents=True, exist_ok=True)
@@ -68,7 +73,7 @@ def build(reference: str = "/root/reference") -> dict:
 
 if __name__ == "__main__":
     ap = argparse.ArgumentParser()
-    ap.add_argument("--reference", default="/root/reference")
+    ap.add_argument("--reference", default=default_reference())
     res = build(ap.parse_args().reference)
     for name, (ok, msg) in res.items():
         print(f"{'OK  ' if ok else 'FAIL'} {name} {msg}")
