@@ -182,21 +182,33 @@ def workload_config(n: int) -> dict:
             "l2_policy": "inputs larger than the 126 MiB L2; no flush between steps"}
 
 
-def gpt2_train_bench(steps: int = 10, warmup: int = 3) -> dict:
-    """GPT-2-small-shaped training step (12 layers, d_model 768, 12 heads, d_ff 3072, seq 1024, batch 8, vocab 50257,
-    random N(0, 0.02) weights, uniform random token ids, Adam lr 3e-4 betas (0.9, 0.95)): forward, cross-entropy,
-    backward and the Adam update, recorded once as a trace (CUDA graph) and replayed, as the reference's traced
-    executor does (bench/autograd/bench_gpt2_full.cpp). Every kernel comes from the C ABI; the host side is
-    tt-perf_b200/nn.py. Returns tokens/s and ms/step."""
+class _DevBytes:
+    """CUDA array interface over a raw device pointer, so that torch.distributed (NCCL) can all-reduce buffers that
+    the library's pool owns."""
+
+    def __init__(self, ptr: int, nbytes: int):
+        self.__cuda_array_interface__ = {"shape": (nbytes,), "typestr": "|u1", "data": (ptr, False), "version": 3}
+
+
+def gpt2_train_bench(steps: int = 10, warmup: int = 3, device: int = 0, rank: int = 0, world: int = 1) -> dict:
+    """GPT-2-small-shaped training step (12 layers, d_model 768, 12 heads, d_ff 3072, seq 1024, batch 8 per GPU, vocab
+    50257, random N(0, 0.02) weights, uniform random token ids, Adam lr 3e-4 betas (0.9, 0.95)): forward, cross-entropy,
+    backward and the Adam update. Every kernel comes from the C ABI; the host side is tt-perf_b200/nn.py.
+
+    One GPU: the whole step is recorded once as a trace (CUDA graph) and replayed, as the reference's traced executor
+    does (bench/autograd/bench_gpt2_full.cpp). N GPUs (data parallel, weak scaling): each rank replays a trace of
+    forward + backward on its own batch that also packs the gradients into two buckets, the buckets are averaged with
+    two NCCL all-reduces (through torch.distributed), then a second trace applies Adam from the buckets. Returns
+    whole-job tokens/s and ms/step."""
     import numpy as np
     from __graft_entry__ import load_package
     pkg = load_package()
-    ctx = pkg.Context(0)
+    ctx = pkg.Context(device)
     DT = pkg.DeviceTensor
     L, D, H, S, V, B = 12, 768, 12, 1024, 50257, 8
     model = pkg.nn.GPT2(ctx, layers=L, d_model=D, heads=H, seq=S, vocab=V)
-    model.init_random(42)
-    rng = np.random.default_rng(42)
+    model.init_random(42)                               # same weights on every rank
+    rng = np.random.default_rng(42 + rank)              # a different batch per rank
     ids = rng.integers(0, V, (B, S)).astype(np.uint32)
     targets = np.roll(ids, -1, axis=1)
     idd = DT.from_numpy(ctx, ids, pkg.U32)
@@ -211,22 +223,89 @@ def gpt2_train_bench(steps: int = 10, warmup: int = 3) -> dict:
     losses = []
     for _ in range(max(2, warmup)):          # eager steps: allocate the pool and scratch, check the loss moves
         losses.append(float(step().numpy()[0]))
-    tid = ctx.trace_begin()
-    loss = step()
-    ctx.trace_end(tid)
-    ctx.trace_execute(tid)
-    ctx.synchronize()
-    t0 = time.perf_counter()
-    for _ in range(steps):
+    if world == 1:
+        tid = ctx.trace_begin()
+        loss = step()
+        ctx.trace_end(tid)
         ctx.trace_execute(tid)
-    ctx.synchronize()
-    dt = (time.perf_counter() - t0) / steps
+        ctx.synchronize()
+        t0 = time.perf_counter()
+        for _ in range(steps):
+            ctx.trace_execute(tid)
+        ctx.synchronize()
+        dt = (time.perf_counter() - t0) / steps
+        executor = "trace replay (CUDA graph)"
+        traces = [tid]
+    else:
+        import torch
+        import torch.distributed as dist
+        # Gradients are packed into one bf16 and one fp32 bucket inside the forward+backward trace, so that the
+        # exchange is two large all-reduces; Adam then reads its gradients straight from the buckets.
+        c = pkg.capi
+
+        def bucket(pairs, dtype):
+            offs, total = [], 0
+            for _, g in pairs:
+                offs.append(total)
+                total += (g.numel + 7) // 8 * 8
+            return DT.zeros(ctx, (total,), dtype), offs
+
+        t_fb = ctx.trace_begin()
+        loss, grads = model.forward_backward(idd, tgd, pos)
+        bf, f32 = model._flat(grads)
+        ctx.trace_end(t_fb)
+        ctx.trace_release(t_fb)
+        flat_bf, off_bf = bucket(bf, pkg.BF16)
+        flat_f32, off_f32 = bucket(f32, pkg.F32)
+        del loss, grads, bf, f32
+        t_fb = ctx.trace_begin()
+        loss, grads = model.forward_backward(idd, tgd, pos)
+        bf, f32 = model._flat(grads)
+        slices_bf, slices_f32 = [], []
+        for (_, g), o in zip(bf, off_bf):
+            sl = DT(ctx, g.shape, pkg.BF16, ptr=flat_bf.ptr + 2 * o, owner=flat_bf)
+            ctx.unary(c.U_COPY, g, sl, g.numel)
+            slices_bf.append(sl)
+        for (_, g), o in zip(f32, off_f32):
+            sl = DT(ctx, g.shape, pkg.F32, ptr=flat_f32.ptr + 4 * o, owner=flat_f32)
+            ctx.unary(c.U_COPY, g, sl, 2 * g.numel)          # a pure copy: fp32 moved as pairs of 16-bit words
+            slices_f32.append(sl)
+        ctx.trace_end(t_fb)
+        t_opt = ctx.trace_begin()
+        model.opt[0].step(slices_bf)
+        model.opt[1].step(slices_f32)
+        ctx.trace_end(t_opt)
+        views = [torch.as_tensor(_DevBytes(flat_bf.ptr, flat_bf.nbytes), device="cuda").view(torch.bfloat16),
+                 torch.as_tensor(_DevBytes(flat_f32.ptr, flat_f32.nbytes), device="cuda").view(torch.float32)]
+
+        def dp_step():
+            ctx.trace_execute(t_fb)
+            ctx.synchronize()                                  # gradients are complete before NCCL reads them
+            for v in views:
+                dist.all_reduce(v, op=dist.ReduceOp.AVG)
+            torch.cuda.current_stream().synchronize()
+            ctx.trace_execute(t_opt)
+
+        dp_step()
+        ctx.synchronize()
+        dist.barrier()
+        t0 = time.perf_counter()
+        for _ in range(steps):
+            dp_step()
+        ctx.synchronize()
+        t = torch.tensor([(time.perf_counter() - t0) / steps], device="cuda")
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        dt = t.item()
+        executor = "two traces (forward+backward+gradient packing, Adam) with two bucketed NCCL all-reduces between them"
+        traces = [t_fb, t_opt]
     final = float(loss.numpy()[0])
-    ctx.trace_release(tid)
+    for t in traces:
+        ctx.trace_release(t)
     flops = 3 * (12 * 24 * B * S * D * D + 2 * B * S * D * V) + 12 * 12 * B * H * 64 * (S * (S + 1) // 2)
-    out = {"metric": "GPT-2-small train tokens/s", "tokens_per_s": B * S / dt, "ms_per_step": dt * 1e3,
-           "model_tflops_per_s": flops / dt / 1e12, "params": model.num_params(), "batch": B, "seq": S,
-           "first_losses": losses, "loss_after_replays": final, "executor": "trace replay (CUDA graph)",
+    out = {"metric": "GPT-2-small train tokens/s", "tokens_per_s": world * B * S / dt, "ms_per_step": dt * 1e3,
+           "model_tflops_per_s": world * flops / dt / 1e12, "params": model.num_params(), "batch_per_gpu": B, "seq": S,
+           "n_gpus": world, "scaling": "weak (data parallel)" if world > 1 else None, "first_losses": losses,
+           "loss_after_replays": final, "executor": executor,
            "data": "synthetic: uniform token ids, targets = ids shifted by one"}
     ctx.close()
     return out
@@ -424,6 +503,13 @@ def run_b200_distributed(args) -> None:
                "d2h_bytes_per_step": M * N * 2, "ms_per_step": t.item() * 1e3, "steps": e2e_steps,
                "note": "per rank: A and the B shard host->device, fused GEMM + all-gather, the full C device->host"}
 
+    mm.close()
+    ctx.close()
+    gpt2 = None
+    if not args.quick:
+        del a, b, b_full
+        torch.cuda.empty_cache()
+        gpt2 = gpt2_train_bench(steps=5, warmup=2, device=local_rank, rank=rank, world=world)
     if rank == 0:
         peaks = load_peaks()
         peak = peaks["bf16_tflops"] * world
@@ -452,13 +538,12 @@ def run_b200_distributed(args) -> None:
             cpu = cpu_matmul_baseline(M, N, K)
             cpu.pop("seconds", None)
             line["cpu_baseline"] = cpu
+            line["gpt2_small_train"] = gpt2
         sys.stdout.flush()
         os.dup2(real_stdout, 1)
         print(json.dumps(line), flush=True)
         os.dup2(2, 1)
     dist.barrier()
-    mm.close()
-    ctx.close()
     dist.destroy_process_group()
 
 
