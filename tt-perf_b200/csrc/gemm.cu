@@ -127,7 +127,7 @@ int b200_gemm(b200_ctx* ctx, const b200_gemm_desc* d, void* stream_v) {
         return fail(B200_ERR_INVALID_ARG, "b200_gemm: tcgen05 path requested but %s", why);
     if (d->algo == B200_GEMM_SIMT || !eligible) return launch_gemm_simt(ctx, *d, stream);
     const int splits = gemm_choose_split_k(ctx, *d);
-    if (splits == 1 && pair_kernel_enabled() && gemm_pair_eligible(ctx, *d, nullptr))
+    if (splits == 1 && pair_kernel_enabled() && gemm_tuned_block_n() == 0 && gemm_pair_eligible(ctx, *d, nullptr))
         return launch_gemm_tcgen05_pair(ctx, *d, stream);
     return launch_gemm_tcgen05(ctx, *d, splits, stream);
 }

@@ -146,5 +146,7 @@ bool gemm_tcgen05_eligible(const b200_gemm_desc& d, const char** why);
 int gemm_choose_split_k(const b200_ctx* ctx, const b200_gemm_desc& d);
 // N-tile width (64, 128 or 256) the tcgen05 path uses for this problem.
 int gemm_choose_block_n(const b200_ctx* ctx, const b200_gemm_desc& d);
+// Non-zero while a tuning sweep (B200_GEMM_TUNE=1, B200_GEMM_BLOCK_N) pins the tile width of the single-CTA kernel.
+int gemm_tuned_block_n();
 
 }  // namespace b200

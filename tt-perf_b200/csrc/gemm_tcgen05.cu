@@ -502,38 +502,90 @@ bool gemm_tcgen05_eligible(const b200_gemm_desc& d, const char** why) {
     return w == nullptr;
 }
 
-int gemm_choose_block_n(const b200_ctx* ctx, const b200_gemm_desc& d) {
-    if (d.N <= 64) return 64;
-    if (d.N <= 128) return 128;
-    // Prefer the 256-wide tile (best operand reuse) unless it leaves most SMs idle and a
-    // narrower tile fills more of them.
-    const long long m_tiles = (d.M + BM - 1) / BM;
-    const long long t256 = d.batch * m_tiles * ((d.N + 255) / 256);
-    if (t256 >= ctx->sm_count) return 256;
-    const long long t128 = d.batch * m_tiles * ((d.N + 127) / 128);
-    if (t128 > t256 && (d.N % 256) != 0 && (d.N % 256) <= 128) return 128;
-    return (t256 * 2 <= ctx->sm_count && t128 > t256) ? 128 : 256;
+namespace {
+
+struct GemmPlan {
+    int bn;
+    int splits;
+};
+
+// Normalises a requested K-slice count so that every slice gets at least one K block.
+int normalise_splits(int want, int num_kb) {
+    want = std::max(1, std::min(want, num_kb));
+    const int per = (num_kb + want - 1) / want;
+    return (num_kb + per - 1) / per;
 }
 
-int gemm_choose_split_k(const b200_ctx* ctx, const b200_gemm_desc& d) {
-    if (d.split_k == 1) return 1;
+// Picks the tile width and the K-slice count together from a cost model fitted to timings on B200. The unit is the
+// time one 128-row tile spends on one output column of one K block at full tensor rate (about 1 ns).
+//   main loop: rounds of the persistent grid x (K blocks per work item + pipeline fill) x tile width x c(width);
+//              c = 1, 1.5, 3 for 256, 128, 64 columns: a narrower tile re-reads the A block more often per flop
+//              and the shared-memory fill rate, not the tensor pipe, then sets the pace;
+//   split-K:   a fixed charge for the second launch plus the fp32 partial sums written and read back.
+GemmPlan plan_gemm(const b200_ctx* ctx, const b200_gemm_desc& d) {
     const int num_kb = static_cast<int>((d.K + BK - 1) / BK);
-    if (num_kb <= 1) return 1;
-    int want;
-    if (d.split_k > 1) {
-        want = d.split_k;
-    } else {
-        const int bn = gemm_choose_block_n(ctx, d);
-        const long long tiles = d.batch * ((d.M + BM - 1) / BM) * ((d.N + bn - 1) / bn);
-        if (tiles * 2 > ctx->sm_count || num_kb < 8) return 1;
-        want = static_cast<int>(ctx->sm_count / tiles);
-        want = min(want, num_kb / 4);  // keep at least 4 K blocks per slice
-        want = min(want, 32);
+    const long long m_tiles = d.batch * ((d.M + BM - 1) / BM);
+    const int widths[3] = {256, 128, 64};
+    const double cost_per_col[3] = {1.0, 1.5, 3.0};
+    const double split_fixed = 6500.0;
+    const double split_per_elem = 2.56e-3;  // 8 bytes of partial-sum traffic per element per slice
+    const double out_elems = static_cast<double>(d.batch) * d.M * d.N;
+    GemmPlan best{256, 1};
+    double best_cost = 0.0;
+    for (int i = 0; i < 3; ++i) {
+        const int bn = widths[i];
+        if (i < 2 && d.N <= bn / 2) continue;  // more than half of the tile would be padding
+        const long long tiles = m_tiles * ((d.N + bn - 1) / bn);
+        int cand[4] = {1, 0, 0, 0};
+        int n_cand = 1;
+        if (d.split_k > 1) {
+            cand[0] = normalise_splits(d.split_k, num_kb);
+        } else if (d.split_k == 0 && tiles * 2 <= ctx->sm_count && num_kb >= 8) {
+            const int fill = static_cast<int>(ctx->sm_count / tiles);  // slices that fill one round of the grid
+            const int most = std::min(std::min(fill, num_kb / 4), 32); // at least 4 K blocks per slice
+            for (int want : {most, most / 2, most / 4}) {
+                if (want < 2) break;
+                const int s = normalise_splits(want, num_kb);
+                bool seen = false;
+                for (int c = 0; c < n_cand; ++c) seen |= cand[c] == s;
+                if (!seen) cand[n_cand++] = s;
+            }
+        }
+        for (int c = 0; c < n_cand; ++c) {
+            const int splits = cand[c];
+            const long long work = tiles * splits;
+            const long long rounds = (work + ctx->sm_count - 1) / ctx->sm_count;
+            const int kb_per = (num_kb + splits - 1) / splits;
+            double cost = static_cast<double>(rounds) * (kb_per + 6) * bn * cost_per_col[i];
+            if (splits > 1) cost += split_fixed + split_per_elem * splits * out_elems;
+            if (best_cost == 0.0 || cost < best_cost * 0.97) {  // near ties go to the earlier (wider, unsplit) plan
+                best_cost = cost;
+                best = GemmPlan{bn, splits};
+            }
+        }
     }
-    want = max(1, min(want, num_kb));
-    const int per = (num_kb + want - 1) / want;
-    return (num_kb + per - 1) / per;  // every slice gets at least one K block
+    return best;
 }
+
+}  // namespace
+
+// B200_GEMM_TUNE=1 makes every launch read B200_GEMM_BLOCK_N (64, 128 or 256) so that a sweep can compare tile widths
+// inside one process; without it the planner decides.
+int gemm_tuned_block_n() {
+    static const bool enabled = [] { const char* e = getenv("B200_GEMM_TUNE"); return e && atoi(e) != 0; }();
+    if (!enabled) return 0;
+    const char* e = getenv("B200_GEMM_BLOCK_N");
+    const int v = e ? atoi(e) : 0;
+    return (v == 64 || v == 128 || v == 256) ? v : 0;
+}
+
+int gemm_choose_block_n(const b200_ctx* ctx, const b200_gemm_desc& d) {
+    const int forced = gemm_tuned_block_n();
+    if (forced && (forced == 64 || d.N > 64)) return forced;
+    return plan_gemm(ctx, d).bn;
+}
+
+int gemm_choose_split_k(const b200_ctx* ctx, const b200_gemm_desc& d) { return plan_gemm(ctx, d).splits; }
 
 int group_m_setting() {
     static const int value = [] {
@@ -547,7 +599,9 @@ int group_m_setting() {
 int launch_gemm_tcgen05(b200_ctx* ctx, const b200_gemm_desc& d, int k_splits, cudaStream_t stream, const GemmRoute* route) {
     const bool a_kmajor = d.transpose_a == 0;  // A stored [M,K]
     const bool b_kmajor = d.transpose_b != 0;  // B stored [N,K]
-    const int bn = gemm_choose_block_n(ctx, d);
+    b200_gemm_desc planned = d;
+    planned.split_k = k_splits;  // the tile width that suits the slice count the caller settled on
+    const int bn = gemm_choose_block_n(ctx, planned);
 
     GemmParams p{};
     p.M = static_cast<int>(d.M);

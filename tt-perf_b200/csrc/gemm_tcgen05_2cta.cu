@@ -381,7 +381,12 @@ bool gemm_pair_eligible(const b200_ctx* ctx, const b200_gemm_desc& d, const Gemm
     }
     // worth it only when the 256 x 256 tiles keep all CTA pairs busy
     const long long tiles = d.batch * ((d.M + BM_PAIR - 1) / BM_PAIR) * ((d.N + BN - 1) / BN);
-    return d.N >= 256 && d.M >= 256 && tiles >= (ctx->sm_count / 2);
+    if (d.N < 256 || d.M < 256 || tiles < (ctx->sm_count / 2)) return false;
+    // Both kernels give a CTA 128 x 256 outputs per round; the pair kernel must not need more rounds (an odd number
+    // of 128-row blocks, or a tile count just above a multiple of the pair count, costs it one).
+    const long long pairs = ctx->sm_count / 2;
+    const long long tiles_single = d.batch * ((d.M + BM_CTA - 1) / BM_CTA) * ((d.N + BN - 1) / BN);
+    return (tiles + pairs - 1) / pairs <= (tiles_single + ctx->sm_count - 1) / ctx->sm_count;
 }
 
 int launch_gemm_tcgen05_pair(b200_ctx* ctx, const b200_gemm_desc& d, cudaStream_t stream, const GemmRoute* route) {
