@@ -157,6 +157,33 @@ int b200_matmul_host(b200_ctx* ctx, const b200_gemm_desc* desc_with_host_pointer
 /* Bytes of context scratch the split-K path of this descriptor will use (0 when it does not split). */
 int b200_gemm_scratch_bytes(b200_ctx* ctx, const b200_gemm_desc* desc, size_t* out_bytes);
 
+/* ---- fused attention (traced/nn.hpp:164-192 TracedCausalAttention; transformer_train.hpp:54-70
+ * SharedAttentionBuffers::attention_forward / attention_backward; py/nn.py:229-253) ----
+ * O = softmax(scale * Q K^T + mask) V per (batch, head), computed tile by tile on the tensor cores without writing the
+ * [S, S] score or probability matrices to memory: the forward keeps a running row maximum and row sum and emits, next
+ * to O, the row log-sum-exp `lse` (natural log, of the scaled and masked scores); the backward recomputes the
+ * probabilities from Q, K and lse. With causal != 0 key j is visible to query i only when j <= i (the reference adds
+ * -1e9 above the diagonal, traced/nn.hpp:158-161; here those terms are exactly zero).
+ *   operand: bf16, element (b, h, s, d) at ptr[b*stride_b + h*stride_h + s*stride_s + d]; strides in elements and
+ *            multiples of 8, ptr 16-byte aligned. [B,H,S,64] tensors and the un-permuted [B,S,H*64] output of a
+ *            projection (stride_h = 64, stride_s = row length) are both expressible, so no head split/merge copy is needed.
+ *   head_dim must be 64 (B200_ERR_UNSUPPORTED otherwise: compose b200_gemm + b200_softmax instead).
+ *   lse      fp32 [B, H, S]
+ * b200_attention_backward: given dO it writes dQ, dK, dV (bf16, any operand layout). It uses B*H*S*65 floats of
+ * context scratch (fp32 dQ accumulators, summed with atomic adds over the key tiles, and the row sums of dO * O). */
+typedef struct b200_attn_operand {
+    void* ptr;
+    int64_t stride_b, stride_h, stride_s;
+} b200_attn_operand;
+int b200_attention_forward(b200_ctx* ctx, const b200_attn_operand* q, const b200_attn_operand* k, const b200_attn_operand* v,
+                           const b200_attn_operand* o, float* lse, int64_t B, int64_t H, int64_t S, int head_dim,
+                           float scale, int causal, void* stream);
+int b200_attention_backward(b200_ctx* ctx, const b200_attn_operand* q, const b200_attn_operand* k,
+                            const b200_attn_operand* v, const b200_attn_operand* o, const b200_attn_operand* d_o,
+                            const float* lse, const b200_attn_operand* d_q, const b200_attn_operand* d_k,
+                            const b200_attn_operand* d_v, int64_t B, int64_t H, int64_t S, int head_dim, float scale,
+                            int causal, void* stream);
+
 /* ---- row softmax family (traced/ops.hpp:77-81 softmax, :102-106 softmax_backward; py/engine.py:352-384) ----
  * [rows, cols] bf16 matrices, leading dimensions in elements.
  * b200_softmax: y = softmax(alpha * x) along each row. causal_period P > 0 additionally hides, in row r, the

@@ -45,6 +45,11 @@ class GemmDesc(C.Structure):
     ]
 
 
+class AttnOperand(C.Structure):
+    """Mirror of b200_attn_operand: element (b, h, s, d) at ptr[b*stride_b + h*stride_h + s*stride_s + d]."""
+    _fields_ = [("ptr", C.c_void_p), ("stride_b", C.c_int64), ("stride_h", C.c_int64), ("stride_s", C.c_int64)]
+
+
 def lib_path() -> Path:
     return Path(__file__).resolve().parent / "lib" / "libb200ttperf.so"
 
@@ -87,6 +92,11 @@ SIGNATURES = {
     "b200_gemm_reduce_scatter_partials": (C.c_int, [C.c_void_p, C.POINTER(GemmDesc), C.POINTER(C.c_void_p), C.c_int, C.c_int,
                                                     C.c_void_p]),
     "b200_reduce_slices": (C.c_int, [C.c_void_p, C.c_void_p, C.c_int, C.POINTER(GemmDesc), C.c_void_p]),
+    "b200_attention_forward": (C.c_int, [C.c_void_p] + [C.POINTER(AttnOperand)] * 4 + [C.c_void_p, C.c_int64, C.c_int64,
+                                         C.c_int64, C.c_int, C.c_float, C.c_int, C.c_void_p]),
+    "b200_attention_backward": (C.c_int, [C.c_void_p] + [C.POINTER(AttnOperand)] * 5 + [C.c_void_p] +
+                                [C.POINTER(AttnOperand)] * 3 + [C.c_int64, C.c_int64, C.c_int64, C.c_int, C.c_float, C.c_int,
+                                                                C.c_void_p]),
     "b200_softmax": (C.c_int, [C.c_void_p, C.c_void_p, C.c_int64, C.c_void_p, C.c_int64, C.c_int64, C.c_int64, C.c_float,
                                C.c_int64, C.c_void_p]),
     "b200_softmax_backward": (C.c_int, [C.c_void_p, C.c_void_p, C.c_int64, C.c_void_p, C.c_int64, C.c_void_p, C.c_int64,
@@ -270,6 +280,24 @@ class Context:
     # ---- row ops, element-wise ops, optimisers: thin pass-throughs (see the header for semantics) ---------------
     def _s(self, stream):
         return C.c_void_p(ptr(stream))
+
+    @staticmethod
+    def attn_operand(x, stride_b, stride_h, stride_s, offset=0) -> AttnOperand:
+        """Strided bf16 view for the fused attention calls; `offset` in elements from the start of x."""
+        return AttnOperand(ptr(x) + 2 * offset, stride_b, stride_h, stride_s)
+
+    def attention_forward(self, q, k, v, o, lse, B, H, S, *, head_dim=64, scale=None, causal=True, stream=None):
+        """q, k, v, o: AttnOperand; lse: fp32 [B, H, S]."""
+        scale = head_dim ** -0.5 if scale is None else scale
+        check(lib().b200_attention_forward(self._h, C.byref(q), C.byref(k), C.byref(v), C.byref(o), ptr(lse), B, H, S,
+                                           head_dim, scale, int(causal), self._s(stream)))
+
+    def attention_backward(self, q, k, v, o, d_o, lse, d_q, d_k, d_v, B, H, S, *, head_dim=64, scale=None, causal=True,
+                           stream=None):
+        scale = head_dim ** -0.5 if scale is None else scale
+        check(lib().b200_attention_backward(self._h, C.byref(q), C.byref(k), C.byref(v), C.byref(o), C.byref(d_o), ptr(lse),
+                                            C.byref(d_q), C.byref(d_k), C.byref(d_v), B, H, S, head_dim, scale, int(causal),
+                                            self._s(stream)))
 
     def softmax(self, x, y, rows, cols, *, ldx=None, ldy=None, alpha=1.0, causal_period=0, stream=None):
         check(lib().b200_softmax(self._h, ptr(x), ldx or cols, ptr(y), ldy or cols, rows, cols, alpha, causal_period,

@@ -1,0 +1,743 @@
+// Fused attention for head dimension 64 on the sm_100a tensor cores (tcgen05.mma, accumulators in TMEM, operands
+// brought in by TMA): forward with a running softmax, backward with recomputed probabilities. Neither pass writes an
+// [S, S] matrix to memory. Replaces the matmul / scale / mask / softmax / matmul chain of
+// autograd/traced/nn.hpp:164-192 (TracedCausalAttention) and transformer_train.hpp:54-70
+// (SharedAttentionBuffers::attention_forward / attention_backward) of the reference.
+//
+// Tiles are 128 queries x 128 keys. In TMEM a thread of the four compute warps owns one lane, i.e. one row of the
+// accumulator, so row maxima and row sums need no shuffles.
+//
+//   forward, one CTA per (batch, head, 128 queries), two CTAs per SM:
+//     issue warp   TMA loads of Q once and K, V double buffered; S = Q K^T; O_j = P V
+//     4 warps      S (TMEM) -> running max / sum -> P as bf16 into shared memory (the 128-byte-swizzled K-major
+//                  layout the next MMA reads) -> O = O * rescale + O_j in registers -> O / sum, lse
+//   backward, one CTA per (batch, head, 128 keys), looping over the query tiles that see those keys:
+//     issue warp   S^T = K Q^T, dP^T = V dO^T, then dV += P^T dO, dK += dS^T Q, dQ_i = dS K
+//     4 warps      P^T = exp(scale S^T - lse), dS^T = scale P^T (dP^T - rowsum(dO O)) into shared memory as bf16;
+//                  dQ_i from TMEM into fp32 accumulators with vector atomic adds; dK, dV at the end.
+//   The single [128 keys x 128 queries] dS^T tile in shared memory is read both as a K-major A operand (dK) and as an
+//   MN-major A operand (dQ): the two readings share one physical layout.
+//
+// Every wait is bounded: when one runs out the CTA raises the context's status word, drains its copies and returns.
+#include <algorithm>
+#include <cmath>
+
+#include "common.cuh"
+#include "gemm_common.cuh"
+#include "ptx.cuh"
+
+namespace b200 {
+
+using namespace ptx;
+
+namespace {
+
+constexpr int DH = 64;                    // head dimension
+constexpr int BT = 128;                   // queries per tile and keys per tile
+constexpr int TILE_BYTES = BT * DH * 2;   // a [128 x 64] bf16 tile, rows of 128 bytes
+constexpr int PT_BYTES = BT * BT * 2;     // a [128 x 128] bf16 tile stored as two 64-column slabs of 16 KB
+constexpr int UMMA_K = 16;
+constexpr int THREADS = 160;              // 4 compute warps + the issue warp
+constexpr int ISSUE_WARP = 4;
+constexpr float LOG2E = 1.4426950408889634f;
+constexpr float LN2 = 0.6931471805599453f;
+
+struct Geom {
+    int B, H, S;
+    int causal;
+    float scale;       // multiplies the raw scores
+    float scale_log2;  // scale * log2(e)
+};
+
+struct Strided {
+    __nv_bfloat16* ptr;
+    long long sb, sh, ss;
+};
+
+__device__ __forceinline__ float ex2(float x) {
+    float y;
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+    return y;
+}
+
+__device__ __forceinline__ void compute_warps_sync() { asm volatile("bar.sync 1, 128;" ::: "memory"); }
+
+// Byte offset of the 16-byte unit `unit` (0..15, i.e. 8 bf16 columns each) of row `r` inside a [128 x 128] bf16 tile
+// kept as two 128-byte-swizzled slabs of 64 columns.
+__device__ __forceinline__ uint32_t pt_offset(int r, int unit) {
+    return static_cast<uint32_t>((unit >> 3) * TILE_BYTES + r * 128 + (((unit & 7) ^ (r & 7)) << 4));
+}
+
+__device__ __forceinline__ void store_bf16x8(uint8_t* dst, const float* f) {
+    *reinterpret_cast<uint4*>(dst) = make_uint4(pack_bf16x2(f[0], f[1]), pack_bf16x2(f[2], f[3]), pack_bf16x2(f[4], f[5]),
+                                                pack_bf16x2(f[6], f[7]));
+}
+
+// Lets copies that were armed but never consumed land before the CTA's shared memory is released.
+__device__ __forceinline__ void drain(uint64_t* bar, uint32_t parity) {
+    const uint64_t t0 = globaltimer_ns();
+    while (!mbar_try_wait(bar, parity)) {
+        if (globaltimer_ns() - t0 > 100000000ull) break;
+    }
+}
+
+// ------------------------------------------------------------------------------------------------------------------
+// Forward
+// ------------------------------------------------------------------------------------------------------------------
+struct FwdParams {
+    Geom g;
+    Strided o;
+    float* lse;
+    int* status;
+};
+
+constexpr int FWD_TMEM_COLS = 256;  // S: columns 0..127, O_j: 128..191
+constexpr int FWD_SMEM_USED = 5 * TILE_BYTES + PT_BYTES + 64;
+// Two CTAs per SM: 2 * (FWD_SMEM + 1 KB the hardware reserves per CTA) = 228 KB exactly. That leaves 960 bytes, not
+// 1023, for rounding the base up to 1024; the kernel checks that the rounding it needs fits.
+constexpr int FWD_SMEM = FWD_SMEM_USED + 960;
+
+__global__ void __launch_bounds__(THREADS, 2)
+attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
+                const __grid_constant__ CUtensorMap tmV, const FwdParams p) {
+    extern __shared__ uint8_t smem_raw[];
+    const uint32_t pad = (1024u - (smem_u32(smem_raw) & 1023u)) & 1023u;
+    if (pad + FWD_SMEM_USED > FWD_SMEM) {  // uniform over the CTA; nothing has been set up yet
+        if (threadIdx.x == 0) atomicExch(p.status, 1);
+        return;
+    }
+    uint8_t* smem = smem_raw + pad;
+    uint8_t* sQ = smem;
+    uint8_t* sK = sQ + TILE_BYTES;       // 2 stages
+    uint8_t* sV = sK + 2 * TILE_BYTES;   // 2 stages
+    uint8_t* sP = sV + 2 * TILE_BYTES;
+    uint64_t* q_full = reinterpret_cast<uint64_t*>(sP + PT_BYTES);
+    uint64_t* kv_full = q_full + 1;      // 2
+    uint64_t* s_full = kv_full + 2;
+    uint64_t* p_ready = s_full + 1;
+    uint64_t* o_full = p_ready + 1;
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(o_full + 1);
+    volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+    const int warp = threadIdx.x >> 5;
+    const int lane = threadIdx.x & 31;
+    const Geom g = p.g;
+    const int bh = blockIdx.y;
+    const int b = bh / g.H;
+    const int h = bh - b * g.H;
+    const int qt = static_cast<int>(gridDim.x) - 1 - static_cast<int>(blockIdx.x);  // long rows of work first
+    const int q0 = qt * BT;
+    const int n_kv_all = (g.S + BT - 1) / BT;
+    const int n_kv = g.causal ? min(qt + 1, n_kv_all) : n_kv_all;
+
+    if (threadIdx.x == 0) {
+        prefetch_tensormap(&tmQ);
+        prefetch_tensormap(&tmK);
+        prefetch_tensormap(&tmV);
+        mbar_init(q_full, 1);
+        mbar_init(&kv_full[0], 1);
+        mbar_init(&kv_full[1], 1);
+        mbar_init(s_full, 1);
+        mbar_init(p_ready, 128);
+        mbar_init(o_full, 1);
+        *abort_flag = 0;
+        mbar_fence_init();
+    }
+    if (warp == ISSUE_WARP) {
+        tmem_alloc(tmem_slot, FWD_TMEM_COLS);
+        tmem_relinquish_alloc_permit();
+    }
+    tcgen05_fence_before_sync();
+    __syncthreads();
+    tcgen05_fence_after_sync();
+    const uint32_t tmem_base = *tmem_slot;
+
+    if (warp == ISSUE_WARP) {
+        if (lane == 0) {
+            constexpr uint32_t idesc_s = make_idesc_bf16_f32(BT, BT, 0u, 0u);   // Q (K-major) x K (K-major)
+            constexpr uint32_t idesc_o = make_idesc_bf16_f32(BT, DH, 0u, 1u);   // P (K-major) x V (MN-major)
+            int armed[2] = {0, 0};
+            auto load_kv = [&](int tile) {
+                const int st = tile & 1;
+                mbar_arrive_expect_tx(&kv_full[st], 2 * TILE_BYTES);
+                tma_load_4d(sK + st * TILE_BYTES, &tmK, &kv_full[st], 0, tile * BT, h, b);
+                tma_load_4d(sV + st * TILE_BYTES, &tmV, &kv_full[st], 0, tile * BT, h, b);
+                ++armed[st];
+            };
+            auto issue_s = [&](int tile) {
+                const uint32_t a = smem_u32(sQ);
+                const uint32_t bb = smem_u32(sK + (tile & 1) * TILE_BYTES);
+#pragma unroll
+                for (int k = 0; k < DH / UMMA_K; ++k)
+                    umma_f16_ss(tmem_base, make_smem_desc_sw128(a + k * 32, 0, 1024),
+                                make_smem_desc_sw128(bb + k * 32, 0, 1024), idesc_s, k > 0 ? 1u : 0u);
+                umma_commit(s_full);
+            };
+            mbar_arrive_expect_tx(q_full, TILE_BYTES);
+            tma_load_4d(sQ, &tmQ, q_full, 0, q0, h, b);
+            load_kv(0);
+            if (n_kv > 1) load_kv(1);
+            bool ok = mbar_wait(q_full, 0, abort_flag) && mbar_wait(&kv_full[0], 0, abort_flag);
+            if (ok) {
+                tcgen05_fence_after_sync();
+                issue_s(0);
+            }
+            for (int j = 0; ok && j < n_kv; ++j) {
+                if (!mbar_wait(p_ready, j & 1, abort_flag)) { ok = false; break; }
+                tcgen05_fence_after_sync();
+                const uint32_t pa = smem_u32(sP);
+                const uint32_t vb = smem_u32(sV + (j & 1) * TILE_BYTES);
+#pragma unroll
+                for (int k = 0; k < BT / UMMA_K; ++k)
+                    umma_f16_ss(tmem_base + 128, make_smem_desc_sw128(pa + (k >> 2) * TILE_BYTES + (k & 3) * 32, 0, 1024),
+                                make_smem_desc_sw128(vb + k * (UMMA_K * 128), BT * 128, 1024), idesc_o, k > 0 ? 1u : 0u);
+                umma_commit(o_full);
+                if (j + 1 < n_kv) {
+                    if (!mbar_wait(&kv_full[(j + 1) & 1], ((j + 1) >> 1) & 1, abort_flag)) { ok = false; break; }
+                    tcgen05_fence_after_sync();
+                    issue_s(j + 1);
+                }
+                if (j + 2 < n_kv) {
+                    if (!mbar_wait(o_full, j & 1, abort_flag)) { ok = false; break; }  // K_j, V_j no longer read
+                    load_kv(j + 2);
+                }
+            }
+            if (!ok) {
+                if (armed[0]) drain(&kv_full[0], (armed[0] - 1) & 1);
+                if (armed[1]) drain(&kv_full[1], (armed[1] - 1) & 1);
+                drain(q_full, 0);
+            }
+        }
+    } else {
+        const int r = threadIdx.x;  // accumulator row = TMEM lane
+        const int row = q0 + r;
+        const uint32_t lane_addr = tmem_base + (static_cast<uint32_t>(warp * 32) << 16);
+        // last visible key of this row
+        const int limit = g.causal ? min(row, g.S - 1) : g.S - 1;
+        const float sl2 = g.scale_log2;
+        float m = -INFINITY, l = 0.f;
+        float o[DH];
+#pragma unroll
+        for (int i = 0; i < DH; ++i) o[i] = 0.f;
+        bool ok = true;
+        for (int j = 0; j < n_kv; ++j) {
+            const bool got = mbar_wait(s_full, j & 1, abort_flag);
+            if (!__all_sync(0xffffffffu, got)) { ok = false; break; }
+            tcgen05_fence_after_sync();
+            const int lim = limit - j * BT;  // local index of the last visible column; >= 0 for every tile visited
+            const bool masked = lim < BT - 1;
+            float mx = m;
+#pragma unroll 1
+            for (int c = 0; c < 4; ++c) {
+                uint32_t v[32];
+                tmem_ld_32x32b_x32(lane_addr + c * 32, v);
+                tmem_ld_wait();
+                if (!masked) {
+#pragma unroll
+                    for (int i = 0; i < 32; ++i) mx = fmaxf(mx, __uint_as_float(v[i]));
+                } else {
+#pragma unroll
+                    for (int i = 0; i < 32; ++i)
+                        if (c * 32 + i <= lim) mx = fmaxf(mx, __uint_as_float(v[i]));
+                }
+            }
+            const float alpha = ex2((m - mx) * sl2);  // 0 on the first tile (m = -inf)
+            const float mb = mx * sl2;
+            m = mx;
+            float rs = 0.f;
+#pragma unroll 1
+            for (int c = 0; c < 4; ++c) {
+                uint32_t v[32];
+                tmem_ld_32x32b_x32(lane_addr + c * 32, v);
+                tmem_ld_wait();
+                float f[32];
+#pragma unroll
+                for (int i = 0; i < 32; ++i) {
+                    float pr = ex2(fmaf(__uint_as_float(v[i]), sl2, -mb));
+                    if (masked && c * 32 + i > lim) pr = 0.f;
+                    rs += pr;
+                    f[i] = pr;
+                }
+#pragma unroll
+                for (int t = 0; t < 4; ++t) store_bf16x8(sP + pt_offset(r, c * 4 + t), f + 8 * t);
+            }
+            l = l * alpha + rs;
+            fence_proxy_async_smem();
+            tcgen05_fence_before_sync();
+            mbar_arrive(p_ready);
+            const bool got_o = mbar_wait(o_full, j & 1, abort_flag);
+            if (!__all_sync(0xffffffffu, got_o)) { ok = false; break; }
+            tcgen05_fence_after_sync();
+#pragma unroll
+            for (int hh = 0; hh < 2; ++hh) {
+                uint32_t v[32];
+                tmem_ld_32x32b_x32(lane_addr + 128 + hh * 32, v);
+                tmem_ld_wait();
+#pragma unroll
+                for (int i = 0; i < 32; ++i) o[hh * 32 + i] = fmaf(o[hh * 32 + i], alpha, __uint_as_float(v[i]));
+            }
+        }
+        if (ok && row < g.S) {
+            const float inv = 1.f / l;
+#pragma unroll
+            for (int i = 0; i < DH; ++i) o[i] *= inv;
+            uint8_t* dst = reinterpret_cast<uint8_t*>(p.o.ptr + b * p.o.sb + h * p.o.sh + static_cast<long long>(row) * p.o.ss);
+#pragma unroll
+            for (int t = 0; t < DH / 8; ++t) store_bf16x8(dst + t * 16, o + 8 * t);
+            p.lse[(static_cast<long long>(bh)) * g.S + row] = (m * sl2 + log2f(l)) * LN2;
+        }
+    }
+
+    tcgen05_fence_before_sync();
+    __syncthreads();
+    if (threadIdx.x == 0 && *abort_flag != 0) atomicExch(p.status, 1);
+    if (warp == ISSUE_WARP) {
+        tcgen05_fence_after_sync();
+        tmem_dealloc(tmem_base, FWD_TMEM_COLS);
+    }
+}
+
+// ------------------------------------------------------------------------------------------------------------------
+// Backward
+// ------------------------------------------------------------------------------------------------------------------
+struct BwdParams {
+    Geom g;
+    Strided dk, dv;
+    const float* lse;   // [B, H, S]
+    const float* dsum;  // [B, H, S]  rowsum(dO * O)
+    float* dq_acc;      // [B, H, S, 64] fp32, zeroed before the launch
+    int* status;
+};
+
+constexpr int BWD_TMEM_COLS = 512;  // S^T 0..127, dP^T 128..255, dK 256..319, dV 320..383, dQ_i 384..447
+constexpr int BWD_SMEM = 6 * TILE_BYTES + 2 * PT_BYTES + 2048 + 64 + 1024;
+
+__global__ void __launch_bounds__(THREADS, 1)
+attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
+                const __grid_constant__ CUtensorMap tmV, const __grid_constant__ CUtensorMap tmdO, const BwdParams p) {
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t* smem = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
+    uint8_t* sK = smem;
+    uint8_t* sV = sK + TILE_BYTES;
+    uint8_t* sQ = sV + TILE_BYTES;        // 2 stages
+    uint8_t* sdO = sQ + 2 * TILE_BYTES;   // 2 stages
+    uint8_t* sPT = sdO + 2 * TILE_BYTES;  // P^T   [keys x queries]
+    uint8_t* sdST = sPT + PT_BYTES;       // dS^T  [keys x queries]
+    float* lse_s = reinterpret_cast<float*>(sdST + PT_BYTES);  // [2][128], already times log2(e)
+    float* dsum_s = lse_s + 2 * BT;                            // [2][128]
+    uint64_t* kv_full = reinterpret_cast<uint64_t*>(dsum_s + 2 * BT);
+    uint64_t* qdo_full = kv_full + 1;     // 2
+    uint64_t* sdp_full = qdo_full + 2;
+    uint64_t* pds_ready = sdp_full + 1;
+    uint64_t* dq_full = pds_ready + 1;
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(dq_full + 1);
+    volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+    const int warp = threadIdx.x >> 5;
+    const int lane = threadIdx.x & 31;
+    const Geom g = p.g;
+    const int bh = blockIdx.y;
+    const int b = bh / g.H;
+    const int h = bh - b * g.H;
+    const int jt = blockIdx.x;  // key tile; with the causal mask tile 0 has the most work and starts first
+    const int n_q = (g.S + BT - 1) / BT;
+    const int i0 = g.causal ? jt : 0;
+    const int n_it = n_q - i0;
+
+    if (threadIdx.x == 0) {
+        prefetch_tensormap(&tmQ);
+        prefetch_tensormap(&tmK);
+        prefetch_tensormap(&tmV);
+        prefetch_tensormap(&tmdO);
+        mbar_init(kv_full, 1);
+        mbar_init(&qdo_full[0], 1);
+        mbar_init(&qdo_full[1], 1);
+        mbar_init(sdp_full, 1);
+        mbar_init(pds_ready, 128);
+        mbar_init(dq_full, 1);
+        *abort_flag = 0;
+        mbar_fence_init();
+    }
+    if (warp == ISSUE_WARP) {
+        tmem_alloc(tmem_slot, BWD_TMEM_COLS);
+        tmem_relinquish_alloc_permit();
+    }
+    tcgen05_fence_before_sync();
+    __syncthreads();
+    tcgen05_fence_after_sync();
+    const uint32_t tmem_base = *tmem_slot;
+
+    if (warp == ISSUE_WARP) {
+        if (lane == 0) {
+            constexpr uint32_t idesc_nt = make_idesc_bf16_f32(BT, BT, 0u, 0u);  // both operands K-major, N = 128
+            constexpr uint32_t idesc_kn = make_idesc_bf16_f32(BT, DH, 0u, 1u);  // A K-major, B MN-major, N = 64
+            constexpr uint32_t idesc_mn = make_idesc_bf16_f32(BT, DH, 1u, 1u);  // A MN-major, B MN-major, N = 64
+            int armed[2] = {0, 0};
+            auto load_qdo = [&](int it) {
+                const int st = it & 1;
+                mbar_arrive_expect_tx(&qdo_full[st], 2 * TILE_BYTES);
+                tma_load_4d(sQ + st * TILE_BYTES, &tmQ, &qdo_full[st], 0, (i0 + it) * BT, h, b);
+                tma_load_4d(sdO + st * TILE_BYTES, &tmdO, &qdo_full[st], 0, (i0 + it) * BT, h, b);
+                ++armed[st];
+            };
+            mbar_arrive_expect_tx(kv_full, 2 * TILE_BYTES);
+            tma_load_4d(sK, &tmK, kv_full, 0, jt * BT, h, b);
+            tma_load_4d(sV, &tmV, kv_full, 0, jt * BT, h, b);
+            load_qdo(0);
+            if (n_it > 1) load_qdo(1);
+            bool ok = mbar_wait(kv_full, 0, abort_flag);
+            const uint32_t ka = smem_u32(sK), va = smem_u32(sV), pta = smem_u32(sPT), dsa = smem_u32(sdST);
+            for (int it = 0; ok && it < n_it; ++it) {
+                const int st = it & 1;
+                if (!mbar_wait(&qdo_full[st], (it >> 1) & 1, abort_flag)) { ok = false; break; }
+                tcgen05_fence_after_sync();
+                const uint32_t qa = smem_u32(sQ + st * TILE_BYTES);
+                const uint32_t doa = smem_u32(sdO + st * TILE_BYTES);
+#pragma unroll
+                for (int k = 0; k < DH / UMMA_K; ++k)   // S^T = K Q^T
+                    umma_f16_ss(tmem_base, make_smem_desc_sw128(ka + k * 32, 0, 1024),
+                                make_smem_desc_sw128(qa + k * 32, 0, 1024), idesc_nt, k > 0 ? 1u : 0u);
+#pragma unroll
+                for (int k = 0; k < DH / UMMA_K; ++k)   // dP^T = V dO^T
+                    umma_f16_ss(tmem_base + 128, make_smem_desc_sw128(va + k * 32, 0, 1024),
+                                make_smem_desc_sw128(doa + k * 32, 0, 1024), idesc_nt, k > 0 ? 1u : 0u);
+                umma_commit(sdp_full);
+                if (!mbar_wait(pds_ready, it & 1, abort_flag)) { ok = false; break; }
+                tcgen05_fence_after_sync();
+#pragma unroll
+                for (int k = 0; k < BT / UMMA_K; ++k)   // dV += P^T dO   (reduction over the 128 queries)
+                    umma_f16_ss(tmem_base + 320, make_smem_desc_sw128(pta + (k >> 2) * TILE_BYTES + (k & 3) * 32, 0, 1024),
+                                make_smem_desc_sw128(doa + k * (UMMA_K * 128), BT * 128, 1024), idesc_kn,
+                                (it > 0 || k > 0) ? 1u : 0u);
+#pragma unroll
+                for (int k = 0; k < BT / UMMA_K; ++k)   // dK += dS^T Q
+                    umma_f16_ss(tmem_base + 256, make_smem_desc_sw128(dsa + (k >> 2) * TILE_BYTES + (k & 3) * 32, 0, 1024),
+                                make_smem_desc_sw128(qa + k * (UMMA_K * 128), BT * 128, 1024), idesc_kn,
+                                (it > 0 || k > 0) ? 1u : 0u);
+#pragma unroll
+                for (int k = 0; k < BT / UMMA_K; ++k)   // dQ_i = dS K     (reduction over the 128 keys)
+                    umma_f16_ss(tmem_base + 384, make_smem_desc_sw128(dsa + k * (UMMA_K * 128), BT * 128, 1024),
+                                make_smem_desc_sw128(ka + k * (UMMA_K * 128), BT * 128, 1024), idesc_mn, k > 0 ? 1u : 0u);
+                umma_commit(dq_full);
+                if (it + 2 < n_it) {
+                    if (!mbar_wait(dq_full, it & 1, abort_flag)) { ok = false; break; }  // Q_i, dO_i no longer read
+                    load_qdo(it + 2);
+                }
+            }
+            if (!ok) {
+                if (armed[0]) drain(&qdo_full[0], (armed[0] - 1) & 1);
+                if (armed[1]) drain(&qdo_full[1], (armed[1] - 1) & 1);
+                drain(kv_full, 0);
+            }
+        }
+    } else {
+        const int r = threadIdx.x;  // TMEM lane: key row for S^T, dP^T, dK, dV; query row for dQ_i
+        const uint32_t lane_addr = tmem_base + (static_cast<uint32_t>(warp * 32) << 16);
+        const float sl2 = g.scale_log2;
+        bool ok = true;
+        for (int it = 0; it < n_it; ++it) {
+            const int st = it & 1;
+            const int i = i0 + it;
+            const int qrow = i * BT + r;
+            const long long stat = static_cast<long long>(bh) * g.S + qrow;
+            lse_s[st * BT + r] = qrow < g.S ? p.lse[stat] * LOG2E : INFINITY;  // +inf: probability 0 for padding queries
+            dsum_s[st * BT + r] = qrow < g.S ? p.dsum[stat] : 0.f;
+            compute_warps_sync();
+            const bool got = mbar_wait(sdp_full, it & 1, abort_flag);
+            if (!__all_sync(0xffffffffu, got)) { ok = false; break; }
+            tcgen05_fence_after_sync();
+            const bool diag = g.causal && i == jt;  // query (column) c sees key (row) r only when c >= r
+#pragma unroll 1
+            for (int c = 0; c < 4; ++c) {
+                uint32_t s[32], dp[32];
+                tmem_ld_32x32b_x32(lane_addr + c * 32, s);
+                tmem_ld_32x32b_x32(lane_addr + 128 + c * 32, dp);
+                tmem_ld_wait();
+                float pf[32], df[32];
+                const float4* l4 = reinterpret_cast<const float4*>(lse_s + st * BT + c * 32);
+                const float4* d4 = reinterpret_cast<const float4*>(dsum_s + st * BT + c * 32);
+#pragma unroll
+                for (int u = 0; u < 8; ++u) {
+                    const float4 lv = l4[u];
+                    const float4 dv = d4[u];
+                    const float ls[4] = {lv.x, lv.y, lv.z, lv.w};
+                    const float ds[4] = {dv.x, dv.y, dv.z, dv.w};
+#pragma unroll
+                    for (int e = 0; e < 4; ++e) {
+                        const int idx = u * 4 + e;
+                        float pr = ex2(fmaf(__uint_as_float(s[idx]), sl2, -ls[e]));
+                        if (diag && c * 32 + idx < r) pr = 0.f;
+                        pf[idx] = pr;
+                        df[idx] = pr * (__uint_as_float(dp[idx]) - ds[e]) * g.scale;
+                    }
+                }
+#pragma unroll
+                for (int t = 0; t < 4; ++t) {
+                    const uint32_t off = pt_offset(r, c * 4 + t);
+                    store_bf16x8(sPT + off, pf + 8 * t);
+                    store_bf16x8(sdST + off, df + 8 * t);
+                }
+            }
+            fence_proxy_async_smem();
+            tcgen05_fence_before_sync();
+            mbar_arrive(pds_ready);
+            const bool got_dq = mbar_wait(dq_full, it & 1, abort_flag);
+            if (!__all_sync(0xffffffffu, got_dq)) { ok = false; break; }
+            tcgen05_fence_after_sync();
+            float4* acc = reinterpret_cast<float4*>(p.dq_acc + stat * DH);
+#pragma unroll
+            for (int hh = 0; hh < 2; ++hh) {
+                uint32_t v[32];
+                tmem_ld_32x32b_x32(lane_addr + 384 + hh * 32, v);
+                tmem_ld_wait();
+                if (qrow < g.S) {
+#pragma unroll
+                    for (int t = 0; t < 8; ++t)
+                        atomicAdd(acc + hh * 8 + t, make_float4(__uint_as_float(v[4 * t]), __uint_as_float(v[4 * t + 1]),
+                                                                 __uint_as_float(v[4 * t + 2]), __uint_as_float(v[4 * t + 3])));
+                }
+            }
+        }
+        if (ok) {
+            // the last dq_full also covers the final dK / dV accumulation
+            const int key = jt * BT + r;
+#pragma unroll
+            for (int which = 0; which < 2; ++which) {
+                const Strided& dst = which == 0 ? p.dk : p.dv;
+                uint8_t* out = reinterpret_cast<uint8_t*>(dst.ptr + b * dst.sb + h * dst.sh + static_cast<long long>(key) * dst.ss);
+#pragma unroll
+                for (int hh = 0; hh < 2; ++hh) {
+                    uint32_t v[32];
+                    tmem_ld_32x32b_x32(lane_addr + 256 + which * 64 + hh * 32, v);
+                    tmem_ld_wait();
+                    if (key < g.S) {
+                        float f[32];
+#pragma unroll
+                        for (int e = 0; e < 32; ++e) f[e] = __uint_as_float(v[e]);
+#pragma unroll
+                        for (int t = 0; t < 4; ++t) store_bf16x8(out + hh * 64 + t * 16, f + 8 * t);
+                    }
+                }
+            }
+        }
+    }
+
+    tcgen05_fence_before_sync();
+    __syncthreads();
+    if (threadIdx.x == 0 && *abort_flag != 0) atomicExch(p.status, 1);
+    if (warp == ISSUE_WARP) {
+        tcgen05_fence_after_sync();
+        tmem_dealloc(tmem_base, BWD_TMEM_COLS);
+    }
+}
+
+struct StridedIn {
+    const __nv_bfloat16* ptr;
+    long long sb, sh, ss;
+};
+
+// dsum[b, h, s] = sum_d dO * O. Eight threads per row, 8 elements each.
+__global__ void attn_dsum_kernel(StridedIn o, StridedIn d_o, float* dsum, int B, int H, int S) {
+    const long long t = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x;
+    const long long rowi = t >> 3;
+    const int part = static_cast<int>(t & 7);
+    const long long rows = static_cast<long long>(B) * H * S;
+    float acc = 0.f;
+    if (rowi < rows) {
+        const int s = static_cast<int>(rowi % S);
+        const long long bhh = rowi / S;
+        const int h = static_cast<int>(bhh % H);
+        const long long b = bhh / H;
+        const uint4 ov = *reinterpret_cast<const uint4*>(o.ptr + b * o.sb + h * o.sh + s * o.ss + part * 8);
+        const uint4 dv = *reinterpret_cast<const uint4*>(d_o.ptr + b * d_o.sb + h * d_o.sh + s * d_o.ss + part * 8);
+        const uint32_t ow[4] = {ov.x, ov.y, ov.z, ov.w};
+        const uint32_t dw[4] = {dv.x, dv.y, dv.z, dv.w};
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+            acc = fmaf(__uint_as_float(ow[e] << 16), __uint_as_float(dw[e] << 16), acc);
+            acc = fmaf(__uint_as_float(ow[e] & 0xffff0000u), __uint_as_float(dw[e] & 0xffff0000u), acc);
+        }
+    }
+    acc += __shfl_xor_sync(0xffffffffu, acc, 1);
+    acc += __shfl_xor_sync(0xffffffffu, acc, 2);
+    acc += __shfl_xor_sync(0xffffffffu, acc, 4);
+    if (rowi < rows && part == 0) dsum[rowi] = acc;
+}
+
+// fp32 dQ accumulators [B, H, S, 64] -> bf16 in the caller's layout. One thread per 8 elements.
+__global__ void attn_dq_store_kernel(const float* acc, Strided dq, int B, int H, int S) {
+    const long long t = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x;
+    const long long rowi = t >> 3;
+    const int part = static_cast<int>(t & 7);
+    if (rowi >= static_cast<long long>(B) * H * S) return;
+    const int s = static_cast<int>(rowi % S);
+    const long long bhh = rowi / S;
+    const int h = static_cast<int>(bhh % H);
+    const long long b = bhh / H;
+    const float4 a0 = *reinterpret_cast<const float4*>(acc + rowi * DH + part * 8);
+    const float4 a1 = *reinterpret_cast<const float4*>(acc + rowi * DH + part * 8 + 4);
+    *reinterpret_cast<uint4*>(dq.ptr + b * dq.sb + h * dq.sh + s * dq.ss + part * 8) =
+        make_uint4(pack_bf16x2(a0.x, a0.y), pack_bf16x2(a0.z, a0.w), pack_bf16x2(a1.x, a1.y), pack_bf16x2(a1.z, a1.w));
+}
+
+// 4-D tensor map {64, S, H, B} over a strided bf16 operand; box = one [128 x 64] tile, 128-byte swizzle, rows beyond S
+// read as zero.
+int make_attn_map(b200_ctx* ctx, CUtensorMap* out, const b200_attn_operand& t, int64_t B, int64_t H, int64_t S,
+                  const char* name) {
+    cuuint64_t dims[4] = {DH, static_cast<cuuint64_t>(S), static_cast<cuuint64_t>(H), static_cast<cuuint64_t>(B)};
+    // A dimension of extent 1 never contributes to an address; give it a well-formed stride whatever the caller passed.
+    const int64_t sh = H > 1 ? t.stride_h : DH;
+    const int64_t sb = B > 1 ? t.stride_b : DH;
+    cuuint64_t strides[3] = {static_cast<cuuint64_t>(t.stride_s) * 2, static_cast<cuuint64_t>(sh) * 2,
+                             static_cast<cuuint64_t>(sb) * 2};
+    cuuint32_t box[4] = {DH, BT, 1, 1};
+    cuuint32_t estr[4] = {1, 1, 1, 1};
+    CUresult r = ctx->encode_tiled(out, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 4, t.ptr, dims, strides, box, estr,
+                                   CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                                   CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS)
+        return fail(B200_ERR_CUDA, "cuTensorMapEncodeTiled failed (%d) for attention operand %s: ptr %p strides {%lld,%lld,%lld}",
+                    static_cast<int>(r), name, t.ptr, (long long)t.stride_b, (long long)t.stride_h, (long long)t.stride_s);
+    return B200_OK;
+}
+
+int check_operand(const b200_attn_operand* t, const char* name, int64_t B, int64_t H) {
+    B200_REQUIRE(t != nullptr && t->ptr != nullptr, "attention: operand %s is NULL", name);
+    B200_REQUIRE((reinterpret_cast<uintptr_t>(t->ptr) & 15u) == 0, "attention: operand %s is not 16-byte aligned", name);
+    B200_REQUIRE(t->stride_s >= DH && (t->stride_s % 8) == 0, "attention: %s.stride_s must be >= 64 and a multiple of 8", name);
+    B200_REQUIRE(H == 1 || (t->stride_h > 0 && (t->stride_h % 8) == 0), "attention: %s.stride_h must be a positive multiple of 8", name);
+    B200_REQUIRE(B == 1 || (t->stride_b > 0 && (t->stride_b % 8) == 0), "attention: %s.stride_b must be a positive multiple of 8", name);
+    return B200_OK;
+}
+
+int check_geometry(int64_t B, int64_t H, int64_t S, int head_dim, float scale) {
+    if (head_dim != DH)
+        return fail(B200_ERR_UNSUPPORTED, "attention: head_dim %d is not supported by the fused kernels (64 only)", head_dim);
+    B200_REQUIRE(B >= 0 && H >= 0 && S >= 0, "attention: negative extent");
+    B200_REQUIRE(B * H <= 65535, "attention: batch * heads = %lld exceeds 65535", (long long)(B * H));
+    B200_REQUIRE(S <= (1 << 24), "attention: sequence length %lld too large", (long long)S);
+    B200_REQUIRE(scale > 0.f && std::isfinite(scale), "attention: scale must be positive and finite");
+    return B200_OK;
+}
+
+template <typename K>
+int configure_once(K kernel, int smem_bytes, bool (&done)[64]) {
+    int dev = 0;
+    B200_CUDA_TRY(cudaGetDevice(&dev));
+    if (dev < 0 || dev >= 64 || !done[dev]) {
+        B200_CUDA_TRY(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes));
+        if (dev >= 0 && dev < 64) done[dev] = true;
+    }
+    return B200_OK;
+}
+
+Geom make_geom(int64_t B, int64_t H, int64_t S, float scale, int causal) {
+    Geom g;
+    g.B = static_cast<int>(B);
+    g.H = static_cast<int>(H);
+    g.S = static_cast<int>(S);
+    g.causal = causal != 0;
+    g.scale = scale;
+    g.scale_log2 = scale * LOG2E;
+    return g;
+}
+
+Strided as_out(const b200_attn_operand* t) {
+    return Strided{static_cast<__nv_bfloat16*>(t->ptr), t->stride_b, t->stride_h, t->stride_s};
+}
+
+StridedIn as_in(const b200_attn_operand* t) {
+    return StridedIn{static_cast<const __nv_bfloat16*>(t->ptr), t->stride_b, t->stride_h, t->stride_s};
+}
+
+}  // namespace
+}  // namespace b200
+
+using namespace b200;
+
+extern "C" {
+
+int b200_attention_forward(b200_ctx* ctx, const b200_attn_operand* q, const b200_attn_operand* k, const b200_attn_operand* v,
+                           const b200_attn_operand* o, float* lse, int64_t B, int64_t H, int64_t S, int head_dim,
+                           float scale, int causal, void* stream_v) {
+    B200_REQUIRE(ctx != nullptr, "b200_attention_forward: ctx is NULL");
+    int rc = check_geometry(B, H, S, head_dim, scale);
+    if (rc != B200_OK) return rc;
+    if (B == 0 || H == 0 || S == 0) return B200_OK;
+    B200_REQUIRE(lse != nullptr, "b200_attention_forward: lse is NULL");
+    if ((rc = check_operand(q, "q", B, H)) != B200_OK) return rc;
+    if ((rc = check_operand(k, "k", B, H)) != B200_OK) return rc;
+    if ((rc = check_operand(v, "v", B, H)) != B200_OK) return rc;
+    if ((rc = check_operand(o, "o", B, H)) != B200_OK) return rc;
+    DeviceScope scope(ctx->device);
+    cudaStream_t stream = ctx->pick(stream_v);
+    CUtensorMap tmQ, tmK, tmV;
+    if ((rc = make_attn_map(ctx, &tmQ, *q, B, H, S, "q")) != B200_OK) return rc;
+    if ((rc = make_attn_map(ctx, &tmK, *k, B, H, S, "k")) != B200_OK) return rc;
+    if ((rc = make_attn_map(ctx, &tmV, *v, B, H, S, "v")) != B200_OK) return rc;
+    FwdParams p;
+    p.g = make_geom(B, H, S, scale, causal);
+    p.o = as_out(o);
+    p.lse = lse;
+    p.status = ctx->d_status;
+    static bool configured[64] = {};
+    if ((rc = configure_once(attn_fwd_kernel, FWD_SMEM, configured)) != B200_OK) return rc;
+    const dim3 grid(static_cast<unsigned>((S + BT - 1) / BT), static_cast<unsigned>(B * H));
+    attn_fwd_kernel<<<grid, THREADS, FWD_SMEM, stream>>>(tmQ, tmK, tmV, p);
+    B200_CUDA_TRY(cudaGetLastError());
+    return B200_OK;
+}
+
+int b200_attention_backward(b200_ctx* ctx, const b200_attn_operand* q, const b200_attn_operand* k,
+                            const b200_attn_operand* v, const b200_attn_operand* o, const b200_attn_operand* d_o,
+                            const float* lse, const b200_attn_operand* d_q, const b200_attn_operand* d_k,
+                            const b200_attn_operand* d_v, int64_t B, int64_t H, int64_t S, int head_dim, float scale,
+                            int causal, void* stream_v) {
+    B200_REQUIRE(ctx != nullptr, "b200_attention_backward: ctx is NULL");
+    int rc = check_geometry(B, H, S, head_dim, scale);
+    if (rc != B200_OK) return rc;
+    if (B == 0 || H == 0 || S == 0) return B200_OK;
+    B200_REQUIRE(lse != nullptr, "b200_attention_backward: lse is NULL");
+    const b200_attn_operand* ops[8] = {q, k, v, o, d_o, d_q, d_k, d_v};
+    const char* names[8] = {"q", "k", "v", "o", "d_o", "d_q", "d_k", "d_v"};
+    for (int i = 0; i < 8; ++i)
+        if ((rc = check_operand(ops[i], names[i], B, H)) != B200_OK) return rc;
+    DeviceScope scope(ctx->device);
+    cudaStream_t stream = ctx->pick(stream_v);
+    const size_t rows = static_cast<size_t>(B) * H * S;
+    const size_t acc_bytes = rows * DH * sizeof(float);
+    if ((rc = ensure_scratch(ctx, acc_bytes + rows * sizeof(float))) != B200_OK) return rc;
+    float* dq_acc = static_cast<float*>(ctx->d_scratch);
+    float* dsum = dq_acc + rows * DH;
+    CUtensorMap tmQ, tmK, tmV, tmdO;
+    if ((rc = make_attn_map(ctx, &tmQ, *q, B, H, S, "q")) != B200_OK) return rc;
+    if ((rc = make_attn_map(ctx, &tmK, *k, B, H, S, "k")) != B200_OK) return rc;
+    if ((rc = make_attn_map(ctx, &tmV, *v, B, H, S, "v")) != B200_OK) return rc;
+    if ((rc = make_attn_map(ctx, &tmdO, *d_o, B, H, S, "d_o")) != B200_OK) return rc;
+
+    B200_CUDA_TRY(cudaMemsetAsync(dq_acc, 0, acc_bytes, stream));
+    const unsigned blocks = static_cast<unsigned>((rows * 8 + 255) / 256);
+    attn_dsum_kernel<<<blocks, 256, 0, stream>>>(as_in(o), as_in(d_o), dsum, static_cast<int>(B), static_cast<int>(H),
+                                                 static_cast<int>(S));
+    B200_CUDA_TRY(cudaGetLastError());
+
+    BwdParams p;
+    p.g = make_geom(B, H, S, scale, causal);
+    p.dk = as_out(d_k);
+    p.dv = as_out(d_v);
+    p.lse = lse;
+    p.dsum = dsum;
+    p.dq_acc = dq_acc;
+    p.status = ctx->d_status;
+    static bool configured[64] = {};
+    if ((rc = configure_once(attn_bwd_kernel, BWD_SMEM, configured)) != B200_OK) return rc;
+    const dim3 grid(static_cast<unsigned>((S + BT - 1) / BT), static_cast<unsigned>(B * H));
+    attn_bwd_kernel<<<grid, THREADS, BWD_SMEM, stream>>>(tmQ, tmK, tmV, tmdO, p);
+    B200_CUDA_TRY(cudaGetLastError());
+    attn_dq_store_kernel<<<blocks, 256, 0, stream>>>(dq_acc, as_out(d_q), static_cast<int>(B), static_cast<int>(H),
+                                                     static_cast<int>(S));
+    B200_CUDA_TRY(cudaGetLastError());
+    return B200_OK;
+}
+
+}  // extern "C"
