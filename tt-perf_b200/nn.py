@@ -223,29 +223,62 @@ def mlp_train_step(ctx, x, target, params, lr, *, loss="ce", masters=None, strea
 # ---------------------------------------------------------------------------------------------------------------
 # Pre-LN GPT-2 block (verify/compare_grads.py:37-97)
 # ---------------------------------------------------------------------------------------------------------------
+FUSED_HEAD_DIM = 64   # head dimension the fused attention kernels are built for
+
+
+def _head_operands(ctx, t, heads, parts=1):
+    """Per-head strided views of a [B, S, parts * H * dh] projection output: one b200_attn_operand per part, each
+    addressing element (b, h, s, d) in place (no [B,S,H,dh] -> [B,H,S,dh] copy)."""
+    b, s, width = t.shape
+    dh = width // (parts * heads)
+    return [ctx.attn_operand(t, s * width, dh, width, offset=i * heads * dh) for i in range(parts)]
+
+
 def transformer_block_forward(ctx, x, w, heads, *, stream=None):
-    """x [B, S, D]; w: dict with ln1_g, ln1_b, wq, bq, wk, bk, wv, bv, wo, bo, ln2_g, ln2_b, w1, b1, w2, b2.
-    Returns (out, cache)."""
+    """x [B, S, D]; w: dict with ln1_g, ln1_b, wq, bq, wk, bk, wv, bv, wo, bo, ln2_g, ln2_b, w1, b1, w2, b2, and
+    optionally wqkv [3D, D] / bqkv [3D] (the three projections stacked, of which wq.. are then row views): one GEMM
+    instead of three. With head dimension 64 the attention runs in the fused kernels on the projection outputs as
+    they lie; other head dimensions take the materialised softmax path. Returns (out, cache)."""
+    b, s, d = x.shape
+    dh = d // heads
     ln1, mean1, rstd1 = layernorm_forward(ctx, x, w["ln1_g"], w["ln1_b"], stream=stream)
-    q = split_heads(ctx, linear_forward(ctx, ln1, w["wq"], w["bq"], stream=stream), heads, stream=stream)
-    k = split_heads(ctx, linear_forward(ctx, ln1, w["wk"], w["bk"], stream=stream), heads, stream=stream)
-    v = split_heads(ctx, linear_forward(ctx, ln1, w["wv"], w["bv"], stream=stream), heads, stream=stream)
-    attn, p = causal_attention_forward(ctx, q, k, v, stream=stream)
-    merged = merge_heads(ctx, attn, stream=stream)
+    cache = dict(x=x, ln1=ln1, mean1=mean1, rstd1=rstd1)
+    if dh == FUSED_HEAD_DIM:
+        if "wqkv" in w:
+            qkv = linear_forward(ctx, ln1, w["wqkv"], w["bqkv"], stream=stream)            # [B, S, 3D]
+            q_op, k_op, v_op = _head_operands(ctx, qkv, heads, 3)
+            cache["qkv"] = (qkv,)
+        else:
+            q, k, v = (linear_forward(ctx, ln1, w["w" + n], w["b" + n], stream=stream) for n in "qkv")
+            (q_op,), (k_op,), (v_op,) = (_head_operands(ctx, t, heads) for t in (q, k, v))
+            cache["qkv"] = (q, k, v)
+        merged = DeviceTensor(ctx, (b, s, d), BF16)
+        lse = DeviceTensor(ctx, (b, heads, s), F32)
+        (o_op,) = _head_operands(ctx, merged, heads)
+        ctx.attention_forward(q_op, k_op, v_op, o_op, lse, b, heads, s, head_dim=dh, causal=True, stream=stream)
+        cache.update(lse=lse)
+    else:
+        q = split_heads(ctx, linear_forward(ctx, ln1, w["wq"], w["bq"], stream=stream), heads, stream=stream)
+        k = split_heads(ctx, linear_forward(ctx, ln1, w["wk"], w["bk"], stream=stream), heads, stream=stream)
+        v = split_heads(ctx, linear_forward(ctx, ln1, w["wv"], w["bv"], stream=stream), heads, stream=stream)
+        attn, p = causal_attention_forward(ctx, q, k, v, stream=stream)
+        merged = merge_heads(ctx, attn, stream=stream)
+        cache.update(q=q, k=k, v=v, p=p)
     res1 = add(ctx, x, linear_forward(ctx, merged, w["wo"], w["bo"], stream=stream), stream=stream)
     ln2, mean2, rstd2 = layernorm_forward(ctx, res1, w["ln2_g"], w["ln2_b"], stream=stream)
     h1 = linear_forward(ctx, ln2, w["w1"], w["b1"], stream=stream)
     h1g = DeviceTensor(ctx, h1.shape, BF16)
     ctx.unary(capi.U_GELU, h1, h1g, h1g.numel, stream=stream)
     out = add(ctx, res1, linear_forward(ctx, h1g, w["w2"], w["b2"], stream=stream), stream=stream)
-    cache = dict(x=x, ln1=ln1, mean1=mean1, rstd1=rstd1, q=q, k=k, v=v, p=p, merged=merged, res1=res1, ln2=ln2,
-                 mean2=mean2, rstd2=rstd2, h1=h1, h1g=h1g)
+    cache.update(merged=merged, res1=res1, ln2=ln2, mean2=mean2, rstd2=rstd2, h1=h1, h1g=h1g)
     return out, cache
 
 
 def transformer_block_backward(ctx, d_out, w, cache, heads, *, stream=None):
     """Returns (dx, grads) with grads keyed like `w` (LayerNorm gradients are fp32, the rest bf16)."""
     c, g = cache, {}
+    b, s, d = c["x"].shape
+    dh = d // heads
     d_h1g, g["w2"], g["b2"] = linear_backward(ctx, c["h1g"], w["w2"], d_out, stream=stream)
     d_h1 = gelu_backward(ctx, d_h1g, c["h1"], stream=stream)
     d_ln2, g["w1"], g["b1"] = linear_backward(ctx, c["ln2"], w["w1"], d_h1, stream=stream)
@@ -253,12 +286,32 @@ def transformer_block_backward(ctx, d_out, w, cache, heads, *, stream=None):
                                                             stream=stream)
     d_res1 = add(ctx, d_out, d_res1_ln, stream=stream)
     d_merged, g["wo"], g["bo"] = linear_backward(ctx, c["merged"], w["wo"], d_res1, stream=stream)
-    d_attn = split_heads(ctx, d_merged, heads, stream=stream)
-    d_q, d_k, d_v = causal_attention_backward(ctx, c["q"], c["k"], c["v"], c["p"], d_attn, stream=stream)
-    d_ln1_q, g["wq"], g["bq"] = linear_backward(ctx, c["ln1"], w["wq"], merge_heads(ctx, d_q, stream=stream), stream=stream)
-    d_ln1_k, g["wk"], g["bk"] = linear_backward(ctx, c["ln1"], w["wk"], merge_heads(ctx, d_k, stream=stream), stream=stream)
-    d_ln1_v, g["wv"], g["bv"] = linear_backward(ctx, c["ln1"], w["wv"], merge_heads(ctx, d_v, stream=stream), stream=stream)
-    d_ln1 = add(ctx, add(ctx, d_ln1_q, d_ln1_k, stream=stream), d_ln1_v, stream=stream)
+    if "lse" in c:
+        (o_op,), (do_op,) = _head_operands(ctx, c["merged"], heads), _head_operands(ctx, d_merged, heads)
+        if len(c["qkv"]) == 1:
+            q_op, k_op, v_op = _head_operands(ctx, c["qkv"][0], heads, 3)
+            d_qkv = DeviceTensor(ctx, (b, s, 3 * d), BF16)
+            dq_op, dk_op, dv_op = _head_operands(ctx, d_qkv, heads, 3)
+            grads_in = (d_qkv,)
+        else:
+            (q_op,), (k_op,), (v_op,) = (_head_operands(ctx, t, heads) for t in c["qkv"])
+            grads_in = tuple(DeviceTensor(ctx, (b, s, d), BF16) for _ in range(3))
+            (dq_op,), (dk_op,), (dv_op,) = (_head_operands(ctx, t, heads) for t in grads_in)
+        ctx.attention_backward(q_op, k_op, v_op, o_op, do_op, c["lse"], dq_op, dk_op, dv_op, b, heads, s, head_dim=dh,
+                               causal=True, stream=stream)
+    else:
+        d_attn = split_heads(ctx, d_merged, heads, stream=stream)
+        d_q, d_k, d_v = causal_attention_backward(ctx, c["q"], c["k"], c["v"], c["p"], d_attn, stream=stream)
+        grads_in = tuple(merge_heads(ctx, t, stream=stream) for t in (d_q, d_k, d_v))
+    if len(grads_in) == 1:
+        d_ln1, g["wqkv"], g["bqkv"] = linear_backward(ctx, c["ln1"], w["wqkv"], grads_in[0], stream=stream)
+        for i, n in enumerate("qkv"):
+            g["w" + n], g["b" + n] = g["wqkv"].narrow0(i * d, d), g["bqkv"].narrow0(i * d, d)
+    else:
+        d_ln1_q, g["wq"], g["bq"] = linear_backward(ctx, c["ln1"], w["wq"], grads_in[0], stream=stream)
+        d_ln1_k, g["wk"], g["bk"] = linear_backward(ctx, c["ln1"], w["wk"], grads_in[1], stream=stream)
+        d_ln1_v, g["wv"], g["bv"] = linear_backward(ctx, c["ln1"], w["wv"], grads_in[2], stream=stream)
+        d_ln1 = add(ctx, add(ctx, d_ln1_q, d_ln1_k, stream=stream), d_ln1_v, stream=stream)
     d_x_ln, g["ln1_g"], g["ln1_b"] = layernorm_backward(ctx, d_ln1, c["x"], w["ln1_g"], c["mean1"], c["rstd1"],
                                                          stream=stream)
     return add(ctx, d_res1, d_x_ln, stream=stream), g
@@ -269,6 +322,7 @@ def transformer_block_backward(ctx, d_out, w, cache, heads, *, stream=None):
 # (TracedTransformerWithEmbedding, autograd/traced/transformer_train.hpp:363-507; bench/autograd/bench_gpt2_full.cpp)
 # ---------------------------------------------------------------------------------------------------------------
 BLOCK_KEYS = ("ln1_g", "ln1_b", "wq", "bq", "wk", "bk", "wv", "bv", "wo", "bo", "ln2_g", "ln2_b", "w1", "b1", "w2", "b2")
+_QKV_KEYS = ("wq", "bq", "wk", "bk", "wv", "bv")
 _F32_GRADS = ("ln1_g", "ln1_b", "ln2_g", "ln2_b")   # LayerNorm gradients come out of their kernel in fp32
 
 
@@ -300,8 +354,20 @@ class GPT2:
             "lnf_g": DeviceTensor.from_numpy(ctx, host_params["lnf_g"]),
             "lnf_b": DeviceTensor.from_numpy(ctx, host_params["lnf_b"]),
             "head": DeviceTensor.from_numpy(ctx, head),
-            "blocks": [{k: DeviceTensor.from_numpy(ctx, w[k]) for k in BLOCK_KEYS} for w in host_params["blocks"]],
+            "blocks": [self._load_block(w) for w in host_params["blocks"]],
         }
+
+    def _load_block(self, w):
+        """The three attention projections are stored stacked ([3D, D] and [3D]) so that they run as one GEMM; wq, bq,
+        ... stay addressable as row views of the stacked tensors."""
+        import numpy as np
+        ctx, d = self.ctx, self.D
+        blk = {k: DeviceTensor.from_numpy(ctx, w[k]) for k in BLOCK_KEYS if k not in _QKV_KEYS}
+        blk["wqkv"] = DeviceTensor.from_numpy(ctx, np.concatenate([w["wq"], w["wk"], w["wv"]], axis=0))
+        blk["bqkv"] = DeviceTensor.from_numpy(ctx, np.concatenate([w["bq"], w["bk"], w["bv"]], axis=0))
+        for i, n in enumerate("qkv"):
+            blk["w" + n], blk["b" + n] = blk["wqkv"].narrow0(i * d, d), blk["bqkv"].narrow0(i * d, d)
+        return blk
 
     def init_random(self, seed=42, std=0.02) -> None:
         """N(0, std) weights, zero biases, LayerNorm gain 1 (random-init stand-in for a checkpoint)."""

@@ -92,6 +92,13 @@ class DeviceTensor:
             raise ValueError(f"cannot reshape {self.shape} to {tuple(shape)}")
         return DeviceTensor(self.ctx, shape, self.dtype, ptr=self.ptr, owner=self)
 
+    def narrow0(self, start: int, length: int) -> "DeviceTensor":
+        """View of rows [start, start + length) of the first dimension (shares storage)."""
+        if not (0 <= start and start + length <= self.shape[0]):
+            raise ValueError(f"rows [{start}, {start + length}) outside {self.shape}")
+        row_bytes = self.nbytes // self.shape[0] if self.shape[0] else 0
+        return DeviceTensor(self.ctx, (length,) + self.shape[1:], self.dtype, ptr=self.ptr + start * row_bytes, owner=self)
+
     def data_ptr(self) -> int:
         return self.ptr
 
