@@ -218,6 +218,17 @@ int b200_layernorm_forward(b200_ctx* ctx, const void* x, int64_t ldx, const void
 int b200_layernorm_backward(b200_ctx* ctx, const void* dy, int64_t lddy, const void* x, int64_t ldx, const void* gamma,
                             const float* mean, const float* rstd, void* dx, int64_t lddx, float* dgamma_f32,
                             float* dbeta_f32, int64_t rows, int64_t cols, void* stream);
+/* The same with the residual connection folded in, so that no separate element-wise add runs
+ * (transformer_train.hpp:201,212,228,250,256 add the residual in a pass of its own):
+ * b200_add_layernorm_forward: sum_out = x + residual (bf16), y = LayerNorm(sum_out); mean / rstd are those of sum_out.
+ * b200_layernorm_backward_add: dx = LayerNorm'(dy) + upstream, the gradient that reaches the same tensor along the
+ *   residual path. Both accept every shape the plain calls accept. */
+int b200_add_layernorm_forward(b200_ctx* ctx, const void* x, int64_t ldx, const void* residual, int64_t ldres, void* sum_out,
+                               int64_t ldsum, const void* gamma, const void* beta, void* y, int64_t ldy, float* mean,
+                               float* rstd, int64_t rows, int64_t cols, float eps, void* stream);
+int b200_layernorm_backward_add(b200_ctx* ctx, const void* dy, int64_t lddy, const void* x, int64_t ldx, const void* gamma,
+                                const float* mean, const float* rstd, const void* upstream, int64_t ldup, void* dx,
+                                int64_t lddx, float* dgamma_f32, float* dbeta_f32, int64_t rows, int64_t cols, void* stream);
 
 /* ---- element-wise ops on bf16 buffers ------------------------------------------------------------------------
  * Unary (ttnn::neg / relu / gtz / gelu / rsqrt ..., traced/ops.hpp:54-61; tensor (+,*) float forms, traced/ops.hpp:38-52). */

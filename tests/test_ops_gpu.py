@@ -243,3 +243,27 @@ def test_adam_two_steps_golden_and_validation(pkg, ctx, DT):
     for bad in (dict(lr=0.0), dict(eps=0.0), dict(betas=(1.0, 0.9)), dict(betas=(0.9,))):
         with pytest.raises(ValueError):   # tests/adam_optimizer.py:126-151
             pkg.nn.Adam(ctx, [p], **bad)
+
+
+@pytest.mark.parametrize("rows,cols", [(64, 768), (33, 520), (17, 100), (40, 1024), (9, 1600), (5, 2304)])
+def test_layernorm_with_fused_residual_add(pkg, ctx, DT, rows, cols):
+    """b200_add_layernorm_forward / b200_layernorm_backward_add against the separate oracle steps: the sum is rounded to
+    bf16 before it is normalised, as a separate add would leave it."""
+    x, res, dy, up = (rnd((rows, cols), s) for s in (11, 12, 13, 14))
+    gamma = rnd((cols,), 15) * 0.1 + 1
+    beta = rnd((cols,), 16) * 0.1
+    total, y = DT(ctx, (rows, cols)), DT(ctx, (rows, cols))
+    mean, rstd = DT(ctx, (rows,), pkg.F32), DT(ctx, (rows,), pkg.F32)
+    ctx.add_layernorm_forward(DT.from_numpy(ctx, x), DT.from_numpy(ctx, res), total, DT.from_numpy(ctx, gamma),
+                              DT.from_numpy(ctx, beta), y, mean, rstd, rows, cols)
+    ref_total = mo.bf16_round(x + res)
+    assert np.array_equal(total.numpy(), ref_total)
+    ref_y, ref_mean, ref_rstd = mo.layernorm_forward(ref_total, gamma, beta)
+    assert mo.rel_frobenius(y.numpy(), ref_y) <= TOL
+    assert np.allclose(mean.numpy(), ref_mean.ravel(), atol=1e-4) and np.allclose(rstd.numpy(), ref_rstd.ravel(), rtol=1e-3)
+    dx, dg, db = DT(ctx, (rows, cols)), DT(ctx, (cols,), pkg.F32), DT(ctx, (cols,), pkg.F32)
+    ctx.layernorm_backward_add(DT.from_numpy(ctx, dy), total, DT.from_numpy(ctx, gamma), mean, rstd, DT.from_numpy(ctx, up), dx,
+                               dg, db, rows, cols)
+    ref_dx, ref_dg, ref_db = mo.layernorm_backward(dy, ref_total, gamma, ref_mean, ref_rstd)
+    assert mo.rel_frobenius(dx.numpy(), mo.bf16_round(ref_dx) + up) <= TOL
+    assert mo.rel_frobenius(dg.numpy(), ref_dg) <= TOL and mo.rel_frobenius(db.numpy(), ref_db) <= TOL

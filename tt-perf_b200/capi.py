@@ -112,6 +112,12 @@ SIGNATURES = {
     "b200_layernorm_backward": (C.c_int, [C.c_void_p, C.c_void_p, C.c_int64, C.c_void_p, C.c_int64, C.c_void_p, C.c_void_p,
                                           C.c_void_p, C.c_void_p, C.c_int64, C.c_void_p, C.c_void_p, C.c_int64, C.c_int64,
                                           C.c_void_p]),
+    "b200_add_layernorm_forward": (C.c_int, [C.c_void_p, C.c_void_p, C.c_int64, C.c_void_p, C.c_int64, C.c_void_p, C.c_int64,
+                                             C.c_void_p, C.c_void_p, C.c_void_p, C.c_int64, C.c_void_p, C.c_void_p,
+                                             C.c_int64, C.c_int64, C.c_float, C.c_void_p]),
+    "b200_layernorm_backward_add": (C.c_int, [C.c_void_p, C.c_void_p, C.c_int64, C.c_void_p, C.c_int64, C.c_void_p,
+                                              C.c_void_p, C.c_void_p, C.c_void_p, C.c_int64, C.c_void_p, C.c_int64,
+                                              C.c_void_p, C.c_void_p, C.c_int64, C.c_int64, C.c_void_p]),
     "b200_unary": (C.c_int, [C.c_void_p, C.c_int, C.c_void_p, C.c_void_p, C.c_int64, C.c_float, C.c_void_p]),
     "b200_binary": (C.c_int, [C.c_void_p, C.c_int, C.c_void_p, C.POINTER(C.c_int64), C.c_void_p, C.POINTER(C.c_int64),
                               C.c_void_p, C.c_void_p]),
@@ -327,6 +333,18 @@ class Context:
     def layernorm_backward(self, dy, x, gamma, mean, rstd, dx, dgamma, dbeta, rows, cols, *, stream=None):
         check(lib().b200_layernorm_backward(self._h, ptr(dy), cols, ptr(x), cols, ptr(gamma), ptr(mean), ptr(rstd), ptr(dx),
                                             cols, ptr(dgamma), ptr(dbeta), rows, cols, self._s(stream)))
+
+    def add_layernorm_forward(self, x, residual, sum_out, gamma, beta, y, mean, rstd, rows, cols, *, eps=1e-5, stream=None):
+        """sum_out = x + residual; y = LayerNorm(sum_out)."""
+        check(lib().b200_add_layernorm_forward(self._h, ptr(x), cols, ptr(residual), cols, ptr(sum_out), cols, ptr(gamma),
+                                               ptr(beta), ptr(y), cols, ptr(mean), ptr(rstd), rows, cols, eps,
+                                               self._s(stream)))
+
+    def layernorm_backward_add(self, dy, x, gamma, mean, rstd, upstream, dx, dgamma, dbeta, rows, cols, *, stream=None):
+        """dx = LayerNorm'(dy) + upstream."""
+        check(lib().b200_layernorm_backward_add(self._h, ptr(dy), cols, ptr(x), cols, ptr(gamma), ptr(mean), ptr(rstd),
+                                                ptr(upstream), cols, ptr(dx), cols, ptr(dgamma), ptr(dbeta), rows, cols,
+                                                self._s(stream)))
 
     def unary(self, op, x, y, n, *, scalar=0.0, stream=None):
         check(lib().b200_unary(self._h, op, ptr(x), ptr(y), n, scalar, self._s(stream)))

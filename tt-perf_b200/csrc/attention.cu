@@ -4,17 +4,21 @@
 // autograd/traced/nn.hpp:164-192 (TracedCausalAttention) and transformer_train.hpp:54-70
 // (SharedAttentionBuffers::attention_forward / attention_backward) of the reference.
 //
-// Tiles are 128 queries x 128 keys. In TMEM a thread of the four compute warps owns one lane, i.e. one row of the
-// accumulator, so row maxima and row sums need no shuffles.
+// Tiles are 128 queries x 128 keys. A TMEM lane is one row of the accumulator; a warp reads the 32 lanes of its
+// quarter (warp index mod 4), and several warps share a quarter by taking different columns. Both kernels are bound by
+// the latency of their dependent steps (MMA -> exp -> MMA), so they run many compute warps per SM.
 //
 //   forward, one CTA per (batch, head, 128 queries), two CTAs per SM:
-//     issue warp   TMA loads of Q once and K, V double buffered; S = Q K^T; O_j = P V
-//     4 warps      S (TMEM) -> running max / sum -> P as bf16 into shared memory (the 128-byte-swizzled K-major
-//                  layout the next MMA reads) -> O = O * rescale + O_j in registers -> O / sum, lse
+//     thread 0     between the barriers: TMA loads of Q once and K, V double buffered; S = Q K^T; O_j = P V
+//     8 warps      a thread takes one row and one 64-column half of S: local maximum -> exchanged with the other half
+//                  through shared memory -> P = exp2(..) as bf16 into shared memory (the 128-byte-swizzled K-major
+//                  layout the next MMA reads). It also keeps 32 columns of O in registers; O_j is folded in one tile
+//                  late, when the next S is ready, so the wait for the P V product is off the critical path.
 //   backward, one CTA per (batch, head, 128 keys), looping over the query tiles that see those keys:
 //     issue warp   S^T = K Q^T, dP^T = V dO^T, then dV += P^T dO, dK += dS^T Q, dQ_i = dS K
-//     4 warps      P^T = exp(scale S^T - lse), dS^T = scale P^T (dP^T - rowsum(dO O)) into shared memory as bf16;
-//                  dQ_i from TMEM into fp32 accumulators with vector atomic adds; dK, dV at the end.
+//     16 warps     a thread takes one row (key) and 32 columns (queries): P^T = exp(scale S^T - lse),
+//                  dS^T = scale P^T (dP^T - rowsum(dO O)) into shared memory as bf16; then 16 columns of dQ_i from TMEM
+//                  into fp32 accumulators with vector atomic adds; dK, dV at the end.
 //   The single [128 keys x 128 queries] dS^T tile in shared memory is read both as a K-major A operand (dK) and as an
 //   MN-major A operand (dQ): the two readings share one physical layout.
 //
@@ -37,8 +41,9 @@ constexpr int BT = 128;                   // queries per tile and keys per tile
 constexpr int TILE_BYTES = BT * DH * 2;   // a [128 x 64] bf16 tile, rows of 128 bytes
 constexpr int PT_BYTES = BT * BT * 2;     // a [128 x 128] bf16 tile stored as two 64-column slabs of 16 KB
 constexpr int UMMA_K = 16;
-constexpr int THREADS = 160;              // 4 compute warps + the issue warp
-constexpr int ISSUE_WARP = 4;
+constexpr int FWD_THREADS = 256;   // 8 warps, all computing; thread 0 also issues the copies and MMAs
+constexpr int BWD_COMPUTE_WARPS = 16;
+constexpr int BWD_THREADS = (BWD_COMPUTE_WARPS + 1) * 32;
 constexpr float LOG2E = 1.4426950408889634f;
 constexpr float LN2 = 0.6931471805599453f;
 
@@ -60,7 +65,10 @@ __device__ __forceinline__ float ex2(float x) {
     return y;
 }
 
-__device__ __forceinline__ void compute_warps_sync() { asm volatile("bar.sync 1, 128;" ::: "memory"); }
+template <int THREADS>
+__device__ __forceinline__ void compute_warps_sync() {
+    asm volatile("bar.sync 1, %0;" ::"n"(THREADS) : "memory");
+}
 
 // Byte offset of the 16-byte unit `unit` (0..15, i.e. 8 bf16 columns each) of row `r` inside a [128 x 128] bf16 tile
 // kept as two 128-byte-swizzled slabs of 64 columns.
@@ -81,6 +89,18 @@ __device__ __forceinline__ void drain(uint64_t* bar, uint32_t parity) {
     }
 }
 
+#ifdef B200_ATTN_PROFILE
+// Clock stamps of selected warps (instrumented build only): [cta slot][warp slot][tile][stamp].
+__device__ long long g_attn_prof[4][4][16][8];
+#define ATTN_STAMP(cta_slot, warp_slot, tile, k)                                                        \
+    do {                                                                                                \
+        if ((cta_slot) >= 0 && (warp_slot) >= 0 && (tile) < 16 && lane == 0)                            \
+            g_attn_prof[cta_slot][warp_slot][tile][k] = clock64();                                      \
+    } while (0)
+#else
+#define ATTN_STAMP(cta_slot, warp_slot, tile, k) do { } while (0)
+#endif
+
 // ------------------------------------------------------------------------------------------------------------------
 // Forward
 // ------------------------------------------------------------------------------------------------------------------
@@ -92,12 +112,26 @@ struct FwdParams {
 };
 
 constexpr int FWD_TMEM_COLS = 256;  // S: columns 0..127, O_j: 128..191
-constexpr int FWD_SMEM_USED = 5 * TILE_BYTES + PT_BYTES + 64;
-// Two CTAs per SM: 2 * (FWD_SMEM + 1 KB the hardware reserves per CTA) = 228 KB exactly. That leaves 960 bytes, not
-// 1023, for rounding the base up to 1024; the kernel checks that the rounding it needs fits.
-constexpr int FWD_SMEM = FWD_SMEM_USED + 960;
+constexpr int FWD_SMEM_USED = 5 * TILE_BYTES + PT_BYTES + 64 + 512;  // tiles, barriers, row-maximum exchange
+// Two CTAs per SM have 2 * (FWD_SMEM + 1 KB the hardware reserves per CTA) <= 228 KB to share, which leaves no room for
+// rounding the base up to 1024: the kernel relies on the base being 1024-aligned already (it is when the kernel has no
+// static shared memory) and reports an error instead of running when it is not.
+constexpr int FWD_SMEM = FWD_SMEM_USED;
+static_assert(2 * (FWD_SMEM + 1024) <= 228 * 1024, "two forward CTAs must fit one SM");
 
-__global__ void __launch_bounds__(THREADS, 2)
+// Smallest bf16-representable value >= x, as its 16 high bits. The two threads that share a row exchange their local
+// maxima in this form: any common value >= the true maximum stabilises exp2 equally well, and 2 bytes per value is
+// what fits next to the tiles.
+__device__ __forceinline__ uint16_t ceil_bf16_bits(float x) {
+    const uint32_t u = __float_as_uint(x);
+    return static_cast<uint16_t>(((x >= 0.f) ? (u + 0xffffu) : u) >> 16);
+}
+__device__ __forceinline__ float bf16_bits_to_float(uint16_t b) { return __uint_as_float(static_cast<uint32_t>(b) << 16); }
+
+// 256 threads: registers are handed out to pairs of warps, so a ninth warp for issuing would cost a fifth of the
+// register file and the second CTA per SM with it. Thread 0 issues the copies and the MMAs between the barriers
+// instead; it has nothing else to do there but wait for the tensor cores.
+__global__ void __launch_bounds__(FWD_THREADS, 2)
 attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
                 const __grid_constant__ CUtensorMap tmV, const FwdParams p) {
     extern __shared__ uint8_t smem_raw[];
@@ -113,11 +147,13 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
     uint8_t* sP = sV + 2 * TILE_BYTES;
     uint64_t* q_full = reinterpret_cast<uint64_t*>(sP + PT_BYTES);
     uint64_t* kv_full = q_full + 1;      // 2
-    uint64_t* s_full = kv_full + 2;
-    uint64_t* p_ready = s_full + 1;
-    uint64_t* o_full = p_ready + 1;
+    uint64_t* s_full = kv_full + 2;      // S of a tile is in TMEM (and every earlier MMA has run)
+    uint64_t* o_full = s_full + 1;       // the last P V product has run
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(o_full + 1);
     volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+    // [column half][row] local maxima. One buffer is enough: nobody sees the next S before every thread has passed the
+    // barrier that follows the P stores, i.e. has read this tile's values.
+    uint16_t* xch = reinterpret_cast<uint16_t*>(reinterpret_cast<uint8_t*>(q_full) + 64);
 
     const int warp = threadIdx.x >> 5;
     const int lane = threadIdx.x & 31;
@@ -129,6 +165,10 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
     const int q0 = qt * BT;
     const int n_kv_all = (g.S + BT - 1) / BT;
     const int n_kv = g.causal ? min(qt + 1, n_kv_all) : n_kv_all;
+#ifdef B200_ATTN_PROFILE
+    const int prof_cta = (blockIdx.x == 0 && blockIdx.y < 4) ? static_cast<int>(blockIdx.y) : -1;
+    const int prof_warp = warp == 0 ? 0 : (warp == 4 ? 1 : (warp == 3 ? 2 : -1));
+#endif
 
     if (threadIdx.x == 0) {
         prefetch_tensormap(&tmQ);
@@ -138,12 +178,11 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
         mbar_init(&kv_full[0], 1);
         mbar_init(&kv_full[1], 1);
         mbar_init(s_full, 1);
-        mbar_init(p_ready, 128);
         mbar_init(o_full, 1);
         *abort_flag = 0;
         mbar_fence_init();
     }
-    if (warp == ISSUE_WARP) {
+    if (warp == 0) {
         tmem_alloc(tmem_slot, FWD_TMEM_COLS);
         tmem_relinquish_alloc_permit();
     }
@@ -152,146 +191,182 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
     tcgen05_fence_after_sync();
     const uint32_t tmem_base = *tmem_slot;
 
-    if (warp == ISSUE_WARP) {
-        if (lane == 0) {
-            constexpr uint32_t idesc_s = make_idesc_bf16_f32(BT, BT, 0u, 0u);   // Q (K-major) x K (K-major)
-            constexpr uint32_t idesc_o = make_idesc_bf16_f32(BT, DH, 0u, 1u);   // P (K-major) x V (MN-major)
-            int armed[2] = {0, 0};
-            auto load_kv = [&](int tile) {
-                const int st = tile & 1;
-                mbar_arrive_expect_tx(&kv_full[st], 2 * TILE_BYTES);
-                tma_load_4d(sK + st * TILE_BYTES, &tmK, &kv_full[st], 0, tile * BT, h, b);
-                tma_load_4d(sV + st * TILE_BYTES, &tmV, &kv_full[st], 0, tile * BT, h, b);
-                ++armed[st];
-            };
-            auto issue_s = [&](int tile) {
-                const uint32_t a = smem_u32(sQ);
-                const uint32_t bb = smem_u32(sK + (tile & 1) * TILE_BYTES);
+    constexpr uint32_t idesc_s = make_idesc_bf16_f32(BT, BT, 0u, 0u);   // Q (K-major) x K (K-major)
+    constexpr uint32_t idesc_o = make_idesc_bf16_f32(BT, DH, 0u, 1u);   // P (K-major) x V (MN-major)
+    int armed0 = 0, armed1 = 0;  // thread 0: how often each K/V stage has been armed
+    auto load_kv = [&](int tile) {
+        const int st = tile & 1;
+        mbar_arrive_expect_tx(&kv_full[st], 2 * TILE_BYTES);
+        tma_load_4d(sK + st * TILE_BYTES, &tmK, &kv_full[st], 0, tile * BT, h, b);
+        tma_load_4d(sV + st * TILE_BYTES, &tmV, &kv_full[st], 0, tile * BT, h, b);
+        if (st == 0) ++armed0; else ++armed1;
+    };
+    auto issue_s = [&](int tile) {
+        const uint32_t a = smem_u32(sQ);
+        const uint32_t bb = smem_u32(sK + (tile & 1) * TILE_BYTES);
 #pragma unroll
-                for (int k = 0; k < DH / UMMA_K; ++k)
-                    umma_f16_ss(tmem_base, make_smem_desc_sw128(a + k * 32, 0, 1024),
-                                make_smem_desc_sw128(bb + k * 32, 0, 1024), idesc_s, k > 0 ? 1u : 0u);
-                umma_commit(s_full);
-            };
-            mbar_arrive_expect_tx(q_full, TILE_BYTES);
-            tma_load_4d(sQ, &tmQ, q_full, 0, q0, h, b);
-            load_kv(0);
-            if (n_kv > 1) load_kv(1);
-            bool ok = mbar_wait(q_full, 0, abort_flag) && mbar_wait(&kv_full[0], 0, abort_flag);
-            if (ok) {
-                tcgen05_fence_after_sync();
-                issue_s(0);
+        for (int k = 0; k < DH / UMMA_K; ++k)
+            umma_f16_ss(tmem_base, make_smem_desc_sw128(a + k * 32, 0, 1024), make_smem_desc_sw128(bb + k * 32, 0, 1024),
+                        idesc_s, k > 0 ? 1u : 0u);
+        umma_commit(s_full);
+    };
+    bool issuer_ok = true;  // meaningful in thread 0 only
+    if (threadIdx.x == 0) {
+        mbar_arrive_expect_tx(q_full, TILE_BYTES);
+        tma_load_4d(sQ, &tmQ, q_full, 0, q0, h, b);
+        load_kv(0);
+        issuer_ok = mbar_wait(q_full, 0, abort_flag) && mbar_wait(&kv_full[0], 0, abort_flag);
+        if (issuer_ok) {
+            tcgen05_fence_after_sync();
+            issue_s(0);
+        }
+    }
+    __syncwarp();
+
+    const int quarter = warp & 3;
+    const int half = warp >> 2;          // columns [64 * half, 64 * half + 64) of S, [32 * half, +32) of O
+    const int r = quarter * 32 + lane;   // accumulator row = TMEM lane
+    const int row = q0 + r;
+    const uint32_t lane_addr = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16);
+    const int limit = g.causal ? min(row, g.S - 1) : g.S - 1;  // last visible key of this row
+    const float sl2 = g.scale_log2;
+    float m = -INFINITY, l = 0.f, alpha = 0.f;
+    float o[32];
+#pragma unroll
+    for (int i = 0; i < 32; ++i) o[i] = 0.f;
+    auto fold_pv = [&]() {  // O = O * alpha + (P V of the tile before)
+        uint32_t v[32];
+        tmem_ld_32x32b_x32(lane_addr + 128 + half * 32, v);
+        tmem_ld_wait();
+#pragma unroll
+        for (int i = 0; i < 32; ++i) o[i] = fmaf(o[i], alpha, __uint_as_float(v[i]));
+    };
+    // `ok` is uniform over the warp. A warp that gave up keeps walking the loop without touching TMEM or waiting, so
+    // that the other warps never wait for it at the named barriers.
+    bool ok = true;
+    for (int j = 0; j < n_kv; ++j) {
+        ATTN_STAMP(prof_cta, prof_warp, j, 0);
+        if (ok) {
+            // s_full of tile j is committed after the P V product of tile j - 1, so it covers both
+            const bool got = mbar_wait(s_full, j & 1, abort_flag);
+            ok = __all_sync(0xffffffffu, got);
+        }
+        ATTN_STAMP(prof_cta, prof_warp, j, 1);
+        if (threadIdx.x == 0 && ok && j + 1 < n_kv) load_kv(j + 1);  // its stage was last read by the P V product of j - 1
+        __syncwarp();
+        uint32_t s0[32], s1[32];
+        const int lim = limit - j * BT - half * 64;  // index, within this thread's 64 columns, of the last visible one
+        const bool masked = lim < 63;
+        uint16_t mine = 0;
+        if (ok) {
+            tcgen05_fence_after_sync();
+            if (j > 0) fold_pv();
+            tmem_ld_32x32b_x32(lane_addr + half * 64, s0);
+            tmem_ld_32x32b_x32(lane_addr + half * 64 + 32, s1);
+            tmem_ld_wait();
+            float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
+            if (!masked) {
+#pragma unroll
+                for (int i = 0; i < 32; ++i) {
+                    mx4[i & 3] = fmaxf(mx4[i & 3], __uint_as_float(s0[i]));
+                    mx4[i & 3] = fmaxf(mx4[i & 3], __uint_as_float(s1[i]));
+                }
+            } else {
+#pragma unroll
+                for (int i = 0; i < 32; ++i) {
+                    if (i <= lim) mx4[i & 3] = fmaxf(mx4[i & 3], __uint_as_float(s0[i]));
+                    if (i + 32 <= lim) mx4[i & 3] = fmaxf(mx4[i & 3], __uint_as_float(s1[i]));
+                }
             }
-            for (int j = 0; ok && j < n_kv; ++j) {
-                if (!mbar_wait(p_ready, j & 1, abort_flag)) { ok = false; break; }
-                tcgen05_fence_after_sync();
-                const uint32_t pa = smem_u32(sP);
-                const uint32_t vb = smem_u32(sV + (j & 1) * TILE_BYTES);
+            mine = ceil_bf16_bits(fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3])));
+            xch[half * BT + r] = mine;
+        }
+        ATTN_STAMP(prof_cta, prof_warp, j, 2);
+        compute_warps_sync<FWD_THREADS>();
+        ATTN_STAMP(prof_cta, prof_warp, j, 3);
+        if (ok) {
+            // finite: every tile shows each row at least one key
+            const float mx = fmaxf(m, fmaxf(bf16_bits_to_float(mine), bf16_bits_to_float(xch[(half ^ 1) * BT + r])));
+            alpha = ex2((m - mx) * sl2);  // 0 on the first tile (m = -inf)
+            const float mb = mx * sl2;
+            m = mx;
+            float rs4[4] = {0.f, 0.f, 0.f, 0.f};
+            auto emit = [&](const uint32_t (&sv)[32], int c) {  // 32 columns: probabilities, partial sums, bf16 store
 #pragma unroll
-                for (int k = 0; k < BT / UMMA_K; ++k)
-                    umma_f16_ss(tmem_base + 128, make_smem_desc_sw128(pa + (k >> 2) * TILE_BYTES + (k & 3) * 32, 0, 1024),
-                                make_smem_desc_sw128(vb + k * (UMMA_K * 128), BT * 128, 1024), idesc_o, k > 0 ? 1u : 0u);
-                umma_commit(o_full);
-                if (j + 1 < n_kv) {
-                    if (!mbar_wait(&kv_full[(j + 1) & 1], ((j + 1) >> 1) & 1, abort_flag)) { ok = false; break; }
+                for (int t = 0; t < 4; ++t) {
+                    float f[8];
+#pragma unroll
+                    for (int e = 0; e < 8; ++e) {
+                        const int i = t * 8 + e;
+                        float pr = ex2(fmaf(__uint_as_float(sv[i]), sl2, -mb));
+                        if (masked && c * 32 + i > lim) pr = 0.f;
+                        rs4[e & 3] += pr;
+                        f[e] = pr;
+                    }
+                    store_bf16x8(sP + pt_offset(r, half * 8 + c * 4 + t), f);
+                }
+            };
+            emit(s0, 0);
+            emit(s1, 1);
+            l = l * alpha + ((rs4[0] + rs4[1]) + (rs4[2] + rs4[3]));
+            fence_proxy_async_smem();
+            tcgen05_fence_before_sync();
+        }
+        ATTN_STAMP(prof_cta, prof_warp, j, 4);
+        compute_warps_sync<FWD_THREADS>();  // P is complete in shared memory; S and the old P V product have been read
+        if (threadIdx.x == 0 && ok && issuer_ok) {
+            tcgen05_fence_after_sync();
+            const uint32_t pa = smem_u32(sP);
+            const uint32_t vb = smem_u32(sV + (j & 1) * TILE_BYTES);
+#pragma unroll
+            for (int k = 0; k < BT / UMMA_K; ++k)
+                umma_f16_ss(tmem_base + 128, make_smem_desc_sw128(pa + (k >> 2) * TILE_BYTES + (k & 3) * 32, 0, 1024),
+                            make_smem_desc_sw128(vb + k * (UMMA_K * 128), BT * 128, 1024), idesc_o, k > 0 ? 1u : 0u);
+            if (j + 1 < n_kv) {
+                issuer_ok = mbar_wait(&kv_full[(j + 1) & 1], ((j + 1) >> 1) & 1, abort_flag);
+                if (issuer_ok) {
                     tcgen05_fence_after_sync();
                     issue_s(j + 1);
                 }
-                if (j + 2 < n_kv) {
-                    if (!mbar_wait(o_full, j & 1, abort_flag)) { ok = false; break; }  // K_j, V_j no longer read
-                    load_kv(j + 2);
-                }
-            }
-            if (!ok) {
-                if (armed[0]) drain(&kv_full[0], (armed[0] - 1) & 1);
-                if (armed[1]) drain(&kv_full[1], (armed[1] - 1) & 1);
-                drain(q_full, 0);
+            } else {
+                umma_commit(o_full);
             }
         }
-    } else {
-        const int r = threadIdx.x;  // accumulator row = TMEM lane
-        const int row = q0 + r;
-        const uint32_t lane_addr = tmem_base + (static_cast<uint32_t>(warp * 32) << 16);
-        // last visible key of this row
-        const int limit = g.causal ? min(row, g.S - 1) : g.S - 1;
-        const float sl2 = g.scale_log2;
-        float m = -INFINITY, l = 0.f;
-        float o[DH];
+        __syncwarp();
+        ATTN_STAMP(prof_cta, prof_warp, j, 5);
+    }
+    if (ok) {
+        const bool got = mbar_wait(o_full, 0, abort_flag);
+        ok = __all_sync(0xffffffffu, got);
+    }
+    float* lsum = reinterpret_cast<float*>(sP);  // once the last P V product is complete the P tile is free
+    if (ok) {
+        tcgen05_fence_after_sync();
+        fold_pv();
+        lsum[half * BT + r] = l;
+    }
+    compute_warps_sync<FWD_THREADS>();
+    if (ok && row < g.S) {
+        const float total = l + lsum[(half ^ 1) * BT + r];
+        const float inv = 1.f / total;
 #pragma unroll
-        for (int i = 0; i < DH; ++i) o[i] = 0.f;
-        bool ok = true;
-        for (int j = 0; j < n_kv; ++j) {
-            const bool got = mbar_wait(s_full, j & 1, abort_flag);
-            if (!__all_sync(0xffffffffu, got)) { ok = false; break; }
-            tcgen05_fence_after_sync();
-            const int lim = limit - j * BT;  // local index of the last visible column; >= 0 for every tile visited
-            const bool masked = lim < BT - 1;
-            float mx = m;
-#pragma unroll 1
-            for (int c = 0; c < 4; ++c) {
-                uint32_t v[32];
-                tmem_ld_32x32b_x32(lane_addr + c * 32, v);
-                tmem_ld_wait();
-                if (!masked) {
+        for (int i = 0; i < 32; ++i) o[i] *= inv;
+        uint8_t* dst = reinterpret_cast<uint8_t*>(p.o.ptr + b * p.o.sb + h * p.o.sh + static_cast<long long>(row) * p.o.ss +
+                                                  half * 32);
 #pragma unroll
-                    for (int i = 0; i < 32; ++i) mx = fmaxf(mx, __uint_as_float(v[i]));
-                } else {
-#pragma unroll
-                    for (int i = 0; i < 32; ++i)
-                        if (c * 32 + i <= lim) mx = fmaxf(mx, __uint_as_float(v[i]));
-                }
-            }
-            const float alpha = ex2((m - mx) * sl2);  // 0 on the first tile (m = -inf)
-            const float mb = mx * sl2;
-            m = mx;
-            float rs = 0.f;
-#pragma unroll 1
-            for (int c = 0; c < 4; ++c) {
-                uint32_t v[32];
-                tmem_ld_32x32b_x32(lane_addr + c * 32, v);
-                tmem_ld_wait();
-                float f[32];
-#pragma unroll
-                for (int i = 0; i < 32; ++i) {
-                    float pr = ex2(fmaf(__uint_as_float(v[i]), sl2, -mb));
-                    if (masked && c * 32 + i > lim) pr = 0.f;
-                    rs += pr;
-                    f[i] = pr;
-                }
-#pragma unroll
-                for (int t = 0; t < 4; ++t) store_bf16x8(sP + pt_offset(r, c * 4 + t), f + 8 * t);
-            }
-            l = l * alpha + rs;
-            fence_proxy_async_smem();
-            tcgen05_fence_before_sync();
-            mbar_arrive(p_ready);
-            const bool got_o = mbar_wait(o_full, j & 1, abort_flag);
-            if (!__all_sync(0xffffffffu, got_o)) { ok = false; break; }
-            tcgen05_fence_after_sync();
-#pragma unroll
-            for (int hh = 0; hh < 2; ++hh) {
-                uint32_t v[32];
-                tmem_ld_32x32b_x32(lane_addr + 128 + hh * 32, v);
-                tmem_ld_wait();
-#pragma unroll
-                for (int i = 0; i < 32; ++i) o[hh * 32 + i] = fmaf(o[hh * 32 + i], alpha, __uint_as_float(v[i]));
-            }
-        }
-        if (ok && row < g.S) {
-            const float inv = 1.f / l;
-#pragma unroll
-            for (int i = 0; i < DH; ++i) o[i] *= inv;
-            uint8_t* dst = reinterpret_cast<uint8_t*>(p.o.ptr + b * p.o.sb + h * p.o.sh + static_cast<long long>(row) * p.o.ss);
-#pragma unroll
-            for (int t = 0; t < DH / 8; ++t) store_bf16x8(dst + t * 16, o + 8 * t);
-            p.lse[(static_cast<long long>(bh)) * g.S + row] = (m * sl2 + log2f(l)) * LN2;
-        }
+        for (int t = 0; t < 4; ++t) store_bf16x8(dst + t * 16, o + 8 * t);
+        if (half == 0) p.lse[(static_cast<long long>(bh)) * g.S + row] = (m * sl2 + log2f(total)) * LN2;
+    }
+    if (threadIdx.x == 0 && *abort_flag != 0) {  // let armed copies land before the shared memory is released
+        if (armed0) drain(&kv_full[0], (armed0 - 1) & 1);
+        if (armed1) drain(&kv_full[1], (armed1 - 1) & 1);
+        drain(q_full, 0);
     }
 
     tcgen05_fence_before_sync();
     __syncthreads();
     if (threadIdx.x == 0 && *abort_flag != 0) atomicExch(p.status, 1);
-    if (warp == ISSUE_WARP) {
+    if (warp == 0) {
         tcgen05_fence_after_sync();
         tmem_dealloc(tmem_base, FWD_TMEM_COLS);
     }
@@ -312,7 +387,7 @@ struct BwdParams {
 constexpr int BWD_TMEM_COLS = 512;  // S^T 0..127, dP^T 128..255, dK 256..319, dV 320..383, dQ_i 384..447
 constexpr int BWD_SMEM = 6 * TILE_BYTES + 2 * PT_BYTES + 2048 + 64 + 1024;
 
-__global__ void __launch_bounds__(THREADS, 1)
+__global__ void __launch_bounds__(BWD_THREADS, 1)
 attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
                 const __grid_constant__ CUtensorMap tmV, const __grid_constant__ CUtensorMap tmdO, const BwdParams p) {
     extern __shared__ uint8_t smem_raw[];
@@ -327,10 +402,11 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
     float* dsum_s = lse_s + 2 * BT;                            // [2][128]
     uint64_t* kv_full = reinterpret_cast<uint64_t*>(dsum_s + 2 * BT);
     uint64_t* qdo_full = kv_full + 1;     // 2
-    uint64_t* sdp_full = qdo_full + 2;
-    uint64_t* pds_ready = sdp_full + 1;
-    uint64_t* dq_full = pds_ready + 1;
-    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(dq_full + 1);
+    uint64_t* sdp_full = qdo_full + 2;    // S^T and dP^T of a tile are in TMEM
+    uint64_t* pds_ready = sdp_full + 1;   // P^T and dS^T of a tile are in shared memory
+    uint64_t* dq_full = pds_ready + 1;    // dQ_i is in TMEM
+    uint64_t* acc_done = dq_full + 1;     // the dV and dK products of a tile have run
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_done + 1);
     volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
     const int warp = threadIdx.x >> 5;
@@ -353,12 +429,13 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
         mbar_init(&qdo_full[0], 1);
         mbar_init(&qdo_full[1], 1);
         mbar_init(sdp_full, 1);
-        mbar_init(pds_ready, 128);
+        mbar_init(pds_ready, BWD_COMPUTE_WARPS);  // one arrival per warp
         mbar_init(dq_full, 1);
+        mbar_init(acc_done, 1);
         *abort_flag = 0;
         mbar_fence_init();
     }
-    if (warp == ISSUE_WARP) {
+    if (warp == BWD_COMPUTE_WARPS) {
         tmem_alloc(tmem_slot, BWD_TMEM_COLS);
         tmem_relinquish_alloc_permit();
     }
@@ -367,7 +444,7 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
     tcgen05_fence_after_sync();
     const uint32_t tmem_base = *tmem_slot;
 
-    if (warp == ISSUE_WARP) {
+    if (warp == BWD_COMPUTE_WARPS) {
         if (lane == 0) {
             constexpr uint32_t idesc_nt = make_idesc_bf16_f32(BT, BT, 0u, 0u);  // both operands K-major, N = 128
             constexpr uint32_t idesc_kn = make_idesc_bf16_f32(BT, DH, 0u, 1u);  // A K-major, B MN-major, N = 64
@@ -401,9 +478,16 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
                 for (int k = 0; k < DH / UMMA_K; ++k)   // dP^T = V dO^T
                     umma_f16_ss(tmem_base + 128, make_smem_desc_sw128(va + k * 32, 0, 1024),
                                 make_smem_desc_sw128(doa + k * 32, 0, 1024), idesc_nt, k > 0 ? 1u : 0u);
+                // This commit also covers the dV and dK products of the tile before: once it fires P^T and dS^T may be
+                // overwritten.
                 umma_commit(sdp_full);
                 if (!mbar_wait(pds_ready, it & 1, abort_flag)) { ok = false; break; }
                 tcgen05_fence_after_sync();
+#pragma unroll
+                for (int k = 0; k < BT / UMMA_K; ++k)   // dQ_i = dS K (reduction over the 128 keys); first, it is read first
+                    umma_f16_ss(tmem_base + 384, make_smem_desc_sw128(dsa + k * (UMMA_K * 128), BT * 128, 1024),
+                                make_smem_desc_sw128(ka + k * (UMMA_K * 128), BT * 128, 1024), idesc_mn, k > 0 ? 1u : 0u);
+                umma_commit(dq_full);
 #pragma unroll
                 for (int k = 0; k < BT / UMMA_K; ++k)   // dV += P^T dO   (reduction over the 128 queries)
                     umma_f16_ss(tmem_base + 320, make_smem_desc_sw128(pta + (k >> 2) * TILE_BYTES + (k & 3) * 32, 0, 1024),
@@ -414,13 +498,9 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
                     umma_f16_ss(tmem_base + 256, make_smem_desc_sw128(dsa + (k >> 2) * TILE_BYTES + (k & 3) * 32, 0, 1024),
                                 make_smem_desc_sw128(qa + k * (UMMA_K * 128), BT * 128, 1024), idesc_kn,
                                 (it > 0 || k > 0) ? 1u : 0u);
-#pragma unroll
-                for (int k = 0; k < BT / UMMA_K; ++k)   // dQ_i = dS K     (reduction over the 128 keys)
-                    umma_f16_ss(tmem_base + 384, make_smem_desc_sw128(dsa + k * (UMMA_K * 128), BT * 128, 1024),
-                                make_smem_desc_sw128(ka + k * (UMMA_K * 128), BT * 128, 1024), idesc_mn, k > 0 ? 1u : 0u);
-                umma_commit(dq_full);
+                umma_commit(acc_done);
                 if (it + 2 < n_it) {
-                    if (!mbar_wait(dq_full, it & 1, abort_flag)) { ok = false; break; }  // Q_i, dO_i no longer read
+                    if (!mbar_wait(acc_done, it & 1, abort_flag)) { ok = false; break; }  // Q_i, dO_i no longer read
                     load_qdo(it + 2);
                 }
             }
@@ -431,92 +511,106 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
             }
         }
     } else {
-        const int r = threadIdx.x;  // TMEM lane: key row for S^T, dP^T, dK, dV; query row for dQ_i
-        const uint32_t lane_addr = tmem_base + (static_cast<uint32_t>(warp * 32) << 16);
+        const int quarter = warp & 3;
+        const int cg = warp >> 2;            // columns [32 * cg, +32) of S^T / dP^T; [16 * cg, +16) of dQ_i, dK, dV
+        const int r = quarter * 32 + lane;   // TMEM lane: key row for S^T, dP^T, dK, dV; query row for dQ_i
+        const uint32_t lane_addr = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16);
         const float sl2 = g.scale_log2;
+        // `ok` is uniform over the warp. A warp that gave up keeps walking the loop without touching TMEM or waiting, so
+        // that the other warps never wait for it at the named barrier.
         bool ok = true;
         for (int it = 0; it < n_it; ++it) {
             const int st = it & 1;
             const int i = i0 + it;
-            const int qrow = i * BT + r;
-            const long long stat = static_cast<long long>(bh) * g.S + qrow;
-            lse_s[st * BT + r] = qrow < g.S ? p.lse[stat] * LOG2E : INFINITY;  // +inf: probability 0 for padding queries
-            dsum_s[st * BT + r] = qrow < g.S ? p.dsum[stat] : 0.f;
-            compute_warps_sync();
-            const bool got = mbar_wait(sdp_full, it & 1, abort_flag);
-            if (!__all_sync(0xffffffffu, got)) { ok = false; break; }
-            tcgen05_fence_after_sync();
-            const bool diag = g.causal && i == jt;  // query (column) c sees key (row) r only when c >= r
-#pragma unroll 1
-            for (int c = 0; c < 4; ++c) {
-                uint32_t s[32], dp[32];
-                tmem_ld_32x32b_x32(lane_addr + c * 32, s);
-                tmem_ld_32x32b_x32(lane_addr + 128 + c * 32, dp);
+            if (threadIdx.x < 2 * BT) {  // stage this query tile's lse (times log2 e) and rowsum(dO O)
+                const int which = threadIdx.x >> 7, idx = threadIdx.x & (BT - 1);
+                const int qi = i * BT + idx;
+                const long long at = static_cast<long long>(bh) * g.S + qi;
+                if (which == 0)
+                    lse_s[st * BT + idx] = qi < g.S ? p.lse[at] * LOG2E : INFINITY;  // +inf: probability 0 for padding
+                else
+                    dsum_s[st * BT + idx] = qi < g.S ? p.dsum[at] : 0.f;
+            }
+            compute_warps_sync<BWD_COMPUTE_WARPS * 32>();
+            if (ok) {
+                const bool got = mbar_wait(sdp_full, it & 1, abort_flag);
+                ok = __all_sync(0xffffffffu, got);
+            }
+            if (ok) {
+                tcgen05_fence_after_sync();
+                const bool diag = g.causal && i == jt;  // query (column) c sees key (row) r only when c >= r
+                uint32_t sv[32], dp[32];
+                tmem_ld_32x32b_x32(lane_addr + cg * 32, sv);
+                tmem_ld_32x32b_x32(lane_addr + 128 + cg * 32, dp);
                 tmem_ld_wait();
-                float pf[32], df[32];
-                const float4* l4 = reinterpret_cast<const float4*>(lse_s + st * BT + c * 32);
-                const float4* d4 = reinterpret_cast<const float4*>(dsum_s + st * BT + c * 32);
-#pragma unroll
-                for (int u = 0; u < 8; ++u) {
-                    const float4 lv = l4[u];
-                    const float4 dv = d4[u];
-                    const float ls[4] = {lv.x, lv.y, lv.z, lv.w};
-                    const float ds[4] = {dv.x, dv.y, dv.z, dv.w};
-#pragma unroll
-                    for (int e = 0; e < 4; ++e) {
-                        const int idx = u * 4 + e;
-                        float pr = ex2(fmaf(__uint_as_float(s[idx]), sl2, -ls[e]));
-                        if (diag && c * 32 + idx < r) pr = 0.f;
-                        pf[idx] = pr;
-                        df[idx] = pr * (__uint_as_float(dp[idx]) - ds[e]) * g.scale;
-                    }
-                }
+                const float4* l4 = reinterpret_cast<const float4*>(lse_s + st * BT + cg * 32);
+                const float4* d4 = reinterpret_cast<const float4*>(dsum_s + st * BT + cg * 32);
 #pragma unroll
                 for (int t = 0; t < 4; ++t) {
-                    const uint32_t off = pt_offset(r, c * 4 + t);
-                    store_bf16x8(sPT + off, pf + 8 * t);
-                    store_bf16x8(sdST + off, df + 8 * t);
-                }
-            }
-            fence_proxy_async_smem();
-            tcgen05_fence_before_sync();
-            mbar_arrive(pds_ready);
-            const bool got_dq = mbar_wait(dq_full, it & 1, abort_flag);
-            if (!__all_sync(0xffffffffu, got_dq)) { ok = false; break; }
-            tcgen05_fence_after_sync();
-            float4* acc = reinterpret_cast<float4*>(p.dq_acc + stat * DH);
+                    float pf[8], df[8];
 #pragma unroll
-            for (int hh = 0; hh < 2; ++hh) {
-                uint32_t v[32];
-                tmem_ld_32x32b_x32(lane_addr + 384 + hh * 32, v);
+                    for (int u = 0; u < 2; ++u) {
+                        const float4 lv = l4[t * 2 + u];
+                        const float4 dv = d4[t * 2 + u];
+                        const float ls[4] = {lv.x, lv.y, lv.z, lv.w};
+                        const float ds[4] = {dv.x, dv.y, dv.z, dv.w};
+#pragma unroll
+                        for (int e = 0; e < 4; ++e) {
+                            const int idx = t * 8 + u * 4 + e;
+                            float pr = ex2(fmaf(__uint_as_float(sv[idx]), sl2, -ls[e]));
+                            if (diag && cg * 32 + idx < r) pr = 0.f;
+                            pf[u * 4 + e] = pr;
+                            df[u * 4 + e] = pr * (__uint_as_float(dp[idx]) - ds[e]) * g.scale;
+                        }
+                    }
+                    const uint32_t off = pt_offset(r, cg * 4 + t);
+                    store_bf16x8(sPT + off, pf);
+                    store_bf16x8(sdST + off, df);
+                }
+                fence_proxy_async_smem();
+                tcgen05_fence_before_sync();
+                __syncwarp();
+                if (lane == 0) mbar_arrive(pds_ready);
+                const bool got_dq = mbar_wait(dq_full, it & 1, abort_flag);
+                ok = __all_sync(0xffffffffu, got_dq);
+            }
+            if (ok) {
+                tcgen05_fence_after_sync();
+                const int qrow = i * BT + r;
+                uint32_t v[16];
+                tmem_ld_32x32b_x16(lane_addr + 384 + cg * 16, v);
                 tmem_ld_wait();
                 if (qrow < g.S) {
+                    float4* acc = reinterpret_cast<float4*>(p.dq_acc + (static_cast<long long>(bh) * g.S + qrow) * DH + cg * 16);
 #pragma unroll
-                    for (int t = 0; t < 8; ++t)
-                        atomicAdd(acc + hh * 8 + t, make_float4(__uint_as_float(v[4 * t]), __uint_as_float(v[4 * t + 1]),
-                                                                 __uint_as_float(v[4 * t + 2]), __uint_as_float(v[4 * t + 3])));
+                    for (int t = 0; t < 4; ++t)
+                        atomicAdd(acc + t, make_float4(__uint_as_float(v[4 * t]), __uint_as_float(v[4 * t + 1]),
+                                                       __uint_as_float(v[4 * t + 2]), __uint_as_float(v[4 * t + 3])));
                 }
+                tcgen05_fence_before_sync();
             }
         }
         if (ok) {
-            // the last dq_full also covers the final dK / dV accumulation
+            const bool got = mbar_wait(acc_done, (n_it - 1) & 1, abort_flag);
+            ok = __all_sync(0xffffffffu, got);
+        }
+        if (ok) {
+            tcgen05_fence_after_sync();
             const int key = jt * BT + r;
 #pragma unroll
             for (int which = 0; which < 2; ++which) {
                 const Strided& dst = which == 0 ? p.dk : p.dv;
-                uint8_t* out = reinterpret_cast<uint8_t*>(dst.ptr + b * dst.sb + h * dst.sh + static_cast<long long>(key) * dst.ss);
+                uint32_t v[16];
+                tmem_ld_32x32b_x16(lane_addr + 256 + which * 64 + cg * 16, v);
+                tmem_ld_wait();
+                if (key < g.S) {
+                    uint8_t* out = reinterpret_cast<uint8_t*>(dst.ptr + b * dst.sb + h * dst.sh + static_cast<long long>(key) * dst.ss +
+                                                              cg * 16);
+                    float f[16];
 #pragma unroll
-                for (int hh = 0; hh < 2; ++hh) {
-                    uint32_t v[32];
-                    tmem_ld_32x32b_x32(lane_addr + 256 + which * 64 + hh * 32, v);
-                    tmem_ld_wait();
-                    if (key < g.S) {
-                        float f[32];
-#pragma unroll
-                        for (int e = 0; e < 32; ++e) f[e] = __uint_as_float(v[e]);
-#pragma unroll
-                        for (int t = 0; t < 4; ++t) store_bf16x8(out + hh * 64 + t * 16, f + 8 * t);
-                    }
+                    for (int e = 0; e < 16; ++e) f[e] = __uint_as_float(v[e]);
+                    store_bf16x8(out, f);
+                    store_bf16x8(out + 16, f + 8);
                 }
             }
         }
@@ -525,7 +619,7 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
     tcgen05_fence_before_sync();
     __syncthreads();
     if (threadIdx.x == 0 && *abort_flag != 0) atomicExch(p.status, 1);
-    if (warp == ISSUE_WARP) {
+    if (warp == BWD_COMPUTE_WARPS) {
         tcgen05_fence_after_sync();
         tmem_dealloc(tmem_base, BWD_TMEM_COLS);
     }
@@ -626,6 +720,9 @@ int configure_once(K kernel, int smem_bytes, bool (&done)[64]) {
     B200_CUDA_TRY(cudaGetDevice(&dev));
     if (dev < 0 || dev >= 64 || !done[dev]) {
         B200_CUDA_TRY(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes));
+        // Without this the driver sizes the shared-memory carve-out for one CTA and a second one never fits.
+        B200_CUDA_TRY(cudaFuncSetAttribute(kernel, cudaFuncAttributePreferredSharedMemoryCarveout,
+                                           cudaSharedmemCarveoutMaxShared));
         if (dev >= 0 && dev < 64) done[dev] = true;
     }
     return B200_OK;
@@ -657,6 +754,23 @@ using namespace b200;
 
 extern "C" {
 
+#ifdef B200_ATTN_PROFILE
+int b200_debug_attn_occupancy_at(int smem, int* blocks) {
+    B200_CUDA_TRY(cudaOccupancyMaxActiveBlocksPerMultiprocessor(blocks, attn_fwd_kernel, FWD_THREADS, smem));
+    return B200_OK;
+}
+int b200_debug_attn_occupancy(int* fwd_blocks, int* bwd_blocks) {
+    B200_CUDA_TRY(cudaOccupancyMaxActiveBlocksPerMultiprocessor(fwd_blocks, attn_fwd_kernel, FWD_THREADS, FWD_SMEM));
+    B200_CUDA_TRY(cudaOccupancyMaxActiveBlocksPerMultiprocessor(bwd_blocks, attn_bwd_kernel, BWD_THREADS, BWD_SMEM));
+    return B200_OK;
+}
+int b200_debug_attn_prof(void* host_out) {
+    B200_CUDA_TRY(cudaDeviceSynchronize());
+    B200_CUDA_TRY(cudaMemcpyFromSymbol(host_out, g_attn_prof, sizeof(g_attn_prof)));
+    return B200_OK;
+}
+#endif
+
 int b200_attention_forward(b200_ctx* ctx, const b200_attn_operand* q, const b200_attn_operand* k, const b200_attn_operand* v,
                            const b200_attn_operand* o, float* lse, int64_t B, int64_t H, int64_t S, int head_dim,
                            float scale, int causal, void* stream_v) {
@@ -683,7 +797,7 @@ int b200_attention_forward(b200_ctx* ctx, const b200_attn_operand* q, const b200
     static bool configured[64] = {};
     if ((rc = configure_once(attn_fwd_kernel, FWD_SMEM, configured)) != B200_OK) return rc;
     const dim3 grid(static_cast<unsigned>((S + BT - 1) / BT), static_cast<unsigned>(B * H));
-    attn_fwd_kernel<<<grid, THREADS, FWD_SMEM, stream>>>(tmQ, tmK, tmV, p);
+    attn_fwd_kernel<<<grid, FWD_THREADS, FWD_SMEM, stream>>>(tmQ, tmK, tmV, p);
     B200_CUDA_TRY(cudaGetLastError());
     return B200_OK;
 }
@@ -732,7 +846,7 @@ int b200_attention_backward(b200_ctx* ctx, const b200_attn_operand* q, const b20
     static bool configured[64] = {};
     if ((rc = configure_once(attn_bwd_kernel, BWD_SMEM, configured)) != B200_OK) return rc;
     const dim3 grid(static_cast<unsigned>((S + BT - 1) / BT), static_cast<unsigned>(B * H));
-    attn_bwd_kernel<<<grid, THREADS, BWD_SMEM, stream>>>(tmQ, tmK, tmV, tmdO, p);
+    attn_bwd_kernel<<<grid, BWD_THREADS, BWD_SMEM, stream>>>(tmQ, tmK, tmV, tmdO, p);
     B200_CUDA_TRY(cudaGetLastError());
     attn_dq_store_kernel<<<blocks, 256, 0, stream>>>(dq_acc, as_out(d_q), static_cast<int>(B), static_cast<int>(H),
                                                      static_cast<int>(S));

@@ -88,8 +88,8 @@ int b200_ctx_create(int device_ordinal, b200_ctx** out_ctx) {
         delete ctx;
         return fail(B200_ERR_CUDA, "cudaStreamCreate failed: %s", cudaGetErrorString(e));
     }
-    e = cudaMalloc(&ctx->d_status, 256);
-    if (e == cudaSuccess) e = cudaMemset(ctx->d_status, 0, 256);
+    e = cudaMalloc(&ctx->d_status, b200::kStatusBytes);
+    if (e == cudaSuccess) e = cudaMemset(ctx->d_status, 0, b200::kStatusBytes);
     if (e != cudaSuccess) {
         cudaStreamDestroy(ctx->stream);
         delete ctx;

@@ -80,11 +80,7 @@ __device__ __forceinline__ float binary_apply(int op, float a, float b) {
         case B_MUL: return a * b;
         case B_DIV: return a / b;
         case B_RELU_BW: return b > 0.0f ? a : 0.0f;  // a = dy, b = x
-        case B_GELU_BW: {                             // a = dy, b = x; derivative of the exact (erf) GELU
-            const float cdf = 0.5f * (1.0f + erff(b * 0.70710678118654752f));
-            const float pdf = 0.3989422804014327f * __expf(-0.5f * b * b);
-            return a * (cdf + b * pdf);
-        }
+        case B_GELU_BW: return a * gelu_exact_grad(b);  // a = dy, b = x; derivative of the exact (erf) GELU
         case B_MAX: return fmaxf(a, b);
         default: return a;
     }
@@ -305,6 +301,88 @@ __global__ void __launch_bounds__(kThreads) reduce_cols_kernel(const __nv_bfloat
             }
         }
     }
+}
+
+// Column reduction in one launch. Each CTA reduces its slab of rows for 32 column groups into fp32 partials
+// part[outer][row_block][inner]; the CTA that finishes last for a column block (a ticket counter tells it) combines the
+// partials, scales, rounds to bf16 and puts the counter back to zero. No zero-fill, no atomics on the data, no cast pass,
+// and the result does not depend on the order in which the CTAs ran.
+template <int VEC>
+__global__ void __launch_bounds__(kThreads) reduce_cols_ticket_kernel(const __nv_bfloat16* x, float* part, unsigned* tickets,
+                                                                       __nv_bfloat16* y, long long R, long long inner, int op,
+                                                                       long long rows_per_cta, float scale) {
+    __shared__ float sh[8][32][VEC + 1];
+    __shared__ int is_last;
+    const long long o = blockIdx.z;
+    const int row_blocks = gridDim.y;
+    const long long c = (blockIdx.x * 32ll + (threadIdx.x & 31)) * VEC;
+    const int sub = threadIdx.x >> 5;
+    const long long r0 = blockIdx.y * rows_per_cta, r1 = min(R, r0 + rows_per_cta);
+    float acc[VEC];
+#pragma unroll
+    for (int k = 0; k < VEC; ++k) acc[k] = (op == R_MAX) ? -FLT_MAX : 0.0f;
+    if (c < inner) {
+        const __nv_bfloat16* base = x + o * R * inner + c;
+        for (long long r = r0 + sub; r < r1; r += 8) {
+            if (VEC == 8) {
+                float f[8];
+                unpack8(*reinterpret_cast<const uint4*>(base + r * inner), f);
+#pragma unroll
+                for (int k = 0; k < 8; ++k) acc[k] = (op == R_MAX) ? fmaxf(acc[k], f[k]) : acc[k] + f[k];
+            } else {
+                const float f = __bfloat162float(base[r * inner]);
+                acc[0] = (op == R_MAX) ? fmaxf(acc[0], f) : acc[0] + f;
+            }
+        }
+    }
+#pragma unroll
+    for (int k = 0; k < VEC; ++k) sh[sub][threadIdx.x & 31][k] = acc[k];
+    __syncthreads();
+    // thread t now owns column (t / VEC-group, t % VEC) of the CTA's 32 * VEC columns: consecutive threads, consecutive columns
+    const int cols_here = 32 * VEC;
+    float* my_part = part + (o * row_blocks + blockIdx.y) * inner;
+    const long long c0 = blockIdx.x * static_cast<long long>(cols_here);
+    for (int t = threadIdx.x; t < cols_here; t += kThreads) {
+        if (c0 + t >= inner) break;
+        float a = sh[0][t / VEC][t % VEC];
+#pragma unroll
+        for (int j = 1; j < 8; ++j) {
+            const float other = sh[j][t / VEC][t % VEC];
+            a = (op == R_MAX) ? fmaxf(a, other) : a + other;
+        }
+        my_part[c0 + t] = a;
+    }
+    __threadfence();
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        const unsigned ticket = atomicAdd(&tickets[o * gridDim.x + blockIdx.x], 1u);
+        is_last = ticket == static_cast<unsigned>(row_blocks - 1);
+    }
+    __syncthreads();
+    if (!is_last) return;
+    __threadfence();
+    for (int t = threadIdx.x; t < cols_here; t += kThreads) {
+        if (c0 + t >= inner) break;
+        const float* col = part + o * row_blocks * inner + c0 + t;
+        float a4[4];
+#pragma unroll
+        for (int k = 0; k < 4; ++k) a4[k] = (op == R_MAX) ? -FLT_MAX : 0.0f;
+        int rb = 0;
+        for (; rb + 4 <= row_blocks; rb += 4) {
+#pragma unroll
+            for (int k = 0; k < 4; ++k) {
+                const float v = __ldcg(col + (rb + k) * inner);
+                a4[k] = (op == R_MAX) ? fmaxf(a4[k], v) : a4[k] + v;
+            }
+        }
+        for (; rb < row_blocks; ++rb) {
+            const float v = __ldcg(col + rb * inner);
+            a4[0] = (op == R_MAX) ? fmaxf(a4[0], v) : a4[0] + v;
+        }
+        const float a = (op == R_MAX) ? fmaxf(fmaxf(a4[0], a4[1]), fmaxf(a4[2], a4[3])) : (a4[0] + a4[1]) + (a4[2] + a4[3]);
+        y[o * inner + c0 + t] = __float2bfloat16_rn(a * scale);
+    }
+    if (threadIdx.x == 0) tickets[o * gridDim.x + blockIdx.x] = 0u;
 }
 
 __global__ void fill_f32_kernel(float* p, long long n, float v) {
@@ -535,25 +613,46 @@ int b200_reduce(b200_ctx* ctx, int op, const void* x, int64_t outer, int64_t R, 
         B200_CUDA_TRY(cudaGetLastError());
         return B200_OK;
     }
-    // column reduction: fp32 accumulators in context scratch, then a cast
+    // column reduction
     const long long outs = outer * inner;
+    const bool vec8 = al16(x) && (inner % 8 == 0);
+    const long long col_blocks = vec8 ? (inner / 8 + 31) / 32 : (inner + 31) / 32;
+    B200_REQUIRE(outer <= 65535, "b200_reduce: outer dimension too large for a column reduction");
+    const float scale = op == R_MEAN ? 1.0f / static_cast<float>(R) : 1.0f;
+    if (col_blocks * outer <= kTicketCount) {
+        // one launch: per-CTA partials, the last CTA of a column block combines them
+        long long row_blocks = std::max<long long>(1, std::min<long long>(std::min<long long>((R + 31) / 32, 64),
+                                                                           (ctx->sm_count * 4ll) / std::max<long long>(1, col_blocks * outer)));
+        const long long rows_per = (R + row_blocks - 1) / row_blocks;
+        row_blocks = (R + rows_per - 1) / rows_per;
+        int rc = ensure_scratch(ctx, static_cast<size_t>(outs) * row_blocks * sizeof(float));
+        if (rc != B200_OK) return rc;
+        float* part = static_cast<float*>(ctx->d_scratch);
+        dim3 grid(static_cast<unsigned>(col_blocks), static_cast<unsigned>(row_blocks), static_cast<unsigned>(outer));
+        if (vec8)
+            reduce_cols_ticket_kernel<8><<<grid, kThreads, 0, s>>>(static_cast<const __nv_bfloat16*>(x), part, ctx_tickets(ctx),
+                                                                   static_cast<__nv_bfloat16*>(y), R, inner, op, rows_per, scale);
+        else
+            reduce_cols_ticket_kernel<1><<<grid, kThreads, 0, s>>>(static_cast<const __nv_bfloat16*>(x), part, ctx_tickets(ctx),
+                                                                   static_cast<__nv_bfloat16*>(y), R, inner, op, rows_per, scale);
+        B200_CUDA_TRY(cudaGetLastError());
+        return B200_OK;
+    }
+    // very wide outputs: fp32 accumulators in context scratch combined with atomics, then a cast
     int rc = ensure_scratch(ctx, static_cast<size_t>(outs) * sizeof(float));
     if (rc != B200_OK) return rc;
     float* acc = static_cast<float*>(ctx->d_scratch);
     fill_f32_kernel<<<grid_for(ctx, outs), kThreads, 0, s>>>(acc, outs, op == R_MAX ? -FLT_MAX : 0.0f);
-    const bool vec8 = al16(x) && (inner % 8 == 0);
-    const long long col_blocks = vec8 ? (inner / 8 + 31) / 32 : (inner + 31) / 32;
     long long row_blocks = std::max<long long>(1, std::min<long long>((R + 63) / 64, (ctx->sm_count * 4ll) / std::max<long long>(1, col_blocks * outer)));
     const long long rows_per = (R + row_blocks - 1) / row_blocks;
     row_blocks = (R + rows_per - 1) / rows_per;
-    B200_REQUIRE(outer <= 65535 && row_blocks <= 65535, "b200_reduce: outer dimension too large for a column reduction");
+    B200_REQUIRE(row_blocks <= 65535, "b200_reduce: too many row blocks");
     dim3 grid(static_cast<unsigned>(col_blocks), static_cast<unsigned>(row_blocks), static_cast<unsigned>(outer));
     if (vec8)
         reduce_cols_kernel<8><<<grid, kThreads, 0, s>>>(static_cast<const __nv_bfloat16*>(x), acc, R, inner, op, rows_per);
     else
         reduce_cols_kernel<1><<<grid, kThreads, 0, s>>>(static_cast<const __nv_bfloat16*>(x), acc, R, inner, op, rows_per);
-    cast_f32_to_bf16_kernel<<<grid_for(ctx, outs), kThreads, 0, s>>>(acc, static_cast<__nv_bfloat16*>(y), outs,
-                                                                     op == R_MEAN ? 1.0f / static_cast<float>(R) : 1.0f);
+    cast_f32_to_bf16_kernel<<<grid_for(ctx, outs), kThreads, 0, s>>>(acc, static_cast<__nv_bfloat16*>(y), outs, scale);
     B200_CUDA_TRY(cudaGetLastError());
     return B200_OK;
 }

@@ -17,7 +17,32 @@ struct EpiParams {
 
 __device__ __forceinline__ float bf16_bits_to_float(uint16_t b) { return __uint_as_float(static_cast<uint32_t>(b) << 16); }
 
-__device__ __forceinline__ float gelu_exact(float x) { return 0.5f * x * (1.0f + erff(x * 0.70710678118654752f)); }
+// Phi(x) = 0.5 (1 + erf(x / sqrt 2)) and exp(-x^2 / 2) together, from the rational approximation 7.1.26 of Abramowitz &
+// Stegun (|error of erf| <= 1.5e-7, far below bf16 resolution): one reciprocal, one exp2 and a degree-5 polynomial
+// instead of the branching library erff. The exponential is the one the derivative of GELU needs as well.
+__device__ __forceinline__ void normal_cdf_and_exp(float x, float& cdf, float& e) {
+    const float z = fabsf(x) * 0.70710678118654752f;
+    float t;
+    asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(t) : "f"(fmaf(0.3275911f, z, 1.0f)));
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(e) : "f"(x * x * -0.72134752044448170f));  // exp(-x^2 / 2)
+    float poly = fmaf(t, 1.061405429f, -1.453152027f);
+    poly = fmaf(poly, t, 1.421413741f);
+    poly = fmaf(poly, t, -0.284496736f);
+    poly = fmaf(poly, t, 0.254829592f);
+    const float half_tail = 0.5f * poly * t * e;  // 0.5 * (1 - erf(|x| / sqrt 2))
+    cdf = x >= 0.0f ? 1.0f - half_tail : half_tail;
+}
+__device__ __forceinline__ float gelu_exact(float x) {
+    float cdf, e;
+    normal_cdf_and_exp(x, cdf, e);
+    return x * cdf;
+}
+// d/dx [x Phi(x)] = Phi(x) + x phi(x), phi the standard normal density.
+__device__ __forceinline__ float gelu_exact_grad(float x) {
+    float cdf, e;
+    normal_cdf_and_exp(x, cdf, e);
+    return fmaf(x * 0.3989422804014327f, e, cdf);
+}
 __device__ __forceinline__ float gelu_tanh_approx(float x) {
     const float k = 0.7978845608028654f;  // sqrt(2/pi)
     return 0.5f * x * (1.0f + tanhf(k * (x + 0.044715f * x * x * x)));

@@ -509,11 +509,12 @@ int check_rows(const char* who, const void* a, long long lda, long long rows, lo
 // ---- LayerNorm -------------------------------------------------------------------------------------
 // Forward: one warp per row for cols <= 2048 (row in registers), else one CTA per row.
 template <int VPL>
-__global__ void __launch_bounds__(kBlock, VPL <= 4 ? 4 : 2) layernorm_fw_warp_kernel(const __nv_bfloat16* x, long long ldx,
+__global__ void __launch_bounds__(kBlock, VPL <= 4 ? 3 : 2) layernorm_fw_warp_kernel(const __nv_bfloat16* x, long long ldx,
                                                                     const __nv_bfloat16* gamma, const __nv_bfloat16* beta,
                                                                     __nv_bfloat16* y, long long ldy, float* mean_out,
                                                                     float* rstd_out, int rows, int cols, float eps, int vx,
-                                                                    int vy, int vg) {
+                                                                    int vy, int vg, const __nv_bfloat16* res, long long ldres,
+                                                                    __nv_bfloat16* sum_out, long long ldsum, int vres) {
     const int lane = threadIdx.x & 31;
     const int r = blockIdx.x * (kBlock / kWarp) + (threadIdx.x >> 5);
     if (r >= rows) return;
@@ -522,7 +523,15 @@ __global__ void __launch_bounds__(kBlock, VPL <= 4 ? 4 : 2) layernorm_fw_warp_ke
     float s = 0.0f;
 #pragma unroll
     for (int j = 0; j < VPL; ++j) {
-        load8(xr, (j * kWarp + lane) * 8, cols, vx != 0, 0.0f, a[j]);
+        const int c = (j * kWarp + lane) * 8;
+        load8(xr, c, cols, vx != 0, 0.0f, a[j]);
+        if (res != nullptr) {  // normalise x + res; the sum (rounded to bf16, as a separate add would) is also an output
+            float rv[8];
+            load8(res + static_cast<size_t>(r) * ldres, c, cols, vres != 0, 0.0f, rv);
+#pragma unroll
+            for (int i = 0; i < 8; ++i) a[j][i] = __bfloat162float(__float2bfloat16_rn(a[j][i] + rv[i]));
+            if (c < cols) store8(sum_out + static_cast<size_t>(r) * ldsum, c, cols, vres != 0, a[j]);
+        }
 #pragma unroll
         for (int i = 0; i < 8; ++i) s += a[j][i];
     }
@@ -637,6 +646,96 @@ __global__ void __launch_bounds__(kBlock, VPL <= 4 ? 3 : 2) layernorm_bw_dx_warp
 #pragma unroll
         for (int i = 0; i < 8; ++i) g[j][i] = rs * (g[j][i] - s1 - xh[j][i] * s2);
         store8(dx + static_cast<size_t>(r) * lddx, c, cols, vdx != 0, g[j]);
+    }
+}
+
+// Backward in one pass for rows that fit a warp's registers: a persistent grid, one warp per row at a time.
+//   dx      = rstd * (g - mean(g) - xhat * mean(g * xhat)),  g = dy * gamma   (+ `upstream`, when given: the gradient
+//             that reaches the same tensor along the residual path, so that no separate add runs)
+//   dgamma += sum_rows dy * xhat,  dbeta += sum_rows dy: every lane keeps fp32 partial sums for the columns it owns over
+//             all the rows its warp visits; the warps of a CTA combine them in shared memory and the CTA adds one value
+//             per column to the zero-initialised fp32 outputs.
+template <int VPL>
+__global__ void __launch_bounds__(kBlock, VPL <= 3 ? 2 : 1) layernorm_bw_fused_warp_kernel(
+    const __nv_bfloat16* dy, long long lddy, const __nv_bfloat16* x, long long ldx, const __nv_bfloat16* gamma,
+    const float* mean, const float* rstd, const __nv_bfloat16* upstream, long long ldup, __nv_bfloat16* dx, long long lddx,
+    float* dgamma_acc, float* dbeta_acc, int rows, int cols, int vdy, int vx, int vdx, int vg, int vup) {
+    constexpr int WARPS = kBlock / kWarp;
+    __shared__ float red[WARPS][kWarp * 8 + 1];
+    const int lane = threadIdx.x & 31;
+    const int warp = threadIdx.x >> 5;
+    float gm[VPL][8];
+    float ag[VPL][8], ab[VPL][8];
+#pragma unroll
+    for (int j = 0; j < VPL; ++j) {
+        load8(gamma, (j * kWarp + lane) * 8, cols, vg != 0, 0.0f, gm[j]);
+#pragma unroll
+        for (int i = 0; i < 8; ++i) ag[j][i] = ab[j][i] = 0.0f;
+    }
+    const bool params = dgamma_acc != nullptr || dbeta_acc != nullptr;
+    for (int r = blockIdx.x * WARPS + warp; r < rows; r += gridDim.x * WARPS) {
+        const float mu = mean[r], rs = rstd[r];
+        float g[VPL][8], xh[VPL][8];
+        float s1 = 0.0f, s2 = 0.0f;
+#pragma unroll
+        for (int j = 0; j < VPL; ++j) {
+            const int c = (j * kWarp + lane) * 8;
+            load8(dy + static_cast<size_t>(r) * lddy, c, cols, vdy != 0, 0.0f, g[j]);
+            load8(x + static_cast<size_t>(r) * ldx, c, cols, vx != 0, 0.0f, xh[j]);
+#pragma unroll
+            for (int i = 0; i < 8; ++i) {
+                const bool in = c + i < cols;
+                xh[j][i] = in ? (xh[j][i] - mu) * rs : 0.0f;
+                if (params) {
+                    ab[j][i] += g[j][i];
+                    ag[j][i] = fmaf(g[j][i], xh[j][i], ag[j][i]);
+                }
+                g[j][i] = in ? g[j][i] * gm[j][i] : 0.0f;
+                s1 += g[j][i];
+                s2 = fmaf(g[j][i], xh[j][i], s2);
+            }
+        }
+        s1 = warp_sum(s1) / cols;
+        s2 = warp_sum(s2) / cols;
+        if (dx != nullptr) {
+#pragma unroll
+            for (int j = 0; j < VPL; ++j) {
+                const int c = (j * kWarp + lane) * 8;
+                if (c >= cols) continue;
+                float up[8];
+                if (upstream != nullptr) load8(upstream + static_cast<size_t>(r) * ldup, c, cols, vup != 0, 0.0f, up);
+#pragma unroll
+                for (int i = 0; i < 8; ++i) {
+                    g[j][i] = rs * (g[j][i] - s1 - xh[j][i] * s2);
+                    // the separate form rounds dx to bf16 before the add; keep that rounding
+                    if (upstream != nullptr) g[j][i] = __bfloat162float(__float2bfloat16_rn(g[j][i])) + up[i];
+                }
+                store8(dx + static_cast<size_t>(r) * lddx, c, cols, vdx != 0, g[j]);
+            }
+        }
+    }
+    if (!params) return;
+    // combine the warps' partial sums: one column slab (32 lanes x 8 columns) at a time, dgamma then dbeta
+#pragma unroll
+    for (int which = 0; which < 2; ++which) {
+        float* out = which == 0 ? dgamma_acc : dbeta_acc;
+        if (out == nullptr) continue;
+#pragma unroll
+        for (int j = 0; j < VPL; ++j) {
+            __syncthreads();
+#pragma unroll
+            for (int i = 0; i < 8; ++i) red[warp][lane * 8 + i] = which == 0 ? ag[j][i] : ab[j][i];
+            __syncthreads();
+            // 256 threads, 256 columns of this slab: thread t sums column t over the warps
+            const int t = threadIdx.x;
+            const int c = j * kWarp * 8 + t;
+            if (c < cols) {
+                float a = 0.0f;
+#pragma unroll
+                for (int w = 0; w < WARPS; ++w) a += red[w][t];
+                atomicAdd(&out[c], a);
+            }
+        }
     }
 }
 
@@ -847,67 +946,123 @@ int b200_cross_entropy(b200_ctx* ctx, const void* logits, int64_t ld, const uint
     return launch_row_op<OP_CROSS_ENTROPY>(p, ctx->pick(stream));
 }
 
-int b200_layernorm_forward(b200_ctx* ctx, const void* x, int64_t ldx, const void* gamma, const void* beta, void* y,
-                           int64_t ldy, float* mean, float* rstd, int64_t rows, int64_t cols, float eps, void* stream) {
-    B200_REQUIRE(ctx != nullptr, "b200_layernorm_forward: ctx is NULL");
-    int rc = check_rows("b200_layernorm_forward", x, ldx, rows, cols);
-    if (rc == B200_OK) rc = check_rows("b200_layernorm_forward", y, ldy, rows, cols);
+static int layernorm_forward_impl(const char* fn, b200_ctx* ctx, const void* x, int64_t ldx, const void* residual,
+                                  int64_t ldres, void* sum_out, int64_t ldsum, const void* gamma, const void* beta, void* y,
+                                  int64_t ldy, float* mean, float* rstd, int64_t rows, int64_t cols, float eps, void* stream) {
+    B200_REQUIRE(ctx != nullptr, "%s: ctx is NULL", fn);
+    int rc = check_rows(fn, x, ldx, rows, cols);
+    if (rc == B200_OK) rc = check_rows(fn, y, ldy, rows, cols);
+    if (rc == B200_OK && residual) rc = check_rows(fn, residual, ldres, rows, cols);
+    if (rc == B200_OK && residual) rc = check_rows(fn, sum_out, ldsum, rows, cols);
     if (rc != B200_OK) return rc;
     if (rows == 0 || cols == 0) return B200_OK;
-    B200_REQUIRE(gamma && beta, "b200_layernorm_forward: gamma or beta is NULL");
+    B200_REQUIRE(gamma && beta, "%s: gamma or beta is NULL", fn);
     DeviceScope scope(ctx->device);
     cudaStream_t s = ctx->pick(stream);
     const auto* xp = static_cast<const __nv_bfloat16*>(x);
     const auto* gp = static_cast<const __nv_bfloat16*>(gamma);
     const auto* bp = static_cast<const __nv_bfloat16*>(beta);
+    const auto* rp = static_cast<const __nv_bfloat16*>(residual);
+    auto* sp = static_cast<__nv_bfloat16*>(sum_out);
     auto* yp = static_cast<__nv_bfloat16*>(y);
-    const int vx = vec_ok(x, ldx), vy = vec_ok(y, ldy), vg = vec_ok(gamma, 8) & vec_ok(beta, 8);
     const int r = static_cast<int>(rows), c = static_cast<int>(cols);
+    if (residual != nullptr && c > 2048) {
+        // rows too long for the register-resident kernel: add first, then normalise the sum
+        const int64_t shape[4] = {1, 1, rows, cols};
+        B200_REQUIRE(ldx == cols && ldres == cols && ldsum == cols, "%s: rows longer than 2048 must be contiguous", fn);
+        rc = b200_binary(ctx, 0 /* add */, x, shape, residual, shape, sum_out, stream);
+        if (rc != B200_OK) return rc;
+        xp = sp;
+        ldx = ldsum;
+        rp = nullptr;
+    }
+    const int vx = vec_ok(xp, ldx), vy = vec_ok(y, ldy), vg = vec_ok(gamma, 8) & vec_ok(beta, 8);
+    const int vres = rp ? (vec_ok(rp, ldres) & vec_ok(sp, ldsum)) : 0;
     const int blocks = (r + 7) / 8;
     if (c <= 512)
-        layernorm_fw_warp_kernel<2><<<blocks, kBlock, 0, s>>>(xp, ldx, gp, bp, yp, ldy, mean, rstd, r, c, eps, vx, vy, vg);
+        layernorm_fw_warp_kernel<2><<<blocks, kBlock, 0, s>>>(xp, ldx, gp, bp, yp, ldy, mean, rstd, r, c, eps, vx, vy, vg, rp, ldres, sp, ldsum, vres);
+    else if (c <= 768)
+        layernorm_fw_warp_kernel<3><<<blocks, kBlock, 0, s>>>(xp, ldx, gp, bp, yp, ldy, mean, rstd, r, c, eps, vx, vy, vg, rp, ldres, sp, ldsum, vres);
     else if (c <= 1024)
-        layernorm_fw_warp_kernel<4><<<blocks, kBlock, 0, s>>>(xp, ldx, gp, bp, yp, ldy, mean, rstd, r, c, eps, vx, vy, vg);
+        layernorm_fw_warp_kernel<4><<<blocks, kBlock, 0, s>>>(xp, ldx, gp, bp, yp, ldy, mean, rstd, r, c, eps, vx, vy, vg, rp, ldres, sp, ldsum, vres);
     else if (c <= 2048)
-        layernorm_fw_warp_kernel<8><<<blocks, kBlock, 0, s>>>(xp, ldx, gp, bp, yp, ldy, mean, rstd, r, c, eps, vx, vy, vg);
+        layernorm_fw_warp_kernel<8><<<blocks, kBlock, 0, s>>>(xp, ldx, gp, bp, yp, ldy, mean, rstd, r, c, eps, vx, vy, vg, rp, ldres, sp, ldsum, vres);
     else
         layernorm_fw_block_kernel<<<r, kBlock, 0, s>>>(xp, ldx, gp, bp, yp, ldy, mean, rstd, r, c, eps, vx, vy, vg);
     B200_CUDA_TRY(cudaGetLastError());
     return B200_OK;
 }
 
-int b200_layernorm_backward(b200_ctx* ctx, const void* dy, int64_t lddy, const void* x, int64_t ldx, const void* gamma,
-                            const float* mean, const float* rstd, void* dx, int64_t lddx, float* dgamma_f32,
-                            float* dbeta_f32, int64_t rows, int64_t cols, void* stream) {
-    B200_REQUIRE(ctx != nullptr, "b200_layernorm_backward: ctx is NULL");
-    int rc = check_rows("b200_layernorm_backward", dy, lddy, rows, cols);
-    if (rc == B200_OK) rc = check_rows("b200_layernorm_backward", x, ldx, rows, cols);
-    if (rc == B200_OK && dx) rc = check_rows("b200_layernorm_backward", dx, lddx, rows, cols);
+int b200_layernorm_forward(b200_ctx* ctx, const void* x, int64_t ldx, const void* gamma, const void* beta, void* y,
+                           int64_t ldy, float* mean, float* rstd, int64_t rows, int64_t cols, float eps, void* stream) {
+    return layernorm_forward_impl("b200_layernorm_forward", ctx, x, ldx, nullptr, 0, nullptr, 0, gamma, beta, y, ldy, mean,
+                                  rstd, rows, cols, eps, stream);
+}
+
+int b200_add_layernorm_forward(b200_ctx* ctx, const void* x, int64_t ldx, const void* residual, int64_t ldres, void* sum_out,
+                               int64_t ldsum, const void* gamma, const void* beta, void* y, int64_t ldy, float* mean,
+                               float* rstd, int64_t rows, int64_t cols, float eps, void* stream) {
+    B200_REQUIRE(residual != nullptr && sum_out != nullptr, "b200_add_layernorm_forward: residual or sum_out is NULL");
+    return layernorm_forward_impl("b200_add_layernorm_forward", ctx, x, ldx, residual, ldres, sum_out, ldsum, gamma, beta, y,
+                                  ldy, mean, rstd, rows, cols, eps, stream);
+}
+
+static int layernorm_backward_impl(const char* fn, b200_ctx* ctx, const void* dy, int64_t lddy, const void* x, int64_t ldx,
+                                   const void* gamma, const float* mean, const float* rstd, const void* upstream,
+                                   int64_t ldup, void* dx, int64_t lddx, float* dgamma_f32, float* dbeta_f32, int64_t rows,
+                                   int64_t cols, void* stream) {
+    B200_REQUIRE(ctx != nullptr, "%s: ctx is NULL", fn);
+    int rc = check_rows(fn, dy, lddy, rows, cols);
+    if (rc == B200_OK) rc = check_rows(fn, x, ldx, rows, cols);
+    if (rc == B200_OK && dx) rc = check_rows(fn, dx, lddx, rows, cols);
+    if (rc == B200_OK && upstream) rc = check_rows(fn, upstream, ldup, rows, cols);
     if (rc != B200_OK) return rc;
+    B200_REQUIRE(upstream == nullptr || dx != nullptr, "%s: upstream given without dx", fn);
     DeviceScope scope(ctx->device);
     cudaStream_t s = ctx->pick(stream);
     const int r = static_cast<int>(rows), c = static_cast<int>(cols);
     if (dgamma_f32 && c > 0) B200_CUDA_TRY(cudaMemsetAsync(dgamma_f32, 0, sizeof(float) * c, s));
     if (dbeta_f32 && c > 0) B200_CUDA_TRY(cudaMemsetAsync(dbeta_f32, 0, sizeof(float) * c, s));
     if (rows == 0 || cols == 0) return B200_OK;
-    B200_REQUIRE(mean && rstd, "b200_layernorm_backward: mean or rstd is NULL");
+    B200_REQUIRE(mean && rstd, "%s: mean or rstd is NULL", fn);
     const auto* dyp = static_cast<const __nv_bfloat16*>(dy);
     const auto* xp = static_cast<const __nv_bfloat16*>(x);
-    if (dx) {
-        B200_REQUIRE(gamma != nullptr, "b200_layernorm_backward: gamma is NULL");
+    const auto* upp = static_cast<const __nv_bfloat16*>(upstream);
+    auto* dxp = static_cast<__nv_bfloat16*>(dx);
+    if (c <= 1024 && gamma != nullptr && (dx != nullptr || dgamma_f32 || dbeta_f32)) {
+        // one pass: dx, the residual add and the parameter gradients
         const auto* gp = static_cast<const __nv_bfloat16*>(gamma);
-        auto* dxp = static_cast<__nv_bfloat16*>(dx);
+        const int vdy = vec_ok(dy, lddy), vx = vec_ok(x, ldx), vdx = dx ? vec_ok(dx, lddx) : 0, vg = gamma ? vec_ok(gamma, 8) : 0;
+        const int vup = upstream ? vec_ok(upstream, ldup) : 0;
+        const int blocks = std::max(1, std::min((r + 7) / 8, ctx->sm_count * 2));
+        if (c <= 512)
+            layernorm_bw_fused_warp_kernel<2><<<blocks, kBlock, 0, s>>>(dyp, lddy, xp, ldx, gp, mean, rstd, upp, ldup, dxp, lddx,
+                                                                        dgamma_f32, dbeta_f32, r, c, vdy, vx, vdx, vg, vup);
+        else if (c <= 768)
+            layernorm_bw_fused_warp_kernel<3><<<blocks, kBlock, 0, s>>>(dyp, lddy, xp, ldx, gp, mean, rstd, upp, ldup, dxp, lddx,
+                                                                        dgamma_f32, dbeta_f32, r, c, vdy, vx, vdx, vg, vup);
+        else
+            layernorm_bw_fused_warp_kernel<4><<<blocks, kBlock, 0, s>>>(dyp, lddy, xp, ldx, gp, mean, rstd, upp, ldup, dxp, lddx,
+                                                                        dgamma_f32, dbeta_f32, r, c, vdy, vx, vdx, vg, vup);
+        B200_CUDA_TRY(cudaGetLastError());
+        return B200_OK;
+    }
+    if (dx) {
+        B200_REQUIRE(gamma != nullptr, "%s: gamma is NULL", fn);
+        const auto* gp = static_cast<const __nv_bfloat16*>(gamma);
         const int vdy = vec_ok(dy, lddy), vx = vec_ok(x, ldx), vdx = vec_ok(dx, lddx), vg = vec_ok(gamma, 8);
         const int blocks = (r + 7) / 8;
-        if (c <= 512)
-            layernorm_bw_dx_warp_kernel<2><<<blocks, kBlock, 0, s>>>(dyp, lddy, xp, ldx, gp, mean, rstd, dxp, lddx, r, c, vdy, vx, vdx, vg);
-        else if (c <= 1024)
-            layernorm_bw_dx_warp_kernel<4><<<blocks, kBlock, 0, s>>>(dyp, lddy, xp, ldx, gp, mean, rstd, dxp, lddx, r, c, vdy, vx, vdx, vg);
-        else if (c <= 2048)
+        if (c <= 2048)
             layernorm_bw_dx_warp_kernel<8><<<blocks, kBlock, 0, s>>>(dyp, lddy, xp, ldx, gp, mean, rstd, dxp, lddx, r, c, vdy, vx, vdx, vg);
         else
             layernorm_bw_dx_block_kernel<<<r, kBlock, 0, s>>>(dyp, lddy, xp, ldx, gp, mean, rstd, dxp, lddx, r, c, vdy, vx, vdx, vg);
         B200_CUDA_TRY(cudaGetLastError());
+        if (upstream) {
+            const int64_t shape[4] = {1, 1, rows, cols};
+            B200_REQUIRE(lddx == cols && ldup == cols, "%s: rows longer than 1024 must be contiguous when upstream is given", fn);
+            rc = b200_binary(ctx, 0 /* add */, dx, shape, upstream, shape, dx, stream);
+            if (rc != B200_OK) return rc;
+        }
     }
     if (dgamma_f32 || dbeta_f32) {
         const bool vec8 = vec_ok(dy, lddy) && vec_ok(x, ldx) && (c % 8 == 0);
@@ -923,6 +1078,21 @@ int b200_layernorm_backward(b200_ctx* ctx, const void* dy, int64_t lddy, const v
         B200_CUDA_TRY(cudaGetLastError());
     }
     return B200_OK;
+}
+
+int b200_layernorm_backward(b200_ctx* ctx, const void* dy, int64_t lddy, const void* x, int64_t ldx, const void* gamma,
+                            const float* mean, const float* rstd, void* dx, int64_t lddx, float* dgamma_f32,
+                            float* dbeta_f32, int64_t rows, int64_t cols, void* stream) {
+    return layernorm_backward_impl("b200_layernorm_backward", ctx, dy, lddy, x, ldx, gamma, mean, rstd, nullptr, 0, dx, lddx,
+                                   dgamma_f32, dbeta_f32, rows, cols, stream);
+}
+
+int b200_layernorm_backward_add(b200_ctx* ctx, const void* dy, int64_t lddy, const void* x, int64_t ldx, const void* gamma,
+                                const float* mean, const float* rstd, const void* upstream, int64_t ldup, void* dx,
+                                int64_t lddx, float* dgamma_f32, float* dbeta_f32, int64_t rows, int64_t cols, void* stream) {
+    B200_REQUIRE(upstream != nullptr && dx != nullptr, "b200_layernorm_backward_add: upstream or dx is NULL");
+    return layernorm_backward_impl("b200_layernorm_backward_add", ctx, dy, lddy, x, ldx, gamma, mean, rstd, upstream, ldup, dx,
+                                   lddx, dgamma_f32, dbeta_f32, rows, cols, stream);
 }
 
 }  // extern "C"

@@ -93,11 +93,24 @@ def layernorm_forward(ctx, x, gamma, beta, *, eps=1e-5, stream=None):
     return y, mean, rstd
 
 
-def layernorm_backward(ctx, d_y, x, gamma, mean, rstd, *, stream=None):
+def add_layernorm_forward(ctx, x, residual, gamma, beta, *, eps=1e-5, stream=None):
+    """(x + residual, LayerNorm(x + residual), mean, rstd) in one pass over the rows."""
+    rows, cols = _rows(x), x.shape[-1]
+    total, y = DeviceTensor(ctx, x.shape, BF16), DeviceTensor(ctx, x.shape, BF16)
+    mean, rstd = DeviceTensor(ctx, (rows,), F32), DeviceTensor(ctx, (rows,), F32)
+    ctx.add_layernorm_forward(x, residual, total, gamma, beta, y, mean, rstd, rows, cols, eps=eps, stream=stream)
+    return total, y, mean, rstd
+
+
+def layernorm_backward(ctx, d_y, x, gamma, mean, rstd, *, upstream=None, stream=None):
+    """(dx, dgamma, dbeta); with `upstream`, dx also includes that gradient (the residual path) without a separate add."""
     rows, cols = _rows(x), x.shape[-1]
     d_x = DeviceTensor(ctx, x.shape, BF16)
     dg, db = DeviceTensor(ctx, (cols,), F32), DeviceTensor(ctx, (cols,), F32)
-    ctx.layernorm_backward(d_y, x, gamma, mean, rstd, d_x, dg, db, rows, cols, stream=stream)
+    if upstream is None:
+        ctx.layernorm_backward(d_y, x, gamma, mean, rstd, d_x, dg, db, rows, cols, stream=stream)
+    else:
+        ctx.layernorm_backward_add(d_y, x, gamma, mean, rstd, upstream, d_x, dg, db, rows, cols, stream=stream)
     return d_x, dg, db
 
 
@@ -234,14 +247,19 @@ def _head_operands(ctx, t, heads, parts=1):
     return [ctx.attn_operand(t, s * width, dh, width, offset=i * heads * dh) for i in range(parts)]
 
 
-def transformer_block_forward(ctx, x, w, heads, *, stream=None):
-    """x [B, S, D]; w: dict with ln1_g, ln1_b, wq, bq, wk, bk, wv, bv, wo, bo, ln2_g, ln2_b, w1, b1, w2, b2, and
+def transformer_block_forward(ctx, x, w, heads, *, defer_add=False, stream=None):
+    """x [B, S, D], or a pair (a, b) standing for a + b not yet summed (the sum then happens inside the first LayerNorm
+    pass); w: dict with ln1_g, ln1_b, wq, bq, wk, bk, wv, bv, wo, bo, ln2_g, ln2_b, w1, b1, w2, b2, and
     optionally wqkv [3D, D] / bqkv [3D] (the three projections stacked, of which wq.. are then row views): one GEMM
     instead of three. With head dimension 64 the attention runs in the fused kernels on the projection outputs as
-    they lie; other head dimensions take the materialised softmax path. Returns (out, cache)."""
+    they lie; other head dimensions take the materialised softmax path. Returns (out, cache); with defer_add the output
+    is returned as the pair (residual, mlp_out) for the next consumer to sum."""
+    if isinstance(x, tuple):
+        x, ln1, mean1, rstd1 = add_layernorm_forward(ctx, x[0], x[1], w["ln1_g"], w["ln1_b"], stream=stream)
+    else:
+        ln1, mean1, rstd1 = layernorm_forward(ctx, x, w["ln1_g"], w["ln1_b"], stream=stream)
     b, s, d = x.shape
     dh = d // heads
-    ln1, mean1, rstd1 = layernorm_forward(ctx, x, w["ln1_g"], w["ln1_b"], stream=stream)
     cache = dict(x=x, ln1=ln1, mean1=mean1, rstd1=rstd1)
     if dh == FUSED_HEAD_DIM:
         if "wqkv" in w:
@@ -264,14 +282,16 @@ def transformer_block_forward(ctx, x, w, heads, *, stream=None):
         attn, p = causal_attention_forward(ctx, q, k, v, stream=stream)
         merged = merge_heads(ctx, attn, stream=stream)
         cache.update(q=q, k=k, v=v, p=p)
-    res1 = add(ctx, x, linear_forward(ctx, merged, w["wo"], w["bo"], stream=stream), stream=stream)
-    ln2, mean2, rstd2 = layernorm_forward(ctx, res1, w["ln2_g"], w["ln2_b"], stream=stream)
+    res1, ln2, mean2, rstd2 = add_layernorm_forward(ctx, x, linear_forward(ctx, merged, w["wo"], w["bo"], stream=stream),
+                                                    w["ln2_g"], w["ln2_b"], stream=stream)
     h1 = linear_forward(ctx, ln2, w["w1"], w["b1"], stream=stream)
     h1g = DeviceTensor(ctx, h1.shape, BF16)
     ctx.unary(capi.U_GELU, h1, h1g, h1g.numel, stream=stream)
-    out = add(ctx, res1, linear_forward(ctx, h1g, w["w2"], w["b2"], stream=stream), stream=stream)
+    mlp_out = linear_forward(ctx, h1g, w["w2"], w["b2"], stream=stream)
     cache.update(merged=merged, res1=res1, ln2=ln2, mean2=mean2, rstd2=rstd2, h1=h1, h1g=h1g)
-    return out, cache
+    if defer_add:
+        return (res1, mlp_out), cache
+    return add(ctx, res1, mlp_out, stream=stream), cache
 
 
 def transformer_block_backward(ctx, d_out, w, cache, heads, *, stream=None):
@@ -282,9 +302,8 @@ def transformer_block_backward(ctx, d_out, w, cache, heads, *, stream=None):
     d_h1g, g["w2"], g["b2"] = linear_backward(ctx, c["h1g"], w["w2"], d_out, stream=stream)
     d_h1 = gelu_backward(ctx, d_h1g, c["h1"], stream=stream)
     d_ln2, g["w1"], g["b1"] = linear_backward(ctx, c["ln2"], w["w1"], d_h1, stream=stream)
-    d_res1_ln, g["ln2_g"], g["ln2_b"] = layernorm_backward(ctx, d_ln2, c["res1"], w["ln2_g"], c["mean2"], c["rstd2"],
-                                                            stream=stream)
-    d_res1 = add(ctx, d_out, d_res1_ln, stream=stream)
+    d_res1, g["ln2_g"], g["ln2_b"] = layernorm_backward(ctx, d_ln2, c["res1"], w["ln2_g"], c["mean2"], c["rstd2"],
+                                                         upstream=d_out, stream=stream)
     d_merged, g["wo"], g["bo"] = linear_backward(ctx, c["merged"], w["wo"], d_res1, stream=stream)
     if "lse" in c:
         (o_op,), (do_op,) = _head_operands(ctx, c["merged"], heads), _head_operands(ctx, d_merged, heads)
@@ -312,9 +331,9 @@ def transformer_block_backward(ctx, d_out, w, cache, heads, *, stream=None):
         d_ln1_k, g["wk"], g["bk"] = linear_backward(ctx, c["ln1"], w["wk"], grads_in[1], stream=stream)
         d_ln1_v, g["wv"], g["bv"] = linear_backward(ctx, c["ln1"], w["wv"], grads_in[2], stream=stream)
         d_ln1 = add(ctx, add(ctx, d_ln1_q, d_ln1_k, stream=stream), d_ln1_v, stream=stream)
-    d_x_ln, g["ln1_g"], g["ln1_b"] = layernorm_backward(ctx, d_ln1, c["x"], w["ln1_g"], c["mean1"], c["rstd1"],
-                                                         stream=stream)
-    return add(ctx, d_res1, d_x_ln, stream=stream), g
+    d_x, g["ln1_g"], g["ln1_b"] = layernorm_backward(ctx, d_ln1, c["x"], w["ln1_g"], c["mean1"], c["rstd1"],
+                                                      upstream=d_res1, stream=stream)
+    return d_x, g
 
 
 # ---------------------------------------------------------------------------------------------------------------
@@ -336,6 +355,7 @@ class GPT2:
         self.Vp = (vocab + 7) // 8 * 8
         self.params = None
         self.opt = None
+        self._d_logits = None
 
     def block_shapes(self):
         d, f = self.D, self.F
@@ -404,12 +424,19 @@ class GPT2:
         x = add(ctx, tok, pos, stream=stream)
         caches = []
         for w in p["blocks"]:
-            x, cache = transformer_block_forward(ctx, x, w, self.H, stream=stream)
+            x, cache = transformer_block_forward(ctx, x, w, self.H, defer_add=True, stream=stream)
             caches.append(cache)
-        xf, mean_f, rstd_f = layernorm_forward(ctx, x, p["lnf_g"], p["lnf_b"], stream=stream)
+        if isinstance(x, tuple):   # the last block's residual sum happens inside the final LayerNorm pass
+            x, xf, mean_f, rstd_f = add_layernorm_forward(ctx, x[0], x[1], p["lnf_g"], p["lnf_b"], stream=stream)
+        else:
+            xf, mean_f, rstd_f = layernorm_forward(ctx, x, p["lnf_g"], p["lnf_b"], stream=stream)
         logits = matmul(ctx, xf, p["head"], False, True, stream=stream)            # [B, S, Vp]
         loss = DeviceTensor(ctx, (1,), F32)
-        d_logits = DeviceTensor.zeros(ctx, logits.shape, BF16, stream=stream)        # pad columns stay zero
+        # The cross-entropy kernel writes columns [0, V) only; the pad columns must be zero for the head gradient. The
+        # buffer is kept across steps so that they are zeroed once, not every step.
+        if self._d_logits is None or self._d_logits.shape != logits.shape:
+            self._d_logits = DeviceTensor.zeros(ctx, logits.shape, BF16, stream=stream)
+        d_logits = self._d_logits
         ctx.cross_entropy(logits, targets, t, self.V, ld=self.Vp, loss_sum=loss, d_logits=d_logits, ldd=self.Vp,
                           stream=stream)
         grads = {"blocks": [None] * self.L}
