@@ -75,9 +75,17 @@ struct b200_ctx {
 namespace b200 {
 // Layout of the small device block behind b200_ctx::d_status: the status word, then (from byte 256) ticket counters for
 // kernels whose last-arriving CTA finishes a reduction. The counters start at zero and every kernel leaves them at zero.
+// The last ticket is reserved for the LayerNorm backward kernel, whose parameter-gradient staging follows the tickets:
+// kLnCopies replicas of [dgamma | dbeta] with up to kLnMaxCols columns each, zero between kernels as well.
 constexpr int kTicketCount = 4096;
-constexpr size_t kStatusBytes = 256 + sizeof(unsigned) * kTicketCount;
+constexpr int kLnCopies = 8;
+constexpr int kLnMaxCols = 1024;
+constexpr size_t kLnStageBytes = sizeof(float) * kLnCopies * 2 * kLnMaxCols;
+constexpr size_t kStatusBytes = 256 + sizeof(unsigned) * kTicketCount + kLnStageBytes;
 inline unsigned* ctx_tickets(const b200_ctx* ctx) { return reinterpret_cast<unsigned*>(reinterpret_cast<char*>(ctx->d_status) + 256); }
+inline float* ctx_ln_stage(const b200_ctx* ctx) {
+    return reinterpret_cast<float*>(reinterpret_cast<char*>(ctx->d_status) + 256 + sizeof(unsigned) * kTicketCount);
+}
 // Grows the context scratch to at least `bytes` (never shrinks). Not allowed during stream capture.
 int ensure_scratch(b200_ctx* ctx, size_t bytes);
 // Pool / trace state attached to a context (pool.cu).

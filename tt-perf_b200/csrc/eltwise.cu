@@ -70,6 +70,34 @@ __global__ void __launch_bounds__(kThreads) unary_kernel(const __nv_bfloat16* x,
         y[i] = __float2bfloat16_rn(unary_apply(op, __bfloat162float(x[i]), s));
 }
 
+// Whole-vector inputs with the operation fixed at compile time (no per-element switch) and two 16-byte loads in
+// flight per thread. OP = -1 keeps the run-time switch.
+template <int OP>
+__global__ void __launch_bounds__(kThreads) unary_vec_kernel(const uint4* x, uint4* y, long long nvec, int op, float s) {
+    const long long stride = static_cast<long long>(gridDim.x) * blockDim.x;
+    long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x;
+    for (; i + stride < nvec; i += 2 * stride) {
+        const uint4 u0 = x[i], u1 = x[i + stride];
+        float f0[8], f1[8];
+        unpack8(u0, f0);
+        unpack8(u1, f1);
+#pragma unroll
+        for (int k = 0; k < 8; ++k) {
+            f0[k] = unary_apply(OP >= 0 ? OP : op, f0[k], s);
+            f1[k] = unary_apply(OP >= 0 ? OP : op, f1[k], s);
+        }
+        y[i] = pack8(f0);
+        y[i + stride] = pack8(f1);
+    }
+    if (i < nvec) {
+        float f[8];
+        unpack8(x[i], f);
+#pragma unroll
+        for (int k = 0; k < 8; ++k) f[k] = unary_apply(OP >= 0 ? OP : op, f[k], s);
+        y[i] = pack8(f);
+    }
+}
+
 // ---- binary ops with numpy-style broadcasting over up to 4 dims --------------------------------------
 enum BinaryOp : int { B_ADD = 0, B_SUB = 1, B_MUL = 2, B_DIV = 3, B_RELU_BW = 4, B_GELU_BW = 5, B_MAX = 6, B_COUNT = 7 };
 
@@ -109,6 +137,36 @@ __global__ void __launch_bounds__(kThreads) binary_flat_kernel(const __nv_bfloat
 #pragma unroll
         for (int k = 0; k < 8; ++k) fa[k] = binary_apply(op, fa[k], fb[k]);
         reinterpret_cast<uint4*>(out)[i] = pack8(fa);
+    }
+}
+
+// The same with the operation fixed at compile time and two vector pairs in flight per thread.
+template <int OP>
+__global__ void __launch_bounds__(kThreads) binary_vec_kernel(const uint4* a, const uint4* b, uint4* out, long long nvec) {
+    const long long stride = static_cast<long long>(gridDim.x) * blockDim.x;
+    long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x;
+    for (; i + stride < nvec; i += 2 * stride) {
+        const uint4 a0 = a[i], b0 = b[i], a1 = a[i + stride], b1 = b[i + stride];
+        float fa0[8], fb0[8], fa1[8], fb1[8];
+        unpack8(a0, fa0);
+        unpack8(b0, fb0);
+        unpack8(a1, fa1);
+        unpack8(b1, fb1);
+#pragma unroll
+        for (int k = 0; k < 8; ++k) {
+            fa0[k] = binary_apply(OP, fa0[k], fb0[k]);
+            fa1[k] = binary_apply(OP, fa1[k], fb1[k]);
+        }
+        out[i] = pack8(fa0);
+        out[i + stride] = pack8(fa1);
+    }
+    if (i < nvec) {
+        float fa[8], fb[8];
+        unpack8(a[i], fa);
+        unpack8(b[i], fb);
+#pragma unroll
+        for (int k = 0; k < 8; ++k) fa[k] = binary_apply(OP, fa[k], fb[k]);
+        out[i] = pack8(fa);
     }
 }
 
@@ -323,7 +381,23 @@ __global__ void __launch_bounds__(kThreads) reduce_cols_ticket_kernel(const __nv
     for (int k = 0; k < VEC; ++k) acc[k] = (op == R_MAX) ? -FLT_MAX : 0.0f;
     if (c < inner) {
         const __nv_bfloat16* base = x + o * R * inner + c;
-        for (long long r = r0 + sub; r < r1; r += 8) {
+        long long r = r0 + sub;
+        if (VEC == 8) {
+            // eight independent 16-byte loads in flight per thread
+            for (; r + 56 < r1; r += 64) {
+                uint4 v[8];
+#pragma unroll
+                for (int u = 0; u < 8; ++u) v[u] = *reinterpret_cast<const uint4*>(base + (r + 8 * u) * inner);
+#pragma unroll
+                for (int u = 0; u < 8; ++u) {
+                    float f[8];
+                    unpack8(v[u], f);
+#pragma unroll
+                    for (int k = 0; k < 8; ++k) acc[k] = (op == R_MAX) ? fmaxf(acc[k], f[k]) : acc[k] + f[k];
+                }
+            }
+        }
+        for (; r < r1; r += 8) {
             if (VEC == 8) {
                 float f[8];
                 unpack8(*reinterpret_cast<const uint4*>(base + r * inner), f);
@@ -338,12 +412,12 @@ __global__ void __launch_bounds__(kThreads) reduce_cols_ticket_kernel(const __nv
 #pragma unroll
     for (int k = 0; k < VEC; ++k) sh[sub][threadIdx.x & 31][k] = acc[k];
     __syncthreads();
-    // thread t now owns column (t / VEC-group, t % VEC) of the CTA's 32 * VEC columns: consecutive threads, consecutive columns
-    const int cols_here = 32 * VEC;
+    // thread t now owns column t of the CTA's 32 * VEC columns: consecutive threads, consecutive columns
+    constexpr int cols_here = 32 * VEC;
     float* my_part = part + (o * row_blocks + blockIdx.y) * inner;
     const long long c0 = blockIdx.x * static_cast<long long>(cols_here);
-    for (int t = threadIdx.x; t < cols_here; t += kThreads) {
-        if (c0 + t >= inner) break;
+    if (threadIdx.x < cols_here && c0 + threadIdx.x < inner) {
+        const int t = threadIdx.x;
         float a = sh[0][t / VEC][t % VEC];
 #pragma unroll
         for (int j = 1; j < 8; ++j) {
@@ -361,26 +435,57 @@ __global__ void __launch_bounds__(kThreads) reduce_cols_ticket_kernel(const __nv
     __syncthreads();
     if (!is_last) return;
     __threadfence();
-    for (int t = threadIdx.x; t < cols_here; t += kThreads) {
-        if (c0 + t >= inner) break;
-        const float* col = part + o * row_blocks * inner + c0 + t;
-        float a4[4];
+    // The last CTA of this column block combines the partials. All 256 threads take part: a thread owns `Q` adjacent
+    // columns (4 as one 16-byte load when VEC = 8) and every `groups`-th row block, 8 independent loads at a time;
+    // shared memory then combines the groups.
+    constexpr int Q = VEC == 8 ? 4 : 1;
+    constexpr int owners = cols_here / Q;
+    constexpr int groups = kThreads / owners;
+    const int col = (threadIdx.x % owners) * Q, grp = threadIdx.x / owners;
+    float a[Q];
 #pragma unroll
-        for (int k = 0; k < 4; ++k) a4[k] = (op == R_MAX) ? -FLT_MAX : 0.0f;
-        int rb = 0;
-        for (; rb + 4 <= row_blocks; rb += 4) {
+    for (int q = 0; q < Q; ++q) a[q] = (op == R_MAX) ? -FLT_MAX : 0.0f;
+    const bool live = c0 + col < inner;  // inner % 8 == 0 when VEC = 8, so a quad is inside or outside as a whole
+    if (live) {
+        const float* src = part + o * row_blocks * inner + c0 + col;
+        int rb = grp;
+        for (; rb + 7 * groups < row_blocks; rb += 8 * groups) {
+            float v[8][Q];
 #pragma unroll
-            for (int k = 0; k < 4; ++k) {
-                const float v = __ldcg(col + (rb + k) * inner);
-                a4[k] = (op == R_MAX) ? fmaxf(a4[k], v) : a4[k] + v;
+            for (int u = 0; u < 8; ++u) {
+                const float* ptr = src + static_cast<long long>(rb + u * groups) * inner;
+                if (Q == 4) {
+                    const float4 f = __ldcg(reinterpret_cast<const float4*>(ptr));
+                    v[u][0] = f.x; v[u][Q > 1 ? 1 : 0] = f.y; v[u][Q > 2 ? 2 : 0] = f.z; v[u][Q > 3 ? 3 : 0] = f.w;
+                } else {
+                    v[u][0] = __ldcg(ptr);
+                }
+            }
+#pragma unroll
+            for (int u = 0; u < 8; ++u)
+#pragma unroll
+                for (int q = 0; q < Q; ++q) a[q] = (op == R_MAX) ? fmaxf(a[q], v[u][q]) : a[q] + v[u][q];
+        }
+        for (; rb < row_blocks; rb += groups) {
+#pragma unroll
+            for (int q = 0; q < Q; ++q) {
+                const float v = __ldcg(src + static_cast<long long>(rb) * inner + q);
+                a[q] = (op == R_MAX) ? fmaxf(a[q], v) : a[q] + v;
             }
         }
-        for (; rb < row_blocks; ++rb) {
-            const float v = __ldcg(col + rb * inner);
-            a4[0] = (op == R_MAX) ? fmaxf(a4[0], v) : a4[0] + v;
+    }
+    float* comb = &sh[0][0][0];  // reuse: groups * cols_here <= 8 * 32 * (VEC + 1) floats
+    __syncthreads();
+#pragma unroll
+    for (int q = 0; q < Q; ++q) comb[grp * cols_here + col + q] = a[q];
+    __syncthreads();
+    if (threadIdx.x < cols_here && c0 + threadIdx.x < inner) {
+        float r = comb[threadIdx.x];
+        for (int q = 1; q < groups; ++q) {
+            const float other = comb[q * cols_here + threadIdx.x];
+            r = (op == R_MAX) ? fmaxf(r, other) : r + other;
         }
-        const float a = (op == R_MAX) ? fmaxf(fmaxf(a4[0], a4[1]), fmaxf(a4[2], a4[3])) : (a4[0] + a4[1]) + (a4[2] + a4[3]);
-        y[o * inner + c0 + t] = __float2bfloat16_rn(a * scale);
+        y[o * inner + c0 + threadIdx.x] = __float2bfloat16_rn(r * scale);
     }
     if (threadIdx.x == 0) tickets[o * gridDim.x + blockIdx.x] = 0u;
 }
@@ -514,6 +619,17 @@ int b200_unary(b200_ctx* ctx, int op, const void* x, void* y, int64_t n, float s
     B200_REQUIRE(x && y, "b200_unary: NULL buffer");
     DeviceScope scope(ctx->device);
     const int vec = al16(x) && al16(y);
+    if (vec && (n % 8) == 0) {
+        const auto* xv = static_cast<const uint4*>(x);
+        auto* yv = static_cast<uint4*>(y);
+        const int grid = grid_for(ctx, (n / 8 + 1) / 2);
+        if (op == U_GELU)
+            unary_vec_kernel<U_GELU><<<grid, kThreads, 0, ctx->pick(stream)>>>(xv, yv, n / 8, op, scalar);
+        else
+            unary_vec_kernel<-1><<<grid, kThreads, 0, ctx->pick(stream)>>>(xv, yv, n / 8, op, scalar);
+        B200_CUDA_TRY(cudaGetLastError());
+        return B200_OK;
+    }
     unary_kernel<<<grid_for(ctx, (n + 7) / 8), kThreads, 0, ctx->pick(stream)>>>(
         static_cast<const __nv_bfloat16*>(x), static_cast<__nv_bfloat16*>(y), n, op, scalar, vec);
     B200_CUDA_TRY(cudaGetLastError());
@@ -562,7 +678,18 @@ int b200_binary(b200_ctx* ctx, int op, const void* a, const int64_t* a_shape, co
     bool same = true;
     for (int i = 0; i < 4; ++i) same = same && ad[i] == bd[i];
     if (same && (p.n % 8 == 0) && al16(a) && al16(b) && al16(out)) {
-        binary_flat_kernel<<<grid_for(ctx, p.n / 8), kThreads, 0, ctx->pick(stream)>>>(p.a, p.b, p.out, p.n / 8, op);
+        const auto* av = reinterpret_cast<const uint4*>(p.a);
+        const auto* bv = reinterpret_cast<const uint4*>(p.b);
+        auto* ov = reinterpret_cast<uint4*>(p.out);
+        const int grid = grid_for(ctx, (p.n / 8 + 1) / 2);
+        if (op == B_GELU_BW)
+            binary_vec_kernel<B_GELU_BW><<<grid, kThreads, 0, ctx->pick(stream)>>>(av, bv, ov, p.n / 8);
+        else if (op == B_ADD)
+            binary_vec_kernel<B_ADD><<<grid, kThreads, 0, ctx->pick(stream)>>>(av, bv, ov, p.n / 8);
+        else if (op == B_MUL)
+            binary_vec_kernel<B_MUL><<<grid, kThreads, 0, ctx->pick(stream)>>>(av, bv, ov, p.n / 8);
+        else
+            binary_flat_kernel<<<grid_for(ctx, p.n / 8), kThreads, 0, ctx->pick(stream)>>>(p.a, p.b, p.out, p.n / 8, op);
         B200_CUDA_TRY(cudaGetLastError());
         return B200_OK;
     }
@@ -619,9 +746,9 @@ int b200_reduce(b200_ctx* ctx, int op, const void* x, int64_t outer, int64_t R, 
     const long long col_blocks = vec8 ? (inner / 8 + 31) / 32 : (inner + 31) / 32;
     B200_REQUIRE(outer <= 65535, "b200_reduce: outer dimension too large for a column reduction");
     const float scale = op == R_MEAN ? 1.0f / static_cast<float>(R) : 1.0f;
-    if (col_blocks * outer <= kTicketCount) {
+    if (col_blocks * outer < kTicketCount) {
         // one launch: per-CTA partials, the last CTA of a column block combines them
-        long long row_blocks = std::max<long long>(1, std::min<long long>(std::min<long long>((R + 31) / 32, 64),
+        long long row_blocks = std::max<long long>(1, std::min<long long>(std::min<long long>((R + 63) / 64, 128),
                                                                            (ctx->sm_count * 4ll) / std::max<long long>(1, col_blocks * outer)));
         const long long rows_per = (R + row_blocks - 1) / row_blocks;
         row_blocks = (R + rows_per - 1) / rows_per;

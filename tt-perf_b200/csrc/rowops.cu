@@ -649,6 +649,247 @@ __global__ void __launch_bounds__(kBlock, VPL <= 4 ? 3 : 2) layernorm_bw_dx_warp
     }
 }
 
+// ---- fast paths: 16-byte aligned rows, cols % 8 == 0, cols <= 1024 ----------------------------------------------
+__device__ __forceinline__ void unpack_bf16x8(const uint4& u, float (&f)[8]) {
+    const uint32_t w[4] = {u.x, u.y, u.z, u.w};
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        f[2 * i] = __uint_as_float(w[i] << 16);
+        f[2 * i + 1] = __uint_as_float(w[i] & 0xffff0000u);
+    }
+}
+__device__ __forceinline__ uint4 pack_bf16x8(const float (&f)[8]) {
+    return make_uint4(pack_bf16x2(f[0], f[1]), pack_bf16x2(f[2], f[3]), pack_bf16x2(f[4], f[5]), pack_bf16x2(f[6], f[7]));
+}
+
+// Forward, one warp per row. Every load of the row (x, the residual, gamma, beta) is issued before the first use, so
+// the two dependent warp reductions overlap the tail of the memory latency instead of following it.
+template <int VPL>
+__global__ void __launch_bounds__(kBlock, 3) layernorm_fw_vec_kernel(const __nv_bfloat16* x, long long ldx,
+                                                                      const __nv_bfloat16* gamma, const __nv_bfloat16* beta,
+                                                                      __nv_bfloat16* y, long long ldy, float* mean_out,
+                                                                      float* rstd_out, int rows, int cols, float eps,
+                                                                      const __nv_bfloat16* res, long long ldres,
+                                                                      __nv_bfloat16* sum_out, long long ldsum) {
+    const int lane = threadIdx.x & 31;
+    const int r = blockIdx.x * (kBlock / kWarp) + (threadIdx.x >> 5);
+    if (r >= rows) return;
+    const uint4 zero = make_uint4(0u, 0u, 0u, 0u);
+    uint4 xv[VPL], rv[VPL], gv[VPL], bv[VPL];
+#pragma unroll
+    for (int j = 0; j < VPL; ++j) {
+        const int c = (j * kWarp + lane) * 8;
+        const bool in = c < cols;
+        xv[j] = in ? *reinterpret_cast<const uint4*>(x + static_cast<size_t>(r) * ldx + c) : zero;
+        rv[j] = (in && res != nullptr) ? *reinterpret_cast<const uint4*>(res + static_cast<size_t>(r) * ldres + c) : zero;
+        gv[j] = in ? *reinterpret_cast<const uint4*>(gamma + c) : zero;
+        bv[j] = in ? *reinterpret_cast<const uint4*>(beta + c) : zero;
+    }
+    float a[VPL][8];
+    float s = 0.0f;
+#pragma unroll
+    for (int j = 0; j < VPL; ++j) {
+        const int c = (j * kWarp + lane) * 8;
+        unpack_bf16x8(xv[j], a[j]);
+        if (res != nullptr) {  // normalise x + res; the sum (rounded to bf16, as a separate add would) is also an output
+            float rr[8];
+            unpack_bf16x8(rv[j], rr);
+#pragma unroll
+            for (int i = 0; i < 8; ++i) a[j][i] += rr[i];
+            const uint4 packed = pack_bf16x8(a[j]);
+            unpack_bf16x8(packed, a[j]);
+            if (c < cols) *reinterpret_cast<uint4*>(sum_out + static_cast<size_t>(r) * ldsum + c) = packed;
+        }
+#pragma unroll
+        for (int i = 0; i < 8; ++i) s += a[j][i];
+    }
+    const float mean = warp_sum(s) / cols;
+    float q = 0.0f;
+#pragma unroll
+    for (int j = 0; j < VPL; ++j) {
+        const bool in = (j * kWarp + lane) * 8 < cols;
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+            const float d = in ? a[j][i] - mean : 0.0f;
+            q = fmaf(d, d, q);
+        }
+    }
+    const float rstd = rsqrtf(warp_sum(q) / cols + eps);
+    if (lane == 0) {
+        if (mean_out) mean_out[r] = mean;
+        if (rstd_out) rstd_out[r] = rstd;
+    }
+#pragma unroll
+    for (int j = 0; j < VPL; ++j) {
+        const int c = (j * kWarp + lane) * 8;
+        if (c >= cols) continue;
+        float g[8], b[8];
+        unpack_bf16x8(gv[j], g);
+        unpack_bf16x8(bv[j], b);
+#pragma unroll
+        for (int i = 0; i < 8; ++i) a[j][i] = fmaf((a[j][i] - mean) * rstd, g[i], b[i]);
+        *reinterpret_cast<uint4*>(y + static_cast<size_t>(r) * ldy + c) = pack_bf16x8(a[j]);
+    }
+}
+
+// Backward in one pass (see layernorm_bw_fused_warp_kernel below for the arithmetic), persistent grid, one warp per row
+// at a time. The packed dy, x and upstream vectors of the NEXT row are requested before the current row is processed, so
+// every warp has loads in flight all the time. gamma sits in shared memory as fp32. The column sums for dgamma / dbeta
+// live in a private shared-memory slab per warp (plain vector loads and stores, no atomics: a lane only ever touches
+// its own columns); at the end the CTA adds the slabs and issues one global atomic per column.
+template <int VPL>
+__global__ void __launch_bounds__(kBlock, 2) layernorm_bw_vec_kernel(
+    const __nv_bfloat16* dy, long long lddy, const __nv_bfloat16* x, long long ldx, const __nv_bfloat16* gamma,
+    const float* mean, const float* rstd, const __nv_bfloat16* upstream, long long ldup, __nv_bfloat16* dx, long long lddx,
+    float* dgamma_out, float* dbeta_out, int rows, int cols, float* stage, unsigned* ticket) {
+    constexpr int WARPS = kBlock / kWarp;
+    constexpr int W = VPL * kWarp * 8;
+    extern __shared__ float ln_smem[];
+    float* sgam = ln_smem;                 // [W]
+    float* sag = sgam + W;                 // [WARPS][W]
+    float* sab = sag + WARPS * W;          // [WARPS][W]
+    const int lane = threadIdx.x & 31;
+    const int warp = threadIdx.x >> 5;
+    for (int c = threadIdx.x; c < W; c += kBlock) sgam[c] = c < cols ? __bfloat162float(gamma[c]) : 0.0f;
+    for (int c = threadIdx.x; c < 2 * WARPS * W; c += kBlock) sag[c] = 0.0f;
+    __syncthreads();
+    float* my_ag = sag + warp * W;
+    float* my_ab = sab + warp * W;
+    const bool params = dgamma_out != nullptr || dbeta_out != nullptr;
+    const uint4 zero = make_uint4(0u, 0u, 0u, 0u);
+    const int stride = gridDim.x * WARPS;
+    int r = blockIdx.x * WARPS + warp;
+    uint4 dv[VPL], xv[VPL], uv[VPL];
+    float mu = 0.0f, rs = 0.0f;
+    auto fetch = [&](int row) {
+#pragma unroll
+        for (int j = 0; j < VPL; ++j) {
+            const int c = (j * kWarp + lane) * 8;
+            const bool in = c < cols && row < rows;
+            dv[j] = in ? *reinterpret_cast<const uint4*>(dy + static_cast<size_t>(row) * lddy + c) : zero;
+            xv[j] = in ? *reinterpret_cast<const uint4*>(x + static_cast<size_t>(row) * ldx + c) : zero;
+            uv[j] = (in && upstream != nullptr) ? *reinterpret_cast<const uint4*>(upstream + static_cast<size_t>(row) * ldup + c) : zero;
+        }
+        mu = row < rows ? mean[row] : 0.0f;
+        rs = row < rows ? rstd[row] : 0.0f;
+    };
+    fetch(r);
+    for (; r < rows; r += stride) {
+        // move the current row out of the fetch registers, then request the next one
+        uint4 cd[VPL], cx[VPL], cu[VPL];
+#pragma unroll
+        for (int j = 0; j < VPL; ++j) {
+            cd[j] = dv[j];
+            cx[j] = xv[j];
+            cu[j] = uv[j];
+        }
+        const float cmu = mu, crs = rs;
+        fetch(r + stride);
+        float s1 = 0.0f, s2 = 0.0f;
+#pragma unroll
+        for (int j = 0; j < VPL; ++j) {
+            const int c = (j * kWarp + lane) * 8;
+            if (c >= cols) continue;
+            float d[8], xh[8];
+            unpack_bf16x8(cd[j], d);
+            unpack_bf16x8(cx[j], xh);
+            const float4 g0 = *reinterpret_cast<const float4*>(sgam + c);
+            const float4 g1 = *reinterpret_cast<const float4*>(sgam + c + 4);
+            const float gm[8] = {g0.x, g0.y, g0.z, g0.w, g1.x, g1.y, g1.z, g1.w};
+            float pg[8], pb[8];
+            if (params) {
+                const float4 a0 = *reinterpret_cast<const float4*>(my_ag + c), a1 = *reinterpret_cast<const float4*>(my_ag + c + 4);
+                const float4 b0 = *reinterpret_cast<const float4*>(my_ab + c), b1 = *reinterpret_cast<const float4*>(my_ab + c + 4);
+                pg[0] = a0.x; pg[1] = a0.y; pg[2] = a0.z; pg[3] = a0.w; pg[4] = a1.x; pg[5] = a1.y; pg[6] = a1.z; pg[7] = a1.w;
+                pb[0] = b0.x; pb[1] = b0.y; pb[2] = b0.z; pb[3] = b0.w; pb[4] = b1.x; pb[5] = b1.y; pb[6] = b1.z; pb[7] = b1.w;
+            }
+#pragma unroll
+            for (int i = 0; i < 8; ++i) {
+                const float xhat = (xh[i] - cmu) * crs;
+                if (params) {
+                    pb[i] += d[i];
+                    pg[i] = fmaf(d[i], xhat, pg[i]);
+                }
+                const float gg = d[i] * gm[i];
+                s1 += gg;
+                s2 = fmaf(gg, xhat, s2);
+            }
+            if (params) {
+                *reinterpret_cast<float4*>(my_ag + c) = make_float4(pg[0], pg[1], pg[2], pg[3]);
+                *reinterpret_cast<float4*>(my_ag + c + 4) = make_float4(pg[4], pg[5], pg[6], pg[7]);
+                *reinterpret_cast<float4*>(my_ab + c) = make_float4(pb[0], pb[1], pb[2], pb[3]);
+                *reinterpret_cast<float4*>(my_ab + c + 4) = make_float4(pb[4], pb[5], pb[6], pb[7]);
+            }
+        }
+        s1 = warp_sum(s1) / cols;
+        s2 = warp_sum(s2) / cols;
+        if (dx != nullptr) {
+#pragma unroll
+            for (int j = 0; j < VPL; ++j) {
+                const int c = (j * kWarp + lane) * 8;
+                if (c >= cols) continue;
+                float d[8], xh[8], up[8], o[8];
+                unpack_bf16x8(cd[j], d);
+                unpack_bf16x8(cx[j], xh);
+                unpack_bf16x8(cu[j], up);
+                const float4 g0 = *reinterpret_cast<const float4*>(sgam + c);
+                const float4 g1 = *reinterpret_cast<const float4*>(sgam + c + 4);
+                const float gm[8] = {g0.x, g0.y, g0.z, g0.w, g1.x, g1.y, g1.z, g1.w};
+#pragma unroll
+                for (int i = 0; i < 8; ++i) {
+                    const float xhat = (xh[i] - cmu) * crs;
+                    o[i] = crs * (d[i] * gm[i] - s1 - xhat * s2);
+                    // the separate form rounds dx to bf16 before the add; keep that rounding
+                    if (upstream != nullptr) o[i] = __bfloat162float(__float2bfloat16_rn(o[i])) + up[i];
+                }
+                *reinterpret_cast<uint4*>(dx + static_cast<size_t>(r) * lddx + c) = pack_bf16x8(o);
+            }
+        }
+    }
+    if (!params) return;
+    // CTA sums -> one of kLnCopies zero-initialised staging replicas (few CTAs collide on an address) -> the CTA that
+    // arrives last adds the replicas, writes the outputs and leaves replicas and ticket at zero for the next launch.
+    __shared__ int is_last;
+    __syncthreads();
+    float* mine = stage + (blockIdx.x % kLnCopies) * 2 * kLnMaxCols;
+    for (int c = threadIdx.x; c < cols; c += kBlock) {
+        float g = 0.0f, b = 0.0f;
+#pragma unroll
+        for (int w = 0; w < WARPS; ++w) {
+            g += sag[w * W + c];
+            b += sab[w * W + c];
+        }
+        atomicAdd(&mine[c], g);
+        atomicAdd(&mine[kLnMaxCols + c], b);
+    }
+    __threadfence();
+    __syncthreads();
+    if (threadIdx.x == 0) is_last = atomicAdd(ticket, 1u) == gridDim.x - 1;
+    __syncthreads();
+    if (!is_last) return;
+    __threadfence();
+    for (int c = threadIdx.x; c < cols; c += kBlock) {
+        float g = 0.0f, b = 0.0f;
+#pragma unroll
+        for (int k = 0; k < kLnCopies; ++k) {
+            float* copy = stage + k * 2 * kLnMaxCols;
+            g += __ldcg(copy + c);
+            b += __ldcg(copy + kLnMaxCols + c);
+            copy[c] = 0.0f;
+            copy[kLnMaxCols + c] = 0.0f;
+        }
+        if (dgamma_out != nullptr) dgamma_out[c] = g;
+        if (dbeta_out != nullptr) dbeta_out[c] = b;
+    }
+    if (threadIdx.x == 0) *ticket = 0u;
+}
+
+// Dynamic shared memory of layernorm_bw_vec_kernel<VPL>: gamma and the two per-warp accumulator slabs.
+template <int VPL>
+constexpr size_t ln_bw_vec_smem() {
+    return sizeof(float) * (VPL * kWarp * 8) * (1 + 2 * (kBlock / kWarp));
+}
+
 // Backward in one pass for rows that fit a warp's registers: a persistent grid, one warp per row at a time.
 //   dx      = rstd * (g - mean(g) - xhat * mean(g * xhat)),  g = dy * gamma   (+ `upstream`, when given: the gradient
 //             that reaches the same tensor along the residual path, so that no separate add runs)
@@ -979,6 +1220,16 @@ static int layernorm_forward_impl(const char* fn, b200_ctx* ctx, const void* x, 
     const int vx = vec_ok(xp, ldx), vy = vec_ok(y, ldy), vg = vec_ok(gamma, 8) & vec_ok(beta, 8);
     const int vres = rp ? (vec_ok(rp, ldres) & vec_ok(sp, ldsum)) : 0;
     const int blocks = (r + 7) / 8;
+    if (c <= 1024 && (c % 8) == 0 && vx && vy && vg && (rp == nullptr || vres)) {
+        if (c <= 512)
+            layernorm_fw_vec_kernel<2><<<blocks, kBlock, 0, s>>>(xp, ldx, gp, bp, yp, ldy, mean, rstd, r, c, eps, rp, ldres, sp, ldsum);
+        else if (c <= 768)
+            layernorm_fw_vec_kernel<3><<<blocks, kBlock, 0, s>>>(xp, ldx, gp, bp, yp, ldy, mean, rstd, r, c, eps, rp, ldres, sp, ldsum);
+        else
+            layernorm_fw_vec_kernel<4><<<blocks, kBlock, 0, s>>>(xp, ldx, gp, bp, yp, ldy, mean, rstd, r, c, eps, rp, ldres, sp, ldsum);
+        B200_CUDA_TRY(cudaGetLastError());
+        return B200_OK;
+    }
     if (c <= 512)
         layernorm_fw_warp_kernel<2><<<blocks, kBlock, 0, s>>>(xp, ldx, gp, bp, yp, ldy, mean, rstd, r, c, eps, vx, vy, vg, rp, ldres, sp, ldsum, vres);
     else if (c <= 768)
@@ -1021,8 +1272,14 @@ static int layernorm_backward_impl(const char* fn, b200_ctx* ctx, const void* dy
     DeviceScope scope(ctx->device);
     cudaStream_t s = ctx->pick(stream);
     const int r = static_cast<int>(rows), c = static_cast<int>(cols);
-    if (dgamma_f32 && c > 0) B200_CUDA_TRY(cudaMemsetAsync(dgamma_f32, 0, sizeof(float) * c, s));
-    if (dbeta_f32 && c > 0) B200_CUDA_TRY(cudaMemsetAsync(dbeta_f32, 0, sizeof(float) * c, s));
+    // the vector kernel writes dgamma / dbeta itself; every other path accumulates into zeroed outputs
+    const bool vec_path = rows > 0 && c > 0 && c <= 1024 && (c % 8) == 0 && gamma != nullptr && vec_ok(dy, lddy) && vec_ok(x, ldx) &&
+                          vec_ok(gamma, 8) && (dx == nullptr || vec_ok(dx, lddx)) && (upstream == nullptr || vec_ok(upstream, ldup)) &&
+                          (dx != nullptr || dgamma_f32 || dbeta_f32);
+    if (!vec_path) {
+        if (dgamma_f32 && c > 0) B200_CUDA_TRY(cudaMemsetAsync(dgamma_f32, 0, sizeof(float) * c, s));
+        if (dbeta_f32 && c > 0) B200_CUDA_TRY(cudaMemsetAsync(dbeta_f32, 0, sizeof(float) * c, s));
+    }
     if (rows == 0 || cols == 0) return B200_OK;
     B200_REQUIRE(mean && rstd, "%s: mean or rstd is NULL", fn);
     const auto* dyp = static_cast<const __nv_bfloat16*>(dy);
@@ -1035,6 +1292,32 @@ static int layernorm_backward_impl(const char* fn, b200_ctx* ctx, const void* dy
         const int vdy = vec_ok(dy, lddy), vx = vec_ok(x, ldx), vdx = dx ? vec_ok(dx, lddx) : 0, vg = gamma ? vec_ok(gamma, 8) : 0;
         const int vup = upstream ? vec_ok(upstream, ldup) : 0;
         const int blocks = std::max(1, std::min((r + 7) / 8, ctx->sm_count * 2));
+        if (vec_path) {
+            static bool configured[64] = {};
+            int dev = 0;
+            B200_CUDA_TRY(cudaGetDevice(&dev));
+            if (dev < 0 || dev >= 64 || !configured[dev]) {
+                B200_CUDA_TRY(cudaFuncSetAttribute(layernorm_bw_vec_kernel<2>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)ln_bw_vec_smem<2>()));
+                B200_CUDA_TRY(cudaFuncSetAttribute(layernorm_bw_vec_kernel<3>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)ln_bw_vec_smem<3>()));
+                B200_CUDA_TRY(cudaFuncSetAttribute(layernorm_bw_vec_kernel<4>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)ln_bw_vec_smem<4>()));
+                // room for two CTAs per SM (the driver otherwise sizes the carve-out for one)
+                B200_CUDA_TRY(cudaFuncSetAttribute(layernorm_bw_vec_kernel<2>, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared));
+                B200_CUDA_TRY(cudaFuncSetAttribute(layernorm_bw_vec_kernel<3>, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared));
+                B200_CUDA_TRY(cudaFuncSetAttribute(layernorm_bw_vec_kernel<4>, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared));
+                if (dev >= 0 && dev < 64) configured[dev] = true;
+            }
+            if (c <= 512)
+                layernorm_bw_vec_kernel<2><<<blocks, kBlock, ln_bw_vec_smem<2>(), s>>>(dyp, lddy, xp, ldx, gp, mean, rstd, upp, ldup, dxp, lddx,
+                                                                                       dgamma_f32, dbeta_f32, r, c, ctx_ln_stage(ctx), ctx_tickets(ctx) + kTicketCount - 1);
+            else if (c <= 768)
+                layernorm_bw_vec_kernel<3><<<blocks, kBlock, ln_bw_vec_smem<3>(), s>>>(dyp, lddy, xp, ldx, gp, mean, rstd, upp, ldup, dxp, lddx,
+                                                                                       dgamma_f32, dbeta_f32, r, c, ctx_ln_stage(ctx), ctx_tickets(ctx) + kTicketCount - 1);
+            else
+                layernorm_bw_vec_kernel<4><<<blocks, kBlock, ln_bw_vec_smem<4>(), s>>>(dyp, lddy, xp, ldx, gp, mean, rstd, upp, ldup, dxp, lddx,
+                                                                                       dgamma_f32, dbeta_f32, r, c, ctx_ln_stage(ctx), ctx_tickets(ctx) + kTicketCount - 1);
+            B200_CUDA_TRY(cudaGetLastError());
+            return B200_OK;
+        }
         if (c <= 512)
             layernorm_bw_fused_warp_kernel<2><<<blocks, kBlock, 0, s>>>(dyp, lddy, xp, ldx, gp, mean, rstd, upp, ldup, dxp, lddx,
                                                                         dgamma_f32, dbeta_f32, r, c, vdy, vx, vdx, vg, vup);
