@@ -822,6 +822,32 @@ inline Tensor softmax(const Tensor& x, int dim = -1, const std::optional<MemoryC
     return out;
 }
 
+// ---- fused attention --------------------------------------------------------------------------------------------------
+// ttnn::transformer::scaled_dot_product_attention on [B, H, S, 64] tensors: softmax(scale * Q K^T [+ causal mask]) V in one
+// kernel (b200_attention_forward), without the [S, S] score tensor that the matmul / softmax / matmul composition of
+// autograd/traced/nn.hpp:164-175 writes. The reference's executors do not call it; it is offered for code that does.
+namespace transformer {
+inline Tensor scaled_dot_product_attention(const Tensor& q, const Tensor& k, const Tensor& v,
+                                           const std::optional<Tensor>& attn_mask = std::nullopt, bool is_causal = true,
+                                           std::optional<float> scale = std::nullopt) {
+    const char* op = "ttnn::transformer::scaled_dot_product_attention";
+    if (attn_mask) throw std::invalid_argument(std::string(op) + ": explicit masks are not supported, use is_causal");
+    const Shape& s = q.logical_shape();
+    if (s.rank() != 4 || k.logical_shape() != s || v.logical_shape() != s)
+        throw std::invalid_argument(std::string(op) + ": q, k, v must share one [B, H, S, dh] shape");
+    const int64_t B = s[0], H = s[1], S = s[2], dh = s[3];
+    Tensor out = detail::alloc_like(q, s, DataType::BFLOAT16, q.layout(), op);
+    auto lse = detail::device_storage(detail::dev_of(q, op), static_cast<size_t>(B * H * S) * sizeof(float), q.device_index());
+    auto operand = [&](const Tensor& t) { return b200_attn_operand{const_cast<void*>(t.device_ptr()), H * S * dh, S * dh, dh}; };
+    const b200_attn_operand qo = operand(q), ko = operand(k), vo = operand(v), oo = operand(out);
+    detail::check(b200_attention_forward(detail::ctx_of(q, op), &qo, &ko, &vo, &oo, static_cast<float*>(lse->dptr), B, H, S,
+                                         static_cast<int>(dh), scale.value_or(1.0f / std::sqrt(static_cast<float>(dh))),
+                                         is_causal ? 1 : 0, nullptr),
+                  op);
+    return out;
+}
+}  // namespace transformer
+
 // ---- layout ---------------------------------------------------------------------------------------------------------
 inline Tensor reshape(const Tensor& x, const Shape& shape) { return x.view(shape, x.layout()); }
 inline Tensor untilize(const Tensor& x) { return x.with_layout(Layout::ROW_MAJOR); }

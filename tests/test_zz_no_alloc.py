@@ -29,20 +29,26 @@ def _case(pkg, ctx, stream, M, N, K, ta, tb, split, seed, **kw):
     return got, ref, oracle
 
 
+def _same(got, ref):
+    """b200_gemm may pick another kernel or slice count for the same product (its planner also knows the CTA-pair
+    kernel), which changes the order of the fp32 additions: equal up to one bf16 rounding, not bit for bit."""
+    return mo.rel_frobenius(got.float().cpu().numpy(), ref.float().cpu().numpy()) <= 2e-3
+
+
 def test_static_scratch_matches_gemm_on_two_calls_in_a_row(pkg, ctx, stream):
     # call 1: dW-shaped product (reduction over 4096 tokens), 4 K slices
     got, ref, oracle = _case(pkg, ctx, stream, 384, 264, 4096, True, False, 4, seed=101)
-    assert torch.equal(got, ref), "first call differs from b200_gemm"
+    assert _same(got, ref), "first call differs from b200_gemm"
     assert mo.rel_frobenius(got.float().cpu().numpy(), oracle) <= 1e-2
     # call 2 straight after, other shape / form / slice count: must not see call 1's partial sums
     got, ref, oracle = _case(pkg, ctx, stream, 200, 512, 1536, False, True, 3, seed=202)
-    assert torch.equal(got, ref), "second call differs from b200_gemm"
+    assert _same(got, ref), "second call differs from b200_gemm"
     assert mo.rel_frobenius(got.float().cpu().numpy(), oracle) <= 1e-2
     # automatic slice choice, with a fused epilogue
     bias = torch.randn(256, generator=torch.Generator().manual_seed(5)).bfloat16().cuda()
     got, ref, oracle = _case(pkg, ctx, stream, 256, 256, 8192, True, False, 0, seed=303, bias=bias,
                              activation=pkg.ACT_RELU)
-    assert torch.equal(got, ref)
+    assert _same(got, ref)
     assert mo.rel_frobenius(got.float().cpu().numpy(), mo.relu(oracle + bias.float().cpu().numpy())) <= 1e-2
 
 

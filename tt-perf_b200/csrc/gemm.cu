@@ -93,8 +93,13 @@ int b200_gemm_scratch_bytes(b200_ctx* ctx, const b200_gemm_desc* d, size_t* out_
     if (d->M == 0 || d->N == 0 || d->K == 0) return B200_OK;
     if (d->algo == B200_GEMM_SIMT) return B200_OK;
     if (!gemm_tcgen05_eligible(*d, nullptr)) return B200_OK;
-    const int splits = gemm_choose_split_k(ctx, *d);
-    if (splits > 1) *out_bytes = static_cast<size_t>(splits) * d->batch * d->M * d->N * sizeof(float);
+    const GemmPlan plan = gemm_plan(ctx, *d, pair_kernel_enabled() && gemm_tuned_block_n() == 0);
+    if (plan.splits > 1) {
+        if (plan.pair)  // whole 256 x 256 tiles
+            *out_bytes = static_cast<size_t>(plan.splits) * d->batch * ((d->M + 255) / 256) * ((d->N + 255) / 256) * 256 * 256 * sizeof(float);
+        else
+            *out_bytes = static_cast<size_t>(plan.splits) * d->batch * d->M * d->N * sizeof(float);
+    }
     return B200_OK;
 }
 
@@ -126,10 +131,18 @@ int b200_gemm(b200_ctx* ctx, const b200_gemm_desc* d, void* stream_v) {
     if (d->algo == B200_GEMM_TCGEN05 && !eligible)
         return fail(B200_ERR_INVALID_ARG, "b200_gemm: tcgen05 path requested but %s", why);
     if (d->algo == B200_GEMM_SIMT || !eligible) return launch_gemm_simt(ctx, *d, stream);
-    const int splits = gemm_choose_split_k(ctx, *d);
-    if (splits == 1 && pair_kernel_enabled() && gemm_tuned_block_n() == 0 && gemm_pair_eligible(ctx, *d, nullptr))
-        return launch_gemm_tcgen05_pair(ctx, *d, stream);
-    return launch_gemm_tcgen05(ctx, *d, splits, stream);
+    GemmPlan plan = gemm_plan(ctx, *d, pair_kernel_enabled() && gemm_tuned_block_n() == 0);
+    {
+        // tuning sweeps (B200_GEMM_TUNE=1): B200_GEMM_KERNEL=pair pins the CTA-pair kernel with the descriptor's split_k
+        static const bool tune = [] { const char* e = getenv("B200_GEMM_TUNE"); return e && atoi(e) != 0; }();
+        const char* k = tune ? getenv("B200_GEMM_KERNEL") : nullptr;
+        if (k && strcmp(k, "pair") == 0 && gemm_pair_supported(*d, nullptr)) {
+            plan.pair = true;
+            plan.splits = d->split_k > 1 ? static_cast<int>(d->split_k) : 1;
+        }
+    }
+    if (plan.pair) return launch_gemm_tcgen05_pair(ctx, *d, stream, nullptr, plan.splits);
+    return launch_gemm_tcgen05(ctx, *d, plan.splits, stream);
 }
 
 }  // extern "C"

@@ -127,6 +127,8 @@ struct GemmParams {
     int c_vec_ok;      // rows of C start 16-byte aligned, so 16-byte stores are legal
     float* partial;    // k_splits > 1: fp32 partial sums [split][batch][M][N]
     int partial_round_bf16;  // HiFi2 / LoFi: round partial sums to bf16 precision
+    unsigned* tickets; // pair kernel, k_splits > 1: one counter per (tile, CTA of the pair); the CTA whose slice
+                       // finishes last adds the other slices' partial sums to its accumulator and writes C
     EpiParams epi;
     int* status;
     int group_m;       // tile rasterisation: row-tiles per column sweep
@@ -164,7 +166,17 @@ int launch_gemm_tcgen05(b200_ctx* ctx, const b200_gemm_desc& d, int k_splits, cu
 int launch_splitk_reduce(b200_ctx* ctx, const b200_gemm_desc& d, const float* partial, int splits, cudaStream_t stream);
 // CTA-pair (cta_group::2) kernel for large products; `gemm_pair_eligible` says whether it applies.
 bool gemm_pair_eligible(const b200_ctx* ctx, const b200_gemm_desc& d, const GemmRoute* route);
-int launch_gemm_tcgen05_pair(b200_ctx* ctx, const b200_gemm_desc& d, cudaStream_t stream, const GemmRoute* route = nullptr);
+// Layouts the pair kernel can handle at all, whatever the tile count.
+bool gemm_pair_supported(const b200_gemm_desc& d, const GemmRoute* route);
+int launch_gemm_tcgen05_pair(b200_ctx* ctx, const b200_gemm_desc& d, cudaStream_t stream, const GemmRoute* route = nullptr,
+                             int k_splits = 1);
+// Kernel, tile width and K-slice count for one product. allow_pair = false restricts the choice to the single-CTA kernel.
+struct GemmPlan {
+    bool pair;   // CTA-pair kernel (256 x 256 tiles) instead of the single-CTA kernel
+    int bn;      // tile width of the single-CTA kernel
+    int splits;
+};
+GemmPlan gemm_plan(const b200_ctx* ctx, const b200_gemm_desc& d, bool allow_pair);
 int launch_gemm_simt(b200_ctx* ctx, const b200_gemm_desc& d, cudaStream_t stream);
 bool gemm_tcgen05_eligible(const b200_gemm_desc& d, const char** why);
 // Chooses the K-slice count for the tcgen05 path (1 = no split).

@@ -41,8 +41,8 @@ struct TileCfg {
     static constexpr int A_BYTES = BM * BK * 2;
     static constexpr int B_BYTES = BN * BK * 2;
     static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
-    static constexpr int STAGES = (BN == 256) ? 4 : (BN == 128 ? 6 : 8);
-    static constexpr int TMEM_COLS = 2 * BN;
+    static constexpr int STAGES = (BN >= 192) ? 4 : (BN == 128 ? 6 : 8);
+    static constexpr int TMEM_COLS = BN == 192 ? 512 : 2 * BN;  // two accumulators; allocations are powers of two
     static constexpr int EPI_BYTES = 4 * 2 * EPI_STAGE_BYTES;  // 4 epilogue warps, double buffered
     static constexpr int BARRIER_BYTES = 256;
     static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + EPI_BYTES + BARRIER_BYTES + 1024;
@@ -504,11 +504,6 @@ bool gemm_tcgen05_eligible(const b200_gemm_desc& d, const char** why) {
 
 namespace {
 
-struct GemmPlan {
-    int bn;
-    int splits;
-};
-
 // Normalises a requested K-slice count so that every slice gets at least one K block.
 int normalise_splits(int want, int num_kb) {
     want = std::max(1, std::min(want, num_kb));
@@ -516,58 +511,84 @@ int normalise_splits(int want, int num_kb) {
     return (num_kb + per - 1) / per;
 }
 
-// Picks the tile width and the K-slice count together from a cost model fitted to timings on B200. The unit is the
-// time one 128-row tile spends on one output column of one K block at full tensor rate (about 1 ns).
-//   main loop: rounds of the persistent grid x (K blocks per work item + pipeline fill) x tile width x c(width);
-//              c = 1, 1.5, 3 for 256, 128, 64 columns: a narrower tile re-reads the A block more often per flop
-//              and the shared-memory fill rate, not the tensor pipe, then sets the pace;
-//   split-K:   a fixed charge for the second launch plus the fp32 partial sums written and read back.
-GemmPlan plan_gemm(const b200_ctx* ctx, const b200_gemm_desc& d) {
-    const int num_kb = static_cast<int>((d.K + BK - 1) / BK);
-    const long long m_tiles = d.batch * ((d.M + BM - 1) / BM);
-    const int widths[3] = {256, 128, 64};
-    const double cost_per_col[3] = {1.0, 1.5, 3.0};
-    const double split_fixed = 6500.0;
-    const double split_per_elem = 2.56e-3;  // 8 bytes of partial-sum traffic per element per slice
-    const double out_elems = static_cast<double>(d.batch) * d.M * d.N;
-    GemmPlan best{256, 1};
-    double best_cost = 0.0;
-    for (int i = 0; i < 3; ++i) {
-        const int bn = widths[i];
-        if (i < 2 && d.N <= bn / 2) continue;  // more than half of the tile would be padding
-        const long long tiles = m_tiles * ((d.N + bn - 1) / bn);
-        int cand[4] = {1, 0, 0, 0};
-        int n_cand = 1;
-        if (d.split_k > 1) {
-            cand[0] = normalise_splits(d.split_k, num_kb);
-        } else if (d.split_k == 0 && tiles * 2 <= ctx->sm_count && num_kb >= 8) {
-            const int fill = static_cast<int>(ctx->sm_count / tiles);  // slices that fill one round of the grid
-            const int most = std::min(std::min(fill, num_kb / 4), 32); // at least 4 K blocks per slice
-            for (int want : {most, most / 2, most / 4}) {
-                if (want < 2) break;
-                const int s = normalise_splits(want, num_kb);
-                bool seen = false;
-                for (int c = 0; c < n_cand; ++c) seen |= cand[c] == s;
-                if (!seen) cand[n_cand++] = s;
-            }
+// Slice counts worth trying for `tiles` work items on `slots` concurrent CTAs (or CTA pairs).
+int split_candidates(const b200_gemm_desc& d, long long tiles, long long slots, int num_kb, int (&cand)[4]) {
+    cand[0] = 1;
+    int n = 1;
+    if (d.split_k > 1) {
+        cand[0] = normalise_splits(d.split_k, num_kb);
+    } else if (d.split_k == 0 && tiles * 2 <= slots && num_kb >= 8) {
+        const int fill = static_cast<int>(slots / tiles);              // slices that fill one round of the grid
+        const int most = std::min(std::min(fill, num_kb / 4), 32);     // at least 4 K blocks per slice
+        for (int want : {most, most / 2, most / 4}) {
+            if (want < 2) break;
+            const int s = normalise_splits(want, num_kb);
+            bool seen = false;
+            for (int c = 0; c < n; ++c) seen |= cand[c] == s;
+            if (!seen) cand[n++] = s;
         }
-        for (int c = 0; c < n_cand; ++c) {
+    }
+    return n;
+}
+
+}  // namespace
+
+// Picks the kernel, the tile width and the K-slice count together from a cost model fitted to timings on B200. The
+// unit is the time one 128-row tile spends on one output column of one K block at full tensor rate (about 1 ns).
+//   main loop: rounds of the persistent grid x (K blocks per work item + pipeline fill) x tile width x c(width);
+//              c = 1, 1.2, 1.5, 3 for 256, 192, 128, 64 columns: a narrower tile re-reads the A block more often per flop
+//              and the shared-memory fill rate, not the tensor pipe, then sets the pace; 0.95 for the CTA-pair
+//              kernel, whose two CTAs share the B tile;
+//   K slices:  single-CTA kernel: a fixed charge for the second launch plus the fp32 partial sums written and read
+//              back by it; pair kernel: the last slice to finish adds the others inside the same launch: no second
+//              launch, but one CTA reads every other slice of its tile, so the charge grows with the slice count and
+//              two or three slices is where it pays.
+GemmPlan gemm_plan(const b200_ctx* ctx, const b200_gemm_desc& d, bool allow_pair) {
+    const int num_kb = static_cast<int>((d.K + BK - 1) / BK);
+    const double out_elems = static_cast<double>(d.batch) * d.M * d.N;
+    GemmPlan best{false, 256, 1};
+    double best_cost = 0.0;
+    auto offer = [&](const GemmPlan& plan, double cost) {
+        if (best_cost == 0.0 || cost < best_cost * 0.97) {  // near ties go to the earlier plan
+            best_cost = cost;
+            best = plan;
+        }
+    };
+    if (allow_pair && gemm_pair_supported(d, nullptr)) {
+        const long long pairs = ctx->sm_count / 2;
+        const long long tiles = d.batch * ((d.M + 255) / 256) * ((d.N + 255) / 256);
+        int cand[4];
+        const int n = split_candidates(d, tiles, pairs, num_kb, cand);
+        for (int c = 0; c < n; ++c) {
             const int splits = cand[c];
-            const long long work = tiles * splits;
-            const long long rounds = (work + ctx->sm_count - 1) / ctx->sm_count;
+            if (splits > 1 && tiles * 2 >= kTicketCount) continue;
+            const long long rounds = (tiles * splits + pairs - 1) / pairs;
+            const int kb_per = (num_kb + splits - 1) / splits;
+            double cost = static_cast<double>(rounds) * (kb_per + 6) * 256 * 0.95;
+            if (splits > 1) cost += 1000.0 + 4000.0 * splits;
+            offer(GemmPlan{true, 256, splits}, cost);
+        }
+    }
+    const long long m_tiles = d.batch * ((d.M + BM - 1) / BM);
+    const int widths[4] = {256, 192, 128, 64};
+    const double cost_per_col[4] = {1.0, 1.2, 1.5, 3.0};
+    for (int i = 0; i < 4; ++i) {
+        const int bn = widths[i];
+        if (i < 3 && d.N <= bn / 2) continue;  // more than half of the tile would be padding
+        const long long tiles = m_tiles * ((d.N + bn - 1) / bn);
+        int cand[4];
+        const int n = split_candidates(d, tiles, ctx->sm_count, num_kb, cand);
+        for (int c = 0; c < n; ++c) {
+            const int splits = cand[c];
+            const long long rounds = (tiles * splits + ctx->sm_count - 1) / ctx->sm_count;
             const int kb_per = (num_kb + splits - 1) / splits;
             double cost = static_cast<double>(rounds) * (kb_per + 6) * bn * cost_per_col[i];
-            if (splits > 1) cost += split_fixed + split_per_elem * splits * out_elems;
-            if (best_cost == 0.0 || cost < best_cost * 0.97) {  // near ties go to the earlier (wider, unsplit) plan
-                best_cost = cost;
-                best = GemmPlan{bn, splits};
-            }
+            if (splits > 1) cost += 6500.0 + 2.56e-3 * splits * out_elems;
+            offer(GemmPlan{false, bn, splits}, cost);
         }
     }
     return best;
 }
-
-}  // namespace
 
 // B200_GEMM_TUNE=1 makes every launch read B200_GEMM_BLOCK_N (64, 128 or 256) so that a sweep can compare tile widths
 // inside one process; without it the planner decides.
@@ -576,16 +597,16 @@ int gemm_tuned_block_n() {
     if (!enabled) return 0;
     const char* e = getenv("B200_GEMM_BLOCK_N");
     const int v = e ? atoi(e) : 0;
-    return (v == 64 || v == 128 || v == 256) ? v : 0;
+    return (v == 64 || v == 128 || v == 192 || v == 256) ? v : 0;
 }
 
 int gemm_choose_block_n(const b200_ctx* ctx, const b200_gemm_desc& d) {
     const int forced = gemm_tuned_block_n();
     if (forced && (forced == 64 || d.N > 64)) return forced;
-    return plan_gemm(ctx, d).bn;
+    return gemm_plan(ctx, d, false).bn;
 }
 
-int gemm_choose_split_k(const b200_ctx* ctx, const b200_gemm_desc& d) { return plan_gemm(ctx, d).splits; }
+int gemm_choose_split_k(const b200_ctx* ctx, const b200_gemm_desc& d) { return gemm_plan(ctx, d, false).splits; }
 
 int group_m_setting() {
     static const int value = [] {
@@ -691,6 +712,8 @@ int launch_gemm_tcgen05(b200_ctx* ctx, const b200_gemm_desc& d, int k_splits, cu
     const int grid = min(p.total_work, ctx->sm_count);
     if (bn == 256)
         rc = launch_bn<256>(a_kmajor, b_kmajor, tmA, tmB, tmC, p, grid, stream);
+    else if (bn == 192)
+        rc = launch_bn<192>(a_kmajor, b_kmajor, tmA, tmB, tmC, p, grid, stream);
     else if (bn == 128)
         rc = launch_bn<128>(a_kmajor, b_kmajor, tmA, tmB, tmC, p, grid, stream);
     else

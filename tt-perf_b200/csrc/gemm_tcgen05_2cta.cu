@@ -40,13 +40,20 @@ constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + EPI_BYTES + BARRIER_BYTES + 10
 
 struct PairWork {
     int b, m0, n0;
+    int split, tile;   // K slice, and the index of the output tile among batch * tiles (the ticket it uses)
+    int kb_begin, kb_end;
 };
 
 __device__ __forceinline__ PairWork decode_pair(const GemmParams& p, int w) {
     PairWork it;
     const int tiles_mn = p.num_m_tiles * p.num_n_tiles;
-    it.b = w / tiles_mn;
-    const int t = w - it.b * tiles_mn;
+    const int per_split = p.batch * tiles_mn;
+    it.split = w / per_split;
+    it.tile = w - it.split * per_split;
+    it.kb_begin = it.split * p.kb_per_split;
+    it.kb_end = min(p.num_kb, it.kb_begin + p.kb_per_split);
+    it.b = it.tile / tiles_mn;
+    const int t = it.tile - it.b * tiles_mn;
     const int tiles_per_group = p.group_m * p.num_n_tiles;
     const int g = t / tiles_per_group;
     const int first_m = g * p.group_m;
@@ -55,6 +62,23 @@ __device__ __forceinline__ PairWork decode_pair(const GemmParams& p, int w) {
     it.m0 = (first_m + rr % gsz) * BM_PAIR;
     it.n0 = (rr / gsz) * BN;
     return it;
+}
+
+// Named barrier of the four epilogue warps (128 threads), plain and with an AND-reduction of a predicate.
+__device__ __forceinline__ void epilogue_warps_sync() { asm volatile("bar.sync 2, 128;" ::: "memory"); }
+__device__ __forceinline__ bool epilogue_warps_all(bool pred) {
+    uint32_t out;
+    asm volatile(
+        "{\n\t"
+        ".reg .pred p, q;\n\t"
+        "setp.ne.u32 p, %1, 0;\n\t"
+        "barrier.cta.red.and.pred q, 2, 128, p;\n\t"
+        "selp.u32 %0, 1, 0, q;\n\t"
+        "}\n"
+        : "=r"(out)
+        : "r"(static_cast<uint32_t>(pred))
+        : "memory");
+    return out != 0;
 }
 
 template <bool A_KMAJOR, bool B_KMAJOR>
@@ -71,6 +95,7 @@ gemm_tcgen05_2cta_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_c
     uint64_t* tmem_empty_bar = tmem_full_bar + 2;                  // used in the leader only: 8 arrivals (4 warps x 2 CTAs)
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(tmem_empty_bar + 2);
     volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+    volatile int* last_flag = abort_flag + 1;      // split-K: this CTA drew the last ticket of its tile
 
     const int warp = threadIdx.x >> 5;
     const int lane = threadIdx.x & 31;
@@ -115,7 +140,7 @@ gemm_tcgen05_2cta_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_c
                 const int bb = p.b_batched ? it.b : 0;
                 const int m_cta = it.m0 + static_cast<int>(rank) * BM_CTA;
                 const int n_cta = it.n0 + static_cast<int>(rank) * BN_CTA;
-                for (int kb = 0; kb < p.num_kb; ++kb) {
+                for (int kb = it.kb_begin; kb < it.kb_end; ++kb) {
                     if (!mbar_wait(&empty_bar[stage], phase ^ 1u, abort_flag)) {
                         ok = false;
                         break;
@@ -171,6 +196,7 @@ gemm_tcgen05_2cta_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_c
             uint32_t acc_phase = 0;
             bool ok = true;
             for (int w = cluster_id; ok && w < p.total_work; w += num_clusters) {
+                const PairWork it = decode_pair(p, w);
                 if (!mbar_wait(&tmem_empty_bar[acc], acc_phase ^ 1u, abort_flag)) break;
                 tcgen05_fence_after_sync();
                 const uint32_t d_tmem = tmem_base + static_cast<uint32_t>(acc * BN);
@@ -178,7 +204,7 @@ gemm_tcgen05_2cta_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_c
                 const int prof_slot = (w - cluster_id) / num_clusters;
                 if (p.prof && prof_slot < 8) p.prof[(blockIdx.x * 8 + prof_slot) * 8 + 0] = clock64();
 #endif
-                for (int kb = 0; kb < p.num_kb; ++kb) {
+                for (int kb = it.kb_begin; kb < it.kb_end; ++kb) {
                     if (!mbar_wait(&full_bar[stage], phase, abort_flag)) {
                         ok = false;
                         break;
@@ -190,7 +216,7 @@ gemm_tcgen05_2cta_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_c
                     for (int k = 0; k < BK / UMMA_K; ++k) {
                         const uint64_t da = make_smem_desc_sw128(a_addr + k * A_KSTEP, A_LBO, 1024);
                         const uint64_t db = make_smem_desc_sw128(b_addr + k * B_KSTEP, B_LBO, 1024);
-                        umma_f16_ss_pair(d_tmem, da, db, idesc, (kb > 0 || k > 0) ? 1u : 0u);
+                        umma_f16_ss_pair(d_tmem, da, db, idesc, (kb > it.kb_begin || k > 0) ? 1u : 0u);
                     }
                     umma_commit_pair(&empty_bar[stage], 3);  // frees the stage in both CTAs
                     if (++stage == STAGES) {
@@ -222,7 +248,12 @@ gemm_tcgen05_2cta_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_c
         for (int w = cluster_id; w < p.total_work; w += num_clusters) {
             const PairWork it = decode_pair(p, w);
             const bool got = mbar_wait(&tmem_full_bar[acc], acc_phase, abort_flag);
-            if (!__all_sync(0xffffffffu, got)) break;
+            if (p.k_splits > 1) {
+                // the four epilogue warps meet at named barriers below: they must agree on whether to go on
+                if (!epilogue_warps_all(__all_sync(0xffffffffu, got))) break;
+            } else if (!__all_sync(0xffffffffu, got)) {
+                break;
+            }
             tcgen05_fence_after_sync();
 #ifdef B200_GEMM_PROFILE
             const int eprof_slot = (w - cluster_id) / num_clusters;
@@ -237,7 +268,52 @@ gemm_tcgen05_2cta_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_c
                 dst_count = 1;
                 row_coord -= dst_first * p.scatter_rows;
             }
-            if (m_cta < p.M) {  // a CTA whose 128 rows lie entirely below the matrix has nothing to store
+            bool finish = true;  // this CTA writes C for the tile
+            // Partial sums live in a layout of their own, [slice][tile][CTA of the pair][32-column chunk][vector j]
+            // [thread]: the k-th 16-byte vector of a thread's 32 columns sits next to the same vector of its
+            // neighbours, so a warp writes and reads 512 contiguous bytes per instruction (row-major fp32 would cost
+            // one 128-byte line per thread per instruction).
+            const size_t cta_floats = static_cast<size_t>(BM_CTA) * BN;
+            const size_t tiles_total = static_cast<size_t>(p.batch) * p.num_m_tiles * p.num_n_tiles;
+            const int ethread = threadIdx.x - 64;  // 0..127 within the epilogue warps
+            auto part_at = [&](int slice_idx) {
+                return reinterpret_cast<float4*>(p.partial + ((static_cast<size_t>(slice_idx) * tiles_total + it.tile) * 2 + rank) * cta_floats) +
+                       ethread;
+            };
+            if (p.k_splits > 1) {
+                // K slices of one tile run in different CTA pairs. Each writes its fp32 partial sums and then draws a
+                // ticket; whoever draws the last one knows that all the others are complete in memory, adds them to
+                // the sums it still holds in TMEM and runs the normal epilogue. Nobody waits for anybody.
+                float4* mine = part_at(it.split);
+#pragma unroll 1
+                for (int c = 0; c < BN; c += 32) {
+                    if (it.n0 + c >= p.N) break;
+                    uint32_t v[32];
+                    tmem_ld_32x32b_x32(taddr + c, v);
+                    tmem_ld_wait();
+                    if (p.partial_round_bf16) {
+#pragma unroll
+                        for (int i = 0; i < 32; ++i)
+                            v[i] = __float_as_uint(__bfloat162float(__float2bfloat16_rn(__uint_as_float(v[i]))));
+                    }
+                    float4* dst = mine + (c / 32) * 8 * 128;
+#pragma unroll
+                    for (int i = 0; i < 8; ++i)
+                        dst[i * 128] = make_float4(__uint_as_float(v[4 * i]), __uint_as_float(v[4 * i + 1]),
+                                                   __uint_as_float(v[4 * i + 2]), __uint_as_float(v[4 * i + 3]));
+                }
+                __threadfence();
+                epilogue_warps_sync();
+                if (threadIdx.x == 64) {
+                    const unsigned t = atomicAdd(&p.tickets[it.tile * 2 + static_cast<int>(rank)], 1u);
+                    *last_flag = (t == static_cast<unsigned>(p.k_splits - 1)) ? 1 : 0;
+                    if (*last_flag) p.tickets[it.tile * 2 + static_cast<int>(rank)] = 0u;  // ready for the next launch
+                }
+                epilogue_warps_sync();
+                finish = *last_flag != 0;
+                if (finish) __threadfence();
+            }
+            if (finish && m_cta < p.M) {  // a CTA whose 128 rows lie entirely below the matrix has nothing to store
 #pragma unroll 1
                 for (int c = 0; c < BN; c += box_cols) {
                     const int n = it.n0 + c;
@@ -253,6 +329,25 @@ gemm_tcgen05_2cta_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_c
                         uint32_t v[32];
                         tmem_ld_32x32b_x32(taddr + c + h * 32, v);
                         tmem_ld_wait();
+                        if (p.k_splits > 1 && p.partial_round_bf16) {
+#pragma unroll
+                            for (int i = 0; i < 32; ++i)
+                                v[i] = __float_as_uint(__bfloat162float(__float2bfloat16_rn(__uint_as_float(v[i]))));
+                        }
+                        if (p.k_splits > 1) {
+                            for (int sl = 0; sl < p.k_splits; ++sl) {
+                                if (sl == it.split) continue;
+                                const float4* src = part_at(sl) + ((c + h * 32) / 32) * 8 * 128;
+#pragma unroll
+                                for (int i = 0; i < 8; ++i) {
+                                    const float4 a = __ldcg(src + i * 128);
+                                    v[4 * i] = __float_as_uint(__uint_as_float(v[4 * i]) + a.x);
+                                    v[4 * i + 1] = __float_as_uint(__uint_as_float(v[4 * i + 1]) + a.y);
+                                    v[4 * i + 2] = __float_as_uint(__uint_as_float(v[4 * i + 2]) + a.z);
+                                    v[4 * i + 3] = __float_as_uint(__uint_as_float(v[4 * i + 3]) + a.w);
+                                }
+                            }
+                        }
                         float f[32];
                         epi_apply32(p.epi, v, f, row, nh, p.N);
                         if (p.c_f32) {
@@ -370,7 +465,8 @@ static int pair_group_m(int num_m_tiles) {
     return num_m_tiles >= 64 ? 16 : 8;  // measured: 8 is best up to 8192 rows, 16 at 16384
 }
 
-bool gemm_pair_eligible(const b200_ctx* ctx, const b200_gemm_desc& d, const GemmRoute* route) {
+// Operand and output layouts the pair kernel can handle at all (its epilogue always stores through TMA).
+bool gemm_pair_supported(const b200_gemm_desc& d, const GemmRoute* route) {
     if (!gemm_tcgen05_eligible(d, nullptr)) return false;
     const int cvec = d.c_dtype == B200_F32 ? 4 : 8;
     if ((d.ldc % cvec) != 0 || (d.batch > 1 && (d.stride_c % cvec) != 0)) return false;
@@ -379,9 +475,14 @@ bool gemm_pair_eligible(const b200_ctx* ctx, const b200_gemm_desc& d, const Gemm
     } else if (route->scatter_rows > 0 && (route->scatter_rows % BM_CTA) != 0) {
         return false;
     }
+    return d.N >= 256 && d.M >= 256;
+}
+
+bool gemm_pair_eligible(const b200_ctx* ctx, const b200_gemm_desc& d, const GemmRoute* route) {
+    if (!gemm_pair_supported(d, route)) return false;
     // worth it only when the 256 x 256 tiles keep all CTA pairs busy
     const long long tiles = d.batch * ((d.M + BM_PAIR - 1) / BM_PAIR) * ((d.N + BN - 1) / BN);
-    if (d.N < 256 || d.M < 256 || tiles < (ctx->sm_count / 2)) return false;
+    if (tiles < (ctx->sm_count / 2)) return false;
     // Both kernels give a CTA 128 x 256 outputs per round; the pair kernel must not need more rounds (an odd number
     // of 128-row blocks, or a tile count just above a multiple of the pair count, costs it one).
     const long long pairs = ctx->sm_count / 2;
@@ -389,7 +490,8 @@ bool gemm_pair_eligible(const b200_ctx* ctx, const b200_gemm_desc& d, const Gemm
     return (tiles + pairs - 1) / pairs <= (tiles_single + ctx->sm_count - 1) / ctx->sm_count;
 }
 
-int launch_gemm_tcgen05_pair(b200_ctx* ctx, const b200_gemm_desc& d, cudaStream_t stream, const GemmRoute* route) {
+int launch_gemm_tcgen05_pair(b200_ctx* ctx, const b200_gemm_desc& d, cudaStream_t stream, const GemmRoute* route,
+                             int k_splits) {
     const bool a_kmajor = d.transpose_a == 0;
     const bool b_kmajor = d.transpose_b != 0;
     GemmParams p{};
@@ -400,11 +502,24 @@ int launch_gemm_tcgen05_pair(b200_ctx* ctx, const b200_gemm_desc& d, cudaStream_
     p.num_m_tiles = (p.M + BM_PAIR - 1) / BM_PAIR;
     p.num_n_tiles = (p.N + BN - 1) / BN;
     p.num_kb = (p.K + BK - 1) / BK;
-    p.k_splits = 1;
-    p.kb_per_split = p.num_kb;
-    const long long total = static_cast<long long>(p.batch) * p.num_m_tiles * p.num_n_tiles;
+    k_splits = std::max(1, std::min(k_splits, p.num_kb));
+    p.kb_per_split = (p.num_kb + k_splits - 1) / k_splits;
+    p.k_splits = (p.num_kb + p.kb_per_split - 1) / p.kb_per_split;  // every slice gets at least one K block
+    const long long tiles = static_cast<long long>(p.batch) * p.num_m_tiles * p.num_n_tiles;
+    const long long total = tiles * p.k_splits;
     B200_REQUIRE(total < (1ll << 31), "b200_gemm: too many tiles (%lld)", total);
     p.total_work = static_cast<int>(total);
+    p.partial = nullptr;
+    p.tickets = nullptr;
+    if (p.k_splits > 1) {
+        B200_REQUIRE(route == nullptr || route->n_dst == 0, "b200_gemm: routed outputs cannot be combined with K slices");
+        B200_REQUIRE(tiles * 2 < kTicketCount, "b200_gemm: %lld tiles exceed the ticket counters of the sliced pair kernel", tiles);
+        const size_t bytes = static_cast<size_t>(p.k_splits) * tiles * BM_PAIR * BN * sizeof(float);  // whole tiles
+        int rc_s = ensure_scratch(ctx, bytes);
+        if (rc_s != B200_OK) return rc_s;
+        p.partial = static_cast<float*>(ctx->d_scratch);
+        p.tickets = ctx_tickets(ctx);
+    }
     p.a_batched = (d.batch > 1 && d.stride_a != 0) ? 1 : 0;
     p.b_batched = (d.batch > 1 && d.stride_b != 0) ? 1 : 0;
     p.C = d.C;
@@ -419,6 +534,7 @@ int launch_gemm_tcgen05_pair(b200_ctx* ctx, const b200_gemm_desc& d, cudaStream_
     p.epi.gelu_tanh = d.fidelity == B200_LOFI;
     p.epi.causal = d.causal_mask;
     p.epi.mask_value = d.mask_value;
+    p.partial_round_bf16 = (d.fidelity == B200_LOFI || d.fidelity == B200_HIFI2) ? 1 : 0;
     p.status = ctx->d_status;
     p.group_m = pair_group_m(p.num_m_tiles);
     p.epi_mode = 1;
