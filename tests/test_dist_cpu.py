@@ -77,3 +77,27 @@ def test_two_rank_gloo_column_and_row_parallel():
             p.join(120)
         assert all(p.exitcode == 0 for p in procs), [p.exitcode for p in procs]
         assert dict(results) == {0: "ok", 1: "ok"}
+
+
+def test_tensor_parallel_shard_geometry():
+    """Host logic of the tensor-parallel block: uneven head counts, hidden-unit slices, weight shards."""
+    import numpy as np
+    from __graft_entry__ import load_package
+    tp = load_package().tp
+    assert tp.split_counts(25, 8) == [4, 3, 3, 3, 3, 3, 3, 3] and tp.split_counts(25, 2) == [13, 12]
+    assert sum(tp.split_counts(6400 // 8, 8)) * 8 == 6400
+    heads, d, f = 5, 320, 1280
+    rng = np.random.default_rng(0)
+    w = {k: rng.standard_normal(s).astype(np.float32) for k, s in dict(wq=(d, d), wk=(d, d), wv=(d, d), wo=(d, d), w1=(f, d),
+                                                                         w2=(d, f), bq=(d,), bk=(d,), bv=(d,), bo=(d,), b1=(f,),
+                                                                         b2=(d,), ln1_g=(d,), ln1_b=(d,), ln2_g=(d,), ln2_b=(d,)).items()}
+    cover_h, cover_f = np.zeros(d, int), np.zeros(f, int)
+    for r in range(4):
+        sh = tp.shard_weights(w, heads, 4, r)
+        kr = sh["heads"] * 64
+        assert sh["wqkv"].shape == (3 * kr, d) and sh["wo"].shape == (d, kr)
+        assert np.array_equal(sh["wqkv"][kr:2 * kr], w["wk"][sh["h0"]:sh["h1"]])
+        assert np.array_equal(sh["w2"], w["w2"][:, sh["f0"]:sh["f1"]]) and sh["w1"].shape[0] % 8 == 0
+        cover_h[sh["h0"]:sh["h1"]] += 1
+        cover_f[sh["f0"]:sh["f1"]] += 1
+    assert (cover_h == 1).all() and (cover_f == 1).all()   # every head and hidden unit owned exactly once

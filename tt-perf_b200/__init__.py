@@ -9,7 +9,7 @@ library is missing or reports a failure.
 """
 from __future__ import annotations
 
-from . import capi, dist, nn, tensor
+from . import capi, dist, nn, tensor, tp
 from .tensor import DeviceTensor  # noqa: F401
 from .capi import (  # noqa: F401
     ACT_GELU,
@@ -33,7 +33,7 @@ from .capi import (  # noqa: F401
 )
 
 __all__ = [
-    "capi", "dist", "nn", "tensor", "DeviceTensor", "lib", "lib_path", "Context", "GemmDesc", "B200Error",
+    "capi", "dist", "nn", "tensor", "tp", "DeviceTensor", "lib", "lib_path", "Context", "GemmDesc", "B200Error",
     "BF16", "F32", "U32", "ACT_NONE", "ACT_RELU", "ACT_GELU",
     "LOFI", "HIFI2", "HIFI3", "HIFI4", "ALGO_AUTO", "ALGO_TCGEN05", "ALGO_SIMT",
 ]

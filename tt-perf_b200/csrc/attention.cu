@@ -419,6 +419,10 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
     const int n_q = (g.S + BT - 1) / BT;
     const int i0 = g.causal ? jt : 0;
     const int n_it = n_q - i0;
+#ifdef B200_ATTN_PROFILE
+    const int prof_cta = (blockIdx.x == 0 && blockIdx.y < 2) ? 2 + static_cast<int>(blockIdx.y) : -1;
+    const int prof_warp = warp == 0 ? 0 : (warp == 5 ? 1 : (warp == 15 ? 2 : (warp == BWD_COMPUTE_WARPS ? 3 : -1)));
+#endif
 
     if (threadIdx.x == 0) {
         prefetch_tensormap(&tmQ);
@@ -466,7 +470,9 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
             const uint32_t ka = smem_u32(sK), va = smem_u32(sV), pta = smem_u32(sPT), dsa = smem_u32(sdST);
             for (int it = 0; ok && it < n_it; ++it) {
                 const int st = it & 1;
+                ATTN_STAMP(prof_cta, prof_warp, it, 0);
                 if (!mbar_wait(&qdo_full[st], (it >> 1) & 1, abort_flag)) { ok = false; break; }
+                ATTN_STAMP(prof_cta, prof_warp, it, 1);
                 tcgen05_fence_after_sync();
                 const uint32_t qa = smem_u32(sQ + st * TILE_BYTES);
                 const uint32_t doa = smem_u32(sdO + st * TILE_BYTES);
@@ -481,7 +487,9 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
                 // This commit also covers the dV and dK products of the tile before: once it fires P^T and dS^T may be
                 // overwritten.
                 umma_commit(sdp_full);
+                ATTN_STAMP(prof_cta, prof_warp, it, 2);
                 if (!mbar_wait(pds_ready, it & 1, abort_flag)) { ok = false; break; }
+                ATTN_STAMP(prof_cta, prof_warp, it, 3);
                 tcgen05_fence_after_sync();
 #pragma unroll
                 for (int k = 0; k < BT / UMMA_K; ++k)   // dQ_i = dS K (reduction over the 128 keys); first, it is read first
@@ -499,6 +507,7 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
                                 make_smem_desc_sw128(qa + k * (UMMA_K * 128), BT * 128, 1024), idesc_kn,
                                 (it > 0 || k > 0) ? 1u : 0u);
                 umma_commit(acc_done);
+                ATTN_STAMP(prof_cta, prof_warp, it, 4);
                 if (it + 2 < n_it) {
                     if (!mbar_wait(acc_done, it & 1, abort_flag)) { ok = false; break; }  // Q_i, dO_i no longer read
                     load_qdo(it + 2);
@@ -531,11 +540,14 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
                 else
                     dsum_s[st * BT + idx] = qi < g.S ? p.dsum[at] : 0.f;
             }
+            ATTN_STAMP(prof_cta, prof_warp, it, 0);
             compute_warps_sync<BWD_COMPUTE_WARPS * 32>();
+            ATTN_STAMP(prof_cta, prof_warp, it, 1);
             if (ok) {
                 const bool got = mbar_wait(sdp_full, it & 1, abort_flag);
                 ok = __all_sync(0xffffffffu, got);
             }
+            ATTN_STAMP(prof_cta, prof_warp, it, 2);
             if (ok) {
                 tcgen05_fence_after_sync();
                 const bool diag = g.causal && i == jt;  // query (column) c sees key (row) r only when c >= r
@@ -567,12 +579,14 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
                     store_bf16x8(sPT + off, pf);
                     store_bf16x8(sdST + off, df);
                 }
+                ATTN_STAMP(prof_cta, prof_warp, it, 3);
                 fence_proxy_async_smem();
                 tcgen05_fence_before_sync();
                 __syncwarp();
                 if (lane == 0) mbar_arrive(pds_ready);
                 const bool got_dq = mbar_wait(dq_full, it & 1, abort_flag);
                 ok = __all_sync(0xffffffffu, got_dq);
+                ATTN_STAMP(prof_cta, prof_warp, it, 4);
             }
             if (ok) {
                 tcgen05_fence_after_sync();
@@ -588,6 +602,7 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
                                                        __uint_as_float(v[4 * t + 2]), __uint_as_float(v[4 * t + 3])));
                 }
                 tcgen05_fence_before_sync();
+                ATTN_STAMP(prof_cta, prof_warp, it, 5);
             }
         }
         if (ok) {

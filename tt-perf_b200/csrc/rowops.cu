@@ -454,6 +454,102 @@ __global__ void __launch_bounds__(1024) row_block_kernel(const RowParams p) {
     }
 }
 
+// Cross-entropy over long rows (a vocabulary), one CTA of 1024 threads per row, the row staged in shared memory:
+//   pass 1  four 16-byte loads in flight per thread; the row goes to shared memory, running max
+//   pass 2  e = exp(x - max) once per element, summed in fp32 and written back to shared memory as bf16
+//   pass 3  d_logits = (e / sum - onehot) * alpha from shared memory, 16-byte stores
+// One exponential per element instead of two (the special-function unit, not HBM, bounds the two-exponential form on a
+// 50k vocabulary); the label's probability for the loss is computed in fp32 from the logit itself.
+constexpr int kCeThreads = 1024;
+__global__ void __launch_bounds__(kCeThreads, 2) cross_entropy_staged_kernel(const RowParams p) {
+    __shared__ float sh[32];
+    extern __shared__ uint4 srow[];
+    const int r = blockIdx.x;
+    const __nv_bfloat16* x0 = p.in0 + static_cast<size_t>(r) * p.ld0;
+    const int cols = p.cols;
+    const int full = cols / 8;            // whole vectors; a ragged tail of cols % 8 elements is handled by thread 0
+    const int tail0 = full * 8;
+    float m = -FLT_MAX;
+    // four 16-byte loads in flight per thread (two CTAs of 1024 threads leave 32 registers per thread)
+    for (int base = threadIdx.x; base < full; base += 4 * kCeThreads) {
+        uint4 raw[4];
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+            const int v = base + u * kCeThreads;
+            if (v < full) raw[u] = reinterpret_cast<const uint4*>(x0)[v];
+        }
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+            const int v = base + u * kCeThreads;
+            if (v < full) {
+                srow[v] = raw[u];
+                float f[8];
+                unpack_raw(raw[u], f);
+#pragma unroll
+                for (int i = 0; i < 8; ++i) m = fmaxf(m, f[i]);
+            }
+        }
+    }
+    float tail[8];
+    if (threadIdx.x == 0) {
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+            tail[i] = (tail0 + i < cols) ? __bfloat162float(x0[tail0 + i]) : -FLT_MAX;
+            m = fmaxf(m, tail[i]);
+        }
+    }
+    const float gm = block_max(m, sh);
+    const int label = static_cast<int>(p.labels[r]);
+    const float gm2 = gm * 1.4426950408889634f;
+    float s = 0.0f;
+    for (int v = threadIdx.x; v < full; v += kCeThreads) {
+        float f[8];
+        unpack_raw(srow[v], f);
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+            f[i] = exp2f(fmaf(f[i], 1.4426950408889634f, -gm2));
+            s += f[i];
+        }
+        srow[v] = make_uint4(pack_bf16x2(f[0], f[1]), pack_bf16x2(f[2], f[3]), pack_bf16x2(f[4], f[5]), pack_bf16x2(f[6], f[7]));
+    }
+    if (threadIdx.x == 0) {
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+            tail[i] = (tail0 + i < cols) ? exp2f(fmaf(tail[i], 1.4426950408889634f, -gm2)) : 0.0f;
+            s += tail[i];
+        }
+    }
+    const float gs = block_sum(s, sh);
+    const float inv = 1.0f / gs;
+    if (threadIdx.x == 0) {
+        const float xl = (label >= 0 && label < cols) ? __bfloat162float(x0[label]) : gm;
+        const float loss = (gm - xl) + __logf(gs);   // -log(exp(xl - gm) / gs)
+        if (p.row_loss) p.row_loss[r] = loss;
+        if (p.loss_sum) atomicAdd(p.loss_sum, loss * p.alpha);
+    }
+    if (p.out == nullptr) return;
+    __nv_bfloat16* y = p.out + static_cast<size_t>(r) * p.ldo;
+    const float a_inv = inv * p.alpha;
+    for (int v = threadIdx.x; v < full; v += kCeThreads) {
+        float f[8];
+        unpack_raw(srow[v], f);
+#pragma unroll
+        for (int i = 0; i < 8; ++i) f[i] *= a_inv;
+        if (label >= v * 8 && label < v * 8 + 8) {
+#pragma unroll
+            for (int i = 0; i < 8; ++i)
+                if (v * 8 + i == label) f[i] -= p.alpha;
+        }
+        reinterpret_cast<uint4*>(y)[v] =
+            make_uint4(pack_bf16x2(f[0], f[1]), pack_bf16x2(f[2], f[3]), pack_bf16x2(f[4], f[5]), pack_bf16x2(f[6], f[7]));
+    }
+    if (threadIdx.x == 0) {
+#pragma unroll
+        for (int i = 0; i < 8; ++i)
+            if (tail0 + i < cols) y[tail0 + i] = __float2bfloat16_rn(tail[i] * a_inv - ((tail0 + i == label) ? p.alpha : 0.0f));
+    }
+}
+
 template <int OP>
 int launch_row_op(const RowParams& p, cudaStream_t stream) {
     if (p.rows == 0 || p.cols == 0) return B200_OK;
@@ -486,6 +582,15 @@ int launch_row_op(const RowParams& p, cudaStream_t stream) {
         constexpr bool kForward = (OP == OP_SOFTMAX || OP == OP_LOG_SOFTMAX || OP == OP_CROSS_ENTROPY);
         q.stage_row = (kForward && p.vec0 && row_bytes <= 110 * 1024) ? 1 : 0;  // two CTAs per SM still fit
         const size_t smem = q.stage_row ? row_bytes : 0;
+        if (OP == OP_CROSS_ENTROPY && q.stage_row && p.causal_period == 0 && (p.out == nullptr || p.veco) &&
+            true) {
+            B200_CUDA_TRY(cudaFuncSetAttribute(cross_entropy_staged_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 112 * 1024));
+            B200_CUDA_TRY(cudaFuncSetAttribute(cross_entropy_staged_kernel, cudaFuncAttributePreferredSharedMemoryCarveout,
+                                               cudaSharedmemCarveoutMaxShared));
+            cross_entropy_staged_kernel<<<p.rows, kCeThreads, smem, stream>>>(q);
+            B200_CUDA_TRY(cudaGetLastError());
+            return B200_OK;
+        }
         if (smem > 48 * 1024)  // per device function and device; cheap enough to repeat
             B200_CUDA_TRY(cudaFuncSetAttribute(row_block_kernel<OP>, cudaFuncAttributeMaxDynamicSharedMemorySize, 112 * 1024));
         // a staged row allows two CTAs per SM: give each 1024 threads so the SM still has 64 warps in flight
