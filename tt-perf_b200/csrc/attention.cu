@@ -385,20 +385,32 @@ struct BwdParams {
 };
 
 constexpr int BWD_TMEM_COLS = 512;  // S^T 0..127, dP^T 128..255, dK 256..319, dV 320..383, dQ_i 384..447
-constexpr int BWD_SMEM = 6 * TILE_BYTES + 2 * PT_BYTES + 2048 + 64 + 1024;
+constexpr int DQ_BOX_BYTES = BT * 32 * 4;   // [128 queries x 32 fp32 columns], rows of 128 bytes
+// K, V, Q x 2, dO x 2, P^T, dS^T, two dQ staging buffers of two boxes each, lse / rowsum, barriers. That is all of the
+// 227 KB a CTA may have, with 960 bytes to spare for rounding the base up to 1024 (the kernel checks that this suffices).
+constexpr int BWD_SMEM_USED = 6 * TILE_BYTES + 2 * PT_BYTES + 4 * DQ_BOX_BYTES + 2048 + 64;
+constexpr int BWD_SMEM = 227 * 1024;
+static_assert(BWD_SMEM_USED <= BWD_SMEM, "backward shared memory exceeds the per-CTA limit");
 
 __global__ void __launch_bounds__(BWD_THREADS, 1)
 attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
-                const __grid_constant__ CUtensorMap tmV, const __grid_constant__ CUtensorMap tmdO, const BwdParams p) {
+                const __grid_constant__ CUtensorMap tmV, const __grid_constant__ CUtensorMap tmdO,
+                const __grid_constant__ CUtensorMap tmdQ, const BwdParams p) {
     extern __shared__ uint8_t smem_raw[];
-    uint8_t* smem = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
+    const uint32_t pad = (1024u - (smem_u32(smem_raw) & 1023u)) & 1023u;
+    if (pad + BWD_SMEM_USED > BWD_SMEM) {  // uniform over the CTA; nothing has been set up yet
+        if (threadIdx.x == 0) atomicExch(p.status, 1);
+        return;
+    }
+    uint8_t* smem = smem_raw + pad;
     uint8_t* sK = smem;
     uint8_t* sV = sK + TILE_BYTES;
     uint8_t* sQ = sV + TILE_BYTES;        // 2 stages
     uint8_t* sdO = sQ + 2 * TILE_BYTES;   // 2 stages
     uint8_t* sPT = sdO + 2 * TILE_BYTES;  // P^T   [keys x queries]
     uint8_t* sdST = sPT + PT_BYTES;       // dS^T  [keys x queries]
-    float* lse_s = reinterpret_cast<float*>(sdST + PT_BYTES);  // [2][128], already times log2(e)
+    uint8_t* sDQ = sdST + PT_BYTES;       // dQ_i as two swizzled [128 x 32] fp32 boxes on their way to the accumulators, x 2
+    float* lse_s = reinterpret_cast<float*>(sDQ + 4 * DQ_BOX_BYTES);  // [2][128], already times log2(e)
     float* dsum_s = lse_s + 2 * BT;                            // [2][128]
     uint64_t* kv_full = reinterpret_cast<uint64_t*>(dsum_s + 2 * BT);
     uint64_t* qdo_full = kv_full + 1;     // 2
@@ -429,6 +441,7 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
         prefetch_tensormap(&tmK);
         prefetch_tensormap(&tmV);
         prefetch_tensormap(&tmdO);
+        prefetch_tensormap(&tmdQ);
         mbar_init(kv_full, 1);
         mbar_init(&qdo_full[0], 1);
         mbar_init(&qdo_full[1], 1);
@@ -528,18 +541,24 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
         // `ok` is uniform over the warp. A warp that gave up keeps walking the loop without touching TMEM or waiting, so
         // that the other warps never wait for it at the named barrier.
         bool ok = true;
+        // threads 0..127 carry lse (times log2 e), threads 128..255 rowsum(dO O): the value of the NEXT query tile is
+        // requested one iteration ahead so that its latency is hidden
+        const int st_which = threadIdx.x >> 7, st_idx = threadIdx.x & (BT - 1);
+        auto stat_load = [&](int tile) -> float {
+            const int qi = tile * BT + st_idx;
+            const long long at = static_cast<long long>(bh) * g.S + qi;
+            if (st_which == 0) return qi < g.S ? p.lse[at] * LOG2E : INFINITY;   // +inf: probability 0 for padding
+            return qi < g.S ? p.dsum[at] : 0.f;
+        };
+        float stat_next = threadIdx.x < 2 * BT ? stat_load(i0) : 0.f;
         for (int it = 0; it < n_it; ++it) {
             const int st = it & 1;
             const int i = i0 + it;
-            if (threadIdx.x < 2 * BT) {  // stage this query tile's lse (times log2 e) and rowsum(dO O)
-                const int which = threadIdx.x >> 7, idx = threadIdx.x & (BT - 1);
-                const int qi = i * BT + idx;
-                const long long at = static_cast<long long>(bh) * g.S + qi;
-                if (which == 0)
-                    lse_s[st * BT + idx] = qi < g.S ? p.lse[at] * LOG2E : INFINITY;  // +inf: probability 0 for padding
-                else
-                    dsum_s[st * BT + idx] = qi < g.S ? p.dsum[at] : 0.f;
+            if (threadIdx.x < 2 * BT) {
+                (st_which == 0 ? lse_s : dsum_s)[st * BT + st_idx] = stat_next;
+                if (it + 1 < n_it) stat_next = stat_load(i + 1);
             }
+            if (threadIdx.x == 0) tma_store_wait_read<1>();  // the dQ boxes of two tiles ago have left their buffer
             ATTN_STAMP(prof_cta, prof_warp, it, 0);
             compute_warps_sync<BWD_COMPUTE_WARPS * 32>();
             ATTN_STAMP(prof_cta, prof_warp, it, 1);
@@ -589,22 +608,29 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
                 ATTN_STAMP(prof_cta, prof_warp, it, 4);
             }
             if (ok) {
+                // dQ_i: TMEM -> two swizzled [128 x 32] fp32 boxes in shared memory -> one TMA reduction each adds them
+                // to the fp32 accumulators (rows beyond S are dropped by the tensor map)
                 tcgen05_fence_after_sync();
-                const int qrow = i * BT + r;
                 uint32_t v[16];
                 tmem_ld_32x32b_x16(lane_addr + 384 + cg * 16, v);
                 tmem_ld_wait();
-                if (qrow < g.S) {
-                    float4* acc = reinterpret_cast<float4*>(p.dq_acc + (static_cast<long long>(bh) * g.S + qrow) * DH + cg * 16);
+                uint8_t* box_row = sDQ + (st * 2 + (cg >> 1)) * DQ_BOX_BYTES + r * 128;
 #pragma unroll
-                    for (int t = 0; t < 4; ++t)
-                        atomicAdd(acc + t, make_float4(__uint_as_float(v[4 * t]), __uint_as_float(v[4 * t + 1]),
-                                                       __uint_as_float(v[4 * t + 2]), __uint_as_float(v[4 * t + 3])));
-                }
+                for (int t = 0; t < 4; ++t)
+                    *reinterpret_cast<uint4*>(box_row + ((((cg & 1) * 4 + t) ^ (r & 7)) << 4)) =
+                        make_uint4(v[4 * t], v[4 * t + 1], v[4 * t + 2], v[4 * t + 3]);
+                fence_proxy_async_smem();
                 tcgen05_fence_before_sync();
                 ATTN_STAMP(prof_cta, prof_warp, it, 5);
             }
+            compute_warps_sync<BWD_COMPUTE_WARPS * 32>();
+            if (ok && threadIdx.x == 0) {
+                tma_reduce_add_3d(&tmdQ, sDQ + (st * 2) * DQ_BOX_BYTES, 0, i * BT, bh);
+                tma_reduce_add_3d(&tmdQ, sDQ + (st * 2 + 1) * DQ_BOX_BYTES, 32, i * BT, bh);
+                tma_store_commit();
+            }
         }
+        if (threadIdx.x == 0) tma_store_wait_all<0>();
         if (ok) {
             const bool got = mbar_wait(acc_done, (n_it - 1) & 1, abort_flag);
             ok = __all_sync(0xffffffffu, got);
@@ -844,6 +870,19 @@ int b200_attention_backward(b200_ctx* ctx, const b200_attn_operand* q, const b20
     if ((rc = make_attn_map(ctx, &tmV, *v, B, H, S, "v")) != B200_OK) return rc;
     if ((rc = make_attn_map(ctx, &tmdO, *d_o, B, H, S, "d_o")) != B200_OK) return rc;
 
+    CUtensorMap tmdQ;
+    {
+        // fp32 accumulators [B*H, S, 64] as boxes of [128 rows x 32 columns] (128-byte rows, swizzled like the boxes in
+        // shared memory); a box that reaches beyond row S of its (batch, head) slab is clipped there
+        cuuint64_t dims[3] = {DH, static_cast<cuuint64_t>(S), static_cast<cuuint64_t>(B * H)};
+        cuuint64_t strides[2] = {DH * sizeof(float), static_cast<cuuint64_t>(S) * DH * sizeof(float)};
+        cuuint32_t box[3] = {32, BT, 1};
+        cuuint32_t estr[3] = {1, 1, 1};
+        CUresult r = ctx->encode_tiled(&tmdQ, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 3, dq_acc, dims, strides, box, estr,
+                                       CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                                       CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+        if (r != CUDA_SUCCESS) return fail(B200_ERR_CUDA, "cuTensorMapEncodeTiled failed (%d) for the dQ accumulators", static_cast<int>(r));
+    }
     B200_CUDA_TRY(cudaMemsetAsync(dq_acc, 0, acc_bytes, stream));
     const unsigned blocks = static_cast<unsigned>((rows * 8 + 255) / 256);
     attn_dsum_kernel<<<blocks, 256, 0, stream>>>(as_in(o), as_in(d_o), dsum, static_cast<int>(B), static_cast<int>(H),
@@ -861,7 +900,7 @@ int b200_attention_backward(b200_ctx* ctx, const b200_attn_operand* q, const b20
     static bool configured[64] = {};
     if ((rc = configure_once(attn_bwd_kernel, BWD_SMEM, configured)) != B200_OK) return rc;
     const dim3 grid(static_cast<unsigned>((S + BT - 1) / BT), static_cast<unsigned>(B * H));
-    attn_bwd_kernel<<<grid, BWD_THREADS, BWD_SMEM, stream>>>(tmQ, tmK, tmV, tmdO, p);
+    attn_bwd_kernel<<<grid, BWD_THREADS, BWD_SMEM, stream>>>(tmQ, tmK, tmV, tmdO, tmdQ, p);
     B200_CUDA_TRY(cudaGetLastError());
     attn_dq_store_kernel<<<blocks, 256, 0, stream>>>(dq_acc, as_out(d_q), static_cast<int>(B), static_cast<int>(H),
                                                      static_cast<int>(S));

@@ -105,6 +105,15 @@ __device__ __forceinline__ void tma_store_3d(const CUtensorMap* map, const void*
                  : "memory");
 }
 
+// TMA reduction: adds a shared-memory box to global memory (element type and extents come from the tensor map;
+// elements outside the tensor are dropped). Completion is tracked by bulk groups like a TMA store.
+__device__ __forceinline__ void tma_reduce_add_3d(const CUtensorMap* map, const void* smem_src, int c0, int c1, int c2) {
+    asm volatile("cp.reduce.async.bulk.tensor.3d.global.shared::cta.add.tile.bulk_group [%0, {%2, %3, %4}], [%1];" ::"l"(
+                     reinterpret_cast<uint64_t>(map)),
+                 "r"(smem_u32(smem_src)), "r"(c0), "r"(c1), "r"(c2)
+                 : "memory");
+}
+
 __device__ __forceinline__ void tma_store_commit() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
 
 template <int N>
