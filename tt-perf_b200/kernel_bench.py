@@ -1,7 +1,8 @@
 #!/usr/bin/env python3
-"""Times the bandwidth-bound kernels of the hot path (softmax family, cross-entropy, LayerNorm, element-wise,
-reductions, embedding, SGD / Adam) at the GPT-2-small training shapes and reports achieved HBM GB/s against the
-measured copy bandwidth.
+"""Times the bandwidth-bound kernels of the hot path (softmax family, cross-entropy, LayerNorm with and without the
+fused residual add, element-wise, reductions, embedding, SGD / Adam) and the fused attention kernels at the GPT-2-small
+training shapes and reports achieved HBM GB/s against the measured copy bandwidth (for the attention kernels, which
+are not HBM-bound, the GB/s column only says how little memory traffic they need).
 
     python tt-perf_b200/kernel_bench.py [--only NAME] [--iters 20] [--json]
 
@@ -80,6 +81,11 @@ def main() -> None:
     case("layernorm_fwd [16T, 768]", T16 * D * 4 + T16 * 8, lambda: ctx.layernorm_forward(xl, gam, bet, yl, mean, rstd, T16, D))
     case("layernorm_bwd dx+dgamma+dbeta [16T, 768]", T16 * D * (6 + 4) + T16 * 8,
          lambda: ctx.layernorm_backward(dyl, xl, gam, mean, rstd, yl, dg, db, T16, D))
+    res_l, sum_l = rand((T16, D), scale=0.1), DT(ctx, (T16, D))
+    case("add + layernorm_fwd [16T, 768]", T16 * D * 8 + T16 * 8,
+         lambda: ctx.add_layernorm_forward(xl, res_l, sum_l, gam, bet, yl, mean, rstd, T16, D))
+    case("layernorm_bwd + residual add [16T, 768]", T16 * D * (8 + 4) + T16 * 8,
+         lambda: ctx.layernorm_backward_add(dyl, xl, gam, mean, rstd, res_l, yl, dg, db, T16, D))
     case("add [16T, 768] (residual)", T16 * D * 6, lambda: ctx.binary(c.B_ADD, xl, (T16, D), dyl, (T16, D), yl))
     case("bias add [16T, 768] + [1, 768]", T16 * D * 4, lambda: ctx.binary(c.B_ADD, xl, (T16, D), gam, (1, D), yl))
     case("gelu [16T, 768]", T16 * D * 4, lambda: ctx.unary(c.U_GELU, xl, yl, T16 * D))
@@ -99,6 +105,17 @@ def main() -> None:
     case("adam 163M params (bf16 p, g; fp32 m, v): 22 B/param", n_par * 22,
          lambda: ctx.adam_step([p_], [g_], [m_], [v_], [n_par], 1, lr=3e-4, beta1=0.9, beta2=0.95))
     case("sgd 163M params (bf16 p, g): 6 B/param", n_par * 6, lambda: ctx.sgd_step([p_], [g_], [n_par], 0.01))
+
+    # fused attention at the GPT-2-small shape: q, k, v read in place from a stacked [B, S, 3D] projection output
+    qkv_a, o_a, do_a, dqkv_a = rand((B, S, 3 * D), scale=0.5), DT(ctx, (B, S, D)), rand((B, S, D), scale=0.1), DT(ctx, (B, S, 3 * D))
+    lse_a = DT(ctx, (B, H, S), pkg.F32)
+    op3 = [ctx.attn_operand(qkv_a, S * 3 * D, 64, 3 * D, offset=i * D) for i in range(3)]
+    dop3 = [ctx.attn_operand(dqkv_a, S * 3 * D, 64, 3 * D, offset=i * D) for i in range(3)]
+    o_op, do_op = ctx.attn_operand(o_a, S * D, 64, D), ctx.attn_operand(do_a, S * D, 64, D)
+    case("attention_fwd causal [B8, H12, S1024, 64]", B * S * D * 2 * 4 + B * H * S * 4,
+         lambda: ctx.attention_forward(op3[0], op3[1], op3[2], o_op, lse_a, B, H, S))
+    case("attention_bwd causal [B8, H12, S1024, 64]", B * S * D * 2 * 8 + B * H * S * 4,
+         lambda: ctx.attention_backward(op3[0], op3[1], op3[2], o_op, do_op, lse_a, dop3[0], dop3[1], dop3[2], B, H, S))
 
     peak, peak_src = hbm_peak()
     results = []
