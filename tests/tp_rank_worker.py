@@ -41,7 +41,7 @@ def main():
     if bench:
         b, s, heads = 16, 1024, 25                        # GPT-2-XL-shaped block: D 1600, F 6400, T = 16384
     else:
-        b, s, heads = 2, 128 * world, 5                   # 5 heads: uneven head counts on 2 and 4 ranks
+        b, s, heads = 2, 128 * world, max(5, world + 1)   # one head more than ranks (5 on 2 or 4 ranks): uneven head counts
     d, f = heads * 64, 4 * heads * 64
     w = weights(rng, d, f, std=0.02 if bench else 0.03)
     t, tr = b * s, b * s // world

@@ -117,6 +117,8 @@ class TPBlockRank:
             raise ValueError(f"rows per rank {self.T}/{world} must be a multiple of 128")
         if d_model != heads * HEAD_DIM:
             raise ValueError("the tensor-parallel block uses the fused attention kernels: head dimension 64")
+        if heads < world:
+            raise ValueError(f"{heads} heads cannot be spread over {world} ranks (every rank needs at least one)")
         self.Tr = self.T // world
         self.row0 = rank * self.Tr
         self.ptrs = ptrs
