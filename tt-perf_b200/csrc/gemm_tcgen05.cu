@@ -536,7 +536,7 @@ int split_candidates(const b200_gemm_desc& d, long long tiles, long long slots, 
 // Picks the kernel, the tile width and the K-slice count together from a cost model fitted to timings on B200. The
 // unit is the time one 128-row tile spends on one output column of one K block at full tensor rate (about 1 ns).
 //   main loop: rounds of the persistent grid x (K blocks per work item + pipeline fill) x tile width x c(width);
-//              c = 1, 1.3, 1.5, 3 for 256, 192, 128, 64 columns: a narrower tile re-reads the A block more often per flop
+//              c = 1, 1.1-1.3, 1.5, 3 for 256, 192, 128, 64 columns: a narrower tile re-reads the A block more often per flop
 //              and the shared-memory fill rate, not the tensor pipe, then sets the pace; 0.95 for the CTA-pair
 //              kernel, whose two CTAs share the B tile;
 //   K slices:  single-CTA kernel: a fixed charge for the second launch plus the fp32 partial sums written and read
@@ -571,7 +571,8 @@ GemmPlan gemm_plan(const b200_ctx* ctx, const b200_gemm_desc& d, bool allow_pair
     }
     const long long m_tiles = d.batch * ((d.M + BM - 1) / BM);
     const int widths[4] = {256, 192, 128, 64};
-    const double cost_per_col[4] = {1.0, 1.3, 1.5, 3.0};
+    // the 192-column tile loses ground to the wider ones as K grows (measured: level at K <= 3072, 9 % behind at K = 50264)
+    const double cost_per_col[4] = {1.0, 1.1 + 0.2 * std::min(1.0, num_kb / 512.0), 1.5, 3.0};
     for (int i = 0; i < 4; ++i) {
         const int bn = widths[i];
         if (i < 3 && d.N <= bn / 2) continue;  // more than half of the tile would be padding
