@@ -196,10 +196,10 @@ def gpt2_train_bench(steps: int = 10, warmup: int = 3, device: int = 0, rank: in
     backward and the Adam update. Every kernel comes from the C ABI; the host side is tt-perf_b200/nn.py.
 
     One GPU: the whole step is recorded once as a trace (CUDA graph) and replayed, as the reference's traced executor
-    does (bench/autograd/bench_gpt2_full.cpp). N GPUs (data parallel, weak scaling): each rank replays a trace of
-    forward + backward on its own batch that also packs the gradients into two buckets, the buckets are averaged with
-    two NCCL all-reduces (through torch.distributed), then a second trace applies Adam from the buckets. Returns
-    whole-job tokens/s and ms/step."""
+    does (bench/autograd/bench_gpt2_full.cpp). N GPUs (data parallel, weak scaling): each rank replays forward +
+    backward on its own batch as a chain of traces (LM head, then groups of four blocks); every trace packs its
+    gradients into a bucket that NCCL (through torch.distributed) averages over the ranks on a second stream while the
+    next trace runs; a last trace applies Adam from the buckets. Returns whole-job tokens/s and ms/step."""
     import numpy as np
     from __graft_entry__ import load_package
     pkg = load_package()
@@ -239,65 +239,85 @@ def gpt2_train_bench(steps: int = 10, warmup: int = 3, device: int = 0, rank: in
     else:
         import torch
         import torch.distributed as dist
-        # Gradients are packed into one bf16 and one fp32 bucket inside the forward+backward trace, so that the
-        # exchange is two large all-reduces; Adam then reads its gradients straight from the buckets.
+        # The backward pass is recorded as several traces (LM head, then groups of four blocks, the last one with the
+        # embeddings). Each trace ends by packing its gradients into its own bf16 / fp32 bucket; while the next trace
+        # runs on the compute stream, the bucket is averaged over the ranks by NCCL on a second stream (events order
+        # the two, no host synchronisation). A last trace applies Adam straight from the buckets.
         c = pkg.capi
+        specs = []
+        model.forward_backward(idd, tgd, pos, segment_hook=lambda pairs: specs.append([(g.numel, g.dtype) for _, g in pairs]))
+        ctx.synchronize()
+        buckets = []
+        for spec in specs:
+            offs, n_bf, n_f32 = [], 0, 0
+            for numel, dtype in spec:
+                if dtype == pkg.BF16:
+                    offs.append(n_bf)
+                    n_bf += (numel + 7) // 8 * 8
+                else:
+                    offs.append(n_f32)
+                    n_f32 += (numel + 3) // 4 * 4
+            buckets.append((DT.zeros(ctx, (max(n_bf, 8),), pkg.BF16), DT.zeros(ctx, (max(n_f32, 4),), pkg.F32), offs, n_bf, n_f32))
+        ctx.synchronize()
+        slice_of, seg_traces, cur = {}, [], [ctx.trace_begin()]
 
-        def bucket(pairs, dtype):
-            offs, total = [], 0
-            for _, g in pairs:
-                offs.append(total)
-                total += (g.numel + 7) // 8 * 8
-            return DT.zeros(ctx, (total,), dtype), offs
+        def pack_and_cut(pairs):
+            flat_bf, flat_f32, offs, _, _ = buckets[len(seg_traces)]
+            for (prm, g), off in zip(pairs, offs):
+                if g.dtype == pkg.BF16:
+                    sl = DT(ctx, g.shape, pkg.BF16, ptr=flat_bf.ptr + 2 * off, owner=flat_bf)
+                    ctx.unary(c.U_COPY, g, sl, g.numel)
+                else:
+                    sl = DT(ctx, g.shape, pkg.F32, ptr=flat_f32.ptr + 4 * off, owner=flat_f32)
+                    ctx.unary(c.U_COPY, g, sl, 2 * g.numel)      # a pure copy: fp32 moved as pairs of 16-bit words
+                slice_of[id(prm)] = sl
+            ctx.trace_end(cur[0])
+            seg_traces.append(cur[0])
+            if len(seg_traces) < len(specs):
+                cur[0] = ctx.trace_begin()
 
-        t_fb = ctx.trace_begin()
-        loss, grads = model.forward_backward(idd, tgd, pos)
+        loss, grads = model.forward_backward(idd, tgd, pos, segment_hook=pack_and_cut)
         bf, f32 = model._flat(grads)
-        ctx.trace_end(t_fb)
-        ctx.trace_release(t_fb)
-        flat_bf, off_bf = bucket(bf, pkg.BF16)
-        flat_f32, off_f32 = bucket(f32, pkg.F32)
-        del loss, grads, bf, f32
-        t_fb = ctx.trace_begin()
-        loss, grads = model.forward_backward(idd, tgd, pos)
-        bf, f32 = model._flat(grads)
-        slices_bf, slices_f32 = [], []
-        for (_, g), o in zip(bf, off_bf):
-            sl = DT(ctx, g.shape, pkg.BF16, ptr=flat_bf.ptr + 2 * o, owner=flat_bf)
-            ctx.unary(c.U_COPY, g, sl, g.numel)
-            slices_bf.append(sl)
-        for (_, g), o in zip(f32, off_f32):
-            sl = DT(ctx, g.shape, pkg.F32, ptr=flat_f32.ptr + 4 * o, owner=flat_f32)
-            ctx.unary(c.U_COPY, g, sl, 2 * g.numel)          # a pure copy: fp32 moved as pairs of 16-bit words
-            slices_f32.append(sl)
-        ctx.trace_end(t_fb)
         t_opt = ctx.trace_begin()
-        model.opt[0].step(slices_bf)
-        model.opt[1].step(slices_f32)
+        model.opt[0].step([slice_of[id(prm)] for prm, _ in bf])
+        model.opt[1].step([slice_of[id(prm)] for prm, _ in f32])
         ctx.trace_end(t_opt)
-        views = [torch.as_tensor(_DevBytes(flat_bf.ptr, flat_bf.nbytes), device="cuda").view(torch.bfloat16),
-                 torch.as_tensor(_DevBytes(flat_f32.ptr, flat_f32.nbytes), device="cuda").view(torch.float32)]
+        seg_views = []
+        for flat_bf, flat_f32, _, n_bf, n_f32 in buckets:
+            v = []
+            if n_bf:
+                v.append(torch.as_tensor(_DevBytes(flat_bf.ptr, 2 * n_bf), device="cuda").view(torch.bfloat16))
+            if n_f32:
+                v.append(torch.as_tensor(_DevBytes(flat_f32.ptr, 4 * n_f32), device="cuda").view(torch.float32))
+            seg_views.append(v)
+        comp, comm = torch.cuda.Stream(), torch.cuda.Stream()
 
         def dp_step():
-            ctx.trace_execute(t_fb)
-            ctx.synchronize()                                  # gradients are complete before NCCL reads them
-            for v in views:
-                dist.all_reduce(v, op=dist.ReduceOp.AVG)
-            torch.cuda.current_stream().synchronize()
-            ctx.trace_execute(t_opt)
+            for tid, views in zip(seg_traces, seg_views):
+                ctx.trace_execute_on(tid, comp.cuda_stream)
+                ev = torch.cuda.Event()
+                ev.record(comp)
+                comm.wait_event(ev)                            # this segment's gradients are packed
+                with torch.cuda.stream(comm):
+                    for v in views:
+                        dist.all_reduce(v, op=dist.ReduceOp.AVG)
+            comp.wait_stream(comm)                             # every bucket is averaged before Adam reads it
+            ctx.trace_execute_on(t_opt, comp.cuda_stream)
 
-        dp_step()
         ctx.synchronize()
+        dp_step()
+        comp.synchronize()
         dist.barrier()
         t0 = time.perf_counter()
         for _ in range(steps):
             dp_step()
-        ctx.synchronize()
+        comp.synchronize()
         t = torch.tensor([(time.perf_counter() - t0) / steps], device="cuda")
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
         dt = t.item()
-        executor = "two traces (forward+backward+gradient packing, Adam) with two bucketed NCCL all-reduces between them"
-        traces = [t_fb, t_opt]
+        executor = (f"{len(seg_traces)} backward traces on a compute stream, each followed by the NCCL all-reduce of its gradient "
+                    "bucket on a second stream (overlapping the next trace), then an Adam trace")
+        traces = seg_traces + [t_opt]
     final = float(loss.numpy()[0])
     for t in traces:
         ctx.trace_release(t)

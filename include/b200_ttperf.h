@@ -102,6 +102,10 @@ int b200_pool_stats(b200_ctx* ctx, size_t* reserved_bytes, size_t* in_use_bytes)
 int b200_trace_begin(b200_ctx* ctx, uint32_t* out_trace_id);
 int b200_trace_end(b200_ctx* ctx, uint32_t trace_id);
 int b200_trace_execute(b200_ctx* ctx, uint32_t trace_id, int blocking);
+/* Replays a trace on the caller's stream instead of the context's: the caller orders it against its own work with its
+ * own events (a data-parallel step interleaves segments of the backward pass with NCCL all-reduces on another stream
+ * this way). Replays of traces that share buffers must still be ordered by the caller. */
+int b200_trace_execute_on(b200_ctx* ctx, uint32_t trace_id, void* stream);
 int b200_trace_release(b200_ctx* ctx, uint32_t trace_id);
 
 /* ---- dense matmul: ttnn::matmul(a, b, transpose_a, transpose_b, ..., activation, compute_kernel_config)

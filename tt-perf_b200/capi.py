@@ -76,6 +76,7 @@ SIGNATURES = {
     "b200_trace_begin": (C.c_int, [C.c_void_p, C.POINTER(C.c_uint32)]),
     "b200_trace_end": (C.c_int, [C.c_void_p, C.c_uint32]),
     "b200_trace_execute": (C.c_int, [C.c_void_p, C.c_uint32, C.c_int]),
+    "b200_trace_execute_on": (C.c_int, [C.c_void_p, C.c_uint32, C.c_void_p]),
     "b200_trace_release": (C.c_int, [C.c_void_p, C.c_uint32]),
     "b200_gemm_desc_init": (None, [C.POINTER(GemmDesc)]),
     "b200_gemm": (C.c_int, [C.c_void_p, C.POINTER(GemmDesc), C.c_void_p]),
@@ -449,6 +450,10 @@ class Context:
 
     def trace_execute(self, tid: int, blocking: bool = False) -> None:
         check(lib().b200_trace_execute(self._h, tid, int(blocking)))
+
+    def trace_execute_on(self, tid: int, stream) -> None:
+        """Replays the trace on the caller's stream (a cudaStream_t handle)."""
+        check(lib().b200_trace_execute_on(self._h, tid, C.c_void_p(ptr(stream))))
 
     def trace_release(self, tid: int) -> None:
         check(lib().b200_trace_release(self._h, tid))

@@ -207,6 +207,23 @@ int b200_trace_execute(b200_ctx* ctx, uint32_t trace_id, int blocking) {
     return B200_OK;
 }
 
+int b200_trace_execute_on(b200_ctx* ctx, uint32_t trace_id, void* stream_v) {
+    B200_REQUIRE(ctx != nullptr, "b200_trace_execute_on: ctx is NULL");
+    B200_REQUIRE(stream_v != nullptr, "b200_trace_execute_on: a stream is required (b200_trace_execute uses the context's own)");
+    PoolState* p = pool_of(ctx);
+    cudaGraphExec_t exec = nullptr;
+    {
+        std::lock_guard<std::mutex> lock(ctx->mu);
+        auto it = p->traces.find(trace_id);
+        B200_REQUIRE(it != p->traces.end() && it->second.exec != nullptr,
+                     "b200_trace_execute_on: unknown or unfinished trace %u", trace_id);
+        exec = it->second.exec;
+    }
+    DeviceScope scope(ctx->device);
+    B200_CUDA_TRY(cudaGraphLaunch(exec, static_cast<cudaStream_t>(stream_v)));
+    return B200_OK;
+}
+
 int b200_trace_release(b200_ctx* ctx, uint32_t trace_id) {
     B200_REQUIRE(ctx != nullptr, "b200_trace_release: ctx is NULL");
     PoolState* p = pool_of(ctx);

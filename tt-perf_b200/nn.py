@@ -411,9 +411,13 @@ class GPT2:
         self.load({"tok_emb": w(self.V, self.D), "pos_emb": w(self.S, self.D), "lnf_g": np.ones(self.D, np.float32),
                    "lnf_b": np.zeros(self.D, np.float32), "head": w(self.V, self.D), "blocks": blocks})
 
-    def forward_backward(self, ids, targets, pos_ids, *, stream=None):
+    def forward_backward(self, ids, targets, pos_ids, *, stream=None, segment_hook=None, blocks_per_segment=4):
         """ids, targets: uint32 device tensors [B, S] / [B*S]; pos_ids: uint32 [S] = 0..S-1.
-        Returns (loss fp32 scalar tensor, grads structured like params)."""
+        Returns (loss fp32 scalar tensor, grads structured like params).
+        segment_hook(pairs), when given, is called with the (parameter, gradient) pairs that have just become final:
+        after the LM head and final LayerNorm, after every `blocks_per_segment` blocks of the backward pass, and at the
+        end with the remaining blocks and the embeddings. A data-parallel driver ends a trace there and starts the
+        all-reduce of those gradients while the rest of the backward pass runs."""
         ctx, p = self.ctx, self.params
         b = ids.numel // self.S
         t = b * self.S
@@ -442,13 +446,23 @@ class GPT2:
         grads = {"blocks": [None] * self.L}
         d_xf, grads["head"], _ = linear_backward(ctx, xf, p["head"], d_logits, need_db=False, stream=stream)
         d_x, grads["lnf_g"], grads["lnf_b"] = layernorm_backward(ctx, d_xf, x, p["lnf_g"], mean_f, rstd_f, stream=stream)
+        if segment_hook:
+            segment_hook([(p[k], grads[k]) for k in ("head", "lnf_g", "lnf_b")])
+        pending, done = [], 0
         for i in reversed(range(self.L)):
             d_x, grads["blocks"][i] = transformer_block_backward(ctx, d_x, p["blocks"][i], caches[i], self.H, stream=stream)
+            pending += [(p["blocks"][i][k], grads["blocks"][i][k]) for k in BLOCK_KEYS]
+            done += 1
+            if segment_hook and done % blocks_per_segment == 0 and i > 0:
+                segment_hook(pending)
+                pending = []
         grads["tok_emb"] = DeviceTensor(ctx, (self.V, self.D), F32)
         ctx.embedding_backward(ids, t, d_x, self.V, self.D, grads["tok_emb"], stream=stream)
         pos_g = DeviceTensor(ctx, (self.S, self.D), BF16)
         ctx.reduce(capi.R_SUM, d_x, 1, b, self.S * self.D, pos_g, stream=stream)
         grads["pos_emb"] = pos_g
+        if segment_hook:
+            segment_hook(pending + [(p["tok_emb"], grads["tok_emb"]), (p["pos_emb"], grads["pos_emb"])])
         return loss, grads
 
     def _flat(self, tree):
