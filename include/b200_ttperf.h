@@ -233,6 +233,14 @@ int b200_add_layernorm_forward(b200_ctx* ctx, const void* x, int64_t ldx, const 
 int b200_layernorm_backward_add(b200_ctx* ctx, const void* dy, int64_t lddy, const void* x, int64_t ldx, const void* gamma,
                                 const float* mean, const float* rstd, const void* upstream, int64_t ldup, void* dx,
                                 int64_t lddx, float* dgamma_f32, float* dbeta_f32, int64_t rows, int64_t cols, void* stream);
+/* The general form: upstream may be NULL; dx_colsum_bf16 (optional, [cols] bf16) receives the column sums of the dx
+ * that is written. dx is the gradient of a residual stream, i.e. the dY of the Linear layer that feeds that stream
+ * (attention output projection, FC2), so these sums ARE that layer's bias gradient (db = sum_batch dy, static/nn.hpp:
+ * 84-86) and no separate reduction over dx has to run. */
+int b200_layernorm_backward_full(b200_ctx* ctx, const void* dy, int64_t lddy, const void* x, int64_t ldx, const void* gamma,
+                                 const float* mean, const float* rstd, const void* upstream, int64_t ldup, void* dx,
+                                 int64_t lddx, float* dgamma_f32, float* dbeta_f32, void* dx_colsum_bf16, int64_t rows,
+                                 int64_t cols, void* stream);
 
 /* ---- element-wise ops on bf16 buffers ------------------------------------------------------------------------
  * Unary (ttnn::neg / relu / gtz / gelu / rsqrt ..., traced/ops.hpp:54-61; tensor (+,*) float forms, traced/ops.hpp:38-52). */

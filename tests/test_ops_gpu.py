@@ -267,3 +267,21 @@ def test_layernorm_with_fused_residual_add(pkg, ctx, DT, rows, cols):
     ref_dx, ref_dg, ref_db = mo.layernorm_backward(dy, ref_total, gamma, ref_mean, ref_rstd)
     assert mo.rel_frobenius(dx.numpy(), mo.bf16_round(ref_dx) + up) <= TOL
     assert mo.rel_frobenius(dg.numpy(), ref_dg) <= TOL and mo.rel_frobenius(db.numpy(), ref_db) <= TOL
+
+
+@pytest.mark.parametrize("rows,cols,with_upstream", [(256, 768, True), (100, 520, False), (64, 1600, True), (31, 100, True)])
+def test_layernorm_backward_emits_column_sums_of_dx(pkg, ctx, DT, rows, cols, with_upstream):
+    """b200_layernorm_backward_full: the column sums of dx (the bias gradient of the layer that feeds the residual stream)
+    come out of the same kernel and equal a reduction over the stored bf16 dx."""
+    x, dy, up = (rnd((rows, cols), s) for s in (21, 22, 23))
+    gamma = rnd((cols,), 24) * 0.1 + 1
+    ref_y, ref_mean, ref_rstd = mo.layernorm_forward(x, gamma, np.zeros(cols, np.float32))
+    mean, rstd = DT.from_numpy(ctx, ref_mean.ravel(), pkg.F32), DT.from_numpy(ctx, ref_rstd.ravel(), pkg.F32)
+    dx, dg, db, cs = DT(ctx, (rows, cols)), DT(ctx, (cols,), pkg.F32), DT(ctx, (cols,), pkg.F32), DT(ctx, (cols,))
+    ctx.layernorm_backward_full(DT.from_numpy(ctx, dy), DT.from_numpy(ctx, x), DT.from_numpy(ctx, gamma), mean, rstd,
+                                DT.from_numpy(ctx, up) if with_upstream else None, dx, dg, db, cs, rows, cols)
+    ref_dx, ref_dg, ref_db = mo.layernorm_backward(dy, x, gamma, ref_mean, ref_rstd)
+    want = mo.bf16_round(ref_dx) + (up if with_upstream else 0)
+    assert mo.rel_frobenius(dx.numpy(), want) <= TOL
+    assert mo.rel_frobenius(cs.numpy(), dx.numpy().sum(axis=0)) <= TOL
+    assert mo.rel_frobenius(dg.numpy(), ref_dg) <= TOL and mo.rel_frobenius(db.numpy(), ref_db) <= TOL

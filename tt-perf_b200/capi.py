@@ -119,6 +119,9 @@ SIGNATURES = {
     "b200_layernorm_backward_add": (C.c_int, [C.c_void_p, C.c_void_p, C.c_int64, C.c_void_p, C.c_int64, C.c_void_p,
                                               C.c_void_p, C.c_void_p, C.c_void_p, C.c_int64, C.c_void_p, C.c_int64,
                                               C.c_void_p, C.c_void_p, C.c_int64, C.c_int64, C.c_void_p]),
+    "b200_layernorm_backward_full": (C.c_int, [C.c_void_p, C.c_void_p, C.c_int64, C.c_void_p, C.c_int64, C.c_void_p,
+                                               C.c_void_p, C.c_void_p, C.c_void_p, C.c_int64, C.c_void_p, C.c_int64,
+                                               C.c_void_p, C.c_void_p, C.c_void_p, C.c_int64, C.c_int64, C.c_void_p]),
     "b200_unary": (C.c_int, [C.c_void_p, C.c_int, C.c_void_p, C.c_void_p, C.c_int64, C.c_float, C.c_void_p]),
     "b200_binary": (C.c_int, [C.c_void_p, C.c_int, C.c_void_p, C.POINTER(C.c_int64), C.c_void_p, C.POINTER(C.c_int64),
                               C.c_void_p, C.c_void_p]),
@@ -346,6 +349,13 @@ class Context:
         check(lib().b200_layernorm_backward_add(self._h, ptr(dy), cols, ptr(x), cols, ptr(gamma), ptr(mean), ptr(rstd),
                                                 ptr(upstream), cols, ptr(dx), cols, ptr(dgamma), ptr(dbeta), rows, cols,
                                                 self._s(stream)))
+
+    def layernorm_backward_full(self, dy, x, gamma, mean, rstd, upstream, dx, dgamma, dbeta, dx_colsum, rows, cols, *,
+                                stream=None):
+        """dx = LayerNorm'(dy) (+ upstream); dx_colsum (bf16 [cols], optional) = column sums of dx."""
+        check(lib().b200_layernorm_backward_full(self._h, ptr(dy), cols, ptr(x), cols, ptr(gamma), ptr(mean), ptr(rstd),
+                                                 ptr(upstream), cols, ptr(dx), cols, ptr(dgamma), ptr(dbeta), ptr(dx_colsum),
+                                                 rows, cols, self._s(stream)))
 
     def unary(self, op, x, y, n, *, scalar=0.0, stream=None):
         check(lib().b200_unary(self._h, op, ptr(x), ptr(y), n, scalar, self._s(stream)))

@@ -76,11 +76,13 @@ namespace b200 {
 // Layout of the small device block behind b200_ctx::d_status: the status word, then (from byte 256) ticket counters for
 // kernels whose last-arriving CTA finishes a reduction. The counters start at zero and every kernel leaves them at zero.
 // The last ticket is reserved for the LayerNorm backward kernel, whose parameter-gradient staging follows the tickets:
-// kLnCopies replicas of [dgamma | dbeta] with up to kLnMaxCols columns each, zero between kernels as well.
+// kLnCopies replicas of [dgamma | dbeta | column sums of dx] with up to kLnMaxCols columns each, zero between kernels
+// as well.
 constexpr int kTicketCount = 4096;
 constexpr int kLnCopies = 8;
 constexpr int kLnMaxCols = 1024;
-constexpr size_t kLnStageBytes = sizeof(float) * kLnCopies * 2 * kLnMaxCols;
+constexpr int kLnRows = 3;
+constexpr size_t kLnStageBytes = sizeof(float) * kLnCopies * kLnRows * kLnMaxCols;
 constexpr size_t kStatusBytes = 256 + sizeof(unsigned) * kTicketCount + kLnStageBytes;
 inline unsigned* ctx_tickets(const b200_ctx* ctx) { return reinterpret_cast<unsigned*>(reinterpret_cast<char*>(ctx->d_status) + 256); }
 inline float* ctx_ln_stage(const b200_ctx* ctx) {

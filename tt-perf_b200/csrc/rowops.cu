@@ -846,20 +846,23 @@ template <int VPL>
 __global__ void __launch_bounds__(kBlock, 2) layernorm_bw_vec_kernel(
     const __nv_bfloat16* dy, long long lddy, const __nv_bfloat16* x, long long ldx, const __nv_bfloat16* gamma,
     const float* mean, const float* rstd, const __nv_bfloat16* upstream, long long ldup, __nv_bfloat16* dx, long long lddx,
-    float* dgamma_out, float* dbeta_out, int rows, int cols, float* stage, unsigned* ticket) {
+    float* dgamma_out, float* dbeta_out, __nv_bfloat16* dx_colsum_out, int rows, int cols, float* stage, unsigned* ticket) {
     constexpr int WARPS = kBlock / kWarp;
     constexpr int W = VPL * kWarp * 8;
     extern __shared__ float ln_smem[];
     float* sgam = ln_smem;                 // [W]
     float* sag = sgam + W;                 // [WARPS][W]
     float* sab = sag + WARPS * W;          // [WARPS][W]
+    float* sax = sab + WARPS * W;          // [WARPS][W]  column sums of the dx this kernel writes (when asked for)
     const int lane = threadIdx.x & 31;
     const int warp = threadIdx.x >> 5;
     for (int c = threadIdx.x; c < W; c += kBlock) sgam[c] = c < cols ? __bfloat162float(gamma[c]) : 0.0f;
-    for (int c = threadIdx.x; c < 2 * WARPS * W; c += kBlock) sag[c] = 0.0f;
+    for (int c = threadIdx.x; c < 3 * WARPS * W; c += kBlock) sag[c] = 0.0f;
     __syncthreads();
     float* my_ag = sag + warp * W;
     float* my_ab = sab + warp * W;
+    float* my_ax = sax + warp * W;
+    const bool colsum = dx_colsum_out != nullptr;
     const bool params = dgamma_out != nullptr || dbeta_out != nullptr;
     const uint4 zero = make_uint4(0u, 0u, 0u, 0u);
     const int stride = gridDim.x * WARPS;
@@ -947,25 +950,39 @@ __global__ void __launch_bounds__(kBlock, 2) layernorm_bw_vec_kernel(
                     // the separate form rounds dx to bf16 before the add; keep that rounding
                     if (upstream != nullptr) o[i] = __bfloat162float(__float2bfloat16_rn(o[i])) + up[i];
                 }
-                *reinterpret_cast<uint4*>(dx + static_cast<size_t>(r) * lddx + c) = pack_bf16x8(o);
+                const uint4 packed = pack_bf16x8(o);
+                *reinterpret_cast<uint4*>(dx + static_cast<size_t>(r) * lddx + c) = packed;
+                if (colsum) {  // sums of the rounded values, as a column reduction of the stored tensor would see them
+                    float q[8];
+                    unpack_bf16x8(packed, q);
+                    float4 a0 = *reinterpret_cast<const float4*>(my_ax + c), a1 = *reinterpret_cast<const float4*>(my_ax + c + 4);
+                    a0.x += q[0]; a0.y += q[1]; a0.z += q[2]; a0.w += q[3];
+                    a1.x += q[4]; a1.y += q[5]; a1.z += q[6]; a1.w += q[7];
+                    *reinterpret_cast<float4*>(my_ax + c) = a0;
+                    *reinterpret_cast<float4*>(my_ax + c + 4) = a1;
+                }
             }
         }
     }
-    if (!params) return;
+    if (!params && !colsum) return;
     // CTA sums -> one of kLnCopies zero-initialised staging replicas (few CTAs collide on an address) -> the CTA that
     // arrives last adds the replicas, writes the outputs and leaves replicas and ticket at zero for the next launch.
     __shared__ int is_last;
     __syncthreads();
-    float* mine = stage + (blockIdx.x % kLnCopies) * 2 * kLnMaxCols;
+    float* mine = stage + (blockIdx.x % kLnCopies) * kLnRows * kLnMaxCols;
     for (int c = threadIdx.x; c < cols; c += kBlock) {
-        float g = 0.0f, b = 0.0f;
+        float g = 0.0f, b = 0.0f, x = 0.0f;
 #pragma unroll
         for (int w = 0; w < WARPS; ++w) {
             g += sag[w * W + c];
             b += sab[w * W + c];
+            x += sax[w * W + c];
         }
-        atomicAdd(&mine[c], g);
-        atomicAdd(&mine[kLnMaxCols + c], b);
+        if (params) {
+            atomicAdd(&mine[c], g);
+            atomicAdd(&mine[kLnMaxCols + c], b);
+        }
+        if (colsum) atomicAdd(&mine[2 * kLnMaxCols + c], x);
     }
     __threadfence();
     __syncthreads();
@@ -974,25 +991,28 @@ __global__ void __launch_bounds__(kBlock, 2) layernorm_bw_vec_kernel(
     if (!is_last) return;
     __threadfence();
     for (int c = threadIdx.x; c < cols; c += kBlock) {
-        float g = 0.0f, b = 0.0f;
+        float g = 0.0f, b = 0.0f, x = 0.0f;
 #pragma unroll
         for (int k = 0; k < kLnCopies; ++k) {
-            float* copy = stage + k * 2 * kLnMaxCols;
+            float* copy = stage + k * kLnRows * kLnMaxCols;
             g += __ldcg(copy + c);
             b += __ldcg(copy + kLnMaxCols + c);
+            x += __ldcg(copy + 2 * kLnMaxCols + c);
             copy[c] = 0.0f;
             copy[kLnMaxCols + c] = 0.0f;
+            copy[2 * kLnMaxCols + c] = 0.0f;
         }
         if (dgamma_out != nullptr) dgamma_out[c] = g;
         if (dbeta_out != nullptr) dbeta_out[c] = b;
+        if (colsum) dx_colsum_out[c] = __float2bfloat16_rn(x);
     }
     if (threadIdx.x == 0) *ticket = 0u;
 }
 
-// Dynamic shared memory of layernorm_bw_vec_kernel<VPL>: gamma and the two per-warp accumulator slabs.
+// Dynamic shared memory of layernorm_bw_vec_kernel<VPL>: gamma and the three per-warp accumulator slabs.
 template <int VPL>
 constexpr size_t ln_bw_vec_smem() {
-    return sizeof(float) * (VPL * kWarp * 8) * (1 + 2 * (kBlock / kWarp));
+    return sizeof(float) * (VPL * kWarp * 8) * (1 + 3 * (kBlock / kWarp));
 }
 
 // Backward in one pass for rows that fit a warp's registers: a persistent grid, one warp per row at a time.
@@ -1365,8 +1385,8 @@ int b200_add_layernorm_forward(b200_ctx* ctx, const void* x, int64_t ldx, const 
 
 static int layernorm_backward_impl(const char* fn, b200_ctx* ctx, const void* dy, int64_t lddy, const void* x, int64_t ldx,
                                    const void* gamma, const float* mean, const float* rstd, const void* upstream,
-                                   int64_t ldup, void* dx, int64_t lddx, float* dgamma_f32, float* dbeta_f32, int64_t rows,
-                                   int64_t cols, void* stream) {
+                                   int64_t ldup, void* dx, int64_t lddx, float* dgamma_f32, float* dbeta_f32,
+                                   void* dx_colsum_bf16, int64_t rows, int64_t cols, void* stream) {
     B200_REQUIRE(ctx != nullptr, "%s: ctx is NULL", fn);
     int rc = check_rows(fn, dy, lddy, rows, cols);
     if (rc == B200_OK) rc = check_rows(fn, x, ldx, rows, cols);
@@ -1385,12 +1405,23 @@ static int layernorm_backward_impl(const char* fn, b200_ctx* ctx, const void* dy
         if (dgamma_f32 && c > 0) B200_CUDA_TRY(cudaMemsetAsync(dgamma_f32, 0, sizeof(float) * c, s));
         if (dbeta_f32 && c > 0) B200_CUDA_TRY(cudaMemsetAsync(dbeta_f32, 0, sizeof(float) * c, s));
     }
-    if (rows == 0 || cols == 0) return B200_OK;
+    if (rows == 0 || cols == 0) {
+        if (dx_colsum_bf16 && c > 0) B200_CUDA_TRY(cudaMemsetAsync(dx_colsum_bf16, 0, sizeof(__nv_bfloat16) * c, s));
+        return B200_OK;
+    }
     B200_REQUIRE(mean && rstd, "%s: mean or rstd is NULL", fn);
     const auto* dyp = static_cast<const __nv_bfloat16*>(dy);
     const auto* xp = static_cast<const __nv_bfloat16*>(x);
     const auto* upp = static_cast<const __nv_bfloat16*>(upstream);
     auto* dxp = static_cast<__nv_bfloat16*>(dx);
+    auto* csp = static_cast<__nv_bfloat16*>(dx_colsum_bf16);
+    B200_REQUIRE(dx_colsum_bf16 == nullptr || dx != nullptr, "%s: column sums of dx requested without dx", fn);
+    // Paths other than the vector kernel take the column sums of dx with a reduction over the finished tensor.
+    auto colsum_fallback = [&]() -> int {
+        if (dx_colsum_bf16 == nullptr) return B200_OK;
+        B200_REQUIRE(lddx == cols, "%s: column sums of dx need contiguous rows on this path", fn);
+        return b200_reduce(ctx, 0 /* sum */, dx, 1, rows, cols, dx_colsum_bf16, stream);
+    };
     if (c <= 1024 && gamma != nullptr && (dx != nullptr || dgamma_f32 || dbeta_f32)) {
         // one pass: dx, the residual add and the parameter gradients
         const auto* gp = static_cast<const __nv_bfloat16*>(gamma);
@@ -1413,13 +1444,13 @@ static int layernorm_backward_impl(const char* fn, b200_ctx* ctx, const void* dy
             }
             if (c <= 512)
                 layernorm_bw_vec_kernel<2><<<blocks, kBlock, ln_bw_vec_smem<2>(), s>>>(dyp, lddy, xp, ldx, gp, mean, rstd, upp, ldup, dxp, lddx,
-                                                                                       dgamma_f32, dbeta_f32, r, c, ctx_ln_stage(ctx), ctx_tickets(ctx) + kTicketCount - 1);
+                                                                                       dgamma_f32, dbeta_f32, csp, r, c, ctx_ln_stage(ctx), ctx_tickets(ctx) + kTicketCount - 1);
             else if (c <= 768)
                 layernorm_bw_vec_kernel<3><<<blocks, kBlock, ln_bw_vec_smem<3>(), s>>>(dyp, lddy, xp, ldx, gp, mean, rstd, upp, ldup, dxp, lddx,
-                                                                                       dgamma_f32, dbeta_f32, r, c, ctx_ln_stage(ctx), ctx_tickets(ctx) + kTicketCount - 1);
+                                                                                       dgamma_f32, dbeta_f32, csp, r, c, ctx_ln_stage(ctx), ctx_tickets(ctx) + kTicketCount - 1);
             else
                 layernorm_bw_vec_kernel<4><<<blocks, kBlock, ln_bw_vec_smem<4>(), s>>>(dyp, lddy, xp, ldx, gp, mean, rstd, upp, ldup, dxp, lddx,
-                                                                                       dgamma_f32, dbeta_f32, r, c, ctx_ln_stage(ctx), ctx_tickets(ctx) + kTicketCount - 1);
+                                                                                       dgamma_f32, dbeta_f32, csp, r, c, ctx_ln_stage(ctx), ctx_tickets(ctx) + kTicketCount - 1);
             B200_CUDA_TRY(cudaGetLastError());
             return B200_OK;
         }
@@ -1433,7 +1464,7 @@ static int layernorm_backward_impl(const char* fn, b200_ctx* ctx, const void* dy
             layernorm_bw_fused_warp_kernel<4><<<blocks, kBlock, 0, s>>>(dyp, lddy, xp, ldx, gp, mean, rstd, upp, ldup, dxp, lddx,
                                                                         dgamma_f32, dbeta_f32, r, c, vdy, vx, vdx, vg, vup);
         B200_CUDA_TRY(cudaGetLastError());
-        return B200_OK;
+        return colsum_fallback();
     }
     if (dx) {
         B200_REQUIRE(gamma != nullptr, "%s: gamma is NULL", fn);
@@ -1465,14 +1496,22 @@ static int layernorm_backward_impl(const char* fn, b200_ctx* ctx, const void* dy
             layernorm_bw_param_kernel<1><<<grid, 256, 0, s>>>(dyp, lddy, xp, ldx, mean, rstd, dgamma_f32, dbeta_f32, r, c, rows_per);
         B200_CUDA_TRY(cudaGetLastError());
     }
-    return B200_OK;
+    return colsum_fallback();
 }
 
 int b200_layernorm_backward(b200_ctx* ctx, const void* dy, int64_t lddy, const void* x, int64_t ldx, const void* gamma,
                             const float* mean, const float* rstd, void* dx, int64_t lddx, float* dgamma_f32,
                             float* dbeta_f32, int64_t rows, int64_t cols, void* stream) {
     return layernorm_backward_impl("b200_layernorm_backward", ctx, dy, lddy, x, ldx, gamma, mean, rstd, nullptr, 0, dx, lddx,
-                                   dgamma_f32, dbeta_f32, rows, cols, stream);
+                                   dgamma_f32, dbeta_f32, nullptr, rows, cols, stream);
+}
+
+int b200_layernorm_backward_full(b200_ctx* ctx, const void* dy, int64_t lddy, const void* x, int64_t ldx, const void* gamma,
+                                 const float* mean, const float* rstd, const void* upstream, int64_t ldup, void* dx,
+                                 int64_t lddx, float* dgamma_f32, float* dbeta_f32, void* dx_colsum_bf16, int64_t rows,
+                                 int64_t cols, void* stream) {
+    return layernorm_backward_impl("b200_layernorm_backward_full", ctx, dy, lddy, x, ldx, gamma, mean, rstd, upstream, ldup, dx,
+                                   lddx, dgamma_f32, dbeta_f32, dx_colsum_bf16, rows, cols, stream);
 }
 
 int b200_layernorm_backward_add(b200_ctx* ctx, const void* dy, int64_t lddy, const void* x, int64_t ldx, const void* gamma,
@@ -1480,7 +1519,7 @@ int b200_layernorm_backward_add(b200_ctx* ctx, const void* dy, int64_t lddy, con
                                 int64_t lddx, float* dgamma_f32, float* dbeta_f32, int64_t rows, int64_t cols, void* stream) {
     B200_REQUIRE(upstream != nullptr && dx != nullptr, "b200_layernorm_backward_add: upstream or dx is NULL");
     return layernorm_backward_impl("b200_layernorm_backward_add", ctx, dy, lddy, x, ldx, gamma, mean, rstd, upstream, ldup, dx,
-                                   lddx, dgamma_f32, dbeta_f32, rows, cols, stream);
+                                   lddx, dgamma_f32, dbeta_f32, nullptr, rows, cols, stream);
 }
 
 }  // extern "C"

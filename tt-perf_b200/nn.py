@@ -102,11 +102,17 @@ def add_layernorm_forward(ctx, x, residual, gamma, beta, *, eps=1e-5, stream=Non
     return total, y, mean, rstd
 
 
-def layernorm_backward(ctx, d_y, x, gamma, mean, rstd, *, upstream=None, stream=None):
-    """(dx, dgamma, dbeta); with `upstream`, dx also includes that gradient (the residual path) without a separate add."""
+def layernorm_backward(ctx, d_y, x, gamma, mean, rstd, *, upstream=None, want_colsum=False, stream=None):
+    """(dx, dgamma, dbeta); with `upstream`, dx also includes that gradient (the residual path) without a separate add.
+    want_colsum appends the column sums of dx (bf16 [cols]): dx is the dY of the Linear layer that writes into this
+    residual stream, so the sums are that layer's bias gradient."""
     rows, cols = _rows(x), x.shape[-1]
     d_x = DeviceTensor(ctx, x.shape, BF16)
     dg, db = DeviceTensor(ctx, (cols,), F32), DeviceTensor(ctx, (cols,), F32)
+    if want_colsum:
+        cs = DeviceTensor(ctx, (cols,), BF16)
+        ctx.layernorm_backward_full(d_y, x, gamma, mean, rstd, upstream, d_x, dg, db, cs, rows, cols, stream=stream)
+        return d_x, dg, db, cs
     if upstream is None:
         ctx.layernorm_backward(d_y, x, gamma, mean, rstd, d_x, dg, db, rows, cols, stream=stream)
     else:
@@ -294,17 +300,22 @@ def transformer_block_forward(ctx, x, w, heads, *, defer_add=False, stream=None)
     return add(ctx, res1, mlp_out, stream=stream), cache
 
 
-def transformer_block_backward(ctx, d_out, w, cache, heads, *, stream=None):
-    """Returns (dx, grads) with grads keyed like `w` (LayerNorm gradients are fp32, the rest bf16)."""
+def transformer_block_backward(ctx, d_out, w, cache, heads, *, d_out_colsum=None, want_dx_colsum=False, stream=None):
+    """Returns (dx, grads) with grads keyed like `w` (LayerNorm gradients are fp32, the rest bf16).
+    d_out_colsum: column sums of d_out when the producer of d_out already has them (they are the FC2 bias gradient);
+    want_dx_colsum: also return the column sums of dx as a third value, for the block below."""
     c, g = cache, {}
     b, s, d = c["x"].shape
     dh = d // heads
-    d_h1g, g["w2"], g["b2"] = linear_backward(ctx, c["h1g"], w["w2"], d_out, stream=stream)
+    d_h1g, g["w2"], g["b2"] = linear_backward(ctx, c["h1g"], w["w2"], d_out, need_db=d_out_colsum is None, stream=stream)
+    if d_out_colsum is not None:
+        g["b2"] = d_out_colsum
     d_h1 = gelu_backward(ctx, d_h1g, c["h1"], stream=stream)
     d_ln2, g["w1"], g["b1"] = linear_backward(ctx, c["ln2"], w["w1"], d_h1, stream=stream)
-    d_res1, g["ln2_g"], g["ln2_b"] = layernorm_backward(ctx, d_ln2, c["res1"], w["ln2_g"], c["mean2"], c["rstd2"],
-                                                         upstream=d_out, stream=stream)
-    d_merged, g["wo"], g["bo"] = linear_backward(ctx, c["merged"], w["wo"], d_res1, stream=stream)
+    # d_res1 is the dY of the attention output projection: its column sums (from the same kernel) are that bias gradient
+    d_res1, g["ln2_g"], g["ln2_b"], g["bo"] = layernorm_backward(ctx, d_ln2, c["res1"], w["ln2_g"], c["mean2"], c["rstd2"],
+                                                                  upstream=d_out, want_colsum=True, stream=stream)
+    d_merged, g["wo"], _ = linear_backward(ctx, c["merged"], w["wo"], d_res1, need_db=False, stream=stream)
     if "lse" in c:
         (o_op,), (do_op,) = _head_operands(ctx, c["merged"], heads), _head_operands(ctx, d_merged, heads)
         if len(c["qkv"]) == 1:
@@ -331,6 +342,10 @@ def transformer_block_backward(ctx, d_out, w, cache, heads, *, stream=None):
         d_ln1_k, g["wk"], g["bk"] = linear_backward(ctx, c["ln1"], w["wk"], grads_in[1], stream=stream)
         d_ln1_v, g["wv"], g["bv"] = linear_backward(ctx, c["ln1"], w["wv"], grads_in[2], stream=stream)
         d_ln1 = add(ctx, add(ctx, d_ln1_q, d_ln1_k, stream=stream), d_ln1_v, stream=stream)
+    if want_dx_colsum:
+        d_x, g["ln1_g"], g["ln1_b"], cs = layernorm_backward(ctx, d_ln1, c["x"], w["ln1_g"], c["mean1"], c["rstd1"],
+                                                              upstream=d_res1, want_colsum=True, stream=stream)
+        return d_x, g, cs
     d_x, g["ln1_g"], g["ln1_b"] = layernorm_backward(ctx, d_ln1, c["x"], w["ln1_g"], c["mean1"], c["rstd1"],
                                                       upstream=d_res1, stream=stream)
     return d_x, g
@@ -445,12 +460,15 @@ class GPT2:
                           stream=stream)
         grads = {"blocks": [None] * self.L}
         d_xf, grads["head"], _ = linear_backward(ctx, xf, p["head"], d_logits, need_db=False, stream=stream)
-        d_x, grads["lnf_g"], grads["lnf_b"] = layernorm_backward(ctx, d_xf, x, p["lnf_g"], mean_f, rstd_f, stream=stream)
+        # every d_x below is the dY of the FC2 layer of the block it enters: its column sums travel with it
+        d_x, grads["lnf_g"], grads["lnf_b"], d_x_cs = layernorm_backward(ctx, d_xf, x, p["lnf_g"], mean_f, rstd_f,
+                                                                          want_colsum=True, stream=stream)
         if segment_hook:
             segment_hook([(p[k], grads[k]) for k in ("head", "lnf_g", "lnf_b")])
         pending, done = [], 0
         for i in reversed(range(self.L)):
-            d_x, grads["blocks"][i] = transformer_block_backward(ctx, d_x, p["blocks"][i], caches[i], self.H, stream=stream)
+            d_x, grads["blocks"][i], d_x_cs = transformer_block_backward(ctx, d_x, p["blocks"][i], caches[i], self.H,
+                                                                         d_out_colsum=d_x_cs, want_dx_colsum=True, stream=stream)
             pending += [(p["blocks"][i][k], grads["blocks"][i][k]) for k in BLOCK_KEYS]
             done += 1
             if segment_hook and done % blocks_per_segment == 0 and i > 0:
