@@ -81,3 +81,47 @@ def test_null_arguments_are_rejected(pkg):
     assert lib.b200_synchronize(None, None) == pkg.capi.ERR_INVALID_ARG
     assert lib.b200_malloc(None, 16, None) == pkg.capi.ERR_INVALID_ARG
     assert lib.b200_ctx_destroy(None) == pkg.capi.OK  # destroying nothing is not an error
+
+
+def test_python_ttnn_stand_in_imports_and_serves_the_reference_engine():
+    """The Python `ttnn` stand-in exposes every name the reference's Python side uses; when the reference tree is
+    present, its py/engine.py, py/nn.py and py/optim.py import against it unchanged (no device is opened)."""
+    import importlib
+    import importlib.util
+    import os
+    import sys
+    from pathlib import Path
+    repo = Path(__file__).resolve().parent.parent
+    sys.path.insert(0, str(repo / "tt-perf_b200" / "ttnn_py"))
+    try:
+        sys.modules.pop("ttnn", None)
+        ttnn = importlib.import_module("ttnn")
+        for name in ("open_device", "close_device", "from_torch", "to_torch", "Tensor", "bfloat16", "float32", "uint32",
+                     "TILE_LAYOUT", "ROW_MAJOR_LAYOUT", "add", "sub", "mul", "div", "matmul", "sum", "softmax", "log", "exp",
+                     "tanh", "sqrt", "relu", "gtz", "permute", "reshape", "triu", "embedding", "full_like", "ones_like",
+                     "WormholeComputeKernelConfig", "MathFidelity", "ReadDeviceProfiler"):
+            assert hasattr(ttnn, name), name
+        assert ttnn.MathFidelity.HiFi3 and ttnn.WormholeComputeKernelConfig(math_fidelity=ttnn.MathFidelity.HiFi3)
+        ref = Path(os.environ.get("TTPERF_REFERENCE", "/root/reference"))
+        if (ref / "py" / "engine.py").exists():
+            # the reference's files import each other as `src.*` while the directory is called py/: load it under that name
+            spec = importlib.util.spec_from_file_location("src", ref / "py" / "__init__.py",
+                                                          submodule_search_locations=[str(ref / "py")])
+            pkg = importlib.util.module_from_spec(spec)
+            sys.modules["src"] = pkg
+            try:
+                spec.loader.exec_module(pkg)
+                importlib.import_module("src.engine")
+                sys.modules["grad"] = pkg                      # optim.py says `grad.engine` for the same module
+                sys.modules["grad.engine"] = sys.modules["src.engine"]
+                for mod in ("src.nn", "src.optim"):
+                    importlib.import_module(mod)
+                eng = sys.modules["src.engine"]
+                assert eng.resolve_tt_dtype(None) is ttnn.bfloat16
+                assert eng._DEFAULT_COMPUTE_KERNEL_CONFIG.math_fidelity == ttnn.MathFidelity.HiFi3
+            finally:
+                for mod in [m for m in sys.modules if m in ("src", "grad") or m.startswith(("src.", "grad."))]:
+                    sys.modules.pop(mod, None)
+    finally:
+        sys.path.remove(str(repo / "tt-perf_b200" / "ttnn_py"))
+        sys.modules.pop("ttnn", None)
