@@ -67,6 +67,10 @@ int b200_ctx_create(int device_ordinal, b200_ctx** out_ctx);
 int b200_ctx_destroy(b200_ctx* ctx);
 int b200_ctx_device(const b200_ctx* ctx, int* out_device_ordinal);
 int b200_ctx_sm_count(const b200_ctx* ctx, int* out_sm_count);
+/* The context's own stream (a cudaStream_t), the one calls with stream = NULL run on: lets the host program order its
+ * own work — e.g. a collective of its communication library that serves as a barrier between ranks — after the
+ * kernels queued here without a host synchronisation. */
+int b200_ctx_stream(const b200_ctx* ctx, void** out_stream);
 /* Blocks until all work queued on `stream` has finished, then reports a kernel wait that timed out
  * since the last call as B200_ERR_DEVICE_TIMEOUT (and clears it). */
 int b200_synchronize(b200_ctx* ctx, void* stream);

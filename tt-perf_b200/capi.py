@@ -59,6 +59,7 @@ SIGNATURES = {
     "b200_ctx_create": (C.c_int, [C.c_int, C.POINTER(C.c_void_p)]),
     "b200_ctx_destroy": (C.c_int, [C.c_void_p]),
     "b200_ctx_device": (C.c_int, [C.c_void_p, C.POINTER(C.c_int)]),
+    "b200_ctx_stream": (C.c_int, [C.c_void_p, C.POINTER(C.c_void_p)]),
     "b200_ctx_sm_count": (C.c_int, [C.c_void_p, C.POINTER(C.c_int)]),
     "b200_synchronize": (C.c_int, [C.c_void_p, C.c_void_p]),
     "b200_timer_start": (C.c_int, [C.c_void_p, C.c_void_p, C.POINTER(C.c_void_p)]),
@@ -204,6 +205,13 @@ class Context:
     @property
     def handle(self) -> C.c_void_p:
         return self._h
+
+    @property
+    def stream(self) -> int:
+        """The context's own cudaStream_t (the stream of every call made with stream=None)."""
+        out = C.c_void_p()
+        check(lib().b200_ctx_stream(self._h, C.byref(out)))
+        return out.value or 0
 
     @property
     def sm_count(self) -> int:

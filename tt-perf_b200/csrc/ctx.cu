@@ -138,6 +138,12 @@ int b200_ctx_sm_count(const b200_ctx* ctx, int* out) {
     return B200_OK;
 }
 
+int b200_ctx_stream(const b200_ctx* ctx, void** out) {
+    B200_REQUIRE(ctx && out, "b200_ctx_stream: NULL argument");
+    *out = ctx->stream;
+    return B200_OK;
+}
+
 int b200_synchronize(b200_ctx* ctx, void* stream) {
     B200_REQUIRE(ctx != nullptr, "b200_synchronize: ctx is NULL");
     if (pool_is_recording(ctx) && ctx->pick(stream) == ctx->stream)

@@ -16,8 +16,9 @@ bench/metal/matmul_tensor_parallel.cpp:54-123); the arithmetic is that of its si
 
 Every rank runs the same generator; each `yield` is a point where all ranks must have finished what they queued
 (stores into peers' memory become visible only then). `run_emulated` steps the generators of g ranks that live in one
-process on one GPU in lockstep (one stream orders everything); `run_process` is the one-process-per-GPU form, where a
-yield is a stream synchronisation plus a `torch.distributed` barrier and peer buffers are CUDA IPC mappings."""
+process on one GPU in lockstep (one stream orders everything); `run_process` is the one-process-per-GPU form, where
+peer buffers are CUDA IPC mappings and a yield is a barrier between the ranks queued on the stream (a one-element NCCL
+all-reduce) or, optionally, a host-side synchronisation plus a `torch.distributed` barrier."""
 from __future__ import annotations
 
 import numpy as np
@@ -80,6 +81,7 @@ class ProcessFabric:
     def __init__(self, ctx, rank: int, world: int, group=None):
         self.ctx, self.rank, self.world, self.group = ctx, rank, world, group
         self._bufs = []
+        self._flag = self._ext = None
 
     def shared(self, nbytes: int) -> list[int]:
         from .dist import _PeerBuffers
@@ -88,9 +90,22 @@ class ProcessFabric:
         return b.ptrs
 
     def barrier(self) -> None:
+        """Host-side: wait for this rank's stream, then for every rank."""
         import torch.distributed as dist
         self.ctx.synchronize()
         dist.barrier(group=self.group)
+
+    def stream_barrier(self) -> None:
+        """Device-side: a one-element NCCL all-reduce queued on the context's stream. It starts only after the kernels
+        and peer copies this rank queued before it and completes only when every rank has reached it, so whatever runs
+        after it on this stream sees all peers' stores. No host synchronisation."""
+        import torch
+        import torch.distributed as dist
+        if self._flag is None:
+            self._flag = torch.zeros(1, device="cuda")
+            self._ext = torch.cuda.ExternalStream(self.ctx.stream)
+        with torch.cuda.stream(self._ext):
+            dist.all_reduce(self._flag, group=self.group)
 
     def close(self) -> None:
         for b in self._bufs:
@@ -307,7 +322,10 @@ def make_process(ctx, rank: int, world: int, *, batch: int, seq: int, d_model: i
     return TPBlockRank(ctx, rank, world, batch=batch, seq=seq, d_model=d_model, heads=heads, host_w=host_w, ptrs=ptrs), fabric
 
 
-def run_process(generator, fabric: ProcessFabric) -> None:
+def run_process(generator, fabric: ProcessFabric, *, host_barriers: bool = False) -> None:
+    """Runs one rank's generator; every exchange point is a barrier between the ranks — on the stream (default: nothing
+    blocks the host, the ranks' kernels simply queue up) or on the host (`host_barriers`, the conservative form)."""
+    wait = fabric.barrier if host_barriers else fabric.stream_barrier
     for _ in generator:
-        fabric.barrier()
-    fabric.barrier()
+        wait()
+    wait()
