@@ -61,15 +61,25 @@ def main():
         for _ in range(3):
             step()
         fabric.barrier()
-        n = 10
+        run, executor = step, "eager launches"
+        if os.environ.get("TP_GRAPH", "1") == "1":
+            # the whole step of this rank — kernels, peer copies and the on-stream NCCL barriers — as one CUDA graph
+            tid = ctx.trace_begin()
+            step()
+            ctx.trace_end(tid)
+            run, executor = (lambda: ctx.trace_execute(tid)), "trace replay (CUDA graph per rank, NCCL barriers inside)"
+            run()
+            fabric.barrier()
+        n = 20
         t0 = time.perf_counter()
         for _ in range(n):
-            step()
+            run()
         fabric.barrier()
         ms = torch.tensor([(time.perf_counter() - t0) / n * 1e3], device="cuda")
         dist.all_reduce(ms, op=dist.ReduceOp.MAX)
         if rank == 0:
             print(json.dumps({"metric": "TP GPT-2-XL block step", "ms_per_step": float(ms.item()), "n_gpus": world,
+                              "executor": executor,
                               "tokens_per_s": t / float(ms.item()) * 1e3, "config": {"batch": b, "seq": s, "d_model": d,
                                                                                       "heads": heads, "d_ff": f}}))
     else:
