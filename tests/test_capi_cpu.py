@@ -102,7 +102,10 @@ def test_python_ttnn_stand_in_imports_and_serves_the_reference_engine():
                      "WormholeComputeKernelConfig", "MathFidelity", "ReadDeviceProfiler"):
             assert hasattr(ttnn, name), name
         assert ttnn.MathFidelity.HiFi3 and ttnn.WormholeComputeKernelConfig(math_fidelity=ttnn.MathFidelity.HiFi3)
-        ref = Path(os.environ.get("TTPERF_REFERENCE", "/root/reference"))
+        spec_b = importlib.util.spec_from_file_location("build_ref_mains", repo / "tests" / "ref_mains" / "build_ref_mains.py")
+        brm = importlib.util.module_from_spec(spec_b)
+        spec_b.loader.exec_module(brm)
+        ref = Path(brm.default_reference())     # TTPERF_REFERENCE, else the default location of the tree
         if (ref / "py" / "engine.py").exists():
             # the reference's files import each other as `src.*` while the directory is called py/: load it under that name
             spec = importlib.util.spec_from_file_location("src", ref / "py" / "__init__.py",
