@@ -283,6 +283,9 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
                     dst_count = 1;
                     row_coord -= dst_first * p.scatter_rows;
                 }
+                uint32_t nx0[32], nx1[32];
+                tmem_ld_32x32b_x32(taddr, nx0);
+                if (box_cols == 64 && it.n0 + 32 < p.N) tmem_ld_32x32b_x32(taddr + 32, nx1);
 #pragma unroll 1
                 for (int c = 0; c < BN; c += box_cols) {
                     const int n = it.n0 + c;
@@ -291,13 +294,26 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
                     if (lane == 0) tma_store_wait_read<1>();  // the box stored two iterations ago has left this buffer
                     __syncwarp();
                     uint8_t* srow = sbuf + lane * 128;
+                    // The TMEM loads of the NEXT box are in flight while this one is converted and staged.
+                    tmem_ld_wait();
+                    uint32_t v0[32], v1[32];
+#pragma unroll
+                    for (int i = 0; i < 32; ++i) {
+                        v0[i] = nx0[i];
+                        v1[i] = nx1[i];
+                    }
+                    {
+                        const int cn = c + box_cols;
+                        if (cn < BN && it.n0 + cn < p.N) {
+                            tmem_ld_32x32b_x32(taddr + cn, nx0);
+                            if (box_cols == 64 && it.n0 + cn + 32 < p.N) tmem_ld_32x32b_x32(taddr + cn + 32, nx1);
+                        }
+                    }
 #pragma unroll 1
                     for (int h = 0; h * 32 < box_cols; ++h) {
                         const int nh = n + h * 32;
                         if (nh >= p.N) break;
-                        uint32_t v[32];
-                        tmem_ld_32x32b_x32(taddr + c + h * 32, v);
-                        tmem_ld_wait();
+                        uint32_t (&v)[32] = h == 0 ? v0 : v1;
                         float f[32];
                         epi_apply32(p.epi, v, f, row, nh, p.N);
                         if (p.c_f32) {
