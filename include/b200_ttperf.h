@@ -30,7 +30,7 @@
 extern "C" {
 #endif
 
-#define B200_TTPERF_ABI_VERSION 1
+#define B200_TTPERF_ABI_VERSION 2
 
 typedef enum b200_status {
     B200_OK = 0,
@@ -42,7 +42,7 @@ typedef enum b200_status {
     B200_ERR_COMM = 6            /* collective layer (NCCL) failure */
 } b200_status;
 
-typedef enum b200_dtype { B200_BF16 = 0, B200_F32 = 1, B200_U32 = 2 } b200_dtype;
+typedef enum b200_dtype { B200_BF16 = 0, B200_F32 = 1, B200_U32 = 2, B200_FP8_E4M3 = 3 } b200_dtype;
 
 /* Fused activations of ttnn::linear / ttnn::matmul (static/nn.hpp:145-146, bench/metal/bench_fusion.cpp:119). */
 typedef enum b200_activation { B200_ACT_NONE = 0, B200_ACT_RELU = 1, B200_ACT_GELU = 2 } b200_activation;
@@ -151,9 +151,16 @@ typedef struct b200_gemm_desc {
     int32_t fidelity; /* b200_fidelity */
     int32_t algo;     /* b200_gemm_algo */
     int32_t split_k;  /* 0 = choose; 1 = never split; n > 1 = split K into n slices (fp32 scratch + reduce) */
+    int32_t ab_dtype; /* B200_BF16 (default) or B200_FP8_E4M3: A and B hold 8-bit e4m3 values (one byte per element,
+                       * lda / ldb / strides in elements, multiples of 16). The tensor cores then run at twice the bf16
+                       * rate (tcgen05 kind::f8f6f4, fp32 accumulation). 8-bit operands cannot be read transposed:
+                       * transpose_a must be 0 and transpose_b 1 (the Linear forward form x . W^T). `alpha` carries the
+                       * de-quantisation factor 1 / (scale_a * scale_b). This is the reduced-fidelity matmul of the
+                       * reference's fidelity study (verify/verify_fidelity.cpp:50-67, 151-208: LoFi trades mantissa
+                       * bits of the operands for speed) in B200 terms. */
 } b200_gemm_desc;
 
-/* Fills a descriptor with defaults: no transposes, batch 1, alpha 1, bf16 output, HIFI4, AUTO. */
+/* Fills a descriptor with defaults: no transposes, batch 1, alpha 1, bf16 operands and output, HIFI4, AUTO. */
 void b200_gemm_desc_init(b200_gemm_desc* desc);
 int b200_gemm(b200_ctx* ctx, const b200_gemm_desc* desc, void* stream);
 /* The same product with A, B and C in HOST memory (pinned memory gives full PCIe speed) — the path a reference program
@@ -271,6 +278,11 @@ int b200_binary(b200_ctx* ctx, int op, const void* a, const int64_t a_shape[4], 
 typedef enum b200_reduce_op { B200_R_SUM = 0, B200_R_MEAN = 1, B200_R_MAX = 2 } b200_reduce_op;
 int b200_reduce(b200_ctx* ctx, int op, const void* x, int64_t outer, int64_t R, int64_t inner, void* y, void* stream);
 
+/* 8-bit operands for b200_gemm with ab_dtype = B200_FP8_E4M3.
+ * b200_absmax: out_f32[0] = max |x| over n bf16 elements (device scalar, overwritten).
+ * b200_quantize_fp8: y[i] = e4m3(x[i] * scale), saturating at +-448; a caller picks scale = 448 / absmax. */
+int b200_absmax(b200_ctx* ctx, const void* x_bf16, int64_t n, float* out_f32, void* stream);
+int b200_quantize_fp8(b200_ctx* ctx, const void* x_bf16, int64_t n, float scale, void* y_fp8, void* stream);
 /* Creation and conversion (ttnn::zeros / ones / full / full_like, traced/nn.hpp:30-52). `value` is converted to dtype. */
 int b200_fill(b200_ctx* ctx, void* dst, int64_t n, int dtype, float value, void* stream);
 int b200_cast(b200_ctx* ctx, const void* src, int src_dtype, void* dst, int dst_dtype, int64_t n, void* stream);

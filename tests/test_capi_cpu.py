@@ -45,22 +45,25 @@ def test_header_compiles_as_plain_c(tmp_path):
 def test_struct_layout_matches_the_header(pkg, tmp_path):
     src = tmp_path / "sz.c"
     src.write_text('#include <stdio.h>\n#include <stddef.h>\n#include "b200_ttperf.h"\n'
-                   'int main(void){ printf("%zu %zu %zu %zu", sizeof(b200_gemm_desc), offsetof(b200_gemm_desc, C),'
-                   ' offsetof(b200_gemm_desc, alpha), offsetof(b200_gemm_desc, split_k)); return 0; }\n')
+                   'int main(void){ printf("%zu %zu %zu %zu %zu", sizeof(b200_gemm_desc), offsetof(b200_gemm_desc, C),'
+                   ' offsetof(b200_gemm_desc, alpha), offsetof(b200_gemm_desc, split_k),'
+                   ' offsetof(b200_gemm_desc, ab_dtype)); return 0; }\n')
     exe = tmp_path / "sz"
     subprocess.run(["gcc", "-I", str(REPO / "include"), str(src), "-o", str(exe)], check=True)
-    size, off_c, off_alpha, off_split = map(int, subprocess.run([str(exe)], capture_output=True, text=True,
+    size, off_c, off_alpha, off_split, off_ab = map(int, subprocess.run([str(exe)], capture_output=True, text=True,
                                                                 check=True).stdout.split())
     G = pkg.GemmDesc
-    assert (C.sizeof(G), G.C.offset, G.alpha.offset, G.split_k.offset) == (size, off_c, off_alpha, off_split)
+    assert (C.sizeof(G), G.C.offset, G.alpha.offset, G.split_k.offset, G.ab_dtype.offset) == (
+        size, off_c, off_alpha, off_split, off_ab)
 
 
 def test_abi_version_and_desc_defaults(pkg):
     lib = pkg.lib()
-    assert lib.b200_abi_version() == 1
+    assert lib.b200_abi_version() == 2
     d = pkg.GemmDesc()
     lib.b200_gemm_desc_init(C.byref(d))
     assert (d.batch, d.alpha, d.c_dtype, d.fidelity, d.algo, d.split_k) == (1, 1.0, pkg.BF16, pkg.HIFI4, 0, 0)
+    assert d.ab_dtype == pkg.BF16
     assert d.transpose_a == 0 and d.transpose_b == 0 and d.activation == pkg.ACT_NONE
 
 

@@ -1,0 +1,142 @@
+"""8-bit (e4m3) operand path of b200_gemm, through the C ABI. The product of the quantised operands is compared with
+the oracle's float64 product of the same codes (the only error left is fp32 accumulation order, so the bound is tight);
+the quantiser and the absmax reduction are compared bit for bit; and the end-to-end error against the bf16 product is
+bounded by what three mantissa bits allow."""
+import numpy as np
+import pytest
+import torch
+
+from oracle import matmul_oracle as mo
+
+pytestmark = pytest.mark.gpu
+
+
+def codes(shape, seed):
+    """Random finite e4m3 codes with magnitudes up to 4 (keeps fp32 partial sums far from cancellation noise)."""
+    rng = np.random.default_rng(seed)
+    x = rng.standard_normal(shape).astype(np.float32)
+    return mo.quantize_e4m3(x)
+
+
+def run(pkg, ctx, stream, a, b, M, N, K, *, batch=1, c_dtype=None, **kw):
+    c_dtype = pkg.F32 if c_dtype is None else c_dtype
+    tdt = torch.float32 if c_dtype == pkg.F32 else torch.bfloat16
+    shape = (batch, M, N) if batch > 1 else (M, N)
+    c = torch.full(shape, float("nan"), dtype=tdt, device="cuda")
+    da, db = torch.from_numpy(a).cuda(), torch.from_numpy(b).cuda()
+    ctx.gemm(ctx.gemm_desc(da, db, c, M, N, K, transpose_b=True, batch=batch, c_dtype=c_dtype,
+                           ab_dtype=pkg.FP8_E4M3, **kw), stream.cuda_stream)
+    ctx.synchronize(stream.cuda_stream)
+    return c.float().cpu().numpy()
+
+
+SHAPES = [
+    (128, 256, 128),     # one tile, one K block
+    (128, 64, 32),       # a single MMA K slice
+    (256, 256, 512),
+    (200, 136, 208),     # ragged everywhere; K ends inside a K block
+    (1000, 520, 784),
+    (513, 72, 1040),
+    (8, 8, 16),
+    (2600, 2824, 784),   # CTA-pair kernel, ragged
+    (4096, 2560, 384),
+    (128, 256, 8192),    # the planner slices K
+]
+
+
+@pytest.mark.parametrize("M,N,K", SHAPES)
+def test_fp8_gemm_matches_oracle(pkg, ctx, stream, M, N, K):
+    a, b = codes((M, K), 1 + M), codes((N, K), 2 + N)
+    got = run(pkg, ctx, stream, a, b, M, N, K, alpha=0.25)
+    assert not np.isnan(got).any(), "output tile left unwritten"
+    assert mo.rel_frobenius(got, mo.matmul_e4m3(a, b, 0.25)) <= 2e-6
+
+
+@pytest.mark.parametrize("split_k", [1, 2, 4, 7])
+def test_fp8_gemm_k_slices(pkg, ctx, stream, split_k):
+    M, N, K = 256, 512, 2048
+    a, b = codes((M, K), 11), codes((N, K), 12)
+    got = run(pkg, ctx, stream, a, b, M, N, K, split_k=split_k)
+    assert mo.rel_frobenius(got, mo.matmul_e4m3(a, b)) <= 2e-6
+
+
+def test_fp8_gemm_batched_bias_gelu_bf16_out(pkg, ctx, stream):
+    B, M, N, K = 3, 192, 320, 256
+    a, b = codes((B, M, K), 21), codes((B, N, K), 22)
+    bias = mo.bf16_round(np.random.default_rng(23).standard_normal(N).astype(np.float32))
+    dbias = torch.from_numpy(bias).bfloat16().cuda()
+    got = run(pkg, ctx, stream, a, b, M, N, K, batch=B, c_dtype=pkg.BF16, bias=dbias, activation=pkg.ACT_GELU,
+              alpha=1.0 / 16)
+    ref = mo.gelu(mo.matmul_e4m3(a, b, 1.0 / 16) + bias)
+    assert mo.rel_frobenius(got, ref) <= 1e-2
+
+
+def test_fp8_gemm_shared_weight_across_batch(pkg, ctx, stream):
+    B, M, N, K = 4, 128, 128, 128
+    a, b = codes((B, M, K), 31), codes((N, K), 32)
+    got = run(pkg, ctx, stream, a, b, M, N, K, batch=B, stride_b=0)
+    assert mo.rel_frobenius(got, mo.matmul_e4m3(a, b)) <= 2e-6
+
+
+def test_fp8_rejects_what_the_tensor_cores_cannot_read(pkg, ctx, stream):
+    a = torch.zeros(64 * 64, dtype=torch.uint8, device="cuda")
+    c = torch.zeros(64, 64, dtype=torch.float32, device="cuda")
+    for kw in (dict(transpose_b=False), dict(transpose_a=True, transpose_b=True), dict(transpose_b=True, lda=72),
+               dict(transpose_b=True, algo=pkg.ALGO_SIMT)):
+        with pytest.raises(pkg.B200Error) as e:
+            ctx.gemm(ctx.gemm_desc(a, a, c, 64, 64, 64, c_dtype=pkg.F32, ab_dtype=pkg.FP8_E4M3, **kw), stream.cuda_stream)
+        assert e.value.code == pkg.capi.ERR_INVALID_ARG
+    with pytest.raises(pkg.B200Error):
+        ctx.gemm(ctx.gemm_desc(a, a, c, 64, 64, 64, transpose_b=True, c_dtype=pkg.F32, ab_dtype=7), stream.cuda_stream)
+
+
+@pytest.mark.parametrize("n,offset", [(1 << 20, 0), (100003, 0), (4099, 1), (7, 0), (16, 0)])
+def test_absmax_and_quantise_are_bit_exact(pkg, ctx, stream, n, offset):
+    rng = np.random.default_rng(n)
+    x = mo.bf16_round((rng.standard_normal(n + offset) * rng.choice([1e-3, 0.1, 1.0, 40.0], n + offset)).astype(np.float32))
+    dx = torch.from_numpy(x).bfloat16().cuda()[offset:]   # offset 1: a 2-byte aligned start, scalar path
+    x = x[offset:]
+    amax = torch.full((1,), -1.0, dtype=torch.float32, device="cuda")
+    ctx.absmax(dx, n, amax, stream=stream.cuda_stream)
+    ctx.synchronize(stream.cuda_stream)
+    want = float(np.abs(x).max())
+    assert float(amax.item()) == want
+    scale = float(np.float32(448.0) / np.float32(want))
+    y = torch.full((n + 16,), 0xAB, dtype=torch.uint8, device="cuda")
+    ctx.quantize_fp8(dx, n, scale, y, stream=stream.cuda_stream)
+    ctx.synchronize(stream.cuda_stream)
+    got = y.cpu().numpy()
+    assert np.array_equal(got[:n], mo.quantize_e4m3(x, scale))
+    assert (got[n:] == 0xAB).all(), "wrote past the end"
+    # out-of-range products saturate instead of becoming NaN
+    ctx.quantize_fp8(dx, n, scale * 8, y, stream=stream.cuda_stream)
+    ctx.synchronize(stream.cuda_stream)
+    assert np.array_equal(y.cpu().numpy()[:n], mo.quantize_e4m3(x, scale * 8))
+
+
+def test_fp8_linear_close_to_the_bf16_product(pkg, ctx, stream):
+    """x . W^T with per-tensor scales: the 8-bit result stays within the error three mantissa bits give (about 2^-4
+    per operand, averaged down over K)."""
+    M, N, K = 512, 768, 1024
+    rng = np.random.default_rng(5)
+    x = mo.bf16_round(rng.standard_normal((M, K)).astype(np.float32))
+    w = mo.bf16_round(rng.standard_normal((N, K)).astype(np.float32) * 0.02)
+    dx, dw = torch.from_numpy(x).bfloat16().cuda(), torch.from_numpy(w).bfloat16().cuda()
+    amax = torch.zeros(2, dtype=torch.float32, device="cuda")
+    ctx.absmax(dx, M * K, amax[0:], stream=stream.cuda_stream)
+    ctx.absmax(dw, N * K, amax[1:], stream=stream.cuda_stream)
+    ctx.synchronize(stream.cuda_stream)
+    sx, sw = 448.0 / float(amax[0]), 448.0 / float(amax[1])
+    qx = torch.empty(M * K, dtype=torch.uint8, device="cuda")
+    qw = torch.empty(N * K, dtype=torch.uint8, device="cuda")
+    ctx.quantize_fp8(dx, M * K, sx, qx, stream=stream.cuda_stream)
+    ctx.quantize_fp8(dw, N * K, sw, qw, stream=stream.cuda_stream)
+    c = torch.empty(M, N, dtype=torch.bfloat16, device="cuda")
+    ctx.gemm(ctx.gemm_desc(qx, qw, c, M, N, K, transpose_b=True, ab_dtype=pkg.FP8_E4M3, alpha=1.0 / (sx * sw)),
+             stream.cuda_stream)
+    ctx.synchronize(stream.cuda_stream)
+    got = c.float().cpu().numpy()
+    assert mo.rel_frobenius(got, mo.matmul(x, w, False, True)) <= 6e-2
+    # and exactly what the oracle gives for those codes
+    ref = mo.matmul_e4m3(qx.cpu().numpy().reshape(M, K), qw.cpu().numpy().reshape(N, K), 1.0 / (sx * sw))
+    assert mo.rel_frobenius(got, ref) <= 1e-2

@@ -24,6 +24,25 @@ def test_bf16_round_matches_torch():
     np.testing.assert_array_equal(mo.from_bf16_bits(bits), ref)
 
 
+def test_e4m3_codec_matches_torch():
+    """Decode table, round-to-nearest-even on every midpoint, saturation: against torch's CPU float8_e4m3fn casts."""
+    torch = pytest.importorskip("torch")
+    table = mo.e4m3_table()
+    ref = torch.arange(256, dtype=torch.uint8).view(torch.float8_e4m3fn).float().numpy().astype(np.float64)
+    np.testing.assert_array_equal(np.isnan(table), np.isnan(ref))
+    np.testing.assert_array_equal(table[~np.isnan(table)], ref[~np.isnan(ref)])
+    rng = np.random.default_rng(3)
+    x = np.clip(rng.standard_normal(100000) * rng.choice([1e-3, 0.1, 1.0, 30.0, 200.0], 100000), -448, 448).astype(np.float32)
+    mids = np.array([(table[i] + table[i + 1]) / 2 for i in range(0x7E)], dtype=np.float32)
+    for v in (x, mids, -mids, np.array([0.0, -0.0, 448.0, -448.0, 2.0 ** -9, 2.0 ** -10], dtype=np.float32)):
+        want = torch.from_numpy(v).to(torch.float8_e4m3fn).view(torch.uint8).numpy()
+        np.testing.assert_array_equal(mo.quantize_e4m3(v), want)
+    np.testing.assert_array_equal(mo.quantize_e4m3(np.array([1e9, -1e9], dtype=np.float32)), [0x7E, 0xFE])
+    codes = mo.quantize_e4m3(x[:64 * 48].reshape(64, 48))
+    a = torch.from_numpy(codes).view(torch.float8_e4m3fn).double()
+    np.testing.assert_allclose(mo.matmul_e4m3(codes, codes[:32], 0.5), (0.5 * a @ a[:32].T).float().numpy(), rtol=1e-6)
+
+
 def test_known_answers_verify_autograd():
     """verify/verify_autograd.py and the C++ KATs (autograd/tests/test_matmul.cpp:22-34, test_softmax.cpp:25-35,
     test_relu.cpp, test_linear.cpp, test_sgd.cpp:57-70)."""

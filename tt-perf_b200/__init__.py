@@ -20,6 +20,7 @@ from .capi import (  # noqa: F401
     ALGO_TCGEN05,
     BF16,
     F32,
+    FP8_E4M3,
     HIFI2,
     HIFI3,
     HIFI4,
@@ -34,6 +35,6 @@ from .capi import (  # noqa: F401
 
 __all__ = [
     "capi", "dist", "nn", "tensor", "tp", "DeviceTensor", "lib", "lib_path", "Context", "GemmDesc", "B200Error",
-    "BF16", "F32", "U32", "ACT_NONE", "ACT_RELU", "ACT_GELU",
+    "BF16", "F32", "U32", "FP8_E4M3", "ACT_NONE", "ACT_RELU", "ACT_GELU",
     "LOFI", "HIFI2", "HIFI3", "HIFI4", "ALGO_AUTO", "ALGO_TCGEN05", "ALGO_SIMT",
 ]

@@ -9,7 +9,7 @@ import ctypes as C
 import os
 from pathlib import Path
 
-BF16, F32, U32 = 0, 1, 2
+BF16, F32, U32, FP8_E4M3 = 0, 1, 2, 3
 ACT_NONE, ACT_RELU, ACT_GELU = 0, 1, 2
 LOFI, HIFI2, HIFI3, HIFI4 = 0, 1, 2, 3
 ALGO_AUTO, ALGO_TCGEN05, ALGO_SIMT = 0, 1, 2
@@ -41,7 +41,7 @@ class GemmDesc(C.Structure):
         ("bias", C.c_void_p), ("bias_dtype", C.c_int32),
         ("activation", C.c_int32), ("alpha", C.c_float),
         ("causal_mask", C.c_int32), ("mask_value", C.c_float),
-        ("fidelity", C.c_int32), ("algo", C.c_int32), ("split_k", C.c_int32),
+        ("fidelity", C.c_int32), ("algo", C.c_int32), ("split_k", C.c_int32), ("ab_dtype", C.c_int32),
     ]
 
 
@@ -127,6 +127,8 @@ SIGNATURES = {
     "b200_binary": (C.c_int, [C.c_void_p, C.c_int, C.c_void_p, C.POINTER(C.c_int64), C.c_void_p, C.POINTER(C.c_int64),
                               C.c_void_p, C.c_void_p]),
     "b200_reduce": (C.c_int, [C.c_void_p, C.c_int, C.c_void_p, C.c_int64, C.c_int64, C.c_int64, C.c_void_p, C.c_void_p]),
+    "b200_absmax": (C.c_int, [C.c_void_p, C.c_void_p, C.c_int64, C.c_void_p, C.c_void_p]),
+    "b200_quantize_fp8": (C.c_int, [C.c_void_p, C.c_void_p, C.c_int64, C.c_float, C.c_void_p, C.c_void_p]),
     "b200_fill": (C.c_int, [C.c_void_p, C.c_void_p, C.c_int64, C.c_int, C.c_float, C.c_void_p]),
     "b200_cast": (C.c_int, [C.c_void_p, C.c_void_p, C.c_int, C.c_void_p, C.c_int, C.c_int64, C.c_void_p]),
     "b200_permute": (C.c_int, [C.c_void_p, C.c_void_p, C.POINTER(C.c_int64), C.POINTER(C.c_int32), C.c_void_p, C.c_void_p]),
@@ -256,8 +258,9 @@ class Context:
     def gemm_desc(self, A, B, Cout, M, N, K, *, transpose_a=False, transpose_b=False, lda=None, ldb=None, ldc=None,
                   batch=1, stride_a=None, stride_b=None, stride_c=None, c_dtype=BF16, bias=None, bias_dtype=BF16,
                   activation=ACT_NONE, alpha=1.0, causal_mask=False, mask_value=-1e9, fidelity=HIFI4,
-                  algo=ALGO_AUTO, split_k=0) -> GemmDesc:
-        """Descriptor for C = act(mask(alpha * op(A) @ op(B) + bias)); dense row-major defaults for ld/strides."""
+                  algo=ALGO_AUTO, split_k=0, ab_dtype=BF16) -> GemmDesc:
+        """Descriptor for C = act(mask(alpha * op(A) @ op(B) + bias)); dense row-major defaults for ld/strides.
+        ab_dtype=FP8_E4M3: A and B hold one-byte e4m3 values (A [M,K], B [N,K] with transpose_b=True)."""
         d = GemmDesc()
         lib().b200_gemm_desc_init(C.byref(d))
         d.transpose_a, d.transpose_b = int(bool(transpose_a)), int(bool(transpose_b))
@@ -275,7 +278,7 @@ class Context:
         d.bias, d.bias_dtype = ptr(bias) or None, bias_dtype
         d.activation, d.alpha = activation, alpha
         d.causal_mask, d.mask_value = int(bool(causal_mask)), mask_value
-        d.fidelity, d.algo, d.split_k = fidelity, algo, split_k
+        d.fidelity, d.algo, d.split_k, d.ab_dtype = fidelity, algo, split_k, ab_dtype
         return d
 
     def gemm(self, desc: GemmDesc, stream=None) -> None:
@@ -381,6 +384,14 @@ class Context:
 
     def reduce(self, op, x, outer, R, inner, y, *, stream=None):
         check(lib().b200_reduce(self._h, op, ptr(x), outer, R, inner, ptr(y), self._s(stream)))
+
+    def absmax(self, x, n, out_f32, *, stream=None):
+        """out_f32[0] = max |x| over n bf16 elements."""
+        check(lib().b200_absmax(self._h, ptr(x), n, ptr(out_f32), self._s(stream)))
+
+    def quantize_fp8(self, x, n, scale, y, *, stream=None):
+        """y[i] = e4m3(x[i] * scale), saturating; y holds n bytes."""
+        check(lib().b200_quantize_fp8(self._h, ptr(x), n, scale, ptr(y), self._s(stream)))
 
     def fill(self, dst, n, dtype, value, *, stream=None):
         check(lib().b200_fill(self._h, ptr(dst), n, dtype, value, self._s(stream)))

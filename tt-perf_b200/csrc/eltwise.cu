@@ -4,6 +4,8 @@
 #include "common.cuh"
 #include "gemm_common.cuh"
 
+#include <cuda_fp8.h>
+
 #include <algorithm>
 #include <cfloat>
 
@@ -27,6 +29,51 @@ __device__ __forceinline__ void unpack8(const uint4& u, float (&f)[8]) {
 }
 __device__ __forceinline__ uint4 pack8(const float (&f)[8]) {
     return make_uint4(pack_bf16x2(f[0], f[1]), pack_bf16x2(f[2], f[3]), pack_bf16x2(f[4], f[5]), pack_bf16x2(f[6], f[7]));
+}
+
+// ---- 8-bit (e4m3) operands for the matmul ----------------------------------------------------------------
+// max |x|: 16-byte loads, warp shuffle, one atomicMax per warp (non-negative floats order like their bit patterns).
+__global__ void absmax_kernel(const __nv_bfloat16* __restrict__ x, long long n, float* __restrict__ out, int vec_ok) {
+    float m = 0.0f;
+    const long long tid = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x;
+    const long long nthreads = static_cast<long long>(gridDim.x) * blockDim.x;
+    const long long nvec = vec_ok ? n / 8 : 0;
+    const uint4* xv = reinterpret_cast<const uint4*>(x);
+    for (long long i = tid; i < nvec; i += nthreads) {
+        float f[8];
+        unpack8(__ldg(xv + i), f);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) m = fmaxf(m, fabsf(f[j]));
+    }
+    for (long long i = nvec * 8 + tid; i < n; i += nthreads) m = fmaxf(m, fabsf(__bfloat162float(x[i])));
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, o));
+    if ((threadIdx.x & 31) == 0 && m > 0.0f) atomicMax(reinterpret_cast<int*>(out), __float_as_int(m));
+}
+
+__device__ __forceinline__ uint32_t pack_e4m3x4(float a, float b, float c, float d, float s) {
+    const uint32_t lo = __nv_cvt_float2_to_fp8x2(make_float2(a * s, b * s), __NV_SATFINITE, __NV_E4M3);
+    const uint32_t hi = __nv_cvt_float2_to_fp8x2(make_float2(c * s, d * s), __NV_SATFINITE, __NV_E4M3);
+    return lo | (hi << 16);
+}
+
+// y = e4m3(x * scale): two 16-byte loads (16 bf16) per 16-byte store.
+__global__ void quantize_e4m3_kernel(const __nv_bfloat16* __restrict__ x, long long n, float scale,
+                                     uint8_t* __restrict__ y, int vec_ok) {
+    const long long tid = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x;
+    const long long nthreads = static_cast<long long>(gridDim.x) * blockDim.x;
+    const long long nvec = vec_ok ? n / 16 : 0;
+    const uint4* xv = reinterpret_cast<const uint4*>(x);
+    uint4* yv = reinterpret_cast<uint4*>(y);
+    for (long long i = tid; i < nvec; i += nthreads) {
+        float a[8], b[8];
+        unpack8(__ldg(xv + 2 * i), a);
+        unpack8(__ldg(xv + 2 * i + 1), b);
+        yv[i] = make_uint4(pack_e4m3x4(a[0], a[1], a[2], a[3], scale), pack_e4m3x4(a[4], a[5], a[6], a[7], scale),
+                           pack_e4m3x4(b[0], b[1], b[2], b[3], scale), pack_e4m3x4(b[4], b[5], b[6], b[7], scale));
+    }
+    for (long long i = nvec * 16 + tid; i < n; i += nthreads)
+        y[i] = static_cast<uint8_t>(__nv_cvt_float_to_fp8(__bfloat162float(x[i]) * scale, __NV_SATFINITE, __NV_E4M3));
 }
 
 // ---- unary / scalar ops ------------------------------------------------------------------------------
@@ -780,6 +827,34 @@ int b200_reduce(b200_ctx* ctx, int op, const void* x, int64_t outer, int64_t R, 
     else
         reduce_cols_kernel<1><<<grid, kThreads, 0, s>>>(static_cast<const __nv_bfloat16*>(x), acc, R, inner, op, rows_per);
     cast_f32_to_bf16_kernel<<<grid_for(ctx, outs), kThreads, 0, s>>>(acc, static_cast<__nv_bfloat16*>(y), outs, scale);
+    B200_CUDA_TRY(cudaGetLastError());
+    return B200_OK;
+}
+
+int b200_absmax(b200_ctx* ctx, const void* x, int64_t n, float* out, void* stream) {
+    B200_REQUIRE(ctx != nullptr, "b200_absmax: ctx is NULL");
+    B200_REQUIRE(n >= 0, "b200_absmax: negative size");
+    B200_REQUIRE(out != nullptr && (n == 0 || x != nullptr), "b200_absmax: NULL buffer");
+    DeviceScope scope(ctx->device);
+    cudaStream_t s = ctx->pick(stream);
+    B200_CUDA_TRY(cudaMemsetAsync(out, 0, sizeof(float), s));
+    if (n == 0) return B200_OK;
+    const int vec_ok = (reinterpret_cast<uintptr_t>(x) & 15u) == 0;
+    absmax_kernel<<<grid_for(ctx, (n + 15) / 16), kThreads, 0, s>>>(static_cast<const __nv_bfloat16*>(x), n, out, vec_ok);
+    B200_CUDA_TRY(cudaGetLastError());
+    return B200_OK;
+}
+
+int b200_quantize_fp8(b200_ctx* ctx, const void* x, int64_t n, float scale, void* y, void* stream) {
+    B200_REQUIRE(ctx != nullptr, "b200_quantize_fp8: ctx is NULL");
+    B200_REQUIRE(n >= 0, "b200_quantize_fp8: negative size");
+    if (n == 0) return B200_OK;
+    B200_REQUIRE(x && y, "b200_quantize_fp8: NULL buffer");
+    B200_REQUIRE(scale > 0.0f && scale <= FLT_MAX, "b200_quantize_fp8: scale must be positive and finite");
+    DeviceScope scope(ctx->device);
+    const int vec_ok = ((reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(y)) & 15u) == 0;
+    quantize_e4m3_kernel<<<grid_for(ctx, (n + 15) / 16), kThreads, 0, ctx->pick(stream)>>>(
+        static_cast<const __nv_bfloat16*>(x), n, scale, static_cast<uint8_t*>(y), vec_ok);
     B200_CUDA_TRY(cudaGetLastError());
     return B200_OK;
 }

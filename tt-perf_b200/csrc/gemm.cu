@@ -38,6 +38,7 @@ int validate(const b200_gemm_desc* d) {
     B200_REQUIRE(d->fidelity >= B200_LOFI && d->fidelity <= B200_HIFI4, "b200_gemm: unknown fidelity %d", d->fidelity);
     B200_REQUIRE(d->algo >= B200_GEMM_AUTO && d->algo <= B200_GEMM_SIMT, "b200_gemm: unknown algo %d", d->algo);
     B200_REQUIRE(d->split_k >= 0, "b200_gemm: split_k must be >= 0");
+    B200_REQUIRE(d->ab_dtype == B200_BF16 || d->ab_dtype == B200_FP8_E4M3, "b200_gemm: ab_dtype must be BF16 or FP8_E4M3");
     if (d->M == 0 || d->N == 0) return B200_OK;
     B200_REQUIRE(d->C != nullptr, "b200_gemm: C is NULL");
     B200_REQUIRE(d->ldc >= d->N, "b200_gemm: ldc (%lld) < N (%lld)", (long long)d->ldc, (long long)d->N);
@@ -83,6 +84,7 @@ void b200_gemm_desc_init(b200_gemm_desc* d) {
     d->fidelity = B200_HIFI4;
     d->algo = B200_GEMM_AUTO;
     d->split_k = 0;
+    d->ab_dtype = B200_BF16;
 }
 
 int b200_gemm_scratch_bytes(b200_ctx* ctx, const b200_gemm_desc* d, size_t* out_bytes) {
@@ -130,6 +132,10 @@ int b200_gemm(b200_ctx* ctx, const b200_gemm_desc* d, void* stream_v) {
     const bool eligible = gemm_tcgen05_eligible(*d, &why);
     if (d->algo == B200_GEMM_TCGEN05 && !eligible)
         return fail(B200_ERR_INVALID_ARG, "b200_gemm: tcgen05 path requested but %s", why);
+    if (d->ab_dtype == B200_FP8_E4M3) {  // tensor cores only: there is no scalar kernel for 8-bit operands
+        B200_REQUIRE(d->algo != B200_GEMM_SIMT, "b200_gemm: 8-bit operands run on the tcgen05 path only");
+        if (!eligible) return fail(B200_ERR_INVALID_ARG, "b200_gemm: 8-bit operands: %s", why);
+    }
     if (d->algo == B200_GEMM_SIMT || !eligible) return launch_gemm_simt(ctx, *d, stream);
     GemmPlan plan = gemm_plan(ctx, *d, pair_kernel_enabled() && gemm_tuned_block_n() == 0);
     {

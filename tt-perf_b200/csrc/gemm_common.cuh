@@ -177,6 +177,8 @@ struct GemmPlan {
     int splits;
 };
 GemmPlan gemm_plan(const b200_ctx* ctx, const b200_gemm_desc& d, bool allow_pair);
+// Elements of K one pipeline stage (128 bytes per row) holds: 64 bf16 or 128 e4m3.
+inline int gemm_bk_elems(const b200_gemm_desc& d) { return d.ab_dtype == B200_FP8_E4M3 ? 128 : 64; }
 int launch_gemm_simt(b200_ctx* ctx, const b200_gemm_desc& d, cudaStream_t stream);
 bool gemm_tcgen05_eligible(const b200_gemm_desc& d, const char** why);
 // Chooses the K-slice count for the tcgen05 path (1 = no split).

@@ -74,12 +74,17 @@ __device__ __forceinline__ WorkItem decode_work(const GemmParams& p, int w, int 
     return it;
 }
 
-template <int BN, bool A_KMAJOR, bool B_KMAJOR>
+// FP8: A and B hold one-byte e4m3 elements. A stage is the same 128 bytes of K per row (128 elements instead of 64),
+// the 32-byte step between MMA K slices is the same (32 elements instead of 16); only the TMA K coordinate, the
+// instruction kind and its descriptor differ. 8-bit operands exist K-major only.
+template <int BN, bool A_KMAJOR, bool B_KMAJOR, bool FP8 = false>
 __global__ void __launch_bounds__(NUM_THREADS, 1)
 gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
                     const __grid_constant__ CMaps tmC, const GemmParams p) {
     using Cfg = TileCfg<BN>;
     constexpr int STAGES = Cfg::STAGES;
+    static_assert(!FP8 || (A_KMAJOR && B_KMAJOR), "8-bit operands are K-major only");
+    constexpr int KB_ELEMS = FP8 ? 2 * BK : BK;  // elements of K per stage
 
     extern __shared__ uint8_t smem_raw[];
     // 128-byte-swizzled tiles must start on a 1024-byte boundary.
@@ -138,14 +143,14 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
                     uint8_t* sB = sA + Cfg::A_BYTES;
                     mbar_arrive_expect_tx(&full_bar[stage], Cfg::STAGE_BYTES);
                     if (A_KMAJOR) {
-                        tma_load_3d(sA, &tmA, &full_bar[stage], kb * BK, it.m0, ab);
+                        tma_load_3d(sA, &tmA, &full_bar[stage], kb * KB_ELEMS, it.m0, ab);
                     } else {
 #pragma unroll
                         for (int j = 0; j < BM / 64; ++j)
                             tma_load_3d(sA + j * (64 * BK * 2), &tmA, &full_bar[stage], it.m0 + 64 * j, kb * BK, ab);
                     }
                     if (B_KMAJOR) {
-                        tma_load_3d(sB, &tmB, &full_bar[stage], kb * BK, it.n0, bb);
+                        tma_load_3d(sB, &tmB, &full_bar[stage], kb * KB_ELEMS, it.n0, bb);
                     } else {
 #pragma unroll
                         for (int j = 0; j < BN / 64; ++j)
@@ -172,7 +177,8 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
     } else if (warp == 1) {
         // ------------------------------------------------------------------ MMA issuer
         if (lane == 0) {
-            constexpr uint32_t idesc = make_idesc_bf16_f32(BM, BN, A_KMAJOR ? 0u : 1u, B_KMAJOR ? 0u : 1u);
+            constexpr uint32_t idesc = FP8 ? make_idesc_e4m3_f32(BM, BN)
+                                           : make_idesc_bf16_f32(BM, BN, A_KMAJOR ? 0u : 1u, B_KMAJOR ? 0u : 1u);
             // Byte step between consecutive 16-deep K slices inside a stage, and the descriptor strides.
             constexpr uint32_t A_KSTEP = A_KMAJOR ? (UMMA_K * 2) : (UMMA_K * 128);
             constexpr uint32_t B_KSTEP = B_KMAJOR ? (UMMA_K * 2) : (UMMA_K * 128);
@@ -204,7 +210,10 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
                     for (int k = 0; k < BK / UMMA_K; ++k) {
                         const uint64_t da = make_smem_desc_sw128(a_addr + k * A_KSTEP, A_LBO, 1024);
                         const uint64_t db = make_smem_desc_sw128(b_addr + k * B_KSTEP, B_LBO, 1024);
-                        umma_f16_ss(d_tmem, da, db, idesc, (kb > it.kb_begin || k > 0) ? 1u : 0u);
+                        if (FP8)
+                            umma_f8_ss(d_tmem, da, db, idesc, (kb > it.kb_begin || k > 0) ? 1u : 0u);
+                        else
+                            umma_f16_ss(d_tmem, da, db, idesc, (kb > it.kb_begin || k > 0) ? 1u : 0u);
                     }
                     umma_commit(&empty_bar[stage]);  // frees the stage once these MMAs have read it
                     if (++stage == STAGES) {
@@ -451,8 +460,8 @@ __global__ void splitk_reduce_kernel(const GemmParams p) {
 // 3-D tensor map {inner, rows, batch} over a bf16 matrix with a 128-byte-swizzled box.
 int make_tensor_map(b200_ctx* ctx, CUtensorMap* out, const void* base, uint64_t inner, uint64_t rows, uint64_t batch,
                     uint64_t ld_elems, uint64_t batch_stride_elems, uint32_t box_inner, uint32_t box_rows,
-                    bool f32 = false) {
-    const uint64_t es = f32 ? 4 : 2;
+                    bool f32 = false, bool u8 = false) {
+    const uint64_t es = u8 ? 1 : (f32 ? 4 : 2);
     cuuint64_t dims[3] = {inner, rows, batch};
     if (batch <= 1 || batch_stride_elems == 0) {
         dims[2] = 1;
@@ -461,7 +470,7 @@ int make_tensor_map(b200_ctx* ctx, CUtensorMap* out, const void* base, uint64_t 
     cuuint64_t strides[2] = {ld_elems * es, batch_stride_elems * es};
     cuuint32_t box[3] = {box_inner, box_rows, 1};
     cuuint32_t estr[3] = {1, 1, 1};
-    CUresult r = ctx->encode_tiled(out, f32 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT32 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, const_cast<void*>(base), dims, strides, box,
+    CUresult r = ctx->encode_tiled(out, u8 ? CU_TENSOR_MAP_DATA_TYPE_UINT8 : f32 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT32 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, const_cast<void*>(base), dims, strides, box,
                                    estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
                                    CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
     if (r != CUDA_SUCCESS) {
@@ -474,11 +483,11 @@ int make_tensor_map(b200_ctx* ctx, CUtensorMap* out, const void* base, uint64_t 
     return B200_OK;
 }
 
-template <int BN, bool A_KMAJOR, bool B_KMAJOR>
+template <int BN, bool A_KMAJOR, bool B_KMAJOR, bool FP8 = false>
 int launch_variant(const CUtensorMap& tmA, const CUtensorMap& tmB, const CMaps& tmC, const GemmParams& p, int grid,
                    cudaStream_t stream) {
     using Cfg = TileCfg<BN>;
-    auto kernel = gemm_tcgen05_kernel<BN, A_KMAJOR, B_KMAJOR>;
+    auto kernel = gemm_tcgen05_kernel<BN, A_KMAJOR, B_KMAJOR, FP8>;
     static bool configured[64] = {};  // per template instance and device: the attribute is per device function
     int dev = 0;
     B200_CUDA_TRY(cudaGetDevice(&dev));
@@ -492,8 +501,9 @@ int launch_variant(const CUtensorMap& tmA, const CUtensorMap& tmB, const CMaps& 
 }
 
 template <int BN>
-int launch_bn(bool a_kmajor, bool b_kmajor, const CUtensorMap& tmA, const CUtensorMap& tmB, const CMaps& tmC,
+int launch_bn(bool a_kmajor, bool b_kmajor, bool fp8, const CUtensorMap& tmA, const CUtensorMap& tmB, const CMaps& tmC,
               const GemmParams& p, int grid, cudaStream_t stream) {
+    if (fp8) return launch_variant<BN, true, true, true>(tmA, tmB, tmC, p, grid, stream);
     if (a_kmajor && b_kmajor) return launch_variant<BN, true, true>(tmA, tmB, tmC, p, grid, stream);
     if (a_kmajor && !b_kmajor) return launch_variant<BN, true, false>(tmA, tmB, tmC, p, grid, stream);
     if (!a_kmajor && b_kmajor) return launch_variant<BN, false, true>(tmA, tmB, tmC, p, grid, stream);
@@ -506,12 +516,17 @@ inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 
 
 bool gemm_tcgen05_eligible(const b200_gemm_desc& d, const char** why) {
     const char* w = nullptr;
+    const bool fp8 = d.ab_dtype == B200_FP8_E4M3;
+    const int64_t mask = fp8 ? 15 : 7;  // 16 bytes
     if (!aligned16(d.A) || !aligned16(d.B))
         w = "A and B must be 16-byte aligned";
-    else if ((d.lda & 7) || (d.ldb & 7))
-        w = "lda and ldb must be multiples of 8 elements";
-    else if (d.batch > 1 && ((d.stride_a & 7) || (d.stride_b & 7)))
-        w = "batch strides of A and B must be multiples of 8 elements";
+    else if ((d.lda & mask) || (d.ldb & mask))
+        w = fp8 ? "lda and ldb must be multiples of 16 elements" : "lda and ldb must be multiples of 8 elements";
+    else if (d.batch > 1 && ((d.stride_a & mask) || (d.stride_b & mask)))
+        w = fp8 ? "batch strides of A and B must be multiples of 16 elements"
+                : "batch strides of A and B must be multiples of 8 elements";
+    else if (fp8 && (d.transpose_a != 0 || d.transpose_b == 0))
+        w = "8-bit operands need transpose_a = 0 and transpose_b = 1";
     else if (d.M >= (1ll << 31) || d.N >= (1ll << 31) || d.K >= (1ll << 31) || d.batch >= (1ll << 31))
         w = "dimension too large";
     if (why) *why = w;
@@ -560,7 +575,8 @@ int split_candidates(const b200_gemm_desc& d, long long tiles, long long slots, 
 //              launch, but one CTA reads every other slice of its tile, so the charge grows with the slice count and
 //              two or three slices is where it pays.
 GemmPlan gemm_plan(const b200_ctx* ctx, const b200_gemm_desc& d, bool allow_pair) {
-    const int num_kb = static_cast<int>((d.K + BK - 1) / BK);
+    const int bk = gemm_bk_elems(d);
+    const int num_kb = static_cast<int>((d.K + bk - 1) / bk);
     const double out_elems = static_cast<double>(d.batch) * d.M * d.N;
     GemmPlan best{false, 256, 1};
     double best_cost = 0.0;
@@ -640,6 +656,8 @@ int launch_gemm_tcgen05(b200_ctx* ctx, const b200_gemm_desc& d, int k_splits, cu
     b200_gemm_desc planned = d;
     planned.split_k = k_splits;  // the tile width that suits the slice count the caller settled on
     const int bn = gemm_choose_block_n(ctx, planned);
+    const bool fp8 = d.ab_dtype == B200_FP8_E4M3;
+    const int bk = gemm_bk_elems(d);
 
     GemmParams p{};
     p.M = static_cast<int>(d.M);
@@ -648,7 +666,7 @@ int launch_gemm_tcgen05(b200_ctx* ctx, const b200_gemm_desc& d, int k_splits, cu
     p.batch = static_cast<int>(d.batch);
     p.num_m_tiles = (p.M + BM - 1) / BM;
     p.num_n_tiles = (p.N + bn - 1) / bn;
-    p.num_kb = (p.K + BK - 1) / BK;
+    p.num_kb = (p.K + bk - 1) / bk;
     p.k_splits = k_splits;
     p.kb_per_split = (p.num_kb + k_splits - 1) / k_splits;
     const long long total = static_cast<long long>(k_splits) * p.batch * p.num_m_tiles * p.num_n_tiles;
@@ -686,12 +704,12 @@ int launch_gemm_tcgen05(b200_ctx* ctx, const b200_gemm_desc& d, int k_splits, cu
     CUtensorMap tmA, tmB;
     int rc;
     if (a_kmajor)
-        rc = make_tensor_map(ctx, &tmA, d.A, d.K, d.M, d.batch, d.lda, d.stride_a, BK, BM);
+        rc = make_tensor_map(ctx, &tmA, d.A, d.K, d.M, d.batch, d.lda, d.stride_a, bk, BM, false, fp8);
     else
         rc = make_tensor_map(ctx, &tmA, d.A, d.M, d.K, d.batch, d.lda, d.stride_a, 64, BK);
     if (rc != B200_OK) return rc;
     if (b_kmajor)
-        rc = make_tensor_map(ctx, &tmB, d.B, d.K, d.N, d.batch, d.ldb, d.stride_b, BK, bn);
+        rc = make_tensor_map(ctx, &tmB, d.B, d.K, d.N, d.batch, d.ldb, d.stride_b, bk, bn, false, fp8);
     else
         rc = make_tensor_map(ctx, &tmB, d.B, d.N, d.K, d.batch, d.ldb, d.stride_b, 64, BK);
     if (rc != B200_OK) return rc;
@@ -728,13 +746,13 @@ int launch_gemm_tcgen05(b200_ctx* ctx, const b200_gemm_desc& d, int k_splits, cu
 
     const int grid = min(p.total_work, ctx->sm_count);
     if (bn == 256)
-        rc = launch_bn<256>(a_kmajor, b_kmajor, tmA, tmB, tmC, p, grid, stream);
+        rc = launch_bn<256>(a_kmajor, b_kmajor, fp8, tmA, tmB, tmC, p, grid, stream);
     else if (bn == 192)
-        rc = launch_bn<192>(a_kmajor, b_kmajor, tmA, tmB, tmC, p, grid, stream);
+        rc = launch_bn<192>(a_kmajor, b_kmajor, fp8, tmA, tmB, tmC, p, grid, stream);
     else if (bn == 128)
-        rc = launch_bn<128>(a_kmajor, b_kmajor, tmA, tmB, tmC, p, grid, stream);
+        rc = launch_bn<128>(a_kmajor, b_kmajor, fp8, tmA, tmB, tmC, p, grid, stream);
     else
-        rc = launch_bn<64>(a_kmajor, b_kmajor, tmA, tmB, tmC, p, grid, stream);
+        rc = launch_bn<64>(a_kmajor, b_kmajor, fp8, tmA, tmB, tmC, p, grid, stream);
     if (rc != B200_OK) return rc;
 
     if (k_splits > 1) {

@@ -81,10 +81,13 @@ __device__ __forceinline__ bool epilogue_warps_all(bool pred) {
     return out != 0;
 }
 
-template <bool A_KMAJOR, bool B_KMAJOR>
+// FP8: one-byte e4m3 operands, K-major only; a stage holds 128 elements of K per row in the same 128 bytes.
+template <bool A_KMAJOR, bool B_KMAJOR, bool FP8 = false>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(NUM_THREADS, 1)
 gemm_tcgen05_2cta_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
                          const __grid_constant__ CMaps tmC, const GemmParams p, const int tmem_cols) {
+    static_assert(!FP8 || (A_KMAJOR && B_KMAJOR), "8-bit operands are K-major only");
+    constexpr int KB_ELEMS = FP8 ? 2 * BK : BK;
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
     uint8_t* epi_smem = smem + STAGES * STAGE_BYTES;
@@ -151,14 +154,14 @@ gemm_tcgen05_2cta_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_c
                     const uint32_t full_leader = mapa_shared(smem_u32(&full_bar[stage]), 0);
                     if (rank == 0) mbar_arrive_expect_tx(&full_bar[stage], 2 * STAGE_BYTES);
                     if (A_KMAJOR) {
-                        tma_load_3d_pair(sA, &tmA, full_leader, kb * BK, m_cta, ab);
+                        tma_load_3d_pair(sA, &tmA, full_leader, kb * KB_ELEMS, m_cta, ab);
                     } else {
 #pragma unroll
                         for (int j = 0; j < BM_CTA / 64; ++j)
                             tma_load_3d_pair(sA + j * (64 * BK * 2), &tmA, full_leader, m_cta + 64 * j, kb * BK, ab);
                     }
                     if (B_KMAJOR) {
-                        tma_load_3d_pair(sB, &tmB, full_leader, kb * BK, n_cta, bb);
+                        tma_load_3d_pair(sB, &tmB, full_leader, kb * KB_ELEMS, n_cta, bb);
                     } else {
 #pragma unroll
                         for (int j = 0; j < BN_CTA / 64; ++j)
@@ -185,7 +188,8 @@ gemm_tcgen05_2cta_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_c
     } else if (warp == 1) {
         // ------------------------------------------------------------------ MMA issuer (leader CTA only)
         if (lane == 0 && rank == 0) {
-            constexpr uint32_t idesc = make_idesc_bf16_f32(BM_PAIR, BN, A_KMAJOR ? 0u : 1u, B_KMAJOR ? 0u : 1u);
+            constexpr uint32_t idesc = FP8 ? make_idesc_e4m3_f32(BM_PAIR, BN)
+                                           : make_idesc_bf16_f32(BM_PAIR, BN, A_KMAJOR ? 0u : 1u, B_KMAJOR ? 0u : 1u);
             constexpr uint32_t A_KSTEP = A_KMAJOR ? (UMMA_K * 2) : (UMMA_K * 128);
             constexpr uint32_t B_KSTEP = B_KMAJOR ? (UMMA_K * 2) : (UMMA_K * 128);
             constexpr uint32_t A_LBO = A_KMAJOR ? 0u : (BK * 128);
@@ -216,7 +220,10 @@ gemm_tcgen05_2cta_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_c
                     for (int k = 0; k < BK / UMMA_K; ++k) {
                         const uint64_t da = make_smem_desc_sw128(a_addr + k * A_KSTEP, A_LBO, 1024);
                         const uint64_t db = make_smem_desc_sw128(b_addr + k * B_KSTEP, B_LBO, 1024);
-                        umma_f16_ss_pair(d_tmem, da, db, idesc, (kb > it.kb_begin || k > 0) ? 1u : 0u);
+                        if (FP8)
+                            umma_f8_ss_pair(d_tmem, da, db, idesc, (kb > it.kb_begin || k > 0) ? 1u : 0u);
+                        else
+                            umma_f16_ss_pair(d_tmem, da, db, idesc, (kb > it.kb_begin || k > 0) ? 1u : 0u);
                     }
                     umma_commit_pair(&empty_bar[stage], 3);  // frees the stage in both CTAs
                     if (++stage == STAGES) {
@@ -420,10 +427,10 @@ gemm_tcgen05_2cta_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_c
     }
 }
 
-template <bool A_KMAJOR, bool B_KMAJOR>
+template <bool A_KMAJOR, bool B_KMAJOR, bool FP8 = false>
 int launch_pair_variant(const CUtensorMap& tmA, const CUtensorMap& tmB, const CMaps& tmC, const GemmParams& p, int grid,
                         int tmem_cols, cudaStream_t stream) {
-    auto kernel = gemm_tcgen05_2cta_kernel<A_KMAJOR, B_KMAJOR>;
+    auto kernel = gemm_tcgen05_2cta_kernel<A_KMAJOR, B_KMAJOR, FP8>;
     static bool configured[64] = {};
     int dev = 0;
     B200_CUDA_TRY(cudaGetDevice(&dev));
@@ -437,8 +444,9 @@ int launch_pair_variant(const CUtensorMap& tmA, const CUtensorMap& tmB, const CM
 }
 
 int encode_map(b200_ctx* ctx, CUtensorMap* out, const void* base, uint64_t inner, uint64_t rows, uint64_t batch,
-               uint64_t ld_elems, uint64_t batch_stride_elems, uint32_t box_inner, uint32_t box_rows, bool f32) {
-    const uint64_t es = f32 ? 4 : 2;
+               uint64_t ld_elems, uint64_t batch_stride_elems, uint32_t box_inner, uint32_t box_rows, bool f32,
+               bool u8 = false) {
+    const uint64_t es = u8 ? 1 : (f32 ? 4 : 2);
     cuuint64_t dims[3] = {inner, rows, batch};
     if (batch <= 1 || batch_stride_elems == 0) {
         dims[2] = 1;
@@ -447,7 +455,7 @@ int encode_map(b200_ctx* ctx, CUtensorMap* out, const void* base, uint64_t inner
     cuuint64_t strides[2] = {ld_elems * es, batch_stride_elems * es};
     cuuint32_t box[3] = {box_inner, box_rows, 1};
     cuuint32_t estr[3] = {1, 1, 1};
-    CUresult r = ctx->encode_tiled(out, f32 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT32 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3,
+    CUresult r = ctx->encode_tiled(out, u8 ? CU_TENSOR_MAP_DATA_TYPE_UINT8 : f32 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT32 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3,
                                    const_cast<void*>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
                                    CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
                                    CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
@@ -510,6 +518,8 @@ int launch_gemm_tcgen05_pair(b200_ctx* ctx, const b200_gemm_desc& d, cudaStream_
                              int k_splits) {
     const bool a_kmajor = d.transpose_a == 0;
     const bool b_kmajor = d.transpose_b != 0;
+    const bool fp8 = d.ab_dtype == B200_FP8_E4M3;
+    const int bk = gemm_bk_elems(d);
     GemmParams p{};
     p.M = static_cast<int>(d.M);
     p.N = static_cast<int>(d.N);
@@ -517,7 +527,7 @@ int launch_gemm_tcgen05_pair(b200_ctx* ctx, const b200_gemm_desc& d, cudaStream_
     p.batch = static_cast<int>(d.batch);
     p.num_m_tiles = (p.M + BM_PAIR - 1) / BM_PAIR;
     p.num_n_tiles = (p.N + BN - 1) / BN;
-    p.num_kb = (p.K + BK - 1) / BK;
+    p.num_kb = (p.K + bk - 1) / bk;
     k_splits = std::max(1, std::min(k_splits, p.num_kb));
     p.kb_per_split = (p.num_kb + k_splits - 1) / k_splits;
     p.k_splits = (p.num_kb + p.kb_per_split - 1) / p.kb_per_split;  // every slice gets at least one K block
@@ -564,12 +574,12 @@ int launch_gemm_tcgen05_pair(b200_ctx* ctx, const b200_gemm_desc& d, cudaStream_
     memset(&tmC, 0, sizeof(tmC));
     int rc;
     if (a_kmajor)
-        rc = encode_map(ctx, &tmA, d.A, d.K, d.M, d.batch, d.lda, d.stride_a, BK, BM_CTA, false);
+        rc = encode_map(ctx, &tmA, d.A, d.K, d.M, d.batch, d.lda, d.stride_a, bk, BM_CTA, false, fp8);
     else
         rc = encode_map(ctx, &tmA, d.A, d.M, d.K, d.batch, d.lda, d.stride_a, 64, BK, false);
     if (rc != B200_OK) return rc;
     if (b_kmajor)
-        rc = encode_map(ctx, &tmB, d.B, d.K, d.N, d.batch, d.ldb, d.stride_b, BK, BN_CTA, false);
+        rc = encode_map(ctx, &tmB, d.B, d.K, d.N, d.batch, d.ldb, d.stride_b, bk, BN_CTA, false, fp8);
     else
         rc = encode_map(ctx, &tmB, d.B, d.N, d.K, d.batch, d.ldb, d.stride_b, 64, BK, false);
     if (rc != B200_OK) return rc;
@@ -591,6 +601,7 @@ int launch_gemm_tcgen05_pair(b200_ctx* ctx, const b200_gemm_desc& d, cudaStream_
     const int clusters = std::min(p.total_work, ctx->sm_count / 2);
     const int grid = 2 * clusters;
     const int cols = pair_tmem_cols();
+    if (fp8) return launch_pair_variant<true, true, true>(tmA, tmB, tmC, p, grid, cols, stream);
     if (a_kmajor && b_kmajor) return launch_pair_variant<true, true>(tmA, tmB, tmC, p, grid, cols, stream);
     if (a_kmajor && !b_kmajor) return launch_pair_variant<true, false>(tmA, tmB, tmC, p, grid, cols, stream);
     if (!a_kmajor && b_kmajor) return launch_pair_variant<false, true>(tmA, tmB, tmC, p, grid, cols, stream);

@@ -38,6 +38,7 @@ extern "C" int b200_matmul_host(b200_ctx* ctx, const b200_gemm_desc* d, int pane
     B200_REQUIRE(d->M > 0 && d->N > 0 && d->K > 0 && d->batch == 1, "b200_matmul_host: needs M, N, K > 0 and batch 1");
     B200_REQUIRE(d->A && d->B && d->C, "b200_matmul_host: A, B or C is NULL");
     B200_REQUIRE(d->c_dtype == B200_BF16 || d->c_dtype == B200_F32, "b200_matmul_host: bad c_dtype");
+    B200_REQUIRE(d->ab_dtype == B200_BF16, "b200_matmul_host: host operands are bf16");
     const int64_t a_rows = d->transpose_a ? d->K : d->M, a_cols = d->transpose_a ? d->M : d->K;
     const int64_t b_rows = d->transpose_b ? d->N : d->K, b_cols = d->transpose_b ? d->K : d->N;
     B200_REQUIRE(d->lda >= a_cols && d->ldb >= b_cols && d->ldc >= d->N, "b200_matmul_host: leading dimension too small");

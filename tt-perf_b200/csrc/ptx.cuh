@@ -169,6 +169,19 @@ __device__ __forceinline__ void umma_f16_ss(uint32_t tmem_d, uint64_t desc_a, ui
         : "memory");
 }
 
+// The same with 8-bit (e4m3 / e5m2) operands: 32 K-elements per instruction, fp32 accumulate.
+__device__ __forceinline__ void umma_f8_ss(uint32_t tmem_d, uint64_t desc_a, uint64_t desc_b, uint32_t idesc,
+                                           uint32_t accumulate) {
+    asm volatile(
+        "{\n\t"
+        ".reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f8f6f4 [%0], %1, %2, %3, p;\n\t"
+        "}\n" ::"r"(tmem_d),
+        "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate)
+        : "memory");
+}
+
 // The mbarrier receives one arrival once every tcgen05 operation issued so far by this
 // thread has completed. Implies tcgen05.fence::before_thread_sync.
 __device__ __forceinline__ void umma_commit(uint64_t* bar) {
@@ -256,6 +269,18 @@ __device__ __forceinline__ void umma_f16_ss_pair(uint32_t tmem_d, uint64_t desc_
         "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate)
         : "memory");
 }
+
+__device__ __forceinline__ void umma_f8_ss_pair(uint32_t tmem_d, uint64_t desc_a, uint64_t desc_b, uint32_t idesc,
+                                                 uint32_t accumulate) {
+    asm volatile(
+        "{\n\t"
+        ".reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::2.kind::f8f6f4 [%0], %1, %2, %3, p;\n\t"
+        "}\n" ::"r"(tmem_d),
+        "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate)
+        : "memory");
+}
 // One arrival on the barrier at the same shared-memory offset in every CTA of `cta_mask` once all tcgen05 operations
 // issued so far by this thread have completed.
 __device__ __forceinline__ void umma_commit_pair(uint64_t* bar, uint16_t cta_mask) {
@@ -294,6 +319,11 @@ __host__ __device__ constexpr uint32_t make_idesc_bf16_f32(uint32_t umma_m, uint
            | (b_mn_major << 16)      // B major
            | ((umma_n >> 3) << 17)   // N / 8
            | ((umma_m >> 4) << 24);  // M / 16
+}
+
+// Instruction descriptor for tcgen05.mma kind::f8f6f4 with e4m3 A/B (format code 0, K-major only) and fp32 D.
+__host__ __device__ constexpr uint32_t make_idesc_e4m3_f32(uint32_t umma_m, uint32_t umma_n) {
+    return (1u << 4) | ((umma_n >> 3) << 17) | ((umma_m >> 4) << 24);
 }
 
 }  // namespace ptx

@@ -60,8 +60,8 @@ def main() -> None:
     T16 = 16 * T
     cases = []
 
-    def case(name, nbytes, fn):
-        cases.append((name, nbytes, fn))
+    def case(name, nbytes, fn, flops=None):
+        cases.append((name, nbytes, fn, flops))
 
     rows = B * H * S
     x_s, y_s, d_s = rand((rows, S)), DT(ctx, (rows, S)), rand((rows, S), scale=0.01)
@@ -117,9 +117,27 @@ def main() -> None:
     case("attention_bwd causal [B8, H12, S1024, 64]", B * S * D * 2 * 8 + B * H * S * 4,
          lambda: ctx.attention_backward(op3[0], op3[1], op3[2], o_op, do_op, lse_a, dop3[0], dop3[1], dop3[2], B, H, S))
 
+    # 8-bit (e4m3) operands: quantisation kernels and the matmul beside its bf16 form (x . W^T, bf16 output)
+    q8 = DT(ctx, (T16 * D // 4,), pkg.U32)
+    amax = DT(ctx, (1,), pkg.F32)
+    case("absmax [16T, 768]", T16 * D * 2, lambda: ctx.absmax(xl, T16 * D, amax))
+    case("quantize_fp8 [16T, 768]", T16 * D * 3, lambda: ctx.quantize_fp8(xl, T16 * D, 2.0, q8))
+    for (gm, gn, gk) in ((8192, 8192, 8192), (4096, 4096, 4096), (8192, 3072, 768), (8192, 768, 3072)):
+        # random operands: a matmul of constants toggles few bits, draws less power and clocks higher than real data
+        a16 = DT.from_numpy(ctx, rng.standard_normal((gm, gk), dtype=np.float32))
+        b16 = DT.from_numpy(ctx, rng.standard_normal((gn, gk), dtype=np.float32))
+        c16 = DT(ctx, (gm, gn))
+        a8, b8 = DT(ctx, (gm * gk // 4,), pkg.U32), DT(ctx, (gn * gk // 4,), pkg.U32)
+        ctx.quantize_fp8(a16, gm * gk, 1.0, a8)
+        ctx.quantize_fp8(b16, gn * gk, 1.0, b8)
+        d16 = ctx.gemm_desc(a16, b16, c16, gm, gn, gk, transpose_b=True)
+        d8 = ctx.gemm_desc(a8, b8, c16, gm, gn, gk, transpose_b=True, ab_dtype=pkg.FP8_E4M3)
+        case(f"gemm bf16 x.W^T {gm}x{gn}x{gk}", (gm * gk + gn * gk + gm * gn) * 2, lambda d=d16: ctx.gemm(d), 2.0 * gm * gn * gk)
+        case(f"gemm fp8 e4m3 x.W^T {gm}x{gn}x{gk}", gm * gk + gn * gk + gm * gn * 2, lambda d=d8: ctx.gemm(d), 2.0 * gm * gn * gk)
+
     peak, peak_src = hbm_peak()
     results = []
-    for name, nbytes, fn in cases:
+    for name, nbytes, fn, flops in cases:
         if args.only and args.only not in name:
             continue
         for _ in range(3):
@@ -131,12 +149,15 @@ def main() -> None:
         ms = ctx.timer_stop(t) / args.iters
         gbs = nbytes / (ms * 1e-3) / 1e9
         results.append({"kernel": name, "ms": ms, "algorithmic_bytes": nbytes, "gb_per_s": gbs, "frac_of_hbm_peak": gbs / peak})
+        if flops:
+            results[-1]["tflops"] = flops / (ms * 1e-3) / 1e12
     if args.json:
         print(json.dumps({"hbm_peak_gbs": peak, "peak_source": peak_src, "results": results}))
     else:
         print(f"HBM peak {peak:.0f} GB/s ({peak_src})")
         for r in results:
-            print(f"{r['kernel']:58s} {r['ms']*1e3:9.1f} us  {r['gb_per_s']:8.0f} GB/s  {100*r['frac_of_hbm_peak']:5.1f} %")
+            tail = f"  {r['tflops']:7.0f} TFLOP/s" if "tflops" in r else ""
+            print(f"{r['kernel']:58s} {r['ms']*1e3:9.1f} us  {r['gb_per_s']:8.0f} GB/s  {100*r['frac_of_hbm_peak']:5.1f} %{tail}")
     ctx.close()
 
 
