@@ -140,3 +140,29 @@ def test_fp8_linear_close_to_the_bf16_product(pkg, ctx, stream):
     # and exactly what the oracle gives for those codes
     ref = mo.matmul_e4m3(qx.cpu().numpy().reshape(M, K), qw.cpu().numpy().reshape(N, K), 1.0 / (sx * sw))
     assert mo.rel_frobenius(got, ref) <= 1e-2
+
+
+def test_fp8_linear_layer_helpers(pkg, ctx):
+    """nn.quantize_fp8 + nn.linear_forward_fp8 on device tensors: codes equal the oracle's, the layer output equals
+    the oracle's product of those codes, and stays close to the bf16 Linear."""
+    nn, DT = pkg.nn, pkg.DeviceTensor
+    rng = np.random.default_rng(9)
+    B, S, D_in, D_out = 4, 96, 256, 384
+    x = mo.bf16_round(rng.standard_normal((B, S, D_in)).astype(np.float32))
+    w = mo.bf16_round(rng.standard_normal((D_out, D_in)).astype(np.float32) * 0.05)
+    bias = mo.bf16_round(rng.standard_normal(D_out).astype(np.float32) * 0.1)
+    dx, dw, db = DT.from_numpy(ctx, x), DT.from_numpy(ctx, w), DT.from_numpy(ctx, bias)
+    xq, sx = nn.quantize_fp8(ctx, dx)
+    wq, sw = nn.quantize_fp8(ctx, dw)
+    assert xq.shape == dx.shape and xq.nbytes == dx.numel
+    assert sx == 448.0 / float(np.abs(x).max()) and sw == 448.0 / float(np.abs(w).max())
+    np.testing.assert_array_equal(xq.numpy(), mo.quantize_e4m3(x, sx))
+    y = nn.linear_forward_fp8(ctx, xq, sx, wq, sw, db, "relu").numpy()
+    ref = mo.relu(mo.matmul_e4m3(xq.numpy().reshape(B * S, D_in), wq.numpy(), 1.0 / (sx * sw)) + bias).reshape(B, S, D_out)
+    assert mo.rel_frobenius(y, ref) <= 1e-2
+    y16 = nn.linear_forward(ctx, dx, dw, db, "relu").numpy()
+    assert mo.rel_frobenius(y, y16) <= 8e-2
+    # a caller-supplied scale keeps the call asynchronous and saturates what it does not cover
+    xq2, s2 = nn.quantize_fp8(ctx, dx, scale=1000.0)
+    assert s2 == 1000.0
+    np.testing.assert_array_equal(xq2.numpy(), mo.quantize_e4m3(x, 1000.0))

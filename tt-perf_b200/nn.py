@@ -12,7 +12,7 @@ from __future__ import annotations
 import math
 
 from . import capi
-from .capi import ACT_GELU, ACT_NONE, ACT_RELU, BF16, F32
+from .capi import ACT_GELU, ACT_NONE, ACT_RELU, BF16, F32, FP8_E4M3
 from .tensor import DeviceTensor
 
 _ACT = {None: ACT_NONE, "relu": ACT_RELU, "gelu": ACT_GELU}
@@ -52,6 +52,31 @@ def matmul(ctx, a: DeviceTensor, b: DeviceTensor, transpose_a=False, transpose_b
 def linear_forward(ctx, x, w, bias=None, activation=None, *, stream=None) -> DeviceTensor:
     """y = act(x . w^T + b); w is [out, in] (ttnn::linear(x, w, bias, false, true, ..., "relu"))."""
     return matmul(ctx, x, w, False, True, bias=bias, activation=activation, stream=stream)
+
+
+E4M3_MAX = 448.0
+
+
+def quantize_fp8(ctx, x: DeviceTensor, *, scale=None, stream=None):
+    """Returns (codes, scale): codes = e4m3(x * scale) as a one-byte-per-element tensor of x's shape.
+    scale=None picks 448 / max|x| (one reduction and a host read of its result, so not for use while a trace is
+    being recorded); a caller that tracks the range itself passes its scale and stays asynchronous."""
+    if scale is None:
+        amax = DeviceTensor(ctx, (1,), F32)
+        ctx.absmax(x, x.numel, amax, stream=stream)
+        peak = float(amax.numpy(stream)[0])
+        scale = E4M3_MAX / peak if peak > 0.0 else 1.0
+    q = DeviceTensor(ctx, x.shape, FP8_E4M3)
+    ctx.quantize_fp8(x, x.numel, scale, q, stream=stream)
+    return q, float(scale)
+
+
+def linear_forward_fp8(ctx, x_q, x_scale, w_q, w_scale, bias=None, activation=None, *, out_dtype=BF16, stream=None):
+    """y = act((x_q . w_q^T) / (x_scale * w_scale) + b) on 8-bit operands at twice the bf16 tensor rate; x_q [.., in] and
+    w_q [out, in] come from quantize_fp8. The reduced-precision Linear of the fidelity study
+    (verify/verify_fidelity.cpp:151-208) on this hardware's low-precision operand format."""
+    return matmul(ctx, x_q, w_q, False, True, bias=bias, activation=activation, out_dtype=out_dtype, stream=stream,
+                  alpha=1.0 / (x_scale * w_scale), ab_dtype=FP8_E4M3)
 
 
 def linear_backward(ctx, x, w, d_y, *, need_dx=True, need_db=True, stream=None):

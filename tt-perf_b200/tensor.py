@@ -12,9 +12,9 @@ import math
 import numpy as np
 
 from . import capi
-from .capi import BF16, F32, U32
+from .capi import BF16, F32, FP8_E4M3, U32
 
-_ITEMSIZE = {BF16: 2, F32: 4, U32: 4}
+_ITEMSIZE = {BF16: 2, F32: 4, U32: 4, FP8_E4M3: 1}
 
 
 def f32_to_bf16_bits(x: np.ndarray) -> np.ndarray:
@@ -65,6 +65,8 @@ class DeviceTensor:
             host = f32_to_bf16_bits(np.asarray(array, dtype=np.float32))
         elif self.dtype == F32:
             host = np.ascontiguousarray(array, dtype=np.float32)
+        elif self.dtype == FP8_E4M3:
+            host = np.ascontiguousarray(array, dtype=np.uint8)  # e4m3 codes, one byte each
         else:
             host = np.ascontiguousarray(array, dtype=np.uint32)
         if host.size != self.numel:
@@ -73,11 +75,13 @@ class DeviceTensor:
         self.ctx.synchronize(stream)  # `host` may be a temporary
 
     def numpy(self, stream=None) -> np.ndarray:
-        """Device -> host; bf16 is widened to fp32."""
+        """Device -> host; bf16 is widened to fp32, e4m3 comes back as its one-byte codes."""
         if self.dtype == BF16:
             host = np.empty(self.numel, dtype=np.uint16)
         elif self.dtype == F32:
             host = np.empty(self.numel, dtype=np.float32)
+        elif self.dtype == FP8_E4M3:
+            host = np.empty(self.numel, dtype=np.uint8)
         else:
             host = np.empty(self.numel, dtype=np.uint32)
         if self.numel:
@@ -115,4 +119,4 @@ class DeviceTensor:
             pass
 
     def __repr__(self):
-        return f"DeviceTensor(shape={self.shape}, dtype={('bf16', 'f32', 'u32')[self.dtype]}, ptr=0x{self.ptr:x})"
+        return f"DeviceTensor(shape={self.shape}, dtype={('bf16', 'f32', 'u32', 'e4m3')[self.dtype]}, ptr=0x{self.ptr:x})"
