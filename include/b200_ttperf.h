@@ -283,6 +283,10 @@ int b200_reduce(b200_ctx* ctx, int op, const void* x, int64_t outer, int64_t R, 
  * b200_quantize_fp8: y[i] = e4m3(x[i] * scale), saturating at +-448; a caller picks scale = 448 / absmax. */
 int b200_absmax(b200_ctx* ctx, const void* x_bf16, int64_t n, float* out_f32, void* stream);
 int b200_quantize_fp8(b200_ctx* ctx, const void* x_bf16, int64_t n, float scale, void* y_fp8, void* stream);
+/* y[c * ldy + r] = e4m3(x[r * ldx + c] * scale) for a [rows, cols] bf16 matrix: the transposed 8-bit copy that the
+ * dX (NN) and dW (TN) products of a Linear need, because 8-bit operands are read K-major only. */
+int b200_quantize_fp8_transposed(b200_ctx* ctx, const void* x_bf16, int64_t rows, int64_t cols, int64_t ldx, float scale,
+                                 void* y_fp8, int64_t ldy, void* stream);
 /* Creation and conversion (ttnn::zeros / ones / full / full_like, traced/nn.hpp:30-52). `value` is converted to dtype. */
 int b200_fill(b200_ctx* ctx, void* dst, int64_t n, int dtype, float value, void* stream);
 int b200_cast(b200_ctx* ctx, const void* src, int src_dtype, void* dst, int dst_dtype, int64_t n, void* stream);

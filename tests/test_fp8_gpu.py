@@ -166,3 +166,59 @@ def test_fp8_linear_layer_helpers(pkg, ctx):
     xq2, s2 = nn.quantize_fp8(ctx, dx, scale=1000.0)
     assert s2 == 1000.0
     np.testing.assert_array_equal(xq2.numpy(), mo.quantize_e4m3(x, 1000.0))
+
+
+@pytest.mark.parametrize("rows,cols,off", [(64, 64, 0), (512, 768, 0), (200, 136, 0), (67, 33, 0), (1, 5, 0), (130, 70, 1)])
+def test_transposed_quantiser_is_bit_exact(pkg, ctx, stream, rows, cols, off):
+    rng = np.random.default_rng(rows * 1000 + cols)
+    ld = cols + 6 + off                      # padded rows; an odd pitch takes the scalar load path
+    x = mo.bf16_round((rng.standard_normal((rows, ld)) * 3.0).astype(np.float32))
+    dx = torch.from_numpy(x).bfloat16().cuda()
+    ldy = rows + (4 - rows % 4) % 4 + 4 * off + off   # off: a pitch the 4-byte stores cannot use
+    y = torch.full((cols + 1, ldy), 0xAB, dtype=torch.uint8, device="cuda")
+    ctx.quantize_fp8_transposed(dx, rows, cols, 7.5, y, ldx=ld, ldy=ldy, stream=stream.cuda_stream)
+    ctx.synchronize(stream.cuda_stream)
+    got = y.cpu().numpy()
+    np.testing.assert_array_equal(got[:cols, :rows], mo.quantize_e4m3(x[:, :cols], 7.5).T)
+    assert (got[:cols, rows:] == 0xAB).all() and (got[cols:] == 0xAB).all(), "wrote outside the matrix"
+
+
+def test_fp8_linear_backward_products_through_transposed_copies(pkg, ctx):
+    """dX = dY . W and dW = dY^T . X on 8-bit operands: each reads a transposed quantised copy as its K-major B (and A)."""
+    nn, DT = pkg.nn, pkg.DeviceTensor
+    rng = np.random.default_rng(13)
+    T, D_in, D_out = 384, 256, 320
+    x = mo.bf16_round(rng.standard_normal((T, D_in)).astype(np.float32))
+    w = mo.bf16_round(rng.standard_normal((D_out, D_in)).astype(np.float32) * 0.05)
+    dy = mo.bf16_round(rng.standard_normal((T, D_out)).astype(np.float32) * 0.01)
+    dx_, dw_, ddy = DT.from_numpy(ctx, x), DT.from_numpy(ctx, w), DT.from_numpy(ctx, dy)
+    dyq, sdy = nn.quantize_fp8(ctx, ddy)
+    wtq, sw = nn.quantize_fp8(ctx, dw_, transposed=True)         # [in, out]
+    dytq, _ = nn.quantize_fp8(ctx, ddy, scale=sdy, transposed=True)  # [out, T]
+    xtq, sx = nn.quantize_fp8(ctx, dx_, transposed=True)         # [in, T]
+    assert wtq.shape == (D_in, D_out) and dytq.shape == (D_out, T) and xtq.shape == (D_in, T)
+    d_x = nn.linear_forward_fp8(ctx, dyq, sdy, wtq, sw, out_dtype=pkg.F32).numpy()
+    d_w = nn.linear_forward_fp8(ctx, dytq, sdy, xtq, sx, out_dtype=pkg.F32).numpy()
+    ref_dx = mo.matmul_e4m3(dyq.numpy(), wtq.numpy(), 1.0 / (sdy * sw))
+    ref_dw = mo.matmul_e4m3(dytq.numpy(), xtq.numpy(), 1.0 / (sdy * sx))
+    assert mo.rel_frobenius(d_x, ref_dx) <= 2e-6 and mo.rel_frobenius(d_w, ref_dw) <= 2e-6
+    assert mo.rel_frobenius(d_x, mo.matmul(dy, w)) <= 6e-2
+    assert mo.rel_frobenius(d_w, mo.matmul(dy, x, True, False)) <= 6e-2
+
+
+def test_fidelity_sweep_small(pkg, ctx):
+    """The operand-precision study at a small size: all levels learn, the bf16 levels agree closely, FP8 drifts
+    within what three mantissa bits allow; with constant tensors (the reference's setting) FP8 quantises exactly."""
+    from importlib import import_module
+    fs = import_module(pkg.__name__ + ".fidelity_sweep")
+    res = fs.run(pkg, ctx, "random", batch=128, dims=(512, 256, 128), lr=5.0, steps=5, warmup=1, timed=2, seed=3)
+    base = res["HiFi4"]["loss"]
+    assert base[-1] < base[0]
+    for level in ("HiFi2", "LoFi", "FP8"):
+        loss = res[level]["loss"]
+        assert loss[-1] < loss[0] and res[level]["ms_per_step"] > 0
+        tol = 0.08 if level == "FP8" else 0.02
+        assert all(abs(a - b) <= tol * abs(b) for a, b in zip(loss, base)), (level, loss, base)
+    const = fs.run(pkg, ctx, "constant", batch=64, dims=(512, 256, 128), lr=0.1, steps=3, warmup=1, timed=1,
+                   levels=("HiFi4", "FP8"))
+    assert all(abs(a - b) <= 0.02 * abs(b) for a, b in zip(const["FP8"]["loss"], const["HiFi4"]["loss"]))

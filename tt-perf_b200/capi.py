@@ -129,6 +129,8 @@ SIGNATURES = {
     "b200_reduce": (C.c_int, [C.c_void_p, C.c_int, C.c_void_p, C.c_int64, C.c_int64, C.c_int64, C.c_void_p, C.c_void_p]),
     "b200_absmax": (C.c_int, [C.c_void_p, C.c_void_p, C.c_int64, C.c_void_p, C.c_void_p]),
     "b200_quantize_fp8": (C.c_int, [C.c_void_p, C.c_void_p, C.c_int64, C.c_float, C.c_void_p, C.c_void_p]),
+    "b200_quantize_fp8_transposed": (C.c_int, [C.c_void_p, C.c_void_p, C.c_int64, C.c_int64, C.c_int64, C.c_float, C.c_void_p,
+                                               C.c_int64, C.c_void_p]),
     "b200_fill": (C.c_int, [C.c_void_p, C.c_void_p, C.c_int64, C.c_int, C.c_float, C.c_void_p]),
     "b200_cast": (C.c_int, [C.c_void_p, C.c_void_p, C.c_int, C.c_void_p, C.c_int, C.c_int64, C.c_void_p]),
     "b200_permute": (C.c_int, [C.c_void_p, C.c_void_p, C.POINTER(C.c_int64), C.POINTER(C.c_int32), C.c_void_p, C.c_void_p]),
@@ -392,6 +394,11 @@ class Context:
     def quantize_fp8(self, x, n, scale, y, *, stream=None):
         """y[i] = e4m3(x[i] * scale), saturating; y holds n bytes."""
         check(lib().b200_quantize_fp8(self._h, ptr(x), n, scale, ptr(y), self._s(stream)))
+
+    def quantize_fp8_transposed(self, x, rows, cols, scale, y, *, ldx=None, ldy=None, stream=None):
+        """y[c, r] = e4m3(x[r, c] * scale) for a [rows, cols] bf16 matrix; y is [cols, rows] bytes."""
+        check(lib().b200_quantize_fp8_transposed(self._h, ptr(x), rows, cols, cols if ldx is None else ldx, scale, ptr(y),
+                                                 rows if ldy is None else ldy, self._s(stream)))
 
     def fill(self, dst, n, dtype, value, *, stream=None):
         check(lib().b200_fill(self._h, ptr(dst), n, dtype, value, self._s(stream)))

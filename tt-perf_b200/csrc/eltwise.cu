@@ -76,6 +76,55 @@ __global__ void quantize_e4m3_kernel(const __nv_bfloat16* __restrict__ x, long l
         y[i] = static_cast<uint8_t>(__nv_cvt_float_to_fp8(__bfloat162float(x[i]) * scale, __NV_SATFINITE, __NV_E4M3));
 }
 
+// y[c][r] = e4m3(x[r][c] * scale): the transposed 8-bit copy an NN or TN product needs (8-bit operands are read
+// K-major only). 64 x 64 tiles through shared memory: 4-byte loads along the input rows, 4-byte stores along the
+// output rows.
+__global__ void quantize_e4m3_transpose_kernel(const __nv_bfloat16* __restrict__ x, int rows, int cols, long long ldx,
+                                               float scale, uint8_t* __restrict__ y, long long ldy, int tiles_c,
+                                               long long tiles, int vec_in, int vec_out) {
+    __shared__ __align__(4) uint8_t tile[64][68];
+    const int tid = threadIdx.x;
+    for (long long t = blockIdx.x; t < tiles; t += gridDim.x) {
+        const int r0 = static_cast<int>(t / tiles_c) * 64, c0 = static_cast<int>(t % tiles_c) * 64;
+        const int c2 = tid & 31, ty = tid >> 5;
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+            const int r = r0 + i * 8 + ty, c = c0 + 2 * c2;
+            float v0 = 0.0f, v1 = 0.0f;
+            if (r < rows) {
+                const __nv_bfloat16* src = x + static_cast<long long>(r) * ldx + c;
+                if (vec_in && c + 1 < cols) {
+                    const uint32_t u = __ldg(reinterpret_cast<const uint32_t*>(src));
+                    v0 = __uint_as_float(u << 16);
+                    v1 = __uint_as_float(u & 0xffff0000u);
+                } else {
+                    if (c < cols) v0 = __bfloat162float(src[0]);
+                    if (c + 1 < cols) v1 = __bfloat162float(src[1]);
+                }
+            }
+            const uint32_t q = __nv_cvt_float2_to_fp8x2(make_float2(v0 * scale, v1 * scale), __NV_SATFINITE, __NV_E4M3);
+            tile[2 * c2][i * 8 + ty] = static_cast<uint8_t>(q & 0xffu);
+            tile[2 * c2 + 1][i * 8 + ty] = static_cast<uint8_t>(q >> 8);
+        }
+        __syncthreads();
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            const int idx = i * 256 + tid;
+            const int c = idx >> 4, w = idx & 15;
+            const int oc = c0 + c, orow = r0 + 4 * w;
+            if (oc < cols && orow < rows) {
+                uint8_t* dst = y + static_cast<long long>(oc) * ldy + orow;
+                if (vec_out && orow + 3 < rows) {
+                    *reinterpret_cast<uint32_t*>(dst) = *reinterpret_cast<const uint32_t*>(&tile[c][4 * w]);
+                } else {
+                    for (int j = 0; j < 4 && orow + j < rows; ++j) dst[j] = tile[c][4 * w + j];
+                }
+            }
+        }
+        __syncthreads();
+    }
+}
+
 // ---- unary / scalar ops ------------------------------------------------------------------------------
 enum UnaryOp : int {
     U_NEG = 0, U_RELU = 1, U_GTZ = 2, U_GELU = 3, U_RSQRT = 4, U_EXP = 5, U_LOG = 6, U_TANH = 7, U_SQRT = 8,
@@ -855,6 +904,27 @@ int b200_quantize_fp8(b200_ctx* ctx, const void* x, int64_t n, float scale, void
     const int vec_ok = ((reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(y)) & 15u) == 0;
     quantize_e4m3_kernel<<<grid_for(ctx, (n + 15) / 16), kThreads, 0, ctx->pick(stream)>>>(
         static_cast<const __nv_bfloat16*>(x), n, scale, static_cast<uint8_t*>(y), vec_ok);
+    B200_CUDA_TRY(cudaGetLastError());
+    return B200_OK;
+}
+
+int b200_quantize_fp8_transposed(b200_ctx* ctx, const void* x, int64_t rows, int64_t cols, int64_t ldx, float scale,
+                                 void* y, int64_t ldy, void* stream) {
+    B200_REQUIRE(ctx != nullptr, "b200_quantize_fp8_transposed: ctx is NULL");
+    B200_REQUIRE(rows >= 0 && cols >= 0 && rows < (1ll << 31) && cols < (1ll << 31), "b200_quantize_fp8_transposed: bad shape");
+    if (rows == 0 || cols == 0) return B200_OK;
+    B200_REQUIRE(x && y, "b200_quantize_fp8_transposed: NULL buffer");
+    B200_REQUIRE(ldx >= cols && ldy >= rows, "b200_quantize_fp8_transposed: leading dimension too small");
+    B200_REQUIRE(scale > 0.0f && scale <= FLT_MAX, "b200_quantize_fp8_transposed: scale must be positive and finite");
+    DeviceScope scope(ctx->device);
+    const int tiles_c = static_cast<int>((cols + 63) / 64);
+    const long long tiles = ((rows + 63) / 64) * tiles_c;
+    const int vec_in = (reinterpret_cast<uintptr_t>(x) & 3u) == 0 && (ldx & 1) == 0;
+    const int vec_out = (reinterpret_cast<uintptr_t>(y) & 3u) == 0 && (ldy & 3) == 0;
+    const int grid = static_cast<int>(std::min<long long>(tiles, ctx->sm_count * 8ll));
+    quantize_e4m3_transpose_kernel<<<grid, 256, 0, ctx->pick(stream)>>>(
+        static_cast<const __nv_bfloat16*>(x), static_cast<int>(rows), static_cast<int>(cols), ldx, scale,
+        static_cast<uint8_t*>(y), ldy, tiles_c, tiles, vec_in, vec_out);
     B200_CUDA_TRY(cudaGetLastError());
     return B200_OK;
 }

@@ -57,8 +57,10 @@ def linear_forward(ctx, x, w, bias=None, activation=None, *, stream=None) -> Dev
 E4M3_MAX = 448.0
 
 
-def quantize_fp8(ctx, x: DeviceTensor, *, scale=None, stream=None):
-    """Returns (codes, scale): codes = e4m3(x * scale) as a one-byte-per-element tensor of x's shape.
+def quantize_fp8(ctx, x: DeviceTensor, *, scale=None, transposed=False, stream=None):
+    """Returns (codes, scale): codes = e4m3(x * scale) as a one-byte-per-element tensor of x's shape, or of the
+    transposed shape [cols, rows] of x viewed as a matrix over its last dimension (transposed=True: the copy a
+    dX or dW product reads, since 8-bit operands are K-major only).
     scale=None picks 448 / max|x| (one reduction and a host read of its result, so not for use while a trace is
     being recorded); a caller that tracks the range itself passes its scale and stays asynchronous."""
     if scale is None:
@@ -66,8 +68,13 @@ def quantize_fp8(ctx, x: DeviceTensor, *, scale=None, stream=None):
         ctx.absmax(x, x.numel, amax, stream=stream)
         peak = float(amax.numpy(stream)[0])
         scale = E4M3_MAX / peak if peak > 0.0 else 1.0
-    q = DeviceTensor(ctx, x.shape, FP8_E4M3)
-    ctx.quantize_fp8(x, x.numel, scale, q, stream=stream)
+    if transposed:
+        rows, cols = _rows(x), x.shape[-1]
+        q = DeviceTensor(ctx, (cols, rows), FP8_E4M3)
+        ctx.quantize_fp8_transposed(x, rows, cols, scale, q, stream=stream)
+    else:
+        q = DeviceTensor(ctx, x.shape, FP8_E4M3)
+        ctx.quantize_fp8(x, x.numel, scale, q, stream=stream)
     return q, float(scale)
 
 
@@ -428,6 +435,35 @@ class GPT2:
         for i, n in enumerate("qkv"):
             blk["w" + n], blk["b" + n] = blk["wqkv"].narrow0(i * d, d), blk["bqkv"].narrow0(i * d, d)
         return blk
+
+    def state(self) -> dict:
+        """Host copy of the parameters in the structure `load` takes (fp32 numpy arrays holding the bf16 values; the
+        padding rows of the LM head are dropped). load(state()) reproduces the device state bit for bit."""
+        p = self.params
+        out = {k: p[k].numpy() for k in ("tok_emb", "pos_emb", "lnf_g", "lnf_b")}
+        out["head"] = p["head"].numpy()[: self.V]
+        out["blocks"] = [{k: blk[k].numpy() for k in self.block_shapes()} for blk in p["blocks"]]
+        return out
+
+    def save(self, path) -> None:
+        """Writes the parameters to one .npz file (keys `tok_emb`, ..., `blocks.<i>.<name>`): a weight dump for comparing
+        two runs, or this implementation with another, tensor by tensor."""
+        import numpy as np
+        st = self.state()
+        flat = {k: v for k, v in st.items() if k != "blocks"}
+        for i, blk in enumerate(st["blocks"]):
+            flat.update({f"blocks.{i}.{k}": v for k, v in blk.items()})
+        np.savez(path, **flat)
+
+    def load_file(self, path) -> None:
+        """Loads a file written by `save`; the layer count and shapes must match this model."""
+        import numpy as np
+        with np.load(path) as z:
+            names = set(z.files)
+            blocks = [{k: z[f"blocks.{i}.{k}"] for k in self.block_shapes()} for i in range(self.L)]
+            if f"blocks.{self.L}.w1" in names:
+                raise ValueError(f"{path} holds more than {self.L} blocks")
+            self.load({**{k: z[k] for k in ("tok_emb", "pos_emb", "lnf_g", "lnf_b", "head")}, "blocks": blocks})
 
     def init_random(self, seed=42, std=0.02) -> None:
         """N(0, std) weights, zero biases, LayerNorm gain 1 (random-init stand-in for a checkpoint)."""
