@@ -216,3 +216,34 @@ def test_gpt2_weight_dump_and_reload_is_bit_exact(pkg, ctx, tmp_path):
         pkg.nn.GPT2(ctx, layers=L + 1, d_model=D, heads=H, seq=S, vocab=V).load_file(path)
     with pytest.raises(ValueError):
         pkg.nn.GPT2(ctx, layers=L - 1, d_model=D, heads=H, seq=S, vocab=V).load_file(path)
+
+
+@pytest.mark.parametrize("index", [0, 1, 2, 3])
+def test_layernorm_free_layer_matches_the_reference_libtorch_program(pkg, ctx, index):
+    """The reference's TracedTransformerLayer (attention + ReLU FFN, residuals, no LayerNorm) with its benchmark inputs —
+    all-ones input, every weight 0.01 — against what the reference's own libtorch program printed for the same
+    configuration (tests/golden/bench_transformer_torch.json, from bench/autograd/bench_transformer_torch.cpp)."""
+    nn, DT, c = pkg.nn, pkg.DeviceTensor, pkg.capi
+    case = json.loads((GOLDEN / "bench_transformer_torch.json").read_text())["cases"][index]
+    b, s, d, h, layers, mult = (case[k] for k in ("batch", "seq", "dim", "heads", "layers", "ffn_mult"))
+
+    def w(rows, cols):
+        return DT.from_numpy(ctx, np.full((rows, cols), 0.01, np.float32))
+
+    wq, wk, wv, wo, w1, w2 = w(d, d), w(d, d), w(d, d), w(d, d), w(d, mult * d), w(mult * d, d)
+    x = DT.from_numpy(ctx, np.ones((b, s, d), np.float32))
+    for _ in range(layers):
+        q, k, v = (nn.split_heads(ctx, nn.matmul(ctx, x, wt), h) for wt in (wq, wk, wv))
+        o, _ = nn.causal_attention_forward(ctx, q, k, v)
+        x = nn.add(ctx, x, nn.matmul(ctx, nn.merge_heads(ctx, o), wo))
+        hid = nn.matmul(ctx, x, w1, activation="relu")
+        x = nn.add(ctx, x, nn.matmul(ctx, hid, w2))
+    y = x.numpy()
+    assert list(y.shape) == case["output_shape"]
+    # bf16 steps are 2^-8 relative; the device rounds the fused scale + mask + softmax once where torch rounds each op
+    np.testing.assert_allclose(y[0, 0, :3], case["first_values"], rtol=1e-2 * layers)
+    ref = np.ones((b, s, d), np.float32)
+    hw = {k: np.full(t.shape, 0.01, np.float32) for k, t in dict(wq=wq, wk=wk, wv=wv, wo=wo, w1=w1, w2=w2).items()}
+    for _ in range(layers):
+        ref = mo.simple_transformer_layer_forward(ref, hw["wq"], hw["wk"], hw["wv"], hw["wo"], hw["w1"], hw["w2"], h)
+    assert mo.rel_frobenius(y, ref) <= 1e-2 * layers

@@ -244,3 +244,32 @@ def test_softmax_logsoftmax_and_edge_cases():
     o, p = mo.causal_attention_forward(q, q, q)
     assert np.allclose(np.triu(p, 1), 0) and np.allclose(p.sum(-1), 1, atol=1e-6)
     np.testing.assert_allclose(o[..., 0, :], q[..., 0, :], atol=1e-6)  # first query sees only itself
+
+
+def _ones_layer_stack(case):
+    b, s_, d, h, layers, mult = (case[k] for k in ("batch", "seq", "dim", "heads", "layers", "ffn_mult"))
+    x = np.ones((b, s_, d), np.float32)
+
+    def w(rows, cols):
+        return np.full((rows, cols), 0.01, np.float32)
+
+    for _ in range(layers):
+        x = mo.simple_transformer_layer_forward(x, w(d, d), w(d, d), w(d, d), w(d, d), w(d, mult * d), w(mult * d, d), h)
+    return x
+
+
+def test_simple_transformer_layer_matches_the_compiled_reference_program():
+    """bench/autograd/bench_transformer_torch.cpp, compiled unchanged against libtorch (oracle/build_ref.py), printed
+    the values in tests/golden/bench_transformer_torch.json; the oracle's restatement of its layer reproduces them to
+    the six digits the program prints. When the binary is present it is also run once, live, against the fixture."""
+    gold = load_json("bench_transformer_torch.json")
+    for case in gold["cases"]:
+        y = _ones_layer_stack(case)
+        assert list(y.shape) == case["output_shape"]
+        np.testing.assert_allclose(y[0, 0, :3], case["first_values"], rtol=2e-6)
+    from oracle import build_ref
+    if build_ref.BINARY.exists():
+        case = gold["cases"][1]
+        live = build_ref.run(case["batch"], case["seq"], case["dim"], case["heads"], case["layers"], case["ffn_mult"])
+        assert live["first_values"] == case["first_values"] and live["output_shape"] == case["output_shape"]
+
