@@ -2,6 +2,8 @@
 
     python tt-perf_b200/build.py            # incremental build
     python tt-perf_b200/build.py --force    # rebuild everything
+    python tt-perf_b200/build.py --profile  # development variant with clock stamps inside the GEMM and attention
+                                            # kernels: lib/libb200ttperf_prof.so (used by gemm_timeline.py)
 
 Each .cu file is compiled to an object under build/obj (in parallel) and linked into
 tt-perf_b200/lib/libb200ttperf.so. nvcc cross-compiles, so this works on a machine with no GPU.
@@ -47,45 +49,54 @@ def _headers_mtime() -> float:
     return max((h.stat().st_mtime for h in hdrs), default=0.0)
 
 
-def _compile(src: Path, force: bool, hdr_mtime: float) -> tuple[Path, str]:
-    obj = OBJ_DIR / (src.stem + ".o")
+PROFILE_FLAGS = ["-DB200_GEMM_PROFILE", "-DB200_ATTN_PROFILE"]
+PROFILE_LIB_PATH = LIB_DIR / "libb200ttperf_prof.so"
+
+
+def _compile(src: Path, force: bool, hdr_mtime: float, obj_dir: Path = OBJ_DIR, extra=()) -> tuple[Path, str]:
+    obj = obj_dir / (src.stem + ".o")
     if not force and obj.exists() and obj.stat().st_mtime > max(src.stat().st_mtime, hdr_mtime):
         return obj, ""
-    cmd = [_nvcc(), *NVCC_FLAGS, "-I", str(REPO / "include"), "-c", str(src), "-o", str(obj)]
+    cmd = [_nvcc(), *NVCC_FLAGS, *extra, "-I", str(REPO / "include"), "-c", str(src), "-o", str(obj)]
     r = subprocess.run(cmd, capture_output=True, text=True)
     if r.returncode != 0:
         raise RuntimeError(f"nvcc failed on {src.name}:\n{r.stdout}\n{r.stderr}")
     return obj, r.stderr
 
 
-def build(force: bool = False, verbose: bool = False) -> Path:
-    OBJ_DIR.mkdir(parents=True, exist_ok=True)
+def build(force: bool = False, verbose: bool = False, profile: bool = False) -> Path:
+    obj_dir = REPO / "build" / "obj_prof" if profile else OBJ_DIR
+    lib_path = PROFILE_LIB_PATH if profile else LIB_PATH
+    extra = PROFILE_FLAGS if profile else ()
+    obj_dir.mkdir(parents=True, exist_ok=True)
     LIB_DIR.mkdir(parents=True, exist_ok=True)
     srcs = _sources()
     hdr_mtime = _headers_mtime()
     logs = []
     with cf.ThreadPoolExecutor(max_workers=min(8, len(srcs))) as ex:
-        results = list(ex.map(lambda s: _compile(s, force, hdr_mtime), srcs))
+        results = list(ex.map(lambda s: _compile(s, force, hdr_mtime, obj_dir, extra), srcs))
     objs = [o for o, _ in results]
     logs = [log for _, log in results if log]
     if verbose:
         for log in logs:
             print(log)
-    (REPO / "build" / "ptxas.log").write_text("\n".join(logs))
+    if not profile:
+        (REPO / "build" / "ptxas.log").write_text("\n".join(logs))
     newest_obj = max(o.stat().st_mtime for o in objs)
-    if force or not LIB_PATH.exists() or LIB_PATH.stat().st_mtime < newest_obj:
+    if force or not lib_path.exists() or lib_path.stat().st_mtime < newest_obj:
         # Export only the C ABI: the version script keeps b200_* global and makes every other
         # symbol local.
-        vs = OBJ_DIR / "exports.map"
+        vs = obj_dir / "exports.map"
         vs.write_text("{ global: b200_*; local: *; };\n")
-        cmd = [_nvcc(), "-shared", "-o", str(LIB_PATH), *map(str, objs),
+        cmd = [_nvcc(), "-shared", "-o", str(lib_path), *map(str, objs),
                "-Xlinker", f"--version-script={vs}", "-lcudart_static", "-ldl", "-lpthread", "-lrt"]
         r = subprocess.run(cmd, capture_output=True, text=True)
         if r.returncode != 0:
             raise RuntimeError(f"link failed:\n{r.stdout}\n{r.stderr}")
-    return LIB_PATH
+    return lib_path
 
 
 if __name__ == "__main__":
-    path = build(force="--force" in sys.argv, verbose="-v" in sys.argv or "--verbose" in sys.argv)
+    path = build(force="--force" in sys.argv, verbose="-v" in sys.argv or "--verbose" in sys.argv,
+                 profile="--profile" in sys.argv)
     print(path)

@@ -51,7 +51,10 @@ class AttnOperand(C.Structure):
 
 
 def lib_path() -> Path:
-    return Path(__file__).resolve().parent / "lib" / "libb200ttperf.so"
+    """The library this process binds: B200_TTPERF_LIB when set (a development variant built by build.py --profile),
+    else the product build."""
+    override = os.environ.get("B200_TTPERF_LIB")
+    return Path(override) if override else Path(__file__).resolve().parent / "lib" / "libb200ttperf.so"
 
 
 # name -> (restype, argtypes); kept in one table so tests can check it against the header.

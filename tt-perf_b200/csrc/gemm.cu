@@ -87,6 +87,32 @@ void b200_gemm_desc_init(b200_gemm_desc* d) {
     d->ab_dtype = B200_BF16;
 }
 
+#ifdef B200_GEMM_PROFILE
+// Development builds (-DB200_GEMM_PROFILE): the tcgen05 kernels write clock64() stamps for the first 8 tiles of every
+// CTA into the context scratch, 8 entries per tile: 0 / 1 first and last MMA issue of the tile, 2 epilogue begin (warp
+// 2), 3..6 epilogue end in warps 2..5; entry 7 of a CTA's first tile is the CTA's clock right after the start-up
+// barrier. prepare sizes and clears the area (call it before the launch to be examined, and use split_k = 1: K slices
+// use the same scratch); the second call copies `count` entries to the host after synchronising.
+int b200_debug_gemm_stamps_prepare(b200_ctx* ctx) {
+    B200_REQUIRE(ctx != nullptr, "b200_debug_gemm_stamps_prepare: ctx is NULL");
+    DeviceScope scope(ctx->device);
+    const size_t bytes = static_cast<size_t>(ctx->sm_count) * 64 * sizeof(long long);
+    int rc = ensure_scratch(ctx, bytes);
+    if (rc != B200_OK) return rc;
+    B200_CUDA_TRY(cudaMemsetAsync(ctx->d_scratch, 0, bytes, ctx->stream));
+    B200_CUDA_TRY(cudaStreamSynchronize(ctx->stream));
+    return B200_OK;
+}
+int b200_debug_gemm_stamps(b200_ctx* ctx, long long* host_out, size_t count) {
+    B200_REQUIRE(ctx && host_out, "b200_debug_gemm_stamps: NULL argument");
+    B200_REQUIRE(count * sizeof(long long) <= ctx->scratch_bytes, "b200_debug_gemm_stamps: more entries than prepared");
+    DeviceScope scope(ctx->device);
+    B200_CUDA_TRY(cudaDeviceSynchronize());
+    B200_CUDA_TRY(cudaMemcpy(host_out, ctx->d_scratch, count * sizeof(long long), cudaMemcpyDeviceToHost));
+    return B200_OK;
+}
+#endif
+
 int b200_gemm_scratch_bytes(b200_ctx* ctx, const b200_gemm_desc* d, size_t* out_bytes) {
     B200_REQUIRE(ctx && out_bytes, "b200_gemm_scratch_bytes: NULL argument");
     int rc = validate(d);

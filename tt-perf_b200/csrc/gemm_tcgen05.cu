@@ -123,6 +123,9 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
     __syncthreads();
     tcgen05_fence_after_sync();
     const uint32_t tmem_base = *tmem_slot;
+#ifdef B200_GEMM_PROFILE
+    if (p.prof && threadIdx.x == 0) p.prof[blockIdx.x * 64 + 7] = clock64();  // this CTA's time origin
+#endif
 
     if (warp == 0) {
         // ------------------------------------------------------------------ TMA producer
@@ -394,7 +397,8 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
                 }
             }
 #ifdef B200_GEMM_PROFILE
-            if (p.prof && eprof_slot < 8 && threadIdx.x == 64) p.prof[(blockIdx.x * 8 + eprof_slot) * 8 + 3] = clock64();
+            // end of this tile's epilogue in each of the four epilogue warps: entries 3..6 = warps 2..5
+            if (p.prof && eprof_slot < 8 && lane == 0) p.prof[(blockIdx.x * 8 + eprof_slot) * 8 + warp + 1] = clock64();
 #endif
             // Hand the accumulator buffer back to the MMA warp.
             tcgen05_fence_before_sync();
@@ -690,7 +694,7 @@ int launch_gemm_tcgen05(b200_ctx* ctx, const b200_gemm_desc& d, int k_splits, cu
     p.status = ctx->d_status;
     p.group_m = group_m_setting();
 #ifdef B200_GEMM_PROFILE
-    p.prof = static_cast<long long*>(ctx->d_scratch);  // the probe sizes the scratch beforehand
+    p.prof = static_cast<long long*>(ctx->d_scratch);  // b200_debug_gemm_stamps_prepare sized and cleared it
 #endif
     p.partial = nullptr;
     p.partial_round_bf16 = (d.fidelity == B200_LOFI || d.fidelity == B200_HIFI2) ? 1 : 0;

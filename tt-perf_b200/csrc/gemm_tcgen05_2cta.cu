@@ -130,6 +130,11 @@ gemm_tcgen05_2cta_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_c
     cluster_sync_all();  // both CTAs' barriers are initialised before anyone signals across the pair
     tcgen05_fence_after_sync();
     const uint32_t tmem_base = *tmem_slot;
+#ifdef B200_GEMM_PROFILE
+    // SM clocks are not synchronised: every CTA notes its own clock right after the cluster-wide barrier, so that the
+    // stamps of the two CTAs of a pair can be put on one time axis (entry 7 of the CTA's first slot).
+    if (p.prof && threadIdx.x == 0) p.prof[blockIdx.x * 64 + 7] = clock64();
+#endif
 
     if (warp == 0) {
         // ------------------------------------------------------------------ TMA producer (both CTAs)
@@ -400,7 +405,8 @@ gemm_tcgen05_2cta_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_c
                 }
             }
 #ifdef B200_GEMM_PROFILE
-            if (p.prof && eprof_slot < 8 && threadIdx.x == 64) p.prof[(blockIdx.x * 8 + eprof_slot) * 8 + 3] = clock64();
+            // end of this tile's epilogue in each of the four epilogue warps: entries 3..6 = warps 2..5
+            if (p.prof && eprof_slot < 8 && lane == 0) p.prof[(blockIdx.x * 8 + eprof_slot) * 8 + warp + 1] = clock64();
 #endif
             // Hand the accumulator buffer back to the leader's MMA warp (remote arrive from the peer CTA).
             tcgen05_fence_before_sync();
