@@ -7,7 +7,8 @@
 //     CTAs' shared memory and writes rows 0-127 of the accumulator to the leader's TMEM, rows 128-255 to the peer's;
 //   * TMA completions of both CTAs are counted on the leader's "full" barrier (cta_group::2 loads, no multicast);
 //     `tcgen05.commit` with a 2-CTA multicast mask releases ring stages and publishes accumulators in both CTAs;
-//   * each CTA's four epilogue warps drain their own 128 accumulator rows through the staged TMA-store epilogue.
+//   * each CTA's eight epilogue warps drain their own 128 accumulator rows (two warps per 32 rows, half of the
+//     columns each) through the staged TMA-store epilogue.
 //
 // Same roles, ring protocol, bounded waits and output routing as gemm_tcgen05.cu; requires 16-byte aligned C rows.
 #include <algorithm>
@@ -28,13 +29,14 @@ constexpr int BN = 256;
 constexpr int BN_CTA = 128;   // B columns loaded by each CTA
 constexpr int BK = 64;
 constexpr int UMMA_K = 16;
-constexpr int NUM_THREADS = 192;
+constexpr int EPI_WARPS = 8;   // two warps per TMEM lane quarter, each takes half of the tile's columns
+constexpr int NUM_THREADS = 64 + 32 * EPI_WARPS;
 constexpr int STAGES = 6;
 constexpr int A_BYTES = BM_CTA * BK * 2;
 constexpr int B_BYTES = BN_CTA * BK * 2;
 constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
 constexpr int EPI_STAGE_BYTES = 4096;
-constexpr int EPI_BYTES = 4 * 2 * EPI_STAGE_BYTES;
+constexpr int EPI_BYTES = EPI_WARPS * EPI_STAGE_BYTES;  // one staging box per epilogue warp
 constexpr int BARRIER_BYTES = 256;
 constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + EPI_BYTES + BARRIER_BYTES + 1024;
 
@@ -64,15 +66,15 @@ __device__ __forceinline__ PairWork decode_pair(const GemmParams& p, int w) {
     return it;
 }
 
-// Named barrier of the four epilogue warps (128 threads), plain and with an AND-reduction of a predicate.
-__device__ __forceinline__ void epilogue_warps_sync() { asm volatile("bar.sync 2, 128;" ::: "memory"); }
+// Named barrier of the eight epilogue warps (256 threads), plain and with an AND-reduction of a predicate.
+__device__ __forceinline__ void epilogue_warps_sync() { asm volatile("bar.sync 2, 256;" ::: "memory"); }
 __device__ __forceinline__ bool epilogue_warps_all(bool pred) {
     uint32_t out;
     asm volatile(
         "{\n\t"
         ".reg .pred p, q;\n\t"
         "setp.ne.u32 p, %1, 0;\n\t"
-        "barrier.cta.red.and.pred q, 2, 128, p;\n\t"
+        "barrier.cta.red.and.pred q, 2, 256, p;\n\t"
         "selp.u32 %0, 1, 0, q;\n\t"
         "}\n"
         : "=r"(out)
@@ -95,7 +97,7 @@ gemm_tcgen05_2cta_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_c
     uint64_t* full_bar = reinterpret_cast<uint64_t*>(bar_base);   // used in the leader only
     uint64_t* empty_bar = full_bar + STAGES;                       // one per CTA (multicast commit)
     uint64_t* tmem_full_bar = empty_bar + STAGES;                  // one per CTA (multicast commit)
-    uint64_t* tmem_empty_bar = tmem_full_bar + 2;                  // used in the leader only: 8 arrivals (4 warps x 2 CTAs)
+    uint64_t* tmem_empty_bar = tmem_full_bar + 2;                  // used in the leader only: 16 arrivals (8 warps x 2 CTAs)
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(tmem_empty_bar + 2);
     volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
     volatile int* last_flag = abort_flag + 1;      // split-K: this CTA drew the last ticket of its tile
@@ -116,7 +118,7 @@ gemm_tcgen05_2cta_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_c
         }
         for (int a = 0; a < 2; ++a) {
             mbar_init(&tmem_full_bar[a], 1);
-            mbar_init(&tmem_empty_bar[a], 8);
+            mbar_init(&tmem_empty_bar[a], 2 * EPI_WARPS);  // every epilogue warp of both CTAs
         }
         *abort_flag = 0;
         mbar_fence_init();
@@ -250,18 +252,21 @@ gemm_tcgen05_2cta_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_c
             }
         }
     } else {
-        // ------------------------------------------------------------------ epilogue (warps 2..5, both CTAs)
+        // ------------------------------------------------------------------ epilogue (warps 2..9, both CTAs)
+        // A warp may read the TMEM lane quarter (warp id mod 4); warps w and w + 4 share a quarter and split the tile's
+        // 256 columns between them. Four warps converting and staging a whole tile took as long as a 12-K-block main
+        // loop and slowed the MMAs that ran beside them; eight halve that.
         const int q = warp & 3;
+        const int c_first = ((warp - 2) >> 2) * (BN / 2), c_last = c_first + BN / 2;
         int acc = 0;
         uint32_t acc_phase = 0;
-        int ebuf = 0;
-        uint8_t* stage_base = epi_smem + (warp - 2) * 2 * EPI_STAGE_BYTES;
+        uint8_t* sbuf = epi_smem + (warp - 2) * EPI_STAGE_BYTES;
         const int box_cols = p.c_f32 ? 32 : 64;
         for (int w = cluster_id; w < p.total_work; w += num_clusters) {
             const PairWork it = decode_pair(p, w);
             const bool got = mbar_wait(&tmem_full_bar[acc], acc_phase, abort_flag);
             if (p.k_splits > 1) {
-                // the four epilogue warps meet at named barriers below: they must agree on whether to go on
+                // the epilogue warps meet at named barriers below: they must agree on whether to go on
                 if (!epilogue_warps_all(__all_sync(0xffffffffu, got))) break;
             } else if (!__all_sync(0xffffffffu, got)) {
                 break;
@@ -287,7 +292,7 @@ gemm_tcgen05_2cta_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_c
             // one 128-byte line per thread per instruction).
             const size_t cta_floats = static_cast<size_t>(BM_CTA) * BN;
             const size_t tiles_total = static_cast<size_t>(p.batch) * p.num_m_tiles * p.num_n_tiles;
-            const int ethread = threadIdx.x - 64;  // 0..127 within the epilogue warps
+            const int ethread = q * 32 + lane;  // the accumulator row within the CTA: 0..127
             auto part_at = [&](int slice_idx) {
                 return reinterpret_cast<float4*>(p.partial + ((static_cast<size_t>(slice_idx) * tiles_total + it.tile) * 2 + rank) * cta_floats) +
                        ethread;
@@ -298,7 +303,7 @@ gemm_tcgen05_2cta_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_c
                 // the sums it still holds in TMEM and runs the normal epilogue. Nobody waits for anybody.
                 float4* mine = part_at(it.split);
 #pragma unroll 1
-                for (int c = 0; c < BN; c += 32) {
+                for (int c = c_first; c < c_last; c += 32) {
                     if (it.n0 + c >= p.N) break;
                     uint32_t v[32];
                     tmem_ld_32x32b_x32(taddr + c, v);
@@ -326,32 +331,17 @@ gemm_tcgen05_2cta_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_c
                 if (finish) __threadfence();
             }
             if (finish && m_cta < p.M) {  // a CTA whose 128 rows lie entirely below the matrix has nothing to store
-                uint32_t nx0[32], nx1[32];
-                tmem_ld_32x32b_x32(taddr, nx0);
-                if (box_cols == 64 && it.n0 + 32 < p.N) tmem_ld_32x32b_x32(taddr + 32, nx1);
 #pragma unroll 1
-                for (int c = 0; c < BN; c += box_cols) {
+                for (int c = c_first; c < c_last; c += box_cols) {
                     const int n = it.n0 + c;
                     if (n >= p.N) break;
-                    uint8_t* sbuf = stage_base + ebuf * EPI_STAGE_BYTES;
-                    if (lane == 0) tma_store_wait_read<1>();
+                    uint32_t v0[32], v1[32];
+                    tmem_ld_32x32b_x32(taddr + c, v0);
+                    if (box_cols == 64 && n + 32 < p.N) tmem_ld_32x32b_x32(taddr + c + 32, v1);
+                    if (lane == 0) tma_store_wait_read<0>();  // the box this warp stored before has left its buffer
                     __syncwarp();
                     uint8_t* srow = sbuf + lane * 128;
-                    // The TMEM loads of the NEXT box are in flight while this one is converted and staged.
                     tmem_ld_wait();
-                    uint32_t v0[32], v1[32];
-#pragma unroll
-                    for (int i = 0; i < 32; ++i) {
-                        v0[i] = nx0[i];
-                        v1[i] = nx1[i];
-                    }
-                    {
-                        const int cn = c + box_cols;
-                        if (cn < BN && it.n0 + cn < p.N) {
-                            tmem_ld_32x32b_x32(taddr + cn, nx0);
-                            if (box_cols == 64 && it.n0 + cn + 32 < p.N) tmem_ld_32x32b_x32(taddr + cn + 32, nx1);
-                        }
-                    }
 #pragma unroll 1
                     for (int h = 0; h * 32 < box_cols; ++h) {
                         const int nh = n + h * 32;
@@ -401,12 +391,11 @@ gemm_tcgen05_2cta_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_c
                         }
                         tma_store_commit();
                     }
-                    ebuf ^= 1;
                 }
             }
 #ifdef B200_GEMM_PROFILE
-            // end of this tile's epilogue in each of the four epilogue warps: entries 3..6 = warps 2..5
-            if (p.prof && eprof_slot < 8 && lane == 0) p.prof[(blockIdx.x * 8 + eprof_slot) * 8 + warp + 1] = clock64();
+            // end of this tile's epilogue in the warps of the first column half: entries 3..6 = warps 2..5
+            if (p.prof && eprof_slot < 8 && lane == 0 && warp <= 5) p.prof[(blockIdx.x * 8 + eprof_slot) * 8 + warp + 1] = clock64();
 #endif
             // Hand the accumulator buffer back to the leader's MMA warp (remote arrive from the peer CTA).
             tcgen05_fence_before_sync();
