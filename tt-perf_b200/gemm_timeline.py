@@ -4,8 +4,8 @@ Needs the development variant of the library (`python tt-perf_b200/build.py --pr
 -DB200_GEMM_PROFILE into lib/libb200ttperf_prof.so); the product build carries no stamps. For the first 8 tiles of a
 few CTAs it prints, in SM clocks from the CTA's start: when the MMA warp issued the tile's first and last MMA, when the
 epilogue began (the accumulator was complete) and when epilogue warps 2..5 finished (all four of the single-CTA kernel;
-in the CTA-pair kernel the four that take the first half of the columns). For the CTA-pair kernel the two CTAs of a pair are listed side by side on one time axis (each CTA's clock is taken right after the
-cluster-wide start-up barrier).
+in the CTA-pair kernel the four that take the first half of the columns). For the CTA-pair kernel the two CTAs of a
+pair are listed on one time axis (each CTA's clock is taken right after the cluster-wide start-up barrier).
 
     python tt-perf_b200/gemm_timeline.py --m 8192 --n 3072 --k 768 [--ta] [--tb] [--kernel single|pair] [--bn 256]
 """
