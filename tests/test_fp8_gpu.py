@@ -222,3 +222,25 @@ def test_fidelity_sweep_small(pkg, ctx):
     const = fs.run(pkg, ctx, "constant", batch=64, dims=(512, 256, 128), lr=0.1, steps=3, warmup=1, timed=1,
                    levels=("HiFi4", "FP8"))
     assert all(abs(a - b) <= 0.02 * abs(b) for a, b in zip(const["FP8"]["loss"], const["HiFi4"]["loss"]))
+
+
+def test_fp8_training_steps_follow_the_oracle(pkg, ctx):
+    """Four FP8 training steps of the sweep's MLP (all five matmuls on e4m3 operands, per-tensor scales) against the
+    oracle's emulation of the same arithmetic: the loss at every step and the weight updates."""
+    from importlib import import_module
+    fs = import_module(pkg.__name__ + ".fidelity_sweep")
+    DT = pkg.DeviceTensor
+    batch, dims, lr = 128, (512, 256, 128), 5.0
+    x, t, w1, b1, w2, b2 = fs.make_problem("random", batch, dims, 3)
+    model = fs.FidelityMLP(pkg, ctx, "FP8", w1, b1, w2, b2, lr)
+    dx, dt = DT.from_numpy(ctx, x), DT.from_numpy(ctx, t)
+    params = (w1, b1, w2, b2)
+    for step in range(4):
+        loss_dev = float(model.train_step(dx, dt).numpy()[0])
+        loss_ref, params, _ = mo.mlp_train_step_e4m3(x, t, params, lr)
+        assert abs(loss_dev - loss_ref) <= 1e-2 * loss_ref, (step, loss_dev, loss_ref)
+    start = (mo.bf16_round(w1), mo.bf16_round(b1), mo.bf16_round(w2), mo.bf16_round(b2))
+    for dev, ref, init, name in zip(model.params, params, start, ("w1", "b1", "w2", "b2")):
+        got = dev.numpy().reshape(ref.shape)
+        assert mo.rel_frobenius(got, ref) <= 5e-3, name
+        assert mo.rel_frobenius(got - init, ref - init) <= 8e-2, name     # the updates themselves, not just the weights
