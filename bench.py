@@ -30,9 +30,9 @@ sys.path.insert(0, str(REPO))
 
 L2_BYTES = 126 * 1024 * 1024
 
-# dram__bytes_read.sum + dram__bytes_write.sum of one 8192^3 launch, from the ncu capture summarised in
-# profiles/ (null until a capture of the current kernel exists).
-GEMM_8192_DRAM_TRAFFIC_BYTES = 1.200e9  # 1.072 GB read + 0.128 GB written (ncu, profiles/gemm_tcgen05_2cta_8192x8192x8192.md)
+# dram__bytes_read.sum + dram__bytes_write.sum of one 8192^3 launch of the CTA-pair kernel, from an ncu capture
+# (1.072 GB read + 0.128 GB written).
+GEMM_8192_DRAM_TRAFFIC_BYTES = 1.200e9
 
 
 def load_peaks() -> dict:

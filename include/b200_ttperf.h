@@ -74,6 +74,11 @@ int b200_ctx_stream(const b200_ctx* ctx, void** out_stream);
 /* Blocks until all work queued on `stream` has finished, then reports a kernel wait that timed out
  * since the last call as B200_ERR_DEVICE_TIMEOUT (and clears it). */
 int b200_synchronize(b200_ctx* ctx, void* stream);
+/* Exercises that error path without a fault or a hang: queues a one-CTA kernel that waits, with the same bounded wait
+ * the GEMM and attention kernels use but with `limit_ns` (1 us .. 100 ms) as its limit, on a barrier nothing ever
+ * arrives at; when the limit runs out it raises the status word and returns. The next b200_synchronize therefore
+ * reports B200_ERR_DEVICE_TIMEOUT, clears the context's status block, and the context is usable again. */
+int b200_selftest_wait_timeout(b200_ctx* ctx, uint64_t limit_ns, void* stream);
 /* Device-side timing as the reference's benchmarks do around Finish() (bench/metal/matmul_sweep.cpp:44-79), but with
  * CUDA events on the stream: start records an event, stop records a second one, waits for it and returns the elapsed
  * milliseconds between the two (and releases the timer). */
@@ -162,6 +167,14 @@ typedef struct b200_gemm_desc {
 
 /* Fills a descriptor with defaults: no transposes, batch 1, alpha 1, bf16 operands and output, HIFI4, AUTO. */
 void b200_gemm_desc_init(b200_gemm_desc* desc);
+/* K-sliced products (split_k != 1), attention backward, column reductions and LayerNorm backward keep intermediate
+ * sums in ONE scratch block, ticket-counter set and staging area per context. Calls that use them on different
+ * streams are serialised by the library (the later stream waits for an event recorded on the earlier one), so they
+ * are safe but do not overlap; give concurrent streams their own contexts when that matters. When a call needs more
+ * scratch than the context holds, the block is reallocated: a device-wide synchronisation plus cudaFree / cudaMalloc
+ * (b200_gemm_scratch_bytes tells how much a product needs; run the largest shape once up front). While recorded
+ * traces exist the outgrown block stays mapped until the last trace is released, since replays write to the address
+ * they recorded. */
 int b200_gemm(b200_ctx* ctx, const b200_gemm_desc* desc, void* stream);
 /* The same product with A, B and C in HOST memory (pinned memory gives full PCIe speed) — the path a reference program
  * takes from Tensor::from_vector / to_device through ttnn::matmul to .cpu() (bench/metal/matmul_tensor_parallel.cpp:
@@ -171,6 +184,29 @@ int b200_gemm(b200_ctx* ctx, const b200_gemm_desc* desc, void* stream);
 int b200_matmul_host(b200_ctx* ctx, const b200_gemm_desc* desc_with_host_pointers, int panels);
 /* Bytes of context scratch the split-K path of this descriptor will use (0 when it does not split). */
 int b200_gemm_scratch_bytes(b200_ctx* ctx, const b200_gemm_desc* desc, size_t* out_bytes);
+
+/* Which kernel serves a product, and how. The reference sweeps TTNN's program configurations per shape
+ * (bench/metal/matmul_sweep.cpp:85-117 core grids, bench/autograd/bench_shape_sweep.cpp:57-121); here the library
+ * plans by itself (b200_gemm), the plan can be read (b200_gemm_plan_query, b200_gemm_plan_describe: the kernel's
+ * name and tiling as text, e.g. for a benchmark report) and a sweep can run any other plan (b200_gemm_planned).
+ *   kernel    B200_GEMM_KERNEL_SIMT          CUDA-core kernel, any alignment
+ *             B200_GEMM_KERNEL_TCGEN05       one CTA per 128 x block_n tile (block_n in {64, 128, 192, 256})
+ *             B200_GEMM_KERNEL_TCGEN05_PAIR  two CTAs (cta_group::2) per 256 x 256 tile; needs 16-byte aligned rows of C
+ *   k_slices  K is cut into this many slices (0 and 1 = no cut); the single-CTA kernel sums them in a second
+ *             launch, the pair kernel inside the same launch
+ *   group_m   row-tiles per column sweep of the tile order (0 = default) */
+typedef enum b200_gemm_kernel {
+    B200_GEMM_KERNEL_SIMT = 0, B200_GEMM_KERNEL_TCGEN05 = 1, B200_GEMM_KERNEL_TCGEN05_PAIR = 2
+} b200_gemm_kernel;
+typedef struct b200_gemm_plan {
+    int32_t kernel;
+    int32_t block_n;
+    int32_t k_slices;
+    int32_t group_m;
+} b200_gemm_plan;
+int b200_gemm_plan_query(b200_ctx* ctx, const b200_gemm_desc* desc, b200_gemm_plan* out_plan);
+int b200_gemm_plan_describe(const b200_gemm_desc* desc, const b200_gemm_plan* plan, char* buf, size_t buf_bytes);
+int b200_gemm_planned(b200_ctx* ctx, const b200_gemm_desc* desc, const b200_gemm_plan* plan, void* stream);
 
 /* ---- fused attention (traced/nn.hpp:164-192 TracedCausalAttention; transformer_train.hpp:54-70
  * SharedAttentionBuffers::attention_forward / attention_backward; py/nn.py:229-253) ----
@@ -316,6 +352,15 @@ int b200_sgd_step(b200_ctx* ctx, int64_t count, void* const* params, const void*
 int b200_adam_step(b200_ctx* ctx, int64_t count, void* const* params, const void* const* grads, float* const* m,
                    float* const* v, void* const* shadow_bf16, const int64_t* sizes, int p_dtype, int g_dtype, float lr,
                    float beta1, float beta2, float eps, int64_t step, void* stream);
+/* The same update with the step number in DEVICE memory, for steps that are recorded into a trace and replayed
+ * (TraceContext, autograd/traced/trace.hpp:21-88): the arguments of a recorded kernel are frozen, so a host-side step
+ * count would apply the bias correction of the recording step on every replay. d_state16 is a 16-byte device buffer
+ * the caller zero-fills once ({int64 step; float 1/(1-beta1^step); float 1/(1-beta2^step)}); with advance != 0 a
+ * one-thread kernel increments the step and refreshes the two factors before the update reads them. Several calls of
+ * one optimiser step (parameter groups of different dtypes) share one state: advance on the first call only. */
+int b200_adam_step_device(b200_ctx* ctx, int64_t count, void* const* params, const void* const* grads, float* const* m,
+                          float* const* v, void* const* shadow_bf16, const int64_t* sizes, int p_dtype, int g_dtype, float lr,
+                          float beta1, float beta2, float eps, void* d_state16, int advance, void* stream);
 
 /* ---- sharded matmul over the GPUs of one node, one process per GPU ---------------------------------------------
  * (benchmark_tensor_parallel_matmul, bench/metal/matmul_tensor_parallel.cpp:54-123: replicate A, shard B on dim 1,
@@ -364,10 +409,14 @@ int b200_reduce_slices(b200_ctx* ctx, const float* slices, int n_slices, const b
  * operands do not meet the TMA alignment rules (there is no SIMT path here).
  * All calls on a device share the array: calls whose kernels may overlap on the GPU (different streams
  * or threads) race on it — keep them on one stream. The first call on each device looks up the array's
- * device address and configures the kernels; make it before any stream capture starts. A bounded wait
- * that runs out inside these kernels is recorded in a status word inside the library image, which
- * b200_synchronize does not report. */
+ * device address, and the first call that uses a kernel variant (tile width x operand layouts) on a device
+ * configures that kernel: make one call of every shape class you will use before any stream capture starts.
+ * A bounded wait that runs out inside these kernels is recorded in a status word inside the library image;
+ * b200_synchronize does not see it, b200_static_scratch_status does: it waits for `stream`, returns
+ * B200_ERR_DEVICE_TIMEOUT (and *out_status != 0) when a wait ran out since the last call, and clears the word.
+ * It allocates nothing either. */
 int b200_gemm_static_scratch(int device, const b200_gemm_desc* desc, void* stream);
+int b200_static_scratch_status(int device, void* stream, int* out_status);
 
 #ifdef __cplusplus
 } /* extern "C" */

@@ -23,8 +23,8 @@ BINARY = OUT_DIR / "bench_transformer_torch"
 
 
 def default_reference() -> Path | None:
-    """The reference tree: $TTPERF_REFERENCE, else the checkout beside the build user's home; None when absent."""
-    cand = Path(os.environ.get("TTPERF_REFERENCE", str(Path("/root") / "reference")))
+    """The reference tree: $TTPERF_REFERENCE, else a checkout named `reference` beside this repository; None when absent."""
+    cand = Path(os.environ.get("TTPERF_REFERENCE", str(Path(__file__).resolve().parents[2] / "reference")))
     return cand if (cand / SOURCE).exists() else None
 
 

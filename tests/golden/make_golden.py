@@ -39,7 +39,7 @@ import torch.nn as nn
 import torch.nn.functional as F
 
 HERE = Path(__file__).resolve().parent
-DEFAULT_REFERENCE = str(Path("/root") / "reference")
+DEFAULT_REFERENCE = str(Path(__file__).resolve().parents[3] / "reference")   # a checkout beside this repository
 
 
 def run_script(ref: Path, rel: str) -> str:

@@ -43,7 +43,8 @@ RENAME = {"bench/metal/bench_fusion.cpp": "metal_bench_fusion"}
 
 
 def default_reference() -> str:
-    return os.environ.get("TTPERF_REFERENCE", str(Path("/root") / "reference"))
+    """$TTPERF_REFERENCE, else a checkout named `reference` beside this repository."""
+    return os.environ.get("TTPERF_REFERENCE", str(Path(__file__).resolve().parents[3] / "reference"))
 
 
 def build_one(ref: Path, rel: str) -> tuple[str, bool, str]:

@@ -2,8 +2,6 @@
 
     python tt-perf_b200/build.py            # incremental build
     python tt-perf_b200/build.py --force    # rebuild everything
-    python tt-perf_b200/build.py --profile  # development variant with clock stamps inside the GEMM and attention
-                                            # kernels: lib/libb200ttperf_prof.so (used by gemm_timeline.py)
 
 Each .cu file is compiled to an object under build/obj (in parallel) and linked into
 tt-perf_b200/lib/libb200ttperf.so. nvcc cross-compiles, so this works on a machine with no GPU.
@@ -49,10 +47,6 @@ def _headers_mtime() -> float:
     return max((h.stat().st_mtime for h in hdrs), default=0.0)
 
 
-PROFILE_FLAGS = ["-DB200_GEMM_PROFILE", "-DB200_ATTN_PROFILE"]
-PROFILE_LIB_PATH = LIB_DIR / "libb200ttperf_prof.so"
-
-
 def _compile(src: Path, force: bool, hdr_mtime: float, obj_dir: Path = OBJ_DIR, extra=()) -> tuple[Path, str]:
     obj = obj_dir / (src.stem + ".o")
     if not force and obj.exists() and obj.stat().st_mtime > max(src.stat().st_mtime, hdr_mtime):
@@ -64,10 +58,8 @@ def _compile(src: Path, force: bool, hdr_mtime: float, obj_dir: Path = OBJ_DIR, 
     return obj, r.stderr
 
 
-def build(force: bool = False, verbose: bool = False, profile: bool = False) -> Path:
-    obj_dir = REPO / "build" / "obj_prof" if profile else OBJ_DIR
-    lib_path = PROFILE_LIB_PATH if profile else LIB_PATH
-    extra = PROFILE_FLAGS if profile else ()
+def build(force: bool = False, verbose: bool = False) -> Path:
+    obj_dir, lib_path, extra = OBJ_DIR, LIB_PATH, ()
     obj_dir.mkdir(parents=True, exist_ok=True)
     LIB_DIR.mkdir(parents=True, exist_ok=True)
     srcs = _sources()
@@ -80,8 +72,7 @@ def build(force: bool = False, verbose: bool = False, profile: bool = False) -> 
     if verbose:
         for log in logs:
             print(log)
-    if not profile:
-        (REPO / "build" / "ptxas.log").write_text("\n".join(logs))
+    (REPO / "build" / "ptxas.log").write_text("\n".join(logs))
     newest_obj = max(o.stat().st_mtime for o in objs)
     if force or not lib_path.exists() or lib_path.stat().st_mtime < newest_obj:
         # Export only the C ABI: the version script keeps b200_* global and makes every other
@@ -97,6 +88,5 @@ def build(force: bool = False, verbose: bool = False, profile: bool = False) -> 
 
 
 if __name__ == "__main__":
-    path = build(force="--force" in sys.argv, verbose="-v" in sys.argv or "--verbose" in sys.argv,
-                 profile="--profile" in sys.argv)
+    path = build(force="--force" in sys.argv, verbose="-v" in sys.argv or "--verbose" in sys.argv)
     print(path)

@@ -45,16 +45,22 @@ class GemmDesc(C.Structure):
     ]
 
 
+KERNEL_SIMT, KERNEL_TCGEN05, KERNEL_TCGEN05_PAIR = 0, 1, 2
+
+
+class GemmPlan(C.Structure):
+    """Mirror of `b200_gemm_plan`: kernel, tile width, K slices and tile order of one product."""
+    _fields_ = [("kernel", C.c_int32), ("block_n", C.c_int32), ("k_slices", C.c_int32), ("group_m", C.c_int32)]
+
+
 class AttnOperand(C.Structure):
     """Mirror of b200_attn_operand: element (b, h, s, d) at ptr[b*stride_b + h*stride_h + s*stride_s + d]."""
     _fields_ = [("ptr", C.c_void_p), ("stride_b", C.c_int64), ("stride_h", C.c_int64), ("stride_s", C.c_int64)]
 
 
 def lib_path() -> Path:
-    """The library this process binds: B200_TTPERF_LIB when set (a development variant built by build.py --profile),
-    else the product build."""
-    override = os.environ.get("B200_TTPERF_LIB")
-    return Path(override) if override else Path(__file__).resolve().parent / "lib" / "libb200ttperf.so"
+    """The library this process binds."""
+    return Path(__file__).resolve().parent / "lib" / "libb200ttperf.so"
 
 
 # name -> (restype, argtypes); kept in one table so tests can check it against the header.
@@ -87,6 +93,11 @@ SIGNATURES = {
     "b200_matmul_host": (C.c_int, [C.c_void_p, C.POINTER(GemmDesc), C.c_int]),
     "b200_gemm_scratch_bytes": (C.c_int, [C.c_void_p, C.POINTER(GemmDesc), C.POINTER(C.c_size_t)]),
     "b200_gemm_static_scratch": (C.c_int, [C.c_int, C.POINTER(GemmDesc), C.c_void_p]),
+    "b200_static_scratch_status": (C.c_int, [C.c_int, C.c_void_p, C.POINTER(C.c_int)]),
+    "b200_gemm_plan_query": (C.c_int, [C.c_void_p, C.POINTER(GemmDesc), C.POINTER(GemmPlan)]),
+    "b200_gemm_plan_describe": (C.c_int, [C.POINTER(GemmDesc), C.POINTER(GemmPlan), C.c_char_p, C.c_size_t]),
+    "b200_gemm_planned": (C.c_int, [C.c_void_p, C.POINTER(GemmDesc), C.POINTER(GemmPlan), C.c_void_p]),
+    "b200_selftest_wait_timeout": (C.c_int, [C.c_void_p, C.c_uint64, C.c_void_p]),
     "b200_ipc_get_handle": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p]),
     "b200_ipc_open_handle": (C.c_int, [C.c_void_p, C.c_void_p, C.POINTER(C.c_void_p)]),
     "b200_ipc_close_handle": (C.c_int, [C.c_void_p, C.c_void_p]),
@@ -147,6 +158,9 @@ SIGNATURES = {
     "b200_adam_step": (C.c_int, [C.c_void_p, C.c_int64, C.POINTER(C.c_void_p), C.POINTER(C.c_void_p), C.POINTER(C.c_void_p),
                                  C.POINTER(C.c_void_p), C.POINTER(C.c_void_p), C.POINTER(C.c_int64), C.c_int, C.c_int, C.c_float, C.c_float,
                                  C.c_float, C.c_float, C.c_int64, C.c_void_p]),
+    "b200_adam_step_device": (C.c_int, [C.c_void_p, C.c_int64, C.POINTER(C.c_void_p), C.POINTER(C.c_void_p), C.POINTER(C.c_void_p),
+                                        C.POINTER(C.c_void_p), C.POINTER(C.c_void_p), C.POINTER(C.c_int64), C.c_int, C.c_int,
+                                        C.c_float, C.c_float, C.c_float, C.c_float, C.c_void_p, C.c_int, C.c_void_p]),
 }
 
 U_NEG, U_RELU, U_GTZ, U_GELU, U_RSQRT, U_EXP, U_LOG, U_TANH, U_SQRT, U_ADD_SCALAR, U_MUL_SCALAR, U_RSUB_SCALAR, U_COPY, \
@@ -288,6 +302,32 @@ class Context:
 
     def gemm(self, desc: GemmDesc, stream=None) -> None:
         check(lib().b200_gemm(self._h, C.byref(desc), C.c_void_p(ptr(stream))))
+
+    def gemm_plan(self, desc: GemmDesc) -> GemmPlan:
+        """The plan b200_gemm follows for this product."""
+        plan = GemmPlan()
+        check(lib().b200_gemm_plan_query(self._h, C.byref(desc), C.byref(plan)))
+        return plan
+
+    @staticmethod
+    def gemm_plan_text(desc: GemmDesc, plan: GemmPlan) -> str:
+        buf = C.create_string_buffer(256)
+        check(lib().b200_gemm_plan_describe(C.byref(desc), C.byref(plan), buf, 256))
+        return buf.value.decode()
+
+    def gemm_planned(self, desc: GemmDesc, plan: GemmPlan, stream=None) -> None:
+        """The product with an explicit plan (kernel, tile width, K slices, tile order) instead of the library's own."""
+        check(lib().b200_gemm_planned(self._h, C.byref(desc), C.byref(plan), C.c_void_p(ptr(stream))))
+
+    def selftest_wait_timeout(self, limit_ns: int = 1_000_000, stream=None) -> None:
+        """Queues the one-CTA kernel whose bounded wait runs out after `limit_ns`; the next synchronize() reports it."""
+        check(lib().b200_selftest_wait_timeout(self._h, limit_ns, C.c_void_p(ptr(stream))))
+
+    def static_scratch_status(self, stream) -> int:
+        """Waits for `stream`, then reads and clears the status word of the static-scratch kernels (raises on a time-out)."""
+        out = C.c_int()
+        check(lib().b200_static_scratch_status(self.device, C.c_void_p(ptr(stream)), C.byref(out)))
+        return out.value
 
     def gemm_static_scratch(self, desc: GemmDesc, stream) -> None:
         """Split-K matmul whose partial sums use the library's fixed 32 MiB array: no device allocation at
@@ -439,6 +479,16 @@ class Context:
                                    self._ptr_array(v), self._ptr_array(shadows) if shadows else None,
                                    (C.c_int64 * n)(*sizes), p_dtype, g_dtype, lr, beta1, beta2, eps, step,
                                    self._s(stream)))
+
+    def adam_step_device(self, params, grads, m, v, sizes, state, *, advance=True, lr=1e-3, beta1=0.9, beta2=0.999, eps=1e-8,
+                         p_dtype=BF16, g_dtype=BF16, shadows=None, stream=None):
+        """Adam with the step number in the 16-byte device buffer `state` (zero-filled once by the caller): a step
+        recorded into a trace advances on every replay."""
+        n = len(params)
+        check(lib().b200_adam_step_device(self._h, n, self._ptr_array(params), self._ptr_array(grads), self._ptr_array(m),
+                                          self._ptr_array(v), self._ptr_array(shadows) if shadows else None,
+                                          (C.c_int64 * n)(*sizes), p_dtype, g_dtype, lr, beta1, beta2, eps, ptr(state),
+                                          int(bool(advance)), self._s(stream)))
 
     # ---- sharded matmul --------------------------------------------------------------------------------------------
     def ipc_get_handle(self, dptr) -> bytes:

@@ -89,17 +89,6 @@ __device__ __forceinline__ void drain(uint64_t* bar, uint32_t parity) {
     }
 }
 
-#ifdef B200_ATTN_PROFILE
-// Clock stamps of selected warps (instrumented build only): [cta slot][warp slot][tile][stamp].
-__device__ long long g_attn_prof[4][4][16][8];
-#define ATTN_STAMP(cta_slot, warp_slot, tile, k)                                                        \
-    do {                                                                                                \
-        if ((cta_slot) >= 0 && (warp_slot) >= 0 && (tile) < 16 && lane == 0)                            \
-            g_attn_prof[cta_slot][warp_slot][tile][k] = clock64();                                      \
-    } while (0)
-#else
-#define ATTN_STAMP(cta_slot, warp_slot, tile, k) do { } while (0)
-#endif
 
 // ------------------------------------------------------------------------------------------------------------------
 // Forward
@@ -165,10 +154,6 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
     const int q0 = qt * BT;
     const int n_kv_all = (g.S + BT - 1) / BT;
     const int n_kv = g.causal ? min(qt + 1, n_kv_all) : n_kv_all;
-#ifdef B200_ATTN_PROFILE
-    const int prof_cta = (blockIdx.x == 0 && blockIdx.y < 4) ? static_cast<int>(blockIdx.y) : -1;
-    const int prof_warp = warp == 0 ? 0 : (warp == 4 ? 1 : (warp == 3 ? 2 : -1));
-#endif
 
     if (threadIdx.x == 0) {
         prefetch_tensormap(&tmQ);
@@ -245,13 +230,11 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
     // that the other warps never wait for it at the named barriers.
     bool ok = true;
     for (int j = 0; j < n_kv; ++j) {
-        ATTN_STAMP(prof_cta, prof_warp, j, 0);
         if (ok) {
             // s_full of tile j is committed after the P V product of tile j - 1, so it covers both
             const bool got = mbar_wait(s_full, j & 1, abort_flag);
             ok = __all_sync(0xffffffffu, got);
         }
-        ATTN_STAMP(prof_cta, prof_warp, j, 1);
         if (threadIdx.x == 0 && ok && j + 1 < n_kv) load_kv(j + 1);  // its stage was last read by the P V product of j - 1
         __syncwarp();
         uint32_t s0[32], s1[32];
@@ -281,9 +264,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
             mine = ceil_bf16_bits(fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3])));
             xch[half * BT + r] = mine;
         }
-        ATTN_STAMP(prof_cta, prof_warp, j, 2);
         compute_warps_sync<FWD_THREADS>();
-        ATTN_STAMP(prof_cta, prof_warp, j, 3);
         if (ok) {
             // finite: every tile shows each row at least one key
             const float mx = fmaxf(m, fmaxf(bf16_bits_to_float(mine), bf16_bits_to_float(xch[(half ^ 1) * BT + r])));
@@ -312,7 +293,6 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
             fence_proxy_async_smem();
             tcgen05_fence_before_sync();
         }
-        ATTN_STAMP(prof_cta, prof_warp, j, 4);
         compute_warps_sync<FWD_THREADS>();  // P is complete in shared memory; S and the old P V product have been read
         if (threadIdx.x == 0 && ok && issuer_ok) {
             tcgen05_fence_after_sync();
@@ -333,7 +313,6 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
             }
         }
         __syncwarp();
-        ATTN_STAMP(prof_cta, prof_warp, j, 5);
     }
     if (ok) {
         const bool got = mbar_wait(o_full, 0, abort_flag);
@@ -431,10 +410,6 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
     const int n_q = (g.S + BT - 1) / BT;
     const int i0 = g.causal ? jt : 0;
     const int n_it = n_q - i0;
-#ifdef B200_ATTN_PROFILE
-    const int prof_cta = (blockIdx.x == 0 && blockIdx.y < 2) ? 2 + static_cast<int>(blockIdx.y) : -1;
-    const int prof_warp = warp == 0 ? 0 : (warp == 5 ? 1 : (warp == 15 ? 2 : (warp == BWD_COMPUTE_WARPS ? 3 : -1)));
-#endif
 
     if (threadIdx.x == 0) {
         prefetch_tensormap(&tmQ);
@@ -483,9 +458,7 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
             const uint32_t ka = smem_u32(sK), va = smem_u32(sV), pta = smem_u32(sPT), dsa = smem_u32(sdST);
             for (int it = 0; ok && it < n_it; ++it) {
                 const int st = it & 1;
-                ATTN_STAMP(prof_cta, prof_warp, it, 0);
                 if (!mbar_wait(&qdo_full[st], (it >> 1) & 1, abort_flag)) { ok = false; break; }
-                ATTN_STAMP(prof_cta, prof_warp, it, 1);
                 tcgen05_fence_after_sync();
                 const uint32_t qa = smem_u32(sQ + st * TILE_BYTES);
                 const uint32_t doa = smem_u32(sdO + st * TILE_BYTES);
@@ -500,9 +473,7 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
                 // This commit also covers the dV and dK products of the tile before: once it fires P^T and dS^T may be
                 // overwritten.
                 umma_commit(sdp_full);
-                ATTN_STAMP(prof_cta, prof_warp, it, 2);
                 if (!mbar_wait(pds_ready, it & 1, abort_flag)) { ok = false; break; }
-                ATTN_STAMP(prof_cta, prof_warp, it, 3);
                 tcgen05_fence_after_sync();
 #pragma unroll
                 for (int k = 0; k < BT / UMMA_K; ++k)   // dQ_i = dS K (reduction over the 128 keys); first, it is read first
@@ -520,7 +491,6 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
                                 make_smem_desc_sw128(qa + k * (UMMA_K * 128), BT * 128, 1024), idesc_kn,
                                 (it > 0 || k > 0) ? 1u : 0u);
                 umma_commit(acc_done);
-                ATTN_STAMP(prof_cta, prof_warp, it, 4);
                 if (it + 2 < n_it) {
                     if (!mbar_wait(acc_done, it & 1, abort_flag)) { ok = false; break; }  // Q_i, dO_i no longer read
                     load_qdo(it + 2);
@@ -559,14 +529,11 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
                 if (it + 1 < n_it) stat_next = stat_load(i + 1);
             }
             if (threadIdx.x == 0) tma_store_wait_read<1>();  // the dQ boxes of two tiles ago have left their buffer
-            ATTN_STAMP(prof_cta, prof_warp, it, 0);
             compute_warps_sync<BWD_COMPUTE_WARPS * 32>();
-            ATTN_STAMP(prof_cta, prof_warp, it, 1);
             if (ok) {
                 const bool got = mbar_wait(sdp_full, it & 1, abort_flag);
                 ok = __all_sync(0xffffffffu, got);
             }
-            ATTN_STAMP(prof_cta, prof_warp, it, 2);
             if (ok) {
                 tcgen05_fence_after_sync();
                 const bool diag = g.causal && i == jt;  // query (column) c sees key (row) r only when c >= r
@@ -598,14 +565,12 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
                     store_bf16x8(sPT + off, pf);
                     store_bf16x8(sdST + off, df);
                 }
-                ATTN_STAMP(prof_cta, prof_warp, it, 3);
                 fence_proxy_async_smem();
                 tcgen05_fence_before_sync();
                 __syncwarp();
                 if (lane == 0) mbar_arrive(pds_ready);
                 const bool got_dq = mbar_wait(dq_full, it & 1, abort_flag);
                 ok = __all_sync(0xffffffffu, got_dq);
-                ATTN_STAMP(prof_cta, prof_warp, it, 4);
             }
             if (ok) {
                 // dQ_i: TMEM -> two swizzled [128 x 32] fp32 boxes in shared memory -> one TMA reduction each adds them
@@ -621,7 +586,6 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
                         make_uint4(v[4 * t], v[4 * t + 1], v[4 * t + 2], v[4 * t + 3]);
                 fence_proxy_async_smem();
                 tcgen05_fence_before_sync();
-                ATTN_STAMP(prof_cta, prof_warp, it, 5);
             }
             compute_warps_sync<BWD_COMPUTE_WARPS * 32>();
             if (ok && threadIdx.x == 0) {
@@ -795,22 +759,6 @@ using namespace b200;
 
 extern "C" {
 
-#ifdef B200_ATTN_PROFILE
-int b200_debug_attn_occupancy_at(int smem, int* blocks) {
-    B200_CUDA_TRY(cudaOccupancyMaxActiveBlocksPerMultiprocessor(blocks, attn_fwd_kernel, FWD_THREADS, smem));
-    return B200_OK;
-}
-int b200_debug_attn_occupancy(int* fwd_blocks, int* bwd_blocks) {
-    B200_CUDA_TRY(cudaOccupancyMaxActiveBlocksPerMultiprocessor(fwd_blocks, attn_fwd_kernel, FWD_THREADS, FWD_SMEM));
-    B200_CUDA_TRY(cudaOccupancyMaxActiveBlocksPerMultiprocessor(bwd_blocks, attn_bwd_kernel, BWD_THREADS, BWD_SMEM));
-    return B200_OK;
-}
-int b200_debug_attn_prof(void* host_out) {
-    B200_CUDA_TRY(cudaDeviceSynchronize());
-    B200_CUDA_TRY(cudaMemcpyFromSymbol(host_out, g_attn_prof, sizeof(g_attn_prof)));
-    return B200_OK;
-}
-#endif
 
 int b200_attention_forward(b200_ctx* ctx, const b200_attn_operand* q, const b200_attn_operand* k, const b200_attn_operand* v,
                            const b200_attn_operand* o, float* lse, int64_t B, int64_t H, int64_t S, int head_dim,
@@ -861,7 +809,7 @@ int b200_attention_backward(b200_ctx* ctx, const b200_attn_operand* q, const b20
     cudaStream_t stream = ctx->pick(stream_v);
     const size_t rows = static_cast<size_t>(B) * H * S;
     const size_t acc_bytes = rows * DH * sizeof(float);
-    if ((rc = ensure_scratch(ctx, acc_bytes + rows * sizeof(float))) != B200_OK) return rc;
+    if ((rc = ensure_scratch(ctx, acc_bytes + rows * sizeof(float), stream)) != B200_OK) return rc;
     float* dq_acc = static_cast<float*>(ctx->d_scratch);
     float* dsum = dq_acc + rows * DH;
     CUtensorMap tmQ, tmK, tmV, tmdO;

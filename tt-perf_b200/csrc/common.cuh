@@ -9,6 +9,7 @@
 
 #include <mutex>
 #include <string>
+#include <vector>
 
 #include "../../include/b200_ttperf.h"
 
@@ -62,6 +63,16 @@ struct b200_ctx {
     int* d_status = nullptr;           // device word: non-zero once a kernel's bounded wait ran out
     void* d_scratch = nullptr;         // split-K partial sums and other per-call scratch
     size_t scratch_bytes = 0;
+    // Scratch blocks that were outgrown while a recorded trace may still hold their address: kept mapped until the last
+    // trace is released (or the context destroyed), because a replay writes to the address it recorded.
+    std::vector<void*> retired_scratch;
+    // The scratch, the ticket counters and the LayerNorm staging rows are one set per context. Calls that use them on
+    // different streams are put in order with this event (see order_shared_state); order_streams = false (the
+    // allocation-free entry point's parameter holder) leaves the ordering to the caller.
+    cudaStream_t shared_last_stream = nullptr;
+    bool shared_used = false;
+    cudaEvent_t shared_event = nullptr;
+    bool order_streams = true;
     b200::EncodeTiledFn encode_tiled = nullptr;
     // b200_matmul_host: device staging for host operands and the two copy streams of its pipeline
     void* d_stage[3] = {nullptr, nullptr, nullptr};
@@ -88,9 +99,17 @@ inline unsigned* ctx_tickets(const b200_ctx* ctx) { return reinterpret_cast<unsi
 inline float* ctx_ln_stage(const b200_ctx* ctx) {
     return reinterpret_cast<float*>(reinterpret_cast<char*>(ctx->d_status) + 256 + sizeof(unsigned) * kTicketCount);
 }
-// Grows the context scratch to at least `bytes` (never shrinks). Not allowed during stream capture.
-int ensure_scratch(b200_ctx* ctx, size_t bytes);
+// Grows the context scratch to at least `bytes` (never shrinks; not allowed while a trace is being recorded) and puts
+// `stream` in order behind the last stream that used the context's shared state (order_shared_state).
+int ensure_scratch(b200_ctx* ctx, size_t bytes, cudaStream_t stream);
+// A kernel about to use the context's scratch, ticket counters or LayerNorm staging on `stream` must not overlap the
+// previous user on another stream: when the stream changes, an event recorded on the previous stream is waited for
+// by the new one. Skipped while a trace is being recorded (record on the context stream only).
+int order_shared_state(b200_ctx* ctx, cudaStream_t stream);
+// Frees the retired scratch blocks; called when no trace is left that could refer to them.
+void release_retired_scratch(b200_ctx* ctx);
 // Pool / trace state attached to a context (pool.cu).
 void pool_destroy(b200_ctx* ctx);
 bool pool_is_recording(b200_ctx* ctx);
+bool pool_has_traces(b200_ctx* ctx);
 }  // namespace b200

@@ -2,6 +2,7 @@
 #include <stdarg.h>
 
 #include "common.cuh"
+#include "ptx.cuh"
 
 namespace b200 {
 
@@ -26,34 +27,91 @@ int fail(int code, const char* fmt, ...) {
     return code;
 }
 
-int ensure_scratch(b200_ctx* ctx, size_t bytes) {
-    if (bytes <= ctx->scratch_bytes) return B200_OK;
-    if (pool_is_recording(ctx))
-        return fail(B200_ERR_UNSUPPORTED, "an op needs %zu bytes of scratch while a trace is being recorded; run the step "
-                    "once untraced first so the scratch exists", bytes);
-    DeviceScope scope(ctx->device);
-    // Round up so that a sweep over growing shapes reallocates rarely.
-    size_t want = (bytes + (size_t(64) << 20) - 1) & ~((size_t(64) << 20) - 1);
-    if (ctx->d_scratch) {
-        B200_CUDA_TRY(cudaDeviceSynchronize());
-        B200_CUDA_TRY(cudaFree(ctx->d_scratch));
-        ctx->d_scratch = nullptr;
-        ctx->scratch_bytes = 0;
+int order_shared_state(b200_ctx* ctx, cudaStream_t stream) {
+    if (!ctx->order_streams || pool_is_recording(ctx)) return B200_OK;
+    std::lock_guard<std::mutex> lock(ctx->mu);
+    if (ctx->shared_used && ctx->shared_last_stream != stream) {
+        DeviceScope scope(ctx->device);
+        if (ctx->shared_event == nullptr) B200_CUDA_TRY(cudaEventCreateWithFlags(&ctx->shared_event, cudaEventDisableTiming));
+        B200_CUDA_TRY(cudaEventRecord(ctx->shared_event, ctx->shared_last_stream));
+        B200_CUDA_TRY(cudaStreamWaitEvent(stream, ctx->shared_event, 0));
     }
-    cudaError_t e = cudaMalloc(&ctx->d_scratch, want);
-    if (e != cudaSuccess) {
-        cudaGetLastError();
-        return fail(B200_ERR_NOMEM, "scratch allocation of %zu bytes failed: %s", want, cudaGetErrorString(e));
-    }
-    ctx->scratch_bytes = want;
+    ctx->shared_used = true;
+    ctx->shared_last_stream = stream;
     return B200_OK;
 }
 
+void release_retired_scratch(b200_ctx* ctx) {
+    if (ctx->retired_scratch.empty()) return;
+    DeviceScope scope(ctx->device);
+    cudaDeviceSynchronize();
+    for (void* p : ctx->retired_scratch) cudaFree(p);
+    ctx->retired_scratch.clear();
+}
+
+int ensure_scratch(b200_ctx* ctx, size_t bytes, cudaStream_t stream) {
+    if (bytes > ctx->scratch_bytes) {
+        if (pool_is_recording(ctx))
+            return fail(B200_ERR_UNSUPPORTED, "an op needs %zu bytes of scratch while a trace is being recorded; run the step "
+                        "once untraced first so the scratch exists", bytes);
+        DeviceScope scope(ctx->device);
+        // Round up so that a sweep over growing shapes reallocates rarely.
+        size_t want = (bytes + (size_t(64) << 20) - 1) & ~((size_t(64) << 20) - 1);
+        if (ctx->d_scratch) {
+            if (pool_has_traces(ctx)) {
+                // a recorded trace replays on the address it saw: the old block stays mapped until the traces are gone
+                ctx->retired_scratch.push_back(ctx->d_scratch);
+            } else {
+                B200_CUDA_TRY(cudaDeviceSynchronize());
+                B200_CUDA_TRY(cudaFree(ctx->d_scratch));
+            }
+            ctx->d_scratch = nullptr;
+            ctx->scratch_bytes = 0;
+        }
+        cudaError_t e = cudaMalloc(&ctx->d_scratch, want);
+        if (e != cudaSuccess) {
+            cudaGetLastError();
+            return fail(B200_ERR_NOMEM, "scratch allocation of %zu bytes failed: %s", want, cudaGetErrorString(e));
+        }
+        ctx->scratch_bytes = want;
+    }
+    return order_shared_state(ctx, stream);
+}
+
+}  // namespace b200
+
+namespace b200 {
+// One CTA waits on an mbarrier that nothing ever arrives at, with the same bounded wait the GEMM and attention kernels
+// use but a short limit, and then does what they do when a wait runs out: it raises the context's status word and
+// returns. Nothing faults and nothing hangs; it exists so that the error path (status word -> b200_synchronize ->
+// B200_ERR_DEVICE_TIMEOUT -> a clean context) can be exercised on demand.
+__global__ void wait_timeout_selftest_kernel(int* status, unsigned long long limit_ns) {
+    __shared__ __align__(8) uint64_t bar;
+    __shared__ int abort_flag;
+    if (threadIdx.x == 0) {
+        abort_flag = 0;
+        ptx::mbar_init(&bar, 1);
+        ptx::mbar_fence_init();
+    }
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        if (!ptx::mbar_wait(&bar, 0, &abort_flag, limit_ns)) atomicExch(status, 1);
+    }
+}
 }  // namespace b200
 
 using namespace b200;
 
 extern "C" {
+
+int b200_selftest_wait_timeout(b200_ctx* ctx, uint64_t limit_ns, void* stream) {
+    B200_REQUIRE(ctx != nullptr, "b200_selftest_wait_timeout: ctx is NULL");
+    B200_REQUIRE(limit_ns >= 1000 && limit_ns <= 100000000ull, "b200_selftest_wait_timeout: limit must be 1 us .. 100 ms");
+    DeviceScope scope(ctx->device);
+    wait_timeout_selftest_kernel<<<1, 32, 0, ctx->pick(stream)>>>(ctx->d_status, limit_ns);
+    B200_CUDA_TRY(cudaGetLastError());
+    return B200_OK;
+}
 
 const char* b200_last_error(void) { return g_last_error.c_str(); }
 
@@ -120,6 +178,8 @@ int b200_ctx_destroy(b200_ctx* ctx) {
     if (ctx->copy_in) cudaStreamDestroy(ctx->copy_in);
     if (ctx->copy_out) cudaStreamDestroy(ctx->copy_out);
     if (ctx->d_scratch) cudaFree(ctx->d_scratch);
+    for (void* p : ctx->retired_scratch) cudaFree(p);
+    if (ctx->shared_event) cudaEventDestroy(ctx->shared_event);
     if (ctx->d_status) cudaFree(ctx->d_status);
     if (ctx->stream) cudaStreamDestroy(ctx->stream);
     delete ctx;
@@ -153,7 +213,10 @@ int b200_synchronize(b200_ctx* ctx, void* stream) {
     int status = 0;
     B200_CUDA_TRY(cudaMemcpy(&status, ctx->d_status, sizeof(int), cudaMemcpyDeviceToHost));
     if (status != 0) {
-        cudaMemset(ctx->d_status, 0, sizeof(int));
+        // A CTA that gave up may have left ticket counters and LayerNorm staging rows non-zero; later kernels rely on
+        // finding them at zero, so the whole block is cleared, not only the status word.
+        cudaDeviceSynchronize();
+        cudaMemset(ctx->d_status, 0, b200::kStatusBytes);
         return fail(B200_ERR_DEVICE_TIMEOUT, "a kernel gave up a bounded wait (status word %d); its output is invalid",
                     status);
     }

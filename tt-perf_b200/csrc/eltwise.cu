@@ -812,7 +812,7 @@ int b200_reduce(b200_ctx* ctx, int op, const void* x, int64_t outer, int64_t R, 
     DeviceScope scope(ctx->device);
     cudaStream_t s = ctx->pick(stream);
     if (inner == 1 && R >= 16384 && outer <= ctx->sm_count && outer <= 65535) {
-        int rc = ensure_scratch(ctx, static_cast<size_t>(outer) * sizeof(float));
+        int rc = ensure_scratch(ctx, static_cast<size_t>(outer) * sizeof(float), s);
         if (rc != B200_OK) return rc;
         float* acc = static_cast<float*>(ctx->d_scratch);
         fill_f32_kernel<<<grid_for(ctx, outer), kThreads, 0, s>>>(acc, outer, op == R_MAX ? -FLT_MAX : 0.0f);
@@ -848,7 +848,7 @@ int b200_reduce(b200_ctx* ctx, int op, const void* x, int64_t outer, int64_t R, 
                                                                            (ctx->sm_count * 4ll) / std::max<long long>(1, col_blocks * outer)));
         const long long rows_per = (R + row_blocks - 1) / row_blocks;
         row_blocks = (R + rows_per - 1) / rows_per;
-        int rc = ensure_scratch(ctx, static_cast<size_t>(outs) * row_blocks * sizeof(float));
+        int rc = ensure_scratch(ctx, static_cast<size_t>(outs) * row_blocks * sizeof(float), s);
         if (rc != B200_OK) return rc;
         float* part = static_cast<float*>(ctx->d_scratch);
         dim3 grid(static_cast<unsigned>(col_blocks), static_cast<unsigned>(row_blocks), static_cast<unsigned>(outer));
@@ -862,7 +862,7 @@ int b200_reduce(b200_ctx* ctx, int op, const void* x, int64_t outer, int64_t R, 
         return B200_OK;
     }
     // very wide outputs: fp32 accumulators in context scratch combined with atomics, then a cast
-    int rc = ensure_scratch(ctx, static_cast<size_t>(outs) * sizeof(float));
+    int rc = ensure_scratch(ctx, static_cast<size_t>(outs) * sizeof(float), s);
     if (rc != B200_OK) return rc;
     float* acc = static_cast<float*>(ctx->d_scratch);
     fill_f32_kernel<<<grid_for(ctx, outs), kThreads, 0, s>>>(acc, outs, op == R_MAX ? -FLT_MAX : 0.0f);

@@ -26,7 +26,9 @@ __global__ void gemm_k0_kernel(int M, int N, int batch, void* C, long long ldc, 
     }
 }
 
-int validate(const b200_gemm_desc* d) {
+}  // namespace
+
+int gemm_validate_desc(const b200_gemm_desc* d) {
     B200_REQUIRE(d != nullptr, "b200_gemm: desc is NULL");
     B200_REQUIRE(d->M >= 0 && d->N >= 0 && d->K >= 0, "b200_gemm: negative dimension (M=%lld N=%lld K=%lld)",
                  (long long)d->M, (long long)d->N, (long long)d->K);
@@ -56,13 +58,76 @@ int validate(const b200_gemm_desc* d) {
     return B200_OK;
 }
 
-// The CTA-pair kernel serves large products; B200_GEMM_2CTA=0 keeps everything on the single-CTA kernel.
-bool pair_kernel_enabled() {
-    static const bool value = [] {
-        const char* e = getenv("B200_GEMM_2CTA");
-        return e == nullptr || atoi(e) != 0;
-    }();
-    return value;
+namespace {
+
+// The plan b200_gemm follows for a validated, non-empty product.
+b200_gemm_plan resolve_plan(const b200_ctx* ctx, const b200_gemm_desc& d) {
+    b200_gemm_plan out{};
+    if (d.algo == B200_GEMM_SIMT || !gemm_tcgen05_eligible(d, nullptr)) {
+        out.kernel = B200_GEMM_KERNEL_SIMT;
+        out.block_n = 64;
+        out.k_slices = 1;
+        return out;
+    }
+    const GemmPlan plan = gemm_plan(ctx, d, true);
+    out.kernel = plan.pair ? B200_GEMM_KERNEL_TCGEN05_PAIR : B200_GEMM_KERNEL_TCGEN05;
+    out.block_n = plan.pair ? 256 : plan.bn;
+    out.k_slices = plan.splits;
+    out.group_m = 0;
+    return out;
+}
+
+size_t plan_scratch_bytes(const b200_gemm_desc& d, const b200_gemm_plan& plan) {
+    if (plan.k_slices <= 1 || plan.kernel == B200_GEMM_KERNEL_SIMT) return 0;
+    if (plan.kernel == B200_GEMM_KERNEL_TCGEN05_PAIR)  // whole 256 x 256 tiles
+        return static_cast<size_t>(plan.k_slices) * d.batch * ((d.M + 255) / 256) * ((d.N + 255) / 256) * 256 * 256 * sizeof(float);
+    return static_cast<size_t>(plan.k_slices) * d.batch * d.M * d.N * sizeof(float);
+}
+
+int run_plan(b200_ctx* ctx, const b200_gemm_desc& d, const b200_gemm_plan& plan, cudaStream_t stream) {
+    switch (plan.kernel) {
+        case B200_GEMM_KERNEL_SIMT:
+            B200_REQUIRE(d.ab_dtype == B200_BF16, "b200_gemm: 8-bit operands run on the tcgen05 path only");
+            return launch_gemm_simt(ctx, d, stream);
+        case B200_GEMM_KERNEL_TCGEN05:
+            return launch_gemm_tcgen05(ctx, d, std::max(1, plan.k_slices), stream, nullptr, plan.block_n, plan.group_m);
+        case B200_GEMM_KERNEL_TCGEN05_PAIR:
+            B200_REQUIRE(gemm_pair_supported(d, nullptr), "b200_gemm: the CTA-pair kernel needs 16-byte aligned rows of C");
+            return launch_gemm_tcgen05_pair(ctx, d, stream, nullptr, std::max(1, plan.k_slices), plan.group_m);
+        default:
+            return fail(B200_ERR_INVALID_ARG, "b200_gemm: unknown kernel %d in the plan", plan.kernel);
+    }
+}
+
+// K == 0: nothing to multiply, C = act(mask(bias)).
+int run_k0(b200_ctx* ctx, const b200_gemm_desc* d, cudaStream_t stream) {
+    EpiParams epi{};
+    epi.alpha = d->alpha;
+    epi.bias = d->bias;
+    epi.bias_f32 = d->bias_dtype == B200_F32;
+    epi.act = d->activation;
+    epi.gelu_tanh = d->fidelity == B200_LOFI;
+    epi.causal = d->causal_mask;
+    epi.mask_value = d->mask_value;
+    const long long total = d->batch * d->M * d->N;
+    const int blocks = static_cast<int>(std::min<long long>((total + 255) / 256, ctx->sm_count * 8ll));
+    gemm_k0_kernel<<<blocks, 256, 0, stream>>>((int)d->M, (int)d->N, (int)d->batch, d->C, d->ldc, d->stride_c,
+                                               d->c_dtype == B200_F32, epi);
+    B200_CUDA_TRY(cudaGetLastError());
+    return B200_OK;
+}
+
+// Checks that apply to b200_gemm and b200_gemm_planned alike once the descriptor is valid and the product non-empty.
+int check_route(const b200_gemm_desc* d) {
+    const char* why = nullptr;
+    const bool eligible = gemm_tcgen05_eligible(*d, &why);
+    if (d->algo == B200_GEMM_TCGEN05 && !eligible)
+        return fail(B200_ERR_INVALID_ARG, "b200_gemm: tcgen05 path requested but %s", why);
+    if (d->ab_dtype == B200_FP8_E4M3) {  // tensor cores only: there is no scalar kernel for 8-bit operands
+        B200_REQUIRE(d->algo != B200_GEMM_SIMT, "b200_gemm: 8-bit operands run on the tcgen05 path only");
+        if (!eligible) return fail(B200_ERR_INVALID_ARG, "b200_gemm: 8-bit operands: %s", why);
+    }
+    return B200_OK;
 }
 
 }  // namespace
@@ -87,94 +152,87 @@ void b200_gemm_desc_init(b200_gemm_desc* d) {
     d->ab_dtype = B200_BF16;
 }
 
-#ifdef B200_GEMM_PROFILE
-// Development builds (-DB200_GEMM_PROFILE): the tcgen05 kernels write clock64() stamps for the first 8 tiles of every
-// CTA into the context scratch, 8 entries per tile: 0 / 1 first and last MMA issue of the tile, 2 epilogue begin (warp
-// 2), 3..6 epilogue end in warps 2..5; entry 7 of a CTA's first tile is the CTA's clock right after the start-up
-// barrier. prepare sizes and clears the area (call it before the launch to be examined, and use split_k = 1: K slices
-// use the same scratch); the second call copies `count` entries to the host after synchronising.
-int b200_debug_gemm_stamps_prepare(b200_ctx* ctx) {
-    B200_REQUIRE(ctx != nullptr, "b200_debug_gemm_stamps_prepare: ctx is NULL");
-    DeviceScope scope(ctx->device);
-    const size_t bytes = static_cast<size_t>(ctx->sm_count) * 64 * sizeof(long long);
-    int rc = ensure_scratch(ctx, bytes);
-    if (rc != B200_OK) return rc;
-    B200_CUDA_TRY(cudaMemsetAsync(ctx->d_scratch, 0, bytes, ctx->stream));
-    B200_CUDA_TRY(cudaStreamSynchronize(ctx->stream));
-    return B200_OK;
-}
-int b200_debug_gemm_stamps(b200_ctx* ctx, long long* host_out, size_t count) {
-    B200_REQUIRE(ctx && host_out, "b200_debug_gemm_stamps: NULL argument");
-    B200_REQUIRE(count * sizeof(long long) <= ctx->scratch_bytes, "b200_debug_gemm_stamps: more entries than prepared");
-    DeviceScope scope(ctx->device);
-    B200_CUDA_TRY(cudaDeviceSynchronize());
-    B200_CUDA_TRY(cudaMemcpy(host_out, ctx->d_scratch, count * sizeof(long long), cudaMemcpyDeviceToHost));
-    return B200_OK;
-}
-#endif
 
 int b200_gemm_scratch_bytes(b200_ctx* ctx, const b200_gemm_desc* d, size_t* out_bytes) {
     B200_REQUIRE(ctx && out_bytes, "b200_gemm_scratch_bytes: NULL argument");
-    int rc = validate(d);
+    int rc = gemm_validate_desc(d);
     if (rc != B200_OK) return rc;
     *out_bytes = 0;
     if (d->M == 0 || d->N == 0 || d->K == 0) return B200_OK;
-    if (d->algo == B200_GEMM_SIMT) return B200_OK;
-    if (!gemm_tcgen05_eligible(*d, nullptr)) return B200_OK;
-    const GemmPlan plan = gemm_plan(ctx, *d, pair_kernel_enabled() && gemm_tuned_block_n() == 0);
-    if (plan.splits > 1) {
-        if (plan.pair)  // whole 256 x 256 tiles
-            *out_bytes = static_cast<size_t>(plan.splits) * d->batch * ((d->M + 255) / 256) * ((d->N + 255) / 256) * 256 * 256 * sizeof(float);
-        else
-            *out_bytes = static_cast<size_t>(plan.splits) * d->batch * d->M * d->N * sizeof(float);
+    *out_bytes = plan_scratch_bytes(*d, resolve_plan(ctx, *d));
+    return B200_OK;
+}
+
+int b200_gemm_plan_query(b200_ctx* ctx, const b200_gemm_desc* d, b200_gemm_plan* out_plan) {
+    B200_REQUIRE(ctx && out_plan, "b200_gemm_plan_query: NULL argument");
+    int rc = gemm_validate_desc(d);
+    if (rc != B200_OK) return rc;
+    *out_plan = b200_gemm_plan{};
+    if (d->M == 0 || d->N == 0 || d->K == 0) {
+        out_plan->kernel = B200_GEMM_KERNEL_SIMT;
+        out_plan->k_slices = 1;
+        return B200_OK;
+    }
+    rc = check_route(d);
+    if (rc != B200_OK) return rc;
+    *out_plan = resolve_plan(ctx, *d);
+    return B200_OK;
+}
+
+int b200_gemm_plan_describe(const b200_gemm_desc* d, const b200_gemm_plan* plan, char* buf, size_t buf_bytes) {
+    B200_REQUIRE(d && plan && buf && buf_bytes > 0, "b200_gemm_plan_describe: NULL argument");
+    const char* a_major = d->transpose_a ? "MN-major A" : "K-major A";
+    const char* b_major = d->transpose_b ? "K-major B" : "MN-major B";
+    const char* ab = d->ab_dtype == B200_FP8_E4M3 ? "e4m3" : "bf16";
+    const int bk = gemm_bk_elems(*d);
+    switch (plan->kernel) {
+        case B200_GEMM_KERNEL_SIMT:
+            snprintf(buf, buf_bytes, "gemm_simt_kernel (CUDA cores, 64x64x16 tiles)");
+            break;
+        case B200_GEMM_KERNEL_TCGEN05:
+            snprintf(buf, buf_bytes, "gemm_tcgen05_kernel<%d, %s, %s, %s> (128x%dx%d tiles, %d K slice%s%s)", plan->block_n,
+                     a_major, b_major, ab, plan->block_n, bk, plan->k_slices, plan->k_slices == 1 ? "" : "s",
+                     plan->k_slices > 1 ? " + splitk_reduce_kernel" : "");
+            break;
+        case B200_GEMM_KERNEL_TCGEN05_PAIR:
+            snprintf(buf, buf_bytes, "gemm_tcgen05_2cta_kernel<%s, %s, %s> (cta_group::2, 256x256x%d tiles, %d K slice%s)", a_major,
+                     b_major, ab, bk, plan->k_slices, plan->k_slices == 1 ? "" : "s");
+            break;
+        default:
+            return fail(B200_ERR_INVALID_ARG, "b200_gemm_plan_describe: unknown kernel %d", plan->kernel);
     }
     return B200_OK;
 }
 
 int b200_gemm(b200_ctx* ctx, const b200_gemm_desc* d, void* stream_v) {
     B200_REQUIRE(ctx != nullptr, "b200_gemm: ctx is NULL");
-    int rc = validate(d);
+    int rc = gemm_validate_desc(d);
     if (rc != B200_OK) return rc;
     if (d->M == 0 || d->N == 0) return B200_OK;
     DeviceScope scope(ctx->device);
     cudaStream_t stream = ctx->pick(stream_v);
-    if (d->K == 0) {
-        EpiParams epi{};
-        epi.alpha = d->alpha;
-        epi.bias = d->bias;
-        epi.bias_f32 = d->bias_dtype == B200_F32;
-        epi.act = d->activation;
-        epi.gelu_tanh = d->fidelity == B200_LOFI;
-        epi.causal = d->causal_mask;
-        epi.mask_value = d->mask_value;
-        const long long total = d->batch * d->M * d->N;
-        const int blocks = static_cast<int>(std::min<long long>((total + 255) / 256, ctx->sm_count * 8ll));
-        gemm_k0_kernel<<<blocks, 256, 0, stream>>>((int)d->M, (int)d->N, (int)d->batch, d->C, d->ldc, d->stride_c,
-                                                   d->c_dtype == B200_F32, epi);
-        B200_CUDA_TRY(cudaGetLastError());
-        return B200_OK;
+    if (d->K == 0) return run_k0(ctx, d, stream);
+    rc = check_route(d);
+    if (rc != B200_OK) return rc;
+    return run_plan(ctx, *d, resolve_plan(ctx, *d), stream);
+}
+
+int b200_gemm_planned(b200_ctx* ctx, const b200_gemm_desc* d, const b200_gemm_plan* plan, void* stream_v) {
+    B200_REQUIRE(ctx && plan, "b200_gemm_planned: NULL argument");
+    int rc = gemm_validate_desc(d);
+    if (rc != B200_OK) return rc;
+    if (d->M == 0 || d->N == 0) return B200_OK;
+    DeviceScope scope(ctx->device);
+    cudaStream_t stream = ctx->pick(stream_v);
+    if (d->K == 0) return run_k0(ctx, d, stream);
+    rc = check_route(d);
+    if (rc != B200_OK) return rc;
+    B200_REQUIRE(plan->k_slices >= 0 && plan->group_m >= 0 && plan->group_m <= 64, "b200_gemm_planned: bad k_slices or group_m");
+    if (plan->kernel != B200_GEMM_KERNEL_SIMT) {
+        const char* why = nullptr;
+        if (!gemm_tcgen05_eligible(*d, &why)) return fail(B200_ERR_INVALID_ARG, "b200_gemm_planned: tcgen05 kernel requested but %s", why);
     }
-    const char* why = nullptr;
-    const bool eligible = gemm_tcgen05_eligible(*d, &why);
-    if (d->algo == B200_GEMM_TCGEN05 && !eligible)
-        return fail(B200_ERR_INVALID_ARG, "b200_gemm: tcgen05 path requested but %s", why);
-    if (d->ab_dtype == B200_FP8_E4M3) {  // tensor cores only: there is no scalar kernel for 8-bit operands
-        B200_REQUIRE(d->algo != B200_GEMM_SIMT, "b200_gemm: 8-bit operands run on the tcgen05 path only");
-        if (!eligible) return fail(B200_ERR_INVALID_ARG, "b200_gemm: 8-bit operands: %s", why);
-    }
-    if (d->algo == B200_GEMM_SIMT || !eligible) return launch_gemm_simt(ctx, *d, stream);
-    GemmPlan plan = gemm_plan(ctx, *d, pair_kernel_enabled() && gemm_tuned_block_n() == 0);
-    {
-        // tuning sweeps (B200_GEMM_TUNE=1): B200_GEMM_KERNEL=pair pins the CTA-pair kernel with the descriptor's split_k
-        static const bool tune = [] { const char* e = getenv("B200_GEMM_TUNE"); return e && atoi(e) != 0; }();
-        const char* k = tune ? getenv("B200_GEMM_KERNEL") : nullptr;
-        if (k && strcmp(k, "pair") == 0 && gemm_pair_supported(*d, nullptr)) {
-            plan.pair = true;
-            plan.splits = d->split_k > 1 ? static_cast<int>(d->split_k) : 1;
-        }
-    }
-    if (plan.pair) return launch_gemm_tcgen05_pair(ctx, *d, stream, nullptr, plan.splits);
-    return launch_gemm_tcgen05(ctx, *d, plan.splits, stream);
+    return run_plan(ctx, *d, *plan, stream);
 }
 
 }  // extern "C"

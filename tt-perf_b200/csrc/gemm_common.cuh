@@ -140,9 +140,6 @@ struct GemmParams {
     int n_dst;
     int scatter_rows;
     int dst_rotate;    // first destination each box is sent to (ranks start at different peers, so no peer is hit by all at once)
-#ifdef B200_GEMM_PROFILE
-    long long* prof;   // development builds only: per-CTA clock stamps
-#endif
 };
 
 // Destination tensor maps of the TMA-store epilogue.
@@ -160,8 +157,9 @@ struct GemmRoute {
 };
 
 // Host-side launchers implemented in the kernel translation units.
+// block_n = 0 lets the planner pick the tile width for k_splits; group_m = 0 takes the default tile order.
 int launch_gemm_tcgen05(b200_ctx* ctx, const b200_gemm_desc& d, int k_splits, cudaStream_t stream,
-                        const GemmRoute* route = nullptr);
+                        const GemmRoute* route = nullptr, int block_n = 0, int group_m = 0);
 // Sums `splits` fp32 slices [splits][batch][M][N], applies the descriptor's epilogue and writes C.
 int launch_splitk_reduce(b200_ctx* ctx, const b200_gemm_desc& d, const float* partial, int splits, cudaStream_t stream);
 // CTA-pair (cta_group::2) kernel for large products; `gemm_pair_eligible` says whether it applies.
@@ -169,7 +167,7 @@ bool gemm_pair_eligible(const b200_ctx* ctx, const b200_gemm_desc& d, const Gemm
 // Layouts the pair kernel can handle at all, whatever the tile count.
 bool gemm_pair_supported(const b200_gemm_desc& d, const GemmRoute* route);
 int launch_gemm_tcgen05_pair(b200_ctx* ctx, const b200_gemm_desc& d, cudaStream_t stream, const GemmRoute* route = nullptr,
-                             int k_splits = 1);
+                             int k_splits = 1, int group_m = 0);
 // Kernel, tile width and K-slice count for one product. allow_pair = false restricts the choice to the single-CTA kernel.
 struct GemmPlan {
     bool pair;   // CTA-pair kernel (256 x 256 tiles) instead of the single-CTA kernel
@@ -181,11 +179,9 @@ GemmPlan gemm_plan(const b200_ctx* ctx, const b200_gemm_desc& d, bool allow_pair
 inline int gemm_bk_elems(const b200_gemm_desc& d) { return d.ab_dtype == B200_FP8_E4M3 ? 128 : 64; }
 int launch_gemm_simt(b200_ctx* ctx, const b200_gemm_desc& d, cudaStream_t stream);
 bool gemm_tcgen05_eligible(const b200_gemm_desc& d, const char** why);
+// The descriptor checks of b200_gemm (sizes, enums, leading dimensions, batch strides); B200_OK or INVALID_ARG with text.
+int gemm_validate_desc(const b200_gemm_desc* d);
 // Chooses the K-slice count for the tcgen05 path (1 = no split).
 int gemm_choose_split_k(const b200_ctx* ctx, const b200_gemm_desc& d);
-// N-tile width (64, 128 or 256) the tcgen05 path uses for this problem.
-int gemm_choose_block_n(const b200_ctx* ctx, const b200_gemm_desc& d);
-// Non-zero while a tuning sweep (B200_GEMM_TUNE=1, B200_GEMM_BLOCK_N) pins the tile width of the single-CTA kernel.
-int gemm_tuned_block_n();
 
 }  // namespace b200

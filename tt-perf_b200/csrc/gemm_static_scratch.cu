@@ -17,8 +17,12 @@
 // — different streams, or different host threads — race on it. Issue them on one stream.
 //
 // Set-up. The first call on each device looks up the device addresses of the array and of the status
-// word (cudaGetSymbolAddress, with that device current) and raises the GEMM kernels' shared-memory limit
-// (cudaFuncSetAttribute). Make that first call before any stream capture begins.
+// word (cudaGetSymbolAddress, with that device current). The first call that uses a given kernel variant
+// (tile width x operand layouts) on a device also raises that kernel's shared-memory limit
+// (cudaFuncSetAttribute). Make one call of every shape class you will use before a stream capture begins.
+//
+// Errors. A bounded wait that runs out inside these kernels sets a status word next to the array;
+// b200_static_scratch_status reads and clears it (b200_synchronize knows nothing about it).
 #include <mutex>
 
 #include "gemm_common.cuh"
@@ -65,6 +69,7 @@ int static_ctx_for(int device, b200_ctx** out) {
         c->cc_major = prop.major;
         c->cc_minor = prop.minor;
         c->stream = nullptr;
+        c->order_streams = false;  // the caller keeps overlapping calls apart (documented); no event is created here
         c->d_status = static_cast<int*>(status_ptr);
         c->d_scratch = scratch_ptr;                    // fixed: ensure_scratch() never grows it because every
         c->scratch_bytes = B200_STATIC_SCRATCH_BYTES;  // request is checked against this size first
@@ -81,25 +86,17 @@ int static_ctx_for(int device, b200_ctx** out) {
 using namespace b200;
 
 extern "C" int b200_gemm_static_scratch(int device, const b200_gemm_desc* d, void* stream_v) {
-    B200_REQUIRE(d != nullptr, "b200_gemm_static_scratch: desc is NULL");
+    int rc = gemm_validate_desc(d);  // the same descriptor checks as b200_gemm
+    if (rc != B200_OK) return rc;
     B200_REQUIRE(stream_v != nullptr, "b200_gemm_static_scratch: pass the stream to run on (there is no context stream)");
-    B200_REQUIRE(d->M > 0 && d->N > 0 && d->K > 0 && d->batch >= 1,
-                 "b200_gemm_static_scratch: M, N, K must be positive and batch >= 1");
-    B200_REQUIRE(d->A && d->B && d->C, "b200_gemm_static_scratch: A, B or C is NULL");
-    B200_REQUIRE(d->c_dtype == B200_BF16 || d->c_dtype == B200_F32, "b200_gemm_static_scratch: bad c_dtype");
-    B200_REQUIRE(d->bias_dtype == B200_BF16 || d->bias_dtype == B200_F32, "b200_gemm_static_scratch: bad bias_dtype");
-    B200_REQUIRE(d->activation >= B200_ACT_NONE && d->activation <= B200_ACT_GELU, "b200_gemm_static_scratch: bad activation");
-    B200_REQUIRE(d->fidelity >= B200_LOFI && d->fidelity <= B200_HIFI4, "b200_gemm_static_scratch: bad fidelity");
-    B200_REQUIRE(d->ldc >= d->N, "b200_gemm_static_scratch: ldc < N");
-    B200_REQUIRE(d->lda >= (d->transpose_a ? d->M : d->K) && d->ldb >= (d->transpose_b ? d->K : d->N),
-                 "b200_gemm_static_scratch: lda or ldb shorter than a row");
-    B200_REQUIRE(d->split_k >= 0, "b200_gemm_static_scratch: split_k must be >= 0");
+    B200_REQUIRE(d->M > 0 && d->N > 0 && d->K > 0, "b200_gemm_static_scratch: M, N and K must be positive");
+    B200_REQUIRE(d->algo != B200_GEMM_SIMT, "b200_gemm_static_scratch: there is no SIMT path here");
     const char* why = nullptr;
     if (!gemm_tcgen05_eligible(*d, &why))
         return fail(B200_ERR_INVALID_ARG, "b200_gemm_static_scratch: %s (this entry point has no SIMT path)", why);
 
     b200_ctx* sctx = nullptr;
-    int rc = static_ctx_for(device, &sctx);
+    rc = static_ctx_for(device, &sctx);
     if (rc != B200_OK) return rc;
 
     // Same slice count b200_gemm would pick; when the caller left the choice open, lower it until the
@@ -121,4 +118,30 @@ extern "C" int b200_gemm_static_scratch(int device, const b200_gemm_desc* d, voi
                     (size_t)B200_STATIC_SCRATCH_BYTES);
     DeviceScope scope(device);
     return launch_gemm_tcgen05(sctx, *d, splits, static_cast<cudaStream_t>(stream_v));
+}
+
+// Reads and clears the status word of the static-scratch kernels on `device`: *out_status is non-zero when one of
+// their bounded waits ran out since the last call (the output of that launch is then invalid). Waits for the work
+// queued on `stream` first, so it is the counterpart of b200_synchronize for this entry point. Allocates nothing.
+extern "C" int b200_static_scratch_status(int device, void* stream_v, int* out_status) {
+    B200_REQUIRE(out_status != nullptr, "b200_static_scratch_status: out_status is NULL");
+    B200_REQUIRE(stream_v != nullptr, "b200_static_scratch_status: pass the stream the products ran on");
+    *out_status = 0;
+    b200_ctx* sctx = nullptr;
+    int rc = static_ctx_for(device, &sctx);
+    if (rc != B200_OK) return rc;
+    DeviceScope scope(device);
+    cudaStream_t stream = static_cast<cudaStream_t>(stream_v);
+    B200_CUDA_TRY(cudaStreamSynchronize(stream));
+    int status = 0;
+    B200_CUDA_TRY(cudaMemcpyAsync(&status, sctx->d_status, sizeof(int), cudaMemcpyDeviceToHost, stream));
+    B200_CUDA_TRY(cudaStreamSynchronize(stream));
+    if (status != 0) {
+        B200_CUDA_TRY(cudaMemsetAsync(sctx->d_status, 0, sizeof(g_static_status), stream));
+        B200_CUDA_TRY(cudaStreamSynchronize(stream));
+        *out_status = status;
+        return fail(B200_ERR_DEVICE_TIMEOUT, "a static-scratch kernel gave up a bounded wait (status word %d); its output is invalid",
+                    status);
+    }
+    return B200_OK;
 }

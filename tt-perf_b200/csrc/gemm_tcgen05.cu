@@ -123,9 +123,6 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
     __syncthreads();
     tcgen05_fence_after_sync();
     const uint32_t tmem_base = *tmem_slot;
-#ifdef B200_GEMM_PROFILE
-    if (p.prof && threadIdx.x == 0) p.prof[blockIdx.x * 64 + 7] = clock64();  // this CTA's time origin
-#endif
 
     if (warp == 0) {
         // ------------------------------------------------------------------ TMA producer
@@ -197,10 +194,6 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
                 if (!mbar_wait(&tmem_empty_bar[acc], acc_phase ^ 1u, abort_flag)) break;
                 tcgen05_fence_after_sync();
                 const uint32_t d_tmem = tmem_base + static_cast<uint32_t>(acc * BN);
-#ifdef B200_GEMM_PROFILE
-                const int prof_slot = (w - blockIdx.x) / gridDim.x;
-                if (p.prof && prof_slot < 8) p.prof[(blockIdx.x * 8 + prof_slot) * 8 + 0] = clock64();
-#endif
                 for (int kb = it.kb_begin; kb < it.kb_end; ++kb) {
                     if (!mbar_wait(&full_bar[stage], phase, abort_flag)) {
                         ok = false;
@@ -226,9 +219,6 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
                 }
                 if (!ok) break;
                 umma_commit(&tmem_full_bar[acc]);  // accumulator complete
-#ifdef B200_GEMM_PROFILE
-                if (p.prof && prof_slot < 8) p.prof[(blockIdx.x * 8 + prof_slot) * 8 + 1] = clock64();
-#endif
                 acc ^= 1;
                 if (acc == 0) acc_phase ^= 1u;
             }
@@ -245,10 +235,6 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
             const bool got = mbar_wait(&tmem_full_bar[acc], acc_phase, abort_flag);
             if (!__all_sync(0xffffffffu, got)) break;
             tcgen05_fence_after_sync();
-#ifdef B200_GEMM_PROFILE
-            const int eprof_slot = (w - blockIdx.x) / gridDim.x;
-            if (p.prof && eprof_slot < 8 && threadIdx.x == 64) p.prof[(blockIdx.x * 8 + eprof_slot) * 8 + 2] = clock64();
-#endif
             const int row = it.m0 + q * 32 + lane;
             const bool row_ok = row < p.M;
             const uint32_t taddr = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + static_cast<uint32_t>(acc * BN);
@@ -396,10 +382,6 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
                     }
                 }
             }
-#ifdef B200_GEMM_PROFILE
-            // end of this tile's epilogue in each of the four epilogue warps: entries 3..6 = warps 2..5
-            if (p.prof && eprof_slot < 8 && lane == 0) p.prof[(blockIdx.x * 8 + eprof_slot) * 8 + warp + 1] = clock64();
-#endif
             // Hand the accumulator buffer back to the MMA warp.
             tcgen05_fence_before_sync();
             __syncwarp();
@@ -627,39 +609,19 @@ GemmPlan gemm_plan(const b200_ctx* ctx, const b200_gemm_desc& d, bool allow_pair
     return best;
 }
 
-// B200_GEMM_TUNE=1 makes every launch read B200_GEMM_BLOCK_N (64, 128 or 256) so that a sweep can compare tile widths
-// inside one process; without it the planner decides.
-int gemm_tuned_block_n() {
-    static const bool enabled = [] { const char* e = getenv("B200_GEMM_TUNE"); return e && atoi(e) != 0; }();
-    if (!enabled) return 0;
-    const char* e = getenv("B200_GEMM_BLOCK_N");
-    const int v = e ? atoi(e) : 0;
-    return (v == 64 || v == 128 || v == 192 || v == 256) ? v : 0;
-}
-
-int gemm_choose_block_n(const b200_ctx* ctx, const b200_gemm_desc& d) {
-    const int forced = gemm_tuned_block_n();
-    if (forced && (forced == 64 || d.N > 64)) return forced;
-    return gemm_plan(ctx, d, false).bn;
-}
-
 int gemm_choose_split_k(const b200_ctx* ctx, const b200_gemm_desc& d) { return gemm_plan(ctx, d, false).splits; }
 
-int group_m_setting() {
-    static const int value = [] {
-        const char* e = getenv("B200_GEMM_GROUP_M");
-        const int v = e ? atoi(e) : 0;
-        return (v >= 1 && v <= 64) ? v : 16;
-    }();
-    return value;
-}
-
-int launch_gemm_tcgen05(b200_ctx* ctx, const b200_gemm_desc& d, int k_splits, cudaStream_t stream, const GemmRoute* route) {
+int launch_gemm_tcgen05(b200_ctx* ctx, const b200_gemm_desc& d, int k_splits, cudaStream_t stream, const GemmRoute* route,
+                        int block_n, int group_m) {
     const bool a_kmajor = d.transpose_a == 0;  // A stored [M,K]
     const bool b_kmajor = d.transpose_b != 0;  // B stored [N,K]
-    b200_gemm_desc planned = d;
-    planned.split_k = k_splits;  // the tile width that suits the slice count the caller settled on
-    const int bn = gemm_choose_block_n(ctx, planned);
+    int bn = block_n;
+    if (bn == 0) {
+        b200_gemm_desc planned = d;
+        planned.split_k = k_splits;  // the tile width that suits the slice count the caller settled on
+        bn = gemm_plan(ctx, planned, false).bn;
+    }
+    B200_REQUIRE(bn == 64 || bn == 128 || bn == 192 || bn == 256, "b200_gemm: tile width %d is not one of 64, 128, 192, 256", bn);
     const bool fp8 = d.ab_dtype == B200_FP8_E4M3;
     const int bk = gemm_bk_elems(d);
 
@@ -692,15 +654,12 @@ int launch_gemm_tcgen05(b200_ctx* ctx, const b200_gemm_desc& d, int k_splits, cu
     p.epi.causal = d.causal_mask;
     p.epi.mask_value = d.mask_value;
     p.status = ctx->d_status;
-    p.group_m = group_m_setting();
-#ifdef B200_GEMM_PROFILE
-    p.prof = static_cast<long long*>(ctx->d_scratch);  // b200_debug_gemm_stamps_prepare sized and cleared it
-#endif
+    p.group_m = (group_m >= 1 && group_m <= 64) ? group_m : 16;
     p.partial = nullptr;
     p.partial_round_bf16 = (d.fidelity == B200_LOFI || d.fidelity == B200_HIFI2) ? 1 : 0;
     if (k_splits > 1) {
         const size_t bytes = static_cast<size_t>(k_splits) * p.batch * p.M * p.N * sizeof(float);
-        int rc = ensure_scratch(ctx, bytes);
+        int rc = ensure_scratch(ctx, bytes, stream);
         if (rc != B200_OK) return rc;
         p.partial = static_cast<float*>(ctx->d_scratch);
     }

@@ -132,11 +132,6 @@ gemm_tcgen05_2cta_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_c
     cluster_sync_all();  // both CTAs' barriers are initialised before anyone signals across the pair
     tcgen05_fence_after_sync();
     const uint32_t tmem_base = *tmem_slot;
-#ifdef B200_GEMM_PROFILE
-    // SM clocks are not synchronised: every CTA notes its own clock right after the cluster-wide barrier, so that the
-    // stamps of the two CTAs of a pair can be put on one time axis (entry 7 of the CTA's first slot).
-    if (p.prof && threadIdx.x == 0) p.prof[blockIdx.x * 64 + 7] = clock64();
-#endif
 
     if (warp == 0) {
         // ------------------------------------------------------------------ TMA producer (both CTAs)
@@ -211,10 +206,6 @@ gemm_tcgen05_2cta_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_c
                 if (!mbar_wait(&tmem_empty_bar[acc], acc_phase ^ 1u, abort_flag)) break;
                 tcgen05_fence_after_sync();
                 const uint32_t d_tmem = tmem_base + static_cast<uint32_t>(acc * BN);
-#ifdef B200_GEMM_PROFILE
-                const int prof_slot = (w - cluster_id) / num_clusters;
-                if (p.prof && prof_slot < 8) p.prof[(blockIdx.x * 8 + prof_slot) * 8 + 0] = clock64();
-#endif
                 for (int kb = it.kb_begin; kb < it.kb_end; ++kb) {
                     if (!mbar_wait(&full_bar[stage], phase, abort_flag)) {
                         ok = false;
@@ -240,9 +231,6 @@ gemm_tcgen05_2cta_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_c
                 }
                 if (!ok) break;
                 umma_commit_pair(&tmem_full_bar[acc], 3);  // accumulator complete, both CTAs' epilogues may read
-#ifdef B200_GEMM_PROFILE
-                if (p.prof && prof_slot < 8) p.prof[(blockIdx.x * 8 + prof_slot) * 8 + 1] = clock64();
-#endif
                 if (two_bufs) {
                     acc ^= 1;
                     if (acc == 0) acc_phase ^= 1u;
@@ -272,10 +260,6 @@ gemm_tcgen05_2cta_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_c
                 break;
             }
             tcgen05_fence_after_sync();
-#ifdef B200_GEMM_PROFILE
-            const int eprof_slot = (w - cluster_id) / num_clusters;
-            if (p.prof && eprof_slot < 8 && threadIdx.x == 64) p.prof[(blockIdx.x * 8 + eprof_slot) * 8 + 2] = clock64();
-#endif
             const int m_cta = it.m0 + static_cast<int>(rank) * BM_CTA;
             const int row = m_cta + q * 32 + lane;
             const uint32_t taddr = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + static_cast<uint32_t>(acc * BN);
@@ -393,10 +377,6 @@ gemm_tcgen05_2cta_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_c
                     }
                 }
             }
-#ifdef B200_GEMM_PROFILE
-            // end of this tile's epilogue in the warps of the first column half: entries 3..6 = warps 2..5
-            if (p.prof && eprof_slot < 8 && lane == 0 && warp <= 5) p.prof[(blockIdx.x * 8 + eprof_slot) * 8 + warp + 1] = clock64();
-#endif
             // Hand the accumulator buffer back to the leader's MMA warp (remote arrive from the peer CTA).
             tcgen05_fence_before_sync();
             __syncwarp();
@@ -462,27 +442,12 @@ inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 
 
 }  // namespace
 
-// Accumulator columns the pair kernel allocates in each CTA's TMEM: 512 = double buffered (default),
-// 256 = single buffer. B200_GEMM_2CTA_TMEM_COLS overrides (development knob).
-static int pair_tmem_cols() {
-    static const int value = [] {
-        const char* e = getenv("B200_GEMM_2CTA_TMEM_COLS");
-        const int v = e ? atoi(e) : 0;
-        return (v == 256 || v == 512) ? v : 512;
-    }();
-    return value;
-}
+// Accumulator columns the pair kernel allocates in each CTA's TMEM: two 256-column buffers, so that the epilogue of one
+// tile runs under the main loop of the next.
+static int pair_tmem_cols() { return 512; }
 
-// Row-tiles (of 256 rows) per column sweep of the tile order; B200_GEMM_2CTA_GROUP_M overrides (development knob).
-static int pair_group_m(int num_m_tiles) {
-    static const int forced = [] {
-        const char* e = getenv("B200_GEMM_2CTA_GROUP_M");
-        const int v = e ? atoi(e) : 0;
-        return (v >= 1 && v <= 64) ? v : 0;
-    }();
-    if (forced) return forced;
-    return num_m_tiles >= 64 ? 16 : 8;  // measured: 8 is best up to 8192 rows, 16 at 16384
-}
+// Row-tiles (of 256 rows) per column sweep of the tile order. Measured: 8 is best up to 8192 rows, 16 at 16384.
+static int pair_group_m(int num_m_tiles) { return num_m_tiles >= 64 ? 16 : 8; }
 
 // Operand and output layouts the pair kernel can handle at all (its epilogue always stores through TMA).
 bool gemm_pair_supported(const b200_gemm_desc& d, const GemmRoute* route) {
@@ -510,7 +475,7 @@ bool gemm_pair_eligible(const b200_ctx* ctx, const b200_gemm_desc& d, const Gemm
 }
 
 int launch_gemm_tcgen05_pair(b200_ctx* ctx, const b200_gemm_desc& d, cudaStream_t stream, const GemmRoute* route,
-                             int k_splits) {
+                             int k_splits, int group_m) {
     const bool a_kmajor = d.transpose_a == 0;
     const bool b_kmajor = d.transpose_b != 0;
     const bool fp8 = d.ab_dtype == B200_FP8_E4M3;
@@ -536,7 +501,7 @@ int launch_gemm_tcgen05_pair(b200_ctx* ctx, const b200_gemm_desc& d, cudaStream_
         B200_REQUIRE(route == nullptr || route->n_dst == 0, "b200_gemm: routed outputs cannot be combined with K slices");
         B200_REQUIRE(tiles * 2 < kTicketCount, "b200_gemm: %lld tiles exceed the ticket counters of the sliced pair kernel", tiles);
         const size_t bytes = static_cast<size_t>(p.k_splits) * tiles * BM_PAIR * BN * sizeof(float);  // whole tiles
-        int rc_s = ensure_scratch(ctx, bytes);
+        int rc_s = ensure_scratch(ctx, bytes, stream);
         if (rc_s != B200_OK) return rc_s;
         p.partial = static_cast<float*>(ctx->d_scratch);
         p.tickets = ctx_tickets(ctx);
@@ -557,12 +522,9 @@ int launch_gemm_tcgen05_pair(b200_ctx* ctx, const b200_gemm_desc& d, cudaStream_
     p.epi.mask_value = d.mask_value;
     p.partial_round_bf16 = (d.fidelity == B200_LOFI || d.fidelity == B200_HIFI2) ? 1 : 0;
     p.status = ctx->d_status;
-    p.group_m = pair_group_m(p.num_m_tiles);
+    p.group_m = (group_m >= 1 && group_m <= 64) ? group_m : pair_group_m(p.num_m_tiles);
     p.epi_mode = 1;
     p.n_dst = 1;
-#ifdef B200_GEMM_PROFILE
-    p.prof = static_cast<long long*>(ctx->d_scratch);
-#endif
 
     CUtensorMap tmA, tmB;
     CMaps tmC;

@@ -27,7 +27,23 @@ struct TensorTable {
 
 struct AdamScalars {
     float lr, beta1, beta2, eps, inv_bias1, inv_bias2;
+    const float* dev_bias;  // non-null: the two bias-correction factors live in device memory (see adam_advance_kernel)
 };
+
+// Device-resident step state of an optimiser whose step may be replayed from a recorded trace: the step number and
+// the bias-correction factors 1 / (1 - beta^t) derived from it. Kernel arguments are frozen when a trace is recorded;
+// memory is not, so a replayed step advances like an eager one.
+struct AdamDeviceState {
+    long long step;
+    float inv_bias1, inv_bias2;
+};
+
+__global__ void adam_advance_kernel(AdamDeviceState* st, float beta1, float beta2) {
+    const long long t = st->step + 1;
+    st->step = t;
+    st->inv_bias1 = static_cast<float>(1.0 / (1.0 - pow(static_cast<double>(beta1), static_cast<double>(t))));
+    st->inv_bias2 = static_cast<float>(1.0 / (1.0 - pow(static_cast<double>(beta2), static_cast<double>(t))));
+}
 
 __device__ __forceinline__ void unpack8(const uint4& u, float (&f)[8]) {
     const uint32_t w[4] = {u.x, u.y, u.z, u.w};
@@ -74,7 +90,12 @@ __device__ __forceinline__ void store8(void* base, long long i, const float (&f)
 // tensor's last chunk fall straight through. Full, 16-byte aligned chunks use vector accesses with everything in
 // registers; the ragged tail (and unaligned tensors) go element by element.
 template <bool ADAM, bool P_F32, bool G_F32>
-__global__ void __launch_bounds__(kThreads) optim_kernel(const TensorTable t, const AdamScalars s) {
+__global__ void __launch_bounds__(kThreads) optim_kernel(const TensorTable t, const AdamScalars s_in) {
+    AdamScalars s = s_in;
+    if (ADAM && s.dev_bias != nullptr) {
+        s.inv_bias1 = s.dev_bias[0];
+        s.inv_bias2 = s.dev_bias[1];
+    }
     const int ti = blockIdx.y;
     const long long n = t.n[ti];
     void* const pp = t.p[ti];
@@ -207,6 +228,31 @@ int b200_adam_step(b200_ctx* ctx, int64_t count, void* const* params, const void
     s.inv_bias1 = static_cast<float>(1.0 / (1.0 - pow(static_cast<double>(beta1), static_cast<double>(step))));
     s.inv_bias2 = static_cast<float>(1.0 / (1.0 - pow(static_cast<double>(beta2), static_cast<double>(step))));
     return run_optim<true>(ctx, "b200_adam_step", count, params, grads, m, v, shadow_bf16, sizes, p_dtype, g_dtype, s,
+                           stream);
+}
+
+int b200_adam_step_device(b200_ctx* ctx, int64_t count, void* const* params, const void* const* grads, float* const* m,
+                          float* const* v, void* const* shadow_bf16, const int64_t* sizes, int p_dtype, int g_dtype, float lr,
+                          float beta1, float beta2, float eps, void* d_state16, int advance, void* stream) {
+    B200_REQUIRE(ctx != nullptr, "b200_adam_step_device: ctx is NULL");
+    B200_REQUIRE(d_state16 != nullptr && (reinterpret_cast<uintptr_t>(d_state16) & 7u) == 0,
+                 "b200_adam_step_device: d_state16 must be an 8-byte aligned device buffer of 16 bytes");
+    B200_REQUIRE(lr > 0.0f && eps > 0.0f, "b200_adam_step_device: lr and eps must be > 0");
+    B200_REQUIRE(beta1 > 0.0f && beta1 < 1.0f && beta2 > 0.0f && beta2 < 1.0f, "b200_adam_step_device: betas must be in (0, 1)");
+    AdamDeviceState* st = static_cast<AdamDeviceState*>(d_state16);
+    static_assert(sizeof(AdamDeviceState) == 16, "device step state is 16 bytes");
+    if (advance) {
+        DeviceScope scope(ctx->device);
+        adam_advance_kernel<<<1, 1, 0, ctx->pick(stream)>>>(st, beta1, beta2);
+        B200_CUDA_TRY(cudaGetLastError());
+    }
+    AdamScalars s{};
+    s.lr = lr;
+    s.beta1 = beta1;
+    s.beta2 = beta2;
+    s.eps = eps;
+    s.dev_bias = &st->inv_bias1;
+    return run_optim<true>(ctx, "b200_adam_step_device", count, params, grads, m, v, shadow_bf16, sizes, p_dtype, g_dtype, s,
                            stream);
 }
 

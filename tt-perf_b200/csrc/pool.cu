@@ -87,6 +87,7 @@ void pool_destroy(b200_ctx* ctx) {
 }
 
 bool pool_is_recording(b200_ctx* ctx) { return pool_of(ctx)->recording != 0; }
+bool pool_has_traces(b200_ctx* ctx) { return !pool_of(ctx)->traces.empty(); }
 
 }  // namespace b200
 
@@ -246,6 +247,7 @@ int b200_trace_release(b200_ctx* ctx, uint32_t trace_id) {
     for (auto& kv : p->blocks)
         if (kv.second.trace == trace_id) kv.second.trace = 0;
     p->traces.erase(it);
+    if (p->traces.empty()) release_retired_scratch(ctx);  // nothing recorded can refer to an outgrown scratch block now
     return B200_OK;
 }
 

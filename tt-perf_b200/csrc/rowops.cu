@@ -1428,6 +1428,10 @@ static int layernorm_backward_impl(const char* fn, b200_ctx* ctx, const void* dy
         const int vdy = vec_ok(dy, lddy), vx = vec_ok(x, ldx), vdx = dx ? vec_ok(dx, lddx) : 0, vg = gamma ? vec_ok(gamma, 8) : 0;
         const int vup = upstream ? vec_ok(upstream, ldup) : 0;
         const int blocks = std::max(1, std::min((r + 7) / 8, ctx->sm_count * 2));
+        {   // the staging rows and the ticket are one set per context: keep users on different streams apart
+            int rc_o = order_shared_state(ctx, s);
+            if (rc_o != B200_OK) return rc_o;
+        }
         if (vec_path) {
             static bool configured[64] = {};
             int dev = 0;

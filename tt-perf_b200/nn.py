@@ -11,6 +11,8 @@ from __future__ import annotations
 
 import math
 
+import numpy as np
+
 from . import capi
 from .capi import ACT_GELU, ACT_NONE, ACT_RELU, BF16, F32, FP8_E4M3
 from .tensor import DeviceTensor
@@ -222,13 +224,19 @@ class Adam:
         self.lr, self.beta1, self.beta2, self.eps = float(lr), float(betas[0]), float(betas[1]), float(eps)
         self.m = [DeviceTensor.zeros(ctx, p.shape, F32) for p in self.params]
         self.v = [DeviceTensor.zeros(ctx, p.shape, F32) for p in self.params]
-        self.t = 0
+        # The step number lives on the device ({int64 step, two bias-correction factors}): a step that was recorded
+        # into a trace then advances on every replay exactly like an eager step (py/optim.py:73-81 recurrence).
+        self.state = DeviceTensor.zeros(ctx, (4,), F32)
+
+    @property
+    def t(self) -> int:
+        """Steps taken so far (read back from the device)."""
+        return int(self.state.numpy().view(np.int64)[0])
 
     def step(self, grads, *, stream=None) -> None:
-        self.t += 1
-        self.ctx.adam_step(self.params, grads, self.m, self.v, [p.numel for p in self.params], self.t, lr=self.lr,
-                           beta1=self.beta1, beta2=self.beta2, eps=self.eps, p_dtype=self.params[0].dtype,
-                           g_dtype=grads[0].dtype, shadows=self.shadows, stream=stream)
+        self.ctx.adam_step_device(self.params, grads, self.m, self.v, [p.numel for p in self.params], self.state,
+                                  lr=self.lr, beta1=self.beta1, beta2=self.beta2, eps=self.eps,
+                                  p_dtype=self.params[0].dtype, g_dtype=grads[0].dtype, shadows=self.shadows, stream=stream)
 
 
 # ---------------------------------------------------------------------------------------------------------------
