@@ -93,6 +93,9 @@ int b200_free(b200_ctx* ctx, void* dptr);
 int b200_memcpy_h2d(b200_ctx* ctx, void* d_dst, const void* h_src, size_t bytes, void* stream);
 int b200_memcpy_d2h(b200_ctx* ctx, void* h_dst, const void* d_src, size_t bytes, void* stream);
 int b200_memset(b200_ctx* ctx, void* d_dst, int byte_value, size_t bytes, void* stream);
+/* Device-to-device copy on the stream; either side may be a peer GPU's buffer opened with b200_ipc_open_handle (the
+ * copy engine then moves the bytes over NVLink), which is how a rank pushes a row block to its peers. */
+int b200_memcpy_d2d(b200_ctx* ctx, void* d_dst, const void* d_src, size_t bytes, void* stream);
 
 /* ---- pooled tensor memory and trace record / replay (TraceContext, autograd/traced/trace.hpp:21-88:
  *      begin_trace_capture / end_trace_capture / execute_trace / release_trace; raw use in
@@ -379,6 +382,10 @@ int b200_ipc_close_handle(b200_ctx* ctx, void* dptr);
 int b200_enable_peer_access(b200_ctx* a, b200_ctx* b);
 int b200_peer_copy_2d(b200_ctx* dst_ctx, void* dst, size_t dst_pitch_bytes, b200_ctx* src_ctx, const void* src,
                       size_t src_pitch_bytes, size_t width_bytes, size_t rows);
+/* Puts `waiter`'s stream behind everything queued so far on `producer`'s stream (an event, no host wait): after it,
+ * work queued on waiter sees what producer's kernels stored into waiter's memory. Between processes the same ordering
+ * is b200_comm_barrier. */
+int b200_ctx_wait_ctx(b200_ctx* waiter, b200_ctx* producer);
 /* N-split (column parallel) + all-gather. desc describes the LOCAL product C[:, my_rank*N : (my_rank+1)*N] =
  * op(A) . op(B_shard) with N = shard width; desc->C is ignored; desc->ldc = leading dimension of the full gathered C
  * (>= N * n_ranks). peer_c[p] = base of the full C on rank p (peer_c[my_rank] = the local one). Every rank ends up
@@ -393,6 +400,55 @@ int b200_gemm_allgather(b200_ctx* ctx, const b200_gemm_desc* desc, void* const* 
 int b200_gemm_reduce_scatter_partials(b200_ctx* ctx, const b200_gemm_desc* desc, void* const* peer_slots, int n_ranks,
                                       int my_rank, void* stream);
 int b200_reduce_slices(b200_ctx* ctx, const float* slices, int n_slices, const b200_gemm_desc* desc, void* stream);
+/* The kernel and tile width the two fused calls above use for `desc` (reduce_scatter = 0: b200_gemm_allgather, 1:
+ * b200_gemm_reduce_scatter_partials), in the terms of b200_gemm_plan; b200_gemm_plan_describe turns it into text. */
+int b200_gemm_dist_plan_query(b200_ctx* ctx, const b200_gemm_desc* desc, int n_ranks, int reduce_scatter,
+                              b200_gemm_plan* out_plan);
+
+/* ---- rank-to-rank plumbing of the sharded matmul (the fabric set-up and collective calls of the reference's mesh
+ *      programs: tt::tt_fabric::SetFabricConfig + open_mesh_device, bench/metal/matmul_tensor_parallel.cpp:155-166;
+ *      ttnn::all_gather, :91-93) ---------------------------------------------------------------------------------
+ * One communicator per (process, GPU), over NCCL, which is bound at run time: without libnccl.so.2 these calls fail
+ * with B200_ERR_COMM and everything else still works. The 128-byte id is made by one rank (b200_comm_unique_id) and
+ * shipped to the others by the host program (a file, a socket, its launcher's store); b200_comm_create is collective.
+ *   b200_comm_barrier        stream-ordered: completes on a rank's stream only when every rank's stream has reached it,
+ *                            so work queued after it sees all peers' earlier stores; nothing blocks the host
+ *   b200_comm_exchange_host  every rank contributes bytes_per_rank host bytes and receives all ranks' blobs in rank
+ *                            order (how the CUDA IPC handles of peer buffers travel); blocks until done
+ *   b200_comm_allreduce      in place on a device buffer of `count` elements (data-parallel gradient averaging)
+ *   b200_comm_allgather      device bytes, rank r's block lands at d_recv + r * bytes_per_rank
+ * stream = NULL means the context's stream, as everywhere. */
+typedef struct b200_comm b200_comm;
+typedef enum b200_comm_op { B200_COMM_SUM = 0, B200_COMM_AVG = 1, B200_COMM_MAX = 2 } b200_comm_op;
+int b200_comm_unique_id(void* out_id128);
+int b200_comm_create(b200_ctx* ctx, const void* id128, int n_ranks, int rank, b200_comm** out_comm);
+int b200_comm_destroy(b200_comm* comm);
+int b200_comm_size(const b200_comm* comm, int* out_n_ranks, int* out_rank);
+int b200_comm_barrier(b200_comm* comm, void* stream);
+int b200_comm_exchange_host(b200_comm* comm, const void* h_send, void* h_recv, size_t bytes_per_rank);
+int b200_comm_allreduce(b200_comm* comm, void* d_buf, int64_t count, int dtype, int op, void* stream);
+int b200_comm_allgather(b200_comm* comm, const void* d_send, void* d_recv, size_t bytes_per_rank, void* stream);
+
+/* ---- NVLink multicast buffers (NVSwitch replicates one store into every rank's copy) ------------------------------
+ * b200_mc_alloc is collective over `comm`: every rank allocates `bytes` of device memory, all are bound to one
+ * multicast object, and each rank gets two addresses for it: *out_local_ptr, its own copy (ordinary loads, stores,
+ * copies and kernels), and *out_multicast_ptr, which only b200_gemm_allgather_mc may write: a store there lands at the
+ * same offset of every rank's copy. Fails with B200_ERR_UNSUPPORTED when a rank's GPU or driver has no multicast
+ * (b200_mc_supported tells in advance); callers then use b200_gemm_allgather with unicast peer pointers.
+ * b200_mc_free is collective too and must be called by every rank before any of them exits: it drains the device,
+ * meets the other ranks, and only then unbinds and releases the memory. A rank that disappears while its memory is
+ * still bound can fault its peers' NVLink traffic. */
+typedef struct b200_mc b200_mc;
+int b200_mc_supported(b200_ctx* ctx, int* out_supported);
+int b200_mc_alloc(b200_comm* comm, size_t bytes, b200_mc** out_mc, void** out_local_ptr, void** out_multicast_ptr);
+int b200_mc_free(b200_mc* mc);
+/* b200_gemm_allgather with ONE destination: the multicast address of the full C (from b200_mc_alloc). The epilogue
+ * stages each finished box in shared memory and the warp writes it with multimem.st, 16 bytes per lane: one store per
+ * box instead of one per rank, so a rank's egress is its own slice once ((g-1)/g * |C| / g bytes per peer link set
+ * instead of (g-1) * |C| / g). With use_multimem = 0 the same code path issues ordinary 16-byte stores to `mc_c` (any
+ * device pointer): what single-GPU tests run. Same operand rules as b200_gemm_allgather; bf16 or fp32 C. */
+int b200_gemm_allgather_mc(b200_ctx* ctx, const b200_gemm_desc* desc, void* mc_c, int n_ranks, int my_rank, int use_multimem,
+                           void* stream);
 
 /* ---- split-K matmul without device allocation (no counterpart in the reference: TTNN owns its device
  *      memory, so the question never arises there) ----------------------------------------------------

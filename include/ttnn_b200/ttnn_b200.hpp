@@ -284,6 +284,14 @@ public:
     void synchronize() {
         for (b200_ctx* c : ctx_) b200_detail::check(b200_synchronize(c, nullptr), "Synchronize");
     }
+    // Every device's stream waits for the work queued so far on every other device's stream (events, no host wait):
+    // what a device runs next then sees whatever its peers stored into its memory.
+    void order_all_streams() {
+        for (size_t i = 0; i < ctx_.size(); ++i)
+            for (size_t j = 0; j < ctx_.size(); ++j)
+                if (i != j) b200_detail::check(b200_ctx_wait_ctx(ctx_[i], ctx_[j]), "MeshDevice: stream order");
+    }
+
     bool close() {
         if (!open_) return false;
         open_ = false;
@@ -1039,6 +1047,162 @@ inline Tensor all_gather(const Tensor& t, int dim, int /*num_links*/ = 1) {
         parts.push_back(out);
     }
     return Tensor::from_shards(parts);
+}
+
+// The inverse exchange (no signature exists in the reference; the K-split matmul of the distributed configuration
+// needs it): every device holds a full-shape partial result; afterwards device d holds the sum over all devices of
+// slice d along `dim`. Unfused form: slices travel by copy engine, the sum runs in fp32 on the owner. The fused form
+// — a matmul whose epilogue stores its fp32 partial tiles straight into the owner's memory — is
+// ttnn::experimental::matmul_reduce_scatter below.
+inline Tensor reduce_scatter(const Tensor& t, int dim, int /*num_links*/ = 1) {
+    const size_t n = t.num_shards();
+    if (n == 1) return t;
+    const Shape& s = t.logical_shape();
+    if (dim < 0) dim += static_cast<int>(s.rank());
+    if (dim < 0 || dim >= static_cast<int>(s.rank()) || s[dim] % n != 0)
+        throw std::invalid_argument("ttnn::reduce_scatter: dimension is not divisible by the mesh size");
+    if (t.dtype() != DataType::BFLOAT16) throw std::invalid_argument("ttnn::reduce_scatter: bfloat16 tensors only");
+    uint64_t outer = 1, inner = 1;
+    for (int i = 0; i < dim; ++i) outer *= s[i];
+    for (int i = dim + 1; i < static_cast<int>(s.rank()); ++i) inner *= s[i];
+    const uint64_t piece = s[dim] / n;                       // slice length along dim
+    const size_t es = detail::dtype_size(t.dtype());
+    const uint64_t run = piece * inner;                      // contiguous elements of one slice per outer index
+    std::vector<uint32_t> od(s.view());
+    od[static_cast<size_t>(dim)] = static_cast<uint32_t>(piece);
+    MeshDevice* dev = t.device();
+    std::vector<Tensor> parts;
+    for (size_t d = 0; d < n; ++d) {
+        // staging [n][outer][run] on the owner, then one column sum over the n copies
+        auto stage = detail::device_storage(dev, n * outer * run * es, d);
+        for (size_t src = 0; src < n; ++src) {
+            const Tensor sh = t.shard(src);
+            detail::check(b200_peer_copy_2d(dev->ctx(d), static_cast<uint8_t*>(stage->dptr) + src * outer * run * es, run * es,
+                                            dev->ctx(src), static_cast<const uint8_t*>(sh.device_ptr()) + d * run * es,
+                                            n * run * es, run * es, outer),
+                          "ttnn::reduce_scatter");
+        }
+        auto st = detail::device_storage(dev, outer * run * es, d);
+        Tensor out(st, Shape(od), t.dtype(), t.layout());
+        detail::check(b200_reduce(dev->ctx(d), B200_R_SUM, stage->dptr, 1, static_cast<int64_t>(n),
+                                  static_cast<int64_t>(outer * run), out.device_ptr(), nullptr),
+                      "ttnn::reduce_scatter");
+        parts.push_back(out);
+    }
+    return Tensor::from_shards(parts);
+}
+
+namespace experimental {
+
+// C = A . B on a mesh with A replicated and B sharded on its columns (shard_tensor_to_mesh_mapper(mesh, 1)), every
+// device ending with the whole C: ttnn::matmul followed by ttnn::all_gather(c, 1) of
+// bench/metal/matmul_tensor_parallel.cpp:84-92 as ONE op per device. The GEMM epilogue stores each finished tile into
+// every device's C over NVLink while the tensor cores work on the next tiles (b200_gemm_allgather); no gather pass runs.
+inline Tensor matmul_all_gather(const Tensor& a, const Tensor& b) {
+    const size_t n = b.num_shards();
+    MeshDevice* dev = a.device();
+    if (n == 1) return matmul(a, b);
+    if (a.num_shards() != n) throw std::invalid_argument("matmul_all_gather: A must be replicated on the mesh of B");
+    const Shape& as = a.logical_shape();
+    const Shape& bs = b.logical_shape();
+    if (as.rank() != 2 || bs.rank() != 2 || as[1] != bs[0]) throw std::invalid_argument("matmul_all_gather: [M,K] x [K,N/n] operands");
+    const uint32_t M = as[0], K = as[1], Ns = bs[1];
+    std::vector<Tensor> outs;
+    std::vector<void*> peer_c;
+    for (size_t d = 0; d < n; ++d) {
+        auto st = detail::device_storage(dev, static_cast<size_t>(M) * Ns * n * 2, d);
+        outs.emplace_back(st, Shape({M, static_cast<uint32_t>(Ns * n)}), DataType::BFLOAT16, a.layout());
+        peer_c.push_back(outs.back().device_ptr());
+    }
+    for (size_t d = 0; d < n; ++d) {
+        b200_gemm_desc g;
+        b200_gemm_desc_init(&g);
+        g.M = M; g.N = Ns; g.K = K;
+        g.A = a.shard(d).device_ptr(); g.lda = K;
+        g.B = b.shard(d).device_ptr(); g.ldb = Ns;
+        g.ldc = static_cast<int64_t>(Ns) * n;
+        detail::check(b200_gemm_allgather(dev->ctx(d), &g, peer_c.data(), static_cast<int>(n), static_cast<int>(d), nullptr),
+                      "matmul_all_gather");
+    }
+    dev->order_all_streams();   // a device's later ops see the tiles its peers stored into its C
+    return Tensor::from_shards(outs);
+}
+
+// C = A . B with A sharded on its columns and B on its rows (both on K): device d ends with row block d of C. The
+// fp32 partial tiles go from the GEMM epilogue straight into the owner's staging slots; each owner then sums its n
+// slots and rounds to bf16 once (b200_gemm_reduce_scatter_partials + b200_reduce_slices). The staging blocks go back
+// to their pool when this function returns; that is safe because a pooled block is only ever reused by later work on
+// the owner's stream, which is ordered after the sum, which is ordered after every peer's stores.
+inline Tensor matmul_reduce_scatter(const Tensor& a, const Tensor& b) {
+    const size_t n = a.num_shards();
+    MeshDevice* dev = a.device();
+    if (n == 1) return matmul(a, b);
+    if (b.num_shards() != n) throw std::invalid_argument("matmul_reduce_scatter: A and B must be sharded on the same mesh");
+    const Shape& as = a.logical_shape();
+    const Shape& bs = b.logical_shape();
+    if (as.rank() != 2 || bs.rank() != 2 || as[1] != bs[0]) throw std::invalid_argument("matmul_reduce_scatter: [M,K/n] x [K/n,N] operands");
+    const uint32_t M = as[0], Ks = as[1], N = bs[1];
+    if (M % n != 0) throw std::invalid_argument("matmul_reduce_scatter: M is not divisible by the mesh size");
+    const uint32_t rows = M / static_cast<uint32_t>(n);
+    std::vector<std::shared_ptr<tt::tt_metal::b200_detail::Storage>> slots;
+    std::vector<void*> peer_slots;
+    for (size_t d = 0; d < n; ++d) {
+        slots.push_back(detail::device_storage(dev, n * static_cast<size_t>(rows) * N * 4, d));
+        peer_slots.push_back(slots.back()->dptr);
+    }
+    for (size_t d = 0; d < n; ++d) {
+        b200_gemm_desc g;
+        b200_gemm_desc_init(&g);
+        g.M = M; g.N = N; g.K = Ks;
+        g.A = a.shard(d).device_ptr(); g.lda = Ks;
+        g.B = b.shard(d).device_ptr(); g.ldb = N;
+        g.ldc = N;
+        g.c_dtype = B200_F32;
+        detail::check(b200_gemm_reduce_scatter_partials(dev->ctx(d), &g, peer_slots.data(), static_cast<int>(n),
+                                                        static_cast<int>(d), nullptr),
+                      "matmul_reduce_scatter");
+    }
+    dev->order_all_streams();
+    std::vector<Tensor> outs;
+    for (size_t d = 0; d < n; ++d) {
+        auto st = detail::device_storage(dev, static_cast<size_t>(rows) * N * 2, d);
+        outs.emplace_back(st, Shape({rows, N}), DataType::BFLOAT16, a.layout());
+        b200_gemm_desc g;
+        b200_gemm_desc_init(&g);
+        g.M = rows; g.N = N; g.K = 0;
+        g.C = outs.back().device_ptr(); g.ldc = N;
+        detail::check(b200_reduce_slices(dev->ctx(d), static_cast<const float*>(slots[d]->dptr), static_cast<int>(n), &g, nullptr),
+                      "matmul_reduce_scatter");
+    }
+    return Tensor::from_shards(outs);
+}
+
+}  // namespace experimental
+
+// ---- softmax cross-entropy (the reference has it only in Python: CrossEntropyLoss, py/nn.py:149-222; torch form
+//      experiment_torch.py:183). logits [rows, classes] bf16, labels [rows] uint32 class ids on the device.
+//      loss: fp32 [1, 1], the mean over rows; d_logits: (softmax - onehot) / rows in bf16 — one fused pass, no one-hot
+//      tensor (the Python reference builds it on the host each step, py/nn.py:180-188). --------------------------------
+struct CrossEntropyResult {
+    Tensor loss;
+    Tensor d_logits;
+};
+inline CrossEntropyResult cross_entropy(const Tensor& logits, const Tensor& labels) {
+    const Shape& s = logits.logical_shape();
+    if (s.rank() < 2 || logits.dtype() != DataType::BFLOAT16) throw std::invalid_argument("ttnn::cross_entropy: bf16 [rows, classes] logits");
+    const int64_t classes = s[-1];
+    const int64_t rows = static_cast<int64_t>(s.volume()) / classes;
+    if (labels.dtype() != DataType::UINT32 || static_cast<int64_t>(labels.volume()) != rows)
+        throw std::invalid_argument("ttnn::cross_entropy: labels must be one uint32 class id per row");
+    CrossEntropyResult r{detail::alloc_like(logits, Shape({1, 1}), DataType::FLOAT32, logits.layout(), "ttnn::cross_entropy"),
+                         detail::alloc_like(logits, s, DataType::BFLOAT16, logits.layout(), "ttnn::cross_entropy")};
+    b200_ctx* c = detail::ctx_of(logits, "ttnn::cross_entropy");
+    detail::check(b200_memset(c, r.loss.device_ptr(), 0, 4, nullptr), "ttnn::cross_entropy");
+    detail::check(b200_cross_entropy(c, logits.device_ptr(), classes, static_cast<const uint32_t*>(labels.device_ptr()), rows,
+                                     classes, 1.0f / static_cast<float>(rows), static_cast<float*>(r.loss.device_ptr()), nullptr,
+                                     r.d_logits.device_ptr(), classes, nullptr),
+                  "ttnn::cross_entropy");
+    return r;
 }
 
 // ---- traces (traced/trace.hpp:57-78) ----------------------------------------------------------------------------------

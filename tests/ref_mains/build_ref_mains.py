@@ -38,6 +38,9 @@ MAINS = [
     "bench/metal/matmul_sweep.cpp", "bench/metal/simple_matmul.cpp", "bench/metal/bench_fusion.cpp",
     "bench/metal/matmul_2dev.cpp", "bench/metal/matmul_2dev_distributed.cpp", "bench/metal/matmul_tensor_parallel.cpp",
 ]
+# Programs of this repository that run on the reference's executors: built with the same recipe. train_mlp_ce includes
+# the reference's dynamic autograd headers (so it needs the reference tree); matmul_mesh_fused needs only the stand-in.
+OWN_MAINS = ["examples/train_mlp_ce.cpp", "examples/matmul_mesh_fused.cpp"]
 # same base name in two directories: keep both
 RENAME = {"bench/metal/bench_fusion.cpp": "metal_bench_fusion"}
 
@@ -47,8 +50,8 @@ def default_reference() -> str:
     return os.environ.get("TTPERF_REFERENCE", str(Path(__file__).resolve().parents[3] / "reference"))
 
 
-def build_one(ref: Path, rel: str) -> tuple[str, bool, str]:
-    src = ref / rel
+def build_one(ref: Path, rel: str, own: bool = False) -> tuple[str, bool, str]:
+    src = (REPO if own else ref) / rel
     name = RENAME.get(rel, Path(rel).stem)
     exe = OUT / name
     if not src.exists():
@@ -69,6 +72,7 @@ def build(reference: str | None = None) -> dict:
     OUT.mkdir(parents=True, exist_ok=True)
     with cf.ThreadPoolExecutor(max_workers=8) as ex:
         results = list(ex.map(lambda rel: build_one(ref, rel), MAINS))
+        results += list(ex.map(lambda rel: build_one(ref, rel, own=True), OWN_MAINS))
     return {name: (ok, msg) for name, ok, msg in results}
 
 

@@ -1,6 +1,8 @@
 """Parity of the fused attention kernels (b200_attention_forward / b200_attention_backward) with the CPU oracle's
 materialised form S = q k^T * scale, mask, P = softmax(S), O = P v and its backward, through the C ABI.
-Tolerance: relative Frobenius error <= 1e-2 on O, dQ, dK, dV (bf16); lse absolute 2e-2."""
+Tolerance: relative Frobenius error <= 1e-2 on O, dQ, dK, dV (bf16); lse absolute 2e-2. Where the softmax is nearly
+one-hot, dS is the small remainder of a cancellation and the bf16 storage of P, dS and the forward output O dominates
+dQ and dK: that case is compared with the oracle that stores those tensors in bf16 too, at the same 1e-2."""
 import numpy as np
 import pytest
 
@@ -22,7 +24,7 @@ def _lse(q, k, scale, causal):
     return (m + np.log(np.exp(s - m).sum(-1, keepdims=True)))[..., 0]
 
 
-def _run(pkg, ctx, B, H, S, causal, layout, seed=0, qscale=1.0, grad_tol=TOL):
+def _run(pkg, ctx, B, H, S, causal, layout, seed=0, qscale=1.0, bf16_storage=False):
     """layout 'bhsd': separate [B,H,S,64] tensors. layout 'bsd3': q, k, v are column blocks of one [B,S,3*H*64] matrix
     (the output of a fused QKV projection) and o / gradients are [B,S,H*64] (no head split or merge copies)."""
     DT = pkg.DeviceTensor
@@ -51,7 +53,9 @@ def _run(pkg, ctx, B, H, S, causal, layout, seed=0, qscale=1.0, grad_tol=TOL):
     ctx.synchronize()
     scale = dh ** -0.5
     o_ref, p_ref = mo.causal_attention_forward(q, k, v, scale, causal=causal)
-    dq_ref, dk_ref, dv_ref = mo.causal_attention_backward(q, k, v, p_ref, d_o, scale)
+    dq_ref, dk_ref, dv_ref = mo.causal_attention_backward(q, k, v, p_ref, d_o, scale,
+                                                          quantize=mo.bf16_round if bf16_storage else None,
+                                                          o=mo.bf16_round(o_ref) if bf16_storage else None)
     if layout == "bhsd":
         got = dict(o=unpack(to), dq=unpack(tdq), dk=unpack(tdk), dv=unpack(tdv))
     else:
@@ -63,8 +67,7 @@ def _run(pkg, ctx, B, H, S, causal, layout, seed=0, qscale=1.0, grad_tol=TOL):
     for name in ("o", "dq", "dk", "dv"):
         assert np.isfinite(got[name]).all(), name
         err = mo.rel_frobenius(got[name], ref[name])
-        tol = grad_tol if name in ("dq", "dk") else TOL
-        assert err <= tol, f"{name}: relative Frobenius error {err:.3e} > {tol}"
+        assert err <= TOL, f"{name}: relative Frobenius error {err:.3e} > {TOL}"
     assert np.abs(lse.numpy() - _lse(q, k, scale, causal)).max() <= 2e-2
 
 
@@ -81,9 +84,9 @@ def test_attention_on_unpermuted_projection_output(pkg, ctx, B, H, S):
 
 def test_attention_large_scores(pkg, ctx):
     # scores of magnitude ~ 8 * 8 * sqrt(64) / 8: the running maximum has to keep exp() in range. The softmax is then
-    # nearly one-hot, dS = P * (dP - sum(dP * P)) is the small remainder of a cancellation, and the bf16 rounding of P and
-    # dS that any tensor-core attention applies shows in dQ and dK: 3e-2 for those two here, 1e-2 for O and dV.
-    _run(pkg, ctx, 1, 2, 256, True, "bhsd", seed=5, qscale=8.0, grad_tol=3e-2)
+    # nearly one-hot, dS = P * (dP - sum(dP * P)) is the small remainder of a cancellation, and the bf16 storage of P and
+    # dS that any tensor-core attention applies shows in dQ and dK: compared with the oracle that stores them in bf16.
+    _run(pkg, ctx, 1, 2, 256, True, "bhsd", seed=5, qscale=8.0, bf16_storage=True)
 
 
 def test_attention_rejects_other_head_dims(pkg, ctx):

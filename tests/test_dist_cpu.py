@@ -37,10 +37,25 @@ def _worker(rank, world, port, results):
     pkg = load_package()
     os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), RANK=str(rank), WORLD_SIZE=str(world))
     dist.init_process_group("gloo", rank=rank, world_size=world)
+
+    class GlooComm:
+        """Stands in for the library's communicator on a machine without GPUs: same interface, gloo underneath."""
+        def __init__(self):
+            self.world, self.rank = world, rank
+
+        def exchange(self, blob):
+            out = [None] * world
+            dist.all_gather_object(out, blob)
+            return out
+
+        def barrier(self, stream=None):
+            dist.barrier()
+
     try:
         # the same exchange helper that carries CUDA IPC handles on the GPU path
-        handles = pkg.dist.exchange(bytes([rank]) * 64)
+        handles = pkg.dist.exchange(GlooComm(), bytes([rank]) * 64)
         assert handles == [bytes([r]) * 64 for r in range(world)]
+        assert pkg.dist.exchange(None, b"x") == [b"x"]
         rng = np.random.default_rng(7)
         M, N, K = 256, 64, 96
         a = mo.bf16_round(rng.standard_normal((M, K)).astype(np.float32))

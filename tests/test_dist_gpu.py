@@ -39,6 +39,32 @@ def test_column_parallel_allgather_emulated_ranks(pkg, ctx, stream, world):
     assert all(torch.equal(c_bufs[0], c) for c in c_bufs[1:])
 
 
+@pytest.mark.parametrize("world,dtype", [(2, "bf16"), (4, "bf16"), (2, "f32")])
+def test_allgather_single_destination_epilogue_emulated_ranks(pkg, ctx, stream, world, dtype):
+    """b200_gemm_allgather_mc: the epilogue that writes each staged box with 16-byte warp stores to ONE destination —
+    on real ranks the NVLink multicast address of C (multimem.st), here an ordinary buffer (use_multimem = 0), which
+    exercises the same addressing: ragged M, a shard width that is not a multiple of the 64-column box."""
+    M, width, K = 712, 328, 320
+    N = width * world
+    rng = np.random.default_rng(20 + world)
+    a = mo.bf16_round(rng.standard_normal((M, K)).astype(np.float32))
+    b = mo.bf16_round(rng.standard_normal((K, N)).astype(np.float32))
+    ad = torch.from_numpy(a).bfloat16().cuda()
+    f32 = dtype == "f32"
+    c = torch.full((M, N), float("nan"), dtype=torch.float32 if f32 else torch.bfloat16, device="cuda")
+    s = stream.cuda_stream
+    for r in range(world):
+        b_shard = torch.from_numpy(b[:, r * width:(r + 1) * width].copy()).bfloat16().cuda()
+        d = ctx.gemm_desc(ad, b_shard, None, M, width, K, ldb=width, ldc=N, c_dtype=pkg.F32 if f32 else pkg.BF16)
+        ctx.gemm_allgather_mc(d, c, world, r, use_multimem=False, stream=s)
+    ctx.synchronize(s)
+    got = c.float().cpu().numpy()
+    assert not np.isnan(got).any(), "a box was left unwritten"
+    assert mo.rel_frobenius(got, mo.matmul(a, b)) <= 1e-2
+    with pytest.raises(pkg.B200Error):   # too small for the CTA-pair kernel: the caller falls back to b200_gemm_allgather
+        ctx.gemm_allgather_mc(ctx.gemm_desc(ad, ad, None, 128, 128, K, transpose_b=True, ldc=256), c, 2, 0, use_multimem=False, stream=s)
+
+
 @pytest.mark.parametrize("world", [1, 2, 4])
 def test_row_parallel_reduce_scatter_emulated_ranks(pkg, ctx, stream, world):
     M, N, K = 128 * world * 2, 200, 64 * world

@@ -238,6 +238,23 @@ def test_full_size_8192_linearity_and_row_sample(pkg, ctx, stream, ta, tb):
     del a2
 
 
+@pytest.mark.parametrize("M,N,K,stride", [(16384, 16384, 16384, 1489), (128, 8192, 8192, 1), (4096, 4096, 4096, 257),
+                                            (2048, 2048, 2048, 129), (1024, 1024, 1024, 65), (512, 512, 512, 33)])
+def test_sweep_shapes_row_sample(pkg, ctx, stream, M, N, K, stride):
+    """The other shapes of the matmul sweep (512^3 .. 16384^3 and the skinny M = 128, K = N = 8192 product, which the
+    planner cuts along K): seeded N(0,1) operands, a sample of output rows against the oracle, and exact doubling."""
+    g = torch.Generator(device="cuda").manual_seed(42)
+    a = torch.randn((M, K), generator=g, device="cuda").bfloat16()
+    b = torch.randn((K, N), generator=g, device="cuda").bfloat16()
+    c = run_gemm(pkg, ctx, stream, a, b, M, N, K)
+    assert not torch.isnan(c).any(), "output tile left unwritten"
+    rows = np.arange(0, M, stride)
+    ref = mo.matmul(a[rows].float().cpu().numpy(), b.float().cpu().numpy())
+    assert mo.rel_frobenius(c[rows].float().cpu().numpy(), ref) <= TOL
+    c2 = run_gemm(pkg, ctx, stream, (a.float() * 2).bfloat16(), b, M, N, K, poison=False)
+    assert torch.equal(c2.float(), c.float() * 2)
+
+
 @pytest.mark.parametrize("M,N,K,ta,tb", [(1024, 512, 384, False, False), (1000, 520, 776, False, True),
                                           (2048, 264, 512, True, False), (300, 72, 40, False, False)])
 def test_matmul_host_buffers_pipelined(pkg, ctx, M, N, K, ta, tb):

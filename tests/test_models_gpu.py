@@ -2,7 +2,14 @@
   * the 784-128-10 cross-entropy MLP, 10 SGD steps (loss within 1e-3, final weights within 1e-2 rel-Frobenius);
   * the reference's own MLP configurations (verify/verify_mlp.py, verify/verify_comparison.py, the constants of
     examples/train_mlp_traced.cpp:184-185);
-  * the pre-LN GPT-2 block forward + backward against the fixture produced by verify/compare_grads.py's torch block."""
+  * the pre-LN GPT-2 block forward + backward against the fixture produced by verify/compare_grads.py's torch block;
+  * the GPT-2-small and GPT-2-XL widths of the training configurations.
+
+Tolerances are the stated ones and nothing looser: relative Frobenius error <= 1e-2 for outputs and every gradient,
+<= 1e-3 for fp32 losses. The device stores activations and gradients in bf16 between kernels, as the reference's
+executors do between TTNN ops, so gradients that went through several such stores are compared with the oracle run
+with the same storage rounding (`quantize=mo.bf16_round`: the reference's math, rounded where a bf16 executor stores);
+the distance to the oracle without any rounding is printed for information (pytest -s)."""
 import json
 
 import numpy as np
@@ -12,6 +19,8 @@ from oracle import matmul_oracle as mo
 from conftest import GOLDEN
 
 pytestmark = pytest.mark.gpu
+TOL = 1e-2        # outputs and gradients (relative Frobenius error)
+LOSS_TOL = 1e-3   # fp32 losses (relative)
 
 
 def test_mlp_cross_entropy_784_128_10_ten_steps(pkg, ctx):
@@ -30,10 +39,17 @@ def test_mlp_cross_entropy_784_128_10_ten_steps(pkg, ctx):
         ref = float(z["losses"][step])
         assert abs(loss - ref) <= 1e-3 * abs(ref), (step, loss, ref)
         if step == 0:
-            # d_out rows sum to zero, so d_h = d_out . W2 cancels and amplifies the bf16 rounding of d_out: the
-            # layer-1 gradients are compared with a looser bar than the layer-2 ones
-            for g, name, tol in zip(grads, ("dw1_0", "db1_0", "dw2_0", "db2_0"), (6e-2, 6e-2, 1e-2, 1e-2)):
-                assert mo.rel_frobenius(g.numpy(), z[name]) <= tol, (name, mo.rel_frobenius(g.numpy(), z[name]))
+            # Layer 2 against the torch fp32 fixture directly. d_out rows sum to zero, so d_h = d_out . W2 cancels and
+            # amplifies the bf16 rounding of the stored d_out: layer 1 is compared with the oracle that stores d_out
+            # (and the other intermediates) in bf16 too.
+            for g, name in zip(grads[2:], ("dw2_0", "db2_0")):
+                assert mo.rel_frobenius(g.numpy(), z[name]) <= TOL, (name, mo.rel_frobenius(g.numpy(), z[name]))
+            _, _, qgrads = mo.mlp_train_step(mo.bf16_round(z["x"]), z["labels"], tuple(mo.bf16_round(z[k]) for k in names),
+                                             float(z["lr"]), "ce", quantize=mo.bf16_round)
+            for g, qg, name in zip(grads, qgrads, ("dw1_0", "db1_0", "dw2_0", "db2_0")):
+                print(f"{name}: vs bf16-storage oracle {mo.rel_frobenius(g.numpy(), qg):.2e}, vs fp32 fixture "
+                      f"{mo.rel_frobenius(g.numpy(), z[name]):.2e}")
+                assert mo.rel_frobenius(g.numpy(), qg) <= TOL, (name, mo.rel_frobenius(g.numpy(), qg))
     for p, name in zip(masters, ("w1_10", "b1_10", "w2_10", "b2_10")):
         assert mo.rel_frobenius(p.numpy(), z[name]) <= 1e-2, name
 
@@ -57,7 +73,7 @@ def test_mlp_cross_entropy_bf16_weights_follow_the_quantised_oracle(pkg, ctx):
         assert abs(loss - ref_loss) <= 1e-3 * abs(ref_loss), (step, loss, ref_loss)
         if step == 0:
             for g, rg, name in zip(grads, ref_grads, ("dw1", "db1", "dw2", "db2")):
-                assert mo.rel_frobenius(g.numpy(), rg) <= 2e-2, (name, mo.rel_frobenius(g.numpy(), rg))
+                assert mo.rel_frobenius(g.numpy(), rg) <= TOL, (name, mo.rel_frobenius(g.numpy(), rg))
 
 
 @pytest.mark.parametrize("which", ["verify_mlp", "verify_comparison"])
@@ -93,47 +109,74 @@ def _block_params(pkg, ctx, z):
     return {k[2:]: DT.from_numpy(ctx, z[k]) for k in z.files if k.startswith("p_")}
 
 
-def test_gpt2_block_forward_backward_matches_torch_fixture(pkg, ctx):
+def _check_block(pkg, ctx, x, d_out, w, heads, fp32_ref=None):
+    """Device block forward + backward against the oracle with bf16 storage points (<= TOL everywhere); prints the
+    distance to the oracle without rounding (or to `fp32_ref`, a fixture produced by torch)."""
     DT = pkg.DeviceTensor
+    wd = {k: DT.from_numpy(ctx, v) for k, v in w.items()}
+    wq = {k: mo.bf16_round(v) for k, v in w.items()}
+    xq, dq = mo.bf16_round(x), mo.bf16_round(d_out)
+    out, cache = pkg.nn.transformer_block_forward(ctx, DT.from_numpy(ctx, x), wd, heads)
+    d_x, grads = pkg.nn.transformer_block_backward(ctx, DT.from_numpy(ctx, d_out), wd, cache, heads)
+    q_out, q_cache = mo.transformer_block_forward(xq, wq, heads, quantize=mo.bf16_round)
+    q_dx, q_g = mo.transformer_block_backward(dq, wq, q_cache, heads, quantize=mo.bf16_round)
+    if fp32_ref is None:
+        f_out, f_cache = mo.transformer_block_forward(xq, wq, heads)
+        f_dx, f_g = mo.transformer_block_backward(dq, wq, f_cache, heads)
+    else:
+        f_out, f_dx, f_g = fp32_ref
+    got = {"out": out.numpy(), "dx": d_x.numpy(), **{k: grads[k].numpy() for k in q_g}}
+    want = {"out": q_out, "dx": q_dx, **q_g}
+    info = {"out": f_out, "dx": f_dx, **f_g}
+    scale = max(np.linalg.norm(q_g[k]) for k in q_g)
+    for k in want:
+        if k == "bk":   # key bias: mathematically zero (softmax is invariant to it); both sides hold rounding noise only
+            assert np.linalg.norm(got[k]) <= TOL * scale and np.linalg.norm(want[k]) <= TOL * scale, k
+            continue
+        err = mo.rel_frobenius(got[k], want[k])
+        print(f"{k}: vs bf16-storage oracle {err:.2e}, vs fp32 {mo.rel_frobenius(got[k], info[k]):.2e}")
+        assert err <= TOL, (k, err)
+    assert mo.rel_frobenius(got["out"], info["out"]) <= TOL       # the forward also meets the bar without any rounding
+
+
+def test_gpt2_block_forward_backward_matches_torch_fixture(pkg, ctx):
+    """Inputs and fp32 results of verify/compare_grads.py's torch block (tests/golden/block_small.npz)."""
     z = np.load(GOLDEN / "block_small.npz")
     heads = int(z["heads"])
-    w = _block_params(pkg, ctx, z)
-    out, cache = pkg.nn.transformer_block_forward(ctx, DT.from_numpy(ctx, z["x"]), w, heads)
-    assert mo.rel_frobenius(out.numpy(), z["out"]) <= 1e-2
-    d_x, grads = pkg.nn.transformer_block_backward(ctx, DT.from_numpy(ctx, z["d_out"]), w, cache, heads)
-    assert mo.rel_frobenius(d_x.numpy(), z["d_x"]) <= 2e-2
-    scale = max(np.linalg.norm(z["g_" + k]) for k in grads)
-    for k, g in grads.items():
-        ref = z["g_" + k]
-        if np.linalg.norm(ref) < 1e-5:
-            assert np.linalg.norm(g.numpy()) <= 1e-2 * scale, k   # key bias: mathematically zero
-        else:
-            # gradients pass through up to ten bf16-rounded stages; 3e-2 covers the accumulated rounding
-            assert mo.rel_frobenius(g.numpy(), ref) <= 3e-2, (k, mo.rel_frobenius(g.numpy(), ref))
+    w = {k[2:]: z[k] for k in z.files if k.startswith("p_")}
+    g_ref = {k[2:]: z[k] for k in z.files if k.startswith("g_")}
+    _check_block(pkg, ctx, z["x"], z["d_out"], w, heads, fp32_ref=(z["out"], z["d_x"], g_ref))
+
+
+def _random_block(rng, d, f, std=0.02):
+    shapes = dict(wq=(d, d), wk=(d, d), wv=(d, d), wo=(d, d), w1=(f, d), w2=(d, f))
+    w = {k: mo.bf16_round(rng.standard_normal(sh, dtype=np.float32) * std) for k, sh in shapes.items()}
+    for k, n in (("bq", d), ("bk", d), ("bv", d), ("bo", d), ("b1", f), ("b2", d), ("ln1_b", d), ("ln2_b", d)):
+        w[k] = mo.bf16_round(rng.standard_normal(n, dtype=np.float32) * 0.01)
+    w["ln1_g"] = mo.bf16_round(1 + 0.05 * rng.standard_normal(d, dtype=np.float32))
+    w["ln2_g"] = mo.bf16_round(1 + 0.05 * rng.standard_normal(d, dtype=np.float32))
+    return w
 
 
 def test_gpt2_block_larger_against_oracle(pkg, ctx):
     """B=2, S=256, D=256, H=4 (dh 64, the GPT-2 head width) against the numpy oracle on bf16-rounded weights."""
-    DT = pkg.DeviceTensor
     rng = np.random.default_rng(42)
     b, s, d, h = 2, 256, 256, 4
-    shapes = dict(wq=(d, d), wk=(d, d), wv=(d, d), wo=(d, d), w1=(4 * d, d), w2=(d, 4 * d))
-    w = {k: mo.bf16_round(rng.standard_normal(sh).astype(np.float32) * 0.02) for k, sh in shapes.items()}
-    for k, n in (("bq", d), ("bk", d), ("bv", d), ("bo", d), ("b1", 4 * d), ("b2", d), ("ln1_b", d), ("ln2_b", d)):
-        w[k] = np.zeros(n, np.float32)
-    w["ln1_g"] = np.ones(d, np.float32)
-    w["ln2_g"] = np.ones(d, np.float32)
-    x = mo.bf16_round(rng.standard_normal((b, s, d)).astype(np.float32) * 0.1)
-    d_out = mo.bf16_round(rng.standard_normal((b, s, d)).astype(np.float32) * 0.1)
-    wd = {k: DT.from_numpy(ctx, v) for k, v in w.items()}
-    out, cache = pkg.nn.transformer_block_forward(ctx, DT.from_numpy(ctx, x), wd, h)
-    ref_out, ref_cache = mo.transformer_block_forward(x, w, h)
-    assert mo.rel_frobenius(out.numpy(), ref_out) <= 1e-2
-    d_x, grads = pkg.nn.transformer_block_backward(ctx, DT.from_numpy(ctx, d_out), wd, cache, h)
-    ref_dx, ref_g = mo.transformer_block_backward(d_out, w, ref_cache, h)
-    assert mo.rel_frobenius(d_x.numpy(), ref_dx) <= 1e-2
-    for k in ("wq", "wk", "wv", "wo", "w1", "w2", "b1", "b2", "bo", "bv", "bq", "ln1_g", "ln2_g", "ln1_b", "ln2_b"):
-        assert mo.rel_frobenius(grads[k].numpy(), ref_g[k]) <= 2e-2, (k, mo.rel_frobenius(grads[k].numpy(), ref_g[k]))
+    w = _random_block(rng, d, 4 * d)
+    x = mo.bf16_round(rng.standard_normal((b, s, d), dtype=np.float32) * 0.1)
+    d_out = mo.bf16_round(rng.standard_normal((b, s, d), dtype=np.float32) * 0.1)
+    _check_block(pkg, ctx, x, d_out, w, h)
+
+
+def test_gpt2_xl_width_block_against_oracle(pkg, ctx):
+    """The tensor-parallel configuration's block at its own width on one GPU: d_model 1600, 25 heads, d_ff 6400,
+    seq 1024, batch 2 (as verify/compare_grads.py:140 scales its input: 0.1 N(0,1); weights N(0, 0.02))."""
+    rng = np.random.default_rng(1600)
+    b, s, d, h = 2, 1024, 1600, 25
+    w = _random_block(rng, d, 4 * d)
+    x = mo.bf16_round(rng.standard_normal((b, s, d), dtype=np.float32) * 0.1)
+    d_out = mo.bf16_round(rng.standard_normal((b, s, d), dtype=np.float32) * 0.1)
+    _check_block(pkg, ctx, x, d_out, w, h)
 
 
 def test_gpt2_model_loss_and_gradients_small_config(pkg, ctx):
@@ -161,17 +204,12 @@ def test_gpt2_model_loss_and_gradients_small_config(pkg, ctx):
     targets = rng.integers(0, V, (B, S)).astype(np.uint32)
     loss_t, grads = model.forward_backward(DT.from_numpy(ctx, ids, pkg.U32), DT.from_numpy(ctx, targets.ravel(), pkg.U32),
                                            DT.from_numpy(ctx, np.arange(S, dtype=np.uint32), pkg.U32))
-    ref_loss, ref = mo.gpt2_forward_backward(ids, targets, host, H)
+    ref_loss, _ = mo.gpt2_forward_backward(ids, targets, host, H)
+    q_loss, ref = mo.gpt2_forward_backward(ids, targets, host, H, quantize=mo.bf16_round)
     loss = float(loss_t.numpy()[0])
-    assert abs(loss - ref_loss) <= 1e-3 * abs(ref_loss), (loss, ref_loss)
-    assert mo.rel_frobenius(grads["head"].numpy()[:V], ref["head"]) <= 2e-2
-    assert np.all(grads["head"].numpy()[V:] == 0)
-    assert mo.rel_frobenius(grads["tok_emb"].numpy(), ref["tok_emb"]) <= 3e-2
-    assert mo.rel_frobenius(grads["pos_emb"].numpy(), ref["pos_emb"]) <= 3e-2
-    for i in range(L):
-        for k in ("wq", "wv", "wo", "w1", "w2", "ln1_g", "ln2_g", "b1"):
-            err = mo.rel_frobenius(grads["blocks"][i][k].numpy(), ref["blocks"][i][k])
-            assert err <= 4e-2, (i, k, err)
+    assert abs(loss - ref_loss) <= LOSS_TOL * abs(ref_loss), (loss, ref_loss)     # against the unrounded fp32 oracle
+    assert abs(loss - q_loss) <= LOSS_TOL * abs(q_loss), (loss, q_loss)
+    _compare_model_grads(grads, ref, V, L)
     before = model.params["blocks"][0]["w1"].numpy().copy()
     model.adam_step(grads)
     after = model.params["blocks"][0]["w1"].numpy()
@@ -181,6 +219,65 @@ def test_gpt2_model_loss_and_gradients_small_config(pkg, ctx):
     assert model.num_params() == sum(int(np.prod(v.shape)) for v in (host["tok_emb"], host["pos_emb"], host["lnf_g"],
                                                                      host["lnf_b"], host["head"])) + sum(
         int(np.prod(v.shape)) for blk in blocks for v in blk.values())
+
+
+def _compare_model_grads(grads, ref, V, L, keys=("wq", "wk", "wv", "wo", "w1", "w2", "ln1_g", "ln2_g", "b1", "b2", "bo")):
+    """Every gradient of the model against the bf16-storage oracle at TOL."""
+    errs = {"head": mo.rel_frobenius(grads["head"].numpy()[:V], ref["head"])}
+    assert np.all(grads["head"].numpy()[V:] == 0)
+    for k in ("tok_emb", "pos_emb", "lnf_g", "lnf_b"):
+        errs[k] = mo.rel_frobenius(grads[k].numpy(), ref[k])
+    for i in range(L):
+        for k in keys:
+            errs[f"block{i}.{k}"] = mo.rel_frobenius(grads["blocks"][i][k].numpy(), ref["blocks"][i][k])
+    print({k: f"{v:.2e}" for k, v in errs.items()})
+    bad = {k: v for k, v in errs.items() if not v <= TOL}
+    assert not bad, bad
+
+
+def test_gpt2_small_width_two_layer_slice_and_full_depth_loss(pkg, ctx):
+    """The GPT-2-small training configuration at its own width: d_model 768, 12 heads, d_ff 3072, seq 1024, vocab
+    50257, weights N(0, 0.02), uniform token ids. (a) a 2-layer slice at batch 2: loss and every gradient against the
+    oracle; (b) the full 12 layers at batch 1: the loss against the fp32 oracle within 1e-3."""
+    DT = pkg.DeviceTensor
+    D, H, S, V = 768, 12, 1024, 50257
+
+    def build(L, B, seed):
+        rng = np.random.default_rng(seed)
+        model = pkg.nn.GPT2(ctx, layers=L, d_model=D, heads=H, seq=S, vocab=V)
+
+        def w(*shape):
+            return mo.bf16_round(rng.standard_normal(shape, dtype=np.float32) * 0.02)
+
+        blocks = []
+        for _ in range(L):
+            blk = {}
+            for k, shape in model.block_shapes().items():
+                blk[k] = np.ones(shape, np.float32) if k.endswith("_g") else np.zeros(shape, np.float32) if len(shape) == 1 else w(*shape)
+            blocks.append(blk)
+        host = {"tok_emb": w(V, D), "pos_emb": w(S, D), "lnf_g": np.ones(D, np.float32), "lnf_b": np.zeros(D, np.float32),
+                "head": w(V, D), "blocks": blocks}
+        model.load(host)
+        ids = rng.integers(0, V, (B, S)).astype(np.uint32)
+        targets = np.roll(ids, -1, axis=1)
+        loss_t, grads = model.forward_backward(DT.from_numpy(ctx, ids, pkg.U32), DT.from_numpy(ctx, targets.ravel(), pkg.U32),
+                                               DT.from_numpy(ctx, np.arange(S, dtype=np.uint32), pkg.U32))
+        return host, ids, targets, float(loss_t.numpy()[0]), grads
+
+    host, ids, targets, loss, grads = build(2, 2, 768)
+    q_loss, ref = mo.gpt2_forward_backward(ids, targets, host, H, quantize=mo.bf16_round)
+    assert abs(loss - q_loss) <= LOSS_TOL * abs(q_loss), (loss, q_loss)
+    _compare_model_grads(grads, ref, V, 2)
+    del grads, ref
+    host, ids, targets, loss, _ = build(12, 1, 12)
+    params32 = host
+    # forward only on the CPU: the loss of the full-depth model
+    x = mo.embedding_forward(ids.astype(np.int64), params32["tok_emb"]) + params32["pos_emb"][None, :S]
+    for wb in params32["blocks"]:
+        x, _ = mo.transformer_block_forward(x, wb, H)
+    xf, _, _ = mo.layernorm_forward(x, params32["lnf_g"], params32["lnf_b"])
+    ref_loss, _ = mo.cross_entropy(mo.matmul(xf, params32["head"], False, True), targets)
+    assert abs(loss - ref_loss) <= LOSS_TOL * abs(ref_loss), (loss, ref_loss)
 
 
 def test_gpt2_weight_dump_and_reload_is_bit_exact(pkg, ctx, tmp_path):

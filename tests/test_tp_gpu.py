@@ -1,7 +1,8 @@
 """Tensor-parallel transformer block (the GPT-2-XL-shaped configuration, scaled down) against the single-device oracle.
 The ranks are emulated in one process on one GPU: every rank's kernels, peer stores and fused reduce-scatter epilogues
-run for real, a barrier is the stream order. Tolerances as for the single-device block: relative Frobenius error
-<= 1e-2 on the output, 2e-2 on dx, 3e-2 on the weight gradients (they pass through up to ten bf16-rounded stages)."""
+run for real, a barrier is the stream order. Tolerance: relative Frobenius error <= 1e-2 on the output, on dx and on
+every weight gradient, against the oracle block with bf16 storage points (the reference's math, rounded where a bf16
+executor stores a tensor between ops); the output is also held to 1e-2 against the oracle without rounding."""
 import numpy as np
 import pytest
 
@@ -50,8 +51,9 @@ def test_tp_block_matches_single_device_oracle(pkg, ctx, world):
     w = _weights(rng, d, f)
     x = mo.bf16_round(rng.standard_normal((b, s, d)).astype(np.float32) * 0.5)
     d_out = mo.bf16_round(rng.standard_normal((b, s, d)).astype(np.float32) * 0.1)
-    ref_out, ref_cache = mo.transformer_block_forward(x, w, heads)
-    ref_dx, ref_g = mo.transformer_block_backward(d_out, w, ref_cache, heads)
+    fp32_out, _ = mo.transformer_block_forward(x, w, heads)
+    ref_out, ref_cache = mo.transformer_block_forward(x, w, heads, quantize=mo.bf16_round)
+    ref_dx, ref_g = mo.transformer_block_backward(d_out, w, ref_cache, heads, quantize=mo.bf16_round)
 
     ranks, fabric = tp.make_emulated(ctx, world, batch=b, seq=s, d_model=d, heads=heads, host_w=w)
     try:
@@ -60,19 +62,19 @@ def test_tp_block_matches_single_device_oracle(pkg, ctx, world):
         dos = [DT.from_numpy(ctx, d_out.reshape(t, d)[r * tr:(r + 1) * tr]) for r in range(world)]
         tp.run_emulated([rk.forward(xs[i]) for i, rk in enumerate(ranks)])
         out = np.concatenate([rk.out.numpy() for rk in ranks]).reshape(b, s, d)
-        assert mo.rel_frobenius(out, ref_out) <= 1e-2
+        assert mo.rel_frobenius(out, ref_out) <= 1e-2 and mo.rel_frobenius(out, fp32_out) <= 1e-2
         tp.run_emulated([rk.backward(dos[i]) for i, rk in enumerate(ranks)])
         ctx.synchronize()
         dx = np.concatenate([rk.d_x.numpy() for rk in ranks]).reshape(b, s, d)
-        assert mo.rel_frobenius(dx, ref_dx) <= 2e-2
+        assert mo.rel_frobenius(dx, ref_dx) <= 1e-2
         got = _gather_grads(ranks, w, heads)
         scale = max(np.linalg.norm(ref_g[k]) for k in got)
         for k, gk in got.items():
-            if np.linalg.norm(ref_g[k]) < 1e-5:
-                assert np.linalg.norm(gk) <= 1e-2 * scale, k          # key bias: mathematically zero
+            if k == "bk":   # key bias: mathematically zero (softmax is invariant to it); only rounding noise on both sides
+                assert np.linalg.norm(gk) <= 1e-2 * scale and np.linalg.norm(ref_g[k]) <= 1e-2 * scale, k
             else:
                 err = mo.rel_frobenius(gk, ref_g[k])
-                assert err <= 3e-2, (k, err)
+                assert err <= 1e-2, (k, err)
         # one Adam step on a shard equals the oracle's update of the same rows
         before = ranks[1].w["w1"].numpy().copy()
         for rk in ranks:

@@ -106,7 +106,7 @@ def test_softmax_logsoftmax_cross_entropy_chain(tt):
     total = ttnn.sum(nll, dim=0, keepdim=False)
     loss = ttnn.mul(total, ttnn.full_like(total, fill_value=1.0 / (batch * seq)))
     ref = torch.nn.functional.cross_entropy(logits.float().reshape(-1, classes), targets)
-    assert abs(ttnn.to_torch(loss).float().item() - ref.item()) <= 2e-2 * abs(ref.item())
+    assert abs(ttnn.to_torch(loss).float().item() - ref.item()) <= 1e-2 * abs(ref.item())
     grad = ttnn.mul(ttnn.sub(p, toh), ttnn.full_like(p, fill_value=1.0 / (batch * seq)))
     ref_p = torch.softmax(logits.float().reshape(-1, classes), -1)
     assert _err(ttnn.to_torch(grad), (ref_p - one_hot.float()) / (batch * seq)) <= TOL
@@ -115,7 +115,7 @@ def test_softmax_logsoftmax_cross_entropy_chain(tt):
     tdy = ttnn.from_torch(dy, device=dev, layout=ttnn.TILE_LAYOUT, dtype=ttnn.bfloat16)
     dot = ttnn.sum(ttnn.mul(tdy, p), dim=-1, keepdim=True)
     gin = ttnn.mul(p, ttnn.sub(tdy, dot))
-    assert _err(ttnn.to_torch(gin), ref_p * (dy.float() - (dy.float() * ref_p).sum(-1, keepdim=True))) <= 2e-2
+    assert _err(ttnn.to_torch(gin), ref_p * (dy.float() - (dy.float() * ref_p).sum(-1, keepdim=True))) <= 1e-2
     mid = ttnn.softmax(tl, dim=1)
     assert _err(ttnn.to_torch(mid), torch.softmax(logits.float(), 1)) <= TOL
 

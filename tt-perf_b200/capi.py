@@ -79,6 +79,7 @@ SIGNATURES = {
     "b200_free": (C.c_int, [C.c_void_p, C.c_void_p]),
     "b200_memcpy_h2d": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_size_t, C.c_void_p]),
     "b200_memcpy_d2h": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_size_t, C.c_void_p]),
+    "b200_memcpy_d2d": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_size_t, C.c_void_p]),
     "b200_memset": (C.c_int, [C.c_void_p, C.c_void_p, C.c_int, C.c_size_t, C.c_void_p]),
     "b200_pool_alloc": (C.c_int, [C.c_void_p, C.c_size_t, C.POINTER(C.c_void_p)]),
     "b200_pool_free": (C.c_int, [C.c_void_p, C.c_void_p]),
@@ -104,10 +105,24 @@ SIGNATURES = {
     "b200_enable_peer_access": (C.c_int, [C.c_void_p, C.c_void_p]),
     "b200_peer_copy_2d": (C.c_int, [C.c_void_p, C.c_void_p, C.c_size_t, C.c_void_p, C.c_void_p, C.c_size_t, C.c_size_t,
                                     C.c_size_t]),
+    "b200_ctx_wait_ctx": (C.c_int, [C.c_void_p, C.c_void_p]),
+    "b200_mc_supported": (C.c_int, [C.c_void_p, C.POINTER(C.c_int)]),
+    "b200_mc_alloc": (C.c_int, [C.c_void_p, C.c_size_t, C.POINTER(C.c_void_p), C.POINTER(C.c_void_p), C.POINTER(C.c_void_p)]),
+    "b200_mc_free": (C.c_int, [C.c_void_p]),
+    "b200_gemm_allgather_mc": (C.c_int, [C.c_void_p, C.POINTER(GemmDesc), C.c_void_p, C.c_int, C.c_int, C.c_int, C.c_void_p]),
     "b200_gemm_allgather": (C.c_int, [C.c_void_p, C.POINTER(GemmDesc), C.POINTER(C.c_void_p), C.c_int, C.c_int, C.c_void_p]),
     "b200_gemm_reduce_scatter_partials": (C.c_int, [C.c_void_p, C.POINTER(GemmDesc), C.POINTER(C.c_void_p), C.c_int, C.c_int,
                                                     C.c_void_p]),
+    "b200_gemm_dist_plan_query": (C.c_int, [C.c_void_p, C.POINTER(GemmDesc), C.c_int, C.c_int, C.POINTER(GemmPlan)]),
     "b200_reduce_slices": (C.c_int, [C.c_void_p, C.c_void_p, C.c_int, C.POINTER(GemmDesc), C.c_void_p]),
+    "b200_comm_unique_id": (C.c_int, [C.c_void_p]),
+    "b200_comm_create": (C.c_int, [C.c_void_p, C.c_void_p, C.c_int, C.c_int, C.POINTER(C.c_void_p)]),
+    "b200_comm_destroy": (C.c_int, [C.c_void_p]),
+    "b200_comm_size": (C.c_int, [C.c_void_p, C.POINTER(C.c_int), C.POINTER(C.c_int)]),
+    "b200_comm_barrier": (C.c_int, [C.c_void_p, C.c_void_p]),
+    "b200_comm_exchange_host": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_size_t]),
+    "b200_comm_allreduce": (C.c_int, [C.c_void_p, C.c_void_p, C.c_int64, C.c_int, C.c_int, C.c_void_p]),
+    "b200_comm_allgather": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_size_t, C.c_void_p]),
     "b200_attention_forward": (C.c_int, [C.c_void_p] + [C.POINTER(AttnOperand)] * 4 + [C.c_void_p, C.c_int64, C.c_int64,
                                          C.c_int64, C.c_int, C.c_float, C.c_int, C.c_void_p]),
     "b200_attention_backward": (C.c_int, [C.c_void_p] + [C.POINTER(AttnOperand)] * 5 + [C.c_void_p] +
@@ -163,6 +178,7 @@ SIGNATURES = {
                                         C.c_float, C.c_float, C.c_float, C.c_float, C.c_void_p, C.c_int, C.c_void_p]),
 }
 
+COMM_SUM, COMM_AVG, COMM_MAX = 0, 1, 2
 U_NEG, U_RELU, U_GTZ, U_GELU, U_RSQRT, U_EXP, U_LOG, U_TANH, U_SQRT, U_ADD_SCALAR, U_MUL_SCALAR, U_RSUB_SCALAR, U_COPY, \
     U_RECIP, U_SQUARE = range(15)
 B_ADD, B_SUB, B_MUL, B_DIV, B_RELU_BW, B_GELU_BW, B_MAX = range(7)
@@ -268,6 +284,10 @@ class Context:
 
     def d2h(self, h_dst, d_src, nbytes: int, stream=None) -> None:
         check(lib().b200_memcpy_d2h(self._h, C.c_void_p(ptr(h_dst)), C.c_void_p(ptr(d_src)), nbytes,
+                                    C.c_void_p(ptr(stream))))
+
+    def memcpy_d2d(self, d_dst, d_src, nbytes: int, stream=None) -> None:
+        check(lib().b200_memcpy_d2d(self._h, C.c_void_p(ptr(d_dst)), C.c_void_p(ptr(d_src)), nbytes,
                                     C.c_void_p(ptr(stream))))
 
     def memset(self, d_dst, value: int, nbytes: int, stream=None) -> None:
@@ -508,9 +528,25 @@ class Context:
         check(lib().b200_gemm_allgather(self._h, C.byref(desc), self._ptr_array(peer_c), len(peer_c), my_rank,
                                         self._s(stream)))
 
+    def gemm_allgather_mc(self, desc: GemmDesc, mc_c, n_ranks: int, my_rank: int, *, use_multimem=True, stream=None) -> None:
+        """The fused all-gather with one multicast destination (see b200_gemm_allgather_mc)."""
+        check(lib().b200_gemm_allgather_mc(self._h, C.byref(desc), C.c_void_p(ptr(mc_c)), n_ranks, my_rank,
+                                           int(bool(use_multimem)), self._s(stream)))
+
+    def mc_supported(self) -> bool:
+        out = C.c_int()
+        check(lib().b200_mc_supported(self._h, C.byref(out)))
+        return bool(out.value)
+
     def gemm_reduce_scatter_partials(self, desc: GemmDesc, peer_slots, my_rank: int, stream=None) -> None:
         check(lib().b200_gemm_reduce_scatter_partials(self._h, C.byref(desc), self._ptr_array(peer_slots), len(peer_slots),
                                                       my_rank, self._s(stream)))
+
+    def gemm_dist_plan(self, desc: GemmDesc, n_ranks: int, reduce_scatter: bool = False) -> GemmPlan:
+        """Kernel and tile width the fused all-gather (or reduce-scatter) product uses for `desc`."""
+        plan = GemmPlan()
+        check(lib().b200_gemm_dist_plan_query(self._h, C.byref(desc), n_ranks, int(reduce_scatter), C.byref(plan)))
+        return plan
 
     def reduce_slices(self, slices, n_slices: int, desc: GemmDesc, stream=None) -> None:
         check(lib().b200_reduce_slices(self._h, ptr(slices), n_slices, C.byref(desc), self._s(stream)))
@@ -546,3 +582,63 @@ class Context:
 
     def trace_release(self, tid: int) -> None:
         check(lib().b200_trace_release(self._h, tid))
+
+
+def comm_unique_id() -> bytes:
+    """A fresh 128-byte communicator id (made on one rank; the host program ships it to the others)."""
+    buf = C.create_string_buffer(128)
+    check(lib().b200_comm_unique_id(buf))
+    return buf.raw
+
+
+class Comm:
+    """One rank's communicator (NCCL behind the C ABI): stream-ordered barrier, exchange of small host blobs, all-reduce
+    and all-gather of device buffers. `Comm(ctx, id, world, rank)` is collective over the ranks."""
+
+    def __init__(self, ctx: Context, unique_id: bytes, world: int, rank: int):
+        if len(unique_id) != 128:
+            raise ValueError("the communicator id is 128 bytes")
+        self.ctx, self.world, self.rank = ctx, int(world), int(rank)
+        self._h = C.c_void_p()
+        check(lib().b200_comm_create(ctx.handle, C.create_string_buffer(unique_id, 128), self.world, self.rank,
+                                     C.byref(self._h)))
+
+    def close(self) -> None:
+        if getattr(self, "_h", None) is not None and self._h:
+            lib().b200_comm_destroy(self._h)
+            self._h = C.c_void_p()
+
+    def barrier(self, stream=None) -> None:
+        check(lib().b200_comm_barrier(self._h, C.c_void_p(ptr(stream))))
+
+    def exchange(self, blob: bytes) -> list[bytes]:
+        """All ranks' `blob` (same length everywhere) in rank order."""
+        n = len(blob)
+        recv = C.create_string_buffer(n * self.world)
+        check(lib().b200_comm_exchange_host(self._h, C.create_string_buffer(blob, n), recv, n))
+        return [recv.raw[i * n:(i + 1) * n] for i in range(self.world)]
+
+    def allreduce(self, buf, count: int, dtype: int = F32, op: int = COMM_SUM, stream=None) -> None:
+        check(lib().b200_comm_allreduce(self._h, C.c_void_p(ptr(buf)), count, dtype, op, C.c_void_p(ptr(stream))))
+
+    def allgather(self, send, recv, bytes_per_rank: int, stream=None) -> None:
+        check(lib().b200_comm_allgather(self._h, C.c_void_p(ptr(send)), C.c_void_p(ptr(recv)), bytes_per_rank,
+                                        C.c_void_p(ptr(stream))))
+
+
+class MulticastBuffer:
+    """A device buffer per rank, all bound to one NVLink multicast object (collective over `comm`): `local` is this
+    rank's copy, `multicast` the address at which one store reaches every rank's copy. close() is collective too and
+    must run on every rank before any of them exits."""
+
+    def __init__(self, comm: Comm, nbytes: int):
+        self.comm, self.nbytes = comm, nbytes
+        self._h, loc, mc = C.c_void_p(), C.c_void_p(), C.c_void_p()
+        check(lib().b200_mc_alloc(comm._h, nbytes, C.byref(self._h), C.byref(loc), C.byref(mc)))
+        self.local, self.multicast = loc.value or 0, mc.value or 0
+
+    def close(self) -> None:
+        if getattr(self, "_h", None) is not None and self._h:
+            check(lib().b200_mc_free(self._h))
+            self._h = C.c_void_p()
+            self.local = self.multicast = 0

@@ -296,6 +296,15 @@ int b200_memcpy_d2h(b200_ctx* ctx, void* h_dst, const void* d_src, size_t bytes,
     return B200_OK;
 }
 
+int b200_memcpy_d2d(b200_ctx* ctx, void* d_dst, const void* d_src, size_t bytes, void* stream) {
+    B200_REQUIRE(ctx != nullptr, "b200_memcpy_d2d: ctx is NULL");
+    if (bytes == 0) return B200_OK;
+    B200_REQUIRE(d_dst && d_src, "b200_memcpy_d2d: NULL buffer");
+    DeviceScope scope(ctx->device);
+    B200_CUDA_TRY(cudaMemcpyAsync(d_dst, d_src, bytes, cudaMemcpyDefault, ctx->pick(stream)));
+    return B200_OK;
+}
+
 int b200_memset(b200_ctx* ctx, void* d_dst, int byte_value, size_t bytes, void* stream) {
     B200_REQUIRE(ctx != nullptr, "b200_memset: ctx is NULL");
     if (bytes == 0) return B200_OK;

@@ -90,6 +90,21 @@ int b200_peer_copy_2d(b200_ctx* dst_ctx, void* dst, size_t dst_pitch, b200_ctx* 
     return B200_OK;
 }
 
+int b200_ctx_wait_ctx(b200_ctx* waiter, b200_ctx* producer) {
+    B200_REQUIRE(waiter && producer, "b200_ctx_wait_ctx: NULL context");
+    if (waiter == producer) return B200_OK;
+    cudaEvent_t ev;
+    {
+        DeviceScope scope(producer->device);
+        B200_CUDA_TRY(cudaEventCreateWithFlags(&ev, cudaEventDisableTiming));
+        B200_CUDA_TRY(cudaEventRecord(ev, producer->stream));
+    }
+    DeviceScope scope(waiter->device);
+    B200_CUDA_TRY(cudaStreamWaitEvent(waiter->stream, ev, 0));
+    B200_CUDA_TRY(cudaEventDestroy(ev));
+    return B200_OK;
+}
+
 static int check_dist_desc(const char* who, const b200_gemm_desc* d, int n_ranks, int my_rank) {
     B200_REQUIRE(d != nullptr, "%s: desc is NULL", who);
     B200_REQUIRE(n_ranks >= 1 && n_ranks <= 8, "%s: n_ranks must be in [1, 8] (got %d)", who, n_ranks);
@@ -126,6 +141,57 @@ int b200_gemm_allgather(b200_ctx* ctx, const b200_gemm_desc* d, void* const* pee
     DeviceScope scope(ctx->device);
     if (gemm_pair_eligible(ctx, local, &route)) return launch_gemm_tcgen05_pair(ctx, local, ctx->pick(stream), &route);
     return launch_gemm_tcgen05(ctx, local, 1, ctx->pick(stream), &route);
+}
+
+int b200_gemm_allgather_mc(b200_ctx* ctx, const b200_gemm_desc* d, void* mc_c, int n_ranks, int my_rank, int use_multimem,
+                           void* stream) {
+    B200_REQUIRE(ctx != nullptr, "b200_gemm_allgather_mc: ctx is NULL");
+    int rc = check_dist_desc("b200_gemm_allgather_mc", d, n_ranks, my_rank);
+    if (rc != B200_OK) return rc;
+    B200_REQUIRE(mc_c != nullptr, "b200_gemm_allgather_mc: mc_c is NULL");
+    B200_REQUIRE(d->ldc >= d->N * n_ranks, "b200_gemm_allgather_mc: ldc (%lld) must cover the gathered width %lld",
+                 (long long)d->ldc, (long long)(d->N * n_ranks));
+    const size_t es = d->c_dtype == B200_F32 ? 4 : 2;
+    B200_REQUIRE((d->N * es) % 16 == 0 && (d->ldc * es) % 16 == 0,
+                 "b200_gemm_allgather_mc: shard width and leading dimension must be multiples of 16 bytes");
+    GemmRoute route;
+    route.mc_dst = static_cast<char*>(mc_c) + static_cast<size_t>(my_rank) * d->N * es;
+    route.mc_multimem = use_multimem ? 1 : 0;
+    b200_gemm_desc local = *d;
+    local.C = route.mc_dst;
+    local.split_k = 1;
+    DeviceScope scope(ctx->device);
+    if (!gemm_pair_supported(local, nullptr))
+        return fail(B200_ERR_UNSUPPORTED, "b200_gemm_allgather_mc: this product cannot run on the CTA-pair kernel (M and the shard "
+                    "width must be at least 256); use b200_gemm_allgather");
+    return launch_gemm_tcgen05_pair(ctx, local, ctx->pick(stream), &route);
+}
+
+int b200_gemm_dist_plan_query(b200_ctx* ctx, const b200_gemm_desc* d, int n_ranks, int reduce_scatter, b200_gemm_plan* out_plan) {
+    B200_REQUIRE(ctx && out_plan, "b200_gemm_dist_plan_query: NULL argument");
+    int rc = check_dist_desc("b200_gemm_dist_plan_query", d, n_ranks, 0);
+    if (rc != B200_OK) return rc;
+    GemmRoute route;
+    route.n_dst = n_ranks;
+    b200_gemm_desc local = *d;
+    local.split_k = 1;
+    if (reduce_scatter) {
+        B200_REQUIRE(d->M % n_ranks == 0, "b200_gemm_dist_plan_query: M must divide by the rank count");
+        route.scatter_rows = static_cast<int>(d->M / n_ranks);
+        local.c_dtype = B200_F32;
+        local.ldc = d->N;
+    }
+    local.C = reinterpret_cast<void*>(uintptr_t(256));  // destinations are checked at launch; the plan only needs an aligned one
+    *out_plan = b200_gemm_plan{};
+    out_plan->k_slices = 1;
+    if (gemm_pair_eligible(ctx, local, &route)) {
+        out_plan->kernel = B200_GEMM_KERNEL_TCGEN05_PAIR;
+        out_plan->block_n = 256;
+    } else {
+        out_plan->kernel = B200_GEMM_KERNEL_TCGEN05;
+        out_plan->block_n = gemm_plan(ctx, local, false).bn;
+    }
+    return B200_OK;
 }
 
 int b200_gemm_reduce_scatter_partials(b200_ctx* ctx, const b200_gemm_desc* d, void* const* peer_slots, int n_ranks,

@@ -136,7 +136,10 @@ struct GemmParams {
     // (1 = the local C; g = the same column slice of C on every GPU of an all-gather). scatter_rows > 0 selects a
     // single destination per tile instead: map index m0 / scatter_rows, row coordinate relative to that block
     // (row-block owner of a reduce-scatter).
-    int epi_mode;      // 0 = direct predicated stores (any alignment), 1 = shared-memory staging + TMA store
+    int epi_mode;      // 0 = direct predicated stores (any alignment), 1 = shared-memory staging + TMA store,
+                       // 2 = shared-memory staging + 16-byte stores by the warp to `C` (multimem.st when mc_multimem:
+                       //     C is then the NVLink multicast address of the output and every store lands on all ranks)
+    int mc_multimem;
     int n_dst;
     int scatter_rows;
     int dst_rotate;    // first destination each box is sent to (ranks start at different peers, so no peer is hit by all at once)
@@ -154,6 +157,8 @@ struct GemmRoute {
     long long rows[8] = {};        // rows of each destination matrix
     int scatter_rows = 0;
     int rotate = 0;                // index of the destination to store to first
+    void* mc_dst = nullptr;        // non-null: ONE destination written with 16-byte warp stores instead of TMA stores
+    int mc_multimem = 0;           // those stores are multimem.st (mc_dst is a multicast address)
 };
 
 // Host-side launchers implemented in the kernel translation units.

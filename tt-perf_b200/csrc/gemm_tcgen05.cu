@@ -403,11 +403,16 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
     }
 }
 
-// Sums the K slices, applies the epilogue and writes C. One thread per 4 consecutive columns.
+// Sums the K slices, applies the epilogue and writes C. One thread per 4 consecutive columns; 16-byte loads of the
+// partial sums and one 8- or 16-byte store when the addresses allow it, element by element otherwise.
 __global__ void splitk_reduce_kernel(const GemmParams p) {
     const long long cols4 = (p.N + 3) / 4;
     const long long total = static_cast<long long>(p.batch) * p.M * cols4;
     const size_t slice = static_cast<size_t>(p.batch) * p.M * p.N;
+    const bool vec_in = (p.N & 3) == 0 && (reinterpret_cast<uintptr_t>(p.partial) & 15u) == 0;
+    const size_t c_es = p.c_f32 ? 4 : 2;
+    const bool vec_out = (p.N & 3) == 0 && (p.ldc & 3) == 0 && (p.stride_c & 3) == 0 &&
+                         (reinterpret_cast<uintptr_t>(p.C) & (4 * c_es - 1)) == 0;
     for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < total;
          i += static_cast<long long>(gridDim.x) * blockDim.x) {
         const int c4 = static_cast<int>(i % cols4);
@@ -417,7 +422,7 @@ __global__ void splitk_reduce_kernel(const GemmParams p) {
         const int n = c4 * 4;
         const size_t off = (static_cast<size_t>(b) * p.M + m) * p.N + n;
         float acc[4] = {0.f, 0.f, 0.f, 0.f};
-        if ((p.N & 3) == 0) {
+        if (vec_in) {
             for (int s = 0; s < p.k_splits; ++s) {
                 const float4 v = *reinterpret_cast<const float4*>(p.partial + s * slice + off);
                 acc[0] += v.x;
@@ -431,6 +436,17 @@ __global__ void splitk_reduce_kernel(const GemmParams p) {
                     if (n + j < p.N) acc[j] += p.partial[s * slice + off + j];
         }
         const size_t coff = static_cast<size_t>(b) * p.stride_c + static_cast<size_t>(m) * p.ldc + n;
+        if (vec_out) {
+            float v[4];
+#pragma unroll
+            for (int j = 0; j < 4; ++j) v[j] = epi_apply(p.epi, acc[j], m, n + j);
+            if (p.c_f32)
+                *reinterpret_cast<float4*>(static_cast<float*>(p.C) + coff) = make_float4(v[0], v[1], v[2], v[3]);
+            else
+                *reinterpret_cast<uint2*>(static_cast<__nv_bfloat16*>(p.C) + coff) =
+                    make_uint2(pack_bf16x2(v[0], v[1]), pack_bf16x2(v[2], v[3]));
+            continue;
+        }
         for (int j = 0; j < 4; ++j) {
             if (n + j < p.N) {
                 const float v = epi_apply(p.epi, acc[j], m, n + j);

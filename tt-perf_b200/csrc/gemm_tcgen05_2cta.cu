@@ -322,7 +322,7 @@ gemm_tcgen05_2cta_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_c
                     uint32_t v0[32], v1[32];
                     tmem_ld_32x32b_x32(taddr + c, v0);
                     if (box_cols == 64 && n + 32 < p.N) tmem_ld_32x32b_x32(taddr + c + 32, v1);
-                    if (lane == 0) tma_store_wait_read<0>();  // the box this warp stored before has left its buffer
+                    if (p.epi_mode == 1 && lane == 0) tma_store_wait_read<0>();  // the box this warp stored before has left its buffer
                     __syncwarp();
                     uint8_t* srow = sbuf + lane * 128;
                     tmem_ld_wait();
@@ -364,6 +364,28 @@ gemm_tcgen05_2cta_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_c
                                     make_uint4(pack_bf16x2(f[8 * j], f[8 * j + 1]), pack_bf16x2(f[8 * j + 2], f[8 * j + 3]),
                                                pack_bf16x2(f[8 * j + 4], f[8 * j + 5]), pack_bf16x2(f[8 * j + 6], f[8 * j + 7]));
                         }
+                    }
+                    if (p.epi_mode == 2) {
+                        // The warp writes its box itself, 16 bytes per lane and instruction (four 128-byte rows per
+                        // instruction): to a multicast address one such store reaches every rank's C.
+                        __syncwarp();
+                        const size_t es = p.c_f32 ? 4 : 2;
+                        const int per16 = p.c_f32 ? 4 : 8;   // elements per 16-byte chunk
+                        char* gbase = static_cast<char*>(p.C) + (static_cast<size_t>(row_coord) * p.ldc + n) * es;
+#pragma unroll
+                        for (int i = 0; i < 8; ++i) {
+                            const int ci = i * 32 + lane;
+                            const int r = ci >> 3, ch = ci & 7;
+                            if (row_coord + r < p.M && n + ch * per16 < p.N) {
+                                const uint4 val = *reinterpret_cast<const uint4*>(sbuf + r * 128 + ((ch ^ (r & 7)) << 4));
+                                char* dst = gbase + static_cast<size_t>(r) * p.ldc * es + ch * 16;
+                                if (p.mc_multimem)
+                                    multimem_st_v4(dst, val);
+                                else
+                                    *reinterpret_cast<uint4*>(dst) = val;
+                            }
+                        }
+                        continue;
                     }
                     fence_proxy_async_smem();
                     __syncwarp();
@@ -541,7 +563,14 @@ int launch_gemm_tcgen05_pair(b200_ctx* ctx, const b200_gemm_desc& d, cudaStream_
         rc = encode_map(ctx, &tmB, d.B, d.N, d.K, d.batch, d.ldb, d.stride_b, 64, BK, false);
     if (rc != B200_OK) return rc;
     const uint32_t box_cols = p.c_f32 ? 32 : 64;
-    if (route != nullptr && route->n_dst > 0) {
+    if (route != nullptr && route->mc_dst != nullptr) {
+        B200_REQUIRE(aligned16(route->mc_dst) && d.batch == 1, "b200_gemm: the multicast destination must be 16-byte aligned, batch 1");
+        p.C = route->mc_dst;
+        p.epi_mode = 2;
+        p.mc_multimem = route->mc_multimem;
+        rc = encode_map(ctx, &tmC.m[0], d.C, d.N, d.M, 1, d.ldc, 0, box_cols, 32, p.c_f32);  // unused by this mode; kept valid
+        if (rc != B200_OK) return rc;
+    } else if (route != nullptr && route->n_dst > 0) {
         B200_REQUIRE(route->n_dst <= 8, "b200_gemm: at most 8 destinations");
         for (int i = 0; i < route->n_dst; ++i) {
             B200_REQUIRE(aligned16(route->dst[i]), "b200_gemm: destination %d is not 16-byte aligned", i);

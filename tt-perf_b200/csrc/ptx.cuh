@@ -106,6 +106,13 @@ __device__ __forceinline__ void tma_store_3d(const CUtensorMap* map, const void*
                  : "memory");
 }
 
+// One 16-byte store to an NVLink multicast address: the switch writes it to the same offset of every bound GPU's memory.
+__device__ __forceinline__ void multimem_st_v4(void* mc_addr, const uint4& v) {
+    asm volatile("multimem.st.weak.global.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(mc_addr), "f"(__uint_as_float(v.x)),
+                 "f"(__uint_as_float(v.y)), "f"(__uint_as_float(v.z)), "f"(__uint_as_float(v.w))
+                 : "memory");
+}
+
 // TMA reduction: adds a shared-memory box to global memory (element type and extents come from the tensor map;
 // elements outside the tensor are dropped). Completion is tracked by bulk groups like a TMA store.
 __device__ __forceinline__ void tma_reduce_add_3d(const CUtensorMap* map, const void* smem_src, int c0, int c1, int c2) {

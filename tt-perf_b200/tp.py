@@ -17,8 +17,8 @@ bench/metal/matmul_tensor_parallel.cpp:54-123); the arithmetic is that of its si
 Every rank runs the same generator; each `yield` is a point where all ranks must have finished what they queued
 (stores into peers' memory become visible only then). `run_emulated` steps the generators of g ranks that live in one
 process on one GPU in lockstep (one stream orders everything); `run_process` is the one-process-per-GPU form, where
-peer buffers are CUDA IPC mappings and a yield is a barrier between the ranks queued on the stream (a one-element NCCL
-all-reduce) or, optionally, a host-side synchronisation plus a `torch.distributed` barrier."""
+peer buffers are CUDA IPC mappings and a yield is a barrier between the ranks queued on the stream (b200_comm_barrier)
+or, optionally, the same barrier bracketed by host-side synchronisations."""
 from __future__ import annotations
 
 import numpy as np
@@ -76,36 +76,32 @@ class EmulatedFabric:
 
 
 class ProcessFabric:
-    """One process per GPU: a rank allocates its buffer, the others map it through CUDA IPC."""
+    """One process per GPU: a rank allocates its buffer, the others map it through CUDA IPC. `comm` is the ranks'
+    communicator (capi.Comm)."""
 
-    def __init__(self, ctx, rank: int, world: int, group=None):
-        self.ctx, self.rank, self.world, self.group = ctx, rank, world, group
+    def __init__(self, ctx, rank: int, world: int, comm=None):
+        self.ctx, self.rank, self.world, self.comm = ctx, rank, world, comm
         self._bufs = []
-        self._flag = self._ext = None
 
     def shared(self, nbytes: int) -> list[int]:
         from .dist import _PeerBuffers
-        b = _PeerBuffers(self.ctx, nbytes, self.rank, self.world, self.group)
+        b = _PeerBuffers(self.ctx, nbytes, self.rank, self.world, self.comm)
         self._bufs.append(b)
         return b.ptrs
 
     def barrier(self) -> None:
         """Host-side: wait for this rank's stream, then for every rank."""
-        import torch.distributed as dist
         self.ctx.synchronize()
-        dist.barrier(group=self.group)
+        if self.comm is not None:
+            self.comm.barrier()
+            self.ctx.synchronize()
 
     def stream_barrier(self) -> None:
-        """Device-side: a one-element NCCL all-reduce queued on the context's stream. It starts only after the kernels
-        and peer copies this rank queued before it and completes only when every rank has reached it, so whatever runs
+        """Device-side: the communicator's barrier queued on the context's stream. It starts only after the kernels and
+        peer copies this rank queued before it and completes only when every rank has reached it, so whatever runs
         after it on this stream sees all peers' stores. No host synchronisation."""
-        import torch
-        import torch.distributed as dist
-        if self._flag is None:
-            self._flag = torch.zeros(1, device="cuda")
-            self._ext = torch.cuda.ExternalStream(self.ctx.stream)
-        with torch.cuda.stream(self._ext):
-            dist.all_reduce(self._flag, group=self.group)
+        if self.comm is not None:
+            self.comm.barrier()
 
     def close(self) -> None:
         for b in self._bufs:
@@ -314,10 +310,10 @@ def run_emulated(generators) -> None:
         live = nxt
 
 
-def make_process(ctx, rank: int, world: int, *, batch: int, seq: int, d_model: int, heads: int, host_w: dict, group=None):
+def make_process(ctx, rank: int, world: int, *, batch: int, seq: int, d_model: int, heads: int, host_w: dict, comm=None):
     """This process's rank of the block (one process per GPU). Returns (rank object, fabric)."""
     T = batch * seq
-    fabric = ProcessFabric(ctx, rank, world, group)
+    fabric = ProcessFabric(ctx, rank, world, comm)
     ptrs = {name: fabric.shared(nbytes) for name, nbytes in _shared_layout(T, T // world, d_model, world)}
     return TPBlockRank(ctx, rank, world, batch=batch, seq=seq, d_model=d_model, heads=heads, host_w=host_w, ptrs=ptrs), fabric
 
