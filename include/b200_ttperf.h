@@ -224,7 +224,12 @@ int b200_gemm_planned(b200_ctx* ctx, const b200_gemm_desc* desc, const b200_gemm
  *   head_dim must be 64 (B200_ERR_UNSUPPORTED otherwise: compose b200_gemm + b200_softmax instead).
  *   lse      fp32 [B, H, S]
  * b200_attention_backward: given dO it writes dQ, dK, dV (bf16, any operand layout). It uses B*H*S*65 floats of
- * context scratch (fp32 dQ accumulators, summed with atomic adds over the key tiles, and the row sums of dO * O). */
+ * context scratch (fp32 dQ accumulators, summed with atomic adds over the key tiles, and the row sums of dO * O).
+ * The _hp forms carry one more bf16 tensor between the passes, o_lo = bf16(O - bf16(O)): what the rounding of O to bf16
+ * drops. The backward pass needs the row term rowsum(dO * O); with O known only to bf16 that term is off by up to 2^-9
+ * of |dO| |O|, equally for every key of the row, and dQ = dS K (dK = dS^T Q) multiplies that common error with whatever
+ * the keys (queries) have in common — visible in dQ and dK when attention is nearly uniform or nearly one-hot. With
+ * o_lo the row term has fp32 accuracy for 2 more bytes per output element. o_lo = NULL gives the plain forms. */
 typedef struct b200_attn_operand {
     void* ptr;
     int64_t stride_b, stride_h, stride_s;
@@ -237,6 +242,14 @@ int b200_attention_backward(b200_ctx* ctx, const b200_attn_operand* q, const b20
                             const float* lse, const b200_attn_operand* d_q, const b200_attn_operand* d_k,
                             const b200_attn_operand* d_v, int64_t B, int64_t H, int64_t S, int head_dim, float scale,
                             int causal, void* stream);
+int b200_attention_forward_hp(b200_ctx* ctx, const b200_attn_operand* q, const b200_attn_operand* k, const b200_attn_operand* v,
+                              const b200_attn_operand* o, const b200_attn_operand* o_lo, float* lse, int64_t B, int64_t H,
+                              int64_t S, int head_dim, float scale, int causal, void* stream);
+int b200_attention_backward_hp(b200_ctx* ctx, const b200_attn_operand* q, const b200_attn_operand* k,
+                               const b200_attn_operand* v, const b200_attn_operand* o, const b200_attn_operand* o_lo,
+                               const b200_attn_operand* d_o, const float* lse, const b200_attn_operand* d_q,
+                               const b200_attn_operand* d_k, const b200_attn_operand* d_v, int64_t B, int64_t H, int64_t S,
+                               int head_dim, float scale, int causal, void* stream);
 
 /* ---- row softmax family (traced/ops.hpp:77-81 softmax, :102-106 softmax_backward; py/engine.py:352-384) ----
  * [rows, cols] bf16 matrices, leading dimensions in elements.

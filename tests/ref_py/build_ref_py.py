@@ -6,9 +6,10 @@ repository: the outputs are build artefacts under build/ref_py/ (git-ignored; th
 
     python tests/ref_py/build_ref_py.py --reference <path of the tt-perf tree>   (or TTPERF_REFERENCE=<path>)
 
-Layout of build/ref_py/: src/<module>.pyc (the reference's test files import the engine as `src.*` although its
-directory is called py/) and tests/<file>.pyc. The .pyc files are only valid for the Python version that wrote them
-(same image here and on the GPU box)."""
+Layout of build/ref_py/: src/<module>.mod (the reference's test files import the engine as `src.*` although its
+directory is called py/) and tests/<file>.mod. A .mod file is what py_compile writes (a .pyc under another suffix, so
+that tools which skip Python caches when they copy a tree leave it alone); it is only valid for the Python version that
+wrote it (same image here and on the GPU box)."""
 from __future__ import annotations
 
 import argparse
@@ -37,10 +38,10 @@ def build(reference: str | None = None) -> list[str]:
     (OUT / "src").mkdir(parents=True)
     (OUT / "tests").mkdir(parents=True)
     for src in sorted((ref / "py").glob("*.py")):
-        py_compile.compile(str(src), cfile=str(OUT / "src" / (src.stem + ".pyc")), dfile=f"py/{src.name}", doraise=True)
+        py_compile.compile(str(src), cfile=str(OUT / "src" / (src.stem + ".mod")), dfile=f"py/{src.name}", doraise=True)
     names = []
     for src in sorted((ref / "tests").glob("*.py")):
-        py_compile.compile(str(src), cfile=str(OUT / "tests" / (src.stem + ".pyc")), dfile=f"tests/{src.name}", doraise=True)
+        py_compile.compile(str(src), cfile=str(OUT / "tests" / (src.stem + ".mod")), dfile=f"tests/{src.name}", doraise=True)
         names.append(src.stem)
     (OUT / "python_version.txt").write_text(sys.version.split()[0] + "\n")
     return names

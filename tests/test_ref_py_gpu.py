@@ -35,7 +35,7 @@ def _load_sourceless(name: str, path: Path, package_dir: Path | None = None):
 @pytest.fixture(scope="module")
 def reference_engine():
     """`ttnn` = the stand-in; `src` (and its alias `grad`, which py/optim.py uses) = the reference's engine package."""
-    if not (BUILD / "src" / "engine.pyc").exists():
+    if not (BUILD / "src" / "engine.mod").exists():
         pytest.skip("build/ref_py is missing (tests/ref_py/build_ref_py.py needs the reference tree)")
     if (BUILD / "python_version.txt").read_text().split()[0] != sys.version.split()[0]:
         pytest.skip("build/ref_py was compiled by another Python version")
@@ -44,13 +44,13 @@ def reference_engine():
     saved = {k: sys.modules.pop(k) for k in list(sys.modules) if k == "ttnn" or k.split(".")[0] in ("src", "grad")}
     try:
         importlib.import_module("ttnn")
-        pkg = _load_sourceless("src", BUILD / "src" / "__init__.pyc", BUILD / "src")
+        pkg = _load_sourceless("src", BUILD / "src" / "__init__.mod", BUILD / "src")
         for sub in ("engine", "data"):
-            setattr(pkg, sub, _load_sourceless(f"src.{sub}", BUILD / "src" / f"{sub}.pyc"))
+            setattr(pkg, sub, _load_sourceless(f"src.{sub}", BUILD / "src" / f"{sub}.mod"))
         sys.modules["grad"] = pkg
         sys.modules["grad.engine"] = sys.modules["src.engine"]
         for sub in ("nn", "optim"):
-            setattr(pkg, sub, _load_sourceless(f"src.{sub}", BUILD / "src" / f"{sub}.pyc"))
+            setattr(pkg, sub, _load_sourceless(f"src.{sub}", BUILD / "src" / f"{sub}.mod"))
         yield pkg
     finally:
         for k in [k for k in sys.modules if k == "ttnn" or k.split(".")[0] in ("src", "grad", "ref_tests")]:
@@ -61,7 +61,7 @@ def reference_engine():
 
 @pytest.mark.parametrize("name", FILES)
 def test_reference_python_test_file(reference_engine, name):
-    mod = _load_sourceless(f"ref_tests.{name}", BUILD / "tests" / f"{name}.pyc")
+    mod = _load_sourceless(f"ref_tests.{name}", BUILD / "tests" / f"{name}.mod")
     tests = sorted(k for k, v in vars(mod).items() if k.startswith("test_") and callable(v))
     assert tests, f"{name}: no test functions found"
     failed = []

@@ -128,6 +128,11 @@ SIGNATURES = {
     "b200_attention_backward": (C.c_int, [C.c_void_p] + [C.POINTER(AttnOperand)] * 5 + [C.c_void_p] +
                                 [C.POINTER(AttnOperand)] * 3 + [C.c_int64, C.c_int64, C.c_int64, C.c_int, C.c_float, C.c_int,
                                                                 C.c_void_p]),
+    "b200_attention_forward_hp": (C.c_int, [C.c_void_p] + [C.POINTER(AttnOperand)] * 5 + [C.c_void_p, C.c_int64, C.c_int64,
+                                            C.c_int64, C.c_int, C.c_float, C.c_int, C.c_void_p]),
+    "b200_attention_backward_hp": (C.c_int, [C.c_void_p] + [C.POINTER(AttnOperand)] * 6 + [C.c_void_p] +
+                                   [C.POINTER(AttnOperand)] * 3 + [C.c_int64, C.c_int64, C.c_int64, C.c_int, C.c_float, C.c_int,
+                                                                   C.c_void_p]),
     "b200_softmax": (C.c_int, [C.c_void_p, C.c_void_p, C.c_int64, C.c_void_p, C.c_int64, C.c_int64, C.c_int64, C.c_float,
                                C.c_int64, C.c_void_p]),
     "b200_softmax_backward": (C.c_int, [C.c_void_p, C.c_void_p, C.c_int64, C.c_void_p, C.c_int64, C.c_void_p, C.c_int64,
@@ -372,18 +377,21 @@ class Context:
         """Strided bf16 view for the fused attention calls; `offset` in elements from the start of x."""
         return AttnOperand(ptr(x) + 2 * offset, stride_b, stride_h, stride_s)
 
-    def attention_forward(self, q, k, v, o, lse, B, H, S, *, head_dim=64, scale=None, causal=True, stream=None):
-        """q, k, v, o: AttnOperand; lse: fp32 [B, H, S]."""
+    def attention_forward(self, q, k, v, o, lse, B, H, S, *, head_dim=64, scale=None, causal=True, o_lo=None, stream=None):
+        """q, k, v, o: AttnOperand; lse: fp32 [B, H, S]. o_lo (optional AttnOperand): receives bf16(O - bf16(O)) for
+        the backward pass's row term (b200_attention_forward_hp)."""
         scale = head_dim ** -0.5 if scale is None else scale
-        check(lib().b200_attention_forward(self._h, C.byref(q), C.byref(k), C.byref(v), C.byref(o), ptr(lse), B, H, S,
-                                           head_dim, scale, int(causal), self._s(stream)))
+        check(lib().b200_attention_forward_hp(self._h, C.byref(q), C.byref(k), C.byref(v), C.byref(o),
+                                              C.byref(o_lo) if o_lo is not None else None, ptr(lse), B, H, S, head_dim, scale,
+                                              int(causal), self._s(stream)))
 
     def attention_backward(self, q, k, v, o, d_o, lse, d_q, d_k, d_v, B, H, S, *, head_dim=64, scale=None, causal=True,
-                           stream=None):
+                           o_lo=None, stream=None):
         scale = head_dim ** -0.5 if scale is None else scale
-        check(lib().b200_attention_backward(self._h, C.byref(q), C.byref(k), C.byref(v), C.byref(o), C.byref(d_o), ptr(lse),
-                                            C.byref(d_q), C.byref(d_k), C.byref(d_v), B, H, S, head_dim, scale, int(causal),
-                                            self._s(stream)))
+        check(lib().b200_attention_backward_hp(self._h, C.byref(q), C.byref(k), C.byref(v), C.byref(o),
+                                               C.byref(o_lo) if o_lo is not None else None, C.byref(d_o), ptr(lse),
+                                               C.byref(d_q), C.byref(d_k), C.byref(d_v), B, H, S, head_dim, scale, int(causal),
+                                               self._s(stream)))
 
     def softmax(self, x, y, rows, cols, *, ldx=None, ldy=None, alpha=1.0, causal_period=0, stream=None):
         check(lib().b200_softmax(self._h, ptr(x), ldx or cols, ptr(y), ldy or cols, rows, cols, alpha, causal_period,

@@ -96,6 +96,7 @@ __device__ __forceinline__ void drain(uint64_t* bar, uint32_t parity) {
 struct FwdParams {
     Geom g;
     Strided o;
+    Strided o_lo;   // optional (ptr may be null): bf16(O - bf16(O)), what the rounding of O to bf16 drops
     float* lse;
     int* status;
 };
@@ -334,6 +335,17 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
                                                   half * 32);
 #pragma unroll
         for (int t = 0; t < 4; ++t) store_bf16x8(dst + t * 16, o + 8 * t);
+        if (p.o_lo.ptr != nullptr) {
+            // The backward pass needs rowsum(dO * O); with O known only to bf16 that row term is off by up to 2^-9 of
+            // |dO||O|, the same for every key of the row, which the dQ / dK products then multiply with the keys'
+            // (queries') common component. The dropped part of O, stored as a second bf16 tensor, restores it.
+#pragma unroll
+            for (int i = 0; i < 32; ++i) o[i] -= __bfloat162float(__float2bfloat16_rn(o[i]));
+            uint8_t* dst_lo = reinterpret_cast<uint8_t*>(p.o_lo.ptr + b * p.o_lo.sb + h * p.o_lo.sh +
+                                                         static_cast<long long>(row) * p.o_lo.ss + half * 32);
+#pragma unroll
+            for (int t = 0; t < 4; ++t) store_bf16x8(dst_lo + t * 16, o + 8 * t);
+        }
         if (half == 0) p.lse[(static_cast<long long>(bh)) * g.S + row] = (m * sl2 + log2f(total)) * LN2;
     }
     if (threadIdx.x == 0 && *abort_flag != 0) {  // let armed copies land before the shared memory is released
@@ -635,8 +647,8 @@ struct StridedIn {
     long long sb, sh, ss;
 };
 
-// dsum[b, h, s] = sum_d dO * O. Eight threads per row, 8 elements each.
-__global__ void attn_dsum_kernel(StridedIn o, StridedIn d_o, float* dsum, int B, int H, int S) {
+// dsum[b, h, s] = sum_d dO * O (O = o + o_lo when the forward pass kept the low part). Eight threads per row, 8 elements each.
+__global__ void attn_dsum_kernel(StridedIn o, StridedIn o_lo, StridedIn d_o, float* dsum, int B, int H, int S) {
     const long long t = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x;
     const long long rowi = t >> 3;
     const int part = static_cast<int>(t & 7);
@@ -655,6 +667,17 @@ __global__ void attn_dsum_kernel(StridedIn o, StridedIn d_o, float* dsum, int B,
         for (int e = 0; e < 4; ++e) {
             acc = fmaf(__uint_as_float(ow[e] << 16), __uint_as_float(dw[e] << 16), acc);
             acc = fmaf(__uint_as_float(ow[e] & 0xffff0000u), __uint_as_float(dw[e] & 0xffff0000u), acc);
+        }
+        if (o_lo.ptr != nullptr) {
+            const uint4 lv = *reinterpret_cast<const uint4*>(o_lo.ptr + b * o_lo.sb + h * o_lo.sh + s * o_lo.ss + part * 8);
+            const uint32_t lw[4] = {lv.x, lv.y, lv.z, lv.w};
+            float lo = 0.f;
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+                lo = fmaf(__uint_as_float(lw[e] << 16), __uint_as_float(dw[e] << 16), lo);
+                lo = fmaf(__uint_as_float(lw[e] & 0xffff0000u), __uint_as_float(dw[e] & 0xffff0000u), lo);
+            }
+            acc += lo;
         }
     }
     acc += __shfl_xor_sync(0xffffffffu, acc, 1);
@@ -763,6 +786,12 @@ extern "C" {
 int b200_attention_forward(b200_ctx* ctx, const b200_attn_operand* q, const b200_attn_operand* k, const b200_attn_operand* v,
                            const b200_attn_operand* o, float* lse, int64_t B, int64_t H, int64_t S, int head_dim,
                            float scale, int causal, void* stream_v) {
+    return b200_attention_forward_hp(ctx, q, k, v, o, nullptr, lse, B, H, S, head_dim, scale, causal, stream_v);
+}
+
+int b200_attention_forward_hp(b200_ctx* ctx, const b200_attn_operand* q, const b200_attn_operand* k, const b200_attn_operand* v,
+                              const b200_attn_operand* o, const b200_attn_operand* o_lo, float* lse, int64_t B, int64_t H,
+                              int64_t S, int head_dim, float scale, int causal, void* stream_v) {
     B200_REQUIRE(ctx != nullptr, "b200_attention_forward: ctx is NULL");
     int rc = check_geometry(B, H, S, head_dim, scale);
     if (rc != B200_OK) return rc;
@@ -772,6 +801,7 @@ int b200_attention_forward(b200_ctx* ctx, const b200_attn_operand* q, const b200
     if ((rc = check_operand(k, "k", B, H)) != B200_OK) return rc;
     if ((rc = check_operand(v, "v", B, H)) != B200_OK) return rc;
     if ((rc = check_operand(o, "o", B, H)) != B200_OK) return rc;
+    if (o_lo != nullptr && (rc = check_operand(o_lo, "o_lo", B, H)) != B200_OK) return rc;
     DeviceScope scope(ctx->device);
     cudaStream_t stream = ctx->pick(stream_v);
     CUtensorMap tmQ, tmK, tmV;
@@ -781,6 +811,7 @@ int b200_attention_forward(b200_ctx* ctx, const b200_attn_operand* q, const b200
     FwdParams p;
     p.g = make_geom(B, H, S, scale, causal);
     p.o = as_out(o);
+    p.o_lo = o_lo != nullptr ? as_out(o_lo) : Strided{nullptr, 0, 0, 0};
     p.lse = lse;
     p.status = ctx->d_status;
     static bool configured[64] = {};
@@ -796,6 +827,15 @@ int b200_attention_backward(b200_ctx* ctx, const b200_attn_operand* q, const b20
                             const float* lse, const b200_attn_operand* d_q, const b200_attn_operand* d_k,
                             const b200_attn_operand* d_v, int64_t B, int64_t H, int64_t S, int head_dim, float scale,
                             int causal, void* stream_v) {
+    return b200_attention_backward_hp(ctx, q, k, v, o, nullptr, d_o, lse, d_q, d_k, d_v, B, H, S, head_dim, scale, causal,
+                                      stream_v);
+}
+
+int b200_attention_backward_hp(b200_ctx* ctx, const b200_attn_operand* q, const b200_attn_operand* k,
+                               const b200_attn_operand* v, const b200_attn_operand* o, const b200_attn_operand* o_lo,
+                               const b200_attn_operand* d_o, const float* lse, const b200_attn_operand* d_q,
+                               const b200_attn_operand* d_k, const b200_attn_operand* d_v, int64_t B, int64_t H, int64_t S,
+                               int head_dim, float scale, int causal, void* stream_v) {
     B200_REQUIRE(ctx != nullptr, "b200_attention_backward: ctx is NULL");
     int rc = check_geometry(B, H, S, head_dim, scale);
     if (rc != B200_OK) return rc;
@@ -805,6 +845,7 @@ int b200_attention_backward(b200_ctx* ctx, const b200_attn_operand* q, const b20
     const char* names[8] = {"q", "k", "v", "o", "d_o", "d_q", "d_k", "d_v"};
     for (int i = 0; i < 8; ++i)
         if ((rc = check_operand(ops[i], names[i], B, H)) != B200_OK) return rc;
+    if (o_lo != nullptr && (rc = check_operand(o_lo, "o_lo", B, H)) != B200_OK) return rc;
     DeviceScope scope(ctx->device);
     cudaStream_t stream = ctx->pick(stream_v);
     const size_t rows = static_cast<size_t>(B) * H * S;
@@ -833,7 +874,7 @@ int b200_attention_backward(b200_ctx* ctx, const b200_attn_operand* q, const b20
     }
     B200_CUDA_TRY(cudaMemsetAsync(dq_acc, 0, acc_bytes, stream));
     const unsigned blocks = static_cast<unsigned>((rows * 8 + 255) / 256);
-    attn_dsum_kernel<<<blocks, 256, 0, stream>>>(as_in(o), as_in(d_o), dsum, static_cast<int>(B), static_cast<int>(H),
+    attn_dsum_kernel<<<blocks, 256, 0, stream>>>(as_in(o), o_lo != nullptr ? as_in(o_lo) : StridedIn{nullptr, 0, 0, 0}, as_in(d_o), dsum, static_cast<int>(B), static_cast<int>(H),
                                                  static_cast<int>(S));
     B200_CUDA_TRY(cudaGetLastError());
 

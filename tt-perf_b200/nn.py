@@ -318,9 +318,10 @@ def transformer_block_forward(ctx, x, w, heads, *, defer_add=False, stream=None)
             cache["qkv"] = (q, k, v)
         merged = DeviceTensor(ctx, (b, s, d), BF16)
         lse = DeviceTensor(ctx, (b, heads, s), F32)
-        (o_op,) = _head_operands(ctx, merged, heads)
-        ctx.attention_forward(q_op, k_op, v_op, o_op, lse, b, heads, s, head_dim=dh, causal=True, stream=stream)
-        cache.update(lse=lse)
+        merged_lo = DeviceTensor(ctx, (b, s, d), BF16)      # what bf16 drops of the attention output: for the backward row term
+        (o_op,), (olo_op,) = _head_operands(ctx, merged, heads), _head_operands(ctx, merged_lo, heads)
+        ctx.attention_forward(q_op, k_op, v_op, o_op, lse, b, heads, s, head_dim=dh, causal=True, o_lo=olo_op, stream=stream)
+        cache.update(lse=lse, merged_lo=merged_lo)
     else:
         q = split_heads(ctx, linear_forward(ctx, ln1, w["wq"], w["bq"], stream=stream), heads, stream=stream)
         k = split_heads(ctx, linear_forward(ctx, ln1, w["wk"], w["bk"], stream=stream), heads, stream=stream)
@@ -367,8 +368,9 @@ def transformer_block_backward(ctx, d_out, w, cache, heads, *, d_out_colsum=None
             (q_op,), (k_op,), (v_op,) = (_head_operands(ctx, t, heads) for t in c["qkv"])
             grads_in = tuple(DeviceTensor(ctx, (b, s, d), BF16) for _ in range(3))
             (dq_op,), (dk_op,), (dv_op,) = (_head_operands(ctx, t, heads) for t in grads_in)
+        (olo_op,) = _head_operands(ctx, c["merged_lo"], heads)
         ctx.attention_backward(q_op, k_op, v_op, o_op, do_op, c["lse"], dq_op, dk_op, dv_op, b, heads, s, head_dim=dh,
-                               causal=True, stream=stream)
+                               causal=True, o_lo=olo_op, stream=stream)
     else:
         d_attn = split_heads(ctx, d_merged, heads, stream=stream)
         d_q, d_k, d_v = causal_attention_backward(ctx, c["q"], c["k"], c["v"], c["p"], d_attn, stream=stream)

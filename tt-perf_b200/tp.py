@@ -184,9 +184,10 @@ class TPBlockRank:
         q_op, k_op, v_op = nn._head_operands(ctx, qkv, self.hr, 3)
         merged = DeviceTensor(ctx, (B, S, self.Kr), BF16)
         lse = DeviceTensor(ctx, (B, self.hr, S), F32)
-        (o_op,) = nn._head_operands(ctx, merged, self.hr)
-        ctx.attention_forward(q_op, k_op, v_op, o_op, lse, B, self.hr, S, causal=True)
-        c.update(qkv=qkv, merged=merged, lse=lse)
+        merged_lo = DeviceTensor(ctx, (B, S, self.Kr), BF16)
+        (o_op,), (olo_op,) = nn._head_operands(ctx, merged, self.hr), nn._head_operands(ctx, merged_lo, self.hr)
+        ctx.attention_forward(q_op, k_op, v_op, o_op, lse, B, self.hr, S, causal=True, o_lo=olo_op)
+        c.update(qkv=qkv, merged=merged, merged_lo=merged_lo, lse=lse)
         self._scatter_partials("slots0", merged, w["wo"], D, self.Kr, transpose_b=True, lda=self.Kr, ldb=self.Kr)
         yield
         attn_out = DeviceTensor(ctx, (Tr, D), BF16)
@@ -247,7 +248,9 @@ class TPBlockRank:
         (o_op,), (do_op,) = nn._head_operands(ctx, c["merged"], self.hr), nn._head_operands(ctx, d_merged, self.hr)
         d_qkv = DeviceTensor(ctx, (B, S, 3 * self.Kr), BF16)
         dq_op, dk_op, dv_op = nn._head_operands(ctx, d_qkv, self.hr, 3)
-        ctx.attention_backward(q_op, k_op, v_op, o_op, do_op, c["lse"], dq_op, dk_op, dv_op, B, self.hr, S, causal=True)
+        (olo_op,) = nn._head_operands(ctx, c["merged_lo"], self.hr)
+        ctx.attention_backward(q_op, k_op, v_op, o_op, do_op, c["lse"], dq_op, dk_op, dv_op, B, self.hr, S, causal=True,
+                               o_lo=olo_op)
         ln1 = self._view("ln1_full", self.rank, T, shape=(B, S, D))
         _, g["wqkv"], g["bqkv"] = nn.linear_backward(ctx, ln1, w["wqkv"], d_qkv, need_dx=False)
         self._scatter_partials("slots1", d_qkv, w["wqkv"], D, 3 * self.Kr, transpose_b=False, lda=3 * self.Kr, ldb=D)
