@@ -407,12 +407,17 @@ int b200_gemm_allgather(b200_ctx* ctx, const b200_gemm_desc* desc, void* const* 
                         void* stream);
 /* K-split (row parallel) + reduce-scatter, step 1: desc describes the LOCAL partial product over this rank's K range
  * (full M x N). The fp32 partial tiles of row block j (M / n_ranks rows) are stored into slot `my_rank` of rank j's
- * staging buffer peer_slots[j], laid out [n_ranks][M / n_ranks][N] fp32. M / n_ranks must be a multiple of 128.
+ * staging buffer peer_slots[j], laid out [n_ranks][M / n_ranks][N] in desc->c_dtype: B200_F32, or B200_BF16 to halve
+ * the bytes on the links (each partial sum is then rounded once before the fp32 summation: the HiFi2 trade of
+ * verify/verify_fidelity.cpp:50-55 applied to the exchange). M / n_ranks must be a multiple of 128.
  * Step 2, after the ranks have synchronised: b200_reduce_slices sums a rank's n_slices slices ([n_slices][batch][M][N]
- * fp32, M = rows of the block), applies desc's alpha / bias / activation and writes desc->C (bf16 or fp32). */
+ * fp32, M = rows of the block; b200_reduce_slices_typed also takes bf16 slices), applies desc's alpha / bias /
+ * activation and writes desc->C (bf16 or fp32). */
 int b200_gemm_reduce_scatter_partials(b200_ctx* ctx, const b200_gemm_desc* desc, void* const* peer_slots, int n_ranks,
                                       int my_rank, void* stream);
 int b200_reduce_slices(b200_ctx* ctx, const float* slices, int n_slices, const b200_gemm_desc* desc, void* stream);
+int b200_reduce_slices_typed(b200_ctx* ctx, const void* slices, int slices_dtype, int n_slices, const b200_gemm_desc* desc,
+                             void* stream);
 /* The kernel and tile width the two fused calls above use for `desc` (reduce_scatter = 0: b200_gemm_allgather, 1:
  * b200_gemm_reduce_scatter_partials), in the terms of b200_gemm_plan; b200_gemm_plan_describe turns it into text. */
 int b200_gemm_dist_plan_query(b200_ctx* ctx, const b200_gemm_desc* desc, int n_ranks, int reduce_scatter,
@@ -455,6 +460,10 @@ typedef struct b200_mc b200_mc;
 int b200_mc_supported(b200_ctx* ctx, int* out_supported);
 int b200_mc_alloc(b200_comm* comm, size_t bytes, b200_mc** out_mc, void** out_local_ptr, void** out_multicast_ptr);
 int b200_mc_free(b200_mc* mc);
+/* Copies `bytes` from this GPU's memory to a multicast address (multimem.st, 16 bytes per thread): the block arrives
+ * at the same offset of every rank's copy — an all-gather of row blocks in which each rank sends its block once.
+ * Addresses and size are multiples of 16 bytes. Visible to a peer after this rank's stream and a rank barrier. */
+int b200_mc_broadcast(b200_ctx* ctx, void* mc_dst, const void* d_src, size_t bytes, void* stream);
 /* b200_gemm_allgather with ONE destination: the multicast address of the full C (from b200_mc_alloc). The epilogue
  * stages each finished box in shared memory and the warp writes it with multimem.st, 16 bytes per lane: one store per
  * box instead of one per rank, so a rank's egress is its own slice once ((g-1)/g * |C| / g bytes per peer link set

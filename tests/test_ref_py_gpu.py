@@ -23,9 +23,9 @@ FILES = ["adam_optimizer", "causal_attention_single_and_batched", "cross_entropy
 
 def _load_sourceless(name: str, path: Path, package_dir: Path | None = None):
     loader = importlib.machinery.SourcelessFileLoader(name, str(path))
-    spec = importlib.util.spec_from_loader(name, loader, origin=str(path), is_package=package_dir is not None)
-    if package_dir is not None:
-        spec.submodule_search_locations = [str(package_dir)]
+    # a file location, so that the module gets the __file__ the reference's tests derive their import root from
+    spec = importlib.util.spec_from_file_location(name, str(path), loader=loader,
+                                                  submodule_search_locations=[str(package_dir)] if package_dir is not None else None)
     mod = importlib.util.module_from_spec(spec)
     sys.modules[name] = mod
     loader.exec_module(mod)

@@ -42,8 +42,9 @@ def _gather_grads(ranks, w, heads):
     return out
 
 
-@pytest.mark.parametrize("world", [2, 4])
-def test_tp_block_matches_single_device_oracle(pkg, ctx, world):
+@pytest.mark.parametrize("world,partials", [(2, "f32"), (4, "f32"), (4, "bf16")])
+def test_tp_block_matches_single_device_oracle(pkg, ctx, world, partials):
+    """partials = "bf16": the partial tiles of the row-parallel products cross the links as bf16 (half the bytes)."""
     DT, tp = pkg.DeviceTensor, pkg.tp
     rng = np.random.default_rng(7)
     b, s, heads = 2, 256, 5                       # 5 heads do not divide by 2 or 4: uneven head counts
@@ -55,7 +56,8 @@ def test_tp_block_matches_single_device_oracle(pkg, ctx, world):
     ref_out, ref_cache = mo.transformer_block_forward(x, w, heads, quantize=mo.bf16_round)
     ref_dx, ref_g = mo.transformer_block_backward(d_out, w, ref_cache, heads, quantize=mo.bf16_round)
 
-    ranks, fabric = tp.make_emulated(ctx, world, batch=b, seq=s, d_model=d, heads=heads, host_w=w)
+    ranks, fabric = tp.make_emulated(ctx, world, batch=b, seq=s, d_model=d, heads=heads, host_w=w,
+                                     partial_dtype=pkg.BF16 if partials == "bf16" else pkg.F32)
     try:
         t, tr = b * s, b * s // world
         xs = [DT.from_numpy(ctx, x.reshape(t, d)[r * tr:(r + 1) * tr]) for r in range(world)]

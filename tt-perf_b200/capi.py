@@ -109,12 +109,14 @@ SIGNATURES = {
     "b200_mc_supported": (C.c_int, [C.c_void_p, C.POINTER(C.c_int)]),
     "b200_mc_alloc": (C.c_int, [C.c_void_p, C.c_size_t, C.POINTER(C.c_void_p), C.POINTER(C.c_void_p), C.POINTER(C.c_void_p)]),
     "b200_mc_free": (C.c_int, [C.c_void_p]),
+    "b200_mc_broadcast": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_size_t, C.c_void_p]),
     "b200_gemm_allgather_mc": (C.c_int, [C.c_void_p, C.POINTER(GemmDesc), C.c_void_p, C.c_int, C.c_int, C.c_int, C.c_void_p]),
     "b200_gemm_allgather": (C.c_int, [C.c_void_p, C.POINTER(GemmDesc), C.POINTER(C.c_void_p), C.c_int, C.c_int, C.c_void_p]),
     "b200_gemm_reduce_scatter_partials": (C.c_int, [C.c_void_p, C.POINTER(GemmDesc), C.POINTER(C.c_void_p), C.c_int, C.c_int,
                                                     C.c_void_p]),
     "b200_gemm_dist_plan_query": (C.c_int, [C.c_void_p, C.POINTER(GemmDesc), C.c_int, C.c_int, C.POINTER(GemmPlan)]),
     "b200_reduce_slices": (C.c_int, [C.c_void_p, C.c_void_p, C.c_int, C.POINTER(GemmDesc), C.c_void_p]),
+    "b200_reduce_slices_typed": (C.c_int, [C.c_void_p, C.c_void_p, C.c_int, C.c_int, C.POINTER(GemmDesc), C.c_void_p]),
     "b200_comm_unique_id": (C.c_int, [C.c_void_p]),
     "b200_comm_create": (C.c_int, [C.c_void_p, C.c_void_p, C.c_int, C.c_int, C.POINTER(C.c_void_p)]),
     "b200_comm_destroy": (C.c_int, [C.c_void_p]),
@@ -541,6 +543,10 @@ class Context:
         check(lib().b200_gemm_allgather_mc(self._h, C.byref(desc), C.c_void_p(ptr(mc_c)), n_ranks, my_rank,
                                            int(bool(use_multimem)), self._s(stream)))
 
+    def mc_broadcast(self, mc_dst, d_src, nbytes: int, stream=None) -> None:
+        """This GPU's block -> the same offset of every rank's copy (one multimem.st per 16 bytes)."""
+        check(lib().b200_mc_broadcast(self._h, C.c_void_p(ptr(mc_dst)), C.c_void_p(ptr(d_src)), nbytes, self._s(stream)))
+
     def mc_supported(self) -> bool:
         out = C.c_int()
         check(lib().b200_mc_supported(self._h, C.byref(out)))
@@ -556,8 +562,8 @@ class Context:
         check(lib().b200_gemm_dist_plan_query(self._h, C.byref(desc), n_ranks, int(reduce_scatter), C.byref(plan)))
         return plan
 
-    def reduce_slices(self, slices, n_slices: int, desc: GemmDesc, stream=None) -> None:
-        check(lib().b200_reduce_slices(self._h, ptr(slices), n_slices, C.byref(desc), self._s(stream)))
+    def reduce_slices(self, slices, n_slices: int, desc: GemmDesc, stream=None, slices_dtype=F32) -> None:
+        check(lib().b200_reduce_slices_typed(self._h, ptr(slices), slices_dtype, n_slices, C.byref(desc), self._s(stream)))
 
     # ---- pool and traces ---------------------------------------------------------------------------------------------
     def pool_alloc(self, nbytes: int) -> int:

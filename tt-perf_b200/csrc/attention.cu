@@ -102,21 +102,12 @@ struct FwdParams {
 };
 
 constexpr int FWD_TMEM_COLS = 256;  // S: columns 0..127, O_j: 128..191
-constexpr int FWD_SMEM_USED = 5 * TILE_BYTES + PT_BYTES + 64 + 512;  // tiles, barriers, row-maximum exchange
+constexpr int FWD_SMEM_USED = 5 * TILE_BYTES + PT_BYTES + 64 + 1024;  // tiles, barriers, row-maximum exchange
 // Two CTAs per SM have 2 * (FWD_SMEM + 1 KB the hardware reserves per CTA) <= 228 KB to share, which leaves no room for
 // rounding the base up to 1024: the kernel relies on the base being 1024-aligned already (it is when the kernel has no
 // static shared memory) and reports an error instead of running when it is not.
 constexpr int FWD_SMEM = FWD_SMEM_USED;
 static_assert(2 * (FWD_SMEM + 1024) <= 228 * 1024, "two forward CTAs must fit one SM");
-
-// Smallest bf16-representable value >= x, as its 16 high bits. The two threads that share a row exchange their local
-// maxima in this form: any common value >= the true maximum stabilises exp2 equally well, and 2 bytes per value is
-// what fits next to the tiles.
-__device__ __forceinline__ uint16_t ceil_bf16_bits(float x) {
-    const uint32_t u = __float_as_uint(x);
-    return static_cast<uint16_t>(((x >= 0.f) ? (u + 0xffffu) : u) >> 16);
-}
-__device__ __forceinline__ float bf16_bits_to_float(uint16_t b) { return __uint_as_float(static_cast<uint32_t>(b) << 16); }
 
 // 256 threads: registers are handed out to pairs of warps, so a ninth warp for issuing would cost a fifth of the
 // register file and the second CTA per SM with it. Thread 0 issues the copies and the MMAs between the barriers
@@ -141,9 +132,11 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
     uint64_t* o_full = s_full + 1;       // the last P V product has run
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(o_full + 1);
     volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
-    // [column half][row] local maxima. One buffer is enough: nobody sees the next S before every thread has passed the
-    // barrier that follows the P stores, i.e. has read this tile's values.
-    uint16_t* xch = reinterpret_cast<uint16_t*>(reinterpret_cast<uint8_t*>(q_full) + 64);
+    // [column half][row] local maxima, exchanged exactly (fp32): with the true row maximum the largest probability of a
+    // row is exp2(0) = 1, which bf16 holds without error, so a nearly one-hot row loses nothing in the P V product —
+    // the backward pass's cancellation dP - rowsum(dO O) depends on that. One buffer is enough: nobody sees the next S
+    // before every thread has passed the barrier that follows the P stores, i.e. has read this tile's values.
+    float* xch = reinterpret_cast<float*>(reinterpret_cast<uint8_t*>(q_full) + 64);
 
     const int warp = threadIdx.x >> 5;
     const int lane = threadIdx.x & 31;
@@ -241,7 +234,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
         uint32_t s0[32], s1[32];
         const int lim = limit - j * BT - half * 64;  // index, within this thread's 64 columns, of the last visible one
         const bool masked = lim < 63;
-        uint16_t mine = 0;
+        float mine = -INFINITY;
         if (ok) {
             tcgen05_fence_after_sync();
             if (j > 0) fold_pv();
@@ -262,13 +255,13 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
                     if (i + 32 <= lim) mx4[i & 3] = fmaxf(mx4[i & 3], __uint_as_float(s1[i]));
                 }
             }
-            mine = ceil_bf16_bits(fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3])));
+            mine = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3]));
             xch[half * BT + r] = mine;
         }
         compute_warps_sync<FWD_THREADS>();
         if (ok) {
             // finite: every tile shows each row at least one key
-            const float mx = fmaxf(m, fmaxf(bf16_bits_to_float(mine), bf16_bits_to_float(xch[(half ^ 1) * BT + r])));
+            const float mx = fmaxf(m, fmaxf(mine, xch[(half ^ 1) * BT + r]));
             alpha = ex2((m - mx) * sl2);  // 0 on the first tile (m = -inf)
             const float mb = mx * sl2;
             m = mx;

@@ -203,21 +203,22 @@ int b200_gemm_reduce_scatter_partials(b200_ctx* ctx, const b200_gemm_desc* d, vo
     B200_REQUIRE(d->M % n_ranks == 0 && (d->M / n_ranks) % 128 == 0,
                  "b200_gemm_reduce_scatter_partials: M / n_ranks must be a multiple of the 128-row tile (M = %lld)",
                  (long long)d->M);
-    B200_REQUIRE(d->N % 4 == 0, "b200_gemm_reduce_scatter_partials: N must be a multiple of 4");
+    B200_REQUIRE(d->c_dtype == B200_F32 || d->c_dtype == B200_BF16, "b200_gemm_reduce_scatter_partials: partial tiles are F32 or BF16");
+    const size_t pes = d->c_dtype == B200_F32 ? 4 : 2;   // bytes per partial element
+    B200_REQUIRE((d->N * pes) % 16 == 0, "b200_gemm_reduce_scatter_partials: a row of partial sums must be a multiple of 16 bytes");
     const long long rows = d->M / n_ranks;
     GemmRoute route;
     route.n_dst = n_ranks;
     route.scatter_rows = static_cast<int>(rows);
     for (int p = 0; p < n_ranks; ++p) {
         B200_REQUIRE(peer_slots[p] != nullptr, "b200_gemm_reduce_scatter_partials: peer_slots[%d] is NULL", p);
-        // rank p's staging buffer is [n_ranks][rows][N] fp32; this rank writes slot `my_rank`
-        route.dst[p] = static_cast<float*>(peer_slots[p]) + static_cast<size_t>(my_rank) * rows * d->N;
+        // rank p's staging buffer is [n_ranks][rows][N] partial sums; this rank writes slot `my_rank`
+        route.dst[p] = static_cast<char*>(peer_slots[p]) + static_cast<size_t>(my_rank) * rows * d->N * pes;
         route.rows[p] = rows;
     }
     b200_gemm_desc local = *d;
     local.C = route.dst[my_rank];
     local.ldc = d->N;
-    local.c_dtype = B200_F32;
     local.bias = nullptr;
     local.activation = B200_ACT_NONE;
     local.alpha = 1.0f;
@@ -229,13 +230,19 @@ int b200_gemm_reduce_scatter_partials(b200_ctx* ctx, const b200_gemm_desc* d, vo
 }
 
 int b200_reduce_slices(b200_ctx* ctx, const float* slices, int n_slices, const b200_gemm_desc* d, void* stream) {
+    return b200_reduce_slices_typed(ctx, slices, B200_F32, n_slices, d, stream);
+}
+
+int b200_reduce_slices_typed(b200_ctx* ctx, const void* slices, int slices_dtype, int n_slices, const b200_gemm_desc* d,
+                             void* stream) {
     B200_REQUIRE(ctx && d, "b200_reduce_slices: NULL argument");
+    B200_REQUIRE(slices_dtype == B200_F32 || slices_dtype == B200_BF16, "b200_reduce_slices: slices are F32 or BF16");
     B200_REQUIRE(n_slices >= 1 && d->M >= 0 && d->N >= 0 && d->batch >= 1, "b200_reduce_slices: bad sizes");
     if (d->M == 0 || d->N == 0) return B200_OK;
     B200_REQUIRE(slices && d->C, "b200_reduce_slices: NULL buffer");
     B200_REQUIRE(d->ldc >= d->N, "b200_reduce_slices: ldc < N");
     DeviceScope scope(ctx->device);
-    return launch_splitk_reduce(ctx, *d, slices, n_slices, ctx->pick(stream));
+    return launch_splitk_reduce(ctx, *d, slices, n_slices, ctx->pick(stream), slices_dtype == B200_BF16);
 }
 
 }  // extern "C"

@@ -127,6 +127,7 @@ struct GemmParams {
     int c_vec_ok;      // rows of C start 16-byte aligned, so 16-byte stores are legal
     float* partial;    // k_splits > 1: fp32 partial sums [split][batch][M][N]
     int partial_round_bf16;  // HiFi2 / LoFi: round partial sums to bf16 precision
+    int partial_is_bf16;     // splitk_reduce_kernel only: the slices it sums are stored as bf16, not fp32
     unsigned* tickets; // pair kernel, k_splits > 1: one counter per (tile, CTA of the pair); the CTA whose slice
                        // finishes last adds the other slices' partial sums to its accumulator and writes C
     EpiParams epi;
@@ -166,7 +167,8 @@ struct GemmRoute {
 int launch_gemm_tcgen05(b200_ctx* ctx, const b200_gemm_desc& d, int k_splits, cudaStream_t stream,
                         const GemmRoute* route = nullptr, int block_n = 0, int group_m = 0);
 // Sums `splits` fp32 slices [splits][batch][M][N], applies the descriptor's epilogue and writes C.
-int launch_splitk_reduce(b200_ctx* ctx, const b200_gemm_desc& d, const float* partial, int splits, cudaStream_t stream);
+int launch_splitk_reduce(b200_ctx* ctx, const b200_gemm_desc& d, const void* partial, int splits, cudaStream_t stream,
+                         bool partial_bf16 = false);
 // CTA-pair (cta_group::2) kernel for large products; `gemm_pair_eligible` says whether it applies.
 bool gemm_pair_eligible(const b200_ctx* ctx, const b200_gemm_desc& d, const GemmRoute* route);
 // Layouts the pair kernel can handle at all, whatever the tile count.

@@ -410,6 +410,7 @@ __global__ void splitk_reduce_kernel(const GemmParams p) {
     const long long total = static_cast<long long>(p.batch) * p.M * cols4;
     const size_t slice = static_cast<size_t>(p.batch) * p.M * p.N;
     const bool vec_in = (p.N & 3) == 0 && (reinterpret_cast<uintptr_t>(p.partial) & 15u) == 0;
+    const __nv_bfloat16* partial16 = reinterpret_cast<const __nv_bfloat16*>(p.partial);
     const size_t c_es = p.c_f32 ? 4 : 2;
     const bool vec_out = (p.N & 3) == 0 && (p.ldc & 3) == 0 && (p.stride_c & 3) == 0 &&
                          (reinterpret_cast<uintptr_t>(p.C) & (4 * c_es - 1)) == 0;
@@ -422,7 +423,21 @@ __global__ void splitk_reduce_kernel(const GemmParams p) {
         const int n = c4 * 4;
         const size_t off = (static_cast<size_t>(b) * p.M + m) * p.N + n;
         float acc[4] = {0.f, 0.f, 0.f, 0.f};
-        if (vec_in) {
+        if (p.partial_is_bf16) {
+            if (vec_in) {   // 8-byte loads of four bf16 values
+                for (int s = 0; s < p.k_splits; ++s) {
+                    const uint2 v = *reinterpret_cast<const uint2*>(partial16 + s * slice + off);
+                    acc[0] += __uint_as_float(v.x << 16);
+                    acc[1] += __uint_as_float(v.x & 0xffff0000u);
+                    acc[2] += __uint_as_float(v.y << 16);
+                    acc[3] += __uint_as_float(v.y & 0xffff0000u);
+                }
+            } else {
+                for (int s = 0; s < p.k_splits; ++s)
+                    for (int j = 0; j < 4; ++j)
+                        if (n + j < p.N) acc[j] += __bfloat162float(partial16[s * slice + off + j]);
+            }
+        } else if (vec_in) {
             for (int s = 0; s < p.k_splits; ++s) {
                 const float4 v = *reinterpret_cast<const float4*>(p.partial + s * slice + off);
                 acc[0] += v.x;
@@ -744,13 +759,15 @@ int launch_gemm_tcgen05(b200_ctx* ctx, const b200_gemm_desc& d, int k_splits, cu
     return B200_OK;
 }
 
-int launch_splitk_reduce(b200_ctx* ctx, const b200_gemm_desc& d, const float* partial, int splits, cudaStream_t stream) {
+int launch_splitk_reduce(b200_ctx* ctx, const b200_gemm_desc& d, const void* partial, int splits, cudaStream_t stream,
+                         bool partial_bf16) {
     GemmParams p{};
+    p.partial_is_bf16 = partial_bf16 ? 1 : 0;
     p.M = static_cast<int>(d.M);
     p.N = static_cast<int>(d.N);
     p.batch = static_cast<int>(d.batch);
     p.k_splits = splits;
-    p.partial = const_cast<float*>(partial);
+    p.partial = static_cast<float*>(const_cast<void*>(partial));
     p.C = d.C;
     p.ldc = d.ldc;
     p.stride_c = d.stride_c;

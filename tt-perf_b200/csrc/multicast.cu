@@ -14,10 +14,12 @@
 #include <sys/un.h>
 #include <unistd.h>
 
+#include <algorithm>
 #include <cstring>
 #include <vector>
 
 #include "common.cuh"
+#include "ptx.cuh"
 
 struct b200_mc {
     b200_comm* comm = nullptr;
@@ -196,11 +198,20 @@ void mc_release_local(const DriverApi* api, b200_mc* m) {
 }  // namespace
 }  // namespace b200
 
-using namespace b200;
-
 namespace b200 {
 b200_ctx* comm_ctx(b200_comm* comm);   // comm.cu
+
+namespace {
+// 16 bytes per thread and step from this GPU's memory to a multicast address: every bound GPU receives the block.
+__global__ void mc_broadcast_kernel(const uint4* __restrict__ src, uint4* mc_dst, size_t chunks) {
+    const size_t stride = static_cast<size_t>(gridDim.x) * blockDim.x;
+    for (size_t i = blockIdx.x * static_cast<size_t>(blockDim.x) + threadIdx.x; i < chunks; i += stride)
+        ptx::multimem_st_v4(mc_dst + i, src[i]);
 }
+}  // namespace
+}  // namespace b200
+
+using namespace b200;
 
 extern "C" {
 
@@ -331,6 +342,20 @@ int b200_mc_alloc(b200_comm* comm, size_t bytes, b200_mc** out_mc, void** out_lo
     *out_mc = m;
     *out_local_ptr = reinterpret_cast<void*>(m->uc_ptr);
     *out_multicast_ptr = reinterpret_cast<void*>(m->mc_ptr);
+    return B200_OK;
+}
+
+int b200_mc_broadcast(b200_ctx* ctx, void* mc_dst, const void* d_src, size_t bytes, void* stream) {
+    B200_REQUIRE(ctx != nullptr, "b200_mc_broadcast: ctx is NULL");
+    if (bytes == 0) return B200_OK;
+    B200_REQUIRE(mc_dst && d_src, "b200_mc_broadcast: NULL buffer");
+    B200_REQUIRE(((reinterpret_cast<uintptr_t>(mc_dst) | reinterpret_cast<uintptr_t>(d_src) | bytes) & 15u) == 0,
+                 "b200_mc_broadcast: addresses and size must be multiples of 16 bytes");
+    DeviceScope scope(ctx->device);
+    const size_t chunks = bytes / 16;
+    const int blocks = static_cast<int>(std::min<size_t>((chunks + 255) / 256, static_cast<size_t>(ctx->sm_count) * 8));
+    mc_broadcast_kernel<<<blocks, 256, 0, ctx->pick(stream)>>>(static_cast<const uint4*>(d_src), static_cast<uint4*>(mc_dst), chunks);
+    B200_CUDA_TRY(cudaGetLastError());
     return B200_OK;
 }
 

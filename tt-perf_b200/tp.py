@@ -89,6 +89,18 @@ class ProcessFabric:
         self._bufs.append(b)
         return b.ptrs
 
+    def shared_multicast(self, nbytes: int):
+        """(local pointer, multicast pointer) of a buffer that every rank holds a copy of and that one store to the
+        multicast address updates everywhere; None when the GPUs offer no NVLink multicast (collective either way)."""
+        if self.world < 2 or self.comm is None or not self.ctx.mc_supported():
+            return None
+        try:
+            b = capi.MulticastBuffer(self.comm, nbytes)
+        except capi.B200Error:
+            return None
+        self._bufs.append(b)
+        return b.local, b.multicast
+
     def barrier(self) -> None:
         """Host-side: wait for this rank's stream, then for every rank."""
         self.ctx.synchronize()
@@ -120,8 +132,15 @@ def _shared_layout(T: int, Tr: int, D: int, world: int):
 class TPBlockRank:
     """One rank's share of the block. `ptrs[name][p]` is this rank's pointer to rank p's buffer `name`."""
 
-    def __init__(self, ctx, rank: int, world: int, *, batch: int, seq: int, d_model: int, heads: int, host_w: dict, ptrs: dict):
+    def __init__(self, ctx, rank: int, world: int, *, batch: int, seq: int, d_model: int, heads: int, host_w: dict, ptrs: dict,
+                 multicast: dict | None = None, partial_dtype: int = F32):
+        """multicast: {buffer name: multicast address} for the all-gathered buffers that live in NVLink multicast
+        memory (their row blocks are then broadcast with one store instead of one copy per peer).
+        partial_dtype: F32, or BF16 to send the partial tiles of the row-parallel products as bf16 (half the bytes on
+        the links, one more rounding per partial sum)."""
         self.ctx, self.rank, self.world = ctx, rank, world
+        self.mc = multicast or {}
+        self.pdt = partial_dtype
         self.B, self.S, self.D, self.H = batch, seq, d_model, heads
         self.T = batch * seq
         if self.T % world or (self.T // world) % 128:
@@ -155,6 +174,9 @@ class TPBlockRank:
         """Copies this rank's row block of its own `name` buffer into the same rows of every peer's buffer."""
         off = self.row0 * self.D * 2
         pitch = self.D * 2
+        if name in self.mc:     # one multimem.st per 16 bytes reaches every rank (this one included)
+            self.ctx.mc_broadcast(self.mc[name] + off, self.ptrs[name][self.rank] + off, self.Tr * pitch)
+            return
         for step in range(1, self.world):
             p = (self.rank + step) % self.world     # ranks start at different peers
             capi.check(capi.lib().b200_peer_copy_2d(self.ctx._h, self.ptrs[name][p] + off, pitch, self.ctx._h,
@@ -162,12 +184,12 @@ class TPBlockRank:
 
     def _scatter_partials(self, slots: str, a, b, n: int, k: int, *, transpose_b: bool, lda: int, ldb: int) -> None:
         """fp32 partial of a [T, k] x (b) product, row block j stored into slot `rank` of rank j's staging buffer."""
-        d = self.ctx.gemm_desc(a, b, None, self.T, n, k, transpose_b=transpose_b, lda=lda, ldb=ldb, ldc=n, c_dtype=F32)
+        d = self.ctx.gemm_desc(a, b, None, self.T, n, k, transpose_b=transpose_b, lda=lda, ldb=ldb, ldc=n, c_dtype=self.pdt)
         self.ctx.gemm_reduce_scatter_partials(d, self.ptrs[slots], self.rank)
 
     def _reduce_slots(self, slots: str, out: DeviceTensor, n: int, bias=None) -> None:
         d = self.ctx.gemm_desc(None, None, out, self.Tr, n, 0, lda=8, ldb=n, bias=bias)
-        self.ctx.reduce_slices(self.ptrs[slots][self.rank], self.world, d)
+        self.ctx.reduce_slices(self.ptrs[slots][self.rank], self.world, d, slices_dtype=self.pdt)
 
     # -- forward ----------------------------------------------------------------------------------------------------
     def forward(self, x_r: DeviceTensor):
@@ -283,7 +305,7 @@ class TPBlockRank:
         self.opt[1].step([self.grads[k] for k in f32])
 
 
-def make_emulated(ctx, world: int, *, batch: int, seq: int, d_model: int, heads: int, host_w: dict):
+def make_emulated(ctx, world: int, *, batch: int, seq: int, d_model: int, heads: int, host_w: dict, partial_dtype: int = F32):
     """g ranks of one block in this process (one GPU). Returns (ranks, fabric)."""
     T = batch * seq
     fabric = EmulatedFabric(ctx, world)
@@ -292,7 +314,8 @@ def make_emulated(ctx, world: int, *, batch: int, seq: int, d_model: int, heads:
         views = fabric.shared(nbytes)
         for r in range(world):
             per_rank[r][name] = views[r]
-    ranks = [TPBlockRank(ctx, r, world, batch=batch, seq=seq, d_model=d_model, heads=heads, host_w=host_w, ptrs=per_rank[r])
+    ranks = [TPBlockRank(ctx, r, world, batch=batch, seq=seq, d_model=d_model, heads=heads, host_w=host_w, ptrs=per_rank[r],
+                         partial_dtype=partial_dtype)
              for r in range(world)]
     return ranks, fabric
 
@@ -313,12 +336,23 @@ def run_emulated(generators) -> None:
         live = nxt
 
 
-def make_process(ctx, rank: int, world: int, *, batch: int, seq: int, d_model: int, heads: int, host_w: dict, comm=None):
-    """This process's rank of the block (one process per GPU). Returns (rank object, fabric)."""
+def make_process(ctx, rank: int, world: int, *, batch: int, seq: int, d_model: int, heads: int, host_w: dict, comm=None,
+                 multicast: bool = True, partial_dtype: int = F32):
+    """This process's rank of the block (one process per GPU). Returns (rank object, fabric). With `multicast` the four
+    all-gathered activations / gradients live in NVLink multicast memory when the GPUs offer it."""
     T = batch * seq
     fabric = ProcessFabric(ctx, rank, world, comm)
-    ptrs = {name: fabric.shared(nbytes) for name, nbytes in _shared_layout(T, T // world, d_model, world)}
-    return TPBlockRank(ctx, rank, world, batch=batch, seq=seq, d_model=d_model, heads=heads, host_w=host_w, ptrs=ptrs), fabric
+    ptrs, mc = {}, {}
+    for name, nbytes in _shared_layout(T, T // world, d_model, world):
+        pair = fabric.shared_multicast(nbytes) if (multicast and name.endswith("_full")) else None
+        if pair is not None:
+            ptrs[name] = [pair[0]] * world       # only this rank's copy is ever addressed directly
+            mc[name] = pair[1]
+        else:
+            ptrs[name] = fabric.shared(nbytes)
+    rk = TPBlockRank(ctx, rank, world, batch=batch, seq=seq, d_model=d_model, heads=heads, host_w=host_w, ptrs=ptrs,
+                     multicast=mc, partial_dtype=partial_dtype)
+    return rk, fabric
 
 
 def run_process(generator, fabric: ProcessFabric, *, host_barriers: bool = False) -> None:
