@@ -476,7 +476,8 @@ int b200_gemm_allgather_mc(b200_ctx* ctx, const b200_gemm_desc* desc, void* mc_c
  *      memory, so the question never arises there) ----------------------------------------------------
  * Same arguments and result as b200_gemm on the tcgen05 path, for hosts that must not allocate device
  * memory at call time: executors that gave all of HBM to their own arena, loops with a latency bound
- * (cudaMalloc / cudaFree synchronise the device), code running under stream capture. The fp32 partial
+ * (cudaMalloc / cudaFree synchronise the device), processes whose device memory is capped below what a growing
+ * scratch block would need. The fp32 partial
  * sums of the K slices live in a fixed 32 MiB array inside the library image (held by every GPU that
  * loads the library until the process exits) instead of context scratch; the call performs no
  * cudaMalloc, cudaFree or other allocating routine and needs no b200_ctx.

@@ -1,5 +1,5 @@
 """b200_gemm_static_scratch — the split-K matmul for hosts that may not allocate device memory at call time
-(arena-owning executors, latency-bound loops, code under stream capture): its partial sums live in a fixed
+(arena-owning executors, latency-bound loops, processes with a device-memory cap): its partial sums live in a fixed
 32 MiB array inside the library instead of cudaMalloc'ed context scratch.
 
 The file name sorts last on purpose: a run that stops at the first failure has then already run every other
@@ -50,6 +50,36 @@ def test_static_scratch_matches_gemm_on_two_calls_in_a_row(pkg, ctx, stream):
                              activation=pkg.ACT_RELU)
     assert _same(got, ref)
     assert mo.rel_frobenius(got.float().cpu().numpy(), mo.relu(oracle + bias.float().cpu().numpy())) <= 1e-2
+
+
+def test_static_scratch_calls_leave_device_memory_untouched_and_report_their_status(pkg, ctx, stream):
+    """After the set-up call of a shape class, further calls change neither the free device memory nor the caching
+    pools of the process (the property arena-owning hosts need), and b200_static_scratch_status — this entry point's
+    counterpart of b200_synchronize — reports a clean status."""
+    s = stream.cuda_stream
+    g = torch.Generator().manual_seed(404)
+    M, N, K = 256, 384, 4096
+    a = torch.randn(K, M, generator=g).bfloat16().cuda()
+    b = torch.randn(K, N, generator=g).bfloat16().cuda()
+    c = torch.empty(M, N, dtype=torch.bfloat16, device="cuda")
+    desc = ctx.gemm_desc(a, b, c, M, N, K, transpose_a=True, split_k=4)
+    ctx.gemm_static_scratch(desc, s)                    # set-up call: symbol addresses, kernel attributes
+    assert ctx.static_scratch_status(s) == 0
+    torch.cuda.synchronize()
+    free_before, _ = torch.cuda.mem_get_info()
+    for _ in range(5):
+        ctx.gemm_static_scratch(desc, s)
+    assert ctx.static_scratch_status(s) == 0
+    torch.cuda.synchronize()
+    free_after, _ = torch.cuda.mem_get_info()
+    assert free_after == free_before, (free_before, free_after)
+    ref = mo.matmul(a.float().cpu().numpy(), b.float().cpu().numpy(), True, False)
+    assert mo.rel_frobenius(c.float().cpu().numpy(), ref) <= 1e-2
+    # the descriptor checks are those of b200_gemm
+    bad = ctx.gemm_desc(a, b, c, M, N, K, transpose_a=True, split_k=4)
+    bad.ab_dtype = 7
+    with pytest.raises(pkg.B200Error):
+        ctx.gemm_static_scratch(bad, s)
 
 
 def test_static_scratch_rejects_what_does_not_fit(pkg, ctx, stream):

@@ -41,7 +41,6 @@ constexpr int BT = 128;                   // queries per tile and keys per tile
 constexpr int TILE_BYTES = BT * DH * 2;   // a [128 x 64] bf16 tile, rows of 128 bytes
 constexpr int PT_BYTES = BT * BT * 2;     // a [128 x 128] bf16 tile stored as two 64-column slabs of 16 KB
 constexpr int UMMA_K = 16;
-constexpr int FWD_THREADS = 256;   // 8 warps, all computing; thread 0 also issues the copies and MMAs
 constexpr int BWD_COMPUTE_WARPS = 16;
 constexpr int BWD_THREADS = (BWD_COMPUTE_WARPS + 1) * 32;
 constexpr float LOG2E = 1.4426950408889634f;
@@ -101,67 +100,84 @@ struct FwdParams {
     int* status;
 };
 
-constexpr int FWD_TMEM_COLS = 256;  // S: columns 0..127, O_j: 128..191
-constexpr int FWD_SMEM_USED = 5 * TILE_BYTES + PT_BYTES + 64 + 1024;  // tiles, barriers, row-maximum exchange
-// Two CTAs per SM have 2 * (FWD_SMEM + 1 KB the hardware reserves per CTA) <= 228 KB to share, which leaves no room for
-// rounding the base up to 1024: the kernel relies on the base being 1024-aligned already (it is when the kernel has no
-// static shared memory) and reports an error instead of running when it is not.
-constexpr int FWD_SMEM = FWD_SMEM_USED;
-static_assert(2 * (FWD_SMEM + 1024) <= 228 * 1024, "two forward CTAs must fit one SM");
+// One CTA per (batch, head, PAIR of 128-query tiles), one CTA per SM, roles by warp:
+//     warp 0       TMA: Q of both tiles once, then the K tiles and the V tiles through two rings of two stages each
+//     warp 1       one thread issues every MMA: S_t = Q_t K^T and O_t,j = P_t,j V_j for the two tiles t = 0, 1
+//     warps 2-5    softmax of tile 0: a thread owns one query row and all 128 keys of the tile — no exchange with other
+//     warps 6-9    softmax of tile 1  threads, no CTA-wide barrier. Per key tile: row maximum (exact, fp32), P = exp2(.)
+//                  as bf16 into shared memory, running sum; the row's 64 output values live in registers and O_t,j is
+//                  folded into them one tile late.
+// Nothing the softmax threads wait for depends on their own last step: when P_t,j is ready the MMA thread first issues
+// S_t,j+1 (which needs only K_j+1 and the S_t columns, free by then) and publishes it, and only then O_t,j = P_t,j V_j.
+// So P_t and O_t are double-buffered: P_t,j+1 is written while O_t,j still reads P_t,j, and O_t,j is folded (after
+// P_t,j+1 has been handed over, while the tensor core computes S_t,j+2) from the TMEM columns that O_t,j+2 will reuse.
+// TMEM: S_0, S_1 (2 x 128 columns), O_t,b (4 x 64). The exponentials are the slowest unit (16 per clock and SM): while the
+// threads of one tile evaluate theirs, those of the other take maxima, fold or wait.
+constexpr int FWD_THREADS = 320;
+constexpr int FWD_STAGES = 2;
+constexpr int FWD_TMEM_COLS = 512;
+constexpr int FWD_SMEM_USED = 2 * TILE_BYTES + 2 * FWD_STAGES * TILE_BYTES + 4 * PT_BYTES + 256;
+constexpr int FWD_SMEM = FWD_SMEM_USED + 1024;   // room to round the base up to 1024
+static_assert(FWD_SMEM <= 227 * 1024, "forward shared memory exceeds the per-CTA limit");
 
-// 256 threads: registers are handed out to pairs of warps, so a ninth warp for issuing would cost a fifth of the
-// register file and the second CTA per SM with it. Thread 0 issues the copies and the MMAs between the barriers
-// instead; it has nothing else to do there but wait for the tensor cores.
-__global__ void __launch_bounds__(FWD_THREADS, 2)
+__global__ void __launch_bounds__(FWD_THREADS, 1)
 attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
                 const __grid_constant__ CUtensorMap tmV, const FwdParams p) {
     extern __shared__ uint8_t smem_raw[];
-    const uint32_t pad = (1024u - (smem_u32(smem_raw) & 1023u)) & 1023u;
-    if (pad + FWD_SMEM_USED > FWD_SMEM) {  // uniform over the CTA; nothing has been set up yet
-        if (threadIdx.x == 0) atomicExch(p.status, 1);
-        return;
-    }
-    uint8_t* smem = smem_raw + pad;
-    uint8_t* sQ = smem;
-    uint8_t* sK = sQ + TILE_BYTES;       // 2 stages
-    uint8_t* sV = sK + 2 * TILE_BYTES;   // 2 stages
-    uint8_t* sP = sV + 2 * TILE_BYTES;
-    uint64_t* q_full = reinterpret_cast<uint64_t*>(sP + PT_BYTES);
-    uint64_t* kv_full = q_full + 1;      // 2
-    uint64_t* s_full = kv_full + 2;      // S of a tile is in TMEM (and every earlier MMA has run)
-    uint64_t* o_full = s_full + 1;       // the last P V product has run
-    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(o_full + 1);
+    uint8_t* smem = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
+    uint8_t* sQ = smem;                                   // 2 tiles
+    uint8_t* sK = sQ + 2 * TILE_BYTES;                    // FWD_STAGES tiles
+    uint8_t* sV = sK + FWD_STAGES * TILE_BYTES;           // FWD_STAGES tiles
+    uint8_t* sP = sV + FWD_STAGES * TILE_BYTES;           // [tile t][buffer] of [128 x 128] bf16
+    uint64_t* q_full = reinterpret_cast<uint64_t*>(sP + 4 * PT_BYTES);  // 2
+    uint64_t* k_full = q_full + 2;                        // FWD_STAGES
+    uint64_t* k_empty = k_full + FWD_STAGES;              // FWD_STAGES: every S product that reads the stage has run
+    uint64_t* v_full = k_empty + FWD_STAGES;              // FWD_STAGES
+    uint64_t* v_empty = v_full + FWD_STAGES;              // FWD_STAGES: every P V product that reads the stage has run
+    uint64_t* s_full = v_empty + FWD_STAGES;              // 2: S_t of a key tile is in TMEM
+    uint64_t* p_ready = s_full + 2;                       // 2: P_t is in shared memory and S_t has been read (4 arrivals)
+    uint64_t* pv_full = p_ready + 2;                      // 2: O_t,j is in TMEM and P_t,j has been read
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(pv_full + 2);
     volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
-    // [column half][row] local maxima, exchanged exactly (fp32): with the true row maximum the largest probability of a
-    // row is exp2(0) = 1, which bf16 holds without error, so a nearly one-hot row loses nothing in the P V product —
-    // the backward pass's cancellation dP - rowsum(dO O) depends on that. One buffer is enough: nobody sees the next S
-    // before every thread has passed the barrier that follows the P stores, i.e. has read this tile's values.
-    float* xch = reinterpret_cast<float*>(reinterpret_cast<uint8_t*>(q_full) + 64);
 
     const int warp = threadIdx.x >> 5;
     const int lane = threadIdx.x & 31;
     const Geom g = p.g;
-    const int bh = blockIdx.y;
+    // The grid is [batch x head, tile pair] with the first index running fastest: every pair with the most key tiles
+    // is handed out before any lighter one, so the last CTAs to start are the short ones.
+    const int bh = blockIdx.x;
     const int b = bh / g.H;
     const int h = bh - b * g.H;
-    const int qt = static_cast<int>(gridDim.x) - 1 - static_cast<int>(blockIdx.x);  // long rows of work first
-    const int q0 = qt * BT;
-    const int n_kv_all = (g.S + BT - 1) / BT;
-    const int n_kv = g.causal ? min(qt + 1, n_kv_all) : n_kv_all;
+    const int n_q_all = (g.S + BT - 1) / BT;
+    const int n_kv_all = n_q_all;
+    const int pair = static_cast<int>(gridDim.y) - 1 - static_cast<int>(blockIdx.y);
+    int qt[2], n_kv[2];
+    for (int t = 0; t < 2; ++t) {
+        qt[t] = 2 * pair + t;
+        n_kv[t] = qt[t] >= n_q_all ? 0 : (g.causal ? min(qt[t] + 1, n_kv_all) : n_kv_all);
+    }
+    const int n_max = max(n_kv[0], n_kv[1]);
 
     if (threadIdx.x == 0) {
         prefetch_tensormap(&tmQ);
         prefetch_tensormap(&tmK);
         prefetch_tensormap(&tmV);
-        mbar_init(q_full, 1);
-        mbar_init(&kv_full[0], 1);
-        mbar_init(&kv_full[1], 1);
-        mbar_init(s_full, 1);
-        mbar_init(o_full, 1);
+        for (int t = 0; t < 2; ++t) {
+            mbar_init(&q_full[t], 1);
+            mbar_init(&s_full[t], 1);
+            mbar_init(&p_ready[t], 4);
+            mbar_init(&pv_full[t], 1);
+        }
+        for (int st = 0; st < FWD_STAGES; ++st) {
+            mbar_init(&k_full[st], 1);
+            mbar_init(&k_empty[st], 1);
+            mbar_init(&v_full[st], 1);
+            mbar_init(&v_empty[st], 1);
+        }
         *abort_flag = 0;
         mbar_fence_init();
     }
-    if (warp == 0) {
+    if (warp == 1) {
         tmem_alloc(tmem_slot, FWD_TMEM_COLS);
         tmem_relinquish_alloc_permit();
     }
@@ -170,187 +186,228 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
     tcgen05_fence_after_sync();
     const uint32_t tmem_base = *tmem_slot;
 
-    constexpr uint32_t idesc_s = make_idesc_bf16_f32(BT, BT, 0u, 0u);   // Q (K-major) x K (K-major)
-    constexpr uint32_t idesc_o = make_idesc_bf16_f32(BT, DH, 0u, 1u);   // P (K-major) x V (MN-major)
-    int armed0 = 0, armed1 = 0;  // thread 0: how often each K/V stage has been armed
-    auto load_kv = [&](int tile) {
-        const int st = tile & 1;
-        mbar_arrive_expect_tx(&kv_full[st], 2 * TILE_BYTES);
-        tma_load_4d(sK + st * TILE_BYTES, &tmK, &kv_full[st], 0, tile * BT, h, b);
-        tma_load_4d(sV + st * TILE_BYTES, &tmV, &kv_full[st], 0, tile * BT, h, b);
-        if (st == 0) ++armed0; else ++armed1;
-    };
-    auto issue_s = [&](int tile) {
-        const uint32_t a = smem_u32(sQ);
-        const uint32_t bb = smem_u32(sK + (tile & 1) * TILE_BYTES);
-#pragma unroll
-        for (int k = 0; k < DH / UMMA_K; ++k)
-            umma_f16_ss(tmem_base, make_smem_desc_sw128(a + k * 32, 0, 1024), make_smem_desc_sw128(bb + k * 32, 0, 1024),
-                        idesc_s, k > 0 ? 1u : 0u);
-        umma_commit(s_full);
-    };
-    bool issuer_ok = true;  // meaningful in thread 0 only
-    if (threadIdx.x == 0) {
-        mbar_arrive_expect_tx(q_full, TILE_BYTES);
-        tma_load_4d(sQ, &tmQ, q_full, 0, q0, h, b);
-        load_kv(0);
-        issuer_ok = mbar_wait(q_full, 0, abort_flag) && mbar_wait(&kv_full[0], 0, abort_flag);
-        if (issuer_ok) {
-            tcgen05_fence_after_sync();
-            issue_s(0);
+    if (warp == 0) {
+        // ---------------------------------------------------------------------------------- TMA producer
+        if (lane == 0) {
+            int armed_q = 0, armed_k = 0, armed_v = 0;
+            for (int t = 0; t < 2; ++t) {
+                if (n_kv[t] == 0) continue;
+                mbar_arrive_expect_tx(&q_full[t], TILE_BYTES);
+                tma_load_4d(sQ + t * TILE_BYTES, &tmQ, &q_full[t], 0, qt[t] * BT, h, b);
+                armed_q |= 1 << t;
+            }
+            for (int j = 0; j < n_max; ++j) {
+                const int st = j % FWD_STAGES;
+                const uint32_t reuse_parity = ((j / FWD_STAGES) - 1) & 1;
+                if (j >= FWD_STAGES && !mbar_wait(&k_empty[st], reuse_parity, abort_flag)) break;
+                mbar_arrive_expect_tx(&k_full[st], TILE_BYTES);
+                tma_load_4d(sK + st * TILE_BYTES, &tmK, &k_full[st], 0, j * BT, h, b);
+                armed_k = j + 1;
+                if (j >= FWD_STAGES && !mbar_wait(&v_empty[st], reuse_parity, abort_flag)) break;
+                mbar_arrive_expect_tx(&v_full[st], TILE_BYTES);
+                tma_load_4d(sV + st * TILE_BYTES, &tmV, &v_full[st], 0, j * BT, h, b);
+                armed_v = j + 1;
+            }
+            if (*abort_flag != 0) {  // let armed copies land before the shared memory is released
+                for (int t = 0; t < 2; ++t)
+                    if (armed_q & (1 << t)) drain(&q_full[t], 0);
+                for (int j = max(0, armed_k - FWD_STAGES); j < armed_k; ++j) drain(&k_full[j % FWD_STAGES], (j / FWD_STAGES) & 1);
+                for (int j = max(0, armed_v - FWD_STAGES); j < armed_v; ++j) drain(&v_full[j % FWD_STAGES], (j / FWD_STAGES) & 1);
+            }
         }
-    }
-    __syncwarp();
-
-    const int quarter = warp & 3;
-    const int half = warp >> 2;          // columns [64 * half, 64 * half + 64) of S, [32 * half, +32) of O
-    const int r = quarter * 32 + lane;   // accumulator row = TMEM lane
-    const int row = q0 + r;
-    const uint32_t lane_addr = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16);
-    const int limit = g.causal ? min(row, g.S - 1) : g.S - 1;  // last visible key of this row
-    const float sl2 = g.scale_log2;
-    float m = -INFINITY, l = 0.f, alpha = 0.f;
-    float o[32];
+    } else if (warp == 1) {
+        // ---------------------------------------------------------------------------------- MMA issuer
+        if (lane == 0) {
+            constexpr uint32_t idesc_s = make_idesc_bf16_f32(BT, BT, 0u, 0u);   // Q (K-major) x K (K-major)
+            constexpr uint32_t idesc_o = make_idesc_bf16_f32(BT, DH, 0u, 1u);   // P (K-major) x V (MN-major)
+            auto issue_s = [&](int t, int j) {
+                const uint32_t a = smem_u32(sQ + t * TILE_BYTES);
+                const uint32_t bb = smem_u32(sK + (j % FWD_STAGES) * TILE_BYTES);
 #pragma unroll
-    for (int i = 0; i < 32; ++i) o[i] = 0.f;
-    auto fold_pv = [&]() {  // O = O * alpha + (P V of the tile before)
-        uint32_t v[32];
-        tmem_ld_32x32b_x32(lane_addr + 128 + half * 32, v);
-        tmem_ld_wait();
+                for (int k = 0; k < DH / UMMA_K; ++k)
+                    umma_f16_ss(tmem_base + t * BT, make_smem_desc_sw128(a + k * 32, 0, 1024),
+                                make_smem_desc_sw128(bb + k * 32, 0, 1024), idesc_s, k > 0 ? 1u : 0u);
+                umma_commit(&s_full[t]);
+            };
+            auto issue_pv = [&](int t, int j) {
+                const uint32_t pa = smem_u32(sP + (t * 2 + (j & 1)) * PT_BYTES);
+                const uint32_t vb = smem_u32(sV + (j % FWD_STAGES) * TILE_BYTES);
 #pragma unroll
-        for (int i = 0; i < 32; ++i) o[i] = fmaf(o[i], alpha, __uint_as_float(v[i]));
-    };
-    // `ok` is uniform over the warp. A warp that gave up keeps walking the loop without touching TMEM or waiting, so
-    // that the other warps never wait for it at the named barriers.
-    bool ok = true;
-    for (int j = 0; j < n_kv; ++j) {
-        if (ok) {
-            // s_full of tile j is committed after the P V product of tile j - 1, so it covers both
-            const bool got = mbar_wait(s_full, j & 1, abort_flag);
-            ok = __all_sync(0xffffffffu, got);
-        }
-        if (threadIdx.x == 0 && ok && j + 1 < n_kv) load_kv(j + 1);  // its stage was last read by the P V product of j - 1
-        __syncwarp();
-        uint32_t s0[32], s1[32];
-        const int lim = limit - j * BT - half * 64;  // index, within this thread's 64 columns, of the last visible one
-        const bool masked = lim < 63;
-        float mine = -INFINITY;
-        if (ok) {
-            tcgen05_fence_after_sync();
-            if (j > 0) fold_pv();
-            tmem_ld_32x32b_x32(lane_addr + half * 64, s0);
-            tmem_ld_32x32b_x32(lane_addr + half * 64 + 32, s1);
-            tmem_ld_wait();
-            float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
-            if (!masked) {
-#pragma unroll
-                for (int i = 0; i < 32; ++i) {
-                    mx4[i & 3] = fmaxf(mx4[i & 3], __uint_as_float(s0[i]));
-                    mx4[i & 3] = fmaxf(mx4[i & 3], __uint_as_float(s1[i]));
+                for (int k = 0; k < BT / UMMA_K; ++k)
+                    umma_f16_ss(tmem_base + 2 * BT + (t * 2 + (j & 1)) * DH,
+                                make_smem_desc_sw128(pa + (k >> 2) * TILE_BYTES + (k & 3) * 32, 0, 1024),
+                                make_smem_desc_sw128(vb + k * (UMMA_K * 128), BT * 128, 1024), idesc_o, k > 0 ? 1u : 0u);
+                umma_commit(&pv_full[t]);
+            };
+            bool ok = true;
+            int k_seen = 0, v_seen = 0;  // key tiles whose K / V are known to have landed
+            auto need = [&](uint64_t* full, int& seen, int j) {
+                while (ok && seen <= j) {
+                    ok = mbar_wait(&full[seen % FWD_STAGES], (seen / FWD_STAGES) & 1, abort_flag);
+                    ++seen;
                 }
-            } else {
-#pragma unroll
-                for (int i = 0; i < 32; ++i) {
-                    if (i <= lim) mx4[i & 3] = fmaxf(mx4[i & 3], __uint_as_float(s0[i]));
-                    if (i + 32 <= lim) mx4[i & 3] = fmaxf(mx4[i & 3], __uint_as_float(s1[i]));
+                if (ok) tcgen05_fence_after_sync();
+            };
+            for (int t = 0; ok && t < 2; ++t)
+                if (n_kv[t] > 0) ok = mbar_wait(&q_full[t], 0, abort_flag);
+            if (ok && n_max > 0) need(k_full, k_seen, 0);
+            for (int t = 0; ok && t < 2; ++t)
+                if (n_kv[t] > 0) issue_s(t, 0);
+            if (ok && n_max > 0) umma_commit(&k_empty[0]);
+            for (int j = 0; ok && j < n_max; ++j) {
+                for (int t = 0; ok && t < 2; ++t) {
+                    if (j >= n_kv[t]) continue;
+                    ok = mbar_wait(&p_ready[t], j & 1, abort_flag);
+                    if (!ok) break;
+                    tcgen05_fence_after_sync();
+                    if (j + 1 < n_kv[t]) {
+                        need(k_full, k_seen, j + 1);
+                        if (!ok) break;
+                        issue_s(t, j + 1);
+                    }
+                    need(v_full, v_seen, j);
+                    if (!ok) break;
+                    issue_pv(t, j);
+                }
+                if (ok) {   // every product that reads K_j+1 and V_j has been issued
+                    if (j + 1 < n_max) umma_commit(&k_empty[(j + 1) % FWD_STAGES]);
+                    umma_commit(&v_empty[j % FWD_STAGES]);
                 }
             }
-            mine = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3]));
-            xch[half * BT + r] = mine;
         }
-        compute_warps_sync<FWD_THREADS>();
-        if (ok) {
+    } else {
+        // ---------------------------------------------------------------------------------- softmax of tile t
+        const int t = (warp - 2) >> 2;
+        const int quarter = warp & 3;          // the TMEM lane quarter a warp may read
+        const int r = quarter * 32 + lane;     // row of the tile = TMEM lane
+        const int row = qt[t] * BT + r;
+        const uint32_t lane_addr = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16);
+        const uint32_t s_addr = lane_addr + static_cast<uint32_t>(t * BT);
+        const uint32_t o_addr = lane_addr + static_cast<uint32_t>(2 * BT + t * 2 * DH);
+        const int limit = g.causal ? min(row, g.S - 1) : g.S - 1;  // last visible key of this row
+        const float sl2 = g.scale_log2;
+        float m = -INFINITY, l = 0.f, alpha = 0.f;
+        float o[DH];
+#pragma unroll
+        for (int i = 0; i < DH; ++i) o[i] = 0.f;
+        uint32_t va[32], vb[32];   // two TMEM reads in flight
+        auto fold_pv = [&](int j, float a) {  // O = O * a + O_t,j
+            tmem_ld_32x32b_x32(o_addr + (j & 1) * DH, va);
+            tmem_ld_32x32b_x32(o_addr + (j & 1) * DH + 32, vb);
+            tmem_ld_wait();
+#pragma unroll
+            for (int i = 0; i < 32; ++i) o[i] = fmaf(o[i], a, __uint_as_float(va[i]));
+#pragma unroll
+            for (int i = 0; i < 32; ++i) o[32 + i] = fmaf(o[32 + i], a, __uint_as_float(vb[i]));
+        };
+        bool ok = true;   // uniform over the warp
+        const int n_mine = n_kv[t];
+        for (int j = 0; ok && j < n_mine; ++j) {
+            const bool got = mbar_wait(&s_full[t], j & 1, abort_flag);
+            ok = __all_sync(0xffffffffu, got);
+            if (!ok) break;
+            tcgen05_fence_after_sync();
+            const int lim = limit - j * BT;      // index, within the tile, of the last visible key
+            const bool masked = lim < BT - 1;
+            uint8_t* myP = sP + (t * 2 + (j & 1)) * PT_BYTES;
+            // pass 1: the row maximum over the visible keys; the chunks are read in the order 0, 1, 2, 3 and the last
+            // two stay in registers for pass 2
+            float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
+            auto take_max = [&](const uint32_t* sv, int c) {
+                if (!masked) {
+#pragma unroll
+                    for (int i = 0; i < 32; ++i) mx4[i & 3] = fmaxf(mx4[i & 3], __uint_as_float(sv[i]));
+                } else {
+#pragma unroll
+                    for (int i = 0; i < 32; ++i)
+                        if (c * 32 + i <= lim) mx4[i & 3] = fmaxf(mx4[i & 3], __uint_as_float(sv[i]));
+                }
+            };
+            tmem_ld_32x32b_x32(s_addr, va);
+            tmem_ld_32x32b_x32(s_addr + 32, vb);
+            tmem_ld_wait();
+            take_max(va, 0);
+            tmem_ld_32x32b_x32(s_addr + 64, va);
+            take_max(vb, 1);
+            tmem_ld_32x32b_x32(s_addr + 96, vb);
+            tmem_ld_wait();
+            take_max(va, 2);
+            take_max(vb, 3);
             // finite: every tile shows each row at least one key
-            const float mx = fmaxf(m, fmaxf(mine, xch[(half ^ 1) * BT + r]));
-            alpha = ex2((m - mx) * sl2);  // 0 on the first tile (m = -inf)
+            const float mx = fmaxf(m, fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3])));
+            const float alpha_before = alpha;   // belongs to O_t,j-1, folded below
+            alpha = ex2((m - mx) * sl2);        // 0 on the first tile (m = -inf)
             const float mb = mx * sl2;
             m = mx;
+            // pass 2: probabilities as bf16 into the layout the P V product reads, and their sum
             float rs4[4] = {0.f, 0.f, 0.f, 0.f};
-            auto emit = [&](const uint32_t (&sv)[32], int c) {  // 32 columns: probabilities, partial sums, bf16 store
+            auto take_exp = [&](const uint32_t* sv, int c) {
 #pragma unroll
-                for (int t = 0; t < 4; ++t) {
+                for (int u = 0; u < 4; ++u) {
                     float f[8];
 #pragma unroll
                     for (int e = 0; e < 8; ++e) {
-                        const int i = t * 8 + e;
+                        const int i = u * 8 + e;
                         float pr = ex2(fmaf(__uint_as_float(sv[i]), sl2, -mb));
                         if (masked && c * 32 + i > lim) pr = 0.f;
                         rs4[e & 3] += pr;
                         f[e] = pr;
                     }
-                    store_bf16x8(sP + pt_offset(r, half * 8 + c * 4 + t), f);
+                    store_bf16x8(myP + pt_offset(r, c * 4 + u), f);
                 }
             };
-            emit(s0, 0);
-            emit(s1, 1);
+            take_exp(va, 2);
+            tmem_ld_32x32b_x32(s_addr, va);
+            take_exp(vb, 3);
+            tmem_ld_32x32b_x32(s_addr + 32, vb);
+            tmem_ld_wait();
+            take_exp(va, 0);
+            take_exp(vb, 1);
             l = l * alpha + ((rs4[0] + rs4[1]) + (rs4[2] + rs4[3]));
             fence_proxy_async_smem();
             tcgen05_fence_before_sync();
-        }
-        compute_warps_sync<FWD_THREADS>();  // P is complete in shared memory; S and the old P V product have been read
-        if (threadIdx.x == 0 && ok && issuer_ok) {
-            tcgen05_fence_after_sync();
-            const uint32_t pa = smem_u32(sP);
-            const uint32_t vb = smem_u32(sV + (j & 1) * TILE_BYTES);
-#pragma unroll
-            for (int k = 0; k < BT / UMMA_K; ++k)
-                umma_f16_ss(tmem_base + 128, make_smem_desc_sw128(pa + (k >> 2) * TILE_BYTES + (k & 3) * 32, 0, 1024),
-                            make_smem_desc_sw128(vb + k * (UMMA_K * 128), BT * 128, 1024), idesc_o, k > 0 ? 1u : 0u);
-            if (j + 1 < n_kv) {
-                issuer_ok = mbar_wait(&kv_full[(j + 1) & 1], ((j + 1) >> 1) & 1, abort_flag);
-                if (issuer_ok) {
-                    tcgen05_fence_after_sync();
-                    issue_s(j + 1);
-                }
-            } else {
-                umma_commit(o_full);
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&p_ready[t]);
+            if (j > 0) {   // while the tensor core computes S_t,j+1
+                const bool got_o = mbar_wait(&pv_full[t], (j - 1) & 1, abort_flag);
+                ok = __all_sync(0xffffffffu, got_o);
+                if (!ok) break;
+                tcgen05_fence_after_sync();
+                fold_pv(j - 1, alpha_before);
             }
         }
-        __syncwarp();
-    }
-    if (ok) {
-        const bool got = mbar_wait(o_full, 0, abort_flag);
-        ok = __all_sync(0xffffffffu, got);
-    }
-    float* lsum = reinterpret_cast<float*>(sP);  // once the last P V product is complete the P tile is free
-    if (ok) {
-        tcgen05_fence_after_sync();
-        fold_pv();
-        lsum[half * BT + r] = l;
-    }
-    compute_warps_sync<FWD_THREADS>();
-    if (ok && row < g.S) {
-        const float total = l + lsum[(half ^ 1) * BT + r];
-        const float inv = 1.f / total;
-#pragma unroll
-        for (int i = 0; i < 32; ++i) o[i] *= inv;
-        uint8_t* dst = reinterpret_cast<uint8_t*>(p.o.ptr + b * p.o.sb + h * p.o.sh + static_cast<long long>(row) * p.o.ss +
-                                                  half * 32);
-#pragma unroll
-        for (int t = 0; t < 4; ++t) store_bf16x8(dst + t * 16, o + 8 * t);
-        if (p.o_lo.ptr != nullptr) {
-            // The backward pass needs rowsum(dO * O); with O known only to bf16 that row term is off by up to 2^-9 of
-            // |dO||O|, the same for every key of the row, which the dQ / dK products then multiply with the keys'
-            // (queries') common component. The dropped part of O, stored as a second bf16 tensor, restores it.
-#pragma unroll
-            for (int i = 0; i < 32; ++i) o[i] -= __bfloat162float(__float2bfloat16_rn(o[i]));
-            uint8_t* dst_lo = reinterpret_cast<uint8_t*>(p.o_lo.ptr + b * p.o_lo.sb + h * p.o_lo.sh +
-                                                         static_cast<long long>(row) * p.o_lo.ss + half * 32);
-#pragma unroll
-            for (int t = 0; t < 4; ++t) store_bf16x8(dst_lo + t * 16, o + 8 * t);
+        if (ok && n_mine > 0) {
+            const bool got = mbar_wait(&pv_full[t], (n_mine - 1) & 1, abort_flag);
+            ok = __all_sync(0xffffffffu, got);
         }
-        if (half == 0) p.lse[(static_cast<long long>(bh)) * g.S + row] = (m * sl2 + log2f(total)) * LN2;
-    }
-    if (threadIdx.x == 0 && *abort_flag != 0) {  // let armed copies land before the shared memory is released
-        if (armed0) drain(&kv_full[0], (armed0 - 1) & 1);
-        if (armed1) drain(&kv_full[1], (armed1 - 1) & 1);
-        drain(q_full, 0);
+        if (ok && n_mine > 0) {
+            tcgen05_fence_after_sync();
+            fold_pv(n_mine - 1, alpha);
+            if (row < g.S) {
+                const float inv = 1.f / l;
+#pragma unroll
+                for (int i = 0; i < DH; ++i) o[i] *= inv;
+                uint8_t* dst = reinterpret_cast<uint8_t*>(p.o.ptr + b * p.o.sb + h * p.o.sh + static_cast<long long>(row) * p.o.ss);
+#pragma unroll
+                for (int u = 0; u < DH / 8; ++u) store_bf16x8(dst + u * 16, o + 8 * u);
+                if (p.o_lo.ptr != nullptr) {
+                    // what bf16 drops of O, for the backward pass's row term rowsum(dO * O)
+#pragma unroll
+                    for (int i = 0; i < DH; ++i) o[i] -= __bfloat162float(__float2bfloat16_rn(o[i]));
+                    uint8_t* dst_lo = reinterpret_cast<uint8_t*>(p.o_lo.ptr + b * p.o_lo.sb + h * p.o_lo.sh +
+                                                                 static_cast<long long>(row) * p.o_lo.ss);
+#pragma unroll
+                    for (int u = 0; u < DH / 8; ++u) store_bf16x8(dst_lo + u * 16, o + 8 * u);
+                }
+                p.lse[(static_cast<long long>(bh)) * g.S + row] = (m * sl2 + log2f(l)) * LN2;
+            }
+        }
     }
 
     tcgen05_fence_before_sync();
     __syncthreads();
     if (threadIdx.x == 0 && *abort_flag != 0) atomicExch(p.status, 1);
-    if (warp == 0) {
+    if (warp == 1) {
         tcgen05_fence_after_sync();
         tmem_dealloc(tmem_base, FWD_TMEM_COLS);
     }
@@ -408,10 +465,10 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
     const int warp = threadIdx.x >> 5;
     const int lane = threadIdx.x & 31;
     const Geom g = p.g;
-    const int bh = blockIdx.y;
+    const int bh = blockIdx.x;
     const int b = bh / g.H;
     const int h = bh - b * g.H;
-    const int jt = blockIdx.x;  // key tile; with the causal mask tile 0 has the most work and starts first
+    const int jt = blockIdx.y;  // key tile; with the causal mask tile 0 has the most work, and every (batch, head) starts it first
     const int n_q = (g.S + BT - 1) / BT;
     const int i0 = g.causal ? jt : 0;
     const int n_it = n_q - i0;
@@ -729,8 +786,8 @@ int check_geometry(int64_t B, int64_t H, int64_t S, int head_dim, float scale) {
     if (head_dim != DH)
         return fail(B200_ERR_UNSUPPORTED, "attention: head_dim %d is not supported by the fused kernels (64 only)", head_dim);
     B200_REQUIRE(B >= 0 && H >= 0 && S >= 0, "attention: negative extent");
-    B200_REQUIRE(B * H <= 65535, "attention: batch * heads = %lld exceeds 65535", (long long)(B * H));
-    B200_REQUIRE(S <= (1 << 24), "attention: sequence length %lld too large", (long long)S);
+    B200_REQUIRE(B * H <= (1 << 24), "attention: batch * heads = %lld exceeds 2^24", (long long)(B * H));
+    B200_REQUIRE(S <= (1 << 22), "attention: sequence length %lld exceeds 2^22", (long long)S);
     B200_REQUIRE(scale > 0.f && std::isfinite(scale), "attention: scale must be positive and finite");
     return B200_OK;
 }
@@ -809,7 +866,8 @@ int b200_attention_forward_hp(b200_ctx* ctx, const b200_attn_operand* q, const b
     p.status = ctx->d_status;
     static bool configured[64] = {};
     if ((rc = configure_once(attn_fwd_kernel, FWD_SMEM, configured)) != B200_OK) return rc;
-    const dim3 grid(static_cast<unsigned>((S + BT - 1) / BT), static_cast<unsigned>(B * H));
+    const int64_t q_tiles = (S + BT - 1) / BT;
+    const dim3 grid(static_cast<unsigned>(B * H), static_cast<unsigned>((q_tiles + 1) / 2));
     attn_fwd_kernel<<<grid, FWD_THREADS, FWD_SMEM, stream>>>(tmQ, tmK, tmV, p);
     B200_CUDA_TRY(cudaGetLastError());
     return B200_OK;
@@ -881,7 +939,7 @@ int b200_attention_backward_hp(b200_ctx* ctx, const b200_attn_operand* q, const 
     p.status = ctx->d_status;
     static bool configured[64] = {};
     if ((rc = configure_once(attn_bwd_kernel, BWD_SMEM, configured)) != B200_OK) return rc;
-    const dim3 grid(static_cast<unsigned>((S + BT - 1) / BT), static_cast<unsigned>(B * H));
+    const dim3 grid(static_cast<unsigned>(B * H), static_cast<unsigned>((S + BT - 1) / BT));
     attn_bwd_kernel<<<grid, BWD_THREADS, BWD_SMEM, stream>>>(tmQ, tmK, tmV, tmdO, tmdQ, p);
     B200_CUDA_TRY(cudaGetLastError());
     attn_dq_store_kernel<<<blocks, 256, 0, stream>>>(dq_acc, as_out(d_q), static_cast<int>(B), static_cast<int>(H),

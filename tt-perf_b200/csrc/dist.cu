@@ -210,6 +210,10 @@ int b200_gemm_reduce_scatter_partials(b200_ctx* ctx, const b200_gemm_desc* d, vo
     GemmRoute route;
     route.n_dst = n_ranks;
     route.scatter_rows = static_cast<int>(rows);
+    // Every rank walks the row blocks in the same cyclic order but starts one block after its own: at any moment the
+    // ranks store into different owners (all starting at block 0 would aim g - 1 senders at one receiver's links) and
+    // the local block, which needs no link, comes last, when the other ranks' traffic is tailing off.
+    route.m_rotate_rows = static_cast<long long>((my_rank + 1) % n_ranks) * rows;
     for (int p = 0; p < n_ranks; ++p) {
         B200_REQUIRE(peer_slots[p] != nullptr, "b200_gemm_reduce_scatter_partials: peer_slots[%d] is NULL", p);
         // rank p's staging buffer is [n_ranks][rows][N] partial sums; this rank writes slot `my_rank`

@@ -144,6 +144,8 @@ struct GemmParams {
     int n_dst;
     int scatter_rows;
     int dst_rotate;    // first destination each box is sent to (ranks start at different peers, so no peer is hit by all at once)
+    int m_tile_rotate; // the tile order starts at this row tile and wraps around (reduce-scatter: rank r starts with the row
+                       // block of rank r + 1, so that at any moment the ranks store into different owners)
 };
 
 // Destination tensor maps of the TMA-store epilogue.
@@ -158,6 +160,7 @@ struct GemmRoute {
     long long rows[8] = {};        // rows of each destination matrix
     int scatter_rows = 0;
     int rotate = 0;                // index of the destination to store to first
+    long long m_rotate_rows = 0;   // start the tile order at this output row (wraps around)
     void* mc_dst = nullptr;        // non-null: ONE destination written with 16-byte warp stores instead of TMA stores
     int mc_multimem = 0;           // those stores are multimem.st (mc_dst is a multicast address)
 };

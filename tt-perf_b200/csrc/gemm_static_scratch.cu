@@ -3,8 +3,8 @@
 // Who needs it. b200_gemm's split-K path keeps its fp32 partial sums in context scratch that it grows
 // with cudaMalloc on demand. Some hosts cannot tolerate that: an executor that has handed all of HBM to
 // its own arena (a foreign cudaMalloc then fails or fragments the arena), a serving loop with a latency
-// bound (cudaMalloc and cudaFree synchronise the whole device), or code that runs while a stream is
-// being captured (allocation is illegal there). This entry point gives them the same kernels with the
+// bound (cudaMalloc and cudaFree synchronise the whole device), or a process whose device memory is
+// capped below what a growing scratch block would need. This entry point gives them the same kernels with the
 // partial sums in a fixed array that is part of the library image, so a call performs no cudaMalloc,
 // no cudaFree and no other allocating routine — it only encodes two tensor maps on the host and
 // launches the GEMM and the reduce kernel.

@@ -65,7 +65,8 @@ __device__ __forceinline__ WorkItem decode_work(const GemmParams& p, int w, int 
     const int first_m = g * p.group_m;
     const int gsz = min(p.num_m_tiles - first_m, p.group_m);
     const int rr = t - g * tiles_per_group;
-    const int mi = first_m + rr % gsz;
+    int mi = first_m + rr % gsz + p.m_tile_rotate;
+    if (mi >= p.num_m_tiles) mi -= p.num_m_tiles;
     const int ni = rr / gsz;
     it.m0 = mi * BM;
     it.n0 = ni * BN;
@@ -728,6 +729,7 @@ int launch_gemm_tcgen05(b200_ctx* ctx, const b200_gemm_desc& d, int k_splits, cu
             p.epi_mode = 1;
             p.n_dst = route->scatter_rows > 0 ? 1 : route->n_dst;
             p.scatter_rows = route->scatter_rows;
+            p.m_tile_rotate = static_cast<int>((route->m_rotate_rows / BM) % p.num_m_tiles);
             p.dst_rotate = (route->scatter_rows > 0 || route->rotate < 0 || route->rotate >= route->n_dst) ? 0 : route->rotate;
         } else if (p.c_vec_ok) {
             rc = make_tensor_map(ctx, &tmC.m[0], d.C, d.N, d.M, d.batch, d.ldc, d.stride_c, box_cols, 32, p.c_f32);

@@ -61,7 +61,9 @@ __device__ __forceinline__ PairWork decode_pair(const GemmParams& p, int w) {
     const int first_m = g * p.group_m;
     const int gsz = min(p.num_m_tiles - first_m, p.group_m);
     const int rr = t - g * tiles_per_group;
-    it.m0 = (first_m + rr % gsz) * BM_PAIR;
+    int mi = first_m + rr % gsz + p.m_tile_rotate;
+    if (mi >= p.num_m_tiles) mi -= p.num_m_tiles;
+    it.m0 = mi * BM_PAIR;
     it.n0 = (rr / gsz) * BN;
     return it;
 }
@@ -579,6 +581,7 @@ int launch_gemm_tcgen05_pair(b200_ctx* ctx, const b200_gemm_desc& d, cudaStream_
         }
         p.n_dst = route->scatter_rows > 0 ? 1 : route->n_dst;
         p.scatter_rows = route->scatter_rows;
+        p.m_tile_rotate = static_cast<int>((route->m_rotate_rows / BM_PAIR) % p.num_m_tiles);
         p.dst_rotate = (route->scatter_rows > 0 || route->rotate < 0 || route->rotate >= route->n_dst) ? 0 : route->rotate;
     } else {
         rc = encode_map(ctx, &tmC.m[0], d.C, d.N, d.M, d.batch, d.ldc, d.stride_c, box_cols, 32, p.c_f32);
