@@ -42,7 +42,7 @@ constexpr int TILE_BYTES = BT * DH * 2;   // a [128 x 64] bf16 tile, rows of 128
 constexpr int PT_BYTES = BT * BT * 2;     // a [128 x 128] bf16 tile stored as two 64-column slabs of 16 KB
 constexpr int UMMA_K = 16;
 constexpr int BWD_COMPUTE_WARPS = 16;
-constexpr int BWD_THREADS = (BWD_COMPUTE_WARPS + 1) * 32;
+constexpr int BWD_THREADS = (BWD_COMPUTE_WARPS + 2) * 32;   // + the TMA / MMA warp and the dQ store warp
 constexpr float LOG2E = 1.4426950408889634f;
 constexpr float LN2 = 0.6931471805599453f;
 
@@ -78,6 +78,13 @@ __device__ __forceinline__ uint32_t pt_offset(int r, int unit) {
 __device__ __forceinline__ void store_bf16x8(uint8_t* dst, const float* f) {
     *reinterpret_cast<uint4*>(dst) = make_uint4(pack_bf16x2(f[0], f[1]), pack_bf16x2(f[2], f[3]), pack_bf16x2(f[4], f[5]),
                                                 pack_bf16x2(f[6], f[7]));
+}
+
+// Two finite fp32 values to bf16x2, rounding to nearest by adding half a bf16 ulp to the bit pattern and keeping the
+// upper half (ties move away from zero instead of to even: one pattern in 65536). The cvt instruction shares the
+// special-function pipe with the exponentials, which the element-wise phases keep busy; these are integer adds.
+__device__ __forceinline__ uint32_t pack_round_bf16x2(float lo, float hi) {
+    return __byte_perm(__float_as_uint(lo) + 0x8000u, __float_as_uint(hi) + 0x8000u, 0x7632);
 }
 
 // Lets copies that were armed but never consumed land before the CTA's shared memory is released.
@@ -419,17 +426,19 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
 struct BwdParams {
     Geom g;
     Strided dk, dv;
-    const float* lse;   // [B, H, S]
-    const float* dsum;  // [B, H, S]  rowsum(dO * O)
+    const float* lse2;  // [B, H, S_pad]  lse * log2(e); +inf in the padding rows (probability 0)
+    const float* dsc;   // [B, H, S_pad]  rowsum(dO * O) * scale; 0 in the padding rows
+    int s_pad;          // S rounded up to whole tiles
     float* dq_acc;      // [B, H, S, 64] fp32, zeroed before the launch
     int* status;
 };
 
 constexpr int BWD_TMEM_COLS = 512;  // S^T 0..127, dP^T 128..255, dK 256..319, dV 320..383, dQ_i 384..447
 constexpr int DQ_BOX_BYTES = BT * 32 * 4;   // [128 queries x 32 fp32 columns], rows of 128 bytes
-// K, V, Q x 2, dO x 2, P^T, dS^T, two dQ staging buffers of two boxes each, lse / rowsum, barriers. That is all of the
-// 227 KB a CTA may have, with 960 bytes to spare for rounding the base up to 1024 (the kernel checks that this suffices).
-constexpr int BWD_SMEM_USED = 6 * TILE_BYTES + 2 * PT_BYTES + 4 * DQ_BOX_BYTES + 2048 + 64;
+// K, V, Q x 2, dO x 2, P^T, dS^T, two dQ staging buffers of two boxes each, the per-query terms of two tiles, barriers.
+// That is all of the 227 KB a CTA may have, with 896 bytes to spare for rounding the base up to 1024 (the kernel checks
+// that this suffices).
+constexpr int BWD_SMEM_USED = 6 * TILE_BYTES + 2 * PT_BYTES + 4 * DQ_BOX_BYTES + 2048 + 128;
 constexpr int BWD_SMEM = 227 * 1024;
 static_assert(BWD_SMEM_USED <= BWD_SMEM, "backward shared memory exceeds the per-CTA limit");
 
@@ -451,15 +460,18 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
     uint8_t* sPT = sdO + 2 * TILE_BYTES;  // P^T   [keys x queries]
     uint8_t* sdST = sPT + PT_BYTES;       // dS^T  [keys x queries]
     uint8_t* sDQ = sdST + PT_BYTES;       // dQ_i as two swizzled [128 x 32] fp32 boxes on their way to the accumulators, x 2
-    float* lse_s = reinterpret_cast<float*>(sDQ + 4 * DQ_BOX_BYTES);  // [2][128], already times log2(e)
-    float* dsum_s = lse_s + 2 * BT;                            // [2][128]
-    uint64_t* kv_full = reinterpret_cast<uint64_t*>(dsum_s + 2 * BT);
+    float* stat_s = reinterpret_cast<float*>(sDQ + 4 * DQ_BOX_BYTES);   // [column group][tile parity][lse2 | dsc][32]
+    uint64_t* kv_full = reinterpret_cast<uint64_t*>(stat_s + 4 * 2 * 64);
     uint64_t* qdo_full = kv_full + 1;     // 2
     uint64_t* sdp_full = qdo_full + 2;    // S^T and dP^T of a tile are in TMEM
     uint64_t* pds_ready = sdp_full + 1;   // P^T and dS^T of a tile are in shared memory
     uint64_t* dq_full = pds_ready + 1;    // dQ_i is in TMEM
     uint64_t* acc_done = dq_full + 1;     // the dV and dK products of a tile have run
-    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_done + 1);
+    uint64_t* sdp_free = acc_done + 1;    // S^T and dP^T of a tile are in registers: the next tile's may be written
+    uint64_t* dq_staged = sdp_free + 1;   // dQ_i is in its staging boxes
+    uint64_t* dq_free = dq_staged + 1;    // 2: the reduction that read a staging buffer has left it
+    uint64_t* dq_read = dq_free + 2;      // dQ_i has left TMEM
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(dq_read + 1);
     volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
     const int warp = threadIdx.x >> 5;
@@ -486,6 +498,11 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
         mbar_init(pds_ready, BWD_COMPUTE_WARPS);  // one arrival per warp
         mbar_init(dq_full, 1);
         mbar_init(acc_done, 1);
+        mbar_init(sdp_free, BWD_COMPUTE_WARPS);
+        mbar_init(dq_staged, 4);   // the four warps (one per TMEM lane quarter) whose turn it is
+        mbar_init(dq_read, 4);
+        mbar_init(&dq_free[0], 1);
+        mbar_init(&dq_free[1], 1);
         *abort_flag = 0;
         mbar_fence_init();
     }
@@ -518,27 +535,43 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
             if (n_it > 1) load_qdo(1);
             bool ok = mbar_wait(kv_full, 0, abort_flag);
             const uint32_t ka = smem_u32(sK), va = smem_u32(sV), pta = smem_u32(sPT), dsa = smem_u32(sdST);
+            auto issue_sdp = [&](int it) {   // S^T = K Q_i^T and dP^T = V dO_i^T
+                const uint32_t qa = smem_u32(sQ + (it & 1) * TILE_BYTES);
+                const uint32_t doa = smem_u32(sdO + (it & 1) * TILE_BYTES);
+#pragma unroll
+                for (int k = 0; k < DH / UMMA_K; ++k)
+                    umma_f16_ss(tmem_base, make_smem_desc_sw128(ka + k * 32, 0, 1024),
+                                make_smem_desc_sw128(qa + k * 32, 0, 1024), idesc_nt, k > 0 ? 1u : 0u);
+#pragma unroll
+                for (int k = 0; k < DH / UMMA_K; ++k)
+                    umma_f16_ss(tmem_base + 128, make_smem_desc_sw128(va + k * 32, 0, 1024),
+                                make_smem_desc_sw128(doa + k * 32, 0, 1024), idesc_nt, k > 0 ? 1u : 0u);
+                umma_commit(sdp_full);
+            };
+            if (ok) ok = mbar_wait(&qdo_full[0], 0, abort_flag);
+            if (ok) {
+                tcgen05_fence_after_sync();
+                issue_sdp(0);
+            }
+            // The tensor core executes in issue order, and issuing a product takes about as long as the product before
+            // it runs. So S^T and dP^T of tile i + 1 are issued as soon as the element-wise warps hold those of tile i in
+            // registers, and run while the warps evaluate tile i; dQ_i, dV and dK follow when P^T and dS^T of tile i are in
+            // shared memory, and run while the warps evaluate tile i + 1.
             for (int it = 0; ok && it < n_it; ++it) {
                 const int st = it & 1;
-                if (!mbar_wait(&qdo_full[st], (it >> 1) & 1, abort_flag)) { ok = false; break; }
+                if (it + 1 < n_it) {
+                    if (!mbar_wait(sdp_free, it & 1, abort_flag) ||
+                        !mbar_wait(&qdo_full[(it + 1) & 1], ((it + 1) >> 1) & 1, abort_flag)) { ok = false; break; }
+                    tcgen05_fence_after_sync();
+                    issue_sdp(it + 1);
+                }
+                if (!mbar_wait(pds_ready, it & 1, abort_flag)) { ok = false; break; }
+                if (it > 0 && !mbar_wait(dq_read, (it - 1) & 1, abort_flag)) { ok = false; break; }   // dQ_i-1 has left TMEM
                 tcgen05_fence_after_sync();
                 const uint32_t qa = smem_u32(sQ + st * TILE_BYTES);
                 const uint32_t doa = smem_u32(sdO + st * TILE_BYTES);
 #pragma unroll
-                for (int k = 0; k < DH / UMMA_K; ++k)   // S^T = K Q^T
-                    umma_f16_ss(tmem_base, make_smem_desc_sw128(ka + k * 32, 0, 1024),
-                                make_smem_desc_sw128(qa + k * 32, 0, 1024), idesc_nt, k > 0 ? 1u : 0u);
-#pragma unroll
-                for (int k = 0; k < DH / UMMA_K; ++k)   // dP^T = V dO^T
-                    umma_f16_ss(tmem_base + 128, make_smem_desc_sw128(va + k * 32, 0, 1024),
-                                make_smem_desc_sw128(doa + k * 32, 0, 1024), idesc_nt, k > 0 ? 1u : 0u);
-                // This commit also covers the dV and dK products of the tile before: once it fires P^T and dS^T may be
-                // overwritten.
-                umma_commit(sdp_full);
-                if (!mbar_wait(pds_ready, it & 1, abort_flag)) { ok = false; break; }
-                tcgen05_fence_after_sync();
-#pragma unroll
-                for (int k = 0; k < BT / UMMA_K; ++k)   // dQ_i = dS K (reduction over the 128 keys); first, it is read first
+                for (int k = 0; k < BT / UMMA_K; ++k)   // dQ_i = dS K (reduction over the 128 keys)
                     umma_f16_ss(tmem_base + 384, make_smem_desc_sw128(dsa + k * (UMMA_K * 128), BT * 128, 1024),
                                 make_smem_desc_sw128(ka + k * (UMMA_K * 128), BT * 128, 1024), idesc_mn, k > 0 ? 1u : 0u);
                 umma_commit(dq_full);
@@ -564,38 +597,80 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
                 drain(kv_full, 0);
             }
         }
+    } else if (warp == BWD_COMPUTE_WARPS + 1) {
+        // dQ_i leaves through one thread of a warp of its own: issuing the two reductions takes this thread a microsecond
+        // or so, which the element-wise warps would otherwise spend at a barrier.
+        if (lane == 0) {
+            for (int it = 0; it < n_it; ++it) {
+                if (!mbar_wait(dq_staged, it & 1, abort_flag)) break;
+                const int st = it & 1;
+                tma_reduce_add_3d(&tmdQ, sDQ + (st * 2) * DQ_BOX_BYTES, 0, (i0 + it) * BT, bh);
+                tma_reduce_add_3d(&tmdQ, sDQ + (st * 2 + 1) * DQ_BOX_BYTES, 32, (i0 + it) * BT, bh);
+                tma_store_commit();
+                if (it > 0) {   // the boxes of the tile before have been read: their buffer may be refilled
+                    tma_store_wait_read<1>();
+                    mbar_arrive(&dq_free[(it - 1) & 1]);
+                }
+            }
+            tma_store_wait_all<0>();
+        }
     } else {
         const int quarter = warp & 3;
         const int cg = warp >> 2;            // columns [32 * cg, +32) of S^T / dP^T; [16 * cg, +16) of dQ_i, dK, dV
         const int r = quarter * 32 + lane;   // TMEM lane: key row for S^T, dP^T, dK, dV; query row for dQ_i
         const uint32_t lane_addr = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16);
         const float sl2 = g.scale_log2;
-        // `ok` is uniform over the warp. A warp that gave up keeps walking the loop without touching TMEM or waiting, so
-        // that the other warps never wait for it at the named barrier.
-        bool ok = true;
-        // threads 0..127 carry lse (times log2 e), threads 128..255 rowsum(dO O): the value of the NEXT query tile is
-        // requested one iteration ahead so that its latency is hidden
-        const int st_which = threadIdx.x >> 7, st_idx = threadIdx.x & (BT - 1);
-        auto stat_load = [&](int tile) -> float {
-            const int qi = tile * BT + st_idx;
-            const long long at = static_cast<long long>(bh) * g.S + qi;
-            if (st_which == 0) return qi < g.S ? p.lse[at] * LOG2E : INFINITY;   // +inf: probability 0 for padding
-            return qi < g.S ? p.dsum[at] : 0.f;
-        };
-        float stat_next = threadIdx.x < 2 * BT ? stat_load(i0) : 0.f;
-        for (int it = 0; it < n_it; ++it) {
-            const int st = it & 1;
-            const int i = i0 + it;
-            if (threadIdx.x < 2 * BT) {
-                (st_which == 0 ? lse_s : dsum_s)[st * BT + st_idx] = stat_next;
-                if (it + 1 < n_it) stat_next = stat_load(i + 1);
+        bool ok = true;   // uniform over the warp
+        // The element-wise warps meet only at mbarriers, each at its own pace: no CTA-wide barrier. dQ of a tile is moved
+        // out of TMEM by the four warps of one column group, a different group for every tile, so that no warp is the
+        // slow one twice in a row: TMEM -> two swizzled [128 x 32] fp32 boxes in shared memory, from where one TMA
+        // reduction each adds them to the fp32 accumulators (rows beyond S are dropped by the tensor map).
+        auto stage_dq = [&](int itd) {
+            const int sd = itd & 1;
+            const bool got_dq = mbar_wait(dq_full, itd & 1, abort_flag);
+            ok = __all_sync(0xffffffffu, got_dq);
+            if (ok && itd >= 2) {
+                const bool got_buf = mbar_wait(&dq_free[sd], ((itd - 2) >> 1) & 1, abort_flag);
+                ok = __all_sync(0xffffffffu, got_buf);
             }
-            if (threadIdx.x == 0) tma_store_wait_read<1>();  // the dQ boxes of two tiles ago have left their buffer
-            compute_warps_sync<BWD_COMPUTE_WARPS * 32>();
+            if (!ok) return;
+            tcgen05_fence_after_sync();
+#pragma unroll
+            for (int box = 0; box < 2; ++box) {
+                uint32_t v[32];
+                tmem_ld_32x32b_x32(lane_addr + 384 + box * 32, v);
+                tmem_ld_wait();
+                uint8_t* box_row = sDQ + (sd * 2 + box) * DQ_BOX_BYTES + r * 128;
+#pragma unroll
+                for (int c = 0; c < 8; ++c)
+                    *reinterpret_cast<uint4*>(box_row + ((c ^ (r & 7)) << 4)) = make_uint4(v[4 * c], v[4 * c + 1], v[4 * c + 2], v[4 * c + 3]);
+            }
+            fence_proxy_async_smem();
+            tcgen05_fence_before_sync();
+            __syncwarp();
+            if (lane == 0) {
+                mbar_arrive(dq_read);
+                mbar_arrive(dq_staged);
+            }
+        };
+        // The per-query terms of the 32 queries of this column group reach the four warps that share them through
+        // shared memory: each is requested from global memory a tile ahead by one lane (lanes of quarters 0 and 1),
+        // written when the tile before has been evaluated, and published by a barrier of these four warps alone.
+        const float* stat_src = (quarter == 0 ? p.lse2 : p.dsc) + static_cast<long long>(bh) * p.s_pad + cg * 32 + lane;
+        float* stat_mine = stat_s + cg * 128;
+        float stat_next = 0.f;
+        if (quarter < 2) {
+            stat_mine[quarter * 32 + lane] = stat_src[i0 * BT];
+            if (n_it > 1) stat_next = stat_src[(i0 + 1) * BT];
+        }
+        for (int it = 0; it < n_it; ++it) {   // a warp that gave up keeps walking: its three siblings wait for it at the barrier
+            const int i = i0 + it;
+            asm volatile("bar.sync %0, 128;" ::"r"(1 + cg) : "memory");   // the terms of tile i are in shared memory
             if (ok) {
                 const bool got = mbar_wait(sdp_full, it & 1, abort_flag);
                 ok = __all_sync(0xffffffffu, got);
             }
+            uint32_t pp[16], dd[16];   // P^T and dS^T of this thread's 32 queries as bf16 pairs
             if (ok) {
                 tcgen05_fence_after_sync();
                 const bool diag = g.causal && i == jt;  // query (column) c sees key (row) r only when c >= r
@@ -603,60 +678,67 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
                 tmem_ld_32x32b_x32(lane_addr + cg * 32, sv);
                 tmem_ld_32x32b_x32(lane_addr + 128 + cg * 32, dp);
                 tmem_ld_wait();
-                const float4* l4 = reinterpret_cast<const float4*>(lse_s + st * BT + cg * 32);
-                const float4* d4 = reinterpret_cast<const float4*>(dsum_s + st * BT + cg * 32);
+                if (it + 1 < n_it) {   // both are in registers: the tensor core may write the next tile's
+                    tcgen05_fence_before_sync();
+                    __syncwarp();
+                    if (lane == 0) mbar_arrive(sdp_free);
+                }
+                const float4* l4 = reinterpret_cast<const float4*>(stat_mine + (it & 1) * 64);
+                const float4* d4 = l4 + 8;
+                // P^T = exp2(S^T scale log2 e - lse log2 e); dS^T = P^T (dP^T - rowsum) scale, with rowsum * scale staged
+                auto evaluate = [&](auto masked_c) {
+                    constexpr bool MASKED = decltype(masked_c)::value;
 #pragma unroll
-                for (int t = 0; t < 4; ++t) {
-                    float pf[8], df[8];
+                    for (int t = 0; t < 4; ++t) {
+                        float pf[8], df[8];
 #pragma unroll
-                    for (int u = 0; u < 2; ++u) {
-                        const float4 lv = l4[t * 2 + u];
-                        const float4 dv = d4[t * 2 + u];
-                        const float ls[4] = {lv.x, lv.y, lv.z, lv.w};
-                        const float ds[4] = {dv.x, dv.y, dv.z, dv.w};
+                        for (int u = 0; u < 2; ++u) {
+                            const float4 lv = l4[t * 2 + u];
+                            const float4 dv = d4[t * 2 + u];
+                            const float ls[4] = {lv.x, lv.y, lv.z, lv.w};
+                            const float ds[4] = {dv.x, dv.y, dv.z, dv.w};
+#pragma unroll
+                            for (int e = 0; e < 4; ++e) {
+                                const int idx = t * 8 + u * 4 + e;
+                                float pr = ex2(fmaf(__uint_as_float(sv[idx]), sl2, -ls[e]));
+                                if (MASKED && cg * 32 + idx < r) pr = 0.f;
+                                pf[u * 4 + e] = pr;
+                                df[u * 4 + e] = pr * fmaf(__uint_as_float(dp[idx]), g.scale, -ds[e]);
+                            }
+                        }
 #pragma unroll
                         for (int e = 0; e < 4; ++e) {
-                            const int idx = t * 8 + u * 4 + e;
-                            float pr = ex2(fmaf(__uint_as_float(sv[idx]), sl2, -ls[e]));
-                            if (diag && cg * 32 + idx < r) pr = 0.f;
-                            pf[u * 4 + e] = pr;
-                            df[u * 4 + e] = pr * (__uint_as_float(dp[idx]) - ds[e]) * g.scale;
+                            pp[t * 4 + e] = pack_bf16x2(pf[2 * e], pf[2 * e + 1]);
+                            dd[t * 4 + e] = pack_bf16x2(df[2 * e], df[2 * e + 1]);
                         }
                     }
+                };
+                if (diag) evaluate(std::true_type{});
+                else evaluate(std::false_type{});
+            }
+            if (ok && it > 0 && cg == ((it - 1) & 3)) stage_dq(it - 1);   // its product was issued a whole tile ago
+            if (ok && it > 0) {   // so were the dV and dK products that read the P^T and dS^T about to be replaced
+                const bool got_acc = mbar_wait(acc_done, (it - 1) & 1, abort_flag);
+                ok = __all_sync(0xffffffffu, got_acc);
+            }
+            if (ok) {
+#pragma unroll
+                for (int t = 0; t < 4; ++t) {
                     const uint32_t off = pt_offset(r, cg * 4 + t);
-                    store_bf16x8(sPT + off, pf);
-                    store_bf16x8(sdST + off, df);
+                    *reinterpret_cast<uint4*>(sPT + off) = make_uint4(pp[t * 4], pp[t * 4 + 1], pp[t * 4 + 2], pp[t * 4 + 3]);
+                    *reinterpret_cast<uint4*>(sdST + off) = make_uint4(dd[t * 4], dd[t * 4 + 1], dd[t * 4 + 2], dd[t * 4 + 3]);
                 }
                 fence_proxy_async_smem();
                 tcgen05_fence_before_sync();
                 __syncwarp();
                 if (lane == 0) mbar_arrive(pds_ready);
-                const bool got_dq = mbar_wait(dq_full, it & 1, abort_flag);
-                ok = __all_sync(0xffffffffu, got_dq);
             }
-            if (ok) {
-                // dQ_i: TMEM -> two swizzled [128 x 32] fp32 boxes in shared memory -> one TMA reduction each adds them
-                // to the fp32 accumulators (rows beyond S are dropped by the tensor map)
-                tcgen05_fence_after_sync();
-                uint32_t v[16];
-                tmem_ld_32x32b_x16(lane_addr + 384 + cg * 16, v);
-                tmem_ld_wait();
-                uint8_t* box_row = sDQ + (st * 2 + (cg >> 1)) * DQ_BOX_BYTES + r * 128;
-#pragma unroll
-                for (int t = 0; t < 4; ++t)
-                    *reinterpret_cast<uint4*>(box_row + ((((cg & 1) * 4 + t) ^ (r & 7)) << 4)) =
-                        make_uint4(v[4 * t], v[4 * t + 1], v[4 * t + 2], v[4 * t + 3]);
-                fence_proxy_async_smem();
-                tcgen05_fence_before_sync();
-            }
-            compute_warps_sync<BWD_COMPUTE_WARPS * 32>();
-            if (ok && threadIdx.x == 0) {
-                tma_reduce_add_3d(&tmdQ, sDQ + (st * 2) * DQ_BOX_BYTES, 0, i * BT, bh);
-                tma_reduce_add_3d(&tmdQ, sDQ + (st * 2 + 1) * DQ_BOX_BYTES, 32, i * BT, bh);
-                tma_store_commit();
+            if (quarter < 2 && it + 1 < n_it) {
+                stat_mine[((it + 1) & 1) * 64 + quarter * 32 + lane] = stat_next;
+                if (it + 2 < n_it) stat_next = stat_src[(i + 2) * BT];
             }
         }
-        if (threadIdx.x == 0) tma_store_wait_all<0>();
+        if (ok && cg == ((n_it - 1) & 3)) stage_dq(n_it - 1);
         if (ok) {
             const bool got = mbar_wait(acc_done, (n_it - 1) & 1, abort_flag);
             ok = __all_sync(0xffffffffu, got);
@@ -697,16 +779,20 @@ struct StridedIn {
     long long sb, sh, ss;
 };
 
-// dsum[b, h, s] = sum_d dO * O (O = o + o_lo when the forward pass kept the low part). Eight threads per row, 8 elements each.
-__global__ void attn_dsum_kernel(StridedIn o, StridedIn o_lo, StridedIn d_o, float* dsum, int B, int H, int S) {
+// The per-query terms of the backward pass, padded to whole tiles so that the main kernel reads them without bounds
+// checks: lse2 = lse * log2(e) and dsc = scale * sum_d dO * O (O = o + o_lo when the forward pass kept the low part).
+// Eight threads per row, 8 elements each.
+__global__ void attn_stats_kernel(StridedIn o, StridedIn o_lo, StridedIn d_o, const float* lse, float* lse2, float* dsc, int B,
+                                  int H, int S, int s_pad, float scale) {
     const long long t = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x;
-    const long long rowi = t >> 3;
+    const long long rowi = t >> 3;   // row of the padded [B, H, s_pad] arrays
     const int part = static_cast<int>(t & 7);
-    const long long rows = static_cast<long long>(B) * H * S;
+    const long long rows = static_cast<long long>(B) * H * s_pad;
+    const int s = static_cast<int>(rowi % s_pad);
+    const long long bhh = rowi / s_pad;
+    const bool real = rowi < rows && s < S;
     float acc = 0.f;
-    if (rowi < rows) {
-        const int s = static_cast<int>(rowi % S);
-        const long long bhh = rowi / S;
+    if (real) {
         const int h = static_cast<int>(bhh % H);
         const long long b = bhh / H;
         const uint4 ov = *reinterpret_cast<const uint4*>(o.ptr + b * o.sb + h * o.sh + s * o.ss + part * 8);
@@ -733,7 +819,10 @@ __global__ void attn_dsum_kernel(StridedIn o, StridedIn o_lo, StridedIn d_o, flo
     acc += __shfl_xor_sync(0xffffffffu, acc, 1);
     acc += __shfl_xor_sync(0xffffffffu, acc, 2);
     acc += __shfl_xor_sync(0xffffffffu, acc, 4);
-    if (rowi < rows && part == 0) dsum[rowi] = acc;
+    if (rowi < rows && part == 0) {
+        lse2[rowi] = real ? lse[bhh * S + s] * LOG2E : INFINITY;
+        dsc[rowi] = real ? acc * scale : 0.f;
+    }
 }
 
 // fp32 dQ accumulators [B, H, S, 64] -> bf16 in the caller's layout. One thread per 8 elements.
@@ -901,9 +990,12 @@ int b200_attention_backward_hp(b200_ctx* ctx, const b200_attn_operand* q, const 
     cudaStream_t stream = ctx->pick(stream_v);
     const size_t rows = static_cast<size_t>(B) * H * S;
     const size_t acc_bytes = rows * DH * sizeof(float);
-    if ((rc = ensure_scratch(ctx, acc_bytes + rows * sizeof(float), stream)) != B200_OK) return rc;
+    const int64_t s_pad = (S + BT - 1) / BT * BT;
+    const size_t rows_pad = static_cast<size_t>(B) * H * s_pad;
+    if ((rc = ensure_scratch(ctx, acc_bytes + 2 * rows_pad * sizeof(float), stream)) != B200_OK) return rc;
     float* dq_acc = static_cast<float*>(ctx->d_scratch);
-    float* dsum = dq_acc + rows * DH;
+    float* lse2 = dq_acc + rows * DH;   // 16-byte aligned: rows * 64 floats before it, and s_pad is a multiple of 128
+    float* dsc = lse2 + rows_pad;
     CUtensorMap tmQ, tmK, tmV, tmdO;
     if ((rc = make_attn_map(ctx, &tmQ, *q, B, H, S, "q")) != B200_OK) return rc;
     if ((rc = make_attn_map(ctx, &tmK, *k, B, H, S, "k")) != B200_OK) return rc;
@@ -925,16 +1017,19 @@ int b200_attention_backward_hp(b200_ctx* ctx, const b200_attn_operand* q, const 
     }
     B200_CUDA_TRY(cudaMemsetAsync(dq_acc, 0, acc_bytes, stream));
     const unsigned blocks = static_cast<unsigned>((rows * 8 + 255) / 256);
-    attn_dsum_kernel<<<blocks, 256, 0, stream>>>(as_in(o), o_lo != nullptr ? as_in(o_lo) : StridedIn{nullptr, 0, 0, 0}, as_in(d_o), dsum, static_cast<int>(B), static_cast<int>(H),
-                                                 static_cast<int>(S));
+    const unsigned stat_blocks = static_cast<unsigned>((rows_pad * 8 + 255) / 256);
+    attn_stats_kernel<<<stat_blocks, 256, 0, stream>>>(as_in(o), o_lo != nullptr ? as_in(o_lo) : StridedIn{nullptr, 0, 0, 0}, as_in(d_o),
+                                                       lse, lse2, dsc, static_cast<int>(B), static_cast<int>(H), static_cast<int>(S),
+                                                       static_cast<int>(s_pad), scale);
     B200_CUDA_TRY(cudaGetLastError());
 
     BwdParams p;
     p.g = make_geom(B, H, S, scale, causal);
     p.dk = as_out(d_k);
     p.dv = as_out(d_v);
-    p.lse = lse;
-    p.dsum = dsum;
+    p.lse2 = lse2;
+    p.dsc = dsc;
+    p.s_pad = static_cast<int>(s_pad);
     p.dq_acc = dq_acc;
     p.status = ctx->d_status;
     static bool configured[64] = {};
