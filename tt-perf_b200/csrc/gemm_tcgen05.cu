@@ -615,7 +615,9 @@ GemmPlan gemm_plan(const b200_ctx* ctx, const b200_gemm_desc& d, bool allow_pair
             const long long rounds = (tiles * splits + pairs - 1) / pairs;
             const int kb_per = (num_kb + splits - 1) / splits;
             double cost = static_cast<double>(rounds) * (kb_per + 10) * 256 * 0.95;  // a pair's per-tile overhead is larger
-            if (splits > 1) cost += 1000.0 + 4000.0 * splits;
+            // long reductions (the weight-gradient products, K = tokens): measured 44-48 us for two slices against
+            // 51-52 us for the single-CTA kernel's one round of 128-column tiles at 2304 x 768 x 8192 and 3072 x 768 x 8192
+            if (splits > 1) cost += 1000.0 + (num_kb >= 64 ? 3000.0 : 4000.0) * splits;
             offer(GemmPlan{true, 256, splits}, cost);
         }
     }
