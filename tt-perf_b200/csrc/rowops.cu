@@ -839,11 +839,12 @@ __global__ void __launch_bounds__(kBlock, 3) layernorm_fw_vec_kernel(const __nv_
 
 // Backward in one pass (see layernorm_bw_fused_warp_kernel below for the arithmetic), persistent grid, one warp per row
 // at a time. The packed dy, x and upstream vectors of the NEXT row are requested before the current row is processed, so
-// every warp has loads in flight all the time. gamma sits in shared memory as fp32. The column sums for dgamma / dbeta
-// live in a private shared-memory slab per warp (plain vector loads and stores, no atomics: a lane only ever touches
-// its own columns); at the end the CTA adds the slabs and issues one global atomic per column.
+// every warp has loads in flight all the time. gamma sits in shared memory as fp32. A lane only ever touches its own
+// 8 * VPL columns, so the column sums for dgamma / dbeta (and of dx) stay in its registers over all rows of the warp; at
+// the end every warp writes them to a shared-memory slab of its own, the CTA adds the slabs and issues one global atomic
+// per column.
 template <int VPL>
-__global__ void __launch_bounds__(kBlock, 2) layernorm_bw_vec_kernel(
+__global__ void __launch_bounds__(kBlock, 1) layernorm_bw_vec_kernel(
     const __nv_bfloat16* dy, long long lddy, const __nv_bfloat16* x, long long ldx, const __nv_bfloat16* gamma,
     const float* mean, const float* rstd, const __nv_bfloat16* upstream, long long ldup, __nv_bfloat16* dx, long long lddx,
     float* dgamma_out, float* dbeta_out, __nv_bfloat16* dx_colsum_out, int rows, int cols, float* stage, unsigned* ticket) {
@@ -857,8 +858,12 @@ __global__ void __launch_bounds__(kBlock, 2) layernorm_bw_vec_kernel(
     const int lane = threadIdx.x & 31;
     const int warp = threadIdx.x >> 5;
     for (int c = threadIdx.x; c < W; c += kBlock) sgam[c] = c < cols ? __bfloat162float(gamma[c]) : 0.0f;
-    for (int c = threadIdx.x; c < 3 * WARPS * W; c += kBlock) sag[c] = 0.0f;
     __syncthreads();
+    float ag[VPL][8], ab[VPL][8], ax[VPL][8];
+#pragma unroll
+    for (int j = 0; j < VPL; ++j)
+#pragma unroll
+        for (int i = 0; i < 8; ++i) ag[j][i] = ab[j][i] = ax[j][i] = 0.0f;
     float* my_ag = sag + warp * W;
     float* my_ab = sab + warp * W;
     float* my_ax = sax + warp * W;
@@ -904,29 +909,16 @@ __global__ void __launch_bounds__(kBlock, 2) layernorm_bw_vec_kernel(
             const float4 g0 = *reinterpret_cast<const float4*>(sgam + c);
             const float4 g1 = *reinterpret_cast<const float4*>(sgam + c + 4);
             const float gm[8] = {g0.x, g0.y, g0.z, g0.w, g1.x, g1.y, g1.z, g1.w};
-            float pg[8], pb[8];
-            if (params) {
-                const float4 a0 = *reinterpret_cast<const float4*>(my_ag + c), a1 = *reinterpret_cast<const float4*>(my_ag + c + 4);
-                const float4 b0 = *reinterpret_cast<const float4*>(my_ab + c), b1 = *reinterpret_cast<const float4*>(my_ab + c + 4);
-                pg[0] = a0.x; pg[1] = a0.y; pg[2] = a0.z; pg[3] = a0.w; pg[4] = a1.x; pg[5] = a1.y; pg[6] = a1.z; pg[7] = a1.w;
-                pb[0] = b0.x; pb[1] = b0.y; pb[2] = b0.z; pb[3] = b0.w; pb[4] = b1.x; pb[5] = b1.y; pb[6] = b1.z; pb[7] = b1.w;
-            }
 #pragma unroll
             for (int i = 0; i < 8; ++i) {
                 const float xhat = (xh[i] - cmu) * crs;
                 if (params) {
-                    pb[i] += d[i];
-                    pg[i] = fmaf(d[i], xhat, pg[i]);
+                    ab[j][i] += d[i];
+                    ag[j][i] = fmaf(d[i], xhat, ag[j][i]);
                 }
                 const float gg = d[i] * gm[i];
                 s1 += gg;
                 s2 = fmaf(gg, xhat, s2);
-            }
-            if (params) {
-                *reinterpret_cast<float4*>(my_ag + c) = make_float4(pg[0], pg[1], pg[2], pg[3]);
-                *reinterpret_cast<float4*>(my_ag + c + 4) = make_float4(pg[4], pg[5], pg[6], pg[7]);
-                *reinterpret_cast<float4*>(my_ab + c) = make_float4(pb[0], pb[1], pb[2], pb[3]);
-                *reinterpret_cast<float4*>(my_ab + c + 4) = make_float4(pb[4], pb[5], pb[6], pb[7]);
             }
         }
         s1 = warp_sum(s1) / cols;
@@ -955,34 +947,45 @@ __global__ void __launch_bounds__(kBlock, 2) layernorm_bw_vec_kernel(
                 if (colsum) {  // sums of the rounded values, as a column reduction of the stored tensor would see them
                     float q[8];
                     unpack_bf16x8(packed, q);
-                    float4 a0 = *reinterpret_cast<const float4*>(my_ax + c), a1 = *reinterpret_cast<const float4*>(my_ax + c + 4);
-                    a0.x += q[0]; a0.y += q[1]; a0.z += q[2]; a0.w += q[3];
-                    a1.x += q[4]; a1.y += q[5]; a1.z += q[6]; a1.w += q[7];
-                    *reinterpret_cast<float4*>(my_ax + c) = a0;
-                    *reinterpret_cast<float4*>(my_ax + c + 4) = a1;
+#pragma unroll
+                    for (int i = 0; i < 8; ++i) ax[j][i] += q[i];
                 }
             }
         }
     }
     if (!params && !colsum) return;
+#pragma unroll
+    for (int j = 0; j < VPL; ++j) {
+        const int c = (j * kWarp + lane) * 8;
+        *reinterpret_cast<float4*>(my_ag + c) = make_float4(ag[j][0], ag[j][1], ag[j][2], ag[j][3]);
+        *reinterpret_cast<float4*>(my_ag + c + 4) = make_float4(ag[j][4], ag[j][5], ag[j][6], ag[j][7]);
+        *reinterpret_cast<float4*>(my_ab + c) = make_float4(ab[j][0], ab[j][1], ab[j][2], ab[j][3]);
+        *reinterpret_cast<float4*>(my_ab + c + 4) = make_float4(ab[j][4], ab[j][5], ab[j][6], ab[j][7]);
+        *reinterpret_cast<float4*>(my_ax + c) = make_float4(ax[j][0], ax[j][1], ax[j][2], ax[j][3]);
+        *reinterpret_cast<float4*>(my_ax + c + 4) = make_float4(ax[j][4], ax[j][5], ax[j][6], ax[j][7]);
+    }
     // CTA sums -> one of kLnCopies zero-initialised staging replicas (few CTAs collide on an address) -> the CTA that
     // arrives last adds the replicas, writes the outputs and leaves replicas and ticket at zero for the next launch.
     __shared__ int is_last;
     __syncthreads();
     float* mine = stage + (blockIdx.x % kLnCopies) * kLnRows * kLnMaxCols;
-    for (int c = threadIdx.x; c < cols; c += kBlock) {
-        float g = 0.0f, b = 0.0f, x = 0.0f;
+    // four columns per thread and one 16-byte reduction per row of the replica (cols is a multiple of 8 on this path)
+    for (int c = threadIdx.x * 4; c < cols; c += kBlock * 4) {
+        float4 g = make_float4(0.f, 0.f, 0.f, 0.f), b = g, x = g;
 #pragma unroll
         for (int w = 0; w < WARPS; ++w) {
-            g += sag[w * W + c];
-            b += sab[w * W + c];
-            x += sax[w * W + c];
+            const float4 gw = *reinterpret_cast<const float4*>(sag + w * W + c);
+            const float4 bw = *reinterpret_cast<const float4*>(sab + w * W + c);
+            const float4 xw = *reinterpret_cast<const float4*>(sax + w * W + c);
+            g.x += gw.x; g.y += gw.y; g.z += gw.z; g.w += gw.w;
+            b.x += bw.x; b.y += bw.y; b.z += bw.z; b.w += bw.w;
+            x.x += xw.x; x.y += xw.y; x.z += xw.z; x.w += xw.w;
         }
         if (params) {
-            atomicAdd(&mine[c], g);
-            atomicAdd(&mine[kLnMaxCols + c], b);
+            atomicAdd(reinterpret_cast<float4*>(mine + c), g);
+            atomicAdd(reinterpret_cast<float4*>(mine + kLnMaxCols + c), b);
         }
-        if (colsum) atomicAdd(&mine[2 * kLnMaxCols + c], x);
+        if (colsum) atomicAdd(reinterpret_cast<float4*>(mine + 2 * kLnMaxCols + c), x);
     }
     __threadfence();
     __syncthreads();
@@ -1427,7 +1430,7 @@ static int layernorm_backward_impl(const char* fn, b200_ctx* ctx, const void* dy
         const auto* gp = static_cast<const __nv_bfloat16*>(gamma);
         const int vdy = vec_ok(dy, lddy), vx = vec_ok(x, ldx), vdx = dx ? vec_ok(dx, lddx) : 0, vg = gamma ? vec_ok(gamma, 8) : 0;
         const int vup = upstream ? vec_ok(upstream, ldup) : 0;
-        const int blocks = std::max(1, std::min((r + 7) / 8, ctx->sm_count * 2));
+        const int blocks = std::max(1, std::min((r + 7) / 8, ctx->sm_count * (vec_path ? 1 : 2)));
         {   // the staging rows and the ticket are one set per context: keep users on different streams apart
             int rc_o = order_shared_state(ctx, s);
             if (rc_o != B200_OK) return rc_o;
