@@ -6,19 +6,21 @@
 //
 // Tiles are 128 queries x 128 keys. A TMEM lane is one row of the accumulator; a warp reads the 32 lanes of its
 // quarter (warp index mod 4), and several warps share a quarter by taking different columns. Both kernels are bound by
-// the latency of their dependent steps (MMA -> exp -> MMA), so they run many compute warps per SM.
+// their element-wise warps (exponentials, conversions, the latency of TMEM loads), not by the tensor pipe or by DRAM.
 //
 //   forward, one CTA per (batch, head, 128 queries), two CTAs per SM:
-//     thread 0     between the barriers: TMA loads of Q once and K, V double buffered; S = Q K^T; O_j = P V
-//     8 warps      a thread takes one row and one 64-column half of S: local maximum -> exchanged with the other half
-//                  through shared memory -> P = exp2(..) as bf16 into shared memory (the 128-byte-swizzled K-major
-//                  layout the next MMA reads). It also keeps 32 columns of O in registers; O_j is folded in one tile
-//                  late, when the next S is ready, so the wait for the P V product is off the critical path.
+//     warp 0       TMA: Q once, the K tiles and the V tiles through two rings of two stages
+//     warp 1       one thread issues every MMA: S_j = Q K_j^T and O_j = P_j V_j
+//     warps 2-5    a thread owns one query row and all 128 keys of a key tile: exact row maximum, P = exp2(..) as bf16
+//                  into shared memory (the 128-byte-swizzled K-major layout the P V product reads), running sum; the
+//                  row's 64 output values live in registers and O_j is folded into them one tile late.
 //   backward, one CTA per (batch, head, 128 keys), looping over the query tiles that see those keys:
-//     issue warp   S^T = K Q^T, dP^T = V dO^T, then dV += P^T dO, dK += dS^T Q, dQ_i = dS K
+//     warp 16      TMA and every MMA: S^T = K Q^T and dP^T = V dO^T of the NEXT query tile while the current one is
+//                  evaluated; then dQ_i = dS K, dV += P^T dO, dK += dS^T Q
 //     16 warps     a thread takes one row (key) and 32 columns (queries): P^T = exp(scale S^T - lse),
-//                  dS^T = scale P^T (dP^T - rowsum(dO O)) into shared memory as bf16; then 16 columns of dQ_i from TMEM
-//                  into fp32 accumulators with vector atomic adds; dK, dV at the end.
+//                  dS^T = scale P^T (dP^T - rowsum(dO O)) into shared memory as bf16; the four warps of one column
+//                  group (a different group every tile) move dQ_i from TMEM into fp32 staging boxes; dK, dV at the end
+//     warp 17      one thread adds the staged dQ_i boxes to the fp32 accumulators with TMA reductions
 //   The single [128 keys x 128 queries] dS^T tile in shared memory is read both as a K-major A operand (dK) and as an
 //   MN-major A operand (dQ): the two readings share one physical layout.
 //
@@ -107,74 +109,65 @@ struct FwdParams {
     int* status;
 };
 
-// One CTA per (batch, head, PAIR of 128-query tiles), one CTA per SM, roles by warp:
-//     warp 0       TMA: Q of both tiles once, then the K tiles and the V tiles through two rings of two stages each
-//     warp 1       one thread issues every MMA: S_t = Q_t K^T and O_t,j = P_t,j V_j for the two tiles t = 0, 1
-//     warps 2-5    softmax of tile 0: a thread owns one query row and all 128 keys of the tile — no exchange with other
-//     warps 6-9    softmax of tile 1  threads, no CTA-wide barrier. Per key tile: row maximum (exact, fp32), P = exp2(.)
-//                  as bf16 into shared memory, running sum; the row's 64 output values live in registers and O_t,j is
-//                  folded into them one tile late.
-// Nothing the softmax threads wait for depends on their own last step: when P_t,j is ready the MMA thread first issues
-// S_t,j+1 (which needs only K_j+1 and the S_t columns, free by then) and publishes it, and only then O_t,j = P_t,j V_j.
-// So P_t and O_t are double-buffered: P_t,j+1 is written while O_t,j still reads P_t,j, and O_t,j is folded (after
-// P_t,j+1 has been handed over, while the tensor core computes S_t,j+2) from the TMEM columns that O_t,j+2 will reuse.
-// TMEM: S_0, S_1 (2 x 128 columns), O_t,b (4 x 64). The exponentials are the slowest unit (16 per clock and SM): while the
-// threads of one tile evaluate theirs, those of the other take maxima, fold or wait.
-constexpr int FWD_THREADS = 320;
 constexpr int FWD_STAGES = 2;
-constexpr int FWD_TMEM_COLS = 512;
-constexpr int FWD_SMEM_USED = 2 * TILE_BYTES + 2 * FWD_STAGES * TILE_BYTES + 4 * PT_BYTES + 256;
-constexpr int FWD_SMEM = FWD_SMEM_USED + 1024;   // room to round the base up to 1024
-static_assert(FWD_SMEM <= 227 * 1024, "forward shared memory exceeds the per-CTA limit");
 
-__global__ void __launch_bounds__(FWD_THREADS, 1)
+// One CTA per (batch, head, 128-query tile), two CTAs per SM: the set-up, the first loads and the output epilogue of one
+// CTA run under the key-tile loop of its neighbour. Roles by warp: warp 0 TMA (Q once, K tiles and V tiles through two
+// rings of two stages), warp 1 one MMA-issuing thread, warps 2-5 softmax — a thread owns one query row and all 128 keys of
+// a key tile. P is single-buffered (it is rewritten only after O_j-1 = P_j-1 V_j-1 has read it, which the softmax
+// threads wait for anyway before they fold O_j-1), O is double-buffered in TMEM (S 128 columns, O_b 2 x 64).
+constexpr int FWD_THREADS = 192;
+constexpr int FWD_TMEM_COLS = 256;
+constexpr int FWD_SMEM_USED = TILE_BYTES + 2 * FWD_STAGES * TILE_BYTES + PT_BYTES + 128;
+// Two CTAs per SM have 2 * (FWD_SMEM + 1 KB the hardware reserves per CTA) <= 228 KB to share, which leaves no room for
+// rounding the base up to 1024: the kernel relies on the base being 1024-aligned already (it is when the kernel has no
+// static shared memory) and reports an error instead of running when it is not.
+constexpr int FWD_SMEM = FWD_SMEM_USED;
+static_assert(2 * (FWD_SMEM + 1024) <= 228 * 1024, "two forward CTAs must fit one SM");
+
+__global__ void __launch_bounds__(FWD_THREADS, 2)
 attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
-                const __grid_constant__ CUtensorMap tmV, const FwdParams p) {
+                 const __grid_constant__ CUtensorMap tmV, const FwdParams p) {
     extern __shared__ uint8_t smem_raw[];
-    uint8_t* smem = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
-    uint8_t* sQ = smem;                                   // 2 tiles
-    uint8_t* sK = sQ + 2 * TILE_BYTES;                    // FWD_STAGES tiles
+    if ((smem_u32(smem_raw) & 1023u) != 0) {  // uniform over the CTA; nothing has been set up yet
+        if (threadIdx.x == 0) atomicExch(p.status, 1);
+        return;
+    }
+    uint8_t* sQ = smem_raw;
+    uint8_t* sK = sQ + TILE_BYTES;                        // FWD_STAGES tiles
     uint8_t* sV = sK + FWD_STAGES * TILE_BYTES;           // FWD_STAGES tiles
-    uint8_t* sP = sV + FWD_STAGES * TILE_BYTES;           // [tile t][buffer] of [128 x 128] bf16
-    uint64_t* q_full = reinterpret_cast<uint64_t*>(sP + 4 * PT_BYTES);  // 2
-    uint64_t* k_full = q_full + 2;                        // FWD_STAGES
-    uint64_t* k_empty = k_full + FWD_STAGES;              // FWD_STAGES: every S product that reads the stage has run
+    uint8_t* sP = sV + FWD_STAGES * TILE_BYTES;           // [128 x 128] bf16
+    uint64_t* q_full = reinterpret_cast<uint64_t*>(sP + PT_BYTES);
+    uint64_t* k_full = q_full + 1;                        // FWD_STAGES
+    uint64_t* k_empty = k_full + FWD_STAGES;              // FWD_STAGES
     uint64_t* v_full = k_empty + FWD_STAGES;              // FWD_STAGES
-    uint64_t* v_empty = v_full + FWD_STAGES;              // FWD_STAGES: every P V product that reads the stage has run
-    uint64_t* s_full = v_empty + FWD_STAGES;              // 2: S_t of a key tile is in TMEM
-    uint64_t* p_ready = s_full + 2;                       // 2: P_t is in shared memory and S_t has been read (4 arrivals)
-    uint64_t* pv_full = p_ready + 2;                      // 2: O_t,j is in TMEM and P_t,j has been read
-    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(pv_full + 2);
+    uint64_t* v_empty = v_full + FWD_STAGES;              // FWD_STAGES
+    uint64_t* s_full = v_empty + FWD_STAGES;              // S of a key tile is in TMEM
+    uint64_t* p_ready = s_full + 1;                       // P is in shared memory and S has been read (4 arrivals)
+    uint64_t* pv_full = p_ready + 1;                      // O_j is in TMEM and P_j has been read
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(pv_full + 1);
     volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
     const int warp = threadIdx.x >> 5;
     const int lane = threadIdx.x & 31;
     const Geom g = p.g;
-    // The grid is [batch x head, tile pair] with the first index running fastest: every pair with the most key tiles
-    // is handed out before any lighter one, so the last CTAs to start are the short ones.
+    // The grid is [batch x head, query tile] with the first index running fastest and the tile index reversed: every
+    // tile with the most key tiles is handed out before any lighter one.
     const int bh = blockIdx.x;
     const int b = bh / g.H;
     const int h = bh - b * g.H;
     const int n_q_all = (g.S + BT - 1) / BT;
-    const int n_kv_all = n_q_all;
-    const int pair = static_cast<int>(gridDim.y) - 1 - static_cast<int>(blockIdx.y);
-    int qt[2], n_kv[2];
-    for (int t = 0; t < 2; ++t) {
-        qt[t] = 2 * pair + t;
-        n_kv[t] = qt[t] >= n_q_all ? 0 : (g.causal ? min(qt[t] + 1, n_kv_all) : n_kv_all);
-    }
-    const int n_max = max(n_kv[0], n_kv[1]);
+    const int qt = static_cast<int>(gridDim.y) - 1 - static_cast<int>(blockIdx.y);
+    const int n_kv = g.causal ? min(qt + 1, n_q_all) : n_q_all;
 
     if (threadIdx.x == 0) {
         prefetch_tensormap(&tmQ);
         prefetch_tensormap(&tmK);
         prefetch_tensormap(&tmV);
-        for (int t = 0; t < 2; ++t) {
-            mbar_init(&q_full[t], 1);
-            mbar_init(&s_full[t], 1);
-            mbar_init(&p_ready[t], 4);
-            mbar_init(&pv_full[t], 1);
-        }
+        mbar_init(q_full, 1);
+        mbar_init(s_full, 1);
+        mbar_init(p_ready, 4);
+        mbar_init(pv_full, 1);
         for (int st = 0; st < FWD_STAGES; ++st) {
             mbar_init(&k_full[st], 1);
             mbar_init(&k_empty[st], 1);
@@ -194,16 +187,11 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
     const uint32_t tmem_base = *tmem_slot;
 
     if (warp == 0) {
-        // ---------------------------------------------------------------------------------- TMA producer
         if (lane == 0) {
-            int armed_q = 0, armed_k = 0, armed_v = 0;
-            for (int t = 0; t < 2; ++t) {
-                if (n_kv[t] == 0) continue;
-                mbar_arrive_expect_tx(&q_full[t], TILE_BYTES);
-                tma_load_4d(sQ + t * TILE_BYTES, &tmQ, &q_full[t], 0, qt[t] * BT, h, b);
-                armed_q |= 1 << t;
-            }
-            for (int j = 0; j < n_max; ++j) {
+            int armed_k = 0, armed_v = 0;
+            mbar_arrive_expect_tx(q_full, TILE_BYTES);
+            tma_load_4d(sQ, &tmQ, q_full, 0, qt * BT, h, b);
+            for (int j = 0; j < n_kv; ++j) {
                 const int st = j % FWD_STAGES;
                 const uint32_t reuse_parity = ((j / FWD_STAGES) - 1) & 1;
                 if (j >= FWD_STAGES && !mbar_wait(&k_empty[st], reuse_parity, abort_flag)) break;
@@ -216,81 +204,65 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
                 armed_v = j + 1;
             }
             if (*abort_flag != 0) {  // let armed copies land before the shared memory is released
-                for (int t = 0; t < 2; ++t)
-                    if (armed_q & (1 << t)) drain(&q_full[t], 0);
+                drain(q_full, 0);
                 for (int j = max(0, armed_k - FWD_STAGES); j < armed_k; ++j) drain(&k_full[j % FWD_STAGES], (j / FWD_STAGES) & 1);
                 for (int j = max(0, armed_v - FWD_STAGES); j < armed_v; ++j) drain(&v_full[j % FWD_STAGES], (j / FWD_STAGES) & 1);
             }
         }
     } else if (warp == 1) {
-        // ---------------------------------------------------------------------------------- MMA issuer
         if (lane == 0) {
             constexpr uint32_t idesc_s = make_idesc_bf16_f32(BT, BT, 0u, 0u);   // Q (K-major) x K (K-major)
             constexpr uint32_t idesc_o = make_idesc_bf16_f32(BT, DH, 0u, 1u);   // P (K-major) x V (MN-major)
-            auto issue_s = [&](int t, int j) {
-                const uint32_t a = smem_u32(sQ + t * TILE_BYTES);
-                const uint32_t bb = smem_u32(sK + (j % FWD_STAGES) * TILE_BYTES);
+            static_assert(FWD_STAGES == 2, "the stage of key tile j is j & 1 below");
+            const uint64_t d_q = make_smem_desc_sw128(smem_u32(sQ), 0, 1024);
+            const uint64_t d_k[2] = {make_smem_desc_sw128(smem_u32(sK), 0, 1024), make_smem_desc_sw128(smem_u32(sK + TILE_BYTES), 0, 1024)};
+            const uint64_t d_v[2] = {make_smem_desc_sw128(smem_u32(sV), BT * 128, 1024),
+                                     make_smem_desc_sw128(smem_u32(sV + TILE_BYTES), BT * 128, 1024)};
+            const uint64_t d_p = make_smem_desc_sw128(smem_u32(sP), 0, 1024);
+            auto issue_s = [&](int j) {
+                const uint64_t bb = (j & 1) ? d_k[1] : d_k[0];
 #pragma unroll
-                for (int k = 0; k < DH / UMMA_K; ++k)
-                    umma_f16_ss(tmem_base + t * BT, make_smem_desc_sw128(a + k * 32, 0, 1024),
-                                make_smem_desc_sw128(bb + k * 32, 0, 1024), idesc_s, k > 0 ? 1u : 0u);
-                umma_commit(&s_full[t]);
+                for (int k = 0; k < DH / UMMA_K; ++k) umma_f16_ss(tmem_base, d_q + 2 * k, bb + 2 * k, idesc_s, k > 0 ? 1u : 0u);
+                umma_commit(s_full);
+                umma_commit(&k_empty[j & 1]);
             };
-            auto issue_pv = [&](int t, int j) {
-                const uint32_t pa = smem_u32(sP + (t * 2 + (j & 1)) * PT_BYTES);
-                const uint32_t vb = smem_u32(sV + (j % FWD_STAGES) * TILE_BYTES);
+            auto issue_pv = [&](int j) {
+                const uint64_t vb = (j & 1) ? d_v[1] : d_v[0];
+                const uint32_t dst = tmem_base + BT + (j & 1) * DH;
 #pragma unroll
                 for (int k = 0; k < BT / UMMA_K; ++k)
-                    umma_f16_ss(tmem_base + 2 * BT + (t * 2 + (j & 1)) * DH,
-                                make_smem_desc_sw128(pa + (k >> 2) * TILE_BYTES + (k & 3) * 32, 0, 1024),
-                                make_smem_desc_sw128(vb + k * (UMMA_K * 128), BT * 128, 1024), idesc_o, k > 0 ? 1u : 0u);
-                umma_commit(&pv_full[t]);
+                    umma_f16_ss(dst, d_p + ((k >> 2) * (TILE_BYTES / 16) + (k & 3) * 2), vb + k * (UMMA_K * 128 / 16), idesc_o,
+                                k > 0 ? 1u : 0u);
+                umma_commit(pv_full);
+                umma_commit(&v_empty[j & 1]);
             };
-            bool ok = true;
-            int k_seen = 0, v_seen = 0;  // key tiles whose K / V are known to have landed
-            auto need = [&](uint64_t* full, int& seen, int j) {
-                while (ok && seen <= j) {
-                    ok = mbar_wait(&full[seen % FWD_STAGES], (seen / FWD_STAGES) & 1, abort_flag);
-                    ++seen;
-                }
-                if (ok) tcgen05_fence_after_sync();
-            };
-            for (int t = 0; ok && t < 2; ++t)
-                if (n_kv[t] > 0) ok = mbar_wait(&q_full[t], 0, abort_flag);
-            if (ok && n_max > 0) need(k_full, k_seen, 0);
-            for (int t = 0; ok && t < 2; ++t)
-                if (n_kv[t] > 0) issue_s(t, 0);
-            if (ok && n_max > 0) umma_commit(&k_empty[0]);
-            for (int j = 0; ok && j < n_max; ++j) {
-                for (int t = 0; ok && t < 2; ++t) {
-                    if (j >= n_kv[t]) continue;
-                    ok = mbar_wait(&p_ready[t], j & 1, abort_flag);
+            bool ok = mbar_wait(q_full, 0, abort_flag) && mbar_wait(&k_full[0], 0, abort_flag);
+            if (ok) {
+                tcgen05_fence_after_sync();
+                issue_s(0);
+            }
+            for (int j = 0; ok && j < n_kv; ++j) {
+                ok = mbar_wait(p_ready, j & 1, abort_flag);
+                if (!ok) break;
+                if (j + 1 < n_kv) {
+                    ok = mbar_wait(&k_full[(j + 1) & 1], ((j + 1) >> 1) & 1, abort_flag);
                     if (!ok) break;
                     tcgen05_fence_after_sync();
-                    if (j + 1 < n_kv[t]) {
-                        need(k_full, k_seen, j + 1);
-                        if (!ok) break;
-                        issue_s(t, j + 1);
-                    }
-                    need(v_full, v_seen, j);
-                    if (!ok) break;
-                    issue_pv(t, j);
+                    issue_s(j + 1);
                 }
-                if (ok) {   // every product that reads K_j+1 and V_j has been issued
-                    if (j + 1 < n_max) umma_commit(&k_empty[(j + 1) % FWD_STAGES]);
-                    umma_commit(&v_empty[j % FWD_STAGES]);
-                }
+                ok = mbar_wait(&v_full[j & 1], (j >> 1) & 1, abort_flag);
+                if (!ok) break;
+                tcgen05_fence_after_sync();
+                issue_pv(j);
             }
         }
     } else {
-        // ---------------------------------------------------------------------------------- softmax of tile t
-        const int t = (warp - 2) >> 2;
         const int quarter = warp & 3;          // the TMEM lane quarter a warp may read
         const int r = quarter * 32 + lane;     // row of the tile = TMEM lane
-        const int row = qt[t] * BT + r;
+        const int row = qt * BT + r;
         const uint32_t lane_addr = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16);
-        const uint32_t s_addr = lane_addr + static_cast<uint32_t>(t * BT);
-        const uint32_t o_addr = lane_addr + static_cast<uint32_t>(2 * BT + t * 2 * DH);
+        const uint32_t s_addr = lane_addr;
+        const uint32_t o_addr = lane_addr + static_cast<uint32_t>(BT);
         const int limit = g.causal ? min(row, g.S - 1) : g.S - 1;  // last visible key of this row
         const float sl2 = g.scale_log2;
         float m = -INFINITY, l = 0.f, alpha = 0.f;
@@ -298,7 +270,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
 #pragma unroll
         for (int i = 0; i < DH; ++i) o[i] = 0.f;
         uint32_t va[32], vb[32];   // two TMEM reads in flight
-        auto fold_pv = [&](int j, float a) {  // O = O * a + O_t,j
+        auto fold_pv = [&](int j, float a) {  // O = O * a + O_j
             tmem_ld_32x32b_x32(o_addr + (j & 1) * DH, va);
             tmem_ld_32x32b_x32(o_addr + (j & 1) * DH + 32, vb);
             tmem_ld_wait();
@@ -308,17 +280,13 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
             for (int i = 0; i < 32; ++i) o[32 + i] = fmaf(o[32 + i], a, __uint_as_float(vb[i]));
         };
         bool ok = true;   // uniform over the warp
-        const int n_mine = n_kv[t];
-        for (int j = 0; ok && j < n_mine; ++j) {
-            const bool got = mbar_wait(&s_full[t], j & 1, abort_flag);
+        for (int j = 0; ok && j < n_kv; ++j) {
+            const bool got = mbar_wait(s_full, j & 1, abort_flag);
             ok = __all_sync(0xffffffffu, got);
             if (!ok) break;
             tcgen05_fence_after_sync();
             const int lim = limit - j * BT;      // index, within the tile, of the last visible key
             const bool masked = lim < BT - 1;
-            uint8_t* myP = sP + (t * 2 + (j & 1)) * PT_BYTES;
-            // pass 1: the row maximum over the visible keys; the chunks are read in the order 0, 1, 2, 3 and the last
-            // two stay in registers for pass 2
             float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
             auto take_max = [&](const uint32_t* sv, int c) {
                 if (!masked) {
@@ -340,13 +308,18 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
             tmem_ld_wait();
             take_max(va, 2);
             take_max(vb, 3);
-            // finite: every tile shows each row at least one key
             const float mx = fmaxf(m, fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3])));
-            const float alpha_before = alpha;   // belongs to O_t,j-1, folded below
+            const float alpha_before = alpha;   // belongs to O_j-1, folded below
             alpha = ex2((m - mx) * sl2);        // 0 on the first tile (m = -inf)
             const float mb = mx * sl2;
             m = mx;
-            // pass 2: probabilities as bf16 into the layout the P V product reads, and their sum
+            if (j > 0) {
+                // O_j-1 has read P_j-1 (the buffer about to be rewritten) and is in TMEM. Waiting here also keeps every
+                // barrier at most one phase ahead of its waiter: O_j cannot be issued before P_j is handed over.
+                const bool got_o = mbar_wait(pv_full, (j - 1) & 1, abort_flag);
+                ok = __all_sync(0xffffffffu, got_o);
+                if (!ok) break;
+            }
             float rs4[4] = {0.f, 0.f, 0.f, 0.f};
             auto take_exp = [&](const uint32_t* sv, int c) {
 #pragma unroll
@@ -360,7 +333,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
                         rs4[e & 3] += pr;
                         f[e] = pr;
                     }
-                    store_bf16x8(myP + pt_offset(r, c * 4 + u), f);
+                    store_bf16x8(sP + pt_offset(r, c * 4 + u), f);
                 }
             };
             take_exp(va, 2);
@@ -374,22 +347,19 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
             fence_proxy_async_smem();
             tcgen05_fence_before_sync();
             __syncwarp();
-            if (lane == 0) mbar_arrive(&p_ready[t]);
-            if (j > 0) {   // while the tensor core computes S_t,j+1
-                const bool got_o = mbar_wait(&pv_full[t], (j - 1) & 1, abort_flag);
-                ok = __all_sync(0xffffffffu, got_o);
-                if (!ok) break;
+            if (lane == 0) mbar_arrive(p_ready);
+            if (j > 0) {
                 tcgen05_fence_after_sync();
                 fold_pv(j - 1, alpha_before);
             }
         }
-        if (ok && n_mine > 0) {
-            const bool got = mbar_wait(&pv_full[t], (n_mine - 1) & 1, abort_flag);
+        if (ok && n_kv > 0) {
+            const bool got = mbar_wait(pv_full, (n_kv - 1) & 1, abort_flag);
             ok = __all_sync(0xffffffffu, got);
         }
-        if (ok && n_mine > 0) {
+        if (ok && n_kv > 0) {
             tcgen05_fence_after_sync();
-            fold_pv(n_mine - 1, alpha);
+            fold_pv(n_kv - 1, alpha);
             if (row < g.S) {
                 const float inv = 1.f / l;
 #pragma unroll
@@ -956,7 +926,7 @@ int b200_attention_forward_hp(b200_ctx* ctx, const b200_attn_operand* q, const b
     static bool configured[64] = {};
     if ((rc = configure_once(attn_fwd_kernel, FWD_SMEM, configured)) != B200_OK) return rc;
     const int64_t q_tiles = (S + BT - 1) / BT;
-    const dim3 grid(static_cast<unsigned>(B * H), static_cast<unsigned>((q_tiles + 1) / 2));
+    const dim3 grid(static_cast<unsigned>(B * H), static_cast<unsigned>(q_tiles));
     attn_fwd_kernel<<<grid, FWD_THREADS, FWD_SMEM, stream>>>(tmQ, tmK, tmV, p);
     B200_CUDA_TRY(cudaGetLastError());
     return B200_OK;
