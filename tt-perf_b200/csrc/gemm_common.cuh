@@ -107,6 +107,34 @@ __device__ __forceinline__ void epi_apply32(const EpiParams& e, const uint32_t (
     }
 }
 
+// v <- the sum of the K slices of 32 accumulator columns in slice order, whichever slice the caller holds: slice `own`
+// is v itself (still in registers), the others come from memory through `src_of(slice)` (8 float4, 128 apart). The fixed
+// order makes the result independent of which slice happened to finish last.
+template <class SrcOf>
+__device__ __forceinline__ void sum_slices_in_order(uint32_t (&v)[32], int own, int k_splits, SrcOf src_of) {
+    float acc[32];
+    bool started = false;
+    for (int sl = 0; sl < k_splits; ++sl) {
+        if (sl == own) {
+#pragma unroll
+            for (int i = 0; i < 32; ++i) acc[i] = started ? acc[i] + __uint_as_float(v[i]) : __uint_as_float(v[i]);
+        } else {
+            const float4* src = src_of(sl);
+#pragma unroll
+            for (int i = 0; i < 8; ++i) {
+                const float4 a = __ldcg(src + i * 128);
+                acc[4 * i] = started ? acc[4 * i] + a.x : a.x;
+                acc[4 * i + 1] = started ? acc[4 * i + 1] + a.y : a.y;
+                acc[4 * i + 2] = started ? acc[4 * i + 2] + a.z : a.z;
+                acc[4 * i + 3] = started ? acc[4 * i + 3] + a.w : a.w;
+            }
+        }
+        started = true;
+    }
+#pragma unroll
+    for (int i = 0; i < 32; ++i) v[i] = __float_as_uint(acc[i]);
+}
+
 __device__ __forceinline__ uint32_t pack_bf16x2(float lo, float hi) {
     __nv_bfloat162 h = __floats2bfloat162_rn(lo, hi);
     return *reinterpret_cast<uint32_t*>(&h);

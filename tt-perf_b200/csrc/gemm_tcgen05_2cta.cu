@@ -338,20 +338,9 @@ gemm_tcgen05_2cta_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_c
                             for (int i = 0; i < 32; ++i)
                                 v[i] = __float_as_uint(__bfloat162float(__float2bfloat16_rn(__uint_as_float(v[i]))));
                         }
-                        if (p.k_splits > 1) {
-                            for (int sl = 0; sl < p.k_splits; ++sl) {
-                                if (sl == it.split) continue;
-                                const float4* src = part_at(sl) + ((c + h * 32) / 32) * 8 * 128;
-#pragma unroll
-                                for (int i = 0; i < 8; ++i) {
-                                    const float4 a = __ldcg(src + i * 128);
-                                    v[4 * i] = __float_as_uint(__uint_as_float(v[4 * i]) + a.x);
-                                    v[4 * i + 1] = __float_as_uint(__uint_as_float(v[4 * i + 1]) + a.y);
-                                    v[4 * i + 2] = __float_as_uint(__uint_as_float(v[4 * i + 2]) + a.z);
-                                    v[4 * i + 3] = __float_as_uint(__uint_as_float(v[4 * i + 3]) + a.w);
-                                }
-                            }
-                        }
+                        if (p.k_splits > 1)
+                            sum_slices_in_order(v, it.split, p.k_splits,
+                                                [&](int sl) { return part_at(sl) + ((c + h * 32) / 32) * 8 * 128; });
                         float f[32];
                         epi_apply32(p.epi, v, f, row, nh, p.N);
                         if (p.c_f32) {
