@@ -399,6 +399,17 @@ int b200_peer_copy_2d(b200_ctx* dst_ctx, void* dst, size_t dst_pitch_bytes, b200
  * work queued on waiter sees what producer's kernels stored into waiter's memory. Between processes the same ordering
  * is b200_comm_barrier. */
 int b200_ctx_wait_ctx(b200_ctx* waiter, b200_ctx* producer);
+/* A barrier between one-process-per-GPU ranks that is a kernel on this rank's stream and nothing else: no library
+ * call, no host wait, about one NVLink round trip. peer_flags[p] = rank p's flag array (n_ranks 32-bit words, zero at the
+ * start, peer-mapped: b200_ipc_*), peer_flags[my_rank] the local one; local_epoch = one 32-bit word of this rank's own
+ * memory, zero at the start. Every call adds one to the epoch ON THE DEVICE (a recorded trace advances on every
+ * replay), stores it with release semantics into word my_rank of every rank's array and waits, with acquire loads and
+ * the bounded-wait rule of every kernel here, until its own array shows that epoch in every word. All ranks must call
+ * it the same number of times. What was stored into this rank's memory by a peer's kernels queued before the peer's
+ * call is visible to what this rank queues after its own. A wait that runs out raises the status word
+ * (b200_synchronize then returns B200_ERR_DEVICE_TIMEOUT): a peer that left is found out, not waited for forever.
+ * Ranks emulated on ONE GPU must not use it (kernels that wait for each other need GPUs of their own). */
+int b200_peer_barrier(b200_ctx* ctx, void* const* peer_flags, int n_ranks, int my_rank, void* local_epoch, void* stream);
 /* N-split (column parallel) + all-gather. desc describes the LOCAL product C[:, my_rank*N : (my_rank+1)*N] =
  * op(A) . op(B_shard) with N = shard width; desc->C is ignored; desc->ldc = leading dimension of the full gathered C
  * (>= N * n_ranks). peer_c[p] = base of the full C on rank p (peer_c[my_rank] = the local one). Every rank ends up

@@ -46,6 +46,32 @@ def test_wait_that_runs_out_is_reported_and_the_context_recovers(pkg, ctx, strea
     assert mo.rel_frobenius(colsum.float().cpu().numpy(), x.float().cpu().numpy().sum(0)) <= TOL
 
 
+def test_peer_barrier_alone_and_with_an_absent_peer(pkg, ctx, stream):
+    """b200_peer_barrier on one GPU: with one rank it completes at once and advances its epoch on the device; with a
+    second flag array that nobody writes (a peer that never arrives) the wait runs out, the status word is raised and
+    the context stays usable. (Ranks that do arrive are covered by the one-process-per-GPU TP block tests.)"""
+    s = stream.cuda_stream
+    ctx.synchronize(s)
+    mine = torch.zeros(2, dtype=torch.int32, device="cuda")
+    absent = torch.zeros(2, dtype=torch.int32, device="cuda")
+    epoch = torch.zeros(1, dtype=torch.int32, device="cuda")
+    for _ in range(3):
+        ctx.peer_barrier([mine], 0, epoch, stream=s)
+    ctx.synchronize(s)
+    assert int(epoch.item()) == 3 and int(mine[0].item()) == 3
+    ctx.peer_barrier([mine, absent], 0, epoch, stream=s)      # rank 1 never stores into `mine`
+    with pytest.raises(pkg.B200Error) as e:
+        ctx.synchronize(s)
+    assert e.value.code == pkg.capi.ERR_DEVICE_TIMEOUT
+    assert int(absent[0].item()) == 4                         # this rank did publish its epoch to the peer's array
+    ctx.synchronize(s)                                        # reported once, then clear
+    a, b, ref = _operands(256, 256, 512, False, False, 5)
+    c = torch.empty(256, 256, dtype=torch.bfloat16, device="cuda")
+    ctx.gemm(ctx.gemm_desc(a, b, c, 256, 256, 512), s)
+    ctx.synchronize(s)
+    assert _err(c, ref) <= TOL
+
+
 def test_every_plan_gives_the_same_product(pkg, ctx, stream):
     """b200_gemm_plan_query reports the library's own choice; b200_gemm_planned runs any other kernel, tile width,
     slice count and tile order on the same operands."""

@@ -106,6 +106,7 @@ SIGNATURES = {
     "b200_peer_copy_2d": (C.c_int, [C.c_void_p, C.c_void_p, C.c_size_t, C.c_void_p, C.c_void_p, C.c_size_t, C.c_size_t,
                                     C.c_size_t]),
     "b200_ctx_wait_ctx": (C.c_int, [C.c_void_p, C.c_void_p]),
+    "b200_peer_barrier": (C.c_int, [C.c_void_p, C.POINTER(C.c_void_p), C.c_int, C.c_int, C.c_void_p, C.c_void_p]),
     "b200_mc_supported": (C.c_int, [C.c_void_p, C.POINTER(C.c_int)]),
     "b200_mc_alloc": (C.c_int, [C.c_void_p, C.c_size_t, C.POINTER(C.c_void_p), C.POINTER(C.c_void_p), C.POINTER(C.c_void_p)]),
     "b200_mc_free": (C.c_int, [C.c_void_p]),
@@ -537,6 +538,11 @@ class Context:
     def gemm_allgather(self, desc: GemmDesc, peer_c, my_rank: int, stream=None) -> None:
         check(lib().b200_gemm_allgather(self._h, C.byref(desc), self._ptr_array(peer_c), len(peer_c), my_rank,
                                         self._s(stream)))
+
+    def peer_barrier(self, peer_flags, my_rank: int, local_epoch, stream=None) -> None:
+        """A barrier between one-process-per-GPU ranks as one small kernel on the stream (see b200_peer_barrier)."""
+        check(lib().b200_peer_barrier(self._h, self._ptr_array(peer_flags), len(peer_flags), my_rank, C.c_void_p(ptr(local_epoch)),
+                                      self._s(stream)))
 
     def gemm_allgather_mc(self, desc: GemmDesc, mc_c, n_ranks: int, my_rank: int, *, use_multimem=True, stream=None) -> None:
         """The fused all-gather with one multicast destination (see b200_gemm_allgather_mc)."""

@@ -16,6 +16,7 @@
 #include <cstring>
 
 #include "gemm_common.cuh"
+#include "ptx.cuh"
 
 using namespace b200;
 
@@ -102,6 +103,53 @@ int b200_ctx_wait_ctx(b200_ctx* waiter, b200_ctx* producer) {
     DeviceScope scope(waiter->device);
     B200_CUDA_TRY(cudaStreamWaitEvent(waiter->stream, ev, 0));
     B200_CUDA_TRY(cudaEventDestroy(ev));
+    return B200_OK;
+}
+
+namespace {
+struct PeerFlagArrays {
+    unsigned* p[8];
+};
+
+// One CTA, one thread per rank. Thread 0 advances the epoch; thread r publishes it to rank r and then waits for rank r's
+// word in the local array. The fence before the stores orders them behind everything this GPU wrote earlier.
+__global__ void peer_barrier_kernel(PeerFlagArrays flags, int n_ranks, int my_rank, unsigned* local_epoch, int* status) {
+    __shared__ unsigned epoch;
+    if (threadIdx.x == 0) epoch = ++(*local_epoch);
+    __syncthreads();
+    const int r = threadIdx.x;
+    if (r >= n_ranks) return;
+    const unsigned e = epoch;
+    __threadfence_system();
+    asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(flags.p[r] + my_rank), "r"(e) : "memory");
+    const unsigned* mine = flags.p[my_rank] + r;
+    const uint64_t t0 = ptx::globaltimer_ns();
+    unsigned spins = 0;
+    for (;;) {
+        unsigned seen;
+        asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(seen) : "l"(mine) : "memory");
+        if (static_cast<int>(seen - e) >= 0) break;
+        if ((++spins & 0xffu) == 0 && ptx::globaltimer_ns() - t0 > ptx::kWaitLimitNs) {
+            atomicExch(status, 1);
+            break;
+        }
+    }
+}
+}  // namespace
+
+int b200_peer_barrier(b200_ctx* ctx, void* const* peer_flags, int n_ranks, int my_rank, void* local_epoch, void* stream_v) {
+    B200_REQUIRE(ctx && peer_flags && local_epoch, "b200_peer_barrier: NULL argument");
+    B200_REQUIRE(n_ranks >= 1 && n_ranks <= 8, "b200_peer_barrier: n_ranks must be in [1, 8] (got %d)", n_ranks);
+    B200_REQUIRE(my_rank >= 0 && my_rank < n_ranks, "b200_peer_barrier: my_rank %d out of range", my_rank);
+    PeerFlagArrays f{};
+    for (int i = 0; i < n_ranks; ++i) {
+        B200_REQUIRE(peer_flags[i] != nullptr && (reinterpret_cast<uintptr_t>(peer_flags[i]) & 3u) == 0,
+                     "b200_peer_barrier: flag array %d is NULL or not 4-byte aligned", i);
+        f.p[i] = static_cast<unsigned*>(peer_flags[i]);
+    }
+    DeviceScope scope(ctx->device);
+    peer_barrier_kernel<<<1, 32, 0, ctx->pick(stream_v)>>>(f, n_ranks, my_rank, static_cast<unsigned*>(local_epoch), ctx->d_status);
+    B200_CUDA_TRY(cudaGetLastError());
     return B200_OK;
 }
 
