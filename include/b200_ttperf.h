@@ -223,8 +223,9 @@ int b200_gemm_planned(b200_ctx* ctx, const b200_gemm_desc* desc, const b200_gemm
  *            projection (stride_h = 64, stride_s = row length) are both expressible, so no head split/merge copy is needed.
  *   head_dim must be 64 (B200_ERR_UNSUPPORTED otherwise: compose b200_gemm + b200_softmax instead).
  *   lse      fp32 [B, H, S]
- * b200_attention_backward: given dO it writes dQ, dK, dV (bf16, any operand layout). It uses B*H*S*65 floats of
- * context scratch (fp32 dQ accumulators, summed with atomic adds over the key tiles, and the row sums of dO * O).
+ * b200_attention_backward: given dO it writes dQ, dK, dV (bf16, any operand layout). It uses B*H*S*64 + 2*B*H*S' floats
+ * of context scratch (S' = S rounded up to 128): fp32 dQ accumulators, summed with TMA reductions over the key tiles,
+ * and the per-query terms of the pass (lse and the row sums of dO * O, pre-scaled and padded).
  * The _hp forms carry one more bf16 tensor between the passes, o_lo = bf16(O - bf16(O)): what the rounding of O to bf16
  * drops. The backward pass needs the row term rowsum(dO * O); with O known only to bf16 that term is off by up to 2^-9
  * of |dO| |O|, equally for every key of the row, and dQ = dS K (dK = dS^T Q) multiplies that common error with whatever
@@ -250,6 +251,18 @@ int b200_attention_backward_hp(b200_ctx* ctx, const b200_attn_operand* q, const 
                                const b200_attn_operand* d_o, const float* lse, const b200_attn_operand* d_q,
                                const b200_attn_operand* d_k, const b200_attn_operand* d_v, int64_t B, int64_t H, int64_t S,
                                int head_dim, float scale, int causal, void* stream);
+
+/* The backward pass with options. flags = 0 is b200_attention_backward_hp. B200_ATTN_DETERMINISTIC: every key tile
+ * stores its contribution to dQ into a slab of its own instead of adding it to one accumulator with atomic reductions,
+ * and the final kernel sums the slabs in key order: two runs on the same inputs give the same bits (the default sums in
+ * whatever order the key tiles arrive). It needs ceil(S / 128) times the scratch of the accumulator (B*H*S*64 floats per
+ * key tile) and is the slower of the two. */
+#define B200_ATTN_DETERMINISTIC 1u
+int b200_attention_backward_opts(b200_ctx* ctx, const b200_attn_operand* q, const b200_attn_operand* k,
+                                 const b200_attn_operand* v, const b200_attn_operand* o, const b200_attn_operand* o_lo,
+                                 const b200_attn_operand* d_o, const float* lse, const b200_attn_operand* d_q,
+                                 const b200_attn_operand* d_k, const b200_attn_operand* d_v, int64_t B, int64_t H, int64_t S,
+                                 int head_dim, float scale, int causal, unsigned flags, void* stream);
 
 /* ---- row softmax family (traced/ops.hpp:77-81 softmax, :102-106 softmax_backward; py/engine.py:352-384) ----
  * [rows, cols] bf16 matrices, leading dimensions in elements.

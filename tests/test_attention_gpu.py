@@ -83,6 +83,33 @@ def test_attention_on_unpermuted_projection_output(pkg, ctx, B, H, S):
     _run(pkg, ctx, B, H, S, True, "bsd3", seed=S)
 
 
+@pytest.mark.parametrize("B,H,S,causal", [(2, 3, 640, True), (1, 2, 300, False), (1, 1, 100, True)])
+def test_attention_backward_deterministic_option(pkg, ctx, B, H, S, causal):
+    """B200_ATTN_DETERMINISTIC: dQ from per-key-tile slabs summed in key order. Same parity as the default form, and
+    three runs give the same bits (the default form adds the key tiles' contributions in arrival order)."""
+    DT = pkg.DeviceTensor
+    dh = 64
+    q, k, v, d_o = (rnd((B, H, S, dh), 900 + S + i, 1.0) for i in range(4))
+    tq, tk, tv, tdo = (DT.from_numpy(ctx, t) for t in (q, k, v, d_o))
+    to, tdk, tdv = (DT(ctx, (B, H, S, dh)) for _ in range(3))
+    lse = DT(ctx, (B, H, S), pkg.F32)
+    op = lambda t: ctx.attn_operand(t, H * S * dh, S * dh, dh)
+    ctx.attention_forward(op(tq), op(tk), op(tv), op(to), lse, B, H, S, causal=causal)
+    runs = []
+    for _ in range(3):
+        tdq = DT(ctx, (B, H, S, dh))
+        ctx.attention_backward(op(tq), op(tk), op(tv), op(to), op(tdo), lse, op(tdq), op(tdk), op(tdv), B, H, S, causal=causal,
+                               deterministic=True)
+        ctx.synchronize()
+        runs.append(tdq.numpy().copy())
+    assert np.array_equal(runs[0], runs[1]) and np.array_equal(runs[0], runs[2])
+    scale = dh ** -0.5
+    _, p_ref = mo.causal_attention_forward(q, k, v, scale, causal=causal)
+    dq_ref, dk_ref, dv_ref = mo.causal_attention_backward(q, k, v, p_ref, d_o, scale)
+    assert mo.rel_frobenius(runs[0], dq_ref) <= TOL
+    assert mo.rel_frobenius(tdk.numpy(), dk_ref) <= TOL and mo.rel_frobenius(tdv.numpy(), dv_ref) <= TOL
+
+
 def test_attention_large_scores(pkg, ctx):
     # scores of magnitude ~ 8 * 8 * sqrt(64) / 8: the running maximum has to keep exp() in range. The softmax is then
     # nearly one-hot, dS = P * (dP - sum(dP * P)) is the small remainder of a cancellation, and the bf16 storage of P and

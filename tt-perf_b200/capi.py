@@ -45,6 +45,7 @@ class GemmDesc(C.Structure):
     ]
 
 
+ATTN_DETERMINISTIC = 1
 KERNEL_SIMT, KERNEL_TCGEN05, KERNEL_TCGEN05_PAIR = 0, 1, 2
 
 
@@ -136,6 +137,9 @@ SIGNATURES = {
     "b200_attention_backward_hp": (C.c_int, [C.c_void_p] + [C.POINTER(AttnOperand)] * 6 + [C.c_void_p] +
                                    [C.POINTER(AttnOperand)] * 3 + [C.c_int64, C.c_int64, C.c_int64, C.c_int, C.c_float, C.c_int,
                                                                    C.c_void_p]),
+    "b200_attention_backward_opts": (C.c_int, [C.c_void_p] + [C.POINTER(AttnOperand)] * 6 + [C.c_void_p] +
+                                     [C.POINTER(AttnOperand)] * 3 + [C.c_int64, C.c_int64, C.c_int64, C.c_int, C.c_float,
+                                                                     C.c_int, C.c_uint, C.c_void_p]),
     "b200_softmax": (C.c_int, [C.c_void_p, C.c_void_p, C.c_int64, C.c_void_p, C.c_int64, C.c_int64, C.c_int64, C.c_float,
                                C.c_int64, C.c_void_p]),
     "b200_softmax_backward": (C.c_int, [C.c_void_p, C.c_void_p, C.c_int64, C.c_void_p, C.c_int64, C.c_void_p, C.c_int64,
@@ -389,12 +393,13 @@ class Context:
                                               int(causal), self._s(stream)))
 
     def attention_backward(self, q, k, v, o, d_o, lse, d_q, d_k, d_v, B, H, S, *, head_dim=64, scale=None, causal=True,
-                           o_lo=None, stream=None):
+                           o_lo=None, deterministic=False, stream=None):
+        """deterministic=True: dQ summed over the key tiles in key order (B200_ATTN_DETERMINISTIC) instead of by atomics."""
         scale = head_dim ** -0.5 if scale is None else scale
-        check(lib().b200_attention_backward_hp(self._h, C.byref(q), C.byref(k), C.byref(v), C.byref(o),
-                                               C.byref(o_lo) if o_lo is not None else None, C.byref(d_o), ptr(lse),
-                                               C.byref(d_q), C.byref(d_k), C.byref(d_v), B, H, S, head_dim, scale, int(causal),
-                                               self._s(stream)))
+        check(lib().b200_attention_backward_opts(self._h, C.byref(q), C.byref(k), C.byref(v), C.byref(o),
+                                                 C.byref(o_lo) if o_lo is not None else None, C.byref(d_o), ptr(lse),
+                                                 C.byref(d_q), C.byref(d_k), C.byref(d_v), B, H, S, head_dim, scale,
+                                                 int(causal), ATTN_DETERMINISTIC if deterministic else 0, self._s(stream)))
 
     def softmax(self, x, y, rows, cols, *, ldx=None, ldy=None, alpha=1.0, causal_period=0, stream=None):
         check(lib().b200_softmax(self._h, ptr(x), ldx or cols, ptr(y), ldy or cols, rows, cols, alpha, causal_period,

@@ -399,7 +399,8 @@ struct BwdParams {
     const float* lse2;  // [B, H, S_pad]  lse * log2(e); +inf in the padding rows (probability 0)
     const float* dsc;   // [B, H, S_pad]  rowsum(dO * O) * scale; 0 in the padding rows
     int s_pad;          // S rounded up to whole tiles
-    float* dq_acc;      // [B, H, S, 64] fp32, zeroed before the launch
+    float* dq_acc;      // [B, H, S, 64] fp32, zeroed before the launch; or one such slab per key tile (dq_slabs)
+    int dq_slabs;       // non-zero: key tile j stores dQ contributions into slab j (coordinate j * B * H + bh), no reduction
     int* status;
 };
 
@@ -574,8 +575,14 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
             for (int it = 0; it < n_it; ++it) {
                 if (!mbar_wait(dq_staged, it & 1, abort_flag)) break;
                 const int st = it & 1;
-                tma_reduce_add_3d(&tmdQ, sDQ + (st * 2) * DQ_BOX_BYTES, 0, (i0 + it) * BT, bh);
-                tma_reduce_add_3d(&tmdQ, sDQ + (st * 2 + 1) * DQ_BOX_BYTES, 32, (i0 + it) * BT, bh);
+                if (p.dq_slabs) {
+                    const int slab_bh = jt * static_cast<int>(gridDim.x) + bh;
+                    tma_store_3d(&tmdQ, sDQ + (st * 2) * DQ_BOX_BYTES, 0, (i0 + it) * BT, slab_bh);
+                    tma_store_3d(&tmdQ, sDQ + (st * 2 + 1) * DQ_BOX_BYTES, 32, (i0 + it) * BT, slab_bh);
+                } else {
+                    tma_reduce_add_3d(&tmdQ, sDQ + (st * 2) * DQ_BOX_BYTES, 0, (i0 + it) * BT, bh);
+                    tma_reduce_add_3d(&tmdQ, sDQ + (st * 2 + 1) * DQ_BOX_BYTES, 32, (i0 + it) * BT, bh);
+                }
                 tma_store_commit();
                 if (it > 0) {   // the boxes of the tile before have been read: their buffer may be refilled
                     tma_store_wait_read<1>();
@@ -796,17 +803,28 @@ __global__ void attn_stats_kernel(StridedIn o, StridedIn o_lo, StridedIn d_o, co
 }
 
 // fp32 dQ accumulators [B, H, S, 64] -> bf16 in the caller's layout. One thread per 8 elements.
-__global__ void attn_dq_store_kernel(const float* acc, Strided dq, int B, int H, int S) {
+// `slabs` = 0: acc is the accumulator. Otherwise acc holds one slab per key tile and the row's dQ is their sum in key
+// order over the tiles that see the row (all of them, or those up to the row's own tile with the causal mask).
+__global__ void attn_dq_store_kernel(const float* acc, Strided dq, int B, int H, int S, int slabs, int causal) {
     const long long t = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x;
     const long long rowi = t >> 3;
     const int part = static_cast<int>(t & 7);
-    if (rowi >= static_cast<long long>(B) * H * S) return;
+    const long long rows = static_cast<long long>(B) * H * S;
+    if (rowi >= rows) return;
     const int s = static_cast<int>(rowi % S);
     const long long bhh = rowi / S;
     const int h = static_cast<int>(bhh % H);
     const long long b = bhh / H;
-    const float4 a0 = *reinterpret_cast<const float4*>(acc + rowi * DH + part * 8);
-    const float4 a1 = *reinterpret_cast<const float4*>(acc + rowi * DH + part * 8 + 4);
+    float4 a0 = *reinterpret_cast<const float4*>(acc + rowi * DH + part * 8);
+    float4 a1 = *reinterpret_cast<const float4*>(acc + rowi * DH + part * 8 + 4);
+    const int n_slabs = slabs == 0 ? 1 : (causal ? s / BT + 1 : slabs);
+    for (int j = 1; j < n_slabs; ++j) {
+        const float* src = acc + (static_cast<long long>(j) * rows + rowi) * DH + part * 8;
+        const float4 c0 = *reinterpret_cast<const float4*>(src);
+        const float4 c1 = *reinterpret_cast<const float4*>(src + 4);
+        a0.x += c0.x; a0.y += c0.y; a0.z += c0.z; a0.w += c0.w;
+        a1.x += c1.x; a1.y += c1.y; a1.z += c1.z; a1.w += c1.w;
+    }
     *reinterpret_cast<uint4*>(dq.ptr + b * dq.sb + h * dq.sh + s * dq.ss + part * 8) =
         make_uint4(pack_bf16x2(a0.x, a0.y), pack_bf16x2(a0.z, a0.w), pack_bf16x2(a1.x, a1.y), pack_bf16x2(a1.z, a1.w));
 }
@@ -946,7 +964,17 @@ int b200_attention_backward_hp(b200_ctx* ctx, const b200_attn_operand* q, const 
                                const b200_attn_operand* d_o, const float* lse, const b200_attn_operand* d_q,
                                const b200_attn_operand* d_k, const b200_attn_operand* d_v, int64_t B, int64_t H, int64_t S,
                                int head_dim, float scale, int causal, void* stream_v) {
+    return b200_attention_backward_opts(ctx, q, k, v, o, o_lo, d_o, lse, d_q, d_k, d_v, B, H, S, head_dim, scale, causal, 0u,
+                                        stream_v);
+}
+
+int b200_attention_backward_opts(b200_ctx* ctx, const b200_attn_operand* q, const b200_attn_operand* k,
+                                 const b200_attn_operand* v, const b200_attn_operand* o, const b200_attn_operand* o_lo,
+                                 const b200_attn_operand* d_o, const float* lse, const b200_attn_operand* d_q,
+                                 const b200_attn_operand* d_k, const b200_attn_operand* d_v, int64_t B, int64_t H, int64_t S,
+                                 int head_dim, float scale, int causal, unsigned flags, void* stream_v) {
     B200_REQUIRE(ctx != nullptr, "b200_attention_backward: ctx is NULL");
+    B200_REQUIRE((flags & ~B200_ATTN_DETERMINISTIC) == 0, "b200_attention_backward_opts: unknown flags 0x%x", flags);
     int rc = check_geometry(B, H, S, head_dim, scale);
     if (rc != B200_OK) return rc;
     if (B == 0 || H == 0 || S == 0) return B200_OK;
@@ -959,12 +987,14 @@ int b200_attention_backward_hp(b200_ctx* ctx, const b200_attn_operand* q, const 
     DeviceScope scope(ctx->device);
     cudaStream_t stream = ctx->pick(stream_v);
     const size_t rows = static_cast<size_t>(B) * H * S;
-    const size_t acc_bytes = rows * DH * sizeof(float);
+    const int64_t key_tiles = (S + BT - 1) / BT;
+    const bool slabs = (flags & B200_ATTN_DETERMINISTIC) != 0 && key_tiles > 1;
+    const size_t acc_bytes = rows * DH * sizeof(float) * (slabs ? key_tiles : 1);
     const int64_t s_pad = (S + BT - 1) / BT * BT;
     const size_t rows_pad = static_cast<size_t>(B) * H * s_pad;
     if ((rc = ensure_scratch(ctx, acc_bytes + 2 * rows_pad * sizeof(float), stream)) != B200_OK) return rc;
     float* dq_acc = static_cast<float*>(ctx->d_scratch);
-    float* lse2 = dq_acc + rows * DH;   // 16-byte aligned: rows * 64 floats before it, and s_pad is a multiple of 128
+    float* lse2 = dq_acc + acc_bytes / sizeof(float);   // 16-byte aligned: a multiple of 64 floats before it, and s_pad is a multiple of 128
     float* dsc = lse2 + rows_pad;
     CUtensorMap tmQ, tmK, tmV, tmdO;
     if ((rc = make_attn_map(ctx, &tmQ, *q, B, H, S, "q")) != B200_OK) return rc;
@@ -976,7 +1006,7 @@ int b200_attention_backward_hp(b200_ctx* ctx, const b200_attn_operand* q, const 
     {
         // fp32 accumulators [B*H, S, 64] as boxes of [128 rows x 32 columns] (128-byte rows, swizzled like the boxes in
         // shared memory); a box that reaches beyond row S of its (batch, head) slab is clipped there
-        cuuint64_t dims[3] = {DH, static_cast<cuuint64_t>(S), static_cast<cuuint64_t>(B * H)};
+        cuuint64_t dims[3] = {DH, static_cast<cuuint64_t>(S), static_cast<cuuint64_t>(B * H * (slabs ? key_tiles : 1))};
         cuuint64_t strides[2] = {DH * sizeof(float), static_cast<cuuint64_t>(S) * DH * sizeof(float)};
         cuuint32_t box[3] = {32, BT, 1};
         cuuint32_t estr[3] = {1, 1, 1};
@@ -985,7 +1015,9 @@ int b200_attention_backward_hp(b200_ctx* ctx, const b200_attn_operand* q, const 
                                        CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
         if (r != CUDA_SUCCESS) return fail(B200_ERR_CUDA, "cuTensorMapEncodeTiled failed (%d) for the dQ accumulators", static_cast<int>(r));
     }
-    B200_CUDA_TRY(cudaMemsetAsync(dq_acc, 0, acc_bytes, stream));
+    // With the causal mask key tile j never writes the rows above its own tile in slab j, and the final sum never reads
+    // them; every other part of every slab is stored to. The accumulator of the default form starts at zero.
+    if (!slabs) B200_CUDA_TRY(cudaMemsetAsync(dq_acc, 0, acc_bytes, stream));
     const unsigned blocks = static_cast<unsigned>((rows * 8 + 255) / 256);
     const unsigned stat_blocks = static_cast<unsigned>((rows_pad * 8 + 255) / 256);
     attn_stats_kernel<<<stat_blocks, 256, 0, stream>>>(as_in(o), o_lo != nullptr ? as_in(o_lo) : StridedIn{nullptr, 0, 0, 0}, as_in(d_o),
@@ -1001,6 +1033,7 @@ int b200_attention_backward_hp(b200_ctx* ctx, const b200_attn_operand* q, const 
     p.dsc = dsc;
     p.s_pad = static_cast<int>(s_pad);
     p.dq_acc = dq_acc;
+    p.dq_slabs = slabs ? 1 : 0;
     p.status = ctx->d_status;
     static bool configured[64] = {};
     if ((rc = configure_once(attn_bwd_kernel, BWD_SMEM, configured)) != B200_OK) return rc;
@@ -1008,7 +1041,7 @@ int b200_attention_backward_hp(b200_ctx* ctx, const b200_attn_operand* q, const 
     attn_bwd_kernel<<<grid, BWD_THREADS, BWD_SMEM, stream>>>(tmQ, tmK, tmV, tmdO, tmdQ, p);
     B200_CUDA_TRY(cudaGetLastError());
     attn_dq_store_kernel<<<blocks, 256, 0, stream>>>(dq_acc, as_out(d_q), static_cast<int>(B), static_cast<int>(H),
-                                                     static_cast<int>(S));
+                                                     static_cast<int>(S), slabs ? static_cast<int>(key_tiles) : 0, causal != 0);
     B200_CUDA_TRY(cudaGetLastError());
     return B200_OK;
 }
