@@ -66,11 +66,6 @@ __device__ __forceinline__ float ex2(float x) {
     return y;
 }
 
-template <int THREADS>
-__device__ __forceinline__ void compute_warps_sync() {
-    asm volatile("bar.sync 1, %0;" ::"n"(THREADS) : "memory");
-}
-
 // Byte offset of the 16-byte unit `unit` (0..15, i.e. 8 bf16 columns each) of row `r` inside a [128 x 128] bf16 tile
 // kept as two 128-byte-swizzled slabs of 64 columns.
 __device__ __forceinline__ uint32_t pt_offset(int r, int unit) {
