@@ -343,6 +343,14 @@ int b200_binary(b200_ctx* ctx, int op, const void* a, const int64_t a_shape[4], 
 typedef enum b200_reduce_op { B200_R_SUM = 0, B200_R_MEAN = 1, B200_R_MAX = 2 } b200_reduce_op;
 int b200_reduce(b200_ctx* ctx, int op, const void* x, int64_t outer, int64_t R, int64_t inner, void* y, void* stream);
 
+/* dx = dy * GELU'(x_pre) over a contiguous bf16 [rows, cols] tensor (ttnn::gelu_bw(dy, x, "none"), traced/ops.hpp:96-99)
+ * and, when dx_colsum is not NULL, the column sums of the stored dx (bf16 [cols]) from the same pass: dx is the dY of the
+ * Linear layer in front of the GELU and its column sums are that layer's bias gradient (traced/nn.hpp:81). The result
+ * equals b200_binary(GELU_BW) followed by b200_reduce(SUM) bit for bit in dx; the sums are taken over the rounded dx in
+ * fp32 and rounded once. Uses at most 256 fp32 words of context scratch per column. */
+int b200_gelu_backward(b200_ctx* ctx, const void* dy, const void* x_pre, void* dx, void* dx_colsum, int64_t rows,
+                       int64_t cols, void* stream);
+
 /* 8-bit operands for b200_gemm with ab_dtype = B200_FP8_E4M3.
  * b200_absmax: out_f32[0] = max |x| over n bf16 elements (device scalar, overwritten).
  * b200_quantize_fp8: y[i] = e4m3(x[i] * scale), saturating at +-448; a caller picks scale = 448 / absmax. */

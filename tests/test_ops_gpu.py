@@ -145,6 +145,23 @@ def test_relu_and_gelu_backward(pkg, ctx, DT):
     assert mo.rel_frobenius(got, mo.gelu_backward(dy, x)) <= TOL
 
 
+@pytest.mark.parametrize("rows,cols", [(50, 72), (1, 8), (333, 3072), (4096, 1600), (37, 10), (8192, 768)])
+def test_gelu_backward_with_column_sums(pkg, ctx, DT, rows, cols):
+    """One pass writes dx and the bias gradient of the Linear layer in front of the GELU: dx must equal the separate
+    kernel's bit for bit, the sums must be those of the stored dx."""
+    x, dy = rnd((rows, cols), 53), rnd((rows, cols), 54)
+    xd, dyd = DT.from_numpy(ctx, x), DT.from_numpy(ctx, dy)
+    plain = pkg.nn.gelu_backward(ctx, dyd, xd).numpy()
+    dx, colsum = pkg.nn.gelu_backward(ctx, dyd, xd, want_colsum=True)
+    np.testing.assert_array_equal(dx.numpy(), plain)
+    assert mo.rel_frobenius(plain, mo.gelu_backward(dy, x)) <= TOL
+    want = plain.astype(np.float64).sum(axis=0)
+    assert mo.rel_frobenius(colsum.numpy(), want) <= 4e-3   # one bf16 rounding of an fp32 sum
+    # twice in a row: the ticket counters are back at zero
+    dx2, colsum2 = pkg.nn.gelu_backward(ctx, dyd, xd, want_colsum=True)
+    np.testing.assert_array_equal(colsum2.numpy(), colsum.numpy())
+
+
 @pytest.mark.parametrize("outer,R,inner", [(1, 1024, 128), (1, 64, 10), (16, 768, 1), (3, 50, 7), (1, 8192, 768), (4, 9, 1), (1, 524288, 1),
                                             (5, 100003, 1)])
 def test_reductions(pkg, ctx, DT, outer, R, inner):

@@ -168,6 +168,7 @@ SIGNATURES = {
     "b200_binary": (C.c_int, [C.c_void_p, C.c_int, C.c_void_p, C.POINTER(C.c_int64), C.c_void_p, C.POINTER(C.c_int64),
                               C.c_void_p, C.c_void_p]),
     "b200_reduce": (C.c_int, [C.c_void_p, C.c_int, C.c_void_p, C.c_int64, C.c_int64, C.c_int64, C.c_void_p, C.c_void_p]),
+    "b200_gelu_backward": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_int64, C.c_int64, C.c_void_p]),
     "b200_absmax": (C.c_int, [C.c_void_p, C.c_void_p, C.c_int64, C.c_void_p, C.c_void_p]),
     "b200_quantize_fp8": (C.c_int, [C.c_void_p, C.c_void_p, C.c_int64, C.c_float, C.c_void_p, C.c_void_p]),
     "b200_quantize_fp8_transposed": (C.c_int, [C.c_void_p, C.c_void_p, C.c_int64, C.c_int64, C.c_int64, C.c_float, C.c_void_p,
@@ -465,6 +466,10 @@ class Context:
 
     def reduce(self, op, x, outer, R, inner, y, *, stream=None):
         check(lib().b200_reduce(self._h, op, ptr(x), outer, R, inner, ptr(y), self._s(stream)))
+
+    def gelu_backward(self, dy, x_pre, dx, dx_colsum, rows, cols, *, stream=None):
+        """dx = dy * GELU'(x_pre) over bf16 [rows, cols]; dx_colsum (bf16 [cols], optional) = column sums of dx."""
+        check(lib().b200_gelu_backward(self._h, ptr(dy), ptr(x_pre), ptr(dx), ptr(dx_colsum), rows, cols, self._s(stream)))
 
     def absmax(self, x, n, out_f32, *, stream=None):
         """out_f32[0] = max |x| over n bf16 elements."""

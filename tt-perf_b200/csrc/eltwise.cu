@@ -461,10 +461,15 @@ __global__ void __launch_bounds__(kThreads) reduce_cols_kernel(const __nv_bfloat
 // part[outer][row_block][inner]; the CTA that finishes last for a column block (a ticket counter tells it) combines the
 // partials, scales, rounds to bf16 and puts the counter back to zero. No zero-fill, no atomics on the data, no cast pass,
 // and the result does not depend on the order in which the CTAs ran.
-template <int VEC>
-__global__ void __launch_bounds__(kThreads) reduce_cols_ticket_kernel(const __nv_bfloat16* x, float* part, unsigned* tickets,
+// GELU_BW = true (VEC = 8, sum): the tensor that is reduced does not exist yet. x holds the pre-activations, dy the
+// gradient behind the GELU; the kernel writes dx = dy * GELU'(x) (bf16) and reduces the rounded dx on the way, so that the
+// bias gradient of the Linear layer in front of the GELU costs no second pass over dx.
+template <int VEC, bool GELU_BW = false>
+__global__ void __launch_bounds__(kThreads, 4) reduce_cols_ticket_kernel(const __nv_bfloat16* x, float* part, unsigned* tickets,
                                                                        __nv_bfloat16* y, long long R, long long inner, int op,
-                                                                       long long rows_per_cta, float scale) {
+                                                                       long long rows_per_cta, float scale,
+                                                                       const __nv_bfloat16* dy = nullptr,
+                                                                       __nv_bfloat16* dx = nullptr) {
     __shared__ float sh[8][32][VEC + 1];
     __shared__ int is_last;
     const long long o = blockIdx.z;
@@ -478,6 +483,35 @@ __global__ void __launch_bounds__(kThreads) reduce_cols_ticket_kernel(const __nv
     if (c < inner) {
         const __nv_bfloat16* base = x + o * R * inner + c;
         long long r = r0 + sub;
+        if (GELU_BW) {
+            const __nv_bfloat16* gbase = dy + o * R * inner + c;
+            __nv_bfloat16* obase = dx + o * R * inner + c;
+            auto one = [&](const uint4& xv, const uint4& gv, long long row) {
+                float fx[8], fg[8];
+                unpack8(xv, fx);
+                unpack8(gv, fg);
+#pragma unroll
+                for (int k = 0; k < 8; ++k) fg[k] *= gelu_exact_grad(fx[k]);
+                const uint4 packed = pack8(fg);
+                *reinterpret_cast<uint4*>(obase + row * inner) = packed;
+                unpack8(packed, fg);  // the sum of the stored values, as a reduction of dx would see them
+#pragma unroll
+                for (int k = 0; k < 8; ++k) acc[k] += fg[k];
+            };
+            for (; r + 8 < r1; r += 16) {  // two row pairs in flight per thread, four CTAs per SM
+                uint4 xv[2], gv[2];
+#pragma unroll
+                for (int u = 0; u < 2; ++u) {
+                    xv[u] = *reinterpret_cast<const uint4*>(base + (r + 8 * u) * inner);
+                    gv[u] = *reinterpret_cast<const uint4*>(gbase + (r + 8 * u) * inner);
+                }
+#pragma unroll
+                for (int u = 0; u < 2; ++u) one(xv[u], gv[u], r + 8 * u);
+            }
+            for (; r < r1; r += 8)
+                one(*reinterpret_cast<const uint4*>(base + r * inner), *reinterpret_cast<const uint4*>(gbase + r * inner), r);
+            r = r1;
+        }
         if (VEC == 8) {
             // eight independent 16-byte loads in flight per thread
             for (; r + 56 < r1; r += 64) {
@@ -876,6 +910,41 @@ int b200_reduce(b200_ctx* ctx, int op, const void* x, int64_t outer, int64_t R, 
     else
         reduce_cols_kernel<1><<<grid, kThreads, 0, s>>>(static_cast<const __nv_bfloat16*>(x), acc, R, inner, op, rows_per);
     cast_f32_to_bf16_kernel<<<grid_for(ctx, outs), kThreads, 0, s>>>(acc, static_cast<__nv_bfloat16*>(y), outs, scale);
+    B200_CUDA_TRY(cudaGetLastError());
+    return B200_OK;
+}
+
+int b200_gelu_backward(b200_ctx* ctx, const void* dy, const void* x_pre, void* dx, void* dx_colsum, int64_t rows,
+                       int64_t cols, void* stream) {
+    B200_REQUIRE(ctx != nullptr, "b200_gelu_backward: ctx is NULL");
+    B200_REQUIRE(rows >= 0 && cols >= 0, "b200_gelu_backward: bad sizes (rows %lld, cols %lld)", (long long)rows, (long long)cols);
+    DeviceScope scope(ctx->device);
+    cudaStream_t s = ctx->pick(stream);
+    if (rows == 0 || cols == 0) {
+        if (dx_colsum != nullptr && cols > 0) B200_CUDA_TRY(cudaMemsetAsync(dx_colsum, 0, sizeof(__nv_bfloat16) * cols, s));
+        return B200_OK;
+    }
+    B200_REQUIRE(dy && x_pre && dx, "b200_gelu_backward: NULL buffer");
+    const long long col_blocks = (cols / 8 + 31) / 32;
+    const bool fused = dx_colsum != nullptr && cols % 8 == 0 && al16(dy) && al16(x_pre) && al16(dx) && col_blocks < kTicketCount;
+    if (!fused) {
+        const int64_t shape[4] = {1, 1, rows, cols};
+        int rc = b200_binary(ctx, B_GELU_BW, dy, shape, x_pre, shape, dx, stream);
+        if (rc != B200_OK || dx_colsum == nullptr) return rc;
+        return b200_reduce(ctx, R_SUM, dx, 1, rows, cols, dx_colsum, stream);
+    }
+    // enough CTAs for four per SM, slabs of at least 32 rows
+    long long row_blocks = std::max<long long>(1, std::min<long long>(std::min<long long>((rows + 31) / 32, 256),
+                                                                       (ctx->sm_count * 4ll) / col_blocks));
+    const long long rows_per = (rows + row_blocks - 1) / row_blocks;
+    row_blocks = (rows + rows_per - 1) / rows_per;
+    int rc = ensure_scratch(ctx, static_cast<size_t>(cols) * row_blocks * sizeof(float), s);
+    if (rc != B200_OK) return rc;
+    dim3 grid(static_cast<unsigned>(col_blocks), static_cast<unsigned>(row_blocks), 1);
+    reduce_cols_ticket_kernel<8, true><<<grid, kThreads, 0, s>>>(
+        static_cast<const __nv_bfloat16*>(x_pre), static_cast<float*>(ctx->d_scratch), ctx_tickets(ctx),
+        static_cast<__nv_bfloat16*>(dx_colsum), rows, cols, R_SUM, rows_per, 1.0f, static_cast<const __nv_bfloat16*>(dy),
+        static_cast<__nv_bfloat16*>(dx));
     B200_CUDA_TRY(cudaGetLastError());
     return B200_OK;
 }

@@ -92,6 +92,8 @@ def main() -> None:
         case("bias add [16T, 768] + [1, 768]", T16 * D * 4, lambda: ctx.binary(c.B_ADD, xl, (T16, D), gam, (1, D), yl))
         case("gelu [16T, 768]", T16 * D * 4, lambda: ctx.unary(c.U_GELU, xl, yl, T16 * D))
         case("gelu_bw [16T, 768]", T16 * D * 6, lambda: ctx.binary(c.B_GELU_BW, dyl, (T16 * D,), xl, (T16 * D,), yl))
+        case("gelu_bw + column sums of dx [16T, 768] (one pass)", T16 * D * 6,
+             lambda: ctx.gelu_backward(dyl, xl, yl, gam, T16, D))
         case("column sum (bias grad) [16T, 768] -> [768]", T16 * D * 2, lambda: ctx.reduce(c.R_SUM, xl, 1, T16, D, gam))
         case("mean over all [16T*768] -> [1]", T16 * D * 2, lambda: ctx.reduce(c.R_MEAN, xl, 1, T16 * D, 1, gam))
         xh = rand((16 * B, S, H, 64))

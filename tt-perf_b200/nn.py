@@ -107,10 +107,17 @@ def relu_backward(ctx, d_y, x_pre, *, stream=None) -> DeviceTensor:
     return out
 
 
-def gelu_backward(ctx, d_y, x_pre, *, stream=None) -> DeviceTensor:
+def gelu_backward(ctx, d_y, x_pre, *, want_colsum=False, stream=None):
+    """dx = dy * GELU'(x_pre). want_colsum also returns the column sums of dx over all leading positions (bf16 [cols]):
+    dx is the dY of the Linear layer in front of the GELU, so they are that layer's bias gradient, from the same pass."""
     out = DeviceTensor(ctx, d_y.shape, BF16)
-    ctx.binary(capi.B_GELU_BW, d_y, (d_y.numel,), x_pre, (x_pre.numel,), out, stream=stream)
-    return out
+    if not want_colsum:
+        ctx.binary(capi.B_GELU_BW, d_y, (d_y.numel,), x_pre, (x_pre.numel,), out, stream=stream)
+        return out
+    cols = d_y.shape[-1]
+    colsum = DeviceTensor(ctx, (cols,), BF16)
+    ctx.gelu_backward(d_y, x_pre, out, colsum, _rows(d_y), cols, stream=stream)
+    return out, colsum
 
 
 def add(ctx, a, b, *, stream=None) -> DeviceTensor:
@@ -351,8 +358,8 @@ def transformer_block_backward(ctx, d_out, w, cache, heads, *, d_out_colsum=None
     d_h1g, g["w2"], g["b2"] = linear_backward(ctx, c["h1g"], w["w2"], d_out, need_db=d_out_colsum is None, stream=stream)
     if d_out_colsum is not None:
         g["b2"] = d_out_colsum
-    d_h1 = gelu_backward(ctx, d_h1g, c["h1"], stream=stream)
-    d_ln2, g["w1"], g["b1"] = linear_backward(ctx, c["ln2"], w["w1"], d_h1, stream=stream)
+    d_h1, g["b1"] = gelu_backward(ctx, d_h1g, c["h1"], want_colsum=True, stream=stream)  # b1's gradient = column sums of d_h1
+    d_ln2, g["w1"], _ = linear_backward(ctx, c["ln2"], w["w1"], d_h1, need_db=False, stream=stream)
     # d_res1 is the dY of the attention output projection: its column sums (from the same kernel) are that bias gradient
     d_res1, g["ln2_g"], g["ln2_b"], g["bo"] = layernorm_backward(ctx, d_ln2, c["res1"], w["ln2_g"], c["mean2"], c["rstd2"],
                                                                   upstream=d_out, want_colsum=True, stream=stream)

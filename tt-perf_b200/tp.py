@@ -263,9 +263,9 @@ class TPBlockRank:
         g["w2"] = nn.matmul(ctx, dy2, h1g2, True, False)                             # [D, Fr]
         g["b2"] = DeviceTensor(ctx, (D,), BF16)
         ctx.reduce(capi.R_SUM, dy2, 1, T, D, g["b2"])
-        d_h1 = nn.gelu_backward(ctx, d_h1g, c["h1"])
+        d_h1, g["b1"] = nn.gelu_backward(ctx, d_h1g, c["h1"], want_colsum=True)      # b1's gradient from the same pass
         ln2 = self._view("ln2_full", self.rank, T, shape=(B, S, D))
-        _, g["w1"], g["b1"] = nn.linear_backward(ctx, ln2, w["w1"], d_h1, need_dx=False)
+        _, g["w1"], _ = nn.linear_backward(ctx, ln2, w["w1"], d_h1, need_dx=False, need_db=False)
         self._scatter_partials("slots0", d_h1, w["w1"], D, self.Fr, transpose_b=False, lda=self.Fr, ldb=D)
         yield
         d_ln2 = DeviceTensor(ctx, (Tr, D), BF16)
