@@ -322,7 +322,7 @@ def gpt2_train_bench(steps: int = 10, warmup: int = 3, device: int = 0, rank: in
 
     One GPU: the whole step is recorded once as a trace (CUDA graph) and replayed, as the reference's traced executor
     does (bench/autograd/bench_gpt2_full.cpp). N GPUs (data parallel, weak scaling): each rank replays forward +
-    backward on its own batch as a chain of traces (LM head, then groups of four blocks); every trace packs its
+    backward on its own batch as a chain of traces (LM head, then groups of two blocks, then the embeddings); every trace packs its
     gradients into a bucket that NCCL (b200_comm_allreduce on `comm`, a communicator of this context) averages over
     the ranks on a second stream while the next trace runs; a last trace applies Adam from the buckets. Returns
     whole-job tokens/s and ms/step."""
@@ -363,13 +363,15 @@ def gpt2_train_bench(steps: int = 10, warmup: int = 3, device: int = 0, rank: in
         traces = [tid]
     else:
         import torch
-        # The backward pass is recorded as several traces (LM head, then groups of four blocks, the last one with the
+        # The backward pass is recorded as several traces (LM head, then groups of two blocks, the last one with the
         # embeddings). Each trace ends by packing its gradients into its own bf16 / fp32 bucket; while the next trace
         # runs on the compute stream, the bucket is averaged over the ranks by NCCL on a second stream (events order
         # the two, no host synchronisation). A last trace applies Adam straight from the buckets.
         c = pkg.capi
         specs = []
-        model.forward_backward(idd, tgd, pos, segment_hook=lambda pairs: specs.append([(g.numel, g.dtype) for _, g in pairs]))
+        SEG = 2   # blocks per backward trace: the last block trace's bucket (all that no later trace hides) stays small
+        model.forward_backward(idd, tgd, pos, blocks_per_segment=SEG,
+                               segment_hook=lambda pairs: specs.append([(g.numel, g.dtype) for _, g in pairs]))
         ctx.synchronize()
         buckets = []
         for spec in specs:
@@ -400,12 +402,25 @@ def gpt2_train_bench(steps: int = 10, warmup: int = 3, device: int = 0, rank: in
             if len(seg_traces) < len(specs):
                 cur[0] = ctx.trace_begin()
 
-        loss, grads = model.forward_backward(idd, tgd, pos, segment_hook=pack_and_cut)
+        loss, grads = model.forward_backward(idd, tgd, pos, blocks_per_segment=SEG, segment_hook=pack_and_cut)
         bf, f32 = model._flat(grads)
+        # The last bucket holds the token-embedding gradient (fp32, 154 MB), which exists only when the backward pass
+        # ends: nothing is left to hide its all-reduce under except the optimiser itself. So Adam runs in two parts:
+        # every other parameter as soon as its bucket is averaged, the token embedding after its own all-reduce.
+        tok = model.params["tok_emb"]
+        split_tok = f32[0][0] is tok and sum(1 for _, dt in specs[-1] if dt == pkg.F32) == 1
         t_opt = ctx.trace_begin()
         model.opt[0].step([slice_of[id(prm)] for prm, _ in bf])
-        model.opt[1].step([slice_of[id(prm)] for prm, _ in f32])
+        if split_tok:
+            model.opt[1].step([slice_of[id(prm)] for prm, _ in f32[1:]], indices=range(1, len(f32)))
+        else:
+            model.opt[1].step([slice_of[id(prm)] for prm, _ in f32])
         ctx.trace_end(t_opt)
+        t_opt_tok = None
+        if split_tok:
+            t_opt_tok = ctx.trace_begin()
+            model.opt[1].step([slice_of[id(tok)]], indices=[0], advance=False)
+            ctx.trace_end(t_opt_tok)
         seg_views = []
         for flat_bf, flat_f32, _, n_bf, n_f32 in buckets:
             v = []
@@ -417,15 +432,25 @@ def gpt2_train_bench(steps: int = 10, warmup: int = 3, device: int = 0, rank: in
         comp, comm_st = torch.cuda.Stream(), torch.cuda.Stream()
 
         def dp_step():
-            for tid, views in zip(seg_traces, seg_views):
+            rest_done = None
+            for k, (tid, views) in enumerate(zip(seg_traces, seg_views)):
                 ctx.trace_execute_on(tid, comp.cuda_stream)
                 ev = torch.cuda.Event()
                 ev.record(comp)
                 comm_st.wait_event(ev)                         # this segment's gradients are packed
                 for ptr_, count, dtype in views:
+                    if t_opt_tok is not None and k == len(seg_traces) - 1 and dtype == pkg.F32:
+                        rest_done = torch.cuda.Event()         # everything but the token embedding is averaged
+                        rest_done.record(comm_st)
                     comm.allreduce(ptr_, count, dtype, c.COMM_AVG, stream=comm_st.cuda_stream)
-            comp.wait_stream(comm_st)                          # every bucket is averaged before Adam reads it
-            ctx.trace_execute_on(t_opt, comp.cuda_stream)
+            if rest_done is not None:
+                comp.wait_event(rest_done)
+                ctx.trace_execute_on(t_opt, comp.cuda_stream)  # runs beside the last all-reduce
+                comp.wait_stream(comm_st)
+                ctx.trace_execute_on(t_opt_tok, comp.cuda_stream)
+            else:
+                comp.wait_stream(comm_st)                      # every bucket is averaged before Adam reads it
+                ctx.trace_execute_on(t_opt, comp.cuda_stream)
 
         def rank_barrier():
             comp.synchronize()
@@ -443,8 +468,9 @@ def gpt2_train_bench(steps: int = 10, warmup: int = 3, device: int = 0, rank: in
         comp.synchronize()
         dt = max_over_ranks(pkg, comm, e0.elapsed_time(e1) / steps) * 1e-3
         executor = (f"{len(seg_traces)} backward traces on a compute stream, each followed by the NCCL all-reduce of its gradient "
-                    "bucket on a second stream (overlapping the next trace), then an Adam trace")
-        traces = seg_traces + [t_opt]
+                    "bucket on a second stream (overlapping the next trace), then an Adam trace"
+                    + (" beside the all-reduce of the token-embedding gradient and a second one for that parameter" if t_opt_tok is not None else ""))
+        traces = seg_traces + [t_opt] + ([t_opt_tok] if t_opt_tok is not None else [])
     final = float(loss.numpy()[0])
     for t in traces:
         ctx.trace_release(t)

@@ -262,6 +262,29 @@ def test_adam_two_steps_golden_and_validation(pkg, ctx, DT):
             pkg.nn.Adam(ctx, [p], **bad)
 
 
+def test_adam_step_in_parts_equals_one_step(pkg, ctx, DT):
+    """A step applied to parameter subsets (the second part without advancing the step number) leaves parameters and
+    moments bit for bit as the undivided step does, over two steps."""
+    rng = np.random.default_rng(77)
+    shapes = [(300, 40), (17,), (64, 64)]
+    w0 = [rng.standard_normal(sh).astype(np.float32) for sh in shapes]
+    gs = [[rng.standard_normal(sh).astype(np.float32) for sh in shapes] for _ in range(2)]
+    whole = [DT.from_numpy(ctx, w, pkg.F32) for w in w0]
+    parts = [DT.from_numpy(ctx, w, pkg.F32) for w in w0]
+    opt_w = pkg.nn.Adam(ctx, whole, lr=1e-2, betas=(0.9, 0.95))
+    opt_p = pkg.nn.Adam(ctx, parts, lr=1e-2, betas=(0.9, 0.95))
+    for g in gs:
+        gd = [DT.from_numpy(ctx, x, pkg.F32) for x in g]
+        opt_w.step(gd)
+        opt_p.step(gd[1:], indices=range(1, 3))
+        opt_p.step(gd[:1], indices=[0], advance=False)
+    assert opt_p.t == opt_w.t == 2
+    for a, b in zip(whole, parts):
+        np.testing.assert_array_equal(a.numpy(), b.numpy())
+    for a, b in zip(opt_w.m + opt_w.v, opt_p.m + opt_p.v):
+        np.testing.assert_array_equal(a.numpy(), b.numpy())
+
+
 @pytest.mark.parametrize("rows,cols", [(64, 768), (33, 520), (17, 100), (40, 1024), (9, 1600), (5, 2304)])
 def test_layernorm_with_fused_residual_add(pkg, ctx, DT, rows, cols):
     """b200_add_layernorm_forward / b200_layernorm_backward_add against the separate oracle steps: the sum is rounded to

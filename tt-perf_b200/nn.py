@@ -240,10 +240,17 @@ class Adam:
         """Steps taken so far (read back from the device)."""
         return int(self.state.numpy().view(np.int64)[0])
 
-    def step(self, grads, *, stream=None) -> None:
-        self.ctx.adam_step_device(self.params, grads, self.m, self.v, [p.numel for p in self.params], self.state,
-                                  lr=self.lr, beta1=self.beta1, beta2=self.beta2, eps=self.eps,
-                                  p_dtype=self.params[0].dtype, g_dtype=grads[0].dtype, shadows=self.shadows, stream=stream)
+    def step(self, grads, *, indices=None, advance=True, stream=None) -> None:
+        """One update. `indices` restricts it to those parameters (grads then lines up with indices): a step may be
+        applied in several parts, e.g. while the gradients of the remaining parameters are still being averaged over
+        the ranks; only the first part advances the step number (advance=False for the others)."""
+        idx = list(range(len(self.params))) if indices is None else list(indices)
+        pick = lambda items: [items[i] for i in idx]
+        params = pick(self.params)
+        self.ctx.adam_step_device(params, grads, pick(self.m), pick(self.v), [p.numel for p in params], self.state,
+                                  advance=advance, lr=self.lr, beta1=self.beta1, beta2=self.beta2, eps=self.eps,
+                                  p_dtype=params[0].dtype, g_dtype=grads[0].dtype,
+                                  shadows=pick(self.shadows) if self.shadows else None, stream=stream)
 
 
 # ---------------------------------------------------------------------------------------------------------------
@@ -509,7 +516,7 @@ class GPT2:
         Returns (loss fp32 scalar tensor, grads structured like params).
         segment_hook(pairs), when given, is called with the (parameter, gradient) pairs that have just become final:
         after the LM head and final LayerNorm, after every `blocks_per_segment` blocks of the backward pass, and at the
-        end with the remaining blocks and the embeddings. A data-parallel driver ends a trace there and starts the
+        end with the remaining blocks (none when the count divides the depth) and the embeddings. A data-parallel driver ends a trace there and starts the
         all-reduce of those gradients while the rest of the backward pass runs."""
         ctx, p = self.ctx, self.params
         b = ids.numel // self.S
@@ -549,7 +556,7 @@ class GPT2:
                                                                          d_out_colsum=d_x_cs, want_dx_colsum=True, stream=stream)
             pending += [(p["blocks"][i][k], grads["blocks"][i][k]) for k in BLOCK_KEYS]
             done += 1
-            if segment_hook and done % blocks_per_segment == 0 and i > 0:
+            if segment_hook and done % blocks_per_segment == 0:
                 segment_hook(pending)
                 pending = []
         grads["tok_emb"] = DeviceTensor(ctx, (self.V, self.D), F32)
