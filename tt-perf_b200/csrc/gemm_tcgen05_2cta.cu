@@ -103,6 +103,7 @@ gemm_tcgen05_2cta_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_c
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(tmem_empty_bar + 2);
     volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
     volatile int* last_flag = abort_flag + 1;      // split-K: this CTA drew the last ticket of its tile
+    uint64_t* part_bar = reinterpret_cast<uint64_t*>(bar_base + 160);  // two K slices: the other slice's sums have landed in smem
 
     const int warp = threadIdx.x >> 5;
     const int lane = threadIdx.x & 31;
@@ -122,6 +123,7 @@ gemm_tcgen05_2cta_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_c
             mbar_init(&tmem_full_bar[a], 1);
             mbar_init(&tmem_empty_bar[a], 2 * EPI_WARPS);  // every epilogue warp of both CTAs
         }
+        mbar_init(part_bar, 1);
         *abort_flag = 0;
         mbar_fence_init();
     }
@@ -272,6 +274,7 @@ gemm_tcgen05_2cta_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_c
                 row_coord -= dst_first * p.scatter_rows;
             }
             bool finish = true;  // this CTA writes C for the tile
+            bool staged_partner = false;
             // Partial sums live in a layout of their own, [slice][tile][CTA of the pair][32-column chunk][vector j]
             // [thread]: the k-th 16-byte vector of a thread's 32 columns sits next to the same vector of its
             // neighbours, so a warp writes and reads 512 contiguous bytes per instruction (row-major fp32 would cost
@@ -307,14 +310,35 @@ gemm_tcgen05_2cta_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_c
                 }
                 __threadfence();
                 epilogue_warps_sync();
+                // With two slices and no further work item for this CTA the operand ring is idle: the finishing slice
+                // has the other slice's 128 KB of sums copied into it in bulk and adds them from shared memory. Fetched
+                // with plain loads, 8 at a time per thread, the same sums cost eight L2 round trips in a row.
+                staged_partner = p.k_splits == 2 && w + num_clusters >= p.total_work;
                 if (threadIdx.x == 64) {
                     const unsigned t = atomicAdd(&p.tickets[it.tile * 2 + static_cast<int>(rank)], 1u);
                     *last_flag = (t == static_cast<unsigned>(p.k_splits - 1)) ? 1 : 0;
-                    if (*last_flag) p.tickets[it.tile * 2 + static_cast<int>(rank)] = 0u;  // ready for the next launch
+                    if (*last_flag) {
+                        p.tickets[it.tile * 2 + static_cast<int>(rank)] = 0u;  // ready for the next launch
+                        if (staged_partner) {
+                            __threadfence();
+                            fence_proxy_async_all();  // the other slice's stores (generic proxy) before this bulk read
+                            constexpr uint32_t kPiece = 32768;
+                            const char* src = reinterpret_cast<const char*>(part_at(1 - it.split) - ethread);
+                            mbar_arrive_expect_tx(part_bar, static_cast<uint32_t>(cta_floats * sizeof(float)));
+                            for (uint32_t off = 0; off < cta_floats * sizeof(float); off += kPiece)
+                                bulk_load_g2s(smem + off, src + off, kPiece, part_bar);
+                        }
+                    }
                 }
                 epilogue_warps_sync();
                 finish = *last_flag != 0;
-                if (finish) __threadfence();
+                if (finish) {
+                    __threadfence();
+                    if (staged_partner) {  // all lanes of a warp agree on whether the copy landed
+                        const bool landed = mbar_wait(part_bar, 0, abort_flag);
+                        if (!__all_sync(0xffffffffu, landed)) finish = false;
+                    }
+                }
             }
             if (finish && m_cta < p.M) {  // a CTA whose 128 rows lie entirely below the matrix has nothing to store
 #pragma unroll 1
@@ -338,9 +362,21 @@ gemm_tcgen05_2cta_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_c
                             for (int i = 0; i < 32; ++i)
                                 v[i] = __float_as_uint(__bfloat162float(__float2bfloat16_rn(__uint_as_float(v[i]))));
                         }
-                        if (p.k_splits > 1)
+                        if (staged_partner) {
+                            // two terms: a + b is the same number in either order
+                            const float4* ps = reinterpret_cast<const float4*>(smem) + ((c + h * 32) / 32) * 8 * 128 + ethread;
+#pragma unroll
+                            for (int i = 0; i < 8; ++i) {
+                                const float4 a = ps[i * 128];
+                                v[4 * i] = __float_as_uint(__uint_as_float(v[4 * i]) + a.x);
+                                v[4 * i + 1] = __float_as_uint(__uint_as_float(v[4 * i + 1]) + a.y);
+                                v[4 * i + 2] = __float_as_uint(__uint_as_float(v[4 * i + 2]) + a.z);
+                                v[4 * i + 3] = __float_as_uint(__uint_as_float(v[4 * i + 3]) + a.w);
+                            }
+                        } else if (p.k_splits > 1) {
                             sum_slices_in_order(v, it.split, p.k_splits,
                                                 [&](int sl) { return part_at(sl) + ((c + h * 32) / 32) * 8 * 128; });
+                        }
                         float f[32];
                         epi_apply32(p.epi, v, f, row, nh, p.N);
                         if (p.c_f32) {

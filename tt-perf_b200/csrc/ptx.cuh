@@ -156,6 +156,16 @@ __device__ __forceinline__ void prefetch_tensormap(const CUtensorMap* map) {
 
 // Orders generic-proxy writes to shared memory before later async-proxy (TMA store) reads.
 __device__ __forceinline__ void fence_proxy_async_smem() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
+// Orders this thread's earlier generic-proxy view of memory (global included) before its later async-proxy operations.
+__device__ __forceinline__ void fence_proxy_async_all() { asm volatile("fence.proxy.async;" ::: "memory"); }
+
+// Untiled bulk copy global -> this CTA's shared memory, completion counted in bytes on an mbarrier. Both addresses
+// 16-byte aligned, the size a multiple of 16.
+__device__ __forceinline__ void bulk_load_g2s(void* smem_dst, const void* gsrc, uint32_t bytes, uint64_t* bar) {
+    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(smem_u32(smem_dst)),
+                 "l"(gsrc), "r"(bytes), "r"(smem_u32(bar))
+                 : "memory");
+}
 
 // ----------------------------------------------------------------------------------------------
 // tcgen05 / TMEM
