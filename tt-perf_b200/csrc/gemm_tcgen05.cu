@@ -576,6 +576,20 @@ int split_candidates(const b200_gemm_desc& d, long long tiles, long long slots, 
             for (int c = 0; c < n; ++c) seen |= cand[c] == s;
             if (!seen) cand[n++] = s;
         }
+    } else if (d.split_k == 0 && tiles <= 4 * slots && num_kb >= 64) {
+        // A few rounds of long tiles with the last round partly empty (96 tiles on 74 CTA pairs: two rounds for 1.3
+        // rounds of work): the slice count whose rounds, divided by the slices, waste least.
+        const double whole = static_cast<double>((tiles + slots - 1) / slots);
+        double best = whole * 0.9;  // worth the partial sums only for a tenth or more
+        int pick = 0;
+        for (int s = 2; s <= 6 && num_kb / s >= 32; ++s) {
+            const double eff = static_cast<double>((tiles * s + slots - 1) / slots) / s;
+            if (eff < best - 1e-9) {
+                best = eff;
+                pick = s;
+            }
+        }
+        if (pick > 1) cand[n++] = normalise_splits(pick, num_kb);
     }
     return n;
 }
